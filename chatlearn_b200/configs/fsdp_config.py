@@ -1,0 +1,46 @@
+"""FSDP-style (ZeRO-3) trainer configuration.
+
+Parity: chatlearn/configs/fsdp_config.py:10-52.
+"""
+from dataclasses import dataclass
+
+from .base import BaseConfig, BaseModelConfig
+from .common import PolicyTrainerConfig, RefPolicyConfig
+
+
+@dataclass
+class FSDPConfig(BaseConfig):
+    fsdp_size: int = 1
+    ulysses_sequence_parallel_size: int = 1
+    meta_init: bool = False
+    groupgemm: bool = False
+    use_expandable_segments: bool = False
+
+    def _post_init_impl(self):
+        if isinstance(self, BaseModelConfig) and self.num_gpu:
+            if self.fsdp_size in (-1, 0):
+                self.fsdp_size = self.num_gpu
+            sp = self.ulysses_sequence_parallel_size
+            denom = sp * max(self.num_replica, 1)
+            if self.num_gpu % denom == 0:
+                self.replica_dp_size = self.num_gpu // denom
+
+    def _validate_impl(self):
+        if isinstance(self, BaseModelConfig):
+            assert self.num_gpu > 0, "the FSDP backend needs GPUs (or CPU ranks standing in for them)"
+            sp = self.ulysses_sequence_parallel_size
+            assert self.num_gpu % sp == 0, "num_gpu must be a multiple of ulysses_sequence_parallel_size"
+            assert self.fsdp_size >= 1 and self.num_gpu % self.fsdp_size == 0, \
+                "num_gpu must be a multiple of fsdp_size"
+            assert self.fsdp_size % sp == 0, "fsdp_size must be a multiple of ulysses_sequence_parallel_size"
+
+
+@dataclass
+class FSDPRefPolicyConfig(RefPolicyConfig, FSDPConfig):
+    pass
+
+
+@dataclass
+class FSDPPolicyTrainerConfig(PolicyTrainerConfig, FSDPConfig):
+    gradient_checkpointing: bool = True
+    save_hf: bool = True

@@ -1,0 +1,248 @@
+"""Model architecture description (HuggingFace ``config.json`` compatible).
+
+One dataclass covers the families the reference trains: Llama-2, Qwen2.5/Qwen3
+dense, Qwen3-MoE, and DeepSeek-V3 / Moonlight (MLA attention + sigmoid-routed
+MoE with shared experts).  The reference reads these through ``AutoConfig`` and
+converts them for Megatron in chatlearn/utils/megatron_utils.py:20-164; here the
+same HF keys are read directly.
+"""
+import json
+import os
+from dataclasses import asdict, dataclass, field
+from typing import Any, Dict, Optional
+
+
+@dataclass
+class ModelArch:
+    model_type: str = "qwen3"            # llama | qwen2 | qwen3 | qwen3_moe | deepseek_v3
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: Optional[int] = None
+    head_dim: Optional[int] = None
+    intermediate_size: int = 11008
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    max_position_embeddings: int = 32768
+    qk_norm: bool = False                # Qwen3 per-head RMSNorm on q and k
+    attention_bias: bool = False         # Qwen2 qkv bias
+    tie_word_embeddings: bool = False
+    # MoE
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    router_aux_loss_coef: float = 0.0
+    n_shared_experts: int = 0
+    first_k_dense_replace: int = 0       # leading dense layers (DeepSeek/Moonlight)
+    scoring_func: str = "softmax"        # softmax | sigmoid
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    router_bias: bool = False            # e_score_correction_bias (aux-free balancing)
+    # MLA
+    use_mla: bool = False
+    kv_lora_rank: int = 0
+    q_lora_rank: Optional[int] = None
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    # reward-model head
+    num_labels: int = 0                  # >0: scalar/value head instead of lm_head
+    bos_token_id: Optional[int] = None
+    eos_token_id: Optional[int] = None
+    extra: Dict[str, Any] = field(default_factory=dict)
+
+    def __post_init__(self):
+        if self.num_key_value_heads is None:
+            self.num_key_value_heads = self.num_attention_heads
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+        if self.model_type == "qwen3" or self.model_type == "qwen3_moe":
+            self.qk_norm = True
+        if self.model_type == "qwen2":
+            self.attention_bias = True
+        if self.model_type in ("deepseek_v3", "deepseek_v2", "kimi_k2", "moonlight"):
+            self.use_mla = self.kv_lora_rank > 0
+        if self.eos_token_id is None:
+            self.eos_token_id = self.vocab_size - 1
+
+    # ---- derived sizes ----
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def layer_is_moe(self, layer: int) -> bool:
+        return self.is_moe and layer >= self.first_k_dense_replace
+
+    @property
+    def q_size(self) -> int:
+        if self.use_mla:
+            return self.num_attention_heads * (self.qk_nope_head_dim + self.qk_rope_head_dim)
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    def num_params(self) -> int:
+        h, v = self.hidden_size, self.vocab_size
+        n = v * h * (1 if self.tie_word_embeddings else 2) + h
+        for l in range(self.num_hidden_layers):
+            n += 2 * h
+            if self.use_mla:
+                qd = self.qk_nope_head_dim + self.qk_rope_head_dim
+                nh = self.num_attention_heads
+                if self.q_lora_rank:
+                    n += h * self.q_lora_rank + self.q_lora_rank + self.q_lora_rank * nh * qd
+                else:
+                    n += h * nh * qd
+                n += h * (self.kv_lora_rank + self.qk_rope_head_dim) + self.kv_lora_rank
+                n += self.kv_lora_rank * nh * (self.qk_nope_head_dim + self.v_head_dim)
+                n += nh * self.v_head_dim * h
+            else:
+                n += h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+                if self.qk_norm:
+                    n += 2 * self.head_dim
+                if self.attention_bias:
+                    n += self.q_size + 2 * self.kv_size
+            if self.layer_is_moe(l):
+                n += self.num_experts * h + (self.num_experts if self.router_bias else 0)
+                n += self.num_experts * 3 * h * self.moe_intermediate_size
+                n += self.n_shared_experts * 3 * h * self.moe_intermediate_size
+            else:
+                n += 3 * h * self.intermediate_size
+        return n
+
+    # ---- HF config.json round trip ----
+    _HF_ALIASES = {"num_local_experts": "num_experts", "n_routed_experts": "num_experts",
+                   "norm_eps": "rms_norm_eps"}
+
+    @classmethod
+    def from_hf_dict(cls, d: Dict[str, Any]) -> "ModelArch":
+        known = {f for f in cls.__dataclass_fields__}  # pylint: disable=no-member
+        kw, extra = {}, {}
+        for k, v in d.items():
+            k = cls._HF_ALIASES.get(k, k)
+            if k in known and k != "extra":
+                kw[k] = v
+            else:
+                extra[k] = v
+        arch = cls(**kw)
+        arch.extra = extra
+        return arch
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "ModelArch":
+        with open(os.path.join(path, "config.json"), "r", encoding="utf-8") as f:
+            return cls.from_hf_dict(json.load(f))
+
+    def to_hf_dict(self) -> Dict[str, Any]:
+        d = asdict(self)
+        extra = d.pop("extra")
+        d.update(extra)
+        arch_names = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM",
+                      "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
+                      "deepseek_v3": "DeepseekV3ForCausalLM"}
+        d.setdefault("architectures", [arch_names.get(self.model_type, "LlamaForCausalLM")])
+        if self.model_type == "deepseek_v3":
+            d["n_routed_experts"] = self.num_experts
+        return d
+
+    def save_pretrained(self, path: str):
+        os.makedirs(path, exist_ok=True)
+        with open(os.path.join(path, "config.json"), "w", encoding="utf-8") as f:
+            json.dump(self.to_hf_dict(), f, indent=2)
+
+
+def resolve_arch(model_cfg) -> ModelArch:
+    """Architecture of a role: inline ``model_arch`` dict, a preset name, or the
+    ``config.json`` under ``load``."""
+    ma = getattr(model_cfg, "model_arch", None)
+    if isinstance(ma, ModelArch):
+        return ma
+    if isinstance(ma, str):
+        return PRESETS[ma]()
+    if isinstance(ma, dict) and ma:
+        if "preset" in ma:
+            arch = PRESETS[ma["preset"]]()
+            for k, v in ma.items():
+                if k != "preset":
+                    setattr(arch, k, v)
+            return arch
+        return ModelArch.from_hf_dict(ma)
+    load = getattr(model_cfg, "load", None)
+    if load and os.path.exists(os.path.join(load, "config.json")):
+        return ModelArch.from_pretrained(load)
+    raise ValueError("model needs `model_arch` (inline dict / preset) or `load` with a config.json")
+
+
+# ---- presets: the shapes named by the benchmark configurations ----
+
+def tiny_qwen3() -> ModelArch:
+    return ModelArch(model_type="qwen3", vocab_size=1024, hidden_size=256, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                     intermediate_size=704, rope_theta=1e6, rms_norm_eps=1e-6)
+
+
+def qwen3_8b() -> ModelArch:
+    return ModelArch(model_type="qwen3", vocab_size=151936, hidden_size=4096, num_hidden_layers=36,
+                     num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                     intermediate_size=12288, rope_theta=1e6, rms_norm_eps=1e-6,
+                     max_position_embeddings=40960)
+
+
+def qwen3_30b_a3b() -> ModelArch:
+    return ModelArch(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048,
+                     num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4,
+                     head_dim=128, intermediate_size=6144, moe_intermediate_size=768,
+                     num_experts=128, num_experts_per_tok=8, norm_topk_prob=True,
+                     router_aux_loss_coef=1e-3, rope_theta=1e6)
+
+
+def llama2_7b() -> ModelArch:
+    return ModelArch(model_type="llama", vocab_size=32000, hidden_size=4096, num_hidden_layers=32,
+                     num_attention_heads=32, num_key_value_heads=32, intermediate_size=11008,
+                     rope_theta=10000.0, rms_norm_eps=1e-5, max_position_embeddings=4096)
+
+
+def moonlight_16b_a3b() -> ModelArch:
+    return ModelArch(model_type="deepseek_v3", vocab_size=163840, hidden_size=2048,
+                     num_hidden_layers=27, num_attention_heads=16, num_key_value_heads=16,
+                     intermediate_size=11264, moe_intermediate_size=1408, num_experts=64,
+                     num_experts_per_tok=6, n_shared_experts=2, first_k_dense_replace=1,
+                     scoring_func="sigmoid", n_group=1, topk_group=1, routed_scaling_factor=2.446,
+                     norm_topk_prob=True, router_bias=True, kv_lora_rank=512, q_lora_rank=None,
+                     qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, head_dim=192,
+                     rope_theta=50000.0, rms_norm_eps=1e-5)
+
+
+def tiny_moe() -> ModelArch:
+    return ModelArch(model_type="qwen3_moe", vocab_size=512, hidden_size=128, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                     intermediate_size=256, moe_intermediate_size=64, num_experts=8,
+                     num_experts_per_tok=2, router_aux_loss_coef=1e-3, rope_theta=1e6)
+
+
+def tiny_mla_moe() -> ModelArch:
+    return ModelArch(model_type="deepseek_v3", vocab_size=512, hidden_size=128, num_hidden_layers=3,
+                     num_attention_heads=4, num_key_value_heads=4, intermediate_size=256,
+                     moe_intermediate_size=64, num_experts=8, num_experts_per_tok=2,
+                     n_shared_experts=1, first_k_dense_replace=1, scoring_func="sigmoid",
+                     n_group=2, topk_group=1, routed_scaling_factor=1.5, router_bias=True,
+                     kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                     head_dim=24, rope_theta=10000.0)
+
+
+def tiny_llama() -> ModelArch:
+    return ModelArch(model_type="llama", vocab_size=512, hidden_size=128, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=4, intermediate_size=352,
+                     rope_theta=10000.0, rms_norm_eps=1e-5)
+
+
+PRESETS = {
+    "tiny_qwen3": tiny_qwen3, "qwen3_8b": qwen3_8b, "qwen3_30b_a3b": qwen3_30b_a3b,
+    "llama2_7b": llama2_7b, "moonlight_16b_a3b": moonlight_16b_a3b, "tiny_moe": tiny_moe,
+    "tiny_mla_moe": tiny_mla_moe, "tiny_llama": tiny_llama,
+}

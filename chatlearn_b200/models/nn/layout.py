@@ -1,0 +1,218 @@
+"""Parameter layout: how a model instance's local tensors ("leaves") map onto the
+canonical HuggingFace tensors.
+
+Every model instance — FSDP-style trainer, TP/EP-sharded trainer, rollout
+engine — stores fused leaves (``qkv``, ``gate_up``, stacked expert ``w13``/``w2``)
+holding only its own shard.  A leaf is described by a list of ``Segment``s, each
+saying "this rectangle of the leaf is that rectangle of HF tensor X".  The HF
+coordinate space is the common language: checkpoints read/write through it, and
+the trainer→rollout synchronizer intersects source and destination segments in
+it to obtain copy descriptors.  This replaces the reference's per-engine
+mappers and ``ShardedTensorInfo`` algebra
+(chatlearn/synchronizer/mappers/*.py, chatlearn/utils/mappings/sharded_tensor_info.py)
+with one declarative table; QKV packing, gate/up packing, GQA replication and
+expert re-homing fall out of the segment lists.
+"""
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+from .arch import ModelArch
+
+
+@dataclass(frozen=True)
+class Segment:
+    hf_name: str
+    hf_shape: Tuple[int, int]          # full HF tensor as 2-D (1-D tensors are (n, 1))
+    src_start: Tuple[int, int]         # (row, col) in the HF tensor
+    extent: Tuple[int, int]            # (rows, cols)
+    dst_start: Tuple[int, int]         # (row, col) inside the leaf matrix
+    dst_index: int = 0                 # leading index for 3-D leaves (local expert id)
+
+
+@dataclass
+class Leaf:
+    name: str                          # local name, e.g. "layers.3.qkv"
+    shape: Tuple[int, ...]             # local shape (1-D, 2-D or 3-D [n, rows, cols])
+    init: str = "normal"               # normal | ones | zeros
+    segments: List[Segment] = field(default_factory=list)
+    replicated: bool = False           # same content on every model-parallel rank
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    @property
+    def matrix_shape(self) -> Tuple[int, int]:
+        """(rows, cols) of one 2-D slab of the leaf."""
+        if len(self.shape) == 1:
+            return (self.shape[0], 1)
+        return (self.shape[-2], self.shape[-1])
+
+
+def _full(leaf_name, shape, hf_name, init="normal", replicated=True) -> Leaf:
+    ms = (shape[0], 1) if len(shape) == 1 else tuple(shape)
+    return Leaf(leaf_name, tuple(shape), init,
+                [Segment(hf_name, ms, (0, 0), ms, (0, 0))], replicated)
+
+
+def _rows(hf_name, full_shape, r0, n, dst_row, dst_index=0):
+    return Segment(hf_name, full_shape, (r0, 0), (n, full_shape[1]), (dst_row, 0), dst_index)
+
+
+def _cols(hf_name, full_shape, c0, n, dst_col=0, dst_index=0):
+    return Segment(hf_name, full_shape, (0, c0), (full_shape[0], n), (0, dst_col), dst_index)
+
+
+def kv_head_range(arch: ModelArch, tp: int, tp_rank: int) -> Tuple[int, int]:
+    """(first kv head, count) owned by a TP rank; heads are replicated when tp > n_kv."""
+    nkv = arch.num_key_value_heads
+    if tp <= nkv:
+        assert nkv % tp == 0, f"{nkv} kv heads not divisible by tp={tp}"
+        per = nkv // tp
+        return tp_rank * per, per
+    assert tp % nkv == 0, f"tp={tp} must be a multiple of {nkv} kv heads"
+    return tp_rank // (tp // nkv), 1
+
+
+def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int = 1,
+                 ep_rank: int = 0) -> List[Leaf]:
+    """Leaves of decoder layer ``l`` for one (tp, ep) rank."""
+    H = arch.hidden_size
+    pre, hp = f"layers.{l}.", f"model.layers.{l}."
+    out: List[Leaf] = [_full(pre + "input_layernorm", (H,), hp + "input_layernorm.weight", "ones")]
+    nh = arch.num_attention_heads
+    assert nh % tp == 0, f"{nh} heads not divisible by tp={tp}"
+    nh_l = nh // tp
+    if arch.use_mla:
+        qd = arch.qk_nope_head_dim + arch.qk_rope_head_dim
+        a = hp + "self_attn."
+        if arch.q_lora_rank:
+            out.append(_full(pre + "q_a_proj", (arch.q_lora_rank, H), a + "q_a_proj.weight"))
+            out.append(_full(pre + "q_a_layernorm", (arch.q_lora_rank,), a + "q_a_layernorm.weight", "ones"))
+            fs = (nh * qd, arch.q_lora_rank)
+            out.append(Leaf(pre + "q_b_proj", (nh_l * qd, arch.q_lora_rank), "normal",
+                            [_rows(a + "q_b_proj.weight", fs, tp_rank * nh_l * qd, nh_l * qd, 0)]))
+        else:
+            fs = (nh * qd, H)
+            out.append(Leaf(pre + "q_proj", (nh_l * qd, H), "normal",
+                            [_rows(a + "q_proj.weight", fs, tp_rank * nh_l * qd, nh_l * qd, 0)]))
+        out.append(_full(pre + "kv_a_proj_with_mqa", (arch.kv_lora_rank + arch.qk_rope_head_dim, H),
+                         a + "kv_a_proj_with_mqa.weight"))
+        out.append(_full(pre + "kv_a_layernorm", (arch.kv_lora_rank,), a + "kv_a_layernorm.weight", "ones"))
+        kvd = arch.qk_nope_head_dim + arch.v_head_dim
+        fs = (nh * kvd, arch.kv_lora_rank)
+        out.append(Leaf(pre + "kv_b_proj", (nh_l * kvd, arch.kv_lora_rank), "normal",
+                        [_rows(a + "kv_b_proj.weight", fs, tp_rank * nh_l * kvd, nh_l * kvd, 0)]))
+        fs = (H, nh * arch.v_head_dim)
+        out.append(Leaf(pre + "o_proj", (H, nh_l * arch.v_head_dim), "normal",
+                        [_cols(a + "o_proj.weight", fs, tp_rank * nh_l * arch.v_head_dim,
+                               nh_l * arch.v_head_dim)]))
+    else:
+        d = arch.head_dim
+        kv0, nkv_l = kv_head_range(arch, tp, tp_rank)
+        a = hp + "self_attn."
+        qf, kf = (nh * d, H), (arch.num_key_value_heads * d, H)
+        segs = [_rows(a + "q_proj.weight", qf, tp_rank * nh_l * d, nh_l * d, 0),
+                _rows(a + "k_proj.weight", kf, kv0 * d, nkv_l * d, nh_l * d),
+                _rows(a + "v_proj.weight", kf, kv0 * d, nkv_l * d, (nh_l + nkv_l) * d)]
+        rows = (nh_l + 2 * nkv_l) * d
+        out.append(Leaf(pre + "qkv", (rows, H), "normal", segs))
+        if arch.attention_bias:
+            bs = [Segment(a + "q_proj.bias", (nh * d, 1), (tp_rank * nh_l * d, 0), (nh_l * d, 1), (0, 0)),
+                  Segment(a + "k_proj.bias", (kf[0], 1), (kv0 * d, 0), (nkv_l * d, 1), (nh_l * d, 0)),
+                  Segment(a + "v_proj.bias", (kf[0], 1), (kv0 * d, 0), (nkv_l * d, 1), ((nh_l + nkv_l) * d, 0))]
+            out.append(Leaf(pre + "qkv_bias", (rows,), "zeros", bs))
+        if arch.qk_norm:
+            out.append(_full(pre + "q_norm", (d,), a + "q_norm.weight", "ones"))
+            out.append(_full(pre + "k_norm", (d,), a + "k_norm.weight", "ones"))
+        fs = (H, nh * d)
+        out.append(Leaf(pre + "o_proj", (H, nh_l * d), "normal",
+                        [_cols(a + "o_proj.weight", fs, tp_rank * nh_l * d, nh_l * d)]))
+    out.append(_full(pre + "post_attention_layernorm", (H,), hp + "post_attention_layernorm.weight", "ones"))
+
+    def mlp_leaves(prefix, hf_prefix, F, shard_tp):
+        t, r = (tp, tp_rank) if shard_tp else (1, 0)
+        assert F % t == 0
+        Fl = F // t
+        gu = Leaf(prefix + "gate_up", (2 * Fl, H), "normal",
+                  [_rows(hf_prefix + "gate_proj.weight", (F, H), r * Fl, Fl, 0),
+                   _rows(hf_prefix + "up_proj.weight", (F, H), r * Fl, Fl, Fl)])
+        dn = Leaf(prefix + "down_proj", (H, Fl), "normal",
+                  [_cols(hf_prefix + "down_proj.weight", (H, F), r * Fl, Fl)])
+        return [gu, dn]
+
+    if arch.layer_is_moe(l):
+        E, Fm = arch.num_experts, arch.moe_intermediate_size
+        assert E % ep == 0, f"{E} experts not divisible by ep={ep}"
+        El = E // ep
+        m = hp + "mlp."
+        out.append(_full(pre + "router", (E, H), m + "gate.weight"))
+        if arch.router_bias:
+            out.append(_full(pre + "router_bias", (E,), m + "gate.e_score_correction_bias", "zeros"))
+        s13, s2 = [], []
+        for j in range(El):
+            e = ep_rank * El + j
+            s13.append(_rows(f"{m}experts.{e}.gate_proj.weight", (Fm, H), 0, Fm, 0, j))
+            s13.append(_rows(f"{m}experts.{e}.up_proj.weight", (Fm, H), 0, Fm, Fm, j))
+            s2.append(_rows(f"{m}experts.{e}.down_proj.weight", (H, Fm), 0, H, 0, j))
+        out.append(Leaf(pre + "w13", (El, 2 * Fm, H), "normal", s13))
+        out.append(Leaf(pre + "w2", (El, H, Fm), "normal", s2))
+        if arch.n_shared_experts:
+            Fs = arch.n_shared_experts * Fm
+            sh = mlp_leaves(pre + "shared_", m + "shared_experts.", Fs, True)
+            out.extend(sh)
+    else:
+        out.extend(mlp_leaves(pre, hp + "mlp.", arch.intermediate_size, True))
+    for lf in out:
+        if len(lf.segments) == 1 and lf.segments[0].extent == lf.segments[0].hf_shape:
+            lf.replicated = True
+    return out
+
+
+def embed_leaves(arch: ModelArch, tp: int = 1, tp_rank: int = 0) -> List[Leaf]:
+    V, H = arch.vocab_size, arch.hidden_size
+    assert V % tp == 0
+    Vl = V // tp
+    return [Leaf("embed_tokens", (Vl, H), "normal",
+                 [_rows("model.embed_tokens.weight", (V, H), tp_rank * Vl, Vl, 0)], tp == 1)]
+
+
+def head_leaves(arch: ModelArch, tp: int = 1, tp_rank: int = 0) -> List[Leaf]:
+    V, H = arch.vocab_size, arch.hidden_size
+    out = [_full("norm", (H,), "model.norm.weight", "ones")]
+    if arch.num_labels > 0:
+        out.append(_full("score", (arch.num_labels, H), "score.weight"))
+    elif not arch.tie_word_embeddings:
+        Vl = V // tp
+        out.append(Leaf("lm_head", (Vl, H), "normal",
+                        [_rows("lm_head.weight", (V, H), tp_rank * Vl, Vl, 0)], tp == 1))
+    return out
+
+
+def model_blocks(arch: ModelArch, tp=1, tp_rank=0, ep=1, ep_rank=0,
+                 layer_range: Optional[Tuple[int, int]] = None,
+                 with_embed=True, with_head=True) -> List[Tuple[str, List[Leaf]]]:
+    """Blocks (= FSDP units / offload units) of a model instance in forward order.
+    ``layer_range`` selects a pipeline stage's layers."""
+    lo, hi = layer_range or (0, arch.num_hidden_layers)
+    blocks = []
+    if with_embed:
+        blocks.append(("embed", embed_leaves(arch, tp, tp_rank)))
+    for l in range(lo, hi):
+        blocks.append((f"layer{l}", layer_leaves(arch, l, tp, tp_rank, ep, ep_rank)))
+    if with_head:
+        blocks.append(("head", head_leaves(arch, tp, tp_rank)))
+    return blocks
+
+
+def hf_tensor_shapes(arch: ModelArch) -> Dict[str, Tuple[int, ...]]:
+    """Name → shape of every tensor of the HF checkpoint of ``arch``."""
+    shapes: Dict[str, Tuple[int, ...]] = {}
+    for _, leaves in model_blocks(arch):
+        for lf in leaves:
+            for s in lf.segments:
+                shapes[s.hf_name] = (s.hf_shape[0],) if len(lf.shape) == 1 else tuple(s.hf_shape)
+    return shapes

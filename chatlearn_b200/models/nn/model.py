@@ -1,0 +1,381 @@
+"""Decoder-only transformer written as functions over flat parameter blocks.
+
+One implementation serves the trainer (packed varlen batches, autograd), the
+reference/reward roles (no-grad forward) and the rollout engine (paged KV
+cache), for Llama-2, Qwen2/Qwen3 dense, Qwen3-MoE and DeepSeek-V3/Moonlight
+(MLA + shared-expert MoE).  Parameters live in one contiguous buffer per block
+(embedding, each decoder layer, head); the block is the unit of sharding,
+all-gather/reduce-scatter, offload and weight sync.  The reference relies on
+HF ``AutoModelForCausalLM`` (chatlearn/models/fsdp_module.py:250-295) or
+Megatron-Core ``GPTModel``; neither is used here.
+"""
+import math
+import zlib
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+
+from chatlearn_b200 import ops
+from .arch import ModelArch
+from .layout import Leaf, model_blocks
+
+ALIGN = 128  # leaf offsets inside a block are multiples of this many elements (TMA/vector alignment)
+
+
+def _align(n, a=ALIGN):
+    return (n + a - 1) // a * a
+
+
+class ParamBlock:
+    """Leaves of one block laid out in one flat tensor."""
+
+    def __init__(self, name: str, leaves: List[Leaf], dtype, device, pad_to: int = 1,
+                 allocate: bool = True):
+        self.name, self.leaves = name, leaves
+        self.offsets: Dict[str, int] = {}
+        off = 0
+        for lf in leaves:
+            self.offsets[lf.name] = off
+            off += _align(lf.numel)
+        self.numel = _align(off, ALIGN * pad_to)
+        self.dtype, self.device = dtype, device
+        self.flat: Optional[torch.Tensor] = None
+        self.grad: Optional[torch.Tensor] = None
+        self.params: Dict[str, torch.Tensor] = {}
+        if allocate:
+            self.bind(torch.zeros(self.numel, dtype=dtype, device=device))
+
+    def short(self, leaf_name: str) -> str:
+        return leaf_name.split(".", 2)[-1] if leaf_name.startswith("layers.") else leaf_name
+
+    def bind(self, flat: torch.Tensor):
+        """Point every leaf at ``flat`` (shape ``[numel]``)."""
+        assert flat.numel() == self.numel
+        self.flat = flat
+        for lf in self.leaves:
+            o = self.offsets[lf.name]
+            view = flat[o:o + lf.numel].view(lf.shape)
+            key = self.short(lf.name)
+            if key in self.params:
+                self.params[key].data = view
+            else:
+                self.params[key] = view
+        return self
+
+    def enable_grad(self, grad_flat: torch.Tensor):
+        """Make leaves autograd leaves whose ``.grad`` are views of ``grad_flat``:
+        autograd accumulates into them in place, so the block's gradient is one
+        contiguous buffer ready for reduce-scatter."""
+        self.grad = grad_flat
+        for lf in self.leaves:
+            key = self.short(lf.name)
+            p = self.params[key]
+            if not p.requires_grad:
+                p = p.detach().requires_grad_(True)
+                self.params[key] = p
+            o = self.offsets[lf.name]
+            p.grad = grad_flat[o:o + lf.numel].view(lf.shape)
+
+    def leaf_view(self, flat: torch.Tensor, lf: Leaf) -> torch.Tensor:
+        o = self.offsets[lf.name]
+        return flat[o:o + lf.numel].view(lf.shape)
+
+    @torch.no_grad()
+    def init_weights(self, seed: int, std: float = 0.02):
+        """Deterministic per-leaf initialisation: the generator of each leaf is
+        seeded from (seed, HF tensor names), values are drawn for the *full* HF
+        tensor on CPU only for small tensors; large leaves draw on their device."""
+        for lf in self.leaves:
+            p = self.leaf_view(self.flat, lf)
+            if lf.init == "ones":
+                p.fill_(1.0)
+            elif lf.init == "zeros":
+                p.zero_()
+            else:
+                g = torch.Generator(device=p.device)
+                g.manual_seed((seed * 1000003 + zlib.crc32(lf.name.encode())) % (2 ** 31))
+                if p.dtype in (torch.float32, torch.bfloat16, torch.float16):
+                    p.normal_(0.0, std, generator=g)
+                else:
+                    p.copy_(torch.empty(p.shape, dtype=torch.float32, device=p.device)
+                            .normal_(0.0, std, generator=g))
+
+
+@dataclass
+class KVCtx:
+    """Paged KV-cache view for one forward of the rollout engine."""
+    k_cache: List[torch.Tensor]            # per layer [num_blocks, block, nkv_local, dk]
+    v_cache: List[torch.Tensor]
+    slot_mapping: torch.Tensor             # [T] flat slot of every new token
+    block_tables: torch.Tensor             # [B, max_blocks] int32
+    seq_lens: torch.Tensor                 # [B] lengths including the new tokens
+    q_lens: Optional[torch.Tensor] = None  # [B] new tokens per sequence (None → 1 each)
+    prefill_only: bool = False             # all sequences start at position 0 → varlen kernel
+
+
+@dataclass
+class FwdCtx:
+    positions: torch.Tensor
+    cu_seqlens: Optional[torch.Tensor] = None
+    max_seqlen: int = 0
+    kv: Optional[KVCtx] = None
+    tp: Any = None                         # parallel.groups.Group or None
+    ep: Any = None
+    sp: Any = None                         # Ulysses sequence-parallel group
+    cp: Any = None                         # context-parallel group
+    attn_positions: Optional[torch.Tensor] = None  # positions of the rows attention sees (Ulysses)
+    cp_plan: Optional[Dict[str, Any]] = None       # ContextParallel.plan() of this packed row
+    aux_losses: List[torch.Tensor] = field(default_factory=list)
+    moe_stats: List[torch.Tensor] = field(default_factory=list)
+
+
+def _tp_reduce(x, ctx):
+    if ctx.tp is not None and ctx.tp.size > 1:
+        return ctx.tp.all_reduce(x)
+    return x
+
+
+def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx, layer: int):
+    T = x.shape[0]
+    d = arch.head_dim
+    x = _tp_copy(x, ctx)
+    tp = ctx.tp.size if ctx.tp is not None else 1
+    nh_l = arch.num_attention_heads // tp
+    if arch.use_mla:
+        nope, rp, dv = arch.qk_nope_head_dim, arch.qk_rope_head_dim, arch.v_head_dim
+        if "q_a_proj" in p:
+            qa = ops.rmsnorm(ops.linear(x, p["q_a_proj"]), p["q_a_layernorm"], arch.rms_norm_eps)
+            q = ops.linear(qa, p["q_b_proj"])
+        else:
+            q = ops.linear(x, p["q_proj"])
+        q = q.view(T, nh_l, nope + rp)
+        ckv = ops.linear(x, p["kv_a_proj_with_mqa"])
+        c = ops.rmsnorm(ckv[:, :arch.kv_lora_rank].contiguous(), p["kv_a_layernorm"], arch.rms_norm_eps)
+        k_rope = ckv[:, arch.kv_lora_rank:].reshape(T, 1, rp)
+        kvb = ops.linear(c, p["kv_b_proj"]).view(T, nh_l, nope + dv)
+        k_nope, v = kvb[..., :nope], kvb[..., nope:].contiguous()
+        q_rope = ops.rope(q[..., nope:].contiguous(), ctx.positions, arch.rope_theta)
+        k_rope = ops.rope(k_rope.contiguous(), ctx.positions, arch.rope_theta)
+        q = torch.cat([q[..., :nope], q_rope], dim=-1)
+        k = torch.cat([k_nope, k_rope.expand(T, nh_l, rp)], dim=-1)
+        scale = 1.0 / math.sqrt(nope + rp)
+        nkv_l = nh_l
+    else:
+        qkv = ops.linear(x, p["qkv"], p.get("qkv_bias"))
+        nkv_l = (qkv.shape[-1] // d - nh_l) // 2
+        q = qkv[:, :nh_l * d].view(T, nh_l, d)
+        k = qkv[:, nh_l * d:(nh_l + nkv_l) * d].view(T, nkv_l, d)
+        v = qkv[:, (nh_l + nkv_l) * d:].view(T, nkv_l, d)
+        scale = 1.0 / math.sqrt(d)
+        if ctx.sp is not None and ctx.sp.size > 1:
+            # Ulysses: trade the sequence split for a head split around attention
+            q, k, v = ctx.sp.seq_to_heads(q), ctx.sp.seq_to_heads(k, kv=True), ctx.sp.seq_to_heads(v, kv=True)
+        q, k = ops.qk_norm_rope(q, k, p.get("q_norm"), p.get("k_norm"), arch.rms_norm_eps,
+                                ctx.attn_positions if ctx.attn_positions is not None else ctx.positions,
+                                arch.rope_theta)
+    kv = ctx.kv
+    if kv is not None:
+        ops.kv_append(k, v, kv.k_cache[layer], kv.v_cache[layer], kv.slot_mapping)
+        if kv.prefill_only:
+            o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, scale)
+        else:
+            o = ops.paged_attention(q, kv.k_cache[layer], kv.v_cache[layer], kv.block_tables,
+                                    kv.seq_lens, kv.q_lens, scale)
+    elif ctx.cp is not None and ctx.cp.size > 1:
+        o = ctx.cp.attention(q, k, v, ctx, scale)
+    else:
+        o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, scale)
+    if ctx.sp is not None and ctx.sp.size > 1 and not arch.use_mla:
+        o = ctx.sp.heads_to_seq(o)
+    out = ops.linear(o.reshape(o.shape[0], -1), p["o_proj"])
+    return _tp_reduce(out, ctx)
+
+
+def _tp_copy(x, ctx):
+    if ctx.tp is not None and ctx.tp.size > 1 and torch.is_grad_enabled():
+        return ctx.tp.copy_in(x)
+    return x
+
+
+def dense_mlp(p, x, ctx, prefix=""):
+    x = _tp_copy(x, ctx)
+    h = ops.swiglu(ops.linear(x, p[prefix + "gate_up"]))
+    return ops.linear(h, p[prefix + "down_proj"])
+
+
+def moe_block(arch: ModelArch, p, x, ctx: FwdCtx):
+    logits = ops.linear(x.float(), p["router"].float())
+    w, idx, scores = ops.moe_router(logits, arch.num_experts_per_tok, arch.scoring_func,
+                                    arch.norm_topk_prob, p.get("router_bias"), arch.n_group,
+                                    arch.topk_group, arch.routed_scaling_factor)
+    if arch.router_aux_loss_coef > 0 and torch.is_grad_enabled():
+        ctx.aux_losses.append(arch.router_aux_loss_coef *
+                              ops.moe_aux_loss(scores, idx, arch.num_experts, arch.num_experts_per_tok))
+    if ctx.ep is not None and ctx.ep.size > 1:
+        y = ctx.ep.experts(x, p["w13"], p["w2"], w, idx, arch.num_experts)
+    else:
+        y = ops.moe_experts(x, p["w13"], p["w2"], w, idx)
+    if "shared_gate_up" in p:
+        y = y + _tp_reduce(dense_mlp(p, x, ctx, "shared_"), ctx)
+    return y
+
+
+def decoder_layer(arch: ModelArch, p, x, ctx: FwdCtx, layer: int):
+    h = ops.rmsnorm(x, p["input_layernorm"], arch.rms_norm_eps)
+    x = x + attention_block(arch, p, h, ctx, layer)
+    h = ops.rmsnorm(x, p["post_attention_layernorm"], arch.rms_norm_eps)
+    if "router" in p:
+        return x + moe_block(arch, p, h, ctx)
+    return x + _tp_reduce(dense_mlp(p, h, ctx), ctx)
+
+
+def embed(p, tokens, ctx: FwdCtx):
+    w = p["embed_tokens"]
+    if ctx.tp is not None and ctx.tp.size > 1:
+        Vl = w.shape[0]
+        lo = ctx.tp.rank * Vl
+        local = tokens - lo
+        ok = (local >= 0) & (local < Vl)
+        e = torch.nn.functional.embedding(local.clamp(0, Vl - 1), w)
+        e = e * ok[:, None].to(e.dtype)
+        return ctx.tp.all_reduce(e)
+    return torch.nn.functional.embedding(tokens, w)
+
+
+class CausalLM:
+    """Holds the parameter blocks of one model-parallel rank and runs them."""
+
+    def __init__(self, arch: ModelArch, dtype=torch.float32, device="cpu", tp=1, tp_rank=0,
+                 ep=1, ep_rank=0, layer_range=None, with_embed=True, with_head=True,
+                 pad_to: int = 1, allocate: bool = True):
+        self.arch, self.dtype, self.device = arch, dtype, torch.device(device)
+        self.tp, self.tp_rank, self.ep, self.ep_rank = tp, tp_rank, ep, ep_rank
+        self.layer_range = layer_range or (0, arch.num_hidden_layers)
+        self.blocks: List[ParamBlock] = [
+            ParamBlock(n, leaves, dtype, self.device, pad_to, allocate)
+            for n, leaves in model_blocks(arch, tp, tp_rank, ep, ep_rank, layer_range,
+                                          with_embed, with_head)]
+        self.block_by_name = {b.name: b for b in self.blocks}
+
+    # ---- parameters ----
+    def init_weights(self, seed: int = 1234, std: float = 0.02):
+        for b in self.blocks:
+            b.init_weights(seed, std)
+        return self
+
+    def num_params(self) -> int:
+        return sum(lf.numel for b in self.blocks for lf in b.leaves)
+
+    def named_leaves(self):
+        for b in self.blocks:
+            for lf in b.leaves:
+                yield lf.name, b.params[b.short(lf.name)], lf, b
+
+    def layer_params(self, l: int) -> Dict[str, torch.Tensor]:
+        return self.block_by_name[f"layer{l}"].params
+
+    def to_(self, device=None, dtype=None):
+        for b in self.blocks:
+            b.bind(b.flat.to(device=device or b.flat.device, dtype=dtype or b.flat.dtype))
+            b.device, b.dtype = b.flat.device, b.flat.dtype
+        self.device = self.blocks[0].flat.device
+        self.dtype = self.blocks[0].flat.dtype
+        return self
+
+    def copy_from(self, other: "CausalLM"):
+        for a, b in zip(self.blocks, other.blocks):
+            a.flat.copy_(b.flat)
+        return self
+
+    # ---- forward ----
+    def hidden_states(self, tokens, ctx: FwdCtx, layer_hook=None, x=None):
+        """Embedding + decoder layers (+ final norm when this rank owns the head)."""
+        if "embed" in self.block_by_name:
+            x = embed(self.block_by_name["embed"].params, tokens, ctx)
+            if x.dtype != self.dtype:
+                x = x.to(self.dtype)
+        for l in range(*self.layer_range):
+            p = self.layer_params(l)
+            if layer_hook is not None:
+                x = layer_hook(l, p, x, ctx)
+            else:
+                x = decoder_layer(self.arch, p, x, ctx, l)
+        if "head" in self.block_by_name:
+            x = ops.rmsnorm(x, self.block_by_name["head"].params["norm"], self.arch.rms_norm_eps)
+        return x
+
+    def lm_head_weight(self):
+        if self.arch.tie_word_embeddings:
+            return self.block_by_name["embed"].params["embed_tokens"]
+        return self.block_by_name["head"].params["lm_head"]
+
+    def logits(self, hidden):
+        return ops.linear(hidden, self.lm_head_weight())
+
+    def logprobs(self, tokens, labels, ctx: FwdCtx, temperature=1.0, layer_hook=None):
+        """Per-token log p(label) and entropy for a packed row, never building ``[T, V]``."""
+        h = self.hidden_states(tokens, ctx, layer_hook)
+        return ops.lmhead_logprob_entropy(h, self.lm_head_weight(), labels, temperature)
+
+    def score(self, tokens, ctx: FwdCtx):
+        """Reward/value head: ``[T, num_labels]``."""
+        h = self.hidden_states(tokens, ctx)
+        return ops.linear(h, self.block_by_name["head"].params["score"]).float()
+
+    # ---- HF state dict ----
+    @torch.no_grad()
+    def hf_state_dict(self, dtype=None) -> Dict[str, torch.Tensor]:
+        """Assemble full HF tensors from this rank's leaves (complete only when
+        tp == ep == 1 and all layers are local; otherwise partial tensors of the
+        local shard are returned under the same names)."""
+        out: Dict[str, torch.Tensor] = {}
+        one_d = set()
+        for _, p, lf, _ in self.named_leaves():
+            for s in lf.segments:
+                if len(lf.shape) == 1:
+                    one_d.add(s.hf_name)
+                full = out.get(s.hf_name)
+                if full is None:
+                    full = torch.zeros(s.hf_shape, dtype=dtype or p.dtype, device=p.device)
+                    out[s.hf_name] = full
+                slab = p if len(lf.shape) < 3 else p[s.dst_index]
+                slab = slab.reshape(lf.matrix_shape)
+                r0, c0 = s.dst_start
+                rs, cs = s.src_start
+                nr, nc = s.extent
+                full[rs:rs + nr, cs:cs + nc] = slab[r0:r0 + nr, c0:c0 + nc]
+        for k in one_d:
+            out[k] = out[k].squeeze(1)
+        return out
+
+    @torch.no_grad()
+    def load_hf_state_dict(self, sd: Dict[str, torch.Tensor], strict: bool = True):
+        """Fill the local leaves from full HF tensors (each rank slices its shard)."""
+        missing = []
+        for _, p, lf, _ in self.named_leaves():
+            for s in lf.segments:
+                src = sd.get(s.hf_name)
+                if src is None:
+                    missing.append(s.hf_name)
+                    continue
+                src = src.reshape(s.hf_shape)
+                slab = p if len(lf.shape) < 3 else p[s.dst_index]
+                slab = slab.view(lf.matrix_shape)
+                r0, c0 = s.dst_start
+                rs, cs = s.src_start
+                nr, nc = s.extent
+                slab[r0:r0 + nr, c0:c0 + nc].copy_(src[rs:rs + nr, cs:cs + nc])
+        if strict and missing:
+            raise KeyError(f"missing tensors: {sorted(set(missing))[:8]} …")
+        return missing
+
+
+def packed_ctx(seq_lens: List[int], device, **kw) -> Tuple[FwdCtx, torch.Tensor]:
+    """Context of a packed row made of sequences of the given lengths."""
+    cu = torch.zeros(len(seq_lens) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(seq_lens, dtype=torch.int32).cumsum(0)
+    pos = torch.cat([torch.arange(n) for n in seq_lens]) if seq_lens else torch.zeros(0, dtype=torch.long)
+    ctx = FwdCtx(positions=pos.to(device), cu_seqlens=cu.to(device),
+                 max_seqlen=max(seq_lens) if seq_lens else 0, **kw)
+    return ctx, cu
