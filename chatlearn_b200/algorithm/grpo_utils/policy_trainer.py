@@ -1,0 +1,151 @@
+"""GRPO policy trainer / log-prob scorer on the FSDP-style back end.
+
+Parity: chatlearn/algorithm/grpo_utils/policy_trainer.py:80-365.  Same contract:
+``forward_step`` adds per-token ``old_logprobs`` / ``ref_logprobs`` to each sample;
+``train_step`` runs one optimizer step over a mini-batch (micro-batching or
+sequence packing, optional Ulysses split, GRPO clipped-ratio loss + k3 KL +
+entropy bonus, global-token-mean normalisation, grad-norm clip, AdamW) and
+records ``pg_loss, kl_loss, entropy_loss, grad_norm``.
+
+Differences by design: micro-batches are built directly as packed rows (no
+pad → unpad round trip), log-probs and entropy come from the fused LM-head
+kernel so ``[T, V]`` logits are never materialised, and the loss with all its
+statistics is one fused op.
+"""
+from typing import Dict, List
+
+import torch
+import torch.distributed as dist
+
+from chatlearn_b200 import ops
+from chatlearn_b200.models.fsdp_module import FSDPModule
+from chatlearn_b200.models.nn import FwdCtx
+from .trainer_utils import pack_samples, split_microbatch, unpack_per_sample
+
+
+class PolicyTrainer(FSDPModule):
+    def setup(self):
+        super().setup()
+        self._metric_prefix = "policy_trainer" if self.trainable else self.name
+
+    # ------------------------------------------------------------------ helpers
+    def _max_reduce(self, n: int) -> int:
+        g = self.role_group
+        if g is None or g.size == 1:
+            return n
+        t = torch.tensor([n], dtype=torch.int64, device=self.device)
+        g.all_reduce_(t, op=dist.ReduceOp.MAX)
+        return int(t.item())
+
+    def _microbatches(self, data_list: List[Dict], for_train: bool):
+        ma = self.module_args
+        if ma.packing:
+            return split_microbatch(data_list, packing=True, max_train_token=ma.max_token_in_packing,
+                                    max_reduce=self._max_reduce)
+        mbs = ma.train_micro_batch_size if for_train and hasattr(ma, "train_micro_batch_size") \
+            else ma.generation_batch_size
+        return split_microbatch(data_list, micro_batch_size=max(int(mbs), 1))
+
+    def _ctx_and_inputs(self, batch):
+        """Device tensors + forward context of a packed row (Ulysses-split if sp>1)."""
+        batch.to(self.device)
+        tokens, positions = batch.tokens, batch.positions
+        ctx = FwdCtx(positions=positions, cu_seqlens=batch.cu_seqlens, max_seqlen=batch.max_seqlen)
+        labels = batch.labels
+        if self.sp is not None:
+            ctx.sp = self.sp
+            ctx.attn_positions = positions
+            tokens = self.sp.split(tokens)
+            labels = self.sp.split(labels)
+            ctx.positions = self.sp.split(positions)
+        return tokens, labels, ctx
+
+    def _logprobs(self, batch, need_entropy: bool):
+        tokens, labels, ctx = self._ctx_and_inputs(batch)
+        lp, ent = self.model.logprobs(tokens, labels, ctx)
+        if self.sp is not None:
+            lp = self.sp.gather(lp)
+            ent = self.sp.gather(ent) if need_entropy else None
+        return lp, (ent if need_entropy else None), ctx
+
+    # ------------------------------------------------------------------ scoring
+    @torch.no_grad()
+    def forward_step(self, data_list: List[Dict], iteration: int = 0, **kwargs) -> List[Dict]:
+        tag = "old_logprobs" if self.trainable else "ref_logprobs"
+        if not data_list:
+            return data_list
+        pad = self.sp.size if self.sp is not None else 1
+        for mb in self._microbatches(data_list, for_train=False):
+            if not mb:
+                continue
+            batch = pack_samples(mb, pad_multiple=pad)
+            lp, _, _ = self._logprobs(batch, need_entropy=False)
+            for s, v in zip(mb, unpack_per_sample(lp, batch, mb)):
+                s[tag] = v
+        return data_list
+
+    # ------------------------------------------------------------------ training
+    def train_step(self, data_list: List[Dict], **kwargs):
+        ma = self.module_args
+        st = self.state
+        # global number of response tokens of this optimizer step (all DP ranks)
+        n_local = float(sum(int(s["response_token_length"]) for s in data_list))
+        n_tok = torch.tensor([n_local], dtype=torch.float32, device=self.device)
+        if self.role_group is not None and self.role_group.size > 1:
+            self.role_group.all_reduce_(n_tok)
+            if self.sp is not None:
+                n_tok /= self.sp.size
+        inv_norm = 1.0 / max(float(n_tok.item()), 1.0)
+        st.zero_grad()
+        stats = torch.zeros(6, dtype=torch.float32, device=self.device)
+        pad = self.sp.size if self.sp is not None else 1
+        need_ent = ma.entropy_coef != 0.0
+        use_ref = ma.kl_coef != 0.0
+        for mb in self._microbatches(data_list, for_train=True):
+            if not mb:
+                # ranks with fewer bins still join the collectives of the others
+                continue
+            batch = pack_samples(mb, pad_multiple=pad)
+            lp, ent, ctx = self._logprobs(batch, need_entropy=True)
+            if ma.use_group_sequence_policy:
+                loss_tok, _, _ = ops.gspo_token_loss(
+                    lp, batch.old_logprobs, batch.advantages, batch.seq_ids, len(batch.seq_lens),
+                    batch.loss_mask, ma.pos_clip_ratio, ma.neg_clip_ratio, ma.diff_clip_ratio,
+                    ma.final_clip_ratio)
+                m = batch.loss_mask
+                total = (loss_tok * m).sum()
+                s6 = [(loss_tok.detach() * m).sum()]
+                if use_ref:
+                    kl = ops.kl_k3(lp, batch.ref_logprobs)
+                    total = total + ma.kl_coef * (kl * m).sum()
+                    s6.append((kl.detach() * m).sum())
+                else:
+                    s6.append(torch.zeros((), device=self.device))
+                if need_ent:
+                    total = total - ma.entropy_coef * (ent * m).sum()
+                s6.append((ent.detach() * m).sum())
+                s6 += [torch.zeros((), device=self.device)] * 2 + [m.sum()]
+                loss, s = total * inv_norm, torch.stack(s6)
+            else:
+                loss, s = ops.grpo_loss_fused(
+                    lp, batch.old_logprobs, batch.ref_logprobs if use_ref else None,
+                    batch.advantages, batch.loss_mask, ent if need_ent else ent.detach(),
+                    ma.pos_clip_ratio, ma.neg_clip_ratio, ma.diff_clip_ratio, ma.final_clip_ratio,
+                    ma.kl_coef, ma.entropy_coef if need_ent else 0.0, inv_norm)
+            for aux in ctx.aux_losses:
+                loss = loss + aux * (batch.loss_mask.sum() * inv_norm)
+            loss.backward()
+            stats += s.detach()
+        grad_norm = st.step()
+        # metrics: token means over the whole optimizer step (all ranks)
+        if self.role_group is not None and self.role_group.size > 1:
+            self.role_group.all_reduce_(stats)
+            if self.sp is not None:
+                stats /= self.sp.size
+        n = max(float(stats[5].item()), 1.0)
+        self._metric_list.append({
+            "pg_loss": float(stats[0].item()) / n, "kl_loss": float(stats[1].item()) / n,
+            "entropy_loss": float(stats[2].item()) / n, "grad_norm": float(grad_norm),
+            "clip_pos_frac": float(stats[3].item()) / n, "clip_neg_frac": float(stats[4].item()) / n,
+            "train_tokens": n})
+        self._train_iteration += 1

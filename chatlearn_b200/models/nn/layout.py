@@ -202,7 +202,13 @@ def model_blocks(arch: ModelArch, tp=1, tp_rank=0, ep=1, ep_rank=0,
     if with_embed:
         blocks.append(("embed", embed_leaves(arch, tp, tp_rank)))
     for l in range(lo, hi):
-        blocks.append((f"layer{l}", layer_leaves(arch, l, tp, tp_rank, ep, ep_rank)))
+        leaves = layer_leaves(arch, l, tp, tp_rank, ep, ep_rank)
+        experts = [lf for lf in leaves if lf.name.endswith((".w13", ".w2"))]
+        blocks.append((f"layer{l}", [lf for lf in leaves if lf not in experts]))
+        if experts:
+            # expert weights are replicated over a different group (expert-DP), so
+            # they shard, reduce and offload as a block of their own
+            blocks.append((f"layer{l}.experts", experts))
     if with_head:
         blocks.append(("head", head_leaves(arch, tp, tp_rank)))
     return blocks

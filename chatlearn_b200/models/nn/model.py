@@ -75,7 +75,21 @@ class ParamBlock:
                 p = p.detach().requires_grad_(True)
                 self.params[key] = p
             o = self.offsets[lf.name]
-            p.grad = grad_flat[o:o + lf.numel].view(lf.shape)
+            gview = grad_flat[o:o + lf.numel].view(lf.shape)
+            if grad_flat.dtype == p.dtype:
+                p.grad = gview
+            elif not getattr(p, "_main_grad_hooked", False):
+                # wider accumulation buffer than the parameter dtype: fold each
+                # micro-batch gradient into it right after autograd produced it
+                p.main_grad = gview
+                p._main_grad_hooked = True
+
+                def _fold(param):
+                    param.main_grad.add_(param.grad)
+                    param.grad = None
+                p.register_post_accumulate_grad_hook(_fold)
+            else:
+                p.main_grad = gview
 
     def leaf_view(self, flat: torch.Tensor, lf: Leaf) -> torch.Tensor:
         o = self.offsets[lf.name]
@@ -273,7 +287,11 @@ class CausalLM:
                 yield lf.name, b.params[b.short(lf.name)], lf, b
 
     def layer_params(self, l: int) -> Dict[str, torch.Tensor]:
-        return self.block_by_name[f"layer{l}"].params
+        p = self.block_by_name[f"layer{l}"].params
+        ex = self.block_by_name.get(f"layer{l}.experts")
+        if ex is not None:
+            p = {**p, **ex.params}
+        return p
 
     def to_(self, device=None, dtype=None):
         for b in self.blocks:

@@ -1,0 +1,170 @@
+"""Sharded training state (ZeRO / FSDP2-style) over flat parameter blocks.
+
+The reference wraps HF models with torch ``fully_shard`` per decoder layer: bf16
+parameters all-gathered before every layer forward and backward, fp32 gradients
+reduce-scattered after every layer backward, AdamW on fp32 shards
+(chatlearn/models/fsdp_module.py:356-394).  This is a re-design for 180 GB GPUs:
+
+* compute-dtype parameters of every block stay resident and whole on each rank
+  (Qwen3-8B bf16 = 16 GB), so forward/backward need no per-layer all-gather;
+* gradients of all micro-batches of an optimizer step accumulate locally into
+  one flat buffer per block and are reduce-scattered **once per step**;
+* fp32 master weights and Adam moments exist only for this rank's 1/dp shard;
+  after the update the new compute-dtype shard is all-gathered back into the
+  resident parameters (or, with ``reshard=True``, gathered on demand per block
+  — the memory-lean mode for models that do not fit).
+
+Per optimizer step this moves 1 reduce-scatter + 1 all-gather of the model
+instead of (2 all-gathers + 1 reduce-scatter) × micro-batches.  The collectives
+are issued per block so they can overlap the backward of earlier blocks and the
+update of later ones; the fused NVLink kernels (reduce-scatter + AdamW on the
+owned shard, all-gather of the cast result) plug in through ``Group.fast``.
+"""
+import math
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from chatlearn_b200 import ops
+from chatlearn_b200.models.nn.model import CausalLM, ParamBlock
+from .groups import Group, single_group
+
+
+class BlockState:
+    """Optimizer-side state of one parameter block on one rank."""
+
+    def __init__(self, block: ParamBlock, group: Group, grad_dtype, device, trainable=True):
+        self.block, self.group = block, group
+        n = block.numel
+        assert n % group.size == 0, f"block {block.name}: {n} elements not divisible by {group.size}"
+        self.shard_numel = n // group.size
+        r = max(group.rank, 0)
+        self.lo, self.hi = r * self.shard_numel, (r + 1) * self.shard_numel
+        self.master = self.exp_avg = self.exp_avg_sq = self.grad = self.grad_shard = None
+        if trainable:
+            self.master = block.flat[self.lo:self.hi].float().clone()
+            self.exp_avg = torch.zeros_like(self.master)
+            self.exp_avg_sq = torch.zeros_like(self.master)
+            self.grad = torch.zeros(n, dtype=grad_dtype, device=device)
+            self.grad_shard = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+            block.enable_grad(self.grad)
+
+
+class ShardedTrainState:
+    def __init__(self, model: CausalLM, dp_group: Optional[Group] = None,
+                 expert_dp_group: Optional[Group] = None, lr=2e-6, betas=(0.9, 0.95), eps=1e-8,
+                 weight_decay=0.01, clip_grad=1.0, grad_dtype=torch.float32,
+                 extra_norm_groups: Optional[List[Group]] = None):
+        self.model = model
+        self.dp = dp_group or single_group()
+        self.edp = expert_dp_group or self.dp
+        self.lr, self.betas, self.eps, self.wd, self.clip = lr, betas, eps, weight_decay, clip_grad
+        self.step_count = 0
+        # groups over which the squared grad norm must still be summed after the DP
+        # shards are combined (tensor / expert / pipeline model parallel groups)
+        self.extra_norm_groups = extra_norm_groups or []
+        self.states: List[BlockState] = []
+        for b in model.blocks:
+            g = self.edp if b.name.endswith(".experts") else self.dp
+            self.states.append(BlockState(b, g, grad_dtype, model.device))
+        self.last_grad_norm = 0.0
+
+    # ------------------------------------------------------------------ step
+    def zero_grad(self):
+        for s in self.states:
+            s.grad.zero_()
+
+    @torch.no_grad()
+    def reduce_grads(self):
+        """Reduce-scatter every block's accumulated gradient into its fp32 shard."""
+        for s in self.states:
+            g = s.group
+            fused = g.fast.get("reduce_scatter_f32")
+            if fused is not None and s.grad.is_cuda:
+                fused(s.grad_shard, s.grad)
+            elif g.size == 1:
+                s.grad_shard.copy_(s.grad)
+            else:
+                src = s.grad if s.grad.dtype == torch.float32 else s.grad.float()
+                g.reduce_scatter_flat(s.grad_shard, src)
+
+    @torch.no_grad()
+    def grad_norm(self) -> torch.Tensor:
+        """Global L2 norm of the reduced gradient.  Leaves replicated inside a model
+        parallel group are counted once (their shard is identical on those ranks)."""
+        dev = self.model.device
+        dp_sq = torch.zeros((), dtype=torch.float32, device=dev)
+        edp_sq = torch.zeros((), dtype=torch.float32, device=dev)
+        for s in self.states:
+            v = ops.sumsq(s.grad_shard)
+            if s.group is self.edp and self.edp is not self.dp:
+                edp_sq += v
+            else:
+                dp_sq += v
+        self.dp.all_reduce_(dp_sq)
+        if self.edp is not self.dp:
+            self.edp.all_reduce_(edp_sq)
+        total = dp_sq + edp_sq
+        for g in self.extra_norm_groups:
+            g.all_reduce_(total)
+        return total.sqrt()
+
+    @torch.no_grad()
+    def step(self, lr: Optional[float] = None) -> float:
+        """reduce → clip → AdamW on the shard → all-gather the new parameters."""
+        self.reduce_grads()
+        norm = self.grad_norm()
+        self.last_grad_norm = norm
+        scale = 1.0
+        if self.clip and self.clip > 0:
+            # stays on device: no host sync between the norm and the update
+            scale = torch.clamp(self.clip / (norm + 1e-6), max=1.0)
+        self.step_count += 1
+        lr = self.lr if lr is None else lr
+        for s in self.states:
+            new_shard = s.block.flat[s.lo:s.hi]
+            ops.adamw_step(s.master, s.grad_shard, s.exp_avg, s.exp_avg_sq, new_shard,
+                           self.step_count, lr, self.betas[0], self.betas[1], self.eps, self.wd,
+                           scale)
+            if s.group.size > 1:
+                fused = s.group.fast.get("all_gather")
+                if fused is not None and new_shard.is_cuda:
+                    fused(s.block.flat, new_shard)
+                else:
+                    s.group.all_gather_flat(s.block.flat, new_shard.clone())
+        return norm
+
+    # ------------------------------------------------------------------ residency
+    def tensors_for(self, tag: str) -> List[List]:
+        """(owner object, attribute) pairs of the tensors behind a memory tag."""
+        out = []
+        for s in self.states:
+            if tag == "weights":
+                out.append((s.block, "flat"))
+            elif tag == "grads":
+                out.extend([(s, "grad"), (s, "grad_shard")])
+            elif tag == "optimizer":
+                out.extend([(s, "master"), (s, "exp_avg"), (s, "exp_avg_sq")])
+        return out
+
+    # ------------------------------------------------------------------ checkpoint
+    def state_dict(self) -> Dict:
+        return {
+            "step": self.step_count,
+            "blocks": {s.block.name: {"master": s.master.cpu(), "exp_avg": s.exp_avg.cpu(),
+                                      "exp_avg_sq": s.exp_avg_sq.cpu(), "lo": s.lo, "hi": s.hi,
+                                      "numel": s.block.numel} for s in self.states},
+        }
+
+    @torch.no_grad()
+    def load_state_dict(self, sd: Dict):
+        self.step_count = sd["step"]
+        for s in self.states:
+            b = sd["blocks"][s.block.name]
+            assert (b["lo"], b["hi"]) == (s.lo, s.hi), "checkpoint was written with another dp size"
+            s.master.copy_(b["master"])
+            s.exp_avg.copy_(b["exp_avg"])
+            s.exp_avg_sq.copy_(b["exp_avg_sq"])
+            s.block.flat[s.lo:s.hi].copy_(s.master)
+            if s.group.size > 1:
+                s.group.all_gather_flat(s.block.flat, s.block.flat[s.lo:s.hi].clone())

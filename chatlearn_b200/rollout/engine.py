@@ -1,0 +1,274 @@
+"""The rollout (generation) engine: paged KV cache, continuous batching, sampling.
+
+Takes the place of vLLM / SGLang in the reference
+(chatlearn/models/vllm_module.py:169-216,360-411, chatlearn/models/sglang_module.py:250-315):
+the engine owns a TP/EP-sharded copy of the policy weights in rollout layout, a
+paged KV cache, a continuous-batching scheduler and the sampler.  Memory is
+managed by tag like the reference's sleep/wake-up
+(vllm_module.py:442-469): ``weights`` and ``kv_cache`` can be released and
+re-created independently, so the trainer can use the memory between rollouts.
+"""
+import math
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Sequence as Seq
+
+import torch
+
+from chatlearn_b200 import ops
+from chatlearn_b200.models.nn.arch import ModelArch
+from chatlearn_b200.models.nn.model import CausalLM, FwdCtx, KVCtx
+from chatlearn_b200.utils.constant import TAG_KV_CACHE, TAG_WEIGHTS
+from .scheduler import Scheduler, Sequence, StepPlan
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    min_p: float = 0.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    max_tokens: int = 16
+    stop_token_ids: Seq[int] = ()
+    ignore_eos: bool = False
+
+    @property
+    def has_penalty(self):
+        return (self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
+                or self.repetition_penalty != 1.0)
+
+    def key(self):
+        return (self.temperature, self.top_p, self.top_k, self.min_p, self.presence_penalty,
+                self.frequency_penalty, self.repetition_penalty)
+
+
+class RolloutEngine:
+    def __init__(self, model: CausalLM, tp_group=None, ep_group=None, block_size: int = 64,
+                 num_blocks: Optional[int] = None, max_num_seqs: int = 256,
+                 max_num_batched_tokens: int = 32768, gpu_memory_utilization: float = 0.8,
+                 max_model_len: int = 4096, seed: int = 0, kv_dtype=None,
+                 lockstep_group=None):
+        self.model, self.arch = model, model.arch
+        self.device = model.device
+        self.tp, self.ep = tp_group, ep_group
+        self.block_size = block_size
+        self.max_num_seqs = max_num_seqs
+        self.max_tokens = max_num_batched_tokens
+        self.max_model_len = max_model_len
+        self.util = gpu_memory_utilization
+        self.kv_dtype = kv_dtype or model.dtype
+        self._num_blocks_cfg = num_blocks
+        self.k_cache: List[torch.Tensor] = []
+        self.v_cache: List[torch.Tensor] = []
+        self.num_blocks = 0
+        self.gen = torch.Generator(device=self.device)
+        self.gen.manual_seed(seed)
+        self.stats: Dict[str, float] = {}
+        self._req_counter = 0
+        # ranks that exchange tokens inside a forward (expert parallel) must run the
+        # same number of forwards: they agree on "anyone still busy" every step
+        self.lockstep = lockstep_group
+
+    # ------------------------------------------------------------------ memory
+    def kv_bytes_per_block(self) -> int:
+        a = self.arch
+        tp = self.tp.size if self.tp is not None else 1
+        if a.use_mla:
+            nkv_l = a.num_attention_heads // tp
+            per_tok = nkv_l * ((a.qk_nope_head_dim + a.qk_rope_head_dim) + a.v_head_dim)
+        else:
+            from chatlearn_b200.models.nn.layout import kv_head_range
+            nkv_l = kv_head_range(a, tp, 0)[1]
+            per_tok = nkv_l * a.head_dim * 2
+        esz = torch.empty((), dtype=self.kv_dtype).element_size()
+        return per_tok * esz * self.block_size * a.num_hidden_layers
+
+    def alloc_kv_cache(self):
+        if self.k_cache:
+            return
+        a = self.arch
+        tp = self.tp.size if self.tp is not None else 1
+        nb = self._num_blocks_cfg
+        if nb is None:
+            if self.device.type == "cuda":
+                free, total = torch.cuda.mem_get_info(self.device)
+                budget = int(free - (1.0 - self.util) * total)
+                nb = max(budget // self.kv_bytes_per_block(), 1)
+            else:
+                nb = 256
+            # never more than what max_num_seqs full-length sequences can use
+            cap = self.max_num_seqs * math.ceil(self.max_model_len / self.block_size) + 1
+            nb = min(nb, cap)
+            if self.tp is not None and self.tp.size > 1:
+                t = torch.tensor([nb], device=self.device)
+                import torch.distributed as dist
+                dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.tp.pg)
+                nb = int(t.item())
+        self.num_blocks = nb
+        if a.use_mla:
+            nkv_l = a.num_attention_heads // tp
+            dk, dv = a.qk_nope_head_dim + a.qk_rope_head_dim, a.v_head_dim
+        else:
+            from chatlearn_b200.models.nn.layout import kv_head_range
+            nkv_l = kv_head_range(a, tp, self.tp.rank if self.tp is not None else 0)[1]
+            dk = dv = a.head_dim
+        for _ in range(a.num_hidden_layers):
+            self.k_cache.append(torch.zeros(nb, self.block_size, nkv_l, dk, dtype=self.kv_dtype,
+                                            device=self.device))
+            self.v_cache.append(torch.zeros(nb, self.block_size, nkv_l, dv, dtype=self.kv_dtype,
+                                            device=self.device))
+
+    def free_kv_cache(self):
+        self.k_cache, self.v_cache = [], []
+        self.num_blocks = 0
+
+    # ------------------------------------------------------------------ one step
+    def _build_inputs(self, plan: StepPlan):
+        bs = self.block_size
+        toks, pos, slots, cu = [], [], [], [0]
+        max_blocks = max(len(s.blocks) for s in plan.seqs)
+        bt = torch.zeros(len(plan.seqs), max_blocks, dtype=torch.int32)
+        seq_lens, last_rows = [], []
+        for i, (s, n) in enumerate(zip(plan.seqs, plan.q_lens)):
+            start = s.num_computed
+            all_t = s.tokens
+            toks.extend(all_t[start:start + n])
+            pos.extend(range(start, start + n))
+            for p in range(start, start + n):
+                slots.append(s.blocks[p // bs] * bs + p % bs)
+            bt[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
+            seq_lens.append(start + n)
+            cu.append(cu[-1] + n)
+            last_rows.append(cu[-1] - 1)
+        dev = self.device
+        t = lambda x, dt: torch.tensor(x, dtype=dt).to(dev, non_blocking=True)  # noqa: E731
+        kv = KVCtx(self.k_cache, self.v_cache, t(slots, torch.long), bt.to(dev, non_blocking=True),
+                   t(seq_lens, torch.int32), t(plan.q_lens, torch.int32), plan.is_prefill)
+        ctx = FwdCtx(positions=t(pos, torch.long), cu_seqlens=t(cu, torch.int32),
+                     max_seqlen=max(plan.q_lens), kv=kv, tp=self.tp, ep=self.ep)
+        return t(toks, torch.long), ctx, t(last_rows, torch.long)
+
+    @torch.no_grad()
+    def _logits(self, hidden_last):
+        w = self.model.lm_head_weight()
+        logits = ops.linear(hidden_last, w).float()
+        if self.tp is not None and self.tp.size > 1 and w.shape[0] != self.arch.vocab_size:
+            logits = self.tp.all_gather_cat(logits, dim=1)
+        return logits
+
+    @torch.no_grad()
+    def step(self, sched: Scheduler, plan: StepPlan, eos_id: Optional[int]):
+        tokens, ctx, last_rows = self._build_inputs(plan)
+        hidden = self.model.hidden_states(tokens, ctx)
+        for s, n in zip(plan.seqs, plan.q_lens):
+            s.num_computed += n
+        rows = [i for i, smp in enumerate(plan.samples) if smp]
+        if not rows:
+            return
+        sel = last_rows[torch.tensor(rows, device=self.device)] if len(rows) != len(plan.seqs) else last_rows
+        logits = self._logits(hidden.index_select(0, sel))
+        seqs = [plan.seqs[i] for i in rows]
+        # group rows by sampling parameters (one kernel launch per distinct setting)
+        groups: Dict[Any, List[int]] = {}
+        for j, s in enumerate(seqs):
+            groups.setdefault(s.sampling.key(), []).append(j)
+        ids = torch.empty(len(seqs), dtype=torch.long, device=self.device)
+        lps = torch.empty(len(seqs), dtype=torch.float32, device=self.device)
+        u_all = torch.rand(len(seqs), device=self.device, generator=self.gen)
+        for key, js in groups.items():
+            sp = seqs[js[0]].sampling
+            jj = torch.tensor(js, device=self.device)
+            z = logits if len(js) == len(seqs) else logits.index_select(0, jj)
+            if sp.has_penalty:
+                V = z.shape[-1]
+                counts = torch.zeros(len(js), V, dtype=torch.int32, device=self.device)
+                pmask = torch.zeros(len(js), V, dtype=torch.bool, device=self.device)
+                for r, j in enumerate(js):
+                    if seqs[j].output:
+                        o = torch.tensor(seqs[j].output, device=self.device)
+                        counts[r].index_add_(0, o, torch.ones_like(o, dtype=torch.int32))
+                    pmask[r, torch.tensor(seqs[j].prompt, device=self.device)] = True
+                z = ops.apply_penalties(z, counts, sp.presence_penalty, sp.frequency_penalty,
+                                        sp.repetition_penalty, pmask)
+            i_, l_ = ops.sample(z, u_all if len(js) == len(seqs) else u_all.index_select(0, jj),
+                                sp.temperature, sp.top_k, sp.top_p, sp.min_p)
+            if len(js) == len(seqs):
+                ids, lps = i_, l_
+            else:
+                ids[jj], lps[jj] = i_, l_
+        ids_h, lps_h = ids.tolist(), lps.tolist()
+        for s, tok, lp in zip(seqs, ids_h, lps_h):
+            s.output.append(tok)
+            s.logprobs.append(lp)
+            sp = s.sampling
+            if not sp.ignore_eos and (tok == eos_id or tok in sp.stop_token_ids):
+                sched.finish(s, "stop")
+            elif len(s.output) >= s.max_new_tokens or s.length >= self.max_model_len:
+                sched.finish(s, "length")
+
+    @torch.no_grad()
+    def _idle_step(self):
+        """Forward of zero tokens: keeps this rank in the collectives of its peers."""
+        dev = self.device
+        z = lambda dt: torch.zeros(0, dtype=dt, device=dev)  # noqa: E731
+        kv = KVCtx(self.k_cache, self.v_cache, z(torch.long), torch.zeros(0, 1, dtype=torch.int32, device=dev),
+                   z(torch.int32), z(torch.int32), True)
+        ctx = FwdCtx(positions=z(torch.long), cu_seqlens=torch.zeros(1, dtype=torch.int32, device=dev),
+                     max_seqlen=0, kv=kv, tp=self.tp, ep=self.ep)
+        self.model.hidden_states(z(torch.long), ctx)
+
+    # ------------------------------------------------------------------ public
+    @torch.no_grad()
+    def generate(self, prompts: List[List[int]], sampling: Any, eos_id: Optional[int] = None,
+                 max_new_tokens: Optional[List[int]] = None) -> List[Sequence]:
+        """Generate for a batch of token-id prompts.  ``sampling`` is one
+        ``SamplingParams`` or a list (one per prompt); ``max_new_tokens`` optionally
+        overrides the per-request budget (partial rollout)."""
+        self.alloc_kv_cache()
+        eos_id = self.arch.eos_token_id if eos_id is None else eos_id
+        sched = Scheduler(self.num_blocks, self.block_size, self.max_num_seqs, self.max_tokens)
+        seqs = []
+        for i, p in enumerate(prompts):
+            sp = sampling[i] if isinstance(sampling, (list, tuple)) else sampling
+            mx = max_new_tokens[i] if max_new_tokens is not None else sp.max_tokens
+            mx = max(0, min(mx, self.max_model_len - len(p)))
+            s = Sequence(self._req_counter, list(p), mx, sp)
+            self._req_counter += 1
+            seqs.append(s)
+            if mx == 0:
+                s.finished, s.finish_reason = True, "length"
+            else:
+                sched.add(s)
+        while True:
+            busy = sched.has_work()
+            if self.lockstep is not None and self.lockstep.size > 1:
+                flag = torch.tensor([1 if busy else 0], device=self.device)
+                import torch.distributed as dist
+                self.lockstep.all_reduce_(flag, op=dist.ReduceOp.MAX)
+                if int(flag.item()) == 0:
+                    break
+                if not busy:
+                    self._idle_step()
+                    continue
+            elif not busy:
+                break
+            plan = sched.schedule()
+            if plan is None:
+                if self.lockstep is not None and self.lockstep.size > 1:
+                    self._idle_step()
+                    continue
+                break
+            self.step(sched, plan, eos_id)
+        self.stats = dict(sched.stats)
+        return seqs
+
+    # ------------------------------------------------------------------ sleep / wake
+    def offload(self, tags=(TAG_WEIGHTS, TAG_KV_CACHE)):
+        if TAG_KV_CACHE in tags:
+            self.free_kv_cache()
+
+    def onload(self, tags=(TAG_WEIGHTS, TAG_KV_CACHE)):
+        if TAG_KV_CACHE in tags:
+            self.alloc_kv_cache()

@@ -1,0 +1,185 @@
+"""SPMD executor of a traced model flow.
+
+Parity: chatlearn/runtime/executor.py:62-463 (graph execution per level, DP
+regrouping between producers and consumers of different data-parallel size,
+onload/offload flags for colocated models) and chatlearn/runtime/decorator.py
+(data fetch/merge, timers, consumed samples).  The reference drives Ray actors
+through queues of object refs and ships every stage output through the object
+store.  Here every rank runs the same loop: for each node, the ranks hosting the
+node's model run it on their slice of the episode's sample list; the keys a node
+added are then exchanged so that every rank holds the complete, identically
+ordered list (only the delta travels, and not at all when consumer and producer
+partition the data the same way).
+"""
+import time
+from typing import Any, Callable, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from chatlearn_b200.runtime.model_flow import ModelFlow, ModelNode
+from chatlearn_b200.utils.logger import logger
+from chatlearn_b200.utils.utils import even_slice
+
+
+def _world():
+    return dist.get_world_size() if dist.is_initialized() else 1
+
+
+def _rank():
+    return dist.get_rank() if dist.is_initialized() else 0
+
+
+def all_gather_objects(obj) -> List[Any]:
+    if _world() == 1:
+        return [obj]
+    out = [None] * _world()
+    dist.all_gather_object(out, obj)
+    return out
+
+
+class Executor:
+    def __init__(self, model_flow: Callable):
+        self._flow_fn = model_flow
+        self.models: List = []
+        self.model_flow: Optional[ModelFlow] = None
+        self.timers = None
+        self.global_args = None
+        self._metric_prefix = "executor"
+        self._metric_list: List[Dict] = []
+        self.is_eval = False
+
+    # ------------------------------------------------------------------ wiring
+    def set_timers(self, timers):
+        self.timers = timers
+
+    def update_models(self, models):
+        """Keep the models this flow touches (found by tracing)."""
+        flow = ModelFlow(models).trace(self._flow_fn)
+        used = []
+        for n in flow.model_nodes:
+            if n.model not in used:
+                used.append(n.model)
+        self.models = used
+        self.model_flow = flow
+        return self
+
+    def setup(self):
+        if self.model_flow is None:
+            raise RuntimeError("update_models() must be called before setup()")
+
+    @property
+    def first_node(self) -> ModelNode:
+        return self.model_flow.flow_topology[0][0]
+
+    def first_model(self):
+        return self.first_node.model
+
+    # ------------------------------------------------------------------ execution
+    def _residency_flags(self, model, step: int, num_steps: int):
+        """to_onload for the first step, to_offload for the last, only for colocated
+        models that asked for memory to be freed (executor.py:396-403)."""
+        fg = getattr(model.module_args, "free_gpu_memory", None)
+        wants = fg is not None and (fg.offload_weights or fg.free_grad_buffers or fg.offload_optimizer_states)
+        on = model.is_colocate and wants
+        return on and step == 0, on and step == num_steps - 1
+
+    def _run_node(self, node: ModelNode, my_samples: List[Dict], iteration: int, kwargs: Dict) -> List[Dict]:
+        """Run one node on this rank's slice in batches of generation_batch_size."""
+        model = node.model
+        fn = getattr(model, node.func_name)
+        bs = int(getattr(model.module_args, "generation_batch_size", 0) or 0)
+        if node.func_name == "train_step" or bs <= 0:
+            bs = max(len(my_samples), 1)
+        chunks = [my_samples[s:s + bs] for s in range(0, len(my_samples), bs)] or [[]]
+        out: List[Dict] = []
+        tname = f"{model.name}.{node.func_name}"
+        for i, chunk in enumerate(chunks):
+            to_onload, to_offload = self._residency_flags(model, i, len(chunks))
+            if to_onload:
+                model.onload()
+            model.timers(node.func_name).start()
+            res = fn(chunk, iteration, **kwargs) if node.func_name != "train_step" else fn(chunk, **kwargs)
+            model.timers(node.func_name).stop()
+            if res is not None:
+                out.extend(res)
+            # rollout engines stay resident during evaluation (decorator.py:134-136)
+            if to_offload and not (self.is_eval and node is self.first_node):
+                model.offload()
+        return out
+
+    def execute_flow(self, samples_by_rank_fn: Callable[[Any], List[Dict]], iteration: int,
+                     is_eval: bool = False) -> Dict[ModelNode, List[Dict]]:
+        """Run the traced flow once over an episode.
+
+        ``samples_by_rank_fn(model)`` produces the *input* of the first node on the
+        ranks that host it (this replica's prompts).  Returns, for every return
+        node, the complete sample list in global order (identical on all ranks)."""
+        self.is_eval = is_eval
+        flow = self.model_flow
+        results: Dict[ModelNode, List[Dict]] = {}
+        partition: Dict[ModelNode, Any] = {}
+        kwargs = {"is_eval": True} if is_eval else {}
+        for level in flow.flow_topology:
+            for node in level:
+                model = node.model
+                dp_size = model.data_parallel_size
+                dp_rank = model.data_parallel_rank if model.is_member else -1
+                ins = [n for n in node.input_nodes if n is not None]
+                if not ins:
+                    mine = samples_by_rank_fn(model) if model.is_member else []
+                    start = None
+                else:
+                    merged = results[ins[0]]
+                    for other in ins[1:]:
+                        merged = [{**a, **b} for a, b in zip(merged, results[other])]
+                    b = even_slice(len(merged), dp_size)
+                    if model.is_member:
+                        start = b[dp_rank]
+                        mine = merged[b[dp_rank]:b[dp_rank + 1]]
+                    else:
+                        start, mine = None, []
+                before = [dict(s) for s in mine] if ins else None
+                out = self._run_node(node, mine, iteration, kwargs) if model.is_member else []
+                if node.func_name == "train_step":
+                    results[node] = []
+                    continue
+                # ---- exchange what this node produced ----
+                lead = model.is_member and model.is_data_leader
+                if not ins:
+                    payload = (dp_rank, out) if lead else None
+                    parts = [p for p in all_gather_objects(payload) if p is not None]
+                    parts.sort(key=lambda p: p[0])
+                    results[node] = [s for _, lst in parts for s in lst]
+                else:
+                    if len(out) != len(mine):
+                        # the node re-shaped the sample list (e.g. a manager that filters):
+                        # ship whole samples
+                        payload = (dp_rank, out, True) if lead else None
+                    else:
+                        delta = []
+                        for o, b4 in zip(out, before):
+                            delta.append({k: v for k, v in o.items()
+                                          if k not in b4 or b4[k] is not v})
+                        payload = (dp_rank, delta, False) if lead else None
+                    parts = [p for p in all_gather_objects(payload) if p is not None]
+                    parts.sort(key=lambda p: p[0])
+                    if any(p[2] for p in parts):
+                        results[node] = [s for _, lst, _ in parts for s in lst]
+                    else:
+                        full = [dict(s) for s in merged]
+                        bnd = even_slice(len(full), dp_size)
+                        for r, delta, _ in parts:
+                            for j, d in enumerate(delta):
+                                full[bnd[r] + j].update(d)
+                        results[node] = full
+        return {n: results[n] for n in flow.return_nodes}
+
+    # ------------------------------------------------------------------ metrics
+    def get_and_clear_metrics(self):
+        from chatlearn_b200.utils.utils import map_reduce_metrics
+        if not self._metric_list:
+            return self._metric_prefix, {}
+        m = map_reduce_metrics(self._metric_list)
+        self._metric_list = []
+        return self._metric_prefix, m
