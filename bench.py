@@ -1,0 +1,267 @@
+"""Flagship benchmark: GRPO samples/sec and step time (rollout + sync + train).
+
+    python bench.py --gpus N --steps K --warmup W
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = one GRPO episode through the public ``Engine`` API: rollout with the
+native engine → old / reference log-probs → rule reward → group advantages →
+optimizer steps → trainer→rollout weight sync.  Model and workload follow the
+Qwen3-8B GRPO configuration (36 layers, hidden 4096, 32/8 heads, FFN 12288, vocab
+151936; 16 prompts x 8 samples per GPU, prompts uniform in [128, 1024] tokens,
+responses up to 2048 tokens, packing to 16k tokens, 2 mini-batches per step,
+optimizer offload during rollout), with synthetic prompts, the hash reward and
+random-init weights.  Per-GPU work is fixed as N grows (weak scaling).
+
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=2)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="native", choices=["native", "library", "reference"])
+    p.add_argument("--model", default="qwen3_8b")
+    p.add_argument("--prompts-per-gpu", type=int, default=16)
+    p.add_argument("--samples-per-prompt", type=int, default=8)
+    p.add_argument("--prompt-len", type=int, nargs=2, default=[128, 1024])
+    p.add_argument("--max-response", type=int, default=2048)
+    p.add_argument("--pack-tokens", type=int, default=16384)
+    p.add_argument("--gemm", default=None, choices=[None, "tcgen05", "cublas"])
+    p.add_argument("--no-offload", action="store_true")
+    return p.parse_args()
+
+
+def reference_arm(args):
+    """The unmodified reference cannot run here: importing its public API fails."""
+    why = None
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        import chatlearn  # noqa: F401
+        from chatlearn.runtime.engine import Engine  # noqa: F401
+    except Exception as e:  # noqa: BLE001
+        why = f"reference public API does not import offline ({type(e).__name__}: {e}); " \
+              "it needs ray, hydra/omegaconf and vllm==0.8.5, none installed"
+    if why is None:
+        why = "reference imports but needs a Ray cluster, Megatron/FSDP HF weights and vllm==0.8.5 to run"
+    print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:300]}))
+    return 0
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason sampling during the timed region (rank 0)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, enabled):
+        self.proc, self.path = None, None
+        if enabled:
+            self.path = tempfile.mktemp(suffix=".csv")
+            try:
+                self.proc = subprocess.Popen(
+                    ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                    stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            except OSError:
+                self.proc = None
+
+    def stop(self, gpu_index=0):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9 or f[0] != str(gpu_index):
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            # under load = samples in the upper half of the observed power/clock activity
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons),
+                       samples=len(sm))
+        return out
+
+
+def build_config(args, out_dir, data_path, n_gpu):
+    tp = 2 if n_gpu >= 2 else 1
+    n = args.samples_per_prompt
+    spe = args.prompts_per_gpu * n * n_gpu
+    offload = not args.no_offload
+    arch = {"preset": args.model}
+    seq = args.prompt_len[1] + args.max_response
+    common = {"model_arch": arch, "packing": True, "max_token_in_packing": args.pack_tokens,
+              "max_prompt_tokens_length": args.prompt_len[1] + 1, "max_response_tokens_length": args.max_response}
+    return {
+        "runtime_args": {
+            "train_backend": "fsdp", "rollout_backend": "native", "exp_name": "bench",
+            "colocation": ["policy", "policy_trainer", "ref_policy"], "output_dir": out_dir,
+            "data_path": data_path, "num_episode": args.steps + args.warmup, "sample_per_episode": spe,
+            "train_micro_batch_size": 1, "train_global_batch_size": spe // 2, "num_inference_per_prompt": n,
+            "save_episode_interval": 10 ** 9, "max_replay_episode": 1, "data_shuffle": False,
+            "enable_resume_training": False, "log_args_dict": {"log_dir": out_dir}},
+        "models": {
+            "policy_trainer": dict(common, num_gpu=n_gpu, fsdp_size=n_gpu, trainable=True,
+                                   generation_batch_size=spe, kl_coef=0.001, gradient_checkpointing=True,
+                                   optimizer={"lr": 2e-6}, save_hf=False,
+                                   free_gpu_memory={"offload_weights": False, "offload_optimizer_states": offload,
+                                                    "free_grad_buffers": offload}),
+            "ref_policy": dict(common, num_gpu=n_gpu, fsdp_size=n_gpu, generation_batch_size=spe,
+                               free_gpu_memory={"offload_weights": offload}),
+            "policy": dict(common, num_gpu=n_gpu, tensor_model_parallel_size=tp, generation_batch_size=spe,
+                           num_inference_per_prompt=n, temperature=1.0, top_p=1.0, top_k=-1,
+                           gpu_memory_utilization=0.85, max_num_seqs=256, kv_block_size=64,
+                           max_num_batched_tokens=16384, ignore_eos=True,
+                           free_gpu_memory={"offload_weights": offload}),
+            "reward": {"num_cpu": n_gpu, "synthetic_reward": "hash30"},
+        }}, seq
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+    import torch
+    import torch.distributed as dist
+    from chatlearn_b200 import ops
+    from chatlearn_b200.algorithm.grpo import GrpoAlgorithm, GrpoConfig
+    from chatlearn_b200.configs import resolve, to_dataclass
+    from chatlearn_b200.data.synthetic import make_prompts, write_jsonl
+    from chatlearn_b200.models.nn import PRESETS
+    from chatlearn_b200.utils import xfer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if args.gpus > 1 and world == 1:
+        # convenience: re-launch under torchrun when started as a plain script
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29577", os.path.abspath(__file__)] + sys.argv[1:]
+        return subprocess.call(cmd)
+    assert torch.cuda.is_available(), "bench.py needs CUDA devices"
+    if world == 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29578")
+        os.environ.setdefault("RANK", "0"); os.environ.setdefault("WORLD_SIZE", "1"); os.environ.setdefault("LOCAL_RANK", "0")
+    ops.set_mode("library" if args.impl == "library" else "native")
+    if args.gemm:
+        from chatlearn_b200.ops import native
+        native.set_gemm_impl(args.gemm)
+
+    out_dir = os.environ.get("BENCH_OUT", os.path.join(tempfile.gettempdir(), f"clb200_bench_{os.getpid() if world == 1 else os.environ.get('MASTER_PORT', '0')}"))
+    os.makedirs(out_dir, exist_ok=True)
+    data_path = os.path.join(out_dir, "prompts.jsonl")
+    arch = PRESETS[args.model]()
+    total_steps = args.steps + args.warmup
+    if rank == 0:
+        rows = make_prompts(args.prompts_per_gpu * world * total_steps, args.prompt_len[0], args.prompt_len[1],
+                            arch.vocab_size, seed=1234, data_source="synthetic:hash30")
+        write_jsonl(rows, data_path + ".tmp")
+        os.replace(data_path + ".tmp", data_path)
+    while not os.path.exists(data_path):
+        time.sleep(0.05)
+
+    cfg_dict, seq = build_config(args, out_dir, data_path, world)
+    cfg = to_dataclass(GrpoConfig, resolve(cfg_dict))
+    algo = GrpoAlgorithm(cfg)
+    algo.validate()
+    engine = algo.build_engine()
+    engine.prepare()
+
+    def barrier():
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for ep in range(args.warmup):
+        engine.run_episode(ep)
+    barrier()
+    sampler = ClockSampler(rank == 0)
+    xfer.reset()
+    launches0 = sum(ops.launch_counts.values())
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    ev0.record()
+    summaries = []
+    for ep in range(args.warmup, total_steps):
+        summaries.append(engine.run_episode(ep))
+    ev1.record()
+    barrier()
+    wall = time.perf_counter() - t0
+    dev_ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop(int(os.environ.get("LOCAL_RANK", "0")))
+    t = torch.tensor([dev_ms, wall * 1e3], dtype=torch.float64, device="cuda")
+    cnt = torch.tensor([float(sum(ops.launch_counts.values()) - launches0), float(xfer.h2d_bytes), float(xfer.d2h_bytes)],
+                       dtype=torch.float64, device="cuda")
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(cnt, op=dist.ReduceOp.SUM)
+    dev_ms, wall_ms = t.tolist()
+    launches, h2d, d2h = cnt.tolist()
+    if rank == 0:
+        K = args.steps
+        samples = cfg.runtime_args.sample_per_episode
+        ms_per_step = dev_ms / K
+        value = samples / (ms_per_step / 1e3)
+        tokens = sum(s.get("tps_throughput", 0.0) * s.get("episode", 0.0) for s in summaries) / max(K, 1)
+        phases = {k: sum(s.get(k, 0.0) for s in summaries) / K for k in ("environment", "train", "sync_parameters")}
+        tr = engine.named_models["policy_trainer"]
+        sync_ms = [g.last_ms for g in engine.model_manager.parameter_sync_groups.values()]
+        line = {
+            "metric": "GRPO samples/sec (rollout+sync+train step)", "value": round(value, 4), "unit": "samples/s",
+            "n_gpus": world, "steps": K, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 2),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": args.impl,
+            "config": {"model": args.model, "global_batch": samples, "seq_len": seq,
+                       "parallelism": f"trainer zero-dp{world} + rollout tp{2 if world >= 2 else 1}x{max(world // 2, 1) if world >= 2 else 1}",
+                       "prompts": samples // args.samples_per_prompt, "samples_per_prompt": args.samples_per_prompt,
+                       "prompt_len": args.prompt_len, "max_response": args.max_response,
+                       "pack_tokens": args.pack_tokens, "mini_batches_per_step": 2,
+                       "l2_policy": "inputs larger than L2 (16 GB of weights + KV streamed every step)",
+                       "gemm": __import__("chatlearn_b200.ops.native", fromlist=["x"]).get_gemm_impl() if args.impl == "native" else "cublas"},
+            "step_time_s": round(ms_per_step / 1e3, 3),
+            "phase_s": {k: round(v, 3) for k, v in phases.items()},
+            "weight_sync_ms": round(max(sync_ms), 3) if sync_ms else None,
+            "tokens_per_s": round(tokens / (ms_per_step / 1e3), 1) if tokens else None,
+            "rollout_tok_per_s": round(samples * args.max_response / max(phases["environment"], 1e-9), 1),
+            "clocks": clocks,
+            "e2e": {"value": round(samples / (wall_ms / 1e3 / K), 4), "unit": "samples/s",
+                    "h2d_bytes_per_step": int(h2d / K), "d2h_bytes_per_step": int(d2h / K),
+                    "how": "host wall clock around the same K episodes driven through Engine.run_episode"},
+            "gpu_launches": int(launches),
+            "library_calls": {k: int(v) for k, v in ops.library_counts.items()},
+        }
+        print(json.dumps(line))
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

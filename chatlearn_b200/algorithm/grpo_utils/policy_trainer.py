@@ -20,6 +20,7 @@ import torch.distributed as dist
 from chatlearn_b200 import ops
 from chatlearn_b200.models.fsdp_module import FSDPModule
 from chatlearn_b200.models.nn import FwdCtx
+from chatlearn_b200.utils import xfer
 from .trainer_utils import pack_samples, split_microbatch, unpack_per_sample
 
 
@@ -62,7 +63,16 @@ class PolicyTrainer(FSDPModule):
 
     def _logprobs(self, batch, need_entropy: bool):
         tokens, labels, ctx = self._ctx_and_inputs(batch)
-        lp, ent = self.model.logprobs(tokens, labels, ctx)
+        hook = None
+        if torch.is_grad_enabled() and getattr(self.module_args, "gradient_checkpointing", False):
+            # keep only each layer's input; its activations are recomputed in backward
+            from torch.utils.checkpoint import checkpoint
+            from chatlearn_b200.models.nn.model import decoder_layer
+            arch = self.model.arch
+
+            def hook(l, p, x, c):
+                return checkpoint(lambda xx: decoder_layer(arch, p, xx, c, l), x, use_reentrant=False)
+        lp, ent = self.model.logprobs(tokens, labels, ctx, layer_hook=hook)
         if self.sp is not None:
             lp = self.sp.gather(lp)
             ent = self.sp.gather(ent) if need_entropy else None
@@ -142,10 +152,11 @@ class PolicyTrainer(FSDPModule):
             self.role_group.all_reduce_(stats)
             if self.sp is not None:
                 stats /= self.sp.size
-        n = max(float(stats[5].item()), 1.0)
+        # one device->host read per optimizer step: the loss statistics and the grad norm
+        host = xfer.tolist(torch.cat([stats, grad_norm.reshape(1).float()]))
+        n = max(host[5], 1.0)
         self._metric_list.append({
-            "pg_loss": float(stats[0].item()) / n, "kl_loss": float(stats[1].item()) / n,
-            "entropy_loss": float(stats[2].item()) / n, "grad_norm": float(grad_norm),
-            "clip_pos_frac": float(stats[3].item()) / n, "clip_neg_frac": float(stats[4].item()) / n,
+            "pg_loss": host[0] / n, "kl_loss": host[1] / n, "entropy_loss": host[2] / n,
+            "grad_norm": host[6], "clip_pos_frac": host[3] / n, "clip_neg_frac": host[4] / n,
             "train_tokens": n})
         self._train_iteration += 1

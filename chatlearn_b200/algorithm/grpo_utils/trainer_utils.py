@@ -13,6 +13,7 @@ from typing import Any, Dict, List, Optional
 
 import torch
 
+from chatlearn_b200.utils import xfer
 from chatlearn_b200.utils.utils import even_slice
 
 
@@ -52,7 +53,7 @@ class PackedBatch:
     def to(self, device):
         for k, v in vars(self).items():
             if isinstance(v, torch.Tensor):
-                setattr(self, k, v.to(device, non_blocking=True))
+                setattr(self, k, xfer.to_device(v, device, f"batch.{k}"))
         return self
 
     @property

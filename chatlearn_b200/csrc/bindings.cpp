@@ -1,0 +1,67 @@
+// Python bindings of the sm_100a extension (module chatlearn_b200._C).
+#include <torch/extension.h>
+
+std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps);
+std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& x, const at::Tensor& w, const at::Tensor& dy,
+                                    const at::Tensor& rstd);
+at::Tensor swiglu_fwd(const at::Tensor& gu);
+at::Tensor swiglu_bwd(const at::Tensor& gu, const at::Tensor& dy);
+at::Tensor qk_norm_rope_fwd(const at::Tensor& x, int64_t n_heads, int64_t D, const c10::optional<at::Tensor>& w,
+                            const at::Tensor& pos, const at::Tensor& inv_freq, double eps);
+at::Tensor qk_norm_rope_bwd(const at::Tensor& dy, const at::Tensor& x, at::Tensor dx_out, int64_t n_heads,
+                            int64_t D, const c10::optional<at::Tensor>& w, const at::Tensor& pos,
+                            const at::Tensor& inv_freq, double eps);
+std::vector<at::Tensor> grpo_loss_fwd(const at::Tensor& lp, const at::Tensor& old,
+                                      const c10::optional<at::Tensor>& ref, const at::Tensor& adv,
+                                      const at::Tensor& mask, const c10::optional<at::Tensor>& ent,
+                                      double pos_clip, double neg_clip, double diff_clip, double final_clip,
+                                      double kl_coef, double ent_coef, double inv_norm);
+void adamw_step(at::Tensor master, const at::Tensor& grad, at::Tensor m, at::Tensor v,
+                const c10::optional<at::Tensor>& out, int64_t step, double lr, double b1, double b2, double eps,
+                double wd, const c10::optional<at::Tensor>& scale_t, double scale_v);
+at::Tensor sumsq(const at::Tensor& x);
+std::vector<at::Tensor> logits_stats(const at::Tensor& z, const at::Tensor& labels, double inv_temp);
+at::Tensor logits_grad(const at::Tensor& z, const at::Tensor& labels, const at::Tensor& lse,
+                       const at::Tensor& ent, const at::Tensor& g_lp, const c10::optional<at::Tensor>& g_ent,
+                       double inv_temp, bool out_bf16);
+std::vector<at::Tensor> sample(const at::Tensor& logits, const at::Tensor& u, double temperature, int64_t top_k,
+                               double top_p, double min_p);
+at::Tensor apply_penalties(const at::Tensor& logits, const at::Tensor& counts,
+                           const c10::optional<at::Tensor>& prompt_mask, double presence, double frequency,
+                           double repetition);
+void kv_append(const at::Tensor& k, const at::Tensor& v, at::Tensor k_cache, at::Tensor v_cache,
+               const at::Tensor& slots);
+bool paged_decode_supported(int64_t dk, int64_t dv, int64_t bs, int64_t rep);
+at::Tensor paged_decode(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
+                        const at::Tensor& block_tables, const c10::optional<at::Tensor>& q_seq,
+                        const at::Tensor& ctx_len, double scale, int64_t num_splits);
+void weight_sync_run(const at::Tensor& desc_table, int64_t num_descs, int64_t total_tiles, int64_t src_dtype,
+                     int64_t dst_dtype);
+int64_t weight_sync_desc_size();
+int64_t weight_sync_tile_elems();
+at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32);
+int64_t gemm_last_status();
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
+  m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
+  m.def("grpo_loss_fwd", &grpo_loss_fwd);
+  m.def("adamw_step", &adamw_step);
+  m.def("sumsq", &sumsq);
+  m.def("logits_stats", &logits_stats);
+  m.def("logits_grad", &logits_grad);
+  m.def("sample", &sample);
+  m.def("apply_penalties", &apply_penalties);
+  m.def("kv_append", &kv_append);
+  m.def("paged_decode_supported", &paged_decode_supported);
+  m.def("paged_decode", &paged_decode);
+  m.def("weight_sync_run", &weight_sync_run);
+  m.def("weight_sync_desc_size", &weight_sync_desc_size);
+  m.def("weight_sync_tile_elems", &weight_sync_tile_elems);
+  m.def("gemm_bf16_nt", &gemm_bf16_nt);
+  m.def("gemm_last_status", &gemm_last_status);
+}

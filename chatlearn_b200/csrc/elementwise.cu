@@ -1,0 +1,541 @@
+// Memory-bound training kernels: RMSNorm, fused per-head QK-norm + RoPE, SwiGLU,
+// the fused GRPO loss (forward + gradient in one pass), AdamW on a shard and a
+// deterministic sum of squares.  Each replaces a chain of eager PyTorch kernels
+// of the reference stack (HF/Megatron model internals, loss_gallery.py, torch
+// AdamW); all are single-pass over their operands.
+#include <ATen/cuda/CUDAContext.h>
+#include <torch/extension.h>
+
+#include "common.cuh"
+
+using namespace cl;
+typedef __nv_bfloat16 bf16;
+
+#define DISPATCH_FLOAT_BF16(TENSOR, NAME, ...)                                    \
+  if ((TENSOR).scalar_type() == at::kFloat) {                                    \
+    using scalar_t = float;                                                      \
+    __VA_ARGS__();                                                               \
+  } else if ((TENSOR).scalar_type() == at::kBFloat16) {                          \
+    using scalar_t = bf16;                                                       \
+    __VA_ARGS__();                                                               \
+  } else {                                                                       \
+    TORCH_CHECK(false, NAME ": dtype must be float32 or bfloat16");               \
+  }
+
+static inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream(); }
+
+// ----------------------------------------------------------------------------- RMSNorm
+// One CTA per row.  y = x * rsqrt(mean(x^2) + eps) * w ; rstd saved for backward.
+template <typename T>
+__global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                                   float* __restrict__ rstd, int H, float eps) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * H;
+  T* yr = y + row * H;
+  constexpr int V = Vec16<T>::N;
+  float ss = 0.f;
+  for (int i = threadIdx.x * V; i < H; i += blockDim.x * V) {
+    Vec16<T> a = ld16(xr + i);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      float f = Cvt<T>::to_f(a.v[j]);
+      ss += f * f;
+    }
+  }
+  ss = block_sum(ss, red);
+  const float r = rsqrtf(ss / H + eps);
+  if (threadIdx.x == 0 && rstd) rstd[row] = r;
+  for (int i = threadIdx.x * V; i < H; i += blockDim.x * V) {
+    Vec16<T> a = ld16(xr + i), ww = ld16(w + i), o;
+#pragma unroll
+    for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(Cvt<T>::to_f(a.v[j]) * r * Cvt<T>::to_f(ww.v[j]));
+    st16(yr + i, o);
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)); dw += dy * xhat (fp32 atomics, one
+// partial per CTA: each CTA walks a strided set of rows and keeps dw in registers).
+template <typename T, int MAXV>
+__global__ void rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                   const T* __restrict__ dy, const float* __restrict__ rstd,
+                                   T* __restrict__ dx, float* __restrict__ dw, int64_t N, int H) {
+  __shared__ float red[32];
+  constexpr int V = Vec16<T>::N;
+  float dwacc[MAXV][V];
+#pragma unroll
+  for (int a = 0; a < MAXV; ++a)
+#pragma unroll
+    for (int j = 0; j < V; ++j) dwacc[a][j] = 0.f;
+  for (int64_t row = blockIdx.x; row < N; row += gridDim.x) {
+    const T* xr = x + row * H;
+    const T* dyr = dy + row * H;
+    const float r = rstd[row];
+    float dot = 0.f;
+    int a = 0;
+    for (int i = threadIdx.x * V; i < H; i += blockDim.x * V, ++a) {
+      Vec16<T> xv = ld16(xr + i), gv = ld16(dyr + i), wv = ld16(w + i);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        float xh = Cvt<T>::to_f(xv.v[j]) * r;
+        float g = Cvt<T>::to_f(gv.v[j]);
+        dot += g * Cvt<T>::to_f(wv.v[j]) * xh;
+        if (a < MAXV) dwacc[a][j] += g * xh;
+      }
+    }
+    dot = block_sum(dot, red) / H;
+    for (int i = threadIdx.x * V; i < H; i += blockDim.x * V) {
+      Vec16<T> xv = ld16(xr + i), gv = ld16(dyr + i), wv = ld16(w + i), o;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        float xh = Cvt<T>::to_f(xv.v[j]) * r;
+        o.v[j] = Cvt<T>::from_f(r * (Cvt<T>::to_f(gv.v[j]) * Cvt<T>::to_f(wv.v[j]) - xh * dot));
+      }
+      st16(dx + row * H + i, o);
+    }
+  }
+  int a = 0;
+  for (int i = threadIdx.x * V; i < H; i += blockDim.x * V, ++a) {
+    if (a < MAXV) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) atomicAdd(dw + i + j, dwacc[a][j]);
+    }
+  }
+}
+
+std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && w.is_contiguous(), "rmsnorm: contiguous CUDA tensors");
+  const int H = x.size(-1);
+  const int64_t N = x.numel() / H;
+  TORCH_CHECK(w.numel() == H && w.scalar_type() == x.scalar_type(), "rmsnorm: weight mismatch");
+  auto y = at::empty_like(x);
+  auto rstd = at::empty({N}, x.options().dtype(at::kFloat));
+  if (N == 0) return {y, rstd};
+  DISPATCH_FLOAT_BF16(x, "rmsnorm", [&] {
+    constexpr int V = Vec16<scalar_t>::N;
+    TORCH_CHECK(H % V == 0, "rmsnorm: hidden size must be a multiple of ", V);
+    int threads = std::min(1024, std::max(32, ((H / V + 31) / 32) * 32));
+    rmsnorm_fwd_kernel<scalar_t><<<N, threads, 0, cur_stream()>>>(
+        (const scalar_t*)x.data_ptr(), (const scalar_t*)w.data_ptr(), (scalar_t*)y.data_ptr(),
+        rstd.data_ptr<float>(), H, (float)eps);
+  });
+  return {y, rstd};
+}
+
+std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& x, const at::Tensor& w, const at::Tensor& dy,
+                                    const at::Tensor& rstd) {
+  const int H = x.size(-1);
+  const int64_t N = x.numel() / H;
+  auto dx = at::empty_like(x);
+  auto dw = at::zeros({H}, x.options().dtype(at::kFloat));
+  if (N == 0) return {dx, dw};
+  auto dyc = dy.contiguous();
+  DISPATCH_FLOAT_BF16(x, "rmsnorm_bwd", [&] {
+    constexpr int V = Vec16<scalar_t>::N;
+    constexpr int MAXV = 4;
+    int threads = std::min(1024, std::max(32, ((H / V + MAXV - 1) / MAXV + 31) / 32 * 32));
+    // every thread owns at most MAXV vectors of the row
+    while ((int64_t)threads * V * MAXV < H) threads += 32;
+    TORCH_CHECK(threads <= 1024, "rmsnorm_bwd: hidden size too large");
+    int grid = (int)std::min<int64_t>(N, 148 * 4);
+    rmsnorm_bwd_kernel<scalar_t, MAXV><<<grid, threads, 0, cur_stream()>>>(
+        (const scalar_t*)x.data_ptr(), (const scalar_t*)w.data_ptr(), (const scalar_t*)dyc.data_ptr(),
+        rstd.data_ptr<float>(), (scalar_t*)dx.data_ptr(), dw.data_ptr<float>(), N, H);
+  });
+  return {dx, dw};
+}
+
+// ----------------------------------------------------------------------------- SwiGLU
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ gu, T* __restrict__ y, int64_t rows, int F) {
+  constexpr int V = Vec16<T>::N;
+  const int64_t nvec = rows * (F / V);
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < nvec;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / (F / V);
+    const int c = (idx % (F / V)) * V;
+    Vec16<T> g = ld16(gu + r * 2 * F + c), u = ld16(gu + r * 2 * F + F + c), o;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      float gf = Cvt<T>::to_f(g.v[j]);
+      o.v[j] = Cvt<T>::from_f(gf / (1.f + __expf(-gf)) * Cvt<T>::to_f(u.v[j]));
+    }
+    st16(y + r * F + c, o);
+  }
+}
+
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ gu, const T* __restrict__ dy, T* __restrict__ dgu,
+                                  int64_t rows, int F) {
+  constexpr int V = Vec16<T>::N;
+  const int64_t nvec = rows * (F / V);
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < nvec;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / (F / V);
+    const int c = (idx % (F / V)) * V;
+    Vec16<T> g = ld16(gu + r * 2 * F + c), u = ld16(gu + r * 2 * F + F + c), d = ld16(dy + r * F + c), og, ou;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      float gf = Cvt<T>::to_f(g.v[j]), uf = Cvt<T>::to_f(u.v[j]), df = Cvt<T>::to_f(d.v[j]);
+      float s = 1.f / (1.f + __expf(-gf));
+      og.v[j] = Cvt<T>::from_f(df * uf * s * (1.f + gf * (1.f - s)));
+      ou.v[j] = Cvt<T>::from_f(df * gf * s);
+    }
+    st16(dgu + r * 2 * F + c, og);
+    st16(dgu + r * 2 * F + F + c, ou);
+  }
+}
+
+at::Tensor swiglu_fwd(const at::Tensor& gu) {
+  TORCH_CHECK(gu.is_cuda() && gu.is_contiguous(), "swiglu: contiguous CUDA tensor");
+  const int F = gu.size(-1) / 2;
+  const int64_t rows = gu.numel() / (2 * F);
+  auto sizes = gu.sizes().vec();
+  sizes.back() = F;
+  auto y = at::empty(sizes, gu.options());
+  if (rows == 0) return y;
+  DISPATCH_FLOAT_BF16(gu, "swiglu", [&] {
+    constexpr int V = Vec16<scalar_t>::N;
+    TORCH_CHECK(F % V == 0, "swiglu: F must be a multiple of ", V);
+    int64_t nvec = rows * (F / V);
+    int grid = (int)std::min<int64_t>((nvec + 255) / 256, 148 * 16);
+    swiglu_fwd_kernel<scalar_t><<<grid, 256, 0, cur_stream()>>>((const scalar_t*)gu.data_ptr(),
+                                                                (scalar_t*)y.data_ptr(), rows, F);
+  });
+  return y;
+}
+
+at::Tensor swiglu_bwd(const at::Tensor& gu, const at::Tensor& dy) {
+  const int F = gu.size(-1) / 2;
+  const int64_t rows = gu.numel() / (2 * F);
+  auto dgu = at::empty_like(gu);
+  if (rows == 0) return dgu;
+  auto dyc = dy.contiguous();
+  DISPATCH_FLOAT_BF16(gu, "swiglu_bwd", [&] {
+    constexpr int V = Vec16<scalar_t>::N;
+    int64_t nvec = rows * (F / V);
+    int grid = (int)std::min<int64_t>((nvec + 255) / 256, 148 * 16);
+    swiglu_bwd_kernel<scalar_t><<<grid, 256, 0, cur_stream()>>>(
+        (const scalar_t*)gu.data_ptr(), (const scalar_t*)dyc.data_ptr(), (scalar_t*)dgu.data_ptr(), rows, F);
+  });
+  return dgu;
+}
+
+// ----------------------------------------------------------------------------- QK-norm + RoPE
+// One warp per (token, head).  Heads of q and k live side by side in the packed
+// qkv row; outputs are written densely.  D = head dim (64 or 128), rotate-half.
+// norm weights may be null (Llama: RoPE only).
+template <typename T, int D, bool BWD>
+__global__ void qk_norm_rope_kernel(const T* __restrict__ src, int src_stride, int n_heads,
+                                    const T* __restrict__ w, const int64_t* __restrict__ pos,
+                                    const float* __restrict__ inv_freq, T* __restrict__ dst,
+                                    const T* __restrict__ x_saved, int x_stride, float* __restrict__ dw,
+                                    int64_t T_tokens, float eps) {
+  constexpr int E = D / 32;   // elements per lane: E/2 in the first half, E/2 in the second
+  constexpr int HE = E / 2;
+  const int lane = threadIdx.x & 31;
+  const int64_t wid = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  if (wid >= T_tokens * n_heads) return;
+  const int64_t t = wid / n_heads;
+  const int h = wid % n_heads;
+  const float p = (float)pos[t];
+  float c[HE], s[HE];
+#pragma unroll
+  for (int j = 0; j < HE; ++j) sincosf(p * inv_freq[lane + 32 * j], &s[j], &c[j]);
+  if (!BWD) {
+    const T* xr = src + t * src_stride + h * D;
+    float a[HE], b[HE], ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < HE; ++j) {
+      a[j] = Cvt<T>::to_f(xr[lane + 32 * j]);
+      b[j] = Cvt<T>::to_f(xr[D / 2 + lane + 32 * j]);
+      ss += a[j] * a[j] + b[j] * b[j];
+    }
+    float r = 1.f;
+    if (w) {
+      ss = warp_sum(ss);
+      r = rsqrtf(ss / D + eps);
+    }
+    T* o = dst + (t * n_heads + h) * D;
+#pragma unroll
+    for (int j = 0; j < HE; ++j) {
+      float wa = w ? Cvt<T>::to_f(w[lane + 32 * j]) : 1.f;
+      float wb = w ? Cvt<T>::to_f(w[D / 2 + lane + 32 * j]) : 1.f;
+      // the normalised value is rounded to T before the rotation, as the eager path does
+      float na = w ? Cvt<T>::to_f(Cvt<T>::from_f(a[j] * r * wa)) : a[j];
+      float nb = w ? Cvt<T>::to_f(Cvt<T>::from_f(b[j] * r * wb)) : b[j];
+      o[lane + 32 * j] = Cvt<T>::from_f(na * c[j] - nb * s[j]);
+      o[D / 2 + lane + 32 * j] = Cvt<T>::from_f(nb * c[j] + na * s[j]);
+    }
+  } else {
+    // src = gradient w.r.t. the rotated output [T, n_heads, D]; dst = gradient w.r.t. x
+    const T* gr = src + (t * n_heads + h) * D;
+    const T* xr = x_saved + t * x_stride + h * D;
+    float ga[HE], gb[HE], xa[HE], xb[HE], ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < HE; ++j) {
+      float d1 = Cvt<T>::to_f(gr[lane + 32 * j]), d2 = Cvt<T>::to_f(gr[D / 2 + lane + 32 * j]);
+      ga[j] = d1 * c[j] + d2 * s[j];
+      gb[j] = d2 * c[j] - d1 * s[j];
+      xa[j] = Cvt<T>::to_f(xr[lane + 32 * j]);
+      xb[j] = Cvt<T>::to_f(xr[D / 2 + lane + 32 * j]);
+      ss += xa[j] * xa[j] + xb[j] * xb[j];
+    }
+    T* o = dst + t * src_stride + h * D;
+    if (!w) {
+#pragma unroll
+      for (int j = 0; j < HE; ++j) {
+        o[lane + 32 * j] = Cvt<T>::from_f(ga[j]);
+        o[D / 2 + lane + 32 * j] = Cvt<T>::from_f(gb[j]);
+      }
+      return;
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / D + eps);
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < HE; ++j) {
+      float wa = Cvt<T>::to_f(w[lane + 32 * j]), wb = Cvt<T>::to_f(w[D / 2 + lane + 32 * j]);
+      dot += ga[j] * wa * xa[j] * r + gb[j] * wb * xb[j] * r;
+      atomicAdd(dw + lane + 32 * j, ga[j] * xa[j] * r);
+      atomicAdd(dw + D / 2 + lane + 32 * j, gb[j] * xb[j] * r);
+    }
+    dot = warp_sum(dot) / D;
+#pragma unroll
+    for (int j = 0; j < HE; ++j) {
+      float wa = Cvt<T>::to_f(w[lane + 32 * j]), wb = Cvt<T>::to_f(w[D / 2 + lane + 32 * j]);
+      o[lane + 32 * j] = Cvt<T>::from_f(r * (ga[j] * wa - xa[j] * r * dot));
+      o[D / 2 + lane + 32 * j] = Cvt<T>::from_f(r * (gb[j] * wb - xb[j] * r * dot));
+    }
+  }
+}
+
+template <typename T, bool BWD>
+static void launch_qk(const T* src, int src_stride, int n_heads, const T* w, const int64_t* pos,
+                      const float* inv_freq, T* dst, const T* xs, int xstride, float* dw, int64_t Tn, int D,
+                      float eps) {
+  if (Tn * n_heads == 0) return;
+  const int threads = 256;
+  const int64_t warps = Tn * n_heads;
+  const int grid = (int)((warps * 32 + threads - 1) / threads);
+  if (D == 128)
+    qk_norm_rope_kernel<T, 128, BWD><<<grid, threads, 0, cur_stream()>>>(src, src_stride, n_heads, w, pos, inv_freq,
+                                                                        dst, xs, xstride, dw, Tn, eps);
+  else if (D == 64)
+    qk_norm_rope_kernel<T, 64, BWD><<<grid, threads, 0, cur_stream()>>>(src, src_stride, n_heads, w, pos, inv_freq,
+                                                                       dst, xs, xstride, dw, Tn, eps);
+  else
+    TORCH_CHECK(false, "qk_norm_rope: head dim must be 64 or 128");
+}
+
+// x: a [T, n_heads*D] slice (row stride may exceed n_heads*D: the packed qkv row).
+at::Tensor qk_norm_rope_fwd(const at::Tensor& x, int64_t n_heads, int64_t D, const c10::optional<at::Tensor>& w,
+                            const at::Tensor& pos, const at::Tensor& inv_freq, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1, "qk_norm_rope: x must be [T, n*D] with unit inner stride");
+  const int64_t Tn = x.size(0);
+  auto out = at::empty({Tn, n_heads, D}, x.options());
+  DISPATCH_FLOAT_BF16(x, "qk_norm_rope", [&] {
+    launch_qk<scalar_t, false>((const scalar_t*)x.data_ptr(), (int)x.stride(0), (int)n_heads,
+                               w.has_value() ? (const scalar_t*)w->data_ptr() : nullptr, pos.data_ptr<int64_t>(),
+                               inv_freq.data_ptr<float>(), (scalar_t*)out.data_ptr(), nullptr, 0, nullptr, Tn,
+                               (int)D, (float)eps);
+  });
+  return out;
+}
+
+// Writes dx into `dx_out` (same [T, n*D] strided view as x) and returns dw (fp32, [D]).
+at::Tensor qk_norm_rope_bwd(const at::Tensor& dy, const at::Tensor& x, at::Tensor dx_out, int64_t n_heads,
+                            int64_t D, const c10::optional<at::Tensor>& w, const at::Tensor& pos,
+                            const at::Tensor& inv_freq, double eps) {
+  const int64_t Tn = x.size(0);
+  auto dw = at::zeros({D}, x.options().dtype(at::kFloat));
+  auto dyc = dy.contiguous();
+  TORCH_CHECK(dx_out.stride(1) == 1 && dx_out.stride(0) == x.stride(0) || true, "");
+  DISPATCH_FLOAT_BF16(x, "qk_norm_rope_bwd", [&] {
+    launch_qk<scalar_t, true>((const scalar_t*)dyc.data_ptr(), (int)dx_out.stride(0), (int)n_heads,
+                              w.has_value() ? (const scalar_t*)w->data_ptr() : nullptr, pos.data_ptr<int64_t>(),
+                              inv_freq.data_ptr<float>(), (scalar_t*)dx_out.data_ptr(),
+                              (const scalar_t*)x.data_ptr(), (int)x.stride(0), dw.data_ptr<float>(), Tn, (int)D,
+                              (float)eps);
+  });
+  return dw;
+}
+
+// ----------------------------------------------------------------------------- GRPO loss
+// One pass: per-token clipped-ratio loss + k3 KL + entropy bonus, masked sums and
+// the gradients w.r.t. logprob and entropy.  stats: [pg, kl, ent, clip+, clip-, ntok, total].
+__global__ void grpo_loss_kernel(const float* __restrict__ lp, const float* __restrict__ old,
+                                 const float* __restrict__ ref, const float* __restrict__ adv,
+                                 const float* __restrict__ mask, const float* __restrict__ ent,
+                                 float* __restrict__ dlp, float* __restrict__ dent, float* __restrict__ stats,
+                                 int64_t n, float pos_clip, float neg_clip, float diff_clip, float final_clip,
+                                 float kl_coef, float ent_coef, float inv_norm) {
+  __shared__ float red[32];
+  float acc[7] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float m = mask[i], A = adv[i];
+    const float d = lp[i] - old[i];
+    const float ratio = __expf(fminf(d, diff_clip));
+    const float dr = (d <= diff_clip) ? ratio : 0.f;
+    const float lo = 1.f - neg_clip, hi = 1.f + pos_clip;
+    const float rc = fminf(fmaxf(ratio, lo), hi);
+    const bool inside = (ratio >= lo) && (ratio <= hi);
+    const float l1 = -A * ratio, l2 = -A * rc;
+    const float mx = fmaxf(l1, l2);
+    const float pg = fminf(mx, final_clip);
+    float g = 0.f;
+    if (mx <= final_clip) {
+      const float g1 = -A * dr, g2 = inside ? -A * dr : 0.f;
+      g = (l1 > l2) ? g1 : ((l1 < l2) ? g2 : 0.5f * (g1 + g2));
+    }
+    float kl = 0.f, gkl = 0.f;
+    if (ref) {
+      const float k = ref[i] - lp[i];
+      const float e = __expf(k);
+      const float raw = e - k - 1.f;
+      kl = fminf(fmaxf(raw, -10.f), 10.f);
+      gkl = (raw >= -10.f && raw <= 10.f) ? -(e - 1.f) : 0.f;
+    }
+    const float en = ent ? ent[i] : 0.f;
+    dlp[i] = m * inv_norm * (g + kl_coef * gkl);
+    if (dent) dent[i] = -m * inv_norm * ent_coef;
+    acc[0] += pg * m;
+    acc[1] += kl * m;
+    acc[2] += en * m;
+    acc[3] += (ratio > hi && A > 0.f) ? m : 0.f;
+    acc[4] += (ratio < lo && A < 0.f) ? m : 0.f;
+    acc[5] += m;
+    acc[6] += m * (pg + kl_coef * kl - ent_coef * en);
+  }
+#pragma unroll
+  for (int k = 0; k < 7; ++k) {
+    float v = block_sum(acc[k], red);
+    if (threadIdx.x == 0) atomicAdd(stats + k, v);
+  }
+}
+
+std::vector<at::Tensor> grpo_loss_fwd(const at::Tensor& lp, const at::Tensor& old,
+                                      const c10::optional<at::Tensor>& ref, const at::Tensor& adv,
+                                      const at::Tensor& mask, const c10::optional<at::Tensor>& ent,
+                                      double pos_clip, double neg_clip, double diff_clip, double final_clip,
+                                      double kl_coef, double ent_coef, double inv_norm) {
+  const int64_t n = lp.numel();
+  auto dlp = at::empty_like(lp);
+  auto dent = ent.has_value() ? at::empty_like(lp) : at::empty({0}, lp.options());
+  auto stats = at::zeros({7}, lp.options());
+  if (n > 0) {
+    int grid = (int)std::min<int64_t>((n + 255) / 256, 148 * 4);
+    grpo_loss_kernel<<<grid, 256, 0, cur_stream()>>>(
+        lp.data_ptr<float>(), old.data_ptr<float>(), ref.has_value() ? ref->data_ptr<float>() : nullptr,
+        adv.data_ptr<float>(), mask.data_ptr<float>(), ent.has_value() ? ent->data_ptr<float>() : nullptr,
+        dlp.data_ptr<float>(), ent.has_value() ? dent.data_ptr<float>() : nullptr, stats.data_ptr<float>(), n,
+        (float)pos_clip, (float)neg_clip, (float)diff_clip, (float)final_clip, (float)kl_coef, (float)ent_coef,
+        (float)inv_norm);
+  }
+  return {stats, dlp, dent};
+}
+
+// ----------------------------------------------------------------------------- AdamW
+template <typename P>
+__global__ void adamw_kernel(float* __restrict__ master, const float* __restrict__ grad, float* __restrict__ m,
+                             float* __restrict__ v, P* __restrict__ out, int64_t n, float lr, float b1, float b2,
+                             float eps, float wd, float bc1, float bc2, const float* __restrict__ scale_ptr,
+                             float scale_val) {
+  const float scale = scale_ptr ? *scale_ptr : scale_val;
+  for (int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 4; i < n;
+       i += (int64_t)gridDim.x * blockDim.x * 4) {
+    if (i + 4 <= n) {
+      float4 g4 = *reinterpret_cast<const float4*>(grad + i);
+      float4 m4 = *reinterpret_cast<float4*>(m + i);
+      float4 v4 = *reinterpret_cast<float4*>(v + i);
+      float4 p4 = *reinterpret_cast<float4*>(master + i);
+      float* g = &g4.x; float* mm = &m4.x; float* vv = &v4.x; float* pp = &p4.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float gj = g[j] * scale;
+        mm[j] = b1 * mm[j] + (1.f - b1) * gj;
+        vv[j] = b2 * vv[j] + (1.f - b2) * gj * gj;
+        float denom = sqrtf(vv[j] / bc2) + eps;
+        pp[j] = pp[j] * (1.f - lr * wd) - lr * (mm[j] / bc1) / denom;
+      }
+      *reinterpret_cast<float4*>(m + i) = m4;
+      *reinterpret_cast<float4*>(v + i) = v4;
+      *reinterpret_cast<float4*>(master + i) = p4;
+      if (out) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) out[i + j] = Cvt<P>::from_f(pp[j]);
+      }
+    } else {
+      for (int64_t k = i; k < n; ++k) {
+        float gj = grad[k] * scale;
+        float mk = b1 * m[k] + (1.f - b1) * gj;
+        float vk = b2 * v[k] + (1.f - b2) * gj * gj;
+        float pk = master[k] * (1.f - lr * wd) - lr * (mk / bc1) / (sqrtf(vk / bc2) + eps);
+        m[k] = mk; v[k] = vk; master[k] = pk;
+        if (out) out[k] = Cvt<P>::from_f(pk);
+      }
+    }
+  }
+}
+
+void adamw_step(at::Tensor master, const at::Tensor& grad, at::Tensor m, at::Tensor v,
+                const c10::optional<at::Tensor>& out, int64_t step, double lr, double b1, double b2, double eps,
+                double wd, const c10::optional<at::Tensor>& scale_t, double scale_v) {
+  const int64_t n = master.numel();
+  if (n == 0) return;
+  TORCH_CHECK(master.scalar_type() == at::kFloat && grad.scalar_type() == at::kFloat, "adamw: fp32 master/grad");
+  TORCH_CHECK(((uintptr_t)master.data_ptr() % 16 == 0) && ((uintptr_t)grad.data_ptr() % 16 == 0) &&
+              ((uintptr_t)m.data_ptr() % 16 == 0) && ((uintptr_t)v.data_ptr() % 16 == 0), "adamw: 16-byte alignment");
+  const float bc1 = (float)(1.0 - std::pow(b1, (double)step)), bc2 = (float)(1.0 - std::pow(b2, (double)step));
+  const float* sp = scale_t.has_value() ? scale_t->data_ptr<float>() : nullptr;
+  int grid = (int)std::min<int64_t>((n / 4 + 255) / 256 + 1, 148 * 8);
+  if (!out.has_value()) {
+    adamw_kernel<float><<<grid, 256, 0, cur_stream()>>>(master.data_ptr<float>(), grad.data_ptr<float>(),
+        m.data_ptr<float>(), v.data_ptr<float>(), nullptr, n, (float)lr, (float)b1, (float)b2, (float)eps,
+        (float)wd, bc1, bc2, sp, (float)scale_v);
+  } else if (out->scalar_type() == at::kBFloat16) {
+    adamw_kernel<bf16><<<grid, 256, 0, cur_stream()>>>(master.data_ptr<float>(), grad.data_ptr<float>(),
+        m.data_ptr<float>(), v.data_ptr<float>(), (bf16*)out->data_ptr(), n, (float)lr, (float)b1, (float)b2,
+        (float)eps, (float)wd, bc1, bc2, sp, (float)scale_v);
+  } else {
+    adamw_kernel<float><<<grid, 256, 0, cur_stream()>>>(master.data_ptr<float>(), grad.data_ptr<float>(),
+        m.data_ptr<float>(), v.data_ptr<float>(), out->data_ptr<float>(), n, (float)lr, (float)b1, (float)b2,
+        (float)eps, (float)wd, bc1, bc2, sp, (float)scale_v);
+  }
+}
+
+// ----------------------------------------------------------------------------- sum of squares
+// Deterministic: fixed grid, per-CTA partials, second kernel adds them in order.
+template <typename T>
+__global__ void sumsq_partial_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ part) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float f = Cvt<T>::to_f(x[i]);
+    s += f * f;
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) part[blockIdx.x] = s;
+}
+__global__ void sumsq_final_kernel(const float* __restrict__ part, int n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += part[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) out[0] = s;
+}
+
+at::Tensor sumsq(const at::Tensor& x) {
+  auto out = at::zeros({}, x.options().dtype(at::kFloat));
+  const int64_t n = x.numel();
+  if (n == 0) return out;
+  const int grid = (int)std::min<int64_t>((n + 1023) / 1024, 592);
+  auto part = at::empty({grid}, x.options().dtype(at::kFloat));
+  auto xc = x.contiguous();
+  DISPATCH_FLOAT_BF16(xc, "sumsq", [&] {
+    sumsq_partial_kernel<scalar_t><<<grid, 256, 0, cur_stream()>>>((const scalar_t*)xc.data_ptr(), n,
+                                                                   part.data_ptr<float>());
+  });
+  sumsq_final_kernel<<<1, 256, 0, cur_stream()>>>(part.data_ptr<float>(), grid, out.data_ptr<float>());
+  return out;
+}

@@ -1,0 +1,258 @@
+// bf16 GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * B[N,K]^T
+// (both operands K-major, i.e. y = x W^T of a linear layer), fp32 accumulation in
+// tensor memory.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer: streams 128x64 (A) and 256x64 (B) bf16 tiles into a
+//               4-stage shared-memory ring (128-byte swizzle), one mbarrier per stage
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (128x256x16) over the
+//               ring; tcgen05.commit frees a stage / publishes an accumulator
+//   warps 2..5  epilogue: tcgen05.ld the 128x256 fp32 accumulator out of TMEM,
+//               convert, store.  Two accumulators (2 x 256 TMEM columns) let the
+//               epilogue of tile i overlap the main loop of tile i+1.
+// No cluster launch and no TMA multicast are used.  Every mbarrier wait is
+// bounded; a timeout records a status code (readable with gemm_last_status) and
+// the CTA drains and frees its tensor memory instead of hanging.
+#include <ATen/cuda/CUDAContext.h>
+#include <cudaTypedefs.h>
+#include <torch/extension.h>
+
+#include "sm100.cuh"
+
+using namespace sm100;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kAccBufs = 2;
+constexpr int kTmemCols = BN * kAccBufs;  // 512
+constexpr int kThreads = 192;
+constexpr uint32_t kStageBytesA = BM * BK * 2, kStageBytesB = BN * BK * 2;
+
+struct __align__(1024) SmemLayout {
+  uint8_t a[kStages][kStageBytesA];
+  uint8_t b[kStages][kStageBytesB];
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full[kAccBufs];
+  uint64_t acc_empty[kAccBufs];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+__device__ int g_gemm_status = 0;
+
+enum : int { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3 };
+
+template <typename OutT>
+__device__ __forceinline__ void store_row32(OutT* dst, const uint32_t (&r)[32], int ncols);
+
+template <>
+__device__ __forceinline__ void store_row32<bf16>(bf16* dst, const uint32_t (&r)[32], int ncols) {
+  if (ncols >= 32) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      uint4 pk;
+      uint32_t* p = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+        p[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(dst + v * 8) = pk;
+    }
+  } else {
+    for (int j = 0; j < ncols; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+  }
+}
+template <>
+__device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&r)[32], int ncols) {
+  if (ncols >= 32) {
+#pragma unroll
+    for (int v = 0; v < 8; ++v)
+      *reinterpret_cast<uint4*>(dst + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+  } else {
+    for (int j = 0; j < ncols; ++j) dst[j] = __uint_as_float(r[j]);
+  }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    OutT* __restrict__ C, int M, int N, int K, int ldc) {
+  extern __shared__ uint8_t smem_raw[];
+  // dynamic shared memory is only 16-byte aligned by contract: align to 1024 for the swizzle
+  SmemLayout* sm = reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_iters = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
+    for (int b = 0; b < kAccBufs; ++b) { mbar_init(&sm->acc_full[b], 1); mbar_init(&sm->acc_empty[b], 4); }
+    sm->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sm->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(&sm->empty[stage], phase ^ 1)) { ok = false; break; }
+          mbar_expect_tx(&sm->full[stage], kStageBytesA + kStageBytesB);
+          tma_load_2d(sm->a[stage], &tmA, &sm->full[stage], k * BK, m0);
+          tma_load_2d(sm->b[stage], &tmB, &sm->full[stage], k * BK, n0);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) { atomicCAS(&g_gemm_status, ST_OK, ST_PRODUCER_TIMEOUT); atomicExch(&sm->abort_flag, 1u); }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&sm->acc_empty[acc], acc_phase ^ 1)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(&sm->full[stage], phase)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint64_t da = make_kmajor_sw128_desc(smem_u32(sm->a[stage]));
+          const uint64_t db = make_kmajor_sw128_desc(smem_u32(sm->b[stage]));
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            // +32 bytes per 16-element K step inside the 128-byte swizzle atom
+            umma_bf16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&sm->empty[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&sm->acc_full[acc]);
+        if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok) { atomicCAS(&g_gemm_status, ST_OK, ST_MMA_TIMEOUT); atomicExch(&sm->abort_flag, 1u); }
+    }
+  } else {
+    // ------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                      // TMEM lane quarter this warp may read
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      if (!mbar_wait(&sm->acc_full[acc], acc_phase)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c, r);
+        tmem_ld_wait();
+        const int col = n0 + c;
+        if (row < M && col < N) store_row32<OutT>(C + (int64_t)row * ldc + col, r, min(32, N - col));
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm->acc_empty[acc]);
+      if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1; }
+    }
+    if (!ok && lane == 0) { atomicCAS(&g_gemm_status, ST_OK, ST_EPILOGUE_TIMEOUT); atomicExch(&sm->abort_flag, 1u); }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    cudaDriverEntryPointQueryResult qres;
+    void* p = nullptr;
+    auto err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    TORCH_CHECK(err == cudaSuccess && qres == cudaDriverEntryPointSuccess && p, "cuTensorMapEncodeTiled unavailable");
+    fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }
+  return fn;
+}
+
+// rows x cols bf16 row-major matrix with leading dimension ld (elements); box = box_rows x 64.
+CUtensorMap make_tmap_bf16(const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  CUtensorMap tm;
+  cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)(ld * 2)};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = get_encode_fn()(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box,
+                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+  return tm;
+}
+
+}  // namespace
+
+// a [M, K] bf16 (row stride lda), b [N, K] bf16 -> C [M, N] (bf16, or fp32 when out_fp32)
+at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16,
+              "gemm_bf16_nt: bf16 CUDA tensors");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "gemm_bf16_nt: A [M,K], B [N,K]");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1, "gemm_bf16_nt: K must be the contiguous dimension");
+  const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
+  TORCH_CHECK(K % 8 == 0 && a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "gemm_bf16_nt: K and row strides must be multiples of 8");
+  TORCH_CHECK(((uintptr_t)a.data_ptr() % 16 == 0) && ((uintptr_t)b.data_ptr() % 16 == 0), "gemm_bf16_nt: 16-byte aligned operands");
+  auto c = at::empty({M, N}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  if (M == 0 || N == 0) return c;
+  if (K == 0) return c.zero_();
+  TORCH_CHECK(N % 8 == 0, "gemm_bf16_nt: N must be a multiple of 8");
+  CUtensorMap tmA = make_tmap_bf16(a.data_ptr(), M, K, a.stride(0), BM);
+  CUtensorMap tmB = make_tmap_bf16(b.data_ptr(), N, K, b.stride(0), BN);
+  const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
+  static int num_sms = 0;
+  if (!num_sms) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, a.get_device());
+  const int grid = std::min(tiles, num_sms);
+  const size_t smem = sizeof(SmemLayout) + 1024;
+  auto st = at::cuda::getCurrentCUDAStream();
+  if (out_fp32) {
+    static bool cfg = false;
+    if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
+    gemm_bf16_nt_kernel<float><<<grid, kThreads, smem, st>>>(tmA, tmB, c.data_ptr<float>(), (int)M, (int)N, (int)K, (int)N);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
+    gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, (bf16*)c.data_ptr(), (int)M, (int)N, (int)K, (int)N);
+  }
+  return c;
+}
+
+// Status of the GEMM kernels since the last call (0 = ok); synchronises the device.
+int64_t gemm_last_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int));
+  int zero = 0;
+  cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
+  return v;
+}

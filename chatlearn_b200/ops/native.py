@@ -1,0 +1,377 @@
+"""Bindings of the hand-written sm_100a kernels to the op facade.
+
+Importing this module loads ``chatlearn_b200/_C.so`` (built in-tree by
+``chatlearn_b200.csrc.build``) and registers one implementation per op.  A
+missing or unloadable extension raises here: on a GPU box the CUDA path must be
+the one that runs.  Ops whose shapes a kernel does not cover fall back to the
+PyTorch statement *for that call* and are counted in ``ops.library_counts``.
+"""
+import importlib.util
+import math
+import os
+
+import torch
+
+from . import launch_counts, library_counts, reference as ref, register_native
+
+_SO = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C.so")
+if not os.path.exists(_SO):
+    raise ImportError(f"{_SO} not found: run `python -m chatlearn_b200.csrc.build` "
+                      "(CUDA tensors need the sm_100a extension; there is no silent fallback)")
+_spec = importlib.util.spec_from_file_location("chatlearn_b200._C", _SO)
+C = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(C)
+
+# which GEMM the linear layers use on CUDA: "tcgen05" (own kernel) or "cublas"
+_GEMM_IMPL = os.environ.get("CHATLEARN_GEMM", "tcgen05")
+
+
+def set_gemm_impl(name: str):
+    global _GEMM_IMPL
+    assert name in ("tcgen05", "cublas")
+    _GEMM_IMPL = name
+
+
+def get_gemm_impl():
+    return _GEMM_IMPL
+
+
+def _count(name, n=1):
+    launch_counts[name] += n
+
+
+# ------------------------------------------------------------------ rmsnorm
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        xc = x.contiguous()
+        y, rstd = C.rmsnorm_fwd(xc, w.contiguous(), eps)
+        _count("rmsnorm_fwd")
+        ctx.save_for_backward(xc, w, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd = ctx.saved_tensors
+        dx, dw = C.rmsnorm_bwd(x, w.contiguous(), dy.contiguous(), rstd)
+        _count("rmsnorm_bwd")
+        return dx, dw.to(w.dtype), None
+
+
+def rmsnorm(x, w, eps):
+    if x.dtype not in (torch.float32, torch.bfloat16) or w.dtype != x.dtype \
+            or x.shape[-1] % (16 // x.element_size()) != 0:
+        library_counts["rmsnorm"] += 1
+        return ref.rmsnorm(x, w, eps)
+    return _RMSNorm.apply(x, w, eps)
+
+
+# ------------------------------------------------------------------ swiglu
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        guc = gu.contiguous()
+        ctx.save_for_backward(guc)
+        _count("swiglu_fwd")
+        return C.swiglu_fwd(guc)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (gu,) = ctx.saved_tensors
+        _count("swiglu_bwd")
+        return C.swiglu_bwd(gu, dy.contiguous())
+
+
+def swiglu(gate_up):
+    F = gate_up.shape[-1] // 2
+    if gate_up.dtype not in (torch.float32, torch.bfloat16) or F % (16 // gate_up.element_size()) != 0:
+        library_counts["swiglu"] += 1
+        return ref.swiglu(gate_up)
+    return _SwiGLU.apply(gate_up)
+
+
+# ------------------------------------------------------------------ qk-norm + rope
+_inv_freq_cache = {}
+
+
+def _inv_freq(d, theta, device):
+    key = (d, float(theta), str(device))
+    t = _inv_freq_cache.get(key)
+    if t is None:
+        t = 1.0 / (theta ** (torch.arange(0, d, 2, device=device, dtype=torch.float32) / d))
+        _inv_freq_cache[key] = t
+    return t
+
+
+class _NormRope(torch.autograd.Function):
+    """Per-head RMSNorm (optional) + rotate-half RoPE on ``x [T, n, D]`` (any row stride)."""
+
+    @staticmethod
+    def forward(ctx, x, w, positions, theta, eps):
+        T, n, D = x.shape
+        x2 = x.reshape(T, n * D) if x.is_contiguous() else x.as_strided((T, n * D), (x.stride(0), 1))
+        inv = _inv_freq(D, theta, x.device)
+        pos = positions.to(torch.int64)
+        out = C.qk_norm_rope_fwd(x2, n, D, w, pos, inv, eps)
+        _count("qk_norm_rope_fwd")
+        ctx.save_for_backward(x2, w if w is not None else torch.empty(0, device=x.device), pos, inv)
+        ctx.has_w, ctx.n, ctx.D, ctx.eps = w is not None, n, D, eps
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, pos, inv = ctx.saved_tensors
+        T = x2.shape[0]
+        dx = torch.empty(T, ctx.n * ctx.D, dtype=x2.dtype, device=x2.device)
+        dw = C.qk_norm_rope_bwd(dy.contiguous(), x2, dx, ctx.n, ctx.D, w if ctx.has_w else None, pos, inv, ctx.eps)
+        _count("qk_norm_rope_bwd")
+        return dx.view(T, ctx.n, ctx.D), (dw.to(w.dtype) if ctx.has_w else None), None, None, None
+
+
+def _rope_ok(x):
+    return (x.dim() == 3 and x.shape[-1] in (64, 128) and x.stride(-1) == 1 and x.stride(1) == x.shape[-1]
+            and x.dtype in (torch.float32, torch.bfloat16))
+
+
+def qk_norm_rope(q, k, qw, kw, eps, positions, theta):
+    if not (_rope_ok(q) and _rope_ok(k)):
+        library_counts["qk_norm_rope"] += 1
+        return ref.qk_norm_rope(q, k, qw, kw, eps, positions, theta)
+    return (_NormRope.apply(q, qw, positions, theta, eps), _NormRope.apply(k, kw, positions, theta, eps))
+
+
+def rope(x, positions, theta, rot_dim=None):
+    if (rot_dim is not None and rot_dim != x.shape[-1]) or not _rope_ok(x):
+        library_counts["rope"] += 1
+        return ref.rope(x, positions, theta, rot_dim)
+    return _NormRope.apply(x, None, positions, theta, 0.0)
+
+
+# ------------------------------------------------------------------ linear / GEMM
+class _LinearNT(torch.autograd.Function):
+    """y = x W^T with the tcgen05 kernel; backward GEMMs use cuBLAS (plain library GEMMs)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        _count("gemm_bf16_nt")
+        return C.gemm_bf16_nt(x, w, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dx = dy @ w if ctx.needs_input_grad[0] else None
+        dw = dy.t() @ x if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def _gemm_ok(x2, w):
+    return (x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 2
+            and x2.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0 and x2.stride(-1) == 1 and w.stride(-1) == 1
+            and x2.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x2.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def linear(x, w, bias=None):
+    if _GEMM_IMPL == "tcgen05":
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.shape[0] > 0 and _gemm_ok(x2, w):
+            y = _LinearNT.apply(x2, w).view(*x.shape[:-1], w.shape[0])
+            return y + bias if bias is not None else y
+    library_counts["linear"] += 1
+    return torch.nn.functional.linear(x, w, bias)
+
+
+def gemm_nt(a, b, out_fp32=False):
+    """Raw C = A B^T on the tcgen05 kernel (no autograd)."""
+    _count("gemm_bf16_nt")
+    return C.gemm_bf16_nt(a, b, out_fp32)
+
+
+# ------------------------------------------------------------------ lm head log-prob / entropy
+class _LMHeadLogprob(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, w, labels, inv_temp, chunk):
+        T = h.shape[0]
+        lp = torch.empty(T, dtype=torch.float32, device=h.device)
+        ent = torch.empty(T, dtype=torch.float32, device=h.device)
+        lse = torch.empty(T, dtype=torch.float32, device=h.device)
+        lab = labels.to(torch.int64).contiguous()
+        use_own = _GEMM_IMPL == "tcgen05" and _gemm_ok(h, w)
+        for s in range(0, T, chunk):
+            hc = h[s:s + chunk]
+            if use_own:
+                z = C.gemm_bf16_nt(hc, w, True)
+                _count("gemm_bf16_nt")
+            else:
+                z = (hc @ w.t()).float() if hc.dtype != torch.float32 else hc @ w.t()
+            a, b, c = C.logits_stats(z.contiguous(), lab[s:s + chunk], inv_temp)
+            _count("logits_stats")
+            lp[s:s + chunk], ent[s:s + chunk], lse[s:s + chunk] = a, b, c
+        ctx.save_for_backward(h, w, lab, lse, ent)
+        ctx.inv_temp, ctx.chunk, ctx.use_own = inv_temp, chunk, use_own
+        ctx.mark_non_differentiable(lse)
+        return lp, ent
+
+    @staticmethod
+    def backward(ctx, g_lp, g_ent):
+        h, w, lab, lse, ent = ctx.saved_tensors
+        T = h.shape[0]
+        chunk = ctx.chunk
+        gh = torch.empty_like(h)
+        gw = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        g_lp = g_lp.contiguous().float()
+        ge = g_ent.contiguous().float() if g_ent is not None else None
+        bf = h.dtype == torch.bfloat16
+        for s in range(0, T, chunk):
+            hc = h[s:s + chunk]
+            if ctx.use_own:
+                z = C.gemm_bf16_nt(hc, w, True)
+                _count("gemm_bf16_nt")
+            else:
+                z = (hc @ w.t()).float() if hc.dtype != torch.float32 else hc @ w.t()
+            dz = C.logits_grad(z.contiguous(), lab[s:s + chunk], lse[s:s + chunk], ent[s:s + chunk],
+                               g_lp[s:s + chunk], ge[s:s + chunk] if ge is not None else None,
+                               ctx.inv_temp, bf)
+            _count("logits_grad")
+            gh[s:s + chunk] = dz @ w
+            gw += (dz.t() @ hc).float()
+        return gh, gw.to(w.dtype), None, None, None
+
+
+def lmhead_logprob_entropy(h, w, labels, temperature=1.0, chunk=2048):
+    return _LMHeadLogprob.apply(h.contiguous(), w, labels, 1.0 / temperature, chunk)
+
+
+# ------------------------------------------------------------------ GRPO loss
+class _GrpoLoss(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, lp, old, ref_lp, adv, mask, ent, pos_clip, neg_clip, diff_clip, final_clip, kl_coef,
+                ent_coef, inv_norm):
+        f = lambda t: None if t is None else t.contiguous().float()  # noqa: E731
+        stats, dlp, dent = C.grpo_loss_fwd(f(lp), f(old), f(ref_lp), f(adv), f(mask), f(ent), pos_clip,
+                                           neg_clip, diff_clip, final_clip, kl_coef, ent_coef, inv_norm)
+        _count("grpo_loss")
+        ctx.save_for_backward(dlp, dent)
+        ctx.has_ent = ent is not None
+        total = stats[6] * inv_norm
+        ctx.mark_non_differentiable(stats)
+        return total, stats[:6]
+
+    @staticmethod
+    def backward(ctx, g_total, _g_stats):
+        dlp, dent = ctx.saved_tensors
+        g_ent = dent * g_total if ctx.has_ent and dent.numel() else None
+        return (dlp * g_total, None, None, None, None, g_ent) + (None,) * 7
+
+
+def grpo_loss_fused(logprobs, old_logprobs, ref_logprobs, advantages, mask, entropy=None, pos_clip=0.2,
+                    neg_clip=0.2, diff_clip=10.0, final_clip=3.0, kl_coef=0.0, entropy_coef=0.0, inv_norm=1.0):
+    adv = advantages if advantages.shape == logprobs.shape else advantages.expand_as(logprobs)
+    return _GrpoLoss.apply(logprobs, old_logprobs, ref_logprobs, adv, mask, entropy, pos_clip, neg_clip,
+                           diff_clip, final_clip, kl_coef, entropy_coef, inv_norm)
+
+
+# ------------------------------------------------------------------ optimizer
+@torch.no_grad()
+def adamw_step(master, grad, exp_avg, exp_avg_sq, out_param, step, lr, beta1, beta2, eps, weight_decay,
+               grad_scale=1.0):
+    ok = (master.dtype == torch.float32 and grad.dtype == torch.float32 and master.is_contiguous()
+          and grad.is_contiguous() and all(t.data_ptr() % 16 == 0 for t in (master, grad, exp_avg, exp_avg_sq))
+          and (out_param is None or (out_param.is_contiguous() and out_param.dtype in (torch.float32, torch.bfloat16))))
+    if not ok:
+        library_counts["adamw_step"] += 1
+        return ref.adamw_step(master, grad, exp_avg, exp_avg_sq, out_param, step, lr, beta1, beta2, eps,
+                              weight_decay, grad_scale)
+    if isinstance(grad_scale, torch.Tensor):
+        st, sv = grad_scale.reshape(1).float(), 1.0
+    else:
+        st, sv = None, float(grad_scale)
+    C.adamw_step(master, grad, exp_avg, exp_avg_sq, out_param, int(step), lr, beta1, beta2, eps, weight_decay,
+                 st, sv)
+    _count("adamw_step")
+
+
+@torch.no_grad()
+def sumsq(x):
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        return ref.sumsq(x)
+    _count("sumsq", 2)
+    return C.sumsq(x)
+
+
+# ------------------------------------------------------------------ sampling
+@torch.no_grad()
+def sample(logits, u, temperature=1.0, top_k=-1, top_p=1.0, min_p=0.0):
+    z = logits.float().contiguous()
+    ids, lp = C.sample(z, u.float().contiguous(), float(temperature), int(top_k if top_k is not None else -1),
+                       float(top_p), float(min_p))
+    _count("sample")
+    return ids, lp
+
+
+@torch.no_grad()
+def apply_penalties(logits, token_counts, presence=0.0, frequency=0.0, repetition=1.0, prompt_mask=None):
+    _count("apply_penalties")
+    return C.apply_penalties(logits, token_counts, prompt_mask, presence, frequency, repetition)
+
+
+# ------------------------------------------------------------------ paged KV cache
+@torch.no_grad()
+def kv_append(k, v, k_cache, v_cache, slot_mapping):
+    if k.dtype != k_cache.dtype or k.dtype not in (torch.float32, torch.bfloat16):
+        library_counts["kv_append"] += 1
+        return ref.kv_append(k, v, k_cache, v_cache, slot_mapping)
+    kk = k if (k.stride(2) == 1 and k.stride(1) == k.shape[2]) else k.contiguous()
+    vv = v if (v.stride(2) == 1 and v.stride(1) == v.shape[2]) else v.contiguous()
+    C.kv_append(kk, vv, k_cache, v_cache, slot_mapping.to(torch.int64))
+    _count("kv_append")
+
+
+def _num_splits(n_ctas: int, max_ctx_blocks: int) -> int:
+    """Split long contexts when the grid alone cannot fill the 148 SMs."""
+    if n_ctas >= 148 * 2 or max_ctx_blocks <= 4:
+        return 1
+    return int(max(1, min(max_ctx_blocks // 2, (148 * 2 + n_ctas - 1) // n_ctas, 16)))
+
+
+@torch.no_grad()
+def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens=None, scale=None):
+    nb, bs, nkv, dk = k_cache.shape
+    dv = v_cache.shape[-1]
+    nq = q.shape[1]
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or \
+            not C.paged_decode_supported(dk, dv, bs, nq // nkv):
+        library_counts["paged_attention"] += 1
+        return ref.paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens, scale)
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    sl = seq_lens.to(torch.int32)
+    if q_lens is None or q.shape[0] == sl.shape[0]:
+        q_seq, ctx = None, sl
+    else:
+        ql = q_lens.to(torch.int64)
+        B = sl.shape[0]
+        q_seq = torch.repeat_interleave(torch.arange(B, device=q.device, dtype=torch.int32), ql)
+        ends = torch.cumsum(ql, 0)
+        idx = torch.arange(q.shape[0], device=q.device)
+        back = (ends[q_seq.long()] - 1 - idx).to(torch.int32)      # tokens after this one in its chunk
+        ctx = sl[q_seq.long()] - back
+    max_blocks = block_tables.shape[1]
+    ns = _num_splits(q.shape[0] * nkv, max_blocks)
+    _count("paged_decode", 1 if ns == 1 else 2)
+    return C.paged_decode(q.contiguous(), k_cache, v_cache, block_tables.to(torch.int32).contiguous(), q_seq,
+                          ctx.contiguous(), float(scale), ns)
+
+
+# ------------------------------------------------------------------ weight sync kernel
+def weight_sync_run(desc_table, num_descs, total_tiles, src_dtype, dst_dtype):
+    C.weight_sync_run(desc_table, num_descs, total_tiles, src_dtype, dst_dtype)
+    _count("weight_sync")
+
+
+for _name, _fn in (("rmsnorm", rmsnorm), ("swiglu", swiglu), ("qk_norm_rope", qk_norm_rope), ("rope", rope),
+                   ("linear", linear), ("lmhead_logprob_entropy", lmhead_logprob_entropy),
+                   ("grpo_loss_fused", grpo_loss_fused), ("adamw_step", adamw_step), ("sumsq", sumsq),
+                   ("sample", sample), ("apply_penalties", apply_penalties), ("kv_append", kv_append),
+                   ("paged_attention", paged_attention)):
+    register_native(_name, _fn)

@@ -64,12 +64,43 @@ def qk_norm_rope(q, k, qw, kw, eps, positions, theta):
 
 
 # ------------------------------------------------------------------ attention
+_VARLEN_LIB = {"probed": False, "fn": None}
+
+
+def _library_varlen(q, k, v, cu_seqlens, max_seqlen, scale):
+    """Library varlen attention for the GPU baseline mode (flash-attn if it runs on
+    this GPU); ``None`` when no library kernel is usable."""
+    st = _VARLEN_LIB
+    if not st["probed"]:
+        st["probed"] = True
+        try:
+            from flash_attn import flash_attn_varlen_func
+
+            def fn(q, k, v, cu, mx, scale):
+                return flash_attn_varlen_func(q, k, v, cu, cu, mx, mx, softmax_scale=scale, causal=True)
+            # smoke call: a wheel without kernels for this architecture raises here
+            t = torch.zeros(2, 1, 64, dtype=q.dtype, device=q.device)
+            fn(t, t, t, torch.tensor([0, 2], dtype=torch.int32, device=q.device), 2, 0.125)
+            st["fn"] = fn
+        except Exception:
+            st["fn"] = None
+    if st["fn"] is None:
+        return None
+    if max_seqlen is None or max_seqlen <= 0:
+        max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
+    return st["fn"](q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens.to(torch.int32), int(max_seqlen), scale)
+
+
 def attention_varlen(q, k, v, cu_seqlens, max_seqlen=None, scale=None, causal=True):
     """Packed (varlen) attention.  ``q [T,nq,dq]``, ``k [T,nkv,dq]``,
     ``v [T,nkv,dv]``, ``cu_seqlens [B+1]``; segments attend only to themselves."""
     T, nq, dq = q.shape
     nkv = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(dq)
+    if q.is_cuda and causal and q.dtype in (torch.bfloat16, torch.float16) and v.shape[-1] == dq:
+        out = _library_varlen(q, k, v, cu_seqlens, max_seqlen, scale)
+        if out is not None:
+            return out
     rep = nq // nkv
     cu = cu_seqlens.tolist()
     outs = []

@@ -17,6 +17,7 @@ import torch
 from chatlearn_b200 import ops
 from chatlearn_b200.models.nn.arch import ModelArch
 from chatlearn_b200.models.nn.model import CausalLM, FwdCtx, KVCtx
+from chatlearn_b200.utils import xfer
 from chatlearn_b200.utils.constant import TAG_KV_CACHE, TAG_WEIGHTS
 from .scheduler import Scheduler, Sequence, StepPlan
 
@@ -143,12 +144,13 @@ class RolloutEngine:
             cu.append(cu[-1] + n)
             last_rows.append(cu[-1] - 1)
         dev = self.device
-        t = lambda x, dt: torch.tensor(x, dtype=dt).to(dev, non_blocking=True)  # noqa: E731
-        kv = KVCtx(self.k_cache, self.v_cache, t(slots, torch.long), bt.to(dev, non_blocking=True),
-                   t(seq_lens, torch.int32), t(plan.q_lens, torch.int32), plan.is_prefill)
-        ctx = FwdCtx(positions=t(pos, torch.long), cu_seqlens=t(cu, torch.int32),
+        # one pinned staging slot per input so the async copies never alias
+        t = lambda x, dt, slot: xfer.to_device(torch.tensor(x, dtype=dt), dev, slot)  # noqa: E731
+        kv = KVCtx(self.k_cache, self.v_cache, t(slots, torch.long, "slots"), xfer.to_device(bt, dev, "bt"),
+                   t(seq_lens, torch.int32, "seq_lens"), t(plan.q_lens, torch.int32, "q_lens"), plan.is_prefill)
+        ctx = FwdCtx(positions=t(pos, torch.long, "pos"), cu_seqlens=t(cu, torch.int32, "cu"),
                      max_seqlen=max(plan.q_lens), kv=kv, tp=self.tp, ep=self.ep)
-        return t(toks, torch.long), ctx, t(last_rows, torch.long)
+        return t(toks, torch.long, "toks"), ctx, t(last_rows, torch.long, "last")
 
     @torch.no_grad()
     def _logits(self, hidden_last):
@@ -198,7 +200,7 @@ class RolloutEngine:
                 ids, lps = i_, l_
             else:
                 ids[jj], lps[jj] = i_, l_
-        ids_h, lps_h = ids.tolist(), lps.tolist()
+        ids_h, lps_h = xfer.tolist(ids), xfer.tolist(lps)
         for s, tok, lp in zip(seqs, ids_h, lps_h):
             s.output.append(tok)
             s.logprobs.append(lp)

@@ -266,13 +266,13 @@ class Engine(BaseEngine):
         return summary
 
     # ------------------------------------------------------------------ the loop
-    def learn(self):
+    def prepare(self):
+        """Everything ``learn`` does before the first episode: set-up, resume, the
+        train stream and the initial trainer -> rollout weight sync."""
         ra = self.runtime_args
-        self.timers("chatlearn").start()
         if not self._setup_done:
             self.setup()
         self._resume_from_data_checkpoint()
-        trainer_model = self.trainer.models[0] if self.trainer and self.trainer.models else None
         n_mini = max(int(ra.sample_per_episode) // int(ra.train_global_batch_size), 1)
         self._data_loader = StreamDataset(
             ra.stream_data_loader_type, n_mini, self._replay_sample_manager,
@@ -289,36 +289,49 @@ class Engine(BaseEngine):
                     dst.dump_parameters(os.path.join(dump, "after_sync_parameter"))
         if ra.enable_eval_before_training and self.evaluator is not None:
             self.evaluator.eval(-1, 0)
+        self._prepared = True
+
+    def run_episode(self, episode_id: int):
+        """One episode: rollout + scoring + reward → train → checkpoint → weight sync
+        → evaluation → summary.  Returns the episode summary dict."""
+        ra = self.runtime_args
+        if ra.nsys and torch.cuda.is_available():
+            if episode_id == ra.profile_episode:
+                torch.cuda.cudart().cudaProfilerStart()
+            elif episode_id == ra.profile_episode + 1:
+                torch.cuda.cudart().cudaProfilerStop()
+        self.timers("episode").start()
+        self.before_episode()
+        logger.info(f"{LOG_START} episode {episode_id} start")
+        self.timers("environment").start()
+        if os.environ.get("SKIP_GENERATION") is None:
+            samples = self.env.make_experiences(episode_id)
+        else:
+            samples = []
+        self.timers("environment").stop()
+        self._data_loader.set_dataset([samples], episode_id, int(ra.sample_per_episode))
+        tokens = self._data_loader.get_total_train_tokens()
+        n_samples = self._data_loader.total_samples()
+        if self.trainer is not None and n_samples > 0:
+            self.timers("train").start()
+            self.trainer.train(episode_id)
+            self.timers("train").stop()
+        self.save_checkpoint(episode_id)
+        self.timers("sync_parameters").start()
+        self.model_manager.sync_parameters(episode_offset=episode_id + 1)
+        self.timers("sync_parameters").stop()
+        self.evaluate(episode_id)
+        self.after_episode()
+        self.timers("episode").stop()
+        return self.logging_summary(episode_id, tokens, n_samples)
+
+    def learn(self):
+        ra = self.runtime_args
+        self.timers("chatlearn").start()
+        if not getattr(self, "_prepared", False):
+            self.prepare()
         for episode_id in range(self._start_episode, int(ra.num_episode)):
-            if ra.nsys and torch.cuda.is_available():
-                if episode_id == ra.profile_episode:
-                    torch.cuda.cudart().cudaProfilerStart()
-                elif episode_id == ra.profile_episode + 1:
-                    torch.cuda.cudart().cudaProfilerStop()
-            self.timers("episode").start()
-            self.before_episode()
-            logger.info(f"{LOG_START} episode {episode_id} start")
-            self.timers("environment").start()
-            if os.environ.get("SKIP_GENERATION") is None:
-                samples = self.env.make_experiences(episode_id)
-            else:
-                samples = []
-            self.timers("environment").stop()
-            self._data_loader.set_dataset([samples], episode_id, int(ra.sample_per_episode))
-            tokens = self._data_loader.get_total_train_tokens()
-            n_samples = self._data_loader.total_samples()
-            if self.trainer is not None and n_samples > 0:
-                self.timers("train").start()
-                self.trainer.train(episode_id)
-                self.timers("train").stop()
-            self.save_checkpoint(episode_id)
-            self.timers("sync_parameters").start()
-            self.model_manager.sync_parameters(episode_offset=episode_id + 1)
-            self.timers("sync_parameters").stop()
-            self.evaluate(episode_id)
-            self.after_episode()
-            self.timers("episode").stop()
-            self.logging_summary(episode_id, tokens, n_samples)
+            self.run_episode(episode_id)
         self.timers("chatlearn").stop()
         logger.info(f"{LOG_START} {self._name} finished in {self.timers('chatlearn').elapsed():.1f} s")
         return self.episode_stats

@@ -1,0 +1,68 @@
+"""Whole-model checks on the GPU: native kernels vs the PyTorch statements, and a
+tiny GRPO run through the public engine API on one device."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from chatlearn_b200 import ops
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("preset", ["tiny_qwen3", "tiny_llama"])
+def test_forward_backward_native_vs_library(preset):
+    from chatlearn_b200.models.nn import CausalLM, PRESETS, packed_ctx
+    arch = PRESETS[preset]()
+    torch.manual_seed(0)
+    toks = torch.randint(0, arch.vocab_size, (96,), device="cuda")
+    labels = toks.roll(-1)
+    outs = {}
+    for mode in ("native", "library"):
+        m = CausalLM(arch, dtype=torch.bfloat16, device="cuda").init_weights(5)
+        g = [torch.zeros(b.numel, dtype=torch.bfloat16, device="cuda") for b in m.blocks]
+        for b, gb in zip(m.blocks, g):
+            b.enable_grad(gb)
+        with ops.mode(mode):
+            ctx, _ = packed_ctx([40, 56], "cuda")
+            lp, ent = m.logprobs(toks, labels, ctx)
+            (lp.sum() + 0.1 * ent.sum()).backward()
+        outs[mode] = (lp.detach().float(), ent.detach().float(), torch.cat([x.float() for x in g]))
+    a, b = outs["native"], outs["library"]
+    assert (a[0] - b[0]).abs().max() < 0.15, (a[0] - b[0]).abs().max()
+    assert (a[1] - b[1]).abs().max() < 0.15
+    cos = torch.nn.functional.cosine_similarity(a[2], b[2], dim=0)
+    assert cos > 0.99, cos
+
+
+def test_rollout_engine_native_matches_library():
+    from chatlearn_b200.models.nn import CausalLM, PRESETS
+    from chatlearn_b200.rollout import RolloutEngine, SamplingParams
+    arch = PRESETS["tiny_qwen3"]()
+    m = CausalLM(arch, dtype=torch.bfloat16, device="cuda").init_weights(1, std=0.1)
+    prompts = [torch.randint(0, arch.vocab_size - 1, (n,)).tolist() for n in (5, 70, 33, 130)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    res = {}
+    for mode in ("native", "library"):
+        with ops.mode(mode):
+            eng = RolloutEngine(m, block_size=16, num_blocks=128, max_num_seqs=4, max_num_batched_tokens=64,
+                                max_model_len=256)
+            res[mode] = [s.output for s in eng.generate(prompts, sp)]
+    # greedy decoding with bf16 kernels can diverge after a near-tie; the first tokens must agree
+    agree = sum(a[:4] == b[:4] for a, b in zip(res["native"], res["library"]))
+    assert agree >= 3, res
+
+
+def test_grpo_tiny_one_gpu(tmp_path):
+    script = os.path.join(ROOT, "tests", "grpo_tiny_driver.py")
+    env = dict(os.environ, OUT_DIR=str(tmp_path), RANK="0", WORLD_SIZE="1", LOCAL_RANK="0",
+               MASTER_ADDR="127.0.0.1", MASTER_PORT="29533")
+    out = subprocess.run([sys.executable, script], env=env, capture_output=True, text=True, timeout=900)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    res = [json.loads(l[7:]) for l in out.stdout.splitlines() if l.startswith("RESULT ")]
+    assert res and res[0]["episodes"] == 2 and res[0]["maxdiff"] < 1e-2
+    assert res[0]["native_launches"] > 0
