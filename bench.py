@@ -124,19 +124,21 @@ def build_config(args, out_dir, data_path, n_gpu):
             "colocation": ["policy", "policy_trainer", "ref_policy"], "output_dir": out_dir,
             "data_path": data_path, "num_episode": args.steps + args.warmup, "sample_per_episode": spe,
             "train_micro_batch_size": 1, "train_global_batch_size": spe // 2, "num_inference_per_prompt": n,
-            "save_episode_interval": 10 ** 9, "max_replay_episode": 1, "data_shuffle": False,
+            "save_episode_interval": 0, "max_replay_episode": 1, "data_shuffle": False,
             "enable_resume_training": False, "log_args_dict": {"log_dir": out_dir}},
         "models": {
             "policy_trainer": dict(common, num_gpu=n_gpu, fsdp_size=n_gpu, trainable=True,
                                    generation_batch_size=spe, kl_coef=0.001, gradient_checkpointing=True,
                                    optimizer={"lr": 2e-6}, save_hf=False,
-                                   free_gpu_memory={"offload_weights": False, "offload_optimizer_states": offload,
+                                   # fp32 master + Adam shards stay on the GPU (180 GB HBM); the fp32
+                                   # gradient buffer is released outside training
+                                   free_gpu_memory={"offload_weights": False, "offload_optimizer_states": False,
                                                     "free_grad_buffers": offload}),
             "ref_policy": dict(common, num_gpu=n_gpu, fsdp_size=n_gpu, generation_batch_size=spe,
                                free_gpu_memory={"offload_weights": offload}),
             "policy": dict(common, num_gpu=n_gpu, tensor_model_parallel_size=tp, generation_batch_size=spe,
                            num_inference_per_prompt=n, temperature=1.0, top_p=1.0, top_k=-1,
-                           gpu_memory_utilization=0.85, max_num_seqs=256, kv_block_size=64,
+                           gpu_memory_utilization=0.94, max_num_seqs=256, kv_block_size=64,
                            max_num_batched_tokens=16384, ignore_eos=True,
                            free_gpu_memory={"offload_weights": offload}),
             "reward": {"num_cpu": n_gpu, "synthetic_reward": "hash30"},
@@ -144,6 +146,8 @@ def build_config(args, out_dir, data_path, n_gpu):
 
 
 def main():
+    import faulthandler
+    faulthandler.enable()
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
@@ -256,7 +260,7 @@ def main():
             "gpu_launches": int(launches),
             "library_calls": {k: int(v) for k, v in ops.library_counts.items()},
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

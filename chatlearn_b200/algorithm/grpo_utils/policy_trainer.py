@@ -144,6 +144,9 @@ class PolicyTrainer(FSDPModule):
                     ma.kl_coef, ma.entropy_coef if need_ent else 0.0, inv_norm)
             for aux in ctx.aux_losses:
                 loss = loss + aux * (batch.loss_mask.sum() * inv_norm)
+            if self.device.type == "cuda":
+                self._logger.debug(f"micro-batch of {batch.num_tokens} tokens: "
+                                   f"{torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated before backward")
             loss.backward()
             stats += s.detach()
         grad_norm = st.step()

@@ -35,12 +35,17 @@ bool paged_decode_supported(int64_t dk, int64_t dv, int64_t bs, int64_t rep);
 at::Tensor paged_decode(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
                         const at::Tensor& block_tables, const c10::optional<at::Tensor>& q_seq,
                         const at::Tensor& ctx_len, double scale, int64_t num_splits);
+bool paged_decode_tc_supported(int64_t dk, int64_t dv, int64_t bs, int64_t rep);
+at::Tensor paged_decode_tc(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
+                           const at::Tensor& block_tables, const c10::optional<at::Tensor>& q_seq,
+                           const at::Tensor& ctx_len, double scale, int64_t num_splits);
 void weight_sync_run(const at::Tensor& desc_table, int64_t num_descs, int64_t total_tiles, int64_t src_dtype,
                      int64_t dst_dtype);
 int64_t weight_sync_desc_size();
 int64_t weight_sync_tile_elems();
 at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32);
 int64_t gemm_last_status();
+void gemm_set_splitk(bool on);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
@@ -59,9 +64,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("kv_append", &kv_append);
   m.def("paged_decode_supported", &paged_decode_supported);
   m.def("paged_decode", &paged_decode);
+  m.def("paged_decode_tc_supported", &paged_decode_tc_supported);
+  m.def("paged_decode_tc", &paged_decode_tc);
   m.def("weight_sync_run", &weight_sync_run);
   m.def("weight_sync_desc_size", &weight_sync_desc_size);
   m.def("weight_sync_tile_elems", &weight_sync_tile_elems);
   m.def("gemm_bf16_nt", &gemm_bf16_nt);
   m.def("gemm_last_status", &gemm_last_status);
+  m.def("gemm_set_splitk", &gemm_set_splitk);
 }

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 TARGET = os.path.join(PKG, "_C.so")
 
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "--use_fast_math",
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
               "-std=c++17", "--expt-relaxed-constexpr", "-Xptxas", "-v",
               "-U__CUDA_NO_HALF_OPERATORS__", "-U__CUDA_NO_BFLOAT16_CONVERSIONS__"]
 
@@ -26,7 +26,8 @@ def is_stale() -> bool:
     if not os.path.exists(TARGET):
         return True
     t = os.path.getmtime(TARGET)
-    deps = sources() + glob.glob(os.path.join(HERE, "*.cuh")) + glob.glob(os.path.join(HERE, "*.h"))
+    deps = sources() + glob.glob(os.path.join(HERE, "*.cuh")) + glob.glob(os.path.join(HERE, "*.h")) \
+        + [os.path.abspath(__file__)]          # the flags live in this file
     return any(os.path.getmtime(s) > t for s in deps)
 
 

@@ -43,8 +43,23 @@ struct __align__(1024) SmemLayout {
 };
 
 __device__ int g_gemm_status = 0;
+bool g_allow_splitk = true;
 
 enum : int { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3 };
+
+// Tile order: groups of kGroupM row-blocks are swept column-block by column-block,
+// so the CTAs running at the same time share a narrow band of B (which then stays
+// in L2) instead of each re-streaming the whole weight matrix.
+constexpr int kGroupM = 16;
+__device__ __forceinline__ void tile_origin(int tile, int tiles_m, int tiles_n, int& m0, int& n0) {
+  const int group_size = kGroupM * tiles_n;
+  const int group = tile / group_size;
+  const int first_m = group * kGroupM;
+  const int gm = min(tiles_m - first_m, kGroupM);
+  const int in_group = tile - group * group_size;
+  m0 = (first_m + in_group % gm) * BM;
+  n0 = (in_group / gm) * BN;
+}
 
 template <typename OutT>
 __device__ __forceinline__ void store_row32(OutT* dst, const uint32_t (&r)[32], int ncols);
@@ -64,7 +79,9 @@ __device__ __forceinline__ void store_row32<bf16>(bf16* dst, const uint32_t (&r)
       *reinterpret_cast<uint4*>(dst + v * 8) = pk;
     }
   } else {
-    for (int j = 0; j < ncols; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
   }
 }
 template <>
@@ -74,14 +91,16 @@ __device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&
     for (int v = 0; v < 8; ++v)
       *reinterpret_cast<uint4*>(dst + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
   } else {
-    for (int j = 0; j < ncols; ++j) dst[j] = __uint_as_float(r[j]);
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) dst[j] = __uint_as_float(r[j]);
   }
 }
 
 template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    OutT* __restrict__ C, int M, int N, int K, int ldc) {
+                    OutT* __restrict__ C, float* __restrict__ ws, int M, int N, int K, int ldc, int splits) {
   extern __shared__ uint8_t smem_raw[];
   // dynamic shared memory is only 16-byte aligned by contract: align to 1024 for the swizzle
   SmemLayout* sm = reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -89,6 +108,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int k_iters = (K + BK - 1) / BK;
+  // split-K: a work unit is (tile, k-slice); units of one k-slice are consecutive so
+  // concurrently running CTAs stream disjoint parts of B
+  const int k_per_split = (k_iters + splits - 1) / splits;
+  const int num_units = num_tiles * splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
@@ -112,9 +135,11 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tma_prefetch_desc(&tmB);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
-        for (int k = 0; k < k_iters; ++k) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        int m0, n0;
+        tile_origin(unit % num_tiles, tiles_m, tiles_n, m0, n0);
+        const int k_begin = (unit / num_tiles) * k_per_split, k_end = min(k_begin + k_per_split, k_iters);
+        for (int k = k_begin; k < k_end; ++k) {
           if (!mbar_wait(&sm->empty[stage], phase ^ 1)) { ok = false; break; }
           mbar_expect_tx(&sm->full[stage], kStageBytesA + kStageBytesB);
           tma_load_2d(sm->a[stage], &tmA, &sm->full[stage], k * BK, m0);
@@ -130,11 +155,12 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        const int k_begin = (unit / num_tiles) * k_per_split, k_end = min(k_begin + k_per_split, k_iters);
         if (!mbar_wait(&sm->acc_empty[acc], acc_phase ^ 1)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int k = 0; k < k_iters; ++k) {
+        for (int k = k_begin; k < k_end; ++k) {
           if (!mbar_wait(&sm->full[stage], phase)) { ok = false; break; }
           tc_fence_after_sync();
           const uint64_t da = make_kmajor_sw128_desc(smem_u32(sm->a[stage]));
@@ -142,7 +168,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
             // +32 bytes per 16-element K step inside the 128-byte swizzle atom
-            umma_bf16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (k > 0 || kk > 0) ? 1u : 0u);
+            umma_bf16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (k > k_begin || kk > 0) ? 1u : 0u);
           }
           umma_commit(&sm->empty[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -158,8 +184,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+    for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+      int m0, n0;
+      tile_origin(unit % num_tiles, tiles_m, tiles_n, m0, n0);
+      const bool empty_slice = (unit / num_tiles) * k_per_split >= k_iters;   // nothing was accumulated
       if (!mbar_wait(&sm->acc_full[acc], acc_phase)) { ok = false; break; }
       tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
@@ -170,7 +198,16 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
         const int col = n0 + c;
-        if (row < M && col < N) store_row32<OutT>(C + (int64_t)row * ldc + col, r, min(32, N - col));
+        if (row < M && col < N && !empty_slice) {
+          if (splits == 1) {
+            store_row32<OutT>(C + (int64_t)row * ldc + col, r, min(32, N - col));
+          } else {
+            // every k-slice writes its partial tile to its own plane of the workspace;
+            // the finalize kernel adds the planes (plain stores: no atomics, deterministic)
+            float* w = ws + ((int64_t)(unit / num_tiles) * M + row) * N + col;
+            store_row32<float>(w, r, min(32, N - col));
+          }
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -185,6 +222,33 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+}
+
+// Split-K epilogue: C = sum over the k-slice planes of the workspace.
+template <typename OutT>
+__global__ void splitk_finalize_kernel(const float* __restrict__ ws, OutT* __restrict__ C, int64_t n, int splits) {
+  for (int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(ws + i);
+    for (int s = 1; s < splits; ++s) {
+      const float4 u = *reinterpret_cast<const float4*>(ws + (int64_t)s * n + i);
+      v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+    }
+    if constexpr (sizeof(OutT) == 2) {
+      __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+      uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+      *reinterpret_cast<uint2*>(C + i) = pk;
+    } else {
+      *reinterpret_cast<float4*>(C + i) = v;
+    }
+  }
+}
+
+constexpr int64_t kWorkspaceFloats = 16ll << 20;   // 64 MiB of fp32 partial sums per device
+
+float* splitk_workspace(int device, const at::TensorOptions& opts) {
+  static std::vector<at::Tensor> ws(64);
+  if (!ws[device].defined()) ws[device] = at::empty({kWorkspaceFloats}, opts.dtype(at::kFloat));
+  return ws[device].data_ptr<float>();
 }
 
 PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
@@ -233,17 +297,28 @@ at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32)
   const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
   static int num_sms = 0;
   if (!num_sms) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, a.get_device());
-  const int grid = std::min(tiles, num_sms);
   const size_t smem = sizeof(SmemLayout) + 1024;
   auto st = at::cuda::getCurrentCUDAStream();
+  // few tiles (decode: M <= 128) cannot fill the SMs: slice K so every SM streams weights
+  const int k_iters = (int)((K + BK - 1) / BK);
+  int splits = 1;
+  if (g_allow_splitk && tiles * 2 <= num_sms && N % 4 == 0) {
+    splits = std::min({(num_sms + tiles - 1) / tiles, std::max(k_iters / 4, 1), 16});
+    while (splits > 1 && (int64_t)splits * M * N > kWorkspaceFloats) --splits;
+    while (splits > 1 && ((k_iters + splits - 1) / splits) * (splits - 1) >= k_iters) --splits;  // no empty slice
+  }
+  float* ws = splits > 1 ? splitk_workspace(a.get_device(), a.options()) : nullptr;
+  const int grid = std::min(tiles * splits, num_sms);
   if (out_fp32) {
     static bool cfg = false;
     if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
-    gemm_bf16_nt_kernel<float><<<grid, kThreads, smem, st>>>(tmA, tmB, c.data_ptr<float>(), (int)M, (int)N, (int)K, (int)N);
+    gemm_bf16_nt_kernel<float><<<grid, kThreads, smem, st>>>(tmA, tmB, c.data_ptr<float>(), ws, (int)M, (int)N, (int)K, (int)N, splits);
+    if (splits > 1) splitk_finalize_kernel<float><<<(int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8), 256, 0, st>>>(ws, c.data_ptr<float>(), M * N, splits);
   } else {
     static bool cfg = false;
     if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
-    gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, (bf16*)c.data_ptr(), (int)M, (int)N, (int)K, (int)N);
+    gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, (bf16*)c.data_ptr(), ws, (int)M, (int)N, (int)K, (int)N, splits);
+    if (splits > 1) splitk_finalize_kernel<bf16><<<(int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8), 256, 0, st>>>(ws, (bf16*)c.data_ptr(), M * N, splits);
   }
   return c;
 }
@@ -256,3 +331,5 @@ int64_t gemm_last_status() {
   cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
   return v;
 }
+
+void gemm_set_splitk(bool on) { g_allow_splitk = on; }

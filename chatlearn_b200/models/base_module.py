@@ -421,11 +421,16 @@ class TorchModule(BaseModule):
                     for owner, attr in self._tagged(tag):
                         self._release(owner, attr)
                 else:
-                    mgr.offload(self._tagged(tag), self._release)
+                    # a frozen model's weights never change: after the first offload the
+                    # host copy stays valid and later offloads only drop the device copy
+                    mgr.offload(self._tagged(tag), self._release,
+                                unchanged=(tag == "weights" and not self.trainable))
                 self._resident[tag] = False
         self._barrier()
         self.empty_cache()
         self._metric_list.append({"offload_s": time.perf_counter() - t0})
+        if self.device.type == "cuda":
+            self._logger.debug(f"offload(w={w}, o={o}, g={g}) -> {torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated")
 
     def onload(self, to_onload_weights=None, to_build_grad_buffers=None,
                to_onload_optimizer_states=None, **kwargs):

@@ -127,7 +127,8 @@ class FSDPModule(TorchModule):
                 s.grad = torch.zeros(s.block.numel, dtype=gd, device=self.device)
                 s.block.enable_grad(s.grad)
             if s.grad_shard is None:
-                s.grad_shard = torch.zeros(s.shard_numel, dtype=torch.float32, device=self.device)
+                s.grad_shard = s.grad if (s.group.size == 1 and s.grad.dtype == torch.float32) else \
+                    torch.zeros(s.shard_numel, dtype=torch.float32, device=self.device)
 
     # ------------------------------------------------------------------ parameter sync (source side)
     def sync_layout(self):

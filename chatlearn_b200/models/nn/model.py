@@ -55,7 +55,9 @@ class ParamBlock:
         self.flat = flat
         for lf in self.leaves:
             o = self.offsets[lf.name]
-            view = flat[o:o + lf.numel].view(lf.shape)
+            # detach(): the leaf must not keep a `_base` reference to the flat buffer,
+            # or re-pointing its `.data` (offload) would not release the memory
+            view = flat[o:o + lf.numel].view(lf.shape).detach()
             key = self.short(lf.name)
             if key in self.params:
                 self.params[key].data = view
@@ -67,7 +69,6 @@ class ParamBlock:
         """Make leaves autograd leaves whose ``.grad`` are views of ``grad_flat``:
         autograd accumulates into them in place, so the block's gradient is one
         contiguous buffer ready for reduce-scatter."""
-        self.grad = grad_flat
         for lf in self.leaves:
             key = self.short(lf.name)
             p = self.params[key]

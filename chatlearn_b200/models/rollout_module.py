@@ -97,7 +97,8 @@ class RolloutModule(TorchModule):
             max_num_batched_tokens=int(ma.max_num_batched_tokens),
             gpu_memory_utilization=float(ma.gpu_memory_utilization),
             max_model_len=int(ma.seq_length), seed=int(ma.seed) + 7919 * self.replica_index,
-            lockstep_group=self.ep_group if self._ep > 1 else None)
+            lockstep_group=self.ep_group if self._ep > 1 else None,
+            use_cuda_graphs=not bool(getattr(ma, "enforce_eager", False)))
         from chatlearn_b200.data.tokenizer import load_tokenizer
         self.tokenizer = load_tokenizer(load, self.arch.vocab_size)
 
@@ -185,6 +186,8 @@ class RolloutModule(TorchModule):
                 self._release(b, "flat")
             self._resident["weights"] = False
         self.empty_cache()
+        if self.device.type == "cuda":
+            self._logger.debug(f"offload({tags}) -> {torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated")
 
     def onload(self, tags=None, **kwargs):
         if not self.is_member or self.engine is None:
@@ -194,6 +197,7 @@ class RolloutModule(TorchModule):
             for b in self.model.blocks:
                 b.bind(torch.empty(b.numel, dtype=b.dtype, device=self.device))
             self._resident["weights"] = True
+            self.engine.invalidate_graphs()
         if TAG_KV_CACHE in tags:
             self.engine.alloc_kv_cache()
 

@@ -328,6 +328,15 @@ def kv_append(k, v, k_cache, v_cache, slot_mapping):
     _count("kv_append")
 
 
+_DECODE_IMPL = os.environ.get("CHATLEARN_DECODE", "tc")   # "tc" | "simt"
+
+
+def set_decode_impl(name: str):
+    global _DECODE_IMPL
+    assert name in ("tc", "simt")
+    _DECODE_IMPL = name
+
+
 def _num_splits(n_ctas: int, max_ctx_blocks: int) -> int:
     """Split long contexts when the grid alone cannot fill the 148 SMs."""
     if n_ctas >= 148 * 2 or max_ctx_blocks <= 4:
@@ -359,8 +368,11 @@ def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens=None, sc
     max_blocks = block_tables.shape[1]
     ns = _num_splits(q.shape[0] * nkv, max_blocks)
     _count("paged_decode", 1 if ns == 1 else 2)
-    return C.paged_decode(q.contiguous(), k_cache, v_cache, block_tables.to(torch.int32).contiguous(), q_seq,
-                          ctx.contiguous(), float(scale), ns)
+    # tensor-core kernel for 64-token blocks; the SIMT kernel covers the other block sizes
+    fn = C.paged_decode_tc if (_DECODE_IMPL == "tc" and C.paged_decode_tc_supported(dk, dv, bs, nq // nkv)) \
+        else C.paged_decode
+    return fn(q.contiguous(), k_cache, v_cache, block_tables.to(torch.int32).contiguous(), q_seq,
+              ctx.contiguous(), float(scale), ns)
 
 
 # ------------------------------------------------------------------ weight sync kernel

@@ -46,7 +46,9 @@ class BlockState:
             self.exp_avg = torch.zeros_like(self.master)
             self.exp_avg_sq = torch.zeros_like(self.master)
             self.grad = torch.zeros(n, dtype=grad_dtype, device=device)
-            self.grad_shard = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+            # a group of one owns the whole block: the fp32 accumulation buffer *is* the shard
+            self.grad_shard = self.grad if (group.size == 1 and grad_dtype == torch.float32) else \
+                torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
             block.enable_grad(self.grad)
 
 
@@ -83,7 +85,8 @@ class ShardedTrainState:
             if fused is not None and s.grad.is_cuda:
                 fused(s.grad_shard, s.grad)
             elif g.size == 1:
-                s.grad_shard.copy_(s.grad)
+                if s.grad_shard.data_ptr() != s.grad.data_ptr():
+                    s.grad_shard.copy_(s.grad)
             else:
                 src = s.grad if s.grad.dtype == torch.float32 else s.grad.float()
                 g.reduce_scatter_flat(s.grad_shard, src)

@@ -50,7 +50,7 @@ class RolloutEngine:
                  num_blocks: Optional[int] = None, max_num_seqs: int = 256,
                  max_num_batched_tokens: int = 32768, gpu_memory_utilization: float = 0.8,
                  max_model_len: int = 4096, seed: int = 0, kv_dtype=None,
-                 lockstep_group=None):
+                 lockstep_group=None, use_cuda_graphs: bool = True):
         self.model, self.arch = model, model.arch
         self.device = model.device
         self.tp, self.ep = tp_group, ep_group
@@ -71,6 +71,9 @@ class RolloutEngine:
         # ranks that exchange tokens inside a forward (expert parallel) must run the
         # same number of forwards: they agree on "anyone still busy" every step
         self.lockstep = lockstep_group
+        self.use_graphs = use_cuda_graphs
+        self._graphs: Dict[Any, Any] = {}
+        self._gs = None
 
     # ------------------------------------------------------------------ memory
     def kv_bytes_per_block(self) -> int:
@@ -115,13 +118,17 @@ class RolloutEngine:
             from chatlearn_b200.models.nn.layout import kv_head_range
             nkv_l = kv_head_range(a, tp, self.tp.rank if self.tp is not None else 0)[1]
             dk = dv = a.head_dim
+        # one block beyond the allocator's range is scratch: padded rows of a captured
+        # decode step write their (ignored) KV there
         for _ in range(a.num_hidden_layers):
-            self.k_cache.append(torch.zeros(nb, self.block_size, nkv_l, dk, dtype=self.kv_dtype,
+            self.k_cache.append(torch.zeros(nb + 1, self.block_size, nkv_l, dk, dtype=self.kv_dtype,
                                             device=self.device))
-            self.v_cache.append(torch.zeros(nb, self.block_size, nkv_l, dv, dtype=self.kv_dtype,
+            self.v_cache.append(torch.zeros(nb + 1, self.block_size, nkv_l, dv, dtype=self.kv_dtype,
                                             device=self.device))
+        self.invalidate_graphs()
 
     def free_kv_cache(self):
+        self.invalidate_graphs()
         self.k_cache, self.v_cache = [], []
         self.num_blocks = 0
 
@@ -160,8 +167,112 @@ class RolloutEngine:
             logits = self.tp.all_gather_cat(logits, dim=1)
         return logits
 
+    # ------------------------------------------------------------------ CUDA-graph decode
+    _BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 160, 192, 224, 256, 320, 384, 512)
+
+    def _graph_state(self):
+        """Persistent device inputs/outputs of the captured decode step."""
+        if self._gs is None:
+            dev, n = self.device, max(self.max_num_seqs, 1)
+            n = min(b for b in self._BUCKETS if b >= n) if n <= self._BUCKETS[-1] else n
+            width = math.ceil(self.max_model_len / self.block_size)
+            z = lambda dt, *shape: torch.zeros(*shape, dtype=dt, device=dev)  # noqa: E731
+            self._gs = dict(n=n, width=width, tokens=z(torch.long, n), pos=z(torch.long, n),
+                            slots=z(torch.long, n), seq_lens=z(torch.int32, n), bt=z(torch.int32, n, width),
+                            u=z(torch.float32, n), ids=z(torch.long, n), lp=z(torch.float32, n),
+                            stage=torch.zeros(4, n, dtype=torch.int64, pin_memory=True),
+                            bt_host=torch.zeros(n, width, dtype=torch.int32, pin_memory=True),
+                            bt_len=[0] * n, bt_owner=[None] * n)
+        return self._gs
+
+    def invalidate_graphs(self):
+        """Captured graphs hold raw pointers to the KV cache and the weights."""
+        self._graphs = {}
+        if self._gs is not None:
+            self._gs["bt_owner"] = [None] * self._gs["n"]
+
+    def _decode_body(self, B: int, sp):
+        gs = self._gs
+        kv = KVCtx(self.k_cache, self.v_cache, gs["slots"][:B], gs["bt"][:B], gs["seq_lens"][:B], None, False)
+        ctx = FwdCtx(positions=gs["pos"][:B], cu_seqlens=None, max_seqlen=1, kv=kv, tp=self.tp, ep=self.ep)
+        hidden = self.model.hidden_states(gs["tokens"][:B], ctx)
+        logits = self._logits(hidden)
+        ids, lp = ops.sample(logits, gs["u"][:B], sp.temperature, sp.top_k, sp.top_p, sp.min_p)
+        gs["ids"][:B].copy_(ids)
+        gs["lp"][:B].copy_(lp)
+
+    def _graph_decode(self, plan: StepPlan):
+        """One decode step for every running sequence through a captured CUDA graph.
+        Inputs are written into persistent buffers (one pinned staging copy); the
+        batch is padded to a bucket size with rows that write to a scratch slot."""
+        gs = self._graph_state()
+        seqs = plan.seqs
+        B = len(seqs)
+        Bg = min(b for b in self._BUCKETS if b >= B)
+        bs = self.block_size
+        st = gs["stage"]
+        scratch_block = self.num_blocks          # one block past the allocator's range
+        for i, s in enumerate(seqs):
+            p = s.num_computed                   # position of the token fed now
+            st[0, i] = s.output[-1] if s.output else s.prompt[-1]
+            st[1, i] = p
+            st[2, i] = s.blocks[p // bs] * bs + p % bs
+            st[3, i] = p + 1
+            if gs["bt_owner"][i] is not s or gs["bt_len"][i] != len(s.blocks):
+                nb = len(s.blocks)
+                gs["bt_host"][i, :nb] = torch.tensor(s.blocks, dtype=torch.int32)
+                gs["bt"][i, :nb].copy_(gs["bt_host"][i, :nb], non_blocking=True)
+                xfer.h2d_bytes += nb * 4
+                gs["bt_owner"][i], gs["bt_len"][i] = s, nb
+        for i in range(B, Bg):
+            st[0, i], st[1, i], st[2, i], st[3, i] = 0, 0, scratch_block * bs, 1
+            if gs["bt_owner"][i] != "pad":
+                gs["bt_host"][i, 0] = scratch_block
+                gs["bt"][i, :1].copy_(gs["bt_host"][i, :1], non_blocking=True)
+                gs["bt_owner"][i], gs["bt_len"][i] = "pad", 1
+        gs["tokens"][:Bg].copy_(st[0, :Bg], non_blocking=True)
+        gs["pos"][:Bg].copy_(st[1, :Bg], non_blocking=True)
+        gs["slots"][:Bg].copy_(st[2, :Bg], non_blocking=True)
+        gs["seq_lens"][:Bg].copy_(st[3, :Bg].to(torch.int32), non_blocking=True)
+        xfer.h2d_bytes += Bg * 28
+        gs["u"][:Bg].copy_(torch.rand(Bg, device=self.device, generator=self.gen))
+        sp = seqs[0].sampling
+        key = (Bg, sp.key())
+        g = self._graphs.get(key)
+        if g is None:
+            # warm-up on a side stream, then capture
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._decode_body(Bg, sp)
+            torch.cuda.current_stream().wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._decode_body(Bg, sp)
+            self._graphs[key] = g
+        g.replay()
+        return gs["ids"][:B], gs["lp"][:B]
+
+    def _can_graph(self, plan: StepPlan) -> bool:
+        if not self.use_graphs or self.device.type != "cuda" or plan.is_prefill:
+            return False
+        if ops.get_mode() != "native":
+            return False        # the PyTorch statements of the ops synchronise with the host
+        if any(n != 1 for n in plan.q_lens) or len(plan.seqs) > self._BUCKETS[-1]:
+            return False
+        if self.lockstep is not None and self.lockstep.size > 1:
+            return False
+        k0 = plan.seqs[0].sampling.key()
+        return all(s.sampling.key() == k0 and not s.sampling.has_penalty for s in plan.seqs)
+
     @torch.no_grad()
     def step(self, sched: Scheduler, plan: StepPlan, eos_id: Optional[int]):
+        if self._can_graph(plan):
+            ids, lps = self._graph_decode(plan)
+            for s in plan.seqs:
+                s.num_computed += 1
+            self._finish_step(sched, plan.seqs, ids, lps, eos_id)
+            return
         tokens, ctx, last_rows = self._build_inputs(plan)
         hidden = self.model.hidden_states(tokens, ctx)
         for s, n in zip(plan.seqs, plan.q_lens):
@@ -200,6 +311,10 @@ class RolloutEngine:
                 ids, lps = i_, l_
             else:
                 ids[jj], lps[jj] = i_, l_
+        self._finish_step(sched, seqs, ids, lps, eos_id)
+
+    def _finish_step(self, sched: Scheduler, seqs, ids, lps, eos_id):
+        """Read the sampled tokens back and apply the stop conditions."""
         ids_h, lps_h = xfer.tolist(ids), xfer.tolist(lps)
         for s, tok, lp in zip(seqs, ids_h, lps_h):
             s.output.append(tok)

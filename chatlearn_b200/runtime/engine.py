@@ -72,7 +72,14 @@ class BaseEngine:
             if m.is_member:
                 self.timers(f"setup_{m.name}").start()
                 m.model_setup()
+                # colocated roles release what their config lets them release before the
+                # next role is built (the reference offloads right after setup_engine /
+                # model_setup, runtime/engine.py:103-130)
+                if m.is_colocate:
+                    m.offload()
                 self.timers(f"setup_{m.name}").stop()
+                if torch.cuda.is_available():
+                    logger.debug(f"setup {m.name}: {torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated")
         for m in self.remote_models:
             if m.is_member:
                 m.validate()

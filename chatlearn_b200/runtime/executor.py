@@ -97,7 +97,11 @@ class Executor:
         for i, chunk in enumerate(chunks):
             to_onload, to_offload = self._residency_flags(model, i, len(chunks))
             if to_onload:
-                model.onload()
+                if model.trainable and node.func_name != "train_step":
+                    # scoring with the trainer needs its weights only
+                    model.onload(to_build_grad_buffers=False, to_onload_optimizer_states=False)
+                else:
+                    model.onload()
             model.timers(node.func_name).start()
             res = fn(chunk, iteration, **kwargs) if node.func_name != "train_step" else fn(chunk, **kwargs)
             model.timers(node.func_name).stop()
@@ -106,6 +110,9 @@ class Executor:
             # rollout engines stay resident during evaluation (decorator.py:134-136)
             if to_offload and not (self.is_eval and node is self.first_node):
                 model.offload()
+        if torch.cuda.is_available() and model.total_gpu > 0:
+            logger.debug(f"{tname}: {torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated, "
+                         f"peak {torch.cuda.max_memory_allocated() / 2**30:.1f} GiB")
         return out
 
     def execute_flow(self, samples_by_rank_fn: Callable[[Any], List[Dict]], iteration: int,

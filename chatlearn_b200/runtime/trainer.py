@@ -53,6 +53,9 @@ class Trainer(Executor):
                                                or fg.offload_optimizer_states)
                     if first and frees:
                         m.onload()
+                        if m.device.type == "cuda":
+                            import torch
+                            m._logger.debug(f"train onload: {torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated")
                     m.timers("train_step").start()
                     m.train_step(batch, iteration=self.iteration)
                     m.timers("train_step").stop()

@@ -159,7 +159,10 @@ class ResidencyManager:
         return h
 
     @torch.no_grad()
-    def offload(self, items, release: Optional[Callable] = None):
+    def offload(self, items, release: Optional[Callable] = None, unchanged: bool = False):
+        """``unchanged=True``: the device tensors were not modified since they were
+        last onloaded (frozen models), so an existing host copy is still valid and
+        the device copy is simply dropped."""
         pending = []
         if self.cuda:
             self.stream.wait_stream(torch.cuda.current_stream(self.device))
@@ -168,6 +171,10 @@ class ResidencyManager:
             if t is None or t.device.type == "cpu" or t.numel() == 0:
                 continue
             key = (id(owner), attr)
+            if unchanged and key in self._meta and key in self._host \
+                    and self._host[key].numel() == t.numel():
+                pending.append((owner, attr))
+                continue
             h = self._arena(key, t)
             self._meta[key] = (t.dtype, t.numel())
             if self.cuda:

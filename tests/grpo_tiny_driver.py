@@ -47,6 +47,7 @@ algo.validate()
 stats = algo.run()
 eng = algo.engine
 pol, tr = eng.named_models["policy"], eng.named_models["policy_trainer"]
+tr.onload(to_onload_weights=True, to_build_grad_buffers=False, to_onload_optimizer_states=False)
 sd_t, sd_p = tr.model.hf_state_dict(), pol.model.hf_state_dict()
 maxdiff = 0.0
 for k, v in sd_p.items():

@@ -149,8 +149,10 @@ def test_lmhead_logprob_cublas_path(native, V):
         (lpr * g1 + entr * g2).sum().backward()
         _close(lp, lpr, 2e-2, 2e-2)
         _close(ent, entr, 2e-2, 2e-2)
-        _close(h.grad, hr.grad, 5e-2, 2e-3)
-        _close(w.grad, wr.grad, 5e-2, 2e-3)
+        # gradients pass through bf16 dlogits: compare in relative Frobenius norm
+        for a, b in ((h.grad, hr.grad), (w.grad, wr.grad)):
+            rel = (a.float() - b).norm() / b.norm()
+            assert rel < 2e-2, rel
     finally:
         native.set_gemm_impl("tcgen05")
 
@@ -195,9 +197,20 @@ def test_paged_attention_decode(native, d, nq, nkv, bs):
     vc = torch.randn(nb * 4, bs, nkv, d, device=DEV).bfloat16()
     perm = torch.randperm(nb * 4, device=DEV)[:B * maxb].view(B, maxb).int()
     q = torch.randn(B, nq, d, device=DEV).bfloat16()
-    o = native.paged_attention(q, kc, vc, perm, seq_lens, None, None)
     o_r = ref.paged_attention(q, kc, vc, perm, seq_lens, None, None)
-    _close(o, o_r, 2e-2, 2e-2)
+    for impl in ("tc", "simt"):          # tensor-core kernel (64-token blocks) and the SIMT kernel
+        native.set_decode_impl(impl)
+        o = native.paged_attention(q, kc, vc, perm, seq_lens, None, None)
+        _close(o, o_r, 2e-2, 2e-2)
+    native.set_decode_impl("tc")
+    # long context: exercises the split-KV path and its merge kernel
+    if bs == 64:
+        sl2 = torch.tensor([4000], dtype=torch.int32, device=DEV)
+        nb2 = (4000 + bs - 1) // bs
+        bt2 = torch.randperm(nb * 4, device=DEV)[:nb2].view(1, nb2).int()
+        q1 = torch.randn(1, nq, d, device=DEV).bfloat16()
+        _close(native.paged_attention(q1, kc, vc, bt2, sl2, None, None),
+               ref.paged_attention(q1, kc, vc, bt2, sl2, None, None), 2e-2, 2e-2)
     # chunk continuation: 3 query tokens for the longest sequence, 1 for the others
     q_lens = torch.tensor([1, 1, 1, 1, 3][:B], dtype=torch.int32, device=DEV)
     q2 = torch.randn(int(q_lens.sum()), nq, d, device=DEV).bfloat16()
