@@ -1,0 +1,216 @@
+"""GRPO policy trainer / scorer on the tensor-, pipeline-, context- and
+expert-parallel back end.
+
+Parity: chatlearn/algorithm/grpo_utils/megatron_policy_trainer.py:55-327 and
+megatron_utils/train_helper.py:233-603 (THD packing with every sequence padded for
+CP, CP zig-zag split, per-token loss sums with the global token count, log-prob
+re-gather over CP, last-pipeline-stage outputs).  What Megatron-Core provides in
+the reference (TP layers, 1F1B schedule, alltoall MoE dispatcher, distributed
+optimizer) is this framework's own: TP/EP-sharded ``CausalLM`` leaves with the
+collectives in ``parallel.groups``, the vocab-parallel fused log-prob op, and the
+pipeline schedule below over NCCL point-to-point.
+"""
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from chatlearn_b200 import ops
+from chatlearn_b200.models.megatron_module import MegatronModule
+from chatlearn_b200.models.nn import FwdCtx
+from chatlearn_b200.models.nn.model import decoder_layer
+from chatlearn_b200.parallel.context_parallel import zigzag_indices
+from chatlearn_b200.utils import xfer
+from .trainer_utils import PackedBatch, pack_samples, split_microbatch, unpack_per_sample
+
+
+class MegatronPolicyTrainer(MegatronModule):
+    def setup(self):
+        super().setup()
+        self._metric_prefix = "policy_trainer" if self.trainable else self.name
+
+    # ------------------------------------------------------------------ batching
+    def _max_reduce(self, n: int) -> int:
+        """Bin counts must agree on every rank that runs collectives together: the
+        whole role when pipeline or expert parallelism couples the data-parallel
+        ranks, else the model-parallel group."""
+        t = torch.tensor([n], dtype=torch.int64, device=self.device)
+        for g in (self.mp_group, self.ep_group, self.role_group):
+            if g is not None and g.size > 1:
+                g.all_reduce_(t, op=dist.ReduceOp.MAX)
+        return int(t.item())
+
+    def _microbatches(self, data_list: List[Dict], for_train: bool):
+        ma = self.module_args
+        if ma.packing:
+            return split_microbatch(data_list, packing=True, max_train_token=ma.max_token_in_packing,
+                                    max_reduce=self._max_reduce)
+        mbs = ma.train_micro_batch_size if for_train else ma.generation_batch_size
+        return split_microbatch(data_list, micro_batch_size=max(int(mbs), 1))
+
+    def _prepare(self, mb: List[Dict]):
+        """Packed row of a micro-batch, this CP rank's zig-zag slice and the context."""
+        cp = self.cp_size
+        batch = pack_samples(mb, seq_multiple=2 * cp if cp > 1 else 1) if mb else None
+        if batch is None:
+            return None, None, None
+        batch.to(self.device)
+        ctx = FwdCtx(positions=batch.positions, cu_seqlens=batch.cu_seqlens, max_seqlen=batch.max_seqlen,
+                     tp=self.tp_group if self.tp_size > 1 else None, ep=self.ep)
+        local = None
+        if cp > 1:
+            plan = self.cp.plan(batch.seq_lens, self.device)
+            local = plan["local"]
+            ctx.cp, ctx.cp_plan = self.cp, plan
+            ctx.positions = batch.positions.index_select(0, local)
+        return batch, ctx, local
+
+    # ------------------------------------------------------------------ pipeline plumbing
+    def _send(self, t: torch.Tensor, to_stage: int):
+        dist.send(t.contiguous(), self.pp_group.ranks[to_stage], group=self.pp_group.pg)
+
+    def _recv(self, shape, dtype, from_stage: int) -> torch.Tensor:
+        t = torch.empty(shape, dtype=dtype, device=self.device)
+        dist.recv(t, self.pp_group.ranks[from_stage], group=self.pp_group.pg)
+        return t
+
+    def _stage_forward(self, batch: PackedBatch, ctx: FwdCtx, local, x_in: Optional[torch.Tensor]):
+        """Forward of this pipeline stage.  Returns hidden states (intermediate
+        stages) or ``(logprobs, entropy)`` on the last stage."""
+        tokens = batch.tokens if local is None else batch.tokens.index_select(0, local)
+        hook = None
+        if torch.is_grad_enabled() and getattr(self.module_args, "recompute_granularity", None) == "full":
+            from torch.utils.checkpoint import checkpoint
+            arch = self.model.arch
+
+            def hook(l, p, x, c):
+                return checkpoint(lambda xx: decoder_layer(arch, p, xx, c, l), x, use_reentrant=False)
+        if self.is_first_stage:
+            h = self.model.hidden_states(tokens, ctx, hook)
+        else:
+            h = x_in
+            for l in range(*self.model.layer_range):
+                p = self.model.layer_params(l)
+                h = hook(l, p, h, ctx) if hook else decoder_layer(self.model.arch, p, h, ctx, l)
+            if self.is_last_stage:
+                h = ops.rmsnorm(h, self.model.block_by_name["head"].params["norm"], self.model.arch.rms_norm_eps)
+        if not self.is_last_stage:
+            return h
+        labels = batch.labels if local is None else batch.labels.index_select(0, local)
+        w = self.model.lm_head_weight()
+        if self.tp_size > 1 and w.shape[0] != self.model.arch.vocab_size:
+            from chatlearn_b200.parallel.tp_ops import vocab_parallel_logprob_entropy
+            return vocab_parallel_logprob_entropy(h, w, labels, self.tp_group)
+        return ops.lmhead_logprob_entropy(h, w, labels)
+
+    def _local_tokens(self, batch: PackedBatch, local) -> int:
+        return int(local.numel()) if local is not None else batch.num_tokens
+
+    # ------------------------------------------------------------------ scoring
+    @torch.no_grad()
+    def forward_step(self, data_list: List[Dict], iteration: int = 0, **kwargs) -> List[Dict]:
+        tag = "old_logprobs" if self.trainable else "ref_logprobs"
+        H = self.model.arch.hidden_size
+        for mb in self._microbatches(data_list, for_train=False):
+            batch, ctx, local = self._prepare(mb)
+            if batch is None:
+                continue
+            n_local = self._local_tokens(batch, local)
+            x_in = None if self.is_first_stage else self._recv((n_local, H), self.compute_dtype, self.pp_rank - 1)
+            out = self._stage_forward(batch, ctx, local, x_in)
+            if not self.is_last_stage:
+                self._send(out, self.pp_rank + 1)
+                continue
+            lp = out[0]
+            if self.cp_size > 1:
+                lp = self.cp.gather_tokens(lp, ctx.cp_plan)      # true all-gather, global order
+            for s, v in zip(mb, unpack_per_sample(lp, batch, mb)):
+                s[tag] = v
+        return data_list
+
+    # ------------------------------------------------------------------ training
+    def _loss(self, batch: PackedBatch, local, lp, ent, inv_norm):
+        ma = self.module_args
+        sel = (lambda t: t if (t is None or local is None) else t.index_select(0, local))
+        use_ref = ma.kl_coef != 0.0 and batch.ref_logprobs is not None
+        need_ent = ma.entropy_coef != 0.0
+        if ma.use_group_sequence_policy:
+            # sequence means need every token of a sequence: gather log-probs over CP first
+            lp_full = lp if self.cp_size == 1 else self.cp_group.gather_seq(lp, 0).index_select(0, self.cp.plan(
+                batch.seq_lens, self.device)["inv"])
+            loss_tok, cpos, cneg = ops.gspo_token_loss(
+                lp_full, batch.old_logprobs, batch.advantages, batch.seq_ids, len(batch.seq_lens),
+                batch.loss_mask, ma.pos_clip_ratio, ma.neg_clip_ratio, ma.diff_clip_ratio, ma.final_clip_ratio)
+            m = batch.loss_mask
+            total = (loss_tok * m).sum() / max(self.cp_size, 1)   # every CP rank holds the full row
+            stats = torch.stack([(loss_tok.detach() * m).sum(), torch.zeros((), device=self.device),
+                                 torch.zeros((), device=self.device), (cpos.float() * m).sum(),
+                                 (cneg.float() * m).sum(), m.sum()]) / max(self.cp_size, 1)
+            return total * inv_norm, stats
+        return ops.grpo_loss_fused(
+            lp, sel(batch.old_logprobs), sel(batch.ref_logprobs) if use_ref else None, sel(batch.advantages),
+            sel(batch.loss_mask), ent if need_ent else ent.detach(), ma.pos_clip_ratio, ma.neg_clip_ratio,
+            ma.diff_clip_ratio, ma.final_clip_ratio, ma.kl_coef, ma.entropy_coef if need_ent else 0.0, inv_norm)
+
+    def train_step(self, data_list: List[Dict], **kwargs):
+        st = self.state
+        H = self.model.arch.hidden_size
+        n_tok = torch.tensor([float(sum(int(s["response_token_length"]) for s in data_list))],
+                             dtype=torch.float32, device=self.device)
+        # every rank of a model-parallel group holds the same samples: count them once
+        n_tok /= (self.tp_size * self.cp_size * self.pp_size)
+        self.mp_group.all_reduce_(n_tok)
+        if self.mesh.groups["dp"].size > 1:
+            self.mesh.groups["dp"].all_reduce_(n_tok)
+        inv_norm = 1.0 / max(float(n_tok.item()), 1.0)
+        st.zero_grad()
+        stats = torch.zeros(6, dtype=torch.float32, device=self.device)
+        mbs = [self._prepare(mb) for mb in self._microbatches(data_list, for_train=True)]
+        mbs = [m for m in mbs if m[0] is not None]
+        # schedule: forward every micro-batch through the stages, then backward in reverse
+        # order (activations of a stage are alive between its forward and backward);
+        # the stage boundary tensors travel over NCCL point-to-point
+        pending = []
+        for batch, ctx, local in mbs:
+            n_local = self._local_tokens(batch, local)
+            x_in = None
+            if not self.is_first_stage:
+                x_in = self._recv((n_local, H), self.compute_dtype, self.pp_rank - 1).requires_grad_(True)
+            out = self._stage_forward(batch, ctx, local, x_in)
+            if self.is_last_stage:
+                lp, ent = out
+                loss, s = self._loss(batch, local, lp, ent, inv_norm)
+                for aux in ctx.aux_losses:
+                    loss = loss + aux * (batch.loss_mask.sum() * inv_norm)
+                stats += s.detach()
+                pending.append((loss, x_in, None))
+            else:
+                self._send(out.detach(), self.pp_rank + 1)
+                # auxiliary (router) losses of intermediate stages are back-propagated locally
+                aux = sum(ctx.aux_losses) * (batch.loss_mask.sum() * inv_norm) if ctx.aux_losses else None
+                pending.append((out, x_in, aux))
+        for out, x_in, aux in reversed(pending):
+            if self.is_last_stage:
+                out.backward()
+            else:
+                g = self._recv(out.shape, out.dtype, self.pp_rank + 1)
+                if aux is not None:
+                    torch.autograd.backward([out, aux], [g, torch.ones_like(aux)])
+                else:
+                    out.backward(g)
+            if x_in is not None:
+                self._send(x_in.grad, self.pp_rank - 1)
+        grad_norm = st.step()
+        # metrics live on the last stage; share them with the whole model-parallel group
+        if self.pp_size > 1:
+            self.pp_group.all_reduce_(stats)
+        if self.mesh.groups["dp"].size > 1:
+            self.mesh.groups["dp"].all_reduce_(stats)
+        if self.cp_size > 1:
+            self.cp_group.all_reduce_(stats)
+        host = xfer.tolist(torch.cat([stats, grad_norm.reshape(1).float()]))
+        n = max(host[5], 1.0)
+        self._metric_list.append({
+            "pg_loss": host[0] / n, "kl_loss": host[1] / n, "entropy_loss": host[2] / n, "grad_norm": host[6],
+            "clip_pos_frac": host[3] / n, "clip_neg_frac": host[4] / n, "train_tokens": n})
+        self._train_iteration += 1

@@ -1,0 +1,197 @@
+"""Megatron-style worker: tensor / pipeline / context / expert parallel model role.
+
+Parity: chatlearn/models/megatron_module.py:65-331 (distributed initialisation,
+memory managers, checkpoint hooks, global parameter naming for PP/VPP layer
+offsets and EP expert offsets, parameter metadata for the synchronizer).  The
+reference delegates the model and its parallel runtime to Megatron-Core; here the
+role builds this framework's ``CausalLM`` with TP/EP-sharded leaves for its
+pipeline stage, wires the process groups of ``parallel.mesh`` into the forward
+context, and shards the optimizer state over the (data x context) parallel group
+(dense leaves) and the expert-data-parallel group (expert leaves), i.e. the
+distributed optimizer.  Global naming is implicit: every leaf carries the HF
+tensor rectangles it holds, so PP layer offsets and EP expert offsets need no
+separate translation step.
+"""
+import math
+import os
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from chatlearn_b200.models.base_module import TorchModule
+from chatlearn_b200.models.fsdp_module import FSDPModule
+from chatlearn_b200.models.nn import CausalLM, ModelArch, resolve_arch
+from chatlearn_b200.parallel import ContextParallel, ExpertParallel, build_mesh
+from chatlearn_b200.parallel.zero import ShardedTrainState
+from chatlearn_b200.synchronizer.parameter_sync import layout_of_model
+
+
+def arch_from_megatron_cfg(mc) -> ModelArch:
+    """``MegatronModelArchitectureConfig`` → ``ModelArch`` (inverse of
+    ``utils.megatron_utils.update_cfg``)."""
+    moe = mc.num_experts is not None and mc.num_experts > 0
+    mla = bool(mc.multi_latent_attention)
+    return ModelArch(
+        model_type="deepseek_v3" if mla else ("qwen3_moe" if moe else ("qwen3" if mc.qk_layernorm else "llama")),
+        vocab_size=mc.vocab_size, hidden_size=mc.hidden_size, num_hidden_layers=mc.num_layers,
+        num_attention_heads=mc.num_attention_heads,
+        num_key_value_heads=mc.num_query_groups or mc.num_attention_heads,
+        head_dim=(mc.qk_head_dim + mc.qk_pos_emb_head_dim) if mla else mc.kv_channels,
+        intermediate_size=mc.ffn_hidden_size, rms_norm_eps=mc.norm_epsilon, rope_theta=float(mc.rotary_base),
+        max_position_embeddings=mc.max_position_embeddings, qk_norm=mc.qk_layernorm,
+        attention_bias=mc.add_qkv_bias, tie_word_embeddings=not mc.untie_embeddings_and_output_weights,
+        num_experts=mc.num_experts or 0, num_experts_per_tok=mc.moe_router_topk if moe else 0,
+        moe_intermediate_size=mc.moe_ffn_hidden_size or 0, router_aux_loss_coef=mc.moe_aux_loss_coeff,
+        n_shared_experts=((mc.moe_shared_expert_intermediate_size or 0) // max(mc.moe_ffn_hidden_size or 1, 1)),
+        first_k_dense_replace=(mc.moe_layer_freq.index(1) if isinstance(mc.moe_layer_freq, list)
+                               and 1 in mc.moe_layer_freq else 0),
+        scoring_func=mc.moe_router_score_function, n_group=mc.moe_router_num_groups or 1,
+        topk_group=mc.moe_router_group_topk or 1, routed_scaling_factor=mc.moe_router_topk_scaling_factor or 1.0,
+        router_bias=mc.moe_router_enable_expert_bias, kv_lora_rank=mc.kv_lora_rank if mla else 0,
+        q_lora_rank=mc.q_lora_rank, qk_nope_head_dim=mc.qk_head_dim if mla else 0,
+        qk_rope_head_dim=mc.qk_pos_emb_head_dim if mla else 0, v_head_dim=(mc.v_head_dim or 0) if mla else 0)
+
+
+def pipeline_layer_range(num_layers: int, pp: int, stage: int, first: Optional[int] = None,
+                         last: Optional[int] = None) -> Tuple[int, int]:
+    """Layers of a pipeline stage; ``first`` / ``last`` fix the size of the first and
+    last stage (uneven pipelines, megatron_config ``decoder_first/last_pipeline_num_layers``)."""
+    if pp == 1:
+        return 0, num_layers
+    sizes = [0] * pp
+    rem, mids = num_layers, list(range(pp))
+    if first is not None:
+        sizes[0] = first
+        rem -= first
+        mids.remove(0)
+    if last is not None:
+        sizes[-1] = last
+        rem -= last
+        mids.remove(pp - 1)
+    base, extra = divmod(rem, len(mids))
+    for i, s in enumerate(mids):
+        sizes[s] = base + (1 if i < extra else 0)
+    lo = sum(sizes[:stage])
+    return lo, lo + sizes[stage]
+
+
+class MegatronModule(FSDPModule):
+    """Shares checkpoint / residency plumbing with the FSDP-style role; differs in
+    how the model is partitioned and which groups reduce what."""
+
+    def init(self):
+        ma = self.module_args
+        self.tp_size = int(ma.tensor_model_parallel_size)
+        self.pp_size = int(ma.pipeline_model_parallel_size)
+        self.cp_size = int(ma.context_parallel_size)
+        self.ep_size = int(ma.expert_model_parallel_size)
+        self.etp_size = int(ma.expert_tensor_parallel_size or 1)
+        assert self.etp_size == 1, "expert tensor parallelism > 1 is not supported (experts are EP-sharded)"
+        self.mesh = build_mesh(self.placement, tp=self.tp_size, cp=self.cp_size, pp=self.pp_size,
+                               ep=self.ep_size, etp=self.etp_size,
+                               kinds=("tp", "cp", "dp", "pp", "ep", "edp", "dp_cp", "mp"))
+        self.sp = None
+        if self.is_member:
+            g = self.mesh.groups
+            self.tp_group, self.cp_group, self.pp_group = g["tp"], g["cp"], g["pp"]
+            self.ep_group, self.edp_group = g["ep"], g["edp"]
+            self.dp_group = g["dp_cp"]            # gradients of dense leaves reduce over dp x cp
+            self.role_group = g["dp_cp"]
+            self.mp_group = g["mp"]               # ranks that share one data shard (tp x cp x pp)
+            c = self.mesh.coords
+            self.pp_rank, self.tp_rank, self.cp_rank, self.ep_rank = c["pp"], c["tp"], c["cp"], c["ep"]
+
+    @property
+    def is_data_leader(self) -> bool:
+        if not self.is_member:
+            return False
+        c = self.mesh.coords
+        return c["tp"] == 0 and c["cp"] == 0 and c["pp"] == self.pp_size - 1
+
+    @property
+    def data_parallel_size(self) -> int:
+        return max(len(self.placement) // (self.tp_size * self.cp_size * self.pp_size), 1)
+
+    @property
+    def data_parallel_rank(self) -> int:
+        return self.mesh.coords.get("dp", 0) if self.is_member else -1
+
+    @property
+    def is_first_stage(self):
+        return self.pp_rank == 0
+
+    @property
+    def is_last_stage(self):
+        return self.pp_rank == self.pp_size - 1
+
+    def resolve_arch(self) -> ModelArch:
+        ma = self.module_args
+        if getattr(ma, "model_arch", None) or (ma.load and os.path.exists(os.path.join(ma.load, "config.json"))):
+            return resolve_arch(ma)
+        return arch_from_megatron_cfg(ma.megatron_model_cfg)
+
+    def create_model(self) -> CausalLM:
+        ma = self.module_args
+        arch = self.resolve_arch()
+        lo, hi = pipeline_layer_range(arch.num_hidden_layers, self.pp_size, self.pp_rank,
+                                      ma.decoder_first_pipeline_num_layers, ma.decoder_last_pipeline_num_layers)
+        pad = math.lcm(self.dp_group.size, self.edp_group.size)
+        model = CausalLM(arch, dtype=self.compute_dtype, device=self.device, tp=self.tp_size, tp_rank=self.tp_rank,
+                         ep=self.ep_size, ep_rank=self.ep_rank, layer_range=(lo, hi),
+                         with_embed=self.is_first_stage or (arch.tie_word_embeddings and self.is_last_stage),
+                         with_head=self.is_last_stage, pad_to=pad)
+        from chatlearn_b200.checkpoint.safetensors_io import has_safetensors, load_into_model
+        if ma.load and has_safetensors(ma.load):
+            load_into_model(model, ma.load)
+        else:
+            model.init_weights(int(ma.seed))
+        return model
+
+    def setup(self):
+        if not self.is_member:
+            return
+        self.arch = self.resolve_arch()
+        self.model = self.create_model()
+        self.ep = ExpertParallel(self.ep_group) if self.ep_size > 1 else None
+        self.cp = ContextParallel(self.cp_group) if self.cp_size > 1 else None
+        if self.trainable:
+            oc = self.module_args.optimizer
+            extra = [g for g in (self.tp_group, self.pp_group) if g.size > 1]
+            self.state = ShardedTrainState(
+                self.model, self.dp_group, self.edp_group if self.ep_size > 1 else None, lr=oc.lr,
+                betas=(oc.adam_beta1, oc.adam_beta2), eps=getattr(oc, "adam_eps", 1e-8),
+                weight_decay=oc.weight_decay, clip_grad=oc.clip_grad, extra_norm_groups=extra,
+                tp_size=self.tp_size, ep_group=self.ep_group if self.ep_size > 1 else None,
+                tp_group=self.tp_group if self.tp_size > 1 else None)
+
+    # ------------------------------------------------------------------ checkpoints (Megatron layout)
+    def checkpoint_dir(self, iteration: int) -> str:
+        return os.path.join(self.runtime_args.output_dir, "save_model", self.name)
+
+    def save_checkpoint(self, iteration: int):
+        """``iter_{it:07d}/mp_rank_{tp:02d}[_{pp:03d}][_{ep:03d}]/model_optim_rng.pt`` +
+        ``latest_checkpointed_iteration.txt``; one writer per model-parallel rank
+        (data-parallel rank 0), optimizer shards per data-parallel rank alongside."""
+        if not self.is_member or self.model is None:
+            return
+        from chatlearn_b200.checkpoint.megatron_ckpt import save_megatron_checkpoint
+        save_megatron_checkpoint(self, self.checkpoint_dir(iteration), iteration)
+        if self.role_group is not None:
+            self.role_group.barrier()
+
+    def load_checkpoint(self, path: str):
+        from chatlearn_b200.checkpoint.megatron_ckpt import load_megatron_checkpoint
+        return load_megatron_checkpoint(self, path)
+
+    # ------------------------------------------------------------------ sync metadata (API parity)
+    def map_local_param_name_to_global(self) -> List[str]:
+        """HF tensor names this rank holds a part of (the reference's "global names")."""
+        names = []
+        for _, _, lf, _ in self.model.named_leaves():
+            for s in lf.segments:
+                if s.hf_name not in names:
+                    names.append(s.hf_name)
+        return names
+
+    def get_parameter_metadata(self):
+        return layout_of_model(self.model, self.get_rank(), prefix=f"{self.name}/")

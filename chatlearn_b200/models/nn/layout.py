@@ -36,6 +36,7 @@ class Leaf:
     init: str = "normal"               # normal | ones | zeros
     segments: List[Segment] = field(default_factory=list)
     replicated: bool = False           # same content on every model-parallel rank
+    grad_sum_tp: bool = False          # gradient is a partial sum per TP rank (needs an all-reduce)
 
     @property
     def numel(self) -> int:
@@ -128,6 +129,8 @@ def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int
         if arch.qk_norm:
             out.append(_full(pre + "q_norm", (d,), a + "q_norm.weight", "ones"))
             out.append(_full(pre + "k_norm", (d,), a + "k_norm.weight", "ones"))
+            # shared by all heads: with heads split over TP each rank sees a partial gradient
+            out[-1].grad_sum_tp = out[-2].grad_sum_tp = tp > 1
         fs = (H, nh * d)
         out.append(Leaf(pre + "o_proj", (H, nh_l * d), "normal",
                         [_cols(a + "o_proj.weight", fs, tp_rank * nh_l * d, nh_l * d)]))

@@ -228,7 +228,24 @@ def moe_block(arch: ModelArch, p, x, ctx: FwdCtx):
         ctx.aux_losses.append(arch.router_aux_loss_coef *
                               ops.moe_aux_loss(scores, idx, arch.num_experts, arch.num_experts_per_tok))
     if ctx.ep is not None and ctx.ep.size > 1:
-        y = ctx.ep.experts(x, p["w13"], p["w2"], w, idx, arch.num_experts)
+        tp = ctx.tp
+        if tp is not None and tp.size > 1:
+            # the ranks of a TP group hold the same tokens: each dispatches its own
+            # 1/tp slice, so an expert sees every token once, and the outputs are
+            # all-gathered back (gradient: this rank's slice)
+            T = x.shape[0]
+            pad = (-T) % tp.size
+            # each rank back-propagates only its slice: sum the slices' gradients over TP
+            x_, w_, i_ = _tp_copy(x, ctx), _tp_copy(w, ctx), idx
+            if pad:
+                x_, w_ = torch.nn.functional.pad(x_, (0, 0, 0, pad)), torch.nn.functional.pad(w_, (0, 0, 0, pad))
+                i_ = torch.nn.functional.pad(idx, (0, 0, 0, pad))
+            n = (T + pad) // tp.size
+            sl = slice(tp.rank * n, (tp.rank + 1) * n)
+            y_loc = ctx.ep.experts(x_[sl], p["w13"], p["w2"], w_[sl], i_[sl], arch.num_experts)
+            y = tp.gather_seq(y_loc, 0)[:T]
+        else:
+            y = ctx.ep.experts(x, p["w13"], p["w2"], w, idx, arch.num_experts)
     else:
         y = ops.moe_experts(x, p["w13"], p["w2"], w, idx)
     if "shared_gate_up" in p:
@@ -335,7 +352,11 @@ class CausalLM:
     def logprobs(self, tokens, labels, ctx: FwdCtx, temperature=1.0, layer_hook=None):
         """Per-token log p(label) and entropy for a packed row, never building ``[T, V]``."""
         h = self.hidden_states(tokens, ctx, layer_hook)
-        return ops.lmhead_logprob_entropy(h, self.lm_head_weight(), labels, temperature)
+        w = self.lm_head_weight()
+        if ctx.tp is not None and ctx.tp.size > 1 and w.shape[0] != self.arch.vocab_size:
+            from chatlearn_b200.parallel.tp_ops import vocab_parallel_logprob_entropy
+            return vocab_parallel_logprob_entropy(h, w, labels, ctx.tp, temperature)
+        return ops.lmhead_logprob_entropy(h, w, labels, temperature)
 
     def score(self, tokens, ctx: FwdCtx):
         """Reward/value head: ``[T, num_labels]``."""

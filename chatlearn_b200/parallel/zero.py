@@ -56,8 +56,10 @@ class ShardedTrainState:
     def __init__(self, model: CausalLM, dp_group: Optional[Group] = None,
                  expert_dp_group: Optional[Group] = None, lr=2e-6, betas=(0.9, 0.95), eps=1e-8,
                  weight_decay=0.01, clip_grad=1.0, grad_dtype=torch.float32,
-                 extra_norm_groups: Optional[List[Group]] = None):
+                 extra_norm_groups: Optional[List[Group]] = None, tp_size: int = 1,
+                 ep_group: Optional[Group] = None, tp_group: Optional[Group] = None):
         self.model = model
+        self.tp_size, self.ep_group, self.tp_group = tp_size, ep_group, tp_group
         self.dp = dp_group or single_group()
         self.edp = expert_dp_group or self.dp
         self.lr, self.betas, self.eps, self.wd, self.clip = lr, betas, eps, weight_decay, clip_grad
@@ -80,6 +82,12 @@ class ShardedTrainState:
     def reduce_grads(self):
         """Reduce-scatter every block's accumulated gradient into its fp32 shard."""
         for s in self.states:
+            if self.tp_group is not None and self.tp_group.size > 1:
+                # leaves shared by tensor-sharded heads hold partial sums: complete them first
+                for lf in s.block.leaves:
+                    if getattr(lf, "grad_sum_tp", False):
+                        o = s.block.offsets[lf.name]
+                        self.tp_group.all_reduce_(s.grad[o:o + lf.numel])
             g = s.group
             fused = g.fast.get("reduce_scatter_f32")
             if fused is not None and s.grad.is_cuda:
@@ -92,25 +100,61 @@ class ShardedTrainState:
                 g.reduce_scatter_flat(s.grad_shard, src)
 
     @torch.no_grad()
+    def _norm_ranges(self, s: "BlockState"):
+        """(start, end, weight) pieces of a block's shard for the squared norm: leaves
+        replicated over the tensor-parallel group carry weight 1/tp so that the sum over
+        that group counts them once."""
+        cached = getattr(s, "_norm_ranges", None)
+        if cached is not None:
+            return cached
+        if self.tp_size == 1:
+            out = [(0, s.shard_numel, 1.0)]
+        else:
+            out = []
+            for lf in s.block.leaves:
+                o = s.block.offsets[lf.name]
+                a, b = max(o, s.lo), min(o + lf.numel, s.hi)
+                if b <= a:
+                    continue
+                # expert blocks are summed over the expert-parallel group instead (below)
+                rep = lf.replicated and not s.block.name.endswith(".experts")
+                w = 1.0 / self.tp_size if rep else 1.0
+                if out and out[-1][2] == w and out[-1][1] == a - s.lo:
+                    out[-1] = (out[-1][0], b - s.lo, w)
+                else:
+                    out.append((a - s.lo, b - s.lo, w))
+        s._norm_ranges = out
+        return out
+
     def grad_norm(self) -> torch.Tensor:
-        """Global L2 norm of the reduced gradient.  Leaves replicated inside a model
-        parallel group are counted once (their shard is identical on those ranks)."""
+        """Global L2 norm of the reduced gradient: shards are summed over their
+        data-parallel group, expert shards additionally over the expert-parallel group,
+        then everything over the tensor / pipeline groups (replicated leaves once)."""
         dev = self.model.device
         dp_sq = torch.zeros((), dtype=torch.float32, device=dev)
         edp_sq = torch.zeros((), dtype=torch.float32, device=dev)
         for s in self.states:
-            v = ops.sumsq(s.grad_shard)
+            v = torch.zeros((), dtype=torch.float32, device=dev)
+            for a, b, w in self._norm_ranges(s):
+                v = v + ops.sumsq(s.grad_shard[a:b]) * w
             if s.group is self.edp and self.edp is not self.dp:
                 edp_sq += v
             else:
                 dp_sq += v
+        # dense leaves: shards over dp, then the tensor- and pipeline-parallel groups;
+        # expert leaves: shards over expert-dp, then the expert- and pipeline-parallel
+        # groups (never the tensor group: expert weights are not tensor-sharded)
         self.dp.all_reduce_(dp_sq)
+        for g in self.extra_norm_groups:
+            g.all_reduce_(dp_sq)
         if self.edp is not self.dp:
             self.edp.all_reduce_(edp_sq)
-        total = dp_sq + edp_sq
-        for g in self.extra_norm_groups:
-            g.all_reduce_(total)
-        return total.sqrt()
+            if self.ep_group is not None:
+                self.ep_group.all_reduce_(edp_sq)
+            for g in self.extra_norm_groups:
+                if g is not self.tp_group:
+                    g.all_reduce_(edp_sq)
+        return (dp_sq + edp_sq).sqrt()
 
     @torch.no_grad()
     def step(self, lr: Optional[float] = None) -> float:

@@ -177,8 +177,9 @@ class RolloutEngine:
             n = min(b for b in self._BUCKETS if b >= n) if n <= self._BUCKETS[-1] else n
             width = math.ceil(self.max_model_len / self.block_size)
             z = lambda dt, *shape: torch.zeros(*shape, dtype=dt, device=dev)  # noqa: E731
-            self._gs = dict(n=n, width=width, tokens=z(torch.long, n), pos=z(torch.long, n),
-                            slots=z(torch.long, n), seq_lens=z(torch.int32, n), bt=z(torch.int32, n, width),
+            in64 = z(torch.long, 4, n)          # rows: token, position, KV slot, sequence length
+            self._gs = dict(n=n, width=width, in64=in64, tokens=in64[0], pos=in64[1],
+                            slots=in64[2], seq_lens=z(torch.int32, n), bt=z(torch.int32, n, width),
                             u=z(torch.float32, n), ids=z(torch.long, n), lp=z(torch.float32, n),
                             stage=torch.zeros(4, n, dtype=torch.int64, pin_memory=True),
                             bt_host=torch.zeros(n, width, dtype=torch.int32, pin_memory=True),
@@ -212,29 +213,32 @@ class RolloutEngine:
         bs = self.block_size
         st = gs["stage"]
         scratch_block = self.num_blocks          # one block past the allocator's range
+        # plain Python lists, one tensor construction: per-element tensor writes would
+        # cost more host time than the whole step takes on the GPU
+        rows = [[0] * Bg, [0] * Bg, [scratch_block * bs] * Bg, [1] * Bg]
+        owner, blen = gs["bt_owner"], gs["bt_len"]
         for i, s in enumerate(seqs):
             p = s.num_computed                   # position of the token fed now
-            st[0, i] = s.output[-1] if s.output else s.prompt[-1]
-            st[1, i] = p
-            st[2, i] = s.blocks[p // bs] * bs + p % bs
-            st[3, i] = p + 1
-            if gs["bt_owner"][i] is not s or gs["bt_len"][i] != len(s.blocks):
-                nb = len(s.blocks)
-                gs["bt_host"][i, :nb] = torch.tensor(s.blocks, dtype=torch.int32)
-                gs["bt"][i, :nb].copy_(gs["bt_host"][i, :nb], non_blocking=True)
-                xfer.h2d_bytes += nb * 4
-                gs["bt_owner"][i], gs["bt_len"][i] = s, nb
+            rows[0][i] = s.output[-1] if s.output else s.prompt[-1]
+            rows[1][i] = p
+            rows[2][i] = s.blocks[p // bs] * bs + p % bs
+            rows[3][i] = p + 1
+            nb = len(s.blocks)
+            if owner[i] is not s or blen[i] != nb:
+                first = blen[i] if owner[i] is s else 0        # only the new tail of a known table
+                gs["bt_host"][i, first:nb] = torch.tensor(s.blocks[first:nb], dtype=torch.int32)
+                gs["bt"][i, first:nb].copy_(gs["bt_host"][i, first:nb], non_blocking=True)
+                xfer.h2d_bytes += (nb - first) * 4
+                owner[i], blen[i] = s, nb
         for i in range(B, Bg):
-            st[0, i], st[1, i], st[2, i], st[3, i] = 0, 0, scratch_block * bs, 1
-            if gs["bt_owner"][i] != "pad":
+            if owner[i] != "pad":
                 gs["bt_host"][i, 0] = scratch_block
                 gs["bt"][i, :1].copy_(gs["bt_host"][i, :1], non_blocking=True)
-                gs["bt_owner"][i], gs["bt_len"][i] = "pad", 1
-        gs["tokens"][:Bg].copy_(st[0, :Bg], non_blocking=True)
-        gs["pos"][:Bg].copy_(st[1, :Bg], non_blocking=True)
-        gs["slots"][:Bg].copy_(st[2, :Bg], non_blocking=True)
-        gs["seq_lens"][:Bg].copy_(st[3, :Bg].to(torch.int32), non_blocking=True)
-        xfer.h2d_bytes += Bg * 28
+                owner[i], blen[i] = "pad", 1
+        st[:, :Bg] = torch.tensor(rows, dtype=torch.int64)
+        gs["in64"].copy_(st, non_blocking=True)              # one pinned -> device copy per step
+        gs["seq_lens"].copy_(gs["in64"][3])                   # int64 -> int32 on the device
+        xfer.h2d_bytes += st.numel() * 8
         gs["u"][:Bg].copy_(torch.rand(Bg, device=self.device, generator=self.gen))
         sp = seqs[0].sampling
         key = (Bg, sp.key())
@@ -315,7 +319,9 @@ class RolloutEngine:
 
     def _finish_step(self, sched: Scheduler, seqs, ids, lps, eos_id):
         """Read the sampled tokens back and apply the stop conditions."""
-        ids_h, lps_h = xfer.tolist(ids), xfer.tolist(lps)
+        # one device -> host read per step (token ids are exact in fp32: vocab < 2^24)
+        both = xfer.tolist(torch.stack([ids.float(), lps.float()]))
+        ids_h, lps_h = [int(x) for x in both[0]], both[1]
         for s, tok, lp in zip(seqs, ids_h, lps_h):
             s.output.append(tok)
             s.logprobs.append(lp)

@@ -1,0 +1,107 @@
+"""Runs one forward_step + one train_step of the Megatron-style trainer on a fixed
+batch and saves the result (used by test_megatron_cpu.py; one process per rank)."""
+import json
+import os
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+from chatlearn_b200.algorithm.grpo import GrpoConfig  # noqa: E402
+from chatlearn_b200.checkpoint.safetensors_io import save_hf_checkpoint  # noqa: E402
+from chatlearn_b200.configs import resolve, to_dataclass  # noqa: E402
+from chatlearn_b200.launcher.initialize import init  # noqa: E402
+from chatlearn_b200.models.nn import PRESETS, CausalLM  # noqa: E402
+
+out = os.environ["OUT_DIR"]
+tag = os.environ["TAG"]
+W = int(os.environ.get("WORLD_SIZE", "1"))
+rank = int(os.environ.get("RANK", "0"))
+tp, pp, cp, ep = (int(os.environ.get(k, "1")) for k in ("TP", "PP", "CP", "EP"))
+preset = os.environ.get("PRESET", "tiny_qwen3")
+hf_dir = os.path.join(out, "hf_init")
+if rank == 0 and not os.path.exists(os.path.join(hf_dir, "done")):
+    a0 = PRESETS[preset]()
+    if os.environ.get("NOAUX", "0") == "1":
+        a0.router_aux_loss_coef = 0.0      # the balancing loss depends on how tokens are grouped into micro-batches
+    m = CausalLM(a0, dtype=torch.float32).init_weights(7, std=0.05)
+    save_hf_checkpoint(m, hf_dir, dtype=torch.float32)
+    open(os.path.join(hf_dir, "done"), "w").close()
+while not os.path.exists(os.path.join(hf_dir, "done")):
+    time.sleep(0.05)
+
+cfg = {
+    "runtime_args": {"train_backend": "megatron", "exp_name": tag, "output_dir": os.path.join(out, tag),
+                     "data_path": "none", "num_episode": 1, "sample_per_episode": 8, "train_micro_batch_size": 2,
+                     "train_global_batch_size": 8, "num_inference_per_prompt": 2, "save_episode_interval": 1,
+                     "enable_resume_training": False, "log_args_dict": {"log_dir": out}},
+    "models": {
+        "policy_trainer": {"num_gpu": W, "trainable": True, "load": hf_dir, "tensor_model_parallel_size": tp,
+                           "pipeline_model_parallel_size": pp, "context_parallel_size": cp,
+                           "expert_model_parallel_size": ep, "packing": os.environ.get("PACKING", "1") == "1",
+                           "max_token_in_packing": 96, "generation_batch_size": 4, "kl_coef": 0.01,
+                           "entropy_coef": 0.001, "optimizer": {"lr": 1e-3, "clip_grad": 1.0},
+                           "use_group_sequence_policy": os.environ.get("GSPO", "0") == "1",
+                           "megatron_model_cfg": {"num_layers": 1, "hidden_size": 8, "num_attention_heads": 1,
+                                                  "ffn_hidden_size": 8, "max_position_embeddings": 64,
+                                                  "kv_channels": 8}},
+        "ref_policy": {"num_gpu": W, "load": hf_dir,
+                       "megatron_model_cfg": {"num_layers": 1, "hidden_size": 8, "num_attention_heads": 1,
+                                              "ffn_hidden_size": 8, "max_position_embeddings": 64, "kv_channels": 8}},
+        "policy": {"num_gpu": W, "model_arch": {"preset": preset}},
+        "reward": {"num_cpu": 1},
+    }}
+cfg = to_dataclass(GrpoConfig, resolve(cfg))
+init(cfg)
+from chatlearn_b200.algorithm.grpo_utils.megatron_policy_trainer import MegatronPolicyTrainer  # noqa: E402
+
+mod = MegatronPolicyTrainer("policy_trainer")
+mod.placement = list(range(W))
+mod.role_rank = rank
+mod.init()
+mod.model_setup()
+
+g = torch.Generator().manual_seed(123)
+arch = mod.model.arch
+samples = []
+for i in range(8):
+    pl, rl = int(torch.randint(4, 12, (1,), generator=g)), int(torch.randint(6, 20, (1,), generator=g))
+    toks = torch.randint(0, arch.vocab_size - 1, (pl + rl,), generator=g)
+    samples.append({"all_tokens": toks, "prompt_token_length": pl, "response_token_length": rl,
+                    "advantages": float(torch.randn((), generator=g)), "prompt_uid": str(i // 2), "uid": i})
+noise = [0.05 * torch.randn(s["all_tokens"].numel() - 1, generator=g) for s in samples]
+dp, dpr = mod.data_parallel_size, mod.data_parallel_rank
+per = len(samples) // dp
+mine = samples[dpr * per:(dpr + 1) * per]
+mine_noise = noise[dpr * per:(dpr + 1) * per]
+mod.forward_step(mine)
+if mod.is_data_leader:
+    for s, nz in zip(mine, mine_noise):
+        s["ref_logprobs"] = s["old_logprobs"] + nz
+        s["old_logprobs"] = s["old_logprobs"] - 0.5 * nz
+else:
+    for s, nz in zip(mine, mine_noise):        # non-leaders need the keys to exist; values unused upstream of the loss
+        L = s["all_tokens"].numel() - 1
+        s["old_logprobs"] = torch.zeros(L)
+        s["ref_logprobs"] = torch.zeros(L)
+# every rank of a model-parallel group must train on identical values: broadcast from the leader
+import torch.distributed as dist  # noqa: E402
+if W > 1:
+    objs = [None] * W
+    dist.all_gather_object(objs, [(s["uid"], s["old_logprobs"], s["ref_logprobs"]) for s in mine]
+                           if mod.is_data_leader else [])
+    table = {u: (a, b) for part in objs for (u, a, b) in part}
+    for s in mine:
+        s["old_logprobs"], s["ref_logprobs"] = table[s["uid"]]
+mod.train_step(mine)
+mod.save_checkpoint(1)
+prefix, metrics = mod.get_and_clear_metrics()
+if W > 1:
+    dist.barrier()
+if rank == 0:
+    from chatlearn_b200.offline_ckpt_converter import convert_megatron
+    sd = convert_megatron(mod.checkpoint_dir(1), 1, torch.float32)
+    torch.save({"sd": sd, "metrics": metrics}, os.path.join(out, f"{tag}.pt"))
+    print("RESULT " + json.dumps({k: float(v) for k, v in metrics.items()}))

@@ -1,0 +1,57 @@
+"""The TP / PP / CP / EP trainer must reproduce the single-rank result: same
+log-probs, same loss statistics, same weights after one optimizer step."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from chatlearn_b200.utils.utils import get_free_port
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DRIVER = os.path.join(ROOT, "tests", "megatron_driver.py")
+
+
+def _run(out_dir, tag, world, **env):
+    port = get_free_port()
+    procs = []
+    for r in range(world):
+        e = dict(os.environ, OUT_DIR=str(out_dir), TAG=tag, RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE=str(world),
+                 MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CHATLEARN_FORCE_CPU="1", OMP_NUM_THREADS="2")
+        e.update({k: str(v) for k, v in env.items()})
+        procs.append(subprocess.Popen([sys.executable, DRIVER], env=e, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(o[-2500:] for o in outs)
+    return torch.load(os.path.join(out_dir, f"{tag}.pt"), weights_only=False)
+
+
+def _compare(a, b, tol=2e-4):
+    assert set(a["sd"]) == set(b["sd"])
+    for k in a["sd"]:
+        d = (a["sd"][k] - b["sd"][k]).abs().max().item()
+        assert d < tol, (k, d)
+    for k in ("pg_loss", "kl_loss", "entropy_loss", "grad_norm"):
+        assert abs(a["metrics"][k] - b["metrics"][k]) < 5e-4 * max(1.0, abs(a["metrics"][k])), (k, a["metrics"], b["metrics"])
+
+
+@pytest.mark.parametrize("name,world,env", [
+    ("tp2", 2, dict(TP=2)),
+    ("pp2", 2, dict(PP=2)),
+    ("cp2", 2, dict(CP=2)),
+    ("dp2", 2, dict()),
+    ("tp2_gspo", 2, dict(TP=2, GSPO=1)),
+])
+def test_dense_parallel_matches_single(tmp_path, name, world, env):
+    base_env = {k: v for k, v in env.items() if k == "GSPO"}
+    base = _run(tmp_path, "base", 1, **base_env)
+    par = _run(tmp_path, name, world, **env)
+    _compare(base, par)
+
+
+@pytest.mark.parametrize("name,world,env", [("ep2", 2, dict(EP=2)), ("tp2ep2", 4, dict(TP=2, EP=2))])
+def test_moe_parallel_matches_single(tmp_path, name, world, env):
+    base = _run(tmp_path, "base", 1, PRESET="tiny_moe", NOAUX=1)
+    par = _run(tmp_path, name, world, PRESET="tiny_moe", NOAUX=1, **env)
+    _compare(base, par, tol=5e-4)
