@@ -266,8 +266,11 @@ class RolloutEngine:
             return False
         if self.lockstep is not None and self.lockstep.size > 1:
             return False
-        k0 = plan.seqs[0].sampling.key()
-        return all(s.sampling.key() == k0 and not s.sampling.has_penalty for s in plan.seqs)
+        sp0 = plan.seqs[0].sampling
+        if sp0.has_penalty:
+            return False
+        k0 = sp0.key()
+        return all(s.sampling is sp0 or s.sampling.key() == k0 for s in plan.seqs)
 
     @torch.no_grad()
     def step(self, sched: Scheduler, plan: StepPlan, eos_id: Optional[int]):

@@ -97,19 +97,21 @@ class Scheduler:
         seq.blocks.extend(self.alloc.alloc(need))
         return True
 
-    def _preempt_one(self, keep: Sequence) -> bool:
-        for victim in reversed(self.running):
+    def _preempt_one(self, keep: Sequence) -> Optional[Sequence]:
+        """Evict the youngest running sequence other than ``keep``; returns it."""
+        for i in range(len(self.running) - 1, -1, -1):
+            victim = self.running[i]
             if victim is keep:
                 continue
-            self.running.remove(victim)
+            del self.running[i]
             self.alloc.free(victim.blocks)
             victim.blocks = []
             victim.num_computed = 0
             victim.preemptions += 1
             self.stats["preemptions"] += 1
             self.waiting.appendleft(victim)
-            return True
-        return False
+            return victim
+        return None
 
     def schedule(self) -> Optional[StepPlan]:
         """Next step: prefill work first (admission), else one decode step."""
@@ -151,15 +153,21 @@ class Scheduler:
             if self.waiting:
                 raise RuntimeError("KV cache too small for a single waiting request")
             return None
+        # common case first: every running sequence gets its block without preemption
+        # (linear in the batch; the preemption path below re-validates membership)
+        gone = set()
         ready = []
         for s in list(self.running):
-            if s not in self.running:
+            if id(s) in gone:
                 continue
             while not self._ensure_blocks(s, s.length):
-                if not self._preempt_one(keep=s):
+                victim = self._preempt_one(keep=s)
+                if victim is None:
                     raise RuntimeError("KV cache too small for one sequence")
+                gone.add(id(victim))
             ready.append(s)
-        ready = [s for s in ready if s in self.running]
+        if gone:
+            ready = [s for s in ready if id(s) not in gone]
         self.stats["decode_tokens"] += len(ready)
         return StepPlan(ready, [1] * len(ready), False, [True] * len(ready))
 
