@@ -333,3 +333,114 @@ int64_t gemm_last_status() {
 }
 
 void gemm_set_splitk(bool on) { g_allow_splitk = on; }
+
+// ----------------------------------------------------------------------------
+// Allocation-free entry point (see gemm_noalloc.h): same kernel, split-K planes in a
+// fixed file-scope device array instead of a workspace from the allocator.
+// ----------------------------------------------------------------------------
+#include <cstdio>
+
+#include "gemm_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[CLB200_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+
+struct NoAllocDevice {
+  float* scratch = nullptr;   // device address of g_noalloc_scratch on this device
+  int num_sms = 0;
+  bool ready = false;
+};
+NoAllocDevice g_noalloc_dev[64];
+thread_local char g_noalloc_err[320] = "";
+
+int noalloc_fail(int code, const char* fmt, long long a = 0, long long b = 0, long long c = 0) {
+  std::snprintf(g_noalloc_err, sizeof(g_noalloc_err), fmt, a, b, c);
+  return code;
+}
+
+// In host code the array's name is only a handle: the address a kernel can use comes
+// from cudaGetSymbolAddress, once per device, with that device current.
+int noalloc_setup(int dev) {
+  NoAllocDevice& d = g_noalloc_dev[dev];
+  if (d.ready) return 0;
+  void* p = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+  if (e != cudaSuccess || p == nullptr)
+    return noalloc_fail(10, "cudaGetSymbolAddress(scratch) failed on device %lld: error %lld", dev, (long long)e);
+  e = cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return noalloc_fail(11, "cudaDeviceGetAttribute failed: error %lld", (long long)e);
+  const int smem = (int)(sizeof(SmemLayout) + 1024);
+  e = cudaFuncSetAttribute(gemm_bf16_nt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(gemm_bf16_nt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return noalloc_fail(12, "cudaFuncSetAttribute failed: error %lld", (long long)e);
+  d.scratch = static_cast<float*>(p);
+  d.ready = true;
+  return 0;
+}
+
+bool noalloc_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    cudaDriverEntryPointQueryResult q;
+    void* p = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !p)
+      return false;
+    fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }
+  cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)(ld * 2)};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" const char* clb200_gemm_noalloc_last_error(void) { return g_noalloc_err; }
+
+extern "C" int clb200_gemm_bf16_nt_noalloc(const void* a, const void* b, void* c, int M, int N, int K, int lda,
+                                           int ldb, int out_fp32, void* stream) {
+  g_noalloc_err[0] = '\0';
+  if (!a || !b || !c) return noalloc_fail(1, "null pointer argument");
+  if (M <= 0 || N <= 0 || K <= 0) return noalloc_fail(2, "M, N, K must be positive (got %lld, %lld, %lld)", M, N, K);
+  if (K % 8 || N % 8 || lda % 8 || ldb % 8 || lda < K || ldb < K)
+    return noalloc_fail(3, "K, N and the row strides must be multiples of 8 and lda, ldb >= K");
+  if (((uintptr_t)a % 16) || ((uintptr_t)b % 16) || ((uintptr_t)c % 16))
+    return noalloc_fail(4, "a, b and c must be 16-byte aligned");
+  if (2ll * M * N > CLB200_NOALLOC_SCRATCH_FLOATS)
+    return noalloc_fail(5, "problem too large for the built-in scratch: 2*M*N = %lld floats > %lld",
+                        2ll * M * N, (long long)CLB200_NOALLOC_SCRATCH_FLOATS);
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return noalloc_fail(6, "cudaGetDevice failed");
+  if (int rc = noalloc_setup(dev)) return rc;
+  const NoAllocDevice& d = g_noalloc_dev[dev];
+  CUtensorMap tmA, tmB;
+  if (!noalloc_tmap(&tmA, a, M, K, lda, BM) || !noalloc_tmap(&tmB, b, N, K, ldb, BN))
+    return noalloc_fail(7, "cuTensorMapEncodeTiled rejected the operands");
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int k_iters = (K + BK - 1) / BK;
+  // always slice K (that is what the scratch is for); one slice only when K is a single step
+  int splits = std::min({std::max((d.num_sms + tiles - 1) / tiles, 2), std::max(k_iters / 2, 1), 16});
+  while (splits > 1 && (long long)splits * M * N > CLB200_NOALLOC_SCRATCH_FLOATS) --splits;
+  while (splits > 1 && ((k_iters + splits - 1) / splits) * (splits - 1) >= k_iters) --splits;
+  const int grid = std::min(tiles * splits, d.num_sms);
+  const size_t smem = sizeof(SmemLayout) + 1024;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t mn = (int64_t)M * N;
+  const int fgrid = (int)std::min<int64_t>((mn / 4 + 255) / 256, 148 * 8);
+  if (out_fp32) {
+    gemm_bf16_nt_kernel<float><<<grid, kThreads, smem, st>>>(tmA, tmB, static_cast<float*>(c), d.scratch, M, N, K, N, splits);
+    if (splits > 1) splitk_finalize_kernel<float><<<fgrid, 256, 0, st>>>(d.scratch, static_cast<float*>(c), mn, splits);
+  } else {
+    gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, static_cast<bf16*>(c), d.scratch, M, N, K, N, splits);
+    if (splits > 1) splitk_finalize_kernel<bf16><<<fgrid, 256, 0, st>>>(d.scratch, static_cast<bf16*>(c), mn, splits);
+  }
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return noalloc_fail(8, "kernel launch failed: error %lld", (long long)e);
+  return 0;
+}
