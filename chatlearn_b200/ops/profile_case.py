@@ -1,0 +1,71 @@
+"""Small, self-ending workloads for profiler captures of single kernels.
+
+    python -m chatlearn_b200.ops.profile_case --kernel gemm|decode|rmsnorm|swiglu|logits|adamw|sample|weight_sync
+
+Each case allocates a few hundred MB (operands larger than the 126 MB L2 so DRAM
+figures mean something), runs 3 warm-up launches and 3 measured launches of ONE
+kernel and exits.  Meant to be run as  `<cmd> && ncu --set full --clock-control none
+-k regex:<kernel> -s 3 -c 1 -o <out> <cmd>`.
+"""
+import argparse
+import math
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", required=True)
+    a = ap.parse_args()
+    from chatlearn_b200.ops import native
+    C = native.C
+    dev = "cuda"
+    torch.manual_seed(0)
+    if a.kernel == "gemm":
+        A = torch.randn(8192, 4096, device=dev).bfloat16()
+        B = torch.randn(4096, 4096, device=dev).bfloat16()
+        fn = lambda: C.gemm_bf16_nt(A, B, False)  # noqa: E731
+    elif a.kernel == "gemm_decode":
+        A = torch.randn(128, 4096, device=dev).bfloat16()
+        B = torch.randn(24576, 4096, device=dev).bfloat16()
+        fn = lambda: C.gemm_bf16_nt(A, B, False)  # noqa: E731
+    elif a.kernel == "decode":
+        Bsz, nq, nkv, d, bs, L = 64, 32, 8, 128, 64, 2048
+        nblk = math.ceil(L / bs)
+        kc = torch.randn(Bsz * nblk + 1, bs, nkv, d, device=dev).bfloat16()
+        vc = torch.randn(Bsz * nblk + 1, bs, nkv, d, device=dev).bfloat16()
+        bt = torch.randperm(Bsz * nblk, device=dev).view(Bsz, nblk).int()
+        sl = torch.full((Bsz,), L, dtype=torch.int32, device=dev)
+        q = torch.randn(Bsz, nq, d, device=dev).bfloat16()
+        fn = lambda: native.paged_attention(q, kc, vc, bt, sl, None, None)  # noqa: E731
+    elif a.kernel == "rmsnorm":
+        x = torch.randn(32768, 4096, device=dev).bfloat16()
+        w = torch.ones(4096, device=dev).bfloat16()
+        fn = lambda: C.rmsnorm_fwd(x, w, 1e-6)  # noqa: E731
+    elif a.kernel == "swiglu":
+        gu = torch.randn(8192, 2 * 12288, device=dev).bfloat16()
+        fn = lambda: C.swiglu_fwd(gu)  # noqa: E731
+    elif a.kernel == "logits":
+        z = torch.randn(1024, 151936, device=dev)
+        lab = torch.randint(0, 151936, (1024,), device=dev)
+        fn = lambda: C.logits_stats(z, lab, 1.0)  # noqa: E731
+    elif a.kernel == "adamw":
+        n = 1 << 26
+        m0, g = torch.randn(n, device=dev), torch.randn(n, device=dev)
+        m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        out = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        fn = lambda: C.adamw_step(m0, g, m, v, out, 1, 1e-4, 0.9, 0.95, 1e-8, 0.01, None, 1.0)  # noqa: E731
+    elif a.kernel == "sample":
+        z = torch.randn(128, 151936, device=dev)
+        u = torch.rand(128, device=dev)
+        fn = lambda: C.sample(z, u, 1.0, -1, 1.0, 0.0)  # noqa: E731
+    else:
+        raise SystemExit(f"unknown kernel {a.kernel}")
+    for _ in range(6):
+        fn()
+    torch.cuda.synchronize()
+    print("done", a.kernel)
+
+
+if __name__ == "__main__":
+    main()
