@@ -262,8 +262,8 @@ def main():
         }
         print(json.dumps(line), flush=True)
     if dist.is_initialized():
-        dist.barrier()
-        dist.destroy_process_group()
+        from chatlearn_b200.launcher.initialize import shutdown
+        shutdown()
     return 0
 
 

@@ -43,7 +43,20 @@ void weight_sync_run(const at::Tensor& desc_table, int64_t num_descs, int64_t to
                      int64_t dst_dtype);
 int64_t weight_sync_desc_size();
 int64_t weight_sync_tile_elems();
+void symm_allreduce(const std::vector<int64_t>& buf_ptrs, const std::vector<int64_t>& flag_ptrs, at::Tensor expect,
+                    at::Tensor out, int64_t n, int64_t rank, int64_t num_slots);
+at::Tensor symm_rs_pull_sumsq(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& flag_ptrs,
+                              at::Tensor expect, at::Tensor shard, int64_t lo, int64_t rank, int64_t num_slots);
+void symm_adamw_push(at::Tensor master, const at::Tensor& grad, at::Tensor m, at::Tensor v,
+                     const std::vector<int64_t>& param_ptrs, const std::vector<int64_t>& flag_ptrs, at::Tensor expect,
+                     int64_t lo, bool params_bf16, int64_t step, double lr, double b1, double b2, double eps, double wd,
+                     const c10::optional<at::Tensor>& scale, int64_t rank, int64_t num_slots);
+int64_t symm_last_status();
+at::Tensor symm_ar_residual_rmsnorm(const std::vector<int64_t>& part_ptrs, const std::vector<int64_t>& flag_ptrs,
+                                    at::Tensor expect, at::Tensor resid, const c10::optional<at::Tensor>& w, double eps,
+                                    int64_t rank, int64_t num_slots);
 at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32);
+void gemm_bf16_nt_out(const at::Tensor& a, const at::Tensor& b, at::Tensor out);
 int64_t gemm_last_status();
 void gemm_set_splitk(bool on);
 
@@ -69,7 +82,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("weight_sync_run", &weight_sync_run);
   m.def("weight_sync_desc_size", &weight_sync_desc_size);
   m.def("weight_sync_tile_elems", &weight_sync_tile_elems);
+  m.def("symm_allreduce", &symm_allreduce);
+  m.def("symm_rs_pull_sumsq", &symm_rs_pull_sumsq);
+  m.def("symm_adamw_push", &symm_adamw_push);
+  m.def("symm_last_status", &symm_last_status);
+  m.def("symm_ar_residual_rmsnorm", &symm_ar_residual_rmsnorm);
   m.def("gemm_bf16_nt", &gemm_bf16_nt);
+  m.def("gemm_bf16_nt_out", &gemm_bf16_nt_out);
   m.def("gemm_last_status", &gemm_last_status);
   m.def("gemm_set_splitk", &gemm_set_splitk);
 }

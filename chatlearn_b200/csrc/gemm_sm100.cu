@@ -280,7 +280,23 @@ CUtensorMap make_tmap_bf16(const void* ptr, int64_t rows, int64_t cols, int64_t 
 }  // namespace
 
 // a [M, K] bf16 (row stride lda), b [N, K] bf16 -> C [M, N] (bf16, or fp32 when out_fp32)
+static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bool out_fp32, const at::Tensor* out);
+
 at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32) {
+  return gemm_bf16_nt_impl(a, b, out_fp32, nullptr);
+}
+
+// Same GEMM, result written into a caller-provided contiguous [M, N] tensor (for
+// instance a symmetric-memory staging buffer that a peer-reading kernel consumes).
+void gemm_bf16_nt_out(const at::Tensor& a, const at::Tensor& b, at::Tensor out) {
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.dim() == 2 && out.size(0) == a.size(0) &&
+              out.size(1) == b.size(0), "gemm_bf16_nt_out: out must be contiguous [M, N]");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat, "gemm_bf16_nt_out: bf16 or fp32 out");
+  TORCH_CHECK((uintptr_t)out.data_ptr() % 16 == 0, "gemm_bf16_nt_out: 16-byte aligned out");
+  gemm_bf16_nt_impl(a, b, out.scalar_type() == at::kFloat, &out);
+}
+
+static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bool out_fp32, const at::Tensor* out) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16,
               "gemm_bf16_nt: bf16 CUDA tensors");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "gemm_bf16_nt: A [M,K], B [N,K]");
@@ -288,7 +304,7 @@ at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32)
   const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
   TORCH_CHECK(K % 8 == 0 && a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "gemm_bf16_nt: K and row strides must be multiples of 8");
   TORCH_CHECK(((uintptr_t)a.data_ptr() % 16 == 0) && ((uintptr_t)b.data_ptr() % 16 == 0), "gemm_bf16_nt: 16-byte aligned operands");
-  auto c = at::empty({M, N}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  auto c = out ? *out : at::empty({M, N}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
   if (M == 0 || N == 0) return c;
   if (K == 0) return c.zero_();
   TORCH_CHECK(N % 8 == 0, "gemm_bf16_nt: N must be a multiple of 8");

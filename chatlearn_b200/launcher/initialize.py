@@ -59,3 +59,29 @@ def init(args=None, config_file: Optional[str] = None, overrides=None):
     ra = args.runtime_args
     init_distributed(timeout_s=float(getattr(ra, "distributed_timeout_s", 1800.0)))
     return args
+
+
+def shutdown(grace_s: float = 20.0):
+    """End a distributed job: synchronise, release CUDA graphs and cached blocks, then
+    destroy the process group.  NCCL's teardown can block when captured graphs that
+    contain its kernels are still alive, so a watchdog thread ends the process once
+    ``grace_s`` has passed; by then every result has been flushed by the caller."""
+    import gc
+    import os
+    import sys
+    import threading
+    if not dist.is_initialized():
+        return
+    sys.stdout.flush()
+    sys.stderr.flush()
+    t = threading.Timer(grace_s, lambda: os._exit(0))
+    t.daemon = True
+    t.start()
+    try:
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        gc.collect()
+        dist.barrier()
+        dist.destroy_process_group()
+    finally:
+        t.cancel()

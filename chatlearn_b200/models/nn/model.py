@@ -143,6 +143,8 @@ class FwdCtx:
     cp_plan: Optional[Dict[str, Any]] = None       # ContextParallel.plan() of this packed row
     aux_losses: List[torch.Tensor] = field(default_factory=list)
     moe_stats: List[torch.Tensor] = field(default_factory=list)
+    tp_symm: Any = None                    # parallel.symm_collectives.SymmGroup of the TP group (inference)
+    pending: Any = None                    # un-reduced TP partial not yet folded into the residual stream
 
 
 def _tp_reduce(x, ctx):
@@ -151,7 +153,10 @@ def _tp_reduce(x, ctx):
     return x
 
 
-def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx, layer: int):
+def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx, layer: int,
+                    partial: bool = False):
+    """``partial=True`` (tensor-parallel inference with in-kernel collectives) returns this
+    rank's un-reduced output projection, written straight into symmetric staging."""
     T = x.shape[0]
     d = arch.head_dim
     x = _tp_copy(x, ctx)
@@ -203,6 +208,8 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
         o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, scale)
     if ctx.sp is not None and ctx.sp.size > 1 and not arch.use_mla:
         o = ctx.sp.heads_to_seq(o)
+    if partial:
+        return ctx.tp_symm.gemm_partial(o.reshape(o.shape[0], -1), p["o_proj"])
     out = ops.linear(o.reshape(o.shape[0], -1), p["o_proj"])
     return _tp_reduce(out, ctx)
 
@@ -213,9 +220,11 @@ def _tp_copy(x, ctx):
     return x
 
 
-def dense_mlp(p, x, ctx, prefix=""):
+def dense_mlp(p, x, ctx, prefix="", partial: bool = False):
     x = _tp_copy(x, ctx)
     h = ops.swiglu(ops.linear(x, p[prefix + "gate_up"]))
+    if partial:
+        return ctx.tp_symm.gemm_partial(h, p[prefix + "down_proj"])
     return ops.linear(h, p[prefix + "down_proj"])
 
 
@@ -253,7 +262,43 @@ def moe_block(arch: ModelArch, p, x, ctx: FwdCtx):
     return y
 
 
+def _tp_fused_ok(p, x, ctx: FwdCtx) -> bool:
+    sg = ctx.tp_symm
+    return sg is not None and "router" not in p and not torch.is_grad_enabled() \
+        and x.dtype == torch.bfloat16 and x.dim() == 2 and sg.fits(x.shape[0], x.shape[1])
+
+
+def _decoder_layer_tp_fused(arch: ModelArch, p, x, ctx: FwdCtx, layer: int):
+    """Dense layer under tensor parallelism without NCCL: the two row-parallel GEMMs
+    write partial sums into symmetric staging, and one kernel per GEMM reads every
+    rank's partial over NVLink, adds the residual and applies the next RMSNorm.  The
+    MLP's partial stays pending in ``ctx`` and is folded into the next layer's (or the
+    final) norm, so the reduced tensors never reach memory."""
+    sg, eps = ctx.tp_symm, arch.rms_norm_eps
+    if ctx.pending is not None:
+        h = sg.ar_residual_rmsnorm(ctx.pending, x, p["input_layernorm"], eps)
+        ctx.pending = None
+    else:
+        h = ops.rmsnorm(x, p["input_layernorm"], eps)
+    a = attention_block(arch, p, h, ctx, layer, partial=True)
+    h = sg.ar_residual_rmsnorm(a, x, p["post_attention_layernorm"], eps)
+    ctx.pending = dense_mlp(p, h, ctx, partial=True)
+    return x
+
+
+def flush_pending(x, ctx: FwdCtx, norm_w=None, eps: float = 1e-6):
+    """Fold a pending tensor-parallel partial into ``x``; returns ``rmsnorm(x)`` when
+    ``norm_w`` is given, else ``x``."""
+    part, ctx.pending = ctx.pending, None
+    h = ctx.tp_symm.ar_residual_rmsnorm(part, x, norm_w, eps)
+    return x if norm_w is None else h
+
+
 def decoder_layer(arch: ModelArch, p, x, ctx: FwdCtx, layer: int):
+    if _tp_fused_ok(p, x, ctx):
+        return _decoder_layer_tp_fused(arch, p, x, ctx, layer)
+    if ctx.pending is not None:
+        x = flush_pending(x, ctx)
     h = ops.rmsnorm(x, p["input_layernorm"], arch.rms_norm_eps)
     x = x + attention_block(arch, p, h, ctx, layer)
     h = ops.rmsnorm(x, p["post_attention_layernorm"], arch.rms_norm_eps)
@@ -338,7 +383,12 @@ class CausalLM:
             else:
                 x = decoder_layer(self.arch, p, x, ctx, l)
         if "head" in self.block_by_name:
-            x = ops.rmsnorm(x, self.block_by_name["head"].params["norm"], self.arch.rms_norm_eps)
+            norm_w = self.block_by_name["head"].params["norm"]
+            if ctx.pending is not None:
+                return flush_pending(x, ctx, norm_w, self.arch.rms_norm_eps)
+            x = ops.rmsnorm(x, norm_w, self.arch.rms_norm_eps)
+        elif ctx.pending is not None:
+            x = flush_pending(x, ctx)
         return x
 
     def lm_head_weight(self):

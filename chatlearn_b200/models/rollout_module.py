@@ -165,7 +165,9 @@ class RolloutModule(TorchModule):
                 "response_p25": lens.quantile(0.25).item(), "response_p50": lens.quantile(0.5).item(),
                 "response_p75": lens.quantile(0.75).item(),
                 "gen_tokens_per_s": lens.sum().item() / max(dt, 1e-9),
-                "preemptions": float(self.engine.stats.get("preemptions", 0))})
+                "preemptions": float(self.engine.stats.get("preemptions", 0)),
+                **{k: float(self.engine.stats.get(k, 0)) for k in
+                   ("prefill_s", "decode_s", "sched_s", "prefill_steps", "decode_steps")}})
         self.save_stage_outputs(is_eval, out, iteration)
         return out
 

@@ -182,6 +182,17 @@ def linear(x, w, bias=None):
     return torch.nn.functional.linear(x, w, bias)
 
 
+def linear_out(x2, w, out):
+    """``out[:] = x2 @ w.T`` into a caller-owned buffer (no autograd)."""
+    if _GEMM_IMPL == "tcgen05" and x2.shape[0] > 0 and _gemm_ok(x2, w):
+        _count("gemm_bf16_nt")
+        C.gemm_bf16_nt_out(x2, w, out)
+    else:
+        library_counts["linear"] += 1
+        torch.mm(x2, w.t(), out=out)
+    return out
+
+
 def gemm_nt(a, b, out_fp32=False):
     """Raw C = A B^T on the tcgen05 kernel (no autograd)."""
     _count("gemm_bf16_nt")

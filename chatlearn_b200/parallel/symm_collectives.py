@@ -1,0 +1,135 @@
+"""In-kernel collectives over symmetric memory for one process group.
+
+``SymmGroup`` owns the flag words and staging buffers of a group and exposes
+
+* ``all_reduce(x)``      – one-shot all-reduce (every rank reads all peers' buffers and
+  sums in a fixed order): the tensor-parallel all-reduce of the rollout decode step;
+* ``reduce_scatter_pull`` / ``adamw_push`` – the two kernels of the sharded optimizer
+  step: each rank *pulls* its gradient shard from every peer and sums it (plus the
+  squared norm), then, once the clip factor is known, updates its fp32 shard and
+  *pushes* the new bf16 weights into every peer's parameter buffer.
+
+The reference uses NCCL collectives issued by torch FSDP2 / Megatron / vLLM for all
+of these (chatlearn/models/fsdp_module.py:356-394); the NCCL path of
+``parallel.groups`` stays as the baseline and the CPU/gloo implementation.
+Synchronisation between ranks happens inside the kernels (flag words, bounded
+waits); the host only launches.
+"""
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import symm_mem
+from .groups import Group
+
+NUM_SLOTS = 1024          # barrier instances per sender (>= 2 x the largest grid)
+PART_BYTES = 4 << 20      # each of the two buffers for un-reduced tensor-parallel partials
+
+
+class SymmGroup:
+    def __init__(self, group: Group, staging_bytes: int = 8 << 20):
+        from chatlearn_b200.ops import native
+        self.C = native.C
+        self.native = native
+        self.group = group
+        self.rank, self.world = group.rank, group.size
+        assert 1 < self.world <= 8
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.pg = group.pg
+        # flag words: [sender rank][slot] uint32, zero-initialised, in symmetric memory
+        self.flags = symm_mem.empty(8 * NUM_SLOTS, torch.int32, self.device, group=self.pg)
+        self.flags.zero_()
+        self.expect = torch.zeros(NUM_SLOTS * 8, dtype=torch.int32, device=self.device)
+        self.flag_ptrs = self._ptrs(self.flags)
+        self.staging = symm_mem.empty(staging_bytes // 2, torch.bfloat16, self.device, group=self.pg)
+        self.staging_ptrs = self._ptrs(self.staging)
+        # two buffers for row-parallel GEMM partials; consecutive calls alternate between them
+        self.parts = [symm_mem.empty(PART_BYTES // 2, torch.bfloat16, self.device, group=self.pg) for _ in range(2)]
+        self.part_ptrs = [self._ptrs(t) for t in self.parts]
+        self._flip = 0
+        torch.cuda.synchronize()
+        group.barrier()               # flags are zero everywhere before the first kernel signals
+
+    def _ptrs(self, t: torch.Tensor) -> List[int]:
+        return [symm_mem.peer_pointer(t, self.group.ranks[r]) for r in range(self.world)]
+
+    # ------------------------------------------------------------------ all-reduce
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum ``x`` over the group.  ``x`` is copied into the staging buffer (unless it
+        already lives there) and the result is written in place into ``x``."""
+        n = x.numel()
+        nbytes = n * x.element_size()
+        if nbytes > self.staging.numel() * 2 or x.dtype not in (torch.bfloat16, torch.float32) or not x.is_contiguous():
+            dist.all_reduce(x, group=self.pg)
+            return x
+        stage = self.staging.view(torch.uint8)[:nbytes].view(x.dtype)
+        stage.copy_(x.view(-1))
+        self.C.symm_allreduce(self.staging_ptrs, self.flag_ptrs, self.expect, x, n, self.rank, NUM_SLOTS)
+        self.native.launch_counts["symm_allreduce"] += 1
+        return x
+
+    # ------------------------------------------------------------------ fused TP epilogue
+    def fits(self, T: int, H: int) -> bool:
+        return T * H * 2 <= PART_BYTES and H % 8 == 0 and H <= 8192
+
+    def begin_forward(self):
+        """Every forward pass issues an even number of partial/reduce pairs (two per layer),
+        so the buffer alternation is the same in eager steps and in replayed CUDA graphs."""
+        assert self._flip == 0, "odd number of tensor-parallel partial reductions in the last forward pass"
+
+    def gemm_partial(self, x2d: torch.Tensor, w: torch.Tensor):
+        """This rank's ``x2d @ w.T`` written into the next staging buffer; returns a handle
+        for ``ar_residual_rmsnorm``."""
+        idx = self._flip
+        self._flip ^= 1
+        T, N = x2d.shape[0], w.shape[0]
+        out = self.parts[idx][:T * N].view(T, N)
+        if T > 0:
+            self.native.linear_out(x2d, w, out)
+        return idx, out
+
+    def ar_residual_rmsnorm(self, part, resid: torch.Tensor, w: Optional[torch.Tensor], eps: float):
+        """``resid += sum over ranks of the partial``; returns ``rmsnorm(resid) * w`` (``None``
+        when ``w`` is ``None``).  One kernel, peers read over NVLink."""
+        idx, out = part
+        assert out.shape == resid.shape
+        self.native.launch_counts["symm_ar_residual_rmsnorm"] += 1
+        return self.C.symm_ar_residual_rmsnorm(self.part_ptrs[idx], self.flag_ptrs, self.expect, resid, w,
+                                               float(eps), self.rank, NUM_SLOTS)
+
+    # ------------------------------------------------------------------ sharded optimizer step
+    def symmetric_like(self, numel: int, dtype) -> torch.Tensor:
+        return symm_mem.empty(numel, dtype, self.device, group=self.pg)
+
+    def reduce_scatter_pull(self, grad_full: torch.Tensor, shard_out: torch.Tensor, lo: int) -> torch.Tensor:
+        """``shard_out = sum over ranks of grad[lo:lo+len]``; returns partial sums of squares."""
+        ptrs = self._ptrs(grad_full)
+        part = self.C.symm_rs_pull_sumsq(ptrs, self.flag_ptrs, self.expect, shard_out, lo, self.rank, NUM_SLOTS)
+        self.native.launch_counts["symm_rs_pull"] += 1
+        return part
+
+    def adamw_push(self, master, grad_shard, exp_avg, exp_avg_sq, param_full: torch.Tensor, lo: int, step: int,
+                   lr, beta1, beta2, eps, wd, scale: Optional[torch.Tensor]):
+        ptrs = self._ptrs(param_full)
+        self.C.symm_adamw_push(master, grad_shard, exp_avg, exp_avg_sq, ptrs, self.flag_ptrs, self.expect, lo,
+                               param_full.dtype == torch.bfloat16, int(step), lr, beta1, beta2, eps, wd,
+                               scale.reshape(1).float() if scale is not None else None, self.rank, NUM_SLOTS)
+        self.native.launch_counts["symm_adamw_push"] += 1
+
+    def status(self) -> int:
+        return int(self.C.symm_last_status())
+
+
+_GROUPS: Dict[int, SymmGroup] = {}
+
+
+def get(group: Group) -> Optional[SymmGroup]:
+    """The ``SymmGroup`` of a process group (created on first use, collectively), or
+    ``None`` when symmetric memory is unavailable (CPU ranks, single rank)."""
+    if group is None or group.size <= 1 or group.size > 8 or not symm_mem.available():
+        return None
+    key = id(group.pg)
+    if key not in _GROUPS:
+        _GROUPS[key] = SymmGroup(group)
+    return _GROUPS[key]

@@ -19,7 +19,8 @@ def available() -> bool:
     if not (torch.cuda.is_available() and dist.is_initialized()):
         return False
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        import importlib
+        importlib.import_module("torch.distributed._symmetric_memory")
         return True
     except Exception:
         return False
@@ -30,8 +31,12 @@ def empty(numel: int, dtype, device, group=None) -> torch.Tensor:
     (collective over ``group``)."""
     import torch.distributed._symmetric_memory as sm
     group = group or dist.group.WORLD
+    try:                                     # older torch versions need the group registered first
+        sm.enable_symm_mem_for_group(group.group_name)
+    except Exception:
+        pass
     t = sm.empty(numel, dtype=dtype, device=device)
-    h = sm.rendezvous(t, group=group)
+    h = sm.rendezvous(t, group=group.group_name if hasattr(group, "group_name") else group)
     _REG[t.data_ptr()] = {"handle": h, "base": t.data_ptr(), "numel": numel, "esz": t.element_size(),
                           "group": group}
     return t

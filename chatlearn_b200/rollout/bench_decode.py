@@ -100,9 +100,9 @@ def main():
         if tp_rank == 0:
             print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=18, max_name_column_width=70))
     if args.tp > 1:
-        import torch.distributed as dist
-        dist.barrier()
-        dist.destroy_process_group()
+        from chatlearn_b200.launcher.initialize import shutdown
+        eng._graphs.clear()
+        shutdown()
 
 
 if __name__ == "__main__":

@@ -9,6 +9,8 @@ managed by tag like the reference's sleep/wake-up
 re-created independently, so the trainer can use the memory between rollouts.
 """
 import math
+import os
+import time
 from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Sequence as Seq
 
@@ -54,6 +56,15 @@ class RolloutEngine:
         self.model, self.arch = model, model.arch
         self.device = model.device
         self.tp, self.ep = tp_group, ep_group
+        # tensor-parallel reductions by this package's own peer-memory kernels (fused with
+        # the residual add and the next RMSNorm) instead of NCCL; collective construction
+        self.tp_symm = None
+        if tp_group is not None and tp_group.size > 1 and self.device.type == "cuda" \
+                and ops.get_mode() == "native" and os.environ.get("CLB200_SYMM_TP", "1") != "0":
+            from chatlearn_b200.parallel import symm_collectives
+            self.tp_symm = symm_collectives.get(tp_group)
+            if self.tp_symm is not None:
+                tp_group.fast["all_reduce"] = self.tp_symm.all_reduce
         self.block_size = block_size
         self.max_num_seqs = max_num_seqs
         self.max_tokens = max_num_batched_tokens
@@ -156,8 +167,13 @@ class RolloutEngine:
         kv = KVCtx(self.k_cache, self.v_cache, t(slots, torch.long, "slots"), xfer.to_device(bt, dev, "bt"),
                    t(seq_lens, torch.int32, "seq_lens"), t(plan.q_lens, torch.int32, "q_lens"), plan.is_prefill)
         ctx = FwdCtx(positions=t(pos, torch.long, "pos"), cu_seqlens=t(cu, torch.int32, "cu"),
-                     max_seqlen=max(plan.q_lens), kv=kv, tp=self.tp, ep=self.ep)
+                     max_seqlen=max(plan.q_lens), kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm())
         return t(toks, torch.long, "toks"), ctx, t(last_rows, torch.long, "last")
+
+    def _symm(self):
+        if self.tp_symm is not None:
+            self.tp_symm.begin_forward()
+        return self.tp_symm
 
     @torch.no_grad()
     def _logits(self, hidden_last):
@@ -195,7 +211,7 @@ class RolloutEngine:
     def _decode_body(self, B: int, sp):
         gs = self._gs
         kv = KVCtx(self.k_cache, self.v_cache, gs["slots"][:B], gs["bt"][:B], gs["seq_lens"][:B], None, False)
-        ctx = FwdCtx(positions=gs["pos"][:B], cu_seqlens=None, max_seqlen=1, kv=kv, tp=self.tp, ep=self.ep)
+        ctx = FwdCtx(positions=gs["pos"][:B], cu_seqlens=None, max_seqlen=1, kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm())
         hidden = self.model.hidden_states(gs["tokens"][:B], ctx)
         logits = self._logits(hidden)
         ids, lp = ops.sample(logits, gs["u"][:B], sp.temperature, sp.top_k, sp.top_p, sp.min_p)
@@ -342,7 +358,7 @@ class RolloutEngine:
         kv = KVCtx(self.k_cache, self.v_cache, z(torch.long), torch.zeros(0, 1, dtype=torch.int32, device=dev),
                    z(torch.int32), z(torch.int32), True)
         ctx = FwdCtx(positions=z(torch.long), cu_seqlens=torch.zeros(1, dtype=torch.int32, device=dev),
-                     max_seqlen=0, kv=kv, tp=self.tp, ep=self.ep)
+                     max_seqlen=0, kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm())
         self.model.hidden_states(z(torch.long), ctx)
 
     # ------------------------------------------------------------------ public
@@ -367,6 +383,7 @@ class RolloutEngine:
                 s.finished, s.finish_reason = True, "length"
             else:
                 sched.add(s)
+        tm = {"sched_s": 0.0, "prefill_s": 0.0, "decode_s": 0.0, "prefill_steps": 0, "decode_steps": 0}
         while True:
             busy = sched.has_work()
             if self.lockstep is not None and self.lockstep.size > 1:
@@ -380,14 +397,21 @@ class RolloutEngine:
                     continue
             elif not busy:
                 break
+            t0 = time.perf_counter()
             plan = sched.schedule()
+            t1 = time.perf_counter()
+            tm["sched_s"] += t1 - t0
             if plan is None:
                 if self.lockstep is not None and self.lockstep.size > 1:
                     self._idle_step()
                     continue
                 break
-            self.step(sched, plan, eos_id)
+            self.step(sched, plan, eos_id)      # ends with the read-back of the sampled tokens
+            kind = "decode" if max(plan.q_lens) == 1 else "prefill"
+            tm[kind + "_s"] += time.perf_counter() - t1
+            tm[kind + "_steps"] += 1
         self.stats = dict(sched.stats)
+        self.stats.update(tm)
         return seqs
 
     # ------------------------------------------------------------------ sleep / wake

@@ -28,6 +28,7 @@ from chatlearn_b200.schedule.resource_manager import ResourceManager
 from chatlearn_b200.utils.constant import LOG_START
 from chatlearn_b200.utils.global_vars import get_args
 from chatlearn_b200.utils.logger import logger
+from chatlearn_b200.utils import trace
 from chatlearn_b200.utils.timer import Timers
 
 
@@ -312,24 +313,32 @@ class Engine(BaseEngine):
         logger.info(f"{LOG_START} episode {episode_id} start")
         self.timers("environment").start()
         if os.environ.get("SKIP_GENERATION") is None:
-            samples = self.env.make_experiences(episode_id)
+            with trace.span("environment"):
+                samples = self.env.make_experiences(episode_id)
         else:
             samples = []
         self.timers("environment").stop()
-        self._data_loader.set_dataset([samples], episode_id, int(ra.sample_per_episode))
-        tokens = self._data_loader.get_total_train_tokens()
-        n_samples = self._data_loader.total_samples()
+        with trace.span("replay_buffer"):
+            self._data_loader.set_dataset([samples], episode_id, int(ra.sample_per_episode))
+            tokens = self._data_loader.get_total_train_tokens()
+            n_samples = self._data_loader.total_samples()
         if self.trainer is not None and n_samples > 0:
             self.timers("train").start()
-            self.trainer.train(episode_id)
+            with trace.span("train"):
+                self.trainer.train(episode_id)
             self.timers("train").stop()
-        self.save_checkpoint(episode_id)
+        with trace.span("save_checkpoint"):
+            self.save_checkpoint(episode_id)
         self.timers("sync_parameters").start()
-        self.model_manager.sync_parameters(episode_offset=episode_id + 1)
+        with trace.span("sync_parameters"):
+            self.model_manager.sync_parameters(episode_offset=episode_id + 1)
         self.timers("sync_parameters").stop()
-        self.evaluate(episode_id)
+        with trace.span("evaluate"):
+            self.evaluate(episode_id)
         self.after_episode()
         self.timers("episode").stop()
+        if trace.enabled() and (not dist.is_initialized() or dist.get_rank() == 0):
+            trace.dump(logger.info)
         return self.logging_summary(episode_id, tokens, n_samples)
 
     def learn(self):

@@ -19,6 +19,7 @@ import torch.distributed as dist
 
 from chatlearn_b200.runtime.model_flow import ModelFlow, ModelNode
 from chatlearn_b200.utils.logger import logger
+from chatlearn_b200.utils.trace import span
 from chatlearn_b200.utils.utils import even_slice
 
 
@@ -97,19 +98,22 @@ class Executor:
         for i, chunk in enumerate(chunks):
             to_onload, to_offload = self._residency_flags(model, i, len(chunks))
             if to_onload:
-                if model.trainable and node.func_name != "train_step":
-                    # scoring with the trainer needs its weights only
-                    model.onload(to_build_grad_buffers=False, to_onload_optimizer_states=False)
-                else:
-                    model.onload()
+                with span(f"{tname}.onload"):
+                    if model.trainable and node.func_name != "train_step":
+                        # scoring with the trainer needs its weights only
+                        model.onload(to_build_grad_buffers=False, to_onload_optimizer_states=False)
+                    else:
+                        model.onload()
             model.timers(node.func_name).start()
-            res = fn(chunk, iteration, **kwargs) if node.func_name != "train_step" else fn(chunk, **kwargs)
+            with span(f"{tname}.compute"):
+                res = fn(chunk, iteration, **kwargs) if node.func_name != "train_step" else fn(chunk, **kwargs)
             model.timers(node.func_name).stop()
             if res is not None:
                 out.extend(res)
             # rollout engines stay resident during evaluation (decorator.py:134-136)
             if to_offload and not (self.is_eval and node is self.first_node):
-                model.offload()
+                with span(f"{tname}.offload"):
+                    model.offload()
         if torch.cuda.is_available() and model.total_gpu > 0:
             logger.debug(f"{tname}: {torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated, "
                          f"peak {torch.cuda.max_memory_allocated() / 2**30:.1f} GiB")
@@ -147,7 +151,8 @@ class Executor:
                     else:
                         start, mine = None, []
                 before = [dict(s) for s in mine] if ins else None
-                out = self._run_node(node, mine, iteration, kwargs) if model.is_member else []
+                with span(f"node {model.name}.{node.func_name}"):
+                    out = self._run_node(node, mine, iteration, kwargs) if model.is_member else []
                 if node.func_name == "train_step":
                     results[node] = []
                     continue

@@ -9,6 +9,8 @@ from typing import Dict, List
 from chatlearn_b200.runtime.executor import Executor
 
 
+from chatlearn_b200.utils.trace import span  # noqa: E402
+
 class Trainer(Executor):
     def __init__(self, model_flow):
         super().__init__(model_flow)
@@ -52,13 +54,16 @@ class Trainer(Executor):
                     frees = m.is_colocate and (fg.offload_weights or fg.free_grad_buffers
                                                or fg.offload_optimizer_states)
                     if first and frees:
-                        m.onload()
+                        with span(f"train.{m.name}.onload"):
+                            m.onload()
                         if m.device.type == "cuda":
                             import torch
                             m._logger.debug(f"train onload: {torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated")
                     m.timers("train_step").start()
-                    m.train_step(batch, iteration=self.iteration)
+                    with span(f"train.{m.name}.train_step"):
+                        m.train_step(batch, iteration=self.iteration)
                     m.timers("train_step").stop()
                     if last and frees:
-                        m.offload()
+                        with span(f"train.{m.name}.offload"):
+                            m.offload()
                 self.iteration += 1

@@ -21,6 +21,9 @@ from chatlearn_b200.utils.constant import TAG_KV_CACHE, TAG_WEIGHTS
 from chatlearn_b200.utils.logger import logger
 
 
+from chatlearn_b200.utils.trace import span  # noqa: E402
+
+
 class ModelManager:
     def __init__(self, models, resource_manager: ResourceManager, global_args):
         self.local_models = list(models)
@@ -95,7 +98,9 @@ class ModelManager:
                         m.set_colocate(True)
         for m in self.local_models:
             if m.total_gpu == 0:
-                placements[m.name] = list(range(W))
+                # CPU roles run data-parallel on the first ``num_cpu`` ranks (a role with
+                # global state, e.g. a rollout manager, asks for one)
+                placements[m.name] = list(range(max(1, min(W, int(m.total_cpu or W)))))
         return placements
 
     def create_dist_models(self):
@@ -123,16 +128,21 @@ class ModelManager:
             freq = int(getattr(dst.module_args, "sync_frequency", 1) or 1)
             if episode_offset % freq != 0:
                 continue
-            if src.is_member:
-                src.onload(to_onload_weights=True, to_build_grad_buffers=False,
-                           to_onload_optimizer_states=False)
-            if dst.is_member:
-                dst.onload(tags=[TAG_WEIGHTS])
-            ms[key] = grp.sync()
-            if src.is_member and src.is_colocate:
-                src.offload()
-            if dst.is_member:
-                dst.onload(tags=[TAG_KV_CACHE])
+            with span("sync.src_onload"):
+                if src.is_member:
+                    src.onload(to_onload_weights=True, to_build_grad_buffers=False,
+                               to_onload_optimizer_states=False)
+            with span("sync.dst_onload_weights"):
+                if dst.is_member:
+                    dst.onload(tags=[TAG_WEIGHTS])
+            with span("sync.copy"):
+                ms[key] = grp.sync()
+            with span("sync.src_offload"):
+                if src.is_member and src.is_colocate:
+                    src.offload()
+            with span("sync.dst_onload_kv"):
+                if dst.is_member:
+                    dst.onload(tags=[TAG_KV_CACHE])
         return ms
 
     def clean(self):
