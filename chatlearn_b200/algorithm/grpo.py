@@ -181,7 +181,7 @@ class GrpoAlgorithm(BaseAlgorithm):
         reward = RuleReward("reward")
         if ra.use_rollout_manager:
             from chatlearn_b200.models.agent.rollout_manager import RolloutManager
-            engine = RolloutManagerGRPOEngine(RolloutManager("rollout_manager"), policy, reward,
+            engine = RolloutManagerGRPOEngine(RolloutManager("rollout_manager", engine_module=policy), policy, reward,
                                               ref_policy, policy_trainer)
         else:
             prm = None

@@ -19,6 +19,8 @@ from chatlearn_b200.models.base_module import BaseModule
 
 
 class PartialRolloutManager(BaseModule):
+    whole_batch = True        # the executor hands over the episode in one call, not in generation batches
+
     def setup(self):
         self._metric_prefix = "partial_rollout_manager"
         ma = self.module_args

@@ -47,7 +47,9 @@ class PackedBatch:
     sample_ids: List[int]
     old_logprobs: Optional[torch.Tensor] = None   # [T] aligned with labels
     ref_logprobs: Optional[torch.Tensor] = None
-    advantages: Optional[torch.Tensor] = None     # [T] (sequence advantage broadcast)
+    advantages: Optional[torch.Tensor] = None     # [T] (sequence advantage broadcast, or per token)
+    values: Optional[torch.Tensor] = None         # [T] value estimates at rollout time (PPO critic)
+    returns: Optional[torch.Tensor] = None        # [T] value targets
     pad: int = 0                                  # trailing pad tokens (SP/CP alignment)
 
     def to(self, device):
@@ -89,6 +91,8 @@ def pack_samples(samples: List[Dict[str, Any]], pad_multiple: int = 1, seq_multi
     have_old = all("old_logprobs" in s for s in samples)
     have_ref = all("ref_logprobs" in s for s in samples)
     have_adv = all("advantages" in s for s in samples)
+    vals = [] if all("values" in s for s in samples) else None
+    rets = [] if all("returns" in s for s in samples) else None
     for i, s in enumerate(samples):
         t = torch.as_tensor(s["all_tokens"], dtype=torch.long).flatten()
         pl, rl = int(s["prompt_token_length"]), int(s["response_token_length"])
@@ -117,7 +121,15 @@ def pack_samples(samples: List[Dict[str, Any]], pad_multiple: int = 1, seq_multi
         if have_ref:
             ref.append(torch.nn.functional.pad(_per_token(s["ref_logprobs"], pl, n), (0, n_pad)))
         if have_adv:
-            adv.append(torch.full((L,), float(s["advantages"]), dtype=torch.float32))
+            a = s["advantages"]
+            if torch.is_tensor(a) and a.numel() > 1 or isinstance(a, (list, tuple)):
+                # one advantage per response token (PPO with GAE)
+                adv.append(torch.nn.functional.pad(_per_token(a, pl, n), (0, n_pad)))
+            else:
+                adv.append(torch.full((L,), float(a), dtype=torch.float32))
+        for key, lst in (("values", vals), ("returns", rets)):
+            if lst is not None:
+                lst.append(torch.nn.functional.pad(_per_token(s[key], pl, n), (0, n_pad)))
     T = sum(seq_lens)
     pad = (-T) % pad_multiple
     if pad:
@@ -127,7 +139,7 @@ def pack_samples(samples: List[Dict[str, Any]], pad_multiple: int = 1, seq_multi
         mask.append(torch.zeros(pad))
         sid.append(torch.full((pad,), len(samples), dtype=torch.long))
         seq_lens.append(pad)
-        for lst in (old, ref, adv):
+        for lst in (old, ref, adv, vals, rets):
             if lst:
                 lst.append(torch.zeros(pad))
     cu = torch.zeros(len(seq_lens) + 1, dtype=torch.int32)
@@ -137,7 +149,7 @@ def pack_samples(samples: List[Dict[str, Any]], pad_multiple: int = 1, seq_multi
                        loss_mask=torch.cat(mask), seq_ids=torch.cat(sid), cu_seqlens=cu,
                        seq_lens=seq_lens, max_seqlen=max(seq_lens),
                        sample_ids=[int(s.get("id_in_list", i)) for i, s in enumerate(samples)],
-                       old_logprobs=cat(old), ref_logprobs=cat(ref), advantages=cat(adv), pad=pad)
+                       old_logprobs=cat(old), ref_logprobs=cat(ref), advantages=cat(adv), values=cat(vals or []), returns=cat(rets or []), pad=pad)
 
 
 def unpack_per_sample(values: torch.Tensor, batch: PackedBatch, samples: List[Dict]) -> List[torch.Tensor]:

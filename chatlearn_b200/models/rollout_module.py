@@ -100,7 +100,7 @@ class RolloutModule(TorchModule):
             lockstep_group=self.ep_group if self._ep > 1 else None,
             use_cuda_graphs=not bool(getattr(ma, "enforce_eager", False)))
         from chatlearn_b200.data.tokenizer import load_tokenizer
-        self.tokenizer = load_tokenizer(load, self.arch.vocab_size)
+        self.tokenizer = load_tokenizer(load, self.arch.vocab_size, kind=str(getattr(ma, "tokenizer", "auto")))
 
     # ------------------------------------------------------------------ generation
     def _sampling_params(self, is_eval: bool, max_tokens: int) -> SamplingParams:

@@ -80,7 +80,7 @@ class Executor:
     def _residency_flags(self, model, step: int, num_steps: int):
         """to_onload for the first step, to_offload for the last, only for colocated
         models that asked for memory to be freed (executor.py:396-403)."""
-        fg = getattr(model.module_args, "free_gpu_memory", None)
+        fg = getattr(model, "residency_args", None) or getattr(model.module_args, "free_gpu_memory", None)
         wants = fg is not None and (fg.offload_weights or fg.free_grad_buffers or fg.offload_optimizer_states)
         on = model.is_colocate and wants
         return on and step == 0, on and step == num_steps - 1
@@ -90,7 +90,7 @@ class Executor:
         model = node.model
         fn = getattr(model, node.func_name)
         bs = int(getattr(model.module_args, "generation_batch_size", 0) or 0)
-        if node.func_name == "train_step" or bs <= 0:
+        if node.func_name == "train_step" or bs <= 0 or getattr(model, "whole_batch", False):
             bs = max(len(my_samples), 1)
         chunks = [my_samples[s:s + bs] for s in range(0, len(my_samples), bs)] or [[]]
         out: List[Dict] = []
@@ -185,6 +185,10 @@ class Executor:
                             for j, d in enumerate(delta):
                                 full[bnd[r] + j].update(d)
                         results[node] = full
+                # a role may re-order the complete list (same code on every rank)
+                hook = getattr(model, "post_gather", None)
+                if hook is not None:
+                    results[node] = hook(results[node], node.func_name)
         return {n: results[n] for n in flow.return_nodes}
 
     # ------------------------------------------------------------------ metrics
