@@ -29,7 +29,12 @@ def read_data_path_list(data_path_list, mode: str = "jsonl") -> List[List[Dict[s
                 out.append([json.loads(line) for line in f if line.strip()])
         elif suffix == "json":
             with open(path, "r", encoding="utf-8") as f:
-                rows = json.load(f)
+                text = f.read()
+            try:
+                rows = json.loads(text)
+            except json.JSONDecodeError:
+                # dataset exporters write one JSON object per line into ".json" files
+                rows = [json.loads(line) for line in text.splitlines() if line.strip()]
             out.append(rows if isinstance(rows, list) else [rows])
         elif suffix == "parquet":
             import pandas as pd

@@ -30,12 +30,14 @@ def launch_local(cmd: List[str], nproc: int, cpu: bool = False, env: Optional[di
     """Run ``cmd`` as ``nproc`` ranks on this host; returns 0 or raises ``RankFailure``."""
     port = get_free_port()
     hb_dir = tempfile.mkdtemp(prefix="chatlearn_hb_")
+    err_dir = os.path.join(hb_dir, "errors")      # ranks report caught exceptions here (runtime/decorator.py)
     procs = []
     for r in range(nproc):
         e = dict(os.environ)
         e.update(env or {})
         e.update(RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE=str(nproc), LOCAL_WORLD_SIZE=str(nproc),
-                 MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CHATLEARN_HEARTBEAT_DIR=hb_dir)
+                 MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CHATLEARN_HEARTBEAT_DIR=hb_dir,
+                 CLB200_ERROR_DIR=err_dir)
         if cpu:
             e["CHATLEARN_FORCE_CPU"] = "1"
         procs.append(subprocess.Popen(cmd, env=e, stdout=stdout, stderr=subprocess.STDOUT if stdout else None,
@@ -54,6 +56,11 @@ def launch_local(cmd: List[str], nproc: int, cpu: bool = False, env: Optional[di
                             failed = (r, "heartbeat timeout")
                 elif rc != 0:
                     failed = (r, f"exit code {rc}")
+            if not failed and os.path.isdir(err_dir):
+                errs = sorted(os.listdir(err_dir))
+                if errs:
+                    with open(os.path.join(err_dir, errs[0]), encoding="utf-8") as f:
+                        failed = (int(errs[0][4:-4]), "reported " + f.readline().strip())
             if failed or alive == 0:
                 break
             time.sleep(poll_s)

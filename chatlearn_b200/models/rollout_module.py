@@ -218,5 +218,9 @@ class RolloutModule(TorchModule):
     def dump_parameters(self, path: str):
         import os
         os.makedirs(path, exist_ok=True)
-        torch.save({n: p.detach().float().cpu() for n, p, _, _ in self.model.named_leaves()},
+        import dataclasses
+        m = self.model
+        torch.save({"leaves": {n: p.detach().float().cpu() for n, p, _, _ in m.named_leaves()},
+                    "arch": dataclasses.asdict(m.arch), "tp": m.tp, "tp_rank": m.tp_rank, "ep": m.ep,
+                    "ep_rank": m.ep_rank},
                    os.path.join(path, f"{self.name}_rank{self.get_rank()}.pt"))

@@ -292,9 +292,13 @@ class Engine(BaseEngine):
         self.model_manager.sync_parameters(episode_offset=0)
         self.timers("sync_parameters").stop()
         if dump:
-            for _, dst in self._param_sync_pairs:
+            # what the rollout holds after the sync, and what the trainer says it should hold;
+            # `python -m chatlearn_b200.synchronizer.check_parameter_sync --root_dir <dump>` compares them
+            from chatlearn_b200.synchronizer.check_parameter_sync import dump_expected
+            for src, dst in self._param_sync_pairs:
                 if dst.is_member and hasattr(dst, "dump_parameters"):
                     dst.dump_parameters(os.path.join(dump, "after_sync_parameter"))
+                dump_expected(src, os.path.join(dump, "trainer_hf"))
         if ra.enable_eval_before_training and self.evaluator is not None:
             self.evaluator.eval(-1, 0)
         self._prepared = True

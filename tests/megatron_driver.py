@@ -9,6 +9,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import torch  # noqa: E402
 
+torch.set_num_threads(1)      # fixed reduction order: runs are comparable across machine load
+
 from chatlearn_b200.algorithm.grpo import GrpoConfig  # noqa: E402
 from chatlearn_b200.checkpoint.safetensors_io import save_hf_checkpoint  # noqa: E402
 from chatlearn_b200.configs import resolve, to_dataclass  # noqa: E402
