@@ -128,7 +128,7 @@ def build_config(args, out_dir, data_path, n_gpu):
             "enable_resume_training": False, "log_args_dict": {"log_dir": out_dir}},
         "models": {
             "policy_trainer": dict(common, num_gpu=n_gpu, fsdp_size=n_gpu, trainable=True,
-                                   generation_batch_size=spe, kl_coef=0.001, gradient_checkpointing=True,
+                                   generation_batch_size=spe, kl_coef=0.001, gradient_checkpointing=True, checkpoint_layers="auto",
                                    optimizer={"lr": 2e-6}, save_hf=False,
                                    # fp32 master + Adam shards stay on the GPU (180 GB HBM); the fp32
                                    # gradient buffer is released outside training

@@ -47,6 +47,32 @@ class PolicyTrainer(FSDPModule):
             else ma.generation_batch_size
         return split_microbatch(data_list, micro_batch_size=max(int(mbs), 1))
 
+    def _num_checkpointed_layers(self, num_tokens: int) -> int:
+        """How many leading layers recompute their activations in backward.
+
+        ``checkpoint_layers``: ``all`` (default), an integer, or ``auto``: keep the
+        activations of as many layers as fit into the device memory that is free right
+        now (autograd saves 4·H + 2·(q+kv) + q + 3·F values per token and dense layer),
+        leaving a reserve for the logits chunks, the optimizer step and fragmentation."""
+        a = self.model.arch
+        L = a.num_hidden_layers
+        mode = getattr(self.module_args, "checkpoint_layers", "all")
+        if isinstance(mode, int) or str(mode).isdigit():
+            return max(0, min(L, int(mode)))
+        if str(mode) != "auto" or self.device.type != "cuda":
+            return L
+        q, kv = a.num_attention_heads * a.head_dim, 2 * a.num_key_value_heads * a.head_dim
+        F = a.intermediate_size
+        if a.num_experts:
+            F = a.moe_intermediate_size * (a.num_experts_per_tok + a.n_shared_experts)
+        per_layer = 1.15 * (4 * a.hidden_size + 2 * (q + kv) + q + 3 * F) * 2 * num_tokens
+        if self.sp is not None:
+            per_layer /= self.sp.size
+        free, total = torch.cuda.mem_get_info(self.device)
+        free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+        keep = int(max(free - 0.10 * total - (6 << 30), 0) // per_layer)
+        return max(0, L - keep)
+
     def _ctx_and_inputs(self, batch):
         """Device tensors + forward context of a packed row (Ulysses-split if sp>1)."""
         batch.to(self.device)
@@ -70,7 +96,11 @@ class PolicyTrainer(FSDPModule):
             from chatlearn_b200.models.nn.model import decoder_layer
             arch = self.model.arch
 
+            n_ckpt = self._num_checkpointed_layers(int(tokens.shape[0]))
+
             def hook(l, p, x, c):
+                if l >= n_ckpt:       # the last layers keep their activations: backward reaches them first
+                    return decoder_layer(arch, p, x, c, l)
                 return checkpoint(lambda xx: decoder_layer(arch, p, xx, c, l), x, use_reentrant=False)
         lp, ent = self.model.logprobs(tokens, labels, ctx, layer_hook=hook)
         if self.sp is not None:

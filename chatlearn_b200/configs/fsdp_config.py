@@ -2,6 +2,7 @@
 
 Parity: chatlearn/configs/fsdp_config.py:10-52.
 """
+from typing import Any
 from dataclasses import dataclass
 
 from .base import BaseConfig, BaseModelConfig
@@ -43,4 +44,7 @@ class FSDPRefPolicyConfig(RefPolicyConfig, FSDPConfig):
 @dataclass
 class FSDPPolicyTrainerConfig(PolicyTrainerConfig, FSDPConfig):
     gradient_checkpointing: bool = True
+    # with gradient_checkpointing on: 'auto' keeps the activations of as many layers as the free
+    # device memory holds and recomputes only the rest; an integer fixes the number recomputed
+    checkpoint_layers: Any = "all"
     save_hf: bool = True

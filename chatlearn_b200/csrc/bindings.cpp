@@ -52,6 +52,14 @@ void symm_adamw_push(at::Tensor master, const at::Tensor& grad, at::Tensor m, at
                      int64_t lo, bool params_bf16, int64_t step, double lr, double b1, double b2, double eps, double wd,
                      const c10::optional<at::Tensor>& scale, int64_t rank, int64_t num_slots);
 int64_t symm_last_status();
+at::Tensor grouped_gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets);
+std::vector<at::Tensor> moe_router_topk(const at::Tensor& logits, int64_t k, bool sigmoid, bool norm,
+                                        const c10::optional<at::Tensor>& bias, int64_t n_group, int64_t topk_group,
+                                        double scale);
+std::vector<at::Tensor> moe_permute(const at::Tensor& x, const at::Tensor& idx, const at::Tensor& offsets);
+at::Tensor moe_permute_at(const at::Tensor& x, const at::Tensor& pos, const c10::optional<at::Tensor>& scale);
+at::Tensor moe_combine(const at::Tensor& y, const at::Tensor& pos, const c10::optional<at::Tensor>& weights);
+at::Tensor moe_row_dot(const at::Tensor& dy, const at::Tensor& y, const at::Tensor& pos);
 at::Tensor symm_ar_residual_rmsnorm(const std::vector<int64_t>& part_ptrs, const std::vector<int64_t>& flag_ptrs,
                                     at::Tensor expect, at::Tensor resid, const c10::optional<at::Tensor>& w, double eps,
                                     int64_t rank, int64_t num_slots);
@@ -86,6 +94,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_rs_pull_sumsq", &symm_rs_pull_sumsq);
   m.def("symm_adamw_push", &symm_adamw_push);
   m.def("symm_last_status", &symm_last_status);
+  m.def("grouped_gemm_bf16_nt", &grouped_gemm_bf16_nt);
+  m.def("moe_router_topk", &moe_router_topk);
+  m.def("moe_permute", &moe_permute);
+  m.def("moe_permute_at", &moe_permute_at);
+  m.def("moe_combine", &moe_combine);
+  m.def("moe_row_dot", &moe_row_dot);
   m.def("symm_ar_residual_rmsnorm", &symm_ar_residual_rmsnorm);
   m.def("gemm_bf16_nt", &gemm_bf16_nt);
   m.def("gemm_bf16_nt_out", &gemm_bf16_nt_out);

@@ -97,16 +97,42 @@ __device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&
   }
 }
 
+// Grouped mode (mixture-of-experts): A holds the rows of all groups back to back, B the
+// groups' [N, K] matrices stacked along rows.  `table[i] = {first row, end row, first B
+// row of the group, -}` lists the row tiles (built on the device from the group offsets,
+// so the host never learns the group sizes); `count[0]` is the number of entries.  A row
+// tile may read past its group's rows (they belong to the next group or are zero-filled
+// beyond the tensor); only rows below `end row` are stored.
+struct GroupArgs {
+  const int4* table = nullptr;
+  const int* count = nullptr;
+};
+
+// Origin of a work tile: (first A/C row, first column, first B row of the group, end row).
+__device__ __forceinline__ void unit_origin(const GroupArgs& grp, int tile, int tiles_m, int tiles_n, int M, int& m0,
+                                            int& n0, int& b0, int& row_end) {
+  if (grp.table != nullptr) {
+    const int4 e = grp.table[tile / tiles_n];
+    m0 = e.x; row_end = e.y; b0 = e.z;
+    n0 = (tile % tiles_n) * BN;
+  } else {
+    tile_origin(tile, tiles_m, tiles_n, m0, n0);
+    b0 = 0; row_end = M;
+  }
+}
+
 template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    OutT* __restrict__ C, float* __restrict__ ws, int M, int N, int K, int ldc, int splits) {
+                    OutT* __restrict__ C, float* __restrict__ ws, int M, int N, int K, int ldc, int splits,
+                    GroupArgs grp) {
   extern __shared__ uint8_t smem_raw[];
   // dynamic shared memory is only 16-byte aligned by contract: align to 1024 for the swizzle
   SmemLayout* sm = reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  const bool grouped = grp.table != nullptr;
+  const int num_tiles = (grouped ? min(grp.count[0], tiles_m) : tiles_m) * tiles_n;   // grouped: tiles_m = table capacity
   const int k_iters = (K + BK - 1) / BK;
   // split-K: a work unit is (tile, k-slice); units of one k-slice are consecutive so
   // concurrently running CTAs stream disjoint parts of B
@@ -136,14 +162,14 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
-        int m0, n0;
-        tile_origin(unit % num_tiles, tiles_m, tiles_n, m0, n0);
+        int m0, n0, b0, row_end;
+        unit_origin(grp, unit % num_tiles, tiles_m, tiles_n, M, m0, n0, b0, row_end);
         const int k_begin = (unit / num_tiles) * k_per_split, k_end = min(k_begin + k_per_split, k_iters);
         for (int k = k_begin; k < k_end; ++k) {
           if (!mbar_wait(&sm->empty[stage], phase ^ 1)) { ok = false; break; }
           mbar_expect_tx(&sm->full[stage], kStageBytesA + kStageBytesB);
           tma_load_2d(sm->a[stage], &tmA, &sm->full[stage], k * BK, m0);
-          tma_load_2d(sm->b[stage], &tmB, &sm->full[stage], k * BK, n0);
+          tma_load_2d(sm->b[stage], &tmB, &sm->full[stage], k * BK, b0 + n0);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -185,8 +211,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
-      int m0, n0;
-      tile_origin(unit % num_tiles, tiles_m, tiles_n, m0, n0);
+      int m0, n0, b0, row_end;
+      unit_origin(grp, unit % num_tiles, tiles_m, tiles_n, M, m0, n0, b0, row_end);
       const bool empty_slice = (unit / num_tiles) * k_per_split >= k_iters;   // nothing was accumulated
       if (!mbar_wait(&sm->acc_full[acc], acc_phase)) { ok = false; break; }
       tc_fence_after_sync();
@@ -198,7 +224,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
         const int col = n0 + c;
-        if (row < M && col < N && !empty_slice) {
+        if (row < row_end && col < N && !empty_slice) {
           if (splits == 1) {
             store_row32<OutT>(C + (int64_t)row * ldc + col, r, min(32, N - col));
           } else {
@@ -328,12 +354,12 @@ static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bo
   if (out_fp32) {
     static bool cfg = false;
     if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
-    gemm_bf16_nt_kernel<float><<<grid, kThreads, smem, st>>>(tmA, tmB, c.data_ptr<float>(), ws, (int)M, (int)N, (int)K, (int)N, splits);
+    gemm_bf16_nt_kernel<float><<<grid, kThreads, smem, st>>>(tmA, tmB, c.data_ptr<float>(), ws, (int)M, (int)N, (int)K, (int)N, splits, GroupArgs{});
     if (splits > 1) splitk_finalize_kernel<float><<<(int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8), 256, 0, st>>>(ws, c.data_ptr<float>(), M * N, splits);
   } else {
     static bool cfg = false;
     if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
-    gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, (bf16*)c.data_ptr(), ws, (int)M, (int)N, (int)K, (int)N, splits);
+    gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, (bf16*)c.data_ptr(), ws, (int)M, (int)N, (int)K, (int)N, splits, GroupArgs{});
     if (splits > 1) splitk_finalize_kernel<bf16><<<(int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8), 256, 0, st>>>(ws, (bf16*)c.data_ptr(), M * N, splits);
   }
   return c;
@@ -349,6 +375,71 @@ int64_t gemm_last_status() {
 }
 
 void gemm_set_splitk(bool on) { g_allow_splitk = on; }
+
+// ----------------------------------------------------------------------------
+// Grouped GEMM for mixture-of-experts layers.
+// ----------------------------------------------------------------------------
+// offsets[g] .. offsets[g+1] are the rows of group g.  One block; thread g lists the
+// row tiles of group g after an exclusive scan of the per-group tile counts.
+static __global__ void build_group_table_kernel(const int64_t* __restrict__ offsets, int num_groups, int rows_b,
+                                                int capacity, int4* __restrict__ table, int* __restrict__ count) {
+  __shared__ int scan[1024];
+  const int g = threadIdx.x;
+  int lo = 0, hi = 0;
+  if (g < num_groups) { lo = (int)offsets[g]; hi = (int)offsets[g + 1]; }
+  const int mine = (hi - lo + BM - 1) / BM;
+  scan[g] = mine;
+  __syncthreads();
+  for (int d = 1; d < 1024; d <<= 1) {             // inclusive Hillis-Steele scan
+    const int v = g >= d ? scan[g - d] : 0;
+    __syncthreads();
+    scan[g] += v;
+    __syncthreads();
+  }
+  int at = scan[g] - mine;
+  for (int t = 0; t < mine && at < capacity; ++t, ++at)
+    table[at] = make_int4(lo + t * BM, hi, g * rows_b, 0);
+  if (g == 1023) count[0] = min(scan[1023], capacity);
+}
+
+// a [R, K] bf16 rows sorted by group; b [G, N, K] bf16; offsets [G+1] int64 on the device
+// (offsets[0] = 0, offsets[G] <= R).  Returns C [R, N] bf16; rows at or past offsets[G] are
+// not written.
+at::Tensor grouped_gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && offsets.is_cuda(), "grouped_gemm: CUDA tensors");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && offsets.scalar_type() == at::kLong,
+              "grouped_gemm: bf16 operands, int64 offsets");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 3 && a.size(1) == b.size(2) && a.is_contiguous() && b.is_contiguous(),
+              "grouped_gemm: A [R, K], B [G, N, K], contiguous");
+  const int64_t R = a.size(0), K = a.size(1), G = b.size(0), N = b.size(1);
+  TORCH_CHECK(offsets.numel() == G + 1 && G <= 1024, "grouped_gemm: offsets [G+1], at most 1024 groups");
+  TORCH_CHECK(K % 8 == 0 && N % 8 == 0 && K > 0, "grouped_gemm: K and N must be multiples of 8");
+  TORCH_CHECK(((uintptr_t)a.data_ptr() % 16 == 0) && ((uintptr_t)b.data_ptr() % 16 == 0), "grouped_gemm: 16-byte aligned operands");
+  auto c = at::empty({R, N}, a.options());
+  if (R == 0) return c;
+  const int capacity = (int)((R + BM - 1) / BM + G);      // every group adds at most one partial tile
+  auto table = at::empty({capacity, 4}, a.options().dtype(at::kInt));
+  auto count = at::empty({1}, a.options().dtype(at::kInt));
+  auto st = at::cuda::getCurrentCUDAStream();
+  build_group_table_kernel<<<1, 1024, 0, st>>>(offsets.data_ptr<int64_t>(), (int)G, (int)N, capacity,
+                                               reinterpret_cast<int4*>(table.data_ptr<int>()), count.data_ptr<int>());
+  CUtensorMap tmA = make_tmap_bf16(a.data_ptr(), R, K, K, BM);
+  CUtensorMap tmB = make_tmap_bf16(b.data_ptr(), G * N, K, K, BN);
+  static int num_sms = 0;
+  if (!num_sms) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, a.get_device());
+  const size_t smem = sizeof(SmemLayout) + 1024;
+  static bool cfg = false;
+  if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
+  const int tiles_n = (int)((N + BN - 1) / BN);
+  const int grid = std::min(capacity * tiles_n, num_sms);
+  GroupArgs g;
+  g.table = reinterpret_cast<const int4*>(table.data_ptr<int>());
+  g.count = count.data_ptr<int>();
+  // M = capacity * BM makes the kernel's row-tile bound equal to the table capacity
+  gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, (bf16*)c.data_ptr(), nullptr, capacity * BM, (int)N,
+                                                         (int)K, (int)N, 1, g);
+  return c;
+}
 
 // ----------------------------------------------------------------------------
 // Allocation-free entry point (see gemm_noalloc.h): same kernel, split-K planes in a
@@ -450,10 +541,10 @@ extern "C" int clb200_gemm_bf16_nt_noalloc(const void* a, const void* b, void* c
   const int64_t mn = (int64_t)M * N;
   const int fgrid = (int)std::min<int64_t>((mn / 4 + 255) / 256, 148 * 8);
   if (out_fp32) {
-    gemm_bf16_nt_kernel<float><<<grid, kThreads, smem, st>>>(tmA, tmB, static_cast<float*>(c), d.scratch, M, N, K, N, splits);
+    gemm_bf16_nt_kernel<float><<<grid, kThreads, smem, st>>>(tmA, tmB, static_cast<float*>(c), d.scratch, M, N, K, N, splits, GroupArgs{});
     if (splits > 1) splitk_finalize_kernel<float><<<fgrid, 256, 0, st>>>(d.scratch, static_cast<float*>(c), mn, splits);
   } else {
-    gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, static_cast<bf16*>(c), d.scratch, M, N, K, N, splits);
+    gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, static_cast<bf16*>(c), d.scratch, M, N, K, N, splits, GroupArgs{});
     if (splits > 1) splitk_finalize_kernel<bf16><<<fgrid, 256, 0, st>>>(d.scratch, static_cast<bf16*>(c), mn, splits);
   }
   const cudaError_t e = cudaGetLastError();

@@ -398,3 +398,5 @@ for _name, _fn in (("rmsnorm", rmsnorm), ("swiglu", swiglu), ("qk_norm_rope", qk
                    ("sample", sample), ("apply_penalties", apply_penalties), ("kv_append", kv_append),
                    ("paged_attention", paged_attention)):
     register_native(_name, _fn)
+
+from . import native_moe  # noqa: E402,F401  (registers the mixture-of-experts ops)
