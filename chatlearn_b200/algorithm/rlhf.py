@@ -89,7 +89,7 @@ class ScalarHeadModule(PolicyTrainer):
         from chatlearn_b200.models.nn.model import CausalLM
         ma = self.module_args
         dp = self.dp_group.size if self.dp_group is not None else 1
-        model = CausalLM(_score_arch(ma), dtype=self.compute_dtype, device=self.device, pad_to=dp)
+        model = CausalLM(_score_arch(ma), dtype=self.compute_dtype, device=self.device, pad_to=dp * 8)
         load = getattr(ma, "load", None)
         from chatlearn_b200.checkpoint.safetensors_io import has_safetensors, load_into_model
         if load and has_safetensors(load):

@@ -14,6 +14,8 @@ class FSDPConfig(BaseConfig):
     fsdp_size: int = 1
     ulysses_sequence_parallel_size: int = 1
     meta_init: bool = False
+    # optimizer-step reduce-scatter / all-gather by this package's peer-memory kernels (GPU, 2..8 ranks)
+    fused_optimizer_comm: bool = True
     groupgemm: bool = False
     use_expandable_segments: bool = False
 

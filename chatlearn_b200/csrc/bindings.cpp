@@ -65,6 +65,7 @@ at::Tensor symm_ar_residual_rmsnorm(const std::vector<int64_t>& part_ptrs, const
                                     int64_t rank, int64_t num_slots);
 at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32);
 void gemm_bf16_nt_out(const at::Tensor& a, const at::Tensor& b, at::Tensor out);
+void gemm_set_tile_n(int64_t bn);
 int64_t gemm_last_status();
 void gemm_set_splitk(bool on);
 
@@ -103,6 +104,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_ar_residual_rmsnorm", &symm_ar_residual_rmsnorm);
   m.def("gemm_bf16_nt", &gemm_bf16_nt);
   m.def("gemm_bf16_nt_out", &gemm_bf16_nt_out);
+  m.def("gemm_set_tile_n", &gemm_set_tile_n);
   m.def("gemm_last_status", &gemm_last_status);
   m.def("gemm_set_splitk", &gemm_set_splitk);
 }

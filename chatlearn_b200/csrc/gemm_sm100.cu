@@ -31,9 +31,12 @@ constexpr int kTmemCols = BN * kAccBufs;  // 512
 constexpr int kThreads = 192;
 constexpr uint32_t kStageBytesA = BM * BK * 2, kStageBytesB = BN * BK * 2;
 
-struct __align__(1024) SmemLayout {
+// The kernel is instantiated for tile widths 256 (large problems), 128 and 64 (few rows, as
+// in a decode step: narrower tiles give every SM a tile without slicing K).
+template <int BN_>
+struct __align__(1024) SmemLayoutT {
   uint8_t a[kStages][kStageBytesA];
-  uint8_t b[kStages][kStageBytesB];
+  uint8_t b[kStages][BN_ * BK * 2];
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t acc_full[kAccBufs];
@@ -41,9 +44,11 @@ struct __align__(1024) SmemLayout {
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
+using SmemLayout = SmemLayoutT<BN>;
 
 __device__ int g_gemm_status = 0;
 bool g_allow_splitk = true;
+int g_force_bn = 0;       // 0: choose the tile width per shape
 
 enum : int { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3 };
 
@@ -51,7 +56,7 @@ enum : int { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE
 // so the CTAs running at the same time share a narrow band of B (which then stays
 // in L2) instead of each re-streaming the whole weight matrix.
 constexpr int kGroupM = 16;
-__device__ __forceinline__ void tile_origin(int tile, int tiles_m, int tiles_n, int& m0, int& n0) {
+__device__ __forceinline__ void tile_origin(int tile, int tiles_m, int tiles_n, int& m0, int& n0, int BN) {
   const int group_size = kGroupM * tiles_n;
   const int group = tile / group_size;
   const int first_m = group * kGroupM;
@@ -110,22 +115,27 @@ struct GroupArgs {
 
 // Origin of a work tile: (first A/C row, first column, first B row of the group, end row).
 __device__ __forceinline__ void unit_origin(const GroupArgs& grp, int tile, int tiles_m, int tiles_n, int M, int& m0,
-                                            int& n0, int& b0, int& row_end) {
+                                            int& n0, int& b0, int& row_end, int BN) {
   if (grp.table != nullptr) {
     const int4 e = grp.table[tile / tiles_n];
     m0 = e.x; row_end = e.y; b0 = e.z;
     n0 = (tile % tiles_n) * BN;
   } else {
-    tile_origin(tile, tiles_m, tiles_n, m0, n0);
+    tile_origin(tile, tiles_m, tiles_n, m0, n0, BN);
     b0 = 0; row_end = M;
   }
 }
 
-template <typename OutT>
+template <typename OutT, int BN_ = 256>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     OutT* __restrict__ C, float* __restrict__ ws, int M, int N, int K, int ldc, int splits,
                     GroupArgs grp) {
+  // tile width of this instantiation (these names hide the 256-wide defaults of the file scope)
+  constexpr int BN = BN_;
+  constexpr uint32_t kStageBytesB = BN * BK * 2;
+  constexpr int kTmemCols = BN * kAccBufs;          // 512, 256 or 128 columns: powers of two >= 32
+  using SmemLayout = SmemLayoutT<BN>;
   extern __shared__ uint8_t smem_raw[];
   // dynamic shared memory is only 16-byte aligned by contract: align to 1024 for the swizzle
   SmemLayout* sm = reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -163,7 +173,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
         int m0, n0, b0, row_end;
-        unit_origin(grp, unit % num_tiles, tiles_m, tiles_n, M, m0, n0, b0, row_end);
+        unit_origin(grp, unit % num_tiles, tiles_m, tiles_n, M, m0, n0, b0, row_end, BN);
         const int k_begin = (unit / num_tiles) * k_per_split, k_end = min(k_begin + k_per_split, k_iters);
         for (int k = k_begin; k < k_end; ++k) {
           if (!mbar_wait(&sm->empty[stage], phase ^ 1)) { ok = false; break; }
@@ -212,7 +222,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     bool ok = true;
     for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
       int m0, n0, b0, row_end;
-      unit_origin(grp, unit % num_tiles, tiles_m, tiles_n, M, m0, n0, b0, row_end);
+      unit_origin(grp, unit % num_tiles, tiles_m, tiles_n, M, m0, n0, b0, row_end, BN);
       const bool empty_slice = (unit / num_tiles) * k_per_split >= k_iters;   // nothing was accumulated
       if (!mbar_wait(&sm->acc_full[acc], acc_phase)) { ok = false; break; }
       tc_fence_after_sync();
@@ -334,35 +344,77 @@ static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bo
   if (M == 0 || N == 0) return c;
   if (K == 0) return c.zero_();
   TORCH_CHECK(N % 8 == 0, "gemm_bf16_nt: N must be a multiple of 8");
-  CUtensorMap tmA = make_tmap_bf16(a.data_ptr(), M, K, a.stride(0), BM);
-  CUtensorMap tmB = make_tmap_bf16(b.data_ptr(), N, K, b.stride(0), BN);
-  const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
   static int num_sms = 0;
   if (!num_sms) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, a.get_device());
-  const size_t smem = sizeof(SmemLayout) + 1024;
-  auto st = at::cuda::getCurrentCUDAStream();
-  // few tiles (decode: M <= 128) cannot fill the SMs: slice K so every SM streams weights
+  const int tiles_m = (int)((M + BM - 1) / BM);
   const int k_iters = (int)((K + BK - 1) / BK);
-  int splits = 1;
-  if (g_allow_splitk && tiles * 2 <= num_sms && N % 4 == 0) {
-    splits = std::min({(num_sms + tiles - 1) / tiles, std::max(k_iters / 4, 1), 16});
-    while (splits > 1 && (int64_t)splits * M * N > kWorkspaceFloats) --splits;
-    while (splits > 1 && ((k_iters + splits - 1) / splits) * (splits - 1) >= k_iters) --splits;  // no empty slice
+  // Tile width and K slicing.  Large problems: 256-wide tiles, whole K.  Few rows (a decode
+  // step): every SM should stream weights exactly once, so pick, among widths 256/128/64 and
+  // slice counts that keep all work in one wave, the plan with the least estimated traffic
+  // time: operand bytes per SM-sequence plus, when K is sliced, the fp32 partial planes.
+  int bn = 256, splits = 1;
+  if (g_force_bn) {
+    bn = g_force_bn;
+  } else if (tiles_m * ((N + 255) / 256) < num_sms) {
+    double best = 1e30;
+    for (int cand : {256, 128, 64}) {
+      const int tiles = tiles_m * (int)((N + cand - 1) / cand);
+      int max_s = 1;
+      if (g_allow_splitk && N % 4 == 0 && tiles < num_sms) max_s = std::min({num_sms / tiles, std::max(k_iters / 4, 1), 16});
+      for (int s = 1; s <= max_s; ++s) {
+        if ((int64_t)s * M * N > kWorkspaceFloats) break;
+        const int per = (k_iters + s - 1) / s;
+        if (s > 1 && per * (s - 1) >= k_iters) continue;                 // would leave an empty slice
+        const int waves = (tiles * s + num_sms - 1) / num_sms;
+        // the longer of: all operand bytes at device bandwidth, one SM's tile loads at the rate a
+        // single SM sustains from L2 (activation tiles are re-read there); then, if K is sliced,
+        // the partial planes written and re-read plus a fixed charge for the extra launch
+        const double hbm = ((double)N * K + (double)M * K) * 2 / 6.5e12;
+        const double sm = (double)waves * per * (BM + cand) * BK * 2 / 90e9;
+        double cost = std::max(hbm, sm);
+        if (s > 1) cost += 2.0 * s * M * N * 4 / 6.5e12 + 3.5e-6;
+        if (cost < best) { best = cost; bn = cand; splits = s; }
+      }
+    }
   }
+  if (g_force_bn && g_allow_splitk && N % 4 == 0) {
+    const int tiles = tiles_m * (int)((N + bn - 1) / bn);
+    if (tiles * 2 <= num_sms) {
+      splits = std::min({num_sms / tiles, std::max(k_iters / 4, 1), 16});
+      while (splits > 1 && (int64_t)splits * M * N > kWorkspaceFloats) --splits;
+      while (splits > 1 && ((k_iters + splits - 1) / splits) * (splits - 1) >= k_iters) --splits;
+    }
+  }
+  const int tiles = tiles_m * (int)((N + bn - 1) / bn);
+  CUtensorMap tmA = make_tmap_bf16(a.data_ptr(), M, K, a.stride(0), BM);
+  CUtensorMap tmB = make_tmap_bf16(b.data_ptr(), N, K, b.stride(0), bn);
+  auto st = at::cuda::getCurrentCUDAStream();
   float* ws = splits > 1 ? splitk_workspace(a.get_device(), a.options()) : nullptr;
   const int grid = std::min(tiles * splits, num_sms);
+#define CLB_LAUNCH_GEMM(T, W, PTR)                                                                                    \
+  do {                                                                                                                \
+    const size_t smem = sizeof(SmemLayoutT<W>) + 1024;                                                                \
+    static bool cfg = false;                                                                                          \
+    if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<T, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; } \
+    gemm_bf16_nt_kernel<T, W><<<grid, kThreads, smem, st>>>(tmA, tmB, PTR, ws, (int)M, (int)N, (int)K, (int)N, splits, GroupArgs{}); \
+  } while (0)
   if (out_fp32) {
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
-    gemm_bf16_nt_kernel<float><<<grid, kThreads, smem, st>>>(tmA, tmB, c.data_ptr<float>(), ws, (int)M, (int)N, (int)K, (int)N, splits, GroupArgs{});
-    if (splits > 1) splitk_finalize_kernel<float><<<(int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8), 256, 0, st>>>(ws, c.data_ptr<float>(), M * N, splits);
+    float* p = c.data_ptr<float>();
+    if (bn == 256) CLB_LAUNCH_GEMM(float, 256, p); else if (bn == 128) CLB_LAUNCH_GEMM(float, 128, p); else CLB_LAUNCH_GEMM(float, 64, p);
+    if (splits > 1) splitk_finalize_kernel<float><<<(int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8), 256, 0, st>>>(ws, p, M * N, splits);
   } else {
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
-    gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, (bf16*)c.data_ptr(), ws, (int)M, (int)N, (int)K, (int)N, splits, GroupArgs{});
-    if (splits > 1) splitk_finalize_kernel<bf16><<<(int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8), 256, 0, st>>>(ws, (bf16*)c.data_ptr(), M * N, splits);
+    bf16* p = (bf16*)c.data_ptr();
+    if (bn == 256) CLB_LAUNCH_GEMM(bf16, 256, p); else if (bn == 128) CLB_LAUNCH_GEMM(bf16, 128, p); else CLB_LAUNCH_GEMM(bf16, 64, p);
+    if (splits > 1) splitk_finalize_kernel<bf16><<<(int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8), 256, 0, st>>>(ws, p, M * N, splits);
   }
+#undef CLB_LAUNCH_GEMM
   return c;
+}
+
+// Debug / measurement knob: 0 = choose the tile width per shape, 64 / 128 / 256 = always that width.
+void gemm_set_tile_n(int64_t bn) {
+  TORCH_CHECK(bn == 0 || bn == 64 || bn == 128 || bn == 256, "tile width must be 0, 64, 128 or 256");
+  g_force_bn = (int)bn;
 }
 
 // Status of the GEMM kernels since the last call (0 = ok); synchronises the device.

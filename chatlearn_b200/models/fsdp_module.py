@@ -15,6 +15,7 @@ from typing import Dict, List, Optional
 import numpy as np
 import torch
 
+from chatlearn_b200 import ops
 from chatlearn_b200.models.base_module import TorchModule
 from chatlearn_b200.models.nn import CausalLM, resolve_arch
 from chatlearn_b200.parallel import UlyssesGroup, build_mesh
@@ -53,7 +54,8 @@ class FSDPModule(TorchModule):
     def create_model(self) -> CausalLM:
         arch = resolve_arch(self.module_args)
         dp = self.dp_group.size if self.dp_group is not None else 1
-        model = CausalLM(arch, dtype=self.compute_dtype, device=self.device, pad_to=dp)
+        # blocks padded so that every rank's shard is a whole number of 16-byte vectors
+        model = CausalLM(arch, dtype=self.compute_dtype, device=self.device, pad_to=dp * 8)
         load = getattr(self.module_args, "load", None)
         from chatlearn_b200.checkpoint.safetensors_io import has_safetensors, load_into_model
         if load and has_safetensors(load):
@@ -77,6 +79,13 @@ class FSDPModule(TorchModule):
                 self.model, self.dp_group, lr=oc.lr, betas=(oc.adam_beta1, oc.adam_beta2),
                 eps=getattr(oc, "adam_eps", 1e-8), weight_decay=oc.weight_decay,
                 clip_grad=oc.clip_grad, grad_dtype=grad_dtype)
+            # optimizer-step collectives by this package's peer-memory kernels; needs the
+            # weights and gradient buffers to stay on the device (symmetric memory)
+            fg = self.module_args.free_gpu_memory
+            if bool(getattr(self.module_args, "fused_optimizer_comm", True)) and not fg.offload_weights \
+                    and os.environ.get("CLB200_SYMM_ZERO", "1") != "0" and ops.get_mode() == "native":
+                if self.state.enable_symm():
+                    self._logger.info("optimizer step uses in-kernel reduce-scatter / all-gather over symmetric memory")
             if self.resume_training_path():
                 self.load_checkpoint(self.resume_training_path())
 

@@ -72,6 +72,48 @@ class ShardedTrainState:
             g = self.edp if b.name.endswith(".experts") else self.dp
             self.states.append(BlockState(b, g, grad_dtype, model.device))
         self.last_grad_norm = 0.0
+        self.symm = None            # parallel.symm_collectives.SymmGroup once enable_symm() succeeded
+
+    # ------------------------------------------------------------------ in-kernel collectives
+    def enable_symm(self) -> bool:
+        """Move the parameters and gradient buffers of the data-parallel blocks into
+        symmetric memory, so that the optimizer step runs as two peer-memory kernels per
+        block (pull reduce-scatter + squared norm; AdamW + push all-gather) instead of
+        NCCL reduce-scatter / all-gather.  Collective over the data-parallel group;
+        returns False (and changes nothing) where symmetric memory is unavailable.
+        Buffers in symmetric memory stay resident: they are never offloaded or freed."""
+        from . import symm_collectives, symm_mem
+        dp = self.dp
+        dev = self.model.device
+        if dev.type != "cuda" or dp.size < 2 or dp.size > 8 or self.tp_size != 1:
+            return False
+        mine = [s for s in self.states if s.group is dp and s.grad is not None]
+        if not mine or any(s.grad.dtype != torch.float32 or s.shard_numel % 4 or s.lo % 4 for s in mine):
+            return False
+        sg = symm_collectives.get(dp)
+        if sg is None:
+            return False
+        total = sum(s.block.numel for s in mine)
+        pdt = mine[0].block.flat.dtype
+        p_arena = symm_mem.empty(total, pdt, dev, group=dp.pg)
+        g_arena = symm_mem.empty(total, torch.float32, dev, group=dp.pg)
+        g_arena.zero_()
+        off = 0
+        for s in mine:
+            n = s.block.numel
+            flat = p_arena[off:off + n]
+            flat.copy_(s.block.flat)
+            s.block.bind(flat)
+            s.grad = g_arena[off:off + n]
+            s.block.enable_grad(s.grad)
+            s.grad_shard = torch.zeros(s.shard_numel, dtype=torch.float32, device=dev)
+            s.symm = True
+            off += n
+        self._arenas = (p_arena, g_arena)
+        torch.cuda.synchronize(dev)
+        dp.barrier()
+        self.symm = sg
+        return True
 
     # ------------------------------------------------------------------ step
     def zero_grad(self):
@@ -90,7 +132,11 @@ class ShardedTrainState:
                         self.tp_group.all_reduce_(s.grad[o:o + lf.numel])
             g = s.group
             fused = g.fast.get("reduce_scatter_f32")
-            if fused is not None and s.grad.is_cuda:
+            if self.symm is not None and getattr(s, "symm", False):
+                # every rank pulls its shard from all peers' gradient buffers over NVLink and
+                # sums it; the kernel also leaves the shard's squared norm (per-CTA partials)
+                s.sq_partial = self.symm.reduce_scatter_pull(s.grad, s.grad_shard, s.lo)
+            elif fused is not None and s.grad.is_cuda:
                 fused(s.grad_shard, s.grad)
             elif g.size == 1:
                 if s.grad_shard.data_ptr() != s.grad.data_ptr():
@@ -135,8 +181,12 @@ class ShardedTrainState:
         edp_sq = torch.zeros((), dtype=torch.float32, device=dev)
         for s in self.states:
             v = torch.zeros((), dtype=torch.float32, device=dev)
-            for a, b, w in self._norm_ranges(s):
-                v = v + ops.sumsq(s.grad_shard[a:b]) * w
+            if getattr(s, "sq_partial", None) is not None:
+                v = s.sq_partial.sum()        # computed by the reduce-scatter kernel
+                s.sq_partial = None
+            else:
+                for a, b, w in self._norm_ranges(s):
+                    v = v + ops.sumsq(s.grad_shard[a:b]) * w
             if s.group is self.edp and self.edp is not self.dp:
                 edp_sq += v
             else:
@@ -169,6 +219,13 @@ class ShardedTrainState:
         self.step_count += 1
         lr = self.lr if lr is None else lr
         for s in self.states:
+            if self.symm is not None and getattr(s, "symm", False):
+                # AdamW on the shard; the new weights are stored straight into every rank's
+                # parameter buffer (the all-gather), completion is agreed inside the kernel
+                self.symm.adamw_push(s.master, s.grad_shard, s.exp_avg, s.exp_avg_sq, s.block.flat, s.lo,
+                                     self.step_count, lr, self.betas[0], self.betas[1], self.eps, self.wd,
+                                     scale if torch.is_tensor(scale) else None)
+                continue
             new_shard = s.block.flat[s.lo:s.hi]
             ops.adamw_step(s.master, s.grad_shard, s.exp_avg, s.exp_avg_sq, new_shard,
                            self.step_count, lr, self.betas[0], self.betas[1], self.eps, self.wd,
@@ -186,6 +243,8 @@ class ShardedTrainState:
         """(owner object, attribute) pairs of the tensors behind a memory tag."""
         out = []
         for s in self.states:
+            if getattr(s, "symm", False) and tag in ("weights", "grads"):
+                continue                      # symmetric-memory buffers stay resident
             if tag == "weights":
                 out.append((s.block, "flat"))
             elif tag == "grads":

@@ -160,6 +160,34 @@ for step in (1, 2):
 res["zero_step_ok"] = ok
 res["status"] = sg.status()
 
+# ---- the sharded optimizer step through ShardedTrainState: peer-memory kernels vs NCCL ----
+from chatlearn_b200.models.nn import PRESETS as _P, CausalLM as _LM  # noqa: E402
+from chatlearn_b200.parallel.zero import ShardedTrainState  # noqa: E402
+
+ma = _LM(_P["tiny_qwen3"](), dtype=torch.bfloat16, device=dev, pad_to=world * 8).init_weights(5)
+mb = _LM(_P["tiny_qwen3"](), dtype=torch.bfloat16, device=dev, pad_to=world * 8).init_weights(5)
+sa = ShardedTrainState(ma, g, lr=1e-3, clip_grad=1.0)
+sb = ShardedTrainState(mb, g, lr=1e-3, clip_grad=1.0)
+res["zero_state_symm_enabled"] = bool(sa.enable_symm())
+norms = []
+for step in (1, 2, 3):
+    sa.zero_grad(); sb.zero_grad()
+    torch.manual_seed(50 * step + rank)
+    for x, y in zip(sa.states, sb.states):
+        gr_ = torch.randn(x.block.numel, device=dev) * 0.01
+        x.grad.copy_(gr_); y.grad.copy_(gr_)
+    na, nb = sa.step(), sb.step()
+    norms.append((float(na), float(nb)))
+torch.cuda.synchronize(); dist.barrier()
+res["zero_state_norms"] = norms
+# the two paths round the clip factor differently in the last bit, so a few bf16 weights may differ by one ulp
+mism = sum(int((x.block.flat != y.block.flat).sum()) for x, y in zip(sa.states, sb.states))
+tot = sum(x.block.numel for x in sa.states)
+maxd = max(float((x.block.flat.float() - y.block.flat.float()).abs().max()) for x, y in zip(sa.states, sb.states))
+res["zero_state_mismatch_frac"], res["zero_state_max_diff"] = mism / tot, maxd
+res["zero_state_ok"] = mism / tot < 1e-2 and maxd < 1e-3 and all(abs(a - b) <= 1e-4 * abs(b) for a, b in norms)
+res["zero_state_status"] = sg.status()
+
 # ---- weight sync: pull fp32 ZeRO shards from the peer into the rollout TP layout (bf16) ----
 from chatlearn_b200.models.nn import PRESETS, CausalLM  # noqa: E402
 from chatlearn_b200.parallel import symm_mem  # noqa: E402

@@ -1,0 +1,28 @@
+"""In-kernel collectives on two GPUs (all-reduce, fused all-reduce+residual+RMSNorm, pull
+reduce-scatter + AdamW push, the sharded train state on them, peer weight-sync pull).
+Runs ``tests/symm_driver.py`` under torchrun; skipped on boxes with fewer than two GPUs."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_symm_collectives_two_gpus():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29641", os.path.join(ROOT, "tests", "symm_driver.py")],
+                       capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    lines = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")]
+    assert p.returncode == 0 and lines, p.stdout[-2000:] + p.stderr[-2000:]
+    r = json.loads(lines[-1][7:])
+    for key in ("allreduce_ok", "ar_residual_rmsnorm_ok", "zero_step_ok", "zero_state_symm_enabled", "zero_state_ok",
+                "weight_sync_ok"):
+        assert r[key], (key, r)
+    assert r["status"] == 0 and r["status_after_graph"] == 0 and r["zero_state_status"] == 0
