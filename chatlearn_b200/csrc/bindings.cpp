@@ -52,6 +52,9 @@ void symm_adamw_push(at::Tensor master, const at::Tensor& grad, at::Tensor m, at
                      int64_t lo, bool params_bf16, int64_t step, double lr, double b1, double b2, double eps, double wd,
                      const c10::optional<at::Tensor>& scale, int64_t rank, int64_t num_slots);
 int64_t symm_last_status();
+bool attn_varlen_fwd_supported(int64_t head_dim);
+std::vector<at::Tensor> attn_varlen_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                        const at::Tensor& cu_seqlens, double scale, bool causal);
 at::Tensor grouped_gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets);
 std::vector<at::Tensor> moe_router_topk(const at::Tensor& logits, int64_t k, bool sigmoid, bool norm,
                                         const c10::optional<at::Tensor>& bias, int64_t n_group, int64_t topk_group,
@@ -95,6 +98,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_rs_pull_sumsq", &symm_rs_pull_sumsq);
   m.def("symm_adamw_push", &symm_adamw_push);
   m.def("symm_last_status", &symm_last_status);
+  m.def("attn_varlen_fwd_supported", &attn_varlen_fwd_supported);
+  m.def("attn_varlen_fwd", &attn_varlen_fwd);
   m.def("grouped_gemm_bf16_nt", &grouped_gemm_bf16_nt);
   m.def("moe_router_topk", &moe_router_topk);
   m.def("moe_permute", &moe_permute);

@@ -400,3 +400,4 @@ for _name, _fn in (("rmsnorm", rmsnorm), ("swiglu", swiglu), ("qk_norm_rope", qk
     register_native(_name, _fn)
 
 from . import native_moe  # noqa: E402,F401  (registers the mixture-of-experts ops)
+from . import native_attn  # noqa: E402,F401  (registers the packed attention forward)
