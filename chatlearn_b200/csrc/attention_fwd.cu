@@ -64,7 +64,7 @@ __device__ __forceinline__ void load_rows(bf16 (*dst)[D + kPad], const bf16* src
 }
 
 template <int D>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 attn_varlen_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                        const int* __restrict__ cu, int num_seqs, bf16* __restrict__ out, float* __restrict__ lse,
                        int64_t q_rs, int64_t k_rs, int64_t v_rs, int nq, int nkv, int total_rows, float scale, int causal) {
@@ -97,9 +97,6 @@ attn_varlen_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, c
   __pipeline_commit();
   __pipeline_wait_prior(0);
   __syncthreads();
-  uint32_t qa[D / 16][4];
-#pragma unroll
-  for (int ks = 0; ks < D / 16; ++ks) ldsm4(qa[ks], &sm->q[warp * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
 
   float o_acc[D / 8][4];
 #pragma unroll
@@ -123,16 +120,22 @@ attn_varlen_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, c
     const bool active = !(causal && kv0 > q0 + warp * 16 + 15) && (q0 + warp * 16 < len);
     if (active) {
     // ---- S = Q K^T: 16 rows x 64 keys per warp ----
+    // Q fragments are re-read from shared memory per k-step (two ldmatrix per 16 MMAs) instead of
+    // living in 32 registers: that keeps the kernel at two CTAs per SM
     float s[BN / 8][4];
 #pragma unroll
-    for (int n = 0; n < BN / 8; ++n) {
-      s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
 #pragma unroll
-      for (int ks = 0; ks < D / 16; ks += 2) {
+    for (int ks = 0; ks < D / 16; ks += 2) {
+      uint32_t qa0[4], qa1[4];
+      ldsm4(qa0, &sm->q[warp * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+      ldsm4(qa1, &sm->q[warp * 16 + (lane & 15)][(ks + 1) * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int n = 0; n < BN / 8; ++n) {
         uint32_t kb[4];
         ldsm4(kb, &sm->k[st][n * 8 + (lane & 7)][ks * 16 + (lane >> 3) * 8]);
-        mma16816(s[n], qa[ks], kb[0], kb[1]);
-        mma16816(s[n], qa[ks + 1], kb[2], kb[3]);
+        mma16816(s[n], qa0, kb[0], kb[1]);
+        mma16816(s[n], qa1, kb[2], kb[3]);
       }
     }
     // ---- mask + online softmax (rows row0 and row0+8) ----

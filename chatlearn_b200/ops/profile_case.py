@@ -1,6 +1,6 @@
 """Small, self-ending workloads for profiler captures of single kernels.
 
-    python -m chatlearn_b200.ops.profile_case --kernel gemm|decode|rmsnorm|swiglu|logits|adamw|sample|weight_sync
+    python -m chatlearn_b200.ops.profile_case --kernel gemm|gemm_decode|decode|rmsnorm|swiglu|logits|adamw|sample|attn_fwd|grouped_gemm|moe_router
 
 Each case allocates a few hundred MB (operands larger than the 126 MB L2 so DRAM
 figures mean something), runs 3 warm-up launches and 3 measured launches of ONE
@@ -59,12 +59,41 @@ def main():
         z = torch.randn(128, 151936, device=dev)
         u = torch.rand(128, device=dev)
         fn = lambda: C.sample(z, u, 1.0, -1, 1.0, 0.0)  # noqa: E731
+    elif a.kernel == "attn_fwd":
+        lens = [2730] * 6
+        T, nq, nkv, d = sum(lens), 32, 8, 128
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+        q = torch.randn(T, nq, d, device=dev).bfloat16()
+        k = torch.randn(T, nkv, d, device=dev).bfloat16()
+        v = torch.randn(T, nkv, d, device=dev).bfloat16()
+        fn = lambda: C.attn_varlen_fwd(q, k, v, cu, 1 / math.sqrt(d), True)  # noqa: E731
+    elif a.kernel == "grouped_gemm":
+        # Qwen3-30B-A3B expert up-projection: 128 experts, 16384 tokens x top-8 rows, [1536, 2048] each
+        E, R, N, K = 128, 16384 * 8, 1536, 2048
+        xs = torch.randn(R, K, device=dev).bfloat16()
+        w = (torch.randn(E, N, K, device=dev) * 0.02).bfloat16()
+        cnt = torch.randint(600, 1450, (E,))
+        cnt = (cnt.float() / cnt.sum() * R).long()
+        cnt[-1] += R - cnt.sum()
+        off = torch.zeros(E + 1, dtype=torch.long)
+        off[1:] = cnt.cumsum(0)
+        off = off.to(dev)
+        fn = lambda: C.grouped_gemm_bf16_nt(xs, w, off)  # noqa: E731
+    elif a.kernel == "moe_router":
+        z = torch.randn(131072, 128, device=dev)
+        fn = lambda: C.moe_router_topk(z, 8, False, True, None, 1, 1, 1.0)  # noqa: E731
     else:
         raise SystemExit(f"unknown kernel {a.kernel}")
-    for _ in range(6):
+    for _ in range(3):
         fn()
     torch.cuda.synchronize()
-    print("done", a.kernel)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    print("done", a.kernel, f"{e0.elapsed_time(e1) / 3 * 1e3:.1f} us per call")
 
 
 if __name__ == "__main__":
