@@ -69,6 +69,7 @@ at::Tensor symm_ar_residual_rmsnorm(const std::vector<int64_t>& part_ptrs, const
 at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32);
 void gemm_bf16_nt_out(const at::Tensor& a, const at::Tensor& b, at::Tensor out);
 void gemm_set_tile_n(int64_t bn);
+void gemm_bf16_nt_push(const at::Tensor& a, const at::Tensor& b, at::Tensor out, const std::vector<int64_t>& peer_out);
 int64_t gemm_last_status();
 void gemm_set_splitk(bool on);
 
@@ -110,6 +111,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16_nt", &gemm_bf16_nt);
   m.def("gemm_bf16_nt_out", &gemm_bf16_nt_out);
   m.def("gemm_set_tile_n", &gemm_set_tile_n);
+  m.def("gemm_bf16_nt_push", &gemm_bf16_nt_push);
   m.def("gemm_last_status", &gemm_last_status);
   m.def("gemm_set_splitk", &gemm_set_splitk);
 }

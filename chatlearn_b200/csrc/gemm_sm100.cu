@@ -111,6 +111,10 @@ __device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&
 struct GroupArgs {
   const int4* table = nullptr;
   const int* count = nullptr;
+  // n_peer > 0: the output is stored to these addresses (one per rank of a group, peers' memory
+  // included) instead of C
+  void* peer_out[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int n_peer = 0;
 };
 
 // Origin of a work tile: (first A/C row, first column, first B row of the group, end row).
@@ -236,7 +240,15 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int col = n0 + c;
         if (row < row_end && col < N && !empty_slice) {
           if (splits == 1) {
-            store_row32<OutT>(C + (int64_t)row * ldc + col, r, min(32, N - col));
+            if (grp.n_peer == 0) {
+              store_row32<OutT>(C + (int64_t)row * ldc + col, r, min(32, N - col));
+            } else {
+              // GEMM + all-gather of the partial product: the tile goes straight from tensor memory
+              // into every rank's staging slot (plain stores over NVLink for the peers), while the
+              // MMA warp already works on the next tile in the other accumulator
+              for (int p = 0; p < grp.n_peer; ++p)
+                store_row32<OutT>(static_cast<OutT*>(grp.peer_out[p]) + (int64_t)row * ldc + col, r, min(32, N - col));
+            }
           } else {
             // every k-slice writes its partial tile to its own plane of the workspace;
             // the finalize kernel adds the planes (plain stores: no atomics, deterministic)
@@ -316,7 +328,19 @@ CUtensorMap make_tmap_bf16(const void* ptr, int64_t rows, int64_t cols, int64_t 
 }  // namespace
 
 // a [M, K] bf16 (row stride lda), b [N, K] bf16 -> C [M, N] (bf16, or fp32 when out_fp32)
-static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bool out_fp32, const at::Tensor* out);
+static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bool out_fp32, const at::Tensor* out,
+                                    const std::vector<int64_t>* peer_out = nullptr);
+
+// GEMM whose epilogue stores the [M, N] result to several addresses at once: the copies of a
+// symmetric-memory staging slot on every rank of a tensor-parallel group (this rank's own copy
+// first or anywhere in the list).  `out` is this rank's copy and fixes shape and dtype (bf16).
+void gemm_bf16_nt_push(const at::Tensor& a, const at::Tensor& b, at::Tensor out, const std::vector<int64_t>& peer_out) {
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.dim() == 2 && out.size(0) == a.size(0) && out.size(1) == b.size(0) &&
+              out.scalar_type() == at::kBFloat16, "gemm_bf16_nt_push: out must be contiguous bf16 [M, N]");
+  TORCH_CHECK(!peer_out.empty() && peer_out.size() <= 8, "gemm_bf16_nt_push: 1..8 destinations");
+  for (int64_t p : peer_out) TORCH_CHECK(p % 16 == 0, "gemm_bf16_nt_push: 16-byte aligned destinations");
+  gemm_bf16_nt_impl(a, b, false, &out, &peer_out);
+}
 
 at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32) {
   return gemm_bf16_nt_impl(a, b, out_fp32, nullptr);
@@ -332,7 +356,8 @@ void gemm_bf16_nt_out(const at::Tensor& a, const at::Tensor& b, at::Tensor out) 
   gemm_bf16_nt_impl(a, b, out.scalar_type() == at::kFloat, &out);
 }
 
-static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bool out_fp32, const at::Tensor* out) {
+static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bool out_fp32, const at::Tensor* out,
+                                    const std::vector<int64_t>* peer_out) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16,
               "gemm_bf16_nt: bf16 CUDA tensors");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "gemm_bf16_nt: A [M,K], B [N,K]");
@@ -360,7 +385,7 @@ static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bo
     for (int cand : {256, 128, 64}) {
       const int tiles = tiles_m * (int)((N + cand - 1) / cand);
       int max_s = 1;
-      if (g_allow_splitk && N % 4 == 0 && tiles < num_sms) max_s = std::min({num_sms / tiles, std::max(k_iters / 4, 1), 16});
+      if (g_allow_splitk && N % 4 == 0 && tiles < num_sms && peer_out == nullptr) max_s = std::min({num_sms / tiles, std::max(k_iters / 4, 1), 16});
       for (int s = 1; s <= max_s; ++s) {
         if ((int64_t)s * M * N > kWorkspaceFloats) break;
         const int per = (k_iters + s - 1) / s;
@@ -377,7 +402,7 @@ static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bo
       }
     }
   }
-  if (g_force_bn && g_allow_splitk && N % 4 == 0) {
+  if (g_force_bn && g_allow_splitk && N % 4 == 0 && peer_out == nullptr) {
     const int tiles = tiles_m * (int)((N + bn - 1) / bn);
     if (tiles * 2 <= num_sms) {
       splits = std::min({num_sms / tiles, std::max(k_iters / 4, 1), 16});
@@ -391,12 +416,18 @@ static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bo
   auto st = at::cuda::getCurrentCUDAStream();
   float* ws = splits > 1 ? splitk_workspace(a.get_device(), a.options()) : nullptr;
   const int grid = std::min(tiles * splits, num_sms);
-#define CLB_LAUNCH_GEMM(T, W, PTR)                                                                                    \
+  GroupArgs ga;
+  if (peer_out != nullptr) {
+    TORCH_CHECK(splits == 1, "pushed output needs an unsliced K");
+    ga.n_peer = (int)peer_out->size();
+    for (int i = 0; i < ga.n_peer; ++i) ga.peer_out[i] = reinterpret_cast<void*>((*peer_out)[i]);
+  }
+#define CLB_LAUNCH_GEMM(T, W, PTR)                                                                                   \
   do {                                                                                                                \
     const size_t smem = sizeof(SmemLayoutT<W>) + 1024;                                                                \
     static bool cfg = false;                                                                                          \
     if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<T, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; } \
-    gemm_bf16_nt_kernel<T, W><<<grid, kThreads, smem, st>>>(tmA, tmB, PTR, ws, (int)M, (int)N, (int)K, (int)N, splits, GroupArgs{}); \
+    gemm_bf16_nt_kernel<T, W><<<grid, kThreads, smem, st>>>(tmA, tmB, PTR, ws, (int)M, (int)N, (int)K, (int)N, splits, ga); \
   } while (0)
   if (out_fp32) {
     float* p = c.data_ptr<float>();

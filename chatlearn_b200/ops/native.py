@@ -193,6 +193,19 @@ def linear_out(x2, w, out):
     return out
 
 
+def push_ok(x2, w):
+    return _GEMM_IMPL == "tcgen05" and x2.shape[0] > 0 and _gemm_ok(x2, w)
+
+
+def linear_push(x2, w, out, dst_ptrs):
+    """``x2 @ w.T`` stored by the GEMM epilogue to every address of ``dst_ptrs`` (the copies of a
+    symmetric staging slot on all ranks of a group, peers' memory included); ``out`` is this
+    rank's copy."""
+    _count("gemm_bf16_nt_push")
+    C.gemm_bf16_nt_push(x2, w, out, [int(p) for p in dst_ptrs])
+    return out
+
+
 def gemm_nt(a, b, out_fp32=False):
     """Raw C = A B^T on the tcgen05 kernel (no autograd)."""
     _count("gemm_bf16_nt")

@@ -15,6 +15,7 @@ of these (chatlearn/models/fsdp_module.py:356-394); the NCCL path of
 Synchronisation between ranks happens inside the kernels (flag words, bounded
 waits); the host only launches.
 """
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -44,8 +45,19 @@ class SymmGroup:
         self.flag_ptrs = self._ptrs(self.flags)
         self.staging = symm_mem.empty(staging_bytes // 2, torch.bfloat16, self.device, group=self.pg)
         self.staging_ptrs = self._ptrs(self.staging)
-        # two buffers for row-parallel GEMM partials; consecutive calls alternate between them
-        self.parts = [symm_mem.empty(PART_BYTES // 2, torch.bfloat16, self.device, group=self.pg) for _ in range(2)]
+        # two buffers for row-parallel GEMM partials; consecutive calls alternate between them.
+        # Each buffer has one slot per rank: rank r's GEMM epilogue stores its partial product into
+        # slot r of EVERY rank's buffer (peer stores over NVLink), so the reduction reads local memory.
+        self.slot_elems = PART_BYTES // 2
+        self.parts = [symm_mem.empty(self.world * self.slot_elems, torch.bfloat16, self.device, group=self.pg)
+                      for _ in range(2)]
+        esz = 2
+        self.push_ptrs = [[p + self.rank * self.slot_elems * esz for p in self._ptrs(t)] for t in self.parts]
+        self.slot_ptrs = [[t.data_ptr() + r * self.slot_elems * esz for r in range(self.world)] for t in self.parts]
+        # Measured on two B200 (decode step of 256 sequences, TP=2): pulling (K-sliced GEMM into the local
+        # slot, reduction reads the peer) 13.1 ms; pushing from the GEMM epilogue (no K slicing possible,
+        # stores cross NVLink) 13.8 ms.  Pull is the default; CLB200_TP_PUSH=1 selects the push epilogue.
+        self.push = os.environ.get("CLB200_TP_PUSH", "0") == "1"
         self.part_ptrs = [self._ptrs(t) for t in self.parts]
         self._flip = 0
         torch.cuda.synchronize()
@@ -84,18 +96,26 @@ class SymmGroup:
         idx = self._flip
         self._flip ^= 1
         T, N = x2d.shape[0], w.shape[0]
-        out = self.parts[idx][:T * N].view(T, N)
+        base = self.rank * self.slot_elems
+        out = self.parts[idx][base:base + T * N].view(T, N)           # my slot of my own buffer
+        pushed = self.push and self.native.push_ok(x2d, w)        # same answer on every rank (same shapes)
         if T > 0:
-            self.native.linear_out(x2d, w, out)
-        return idx, out
+            if pushed:
+                self.native.linear_push(x2d, w, out, self.push_ptrs[idx])
+            else:
+                self.native.linear_out(x2d, w, out)
+        return idx, out, pushed
 
     def ar_residual_rmsnorm(self, part, resid: torch.Tensor, w: Optional[torch.Tensor], eps: float):
         """``resid += sum over ranks of the partial``; returns ``rmsnorm(resid) * w`` (``None``
         when ``w`` is ``None``).  One kernel, peers read over NVLink."""
-        idx, out = part
+        idx, out, pushed = part
         assert out.shape == resid.shape
         self.native.launch_counts["symm_ar_residual_rmsnorm"] += 1
-        return self.C.symm_ar_residual_rmsnorm(self.part_ptrs[idx], self.flag_ptrs, self.expect, resid, w,
+        # pushed partials: all slots are in local memory; otherwise read slot r from rank r's buffer
+        ptrs = self.slot_ptrs[idx] if pushed else \
+            [p + r * self.slot_elems * 2 for r, p in enumerate(self.part_ptrs[idx])]
+        return self.C.symm_ar_residual_rmsnorm(ptrs, self.flag_ptrs, self.expect, resid, w,
                                                float(eps), self.rank, NUM_SLOTS)
 
     # ------------------------------------------------------------------ sharded optimizer step

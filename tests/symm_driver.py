@@ -72,6 +72,7 @@ for T in (1, 128, 333):
             ok &= h is None
 sg.begin_forward()
 res["ar_residual_rmsnorm_ok"] = ok
+res["tp_push"] = bool(sg.push)
 
 # device time per reduction inside a CUDA graph (how the decode step runs them): 128 x 4096 bf16
 T = 128
