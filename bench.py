@@ -134,8 +134,10 @@ def build_config(args, out_dir, data_path, n_gpu):
                                    # gradient buffer is released outside training
                                    free_gpu_memory={"offload_weights": False, "offload_optimizer_states": False,
                                                     "free_grad_buffers": offload}),
+            # the frozen reference weights (16 GB) go to pinned host memory between uses only where the
+            # GPU is short of room (1-2 GPUs hold large optimizer shards); from 4 GPUs on they stay resident
             "ref_policy": dict(common, num_gpu=n_gpu, fsdp_size=n_gpu, generation_batch_size=spe,
-                               free_gpu_memory={"offload_weights": offload}),
+                               free_gpu_memory={"offload_weights": offload and n_gpu < 4}),
             "policy": dict(common, num_gpu=n_gpu, tensor_model_parallel_size=tp, generation_batch_size=spe,
                            num_inference_per_prompt=n, temperature=1.0, top_p=1.0, top_k=-1,
                            gpu_memory_utilization=0.94, max_num_seqs=256, kv_block_size=64,
