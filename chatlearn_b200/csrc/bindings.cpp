@@ -52,6 +52,16 @@ void symm_adamw_push(at::Tensor master, const at::Tensor& grad, at::Tensor m, at
                      int64_t lo, bool params_bf16, int64_t step, double lr, double b1, double b2, double eps, double wd,
                      const c10::optional<at::Tensor>& scale, int64_t rank, int64_t num_slots);
 int64_t symm_last_status();
+void grouped_gemm_bf16_nt_table(const at::Tensor& a, const at::Tensor& b, const at::Tensor& table, const at::Tensor& count,
+                                at::Tensor out);
+void symm_moe_barrier(const std::vector<int64_t>& flag_ptrs, at::Tensor expect, int64_t slot, int64_t num_slots, int64_t rank);
+at::Tensor symm_moe_dispatch(const at::Tensor& x, const at::Tensor& idx, const std::vector<int64_t>& recv_x_ptrs,
+                             const std::vector<int64_t>& cursor_ptrs, int64_t experts_per_rank, int64_t capacity);
+std::vector<at::Tensor> symm_moe_region_table(const at::Tensor& cursor, int64_t capacity, int64_t rows_b);
+at::Tensor symm_moe_combine(const std::vector<int64_t>& recv_y_ptrs, const at::Tensor& where, const at::Tensor& weights,
+                            int64_t H, int64_t region_rows);
+void symm_moe_swiglu(const at::Tensor& gu, at::Tensor y, const at::Tensor& table, const at::Tensor& count);
+int64_t symm_moe_last_status();
 bool attn_varlen_fwd_supported(int64_t head_dim);
 std::vector<at::Tensor> attn_varlen_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                         const at::Tensor& cu_seqlens, double scale, bool causal);
@@ -99,6 +109,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_rs_pull_sumsq", &symm_rs_pull_sumsq);
   m.def("symm_adamw_push", &symm_adamw_push);
   m.def("symm_last_status", &symm_last_status);
+  m.def("grouped_gemm_bf16_nt_table", &grouped_gemm_bf16_nt_table);
+  m.def("symm_moe_barrier", &symm_moe_barrier);
+  m.def("symm_moe_dispatch", &symm_moe_dispatch);
+  m.def("symm_moe_region_table", &symm_moe_region_table);
+  m.def("symm_moe_combine", &symm_moe_combine);
+  m.def("symm_moe_swiglu", &symm_moe_swiglu);
+  m.def("symm_moe_last_status", &symm_moe_last_status);
   m.def("attn_varlen_fwd_supported", &attn_varlen_fwd_supported);
   m.def("attn_varlen_fwd", &attn_varlen_fwd);
   m.def("grouped_gemm_bf16_nt", &grouped_gemm_bf16_nt);

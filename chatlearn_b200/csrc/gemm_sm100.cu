@@ -524,6 +524,39 @@ at::Tensor grouped_gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, const 
   return c;
 }
 
+// Grouped GEMM over a caller-built tile table (rows {first, end, first B row, -} as above; `count`
+// on the device), written into `out` [R, N]: used where the groups are regions of a receive
+// buffer rather than back-to-back rows (expert-parallel dispatch into peer memory).
+void grouped_gemm_bf16_nt_table(const at::Tensor& a, const at::Tensor& b, const at::Tensor& table, const at::Tensor& count,
+                                at::Tensor out) {
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16,
+              "grouped_gemm_table: bf16 CUDA tensors");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 3 && a.size(1) == b.size(2) && a.is_contiguous() && b.is_contiguous() && out.is_contiguous(),
+              "grouped_gemm_table: A [R, K], B [G, N, K], contiguous");
+  const int64_t R = a.size(0), K = a.size(1), G = b.size(0), N = b.size(1);
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == R && out.size(1) == N, "grouped_gemm_table: out [R, N]");
+  TORCH_CHECK(table.scalar_type() == at::kInt && table.dim() == 2 && table.size(1) == 4 && count.scalar_type() == at::kInt,
+              "grouped_gemm_table: int32 table [tiles, 4] and count");
+  TORCH_CHECK(K % 8 == 0 && N % 8 == 0 && K > 0, "grouped_gemm_table: K and N must be multiples of 8");
+  const int capacity = (int)table.size(0);
+  if (R == 0 || capacity == 0) return;
+  auto st = at::cuda::getCurrentCUDAStream();
+  CUtensorMap tmA = make_tmap_bf16(a.data_ptr(), R, K, K, BM);
+  CUtensorMap tmB = make_tmap_bf16(b.data_ptr(), G * N, K, K, BN);
+  static int num_sms = 0;
+  if (!num_sms) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, a.get_device());
+  const size_t smem = sizeof(SmemLayout) + 1024;
+  static bool cfg = false;
+  if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
+  const int tiles_n = (int)((N + BN - 1) / BN);
+  const int grid = std::min(capacity * tiles_n, num_sms);
+  GroupArgs g;
+  g.table = reinterpret_cast<const int4*>(table.data_ptr<int>());
+  g.count = count.data_ptr<int>();
+  gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, (bf16*)out.data_ptr(), nullptr, capacity * BM, (int)N,
+                                                         (int)K, (int)N, 1, g);
+}
+
 // ----------------------------------------------------------------------------
 // Allocation-free entry point (see gemm_noalloc.h): same kernel, split-K planes in a
 // fixed file-scope device array instead of a workspace from the allocator.

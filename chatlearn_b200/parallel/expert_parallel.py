@@ -24,7 +24,7 @@ class ExpertParallel:
         """``x [T,H]``; ``w13/w2`` hold this rank's ``E/ep`` experts; ``idx`` are
         global expert ids.  Returns the combined expert output ``[T,H]``."""
         fast = self.group.fast.get("moe_dispatch_combine")
-        if fast is not None and x.is_cuda:
+        if fast is not None and x.is_cuda and not torch.is_grad_enabled() and x.dtype == torch.bfloat16:
             return fast(x, w13, w2, weights, idx, num_experts)
         ep = self.size
         El = num_experts // ep

@@ -65,6 +65,20 @@ class RolloutEngine:
             self.tp_symm = symm_collectives.get(tp_group)
             if self.tp_symm is not None:
                 tp_group.fast["all_reduce"] = self.tp_symm.all_reduce
+        # expert-parallel dispatch / combine through peer memory instead of NCCL all-to-all
+        self.ep_symm = None
+        epg = getattr(ep_group, "group", None)
+        if epg is not None and epg.size > 1 and self.device.type == "cuda" and ops.get_mode() == "native" \
+                and self.arch.num_experts and self.arch.num_experts % epg.size == 0 \
+                and os.environ.get("CLB200_SYMM_EP", "0") == "1":      # opt-in until validated on more than two GPUs
+            from chatlearn_b200.parallel import symm_mem
+            if symm_mem.available() and epg.size <= 8:
+                from chatlearn_b200.parallel.symm_moe import SymmMoE
+                self.ep_symm = SymmMoE(epg, self.arch.num_experts, self.arch.hidden_size)
+                pairs = int(max_num_batched_tokens) * int(self.arch.num_experts_per_tok)
+                moe = self.ep_symm
+                epg.fast["moe_dispatch_combine"] = \
+                    lambda x, w13, w2, w, idx, E: moe.experts(x, w13, w2, w, idx, pairs_per_rank=pairs)
         self.block_size = block_size
         self.max_num_seqs = max_num_seqs
         self.max_tokens = max_num_batched_tokens
@@ -412,6 +426,13 @@ class RolloutEngine:
             tm[kind + "_steps"] += 1
         self.stats = dict(sched.stats)
         self.stats.update(tm)
+        if self.ep_symm is not None:
+            st = self.ep_symm.status()
+            if st:
+                raise RuntimeError(
+                    f"expert-parallel peer-memory dispatch reported status {st} "
+                    "(1: a peer did not arrive within the wait limit, 2: an expert's receive region overflowed; "
+                    "raise the capacity factor or set CLB200_SYMM_EP=0)")
         return seqs
 
     # ------------------------------------------------------------------ sleep / wake

@@ -189,6 +189,31 @@ res["zero_state_mismatch_frac"], res["zero_state_max_diff"] = mism / tot, maxd
 res["zero_state_ok"] = mism / tot < 1e-2 and maxd < 1e-3 and all(abs(a - b) <= 1e-4 * abs(b) for a, b in norms)
 res["zero_state_status"] = sg.status()
 
+# ---- expert-parallel MoE layer through peer memory (dispatch with remote atomics, pull combine) ----
+from chatlearn_b200.parallel.symm_moe import SymmMoE  # noqa: E402
+
+E, Hm, Fm, kk = 8, 256, 128, 2
+El = E // world
+torch.manual_seed(77)
+w13_all = (torch.randn(E, 2 * Fm, Hm, device=dev) * 0.05).bfloat16()
+w2_all = (torch.randn(E, Hm, Fm, device=dev) * 0.05).bfloat16()
+moe = SymmMoE(g, E, Hm)
+ok = True
+for step, Tm in enumerate((64, 300, 17)):
+    torch.manual_seed(900 + 10 * step + rank)
+    xm = torch.randn(Tm, Hm, device=dev).bfloat16()
+    wts, idxm, _ = ref.moe_router(torch.randn(Tm, E, device=dev), kk)
+    got = moe.experts(xm, w13_all[rank * El:(rank + 1) * El].contiguous(), w2_all[rank * El:(rank + 1) * El].contiguous(),
+                      wts, idxm, pairs_per_rank=300 * kk)
+    want = ref.moe_experts(xm.float(), w13_all.float(), w2_all.float(), wts, idxm)
+    torch.cuda.synchronize()
+    rel = float((got.float() - want).norm() / want.norm())
+    ok &= rel < 2e-2
+    res[f"symm_moe_rel_err_{Tm}"] = round(rel, 5)
+dist.barrier()
+res["symm_moe_ok"] = ok
+res["symm_moe_status"] = moe.status()
+
 # ---- weight sync: pull fp32 ZeRO shards from the peer into the rollout TP layout (bf16) ----
 from chatlearn_b200.models.nn import PRESETS, CausalLM  # noqa: E402
 from chatlearn_b200.parallel import symm_mem  # noqa: E402

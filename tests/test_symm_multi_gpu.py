@@ -22,7 +22,7 @@ def test_symm_collectives_two_gpus():
     lines = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")]
     assert p.returncode == 0 and lines, p.stdout[-2000:] + p.stderr[-2000:]
     r = json.loads(lines[-1][7:])
-    for key in ("allreduce_ok", "ar_residual_rmsnorm_ok", "zero_step_ok", "zero_state_symm_enabled", "zero_state_ok",
+    for key in ("allreduce_ok", "ar_residual_rmsnorm_ok", "zero_step_ok", "zero_state_symm_enabled", "zero_state_ok", "symm_moe_ok",
                 "weight_sync_ok"):
         assert r[key], (key, r)
-    assert r["status"] == 0 and r["status_after_graph"] == 0 and r["zero_state_status"] == 0
+    assert r["status"] == 0 and r["status_after_graph"] == 0 and r["zero_state_status"] == 0 and r["symm_moe_status"] == 0
