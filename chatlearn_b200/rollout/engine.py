@@ -70,7 +70,7 @@ class RolloutEngine:
         epg = getattr(ep_group, "group", None)
         if epg is not None and epg.size > 1 and self.device.type == "cuda" and ops.get_mode() == "native" \
                 and self.arch.num_experts and self.arch.num_experts % epg.size == 0 \
-                and os.environ.get("CLB200_SYMM_EP", "0") == "1":      # opt-in until validated on more than two GPUs
+                and os.environ.get("CLB200_SYMM_EP", "1") != "0":
             from chatlearn_b200.parallel import symm_mem
             if symm_mem.available() and epg.size <= 8:
                 from chatlearn_b200.parallel.symm_moe import SymmMoE

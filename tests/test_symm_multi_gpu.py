@@ -26,3 +26,18 @@ def test_symm_collectives_two_gpus():
                 "weight_sync_ok"):
         assert r[key], (key, r)
     assert r["status"] == 0 and r["status_after_graph"] == 0 and r["zero_state_status"] == 0 and r["symm_moe_status"] == 0
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_rollout_paths_agree():
+    outs = {}
+    for flag in ("0", "1"):
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0", CLB200_SYMM_EP=flag)
+        p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                            "--master-addr", "127.0.0.1", "--master-port", "29643", os.path.join(ROOT, "tests", "ep_rollout_driver.py")],
+                           capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+        res = [json.loads(l[7:]) for l in p.stdout.splitlines() if l.startswith("RESULT ")]
+        assert p.returncode == 0 and len(res) == 2, p.stdout[-2000:] + p.stderr[-2000:]
+        outs[flag] = {r["rank"]: r for r in res}
+    assert all(outs["1"][r]["symm_ep"] and not outs["0"][r]["symm_ep"] for r in (0, 1))
+    assert all(outs["1"][r]["checksum"] == outs["0"][r]["checksum"] for r in (0, 1))
