@@ -77,7 +77,8 @@ class PolicyTrainer(FSDPModule):
         """Device tensors + forward context of a packed row (Ulysses-split if sp>1)."""
         batch.to(self.device)
         tokens, positions = batch.tokens, batch.positions
-        ctx = FwdCtx(positions=positions, cu_seqlens=batch.cu_seqlens, max_seqlen=batch.max_seqlen)
+        ctx = FwdCtx(positions=positions, cu_seqlens=batch.cu_seqlens, max_seqlen=batch.max_seqlen,
+                     fuse_add_norm=not torch.is_grad_enabled())
         labels = batch.labels
         if self.sp is not None:
             ctx.sp = self.sp

@@ -52,6 +52,7 @@ void symm_adamw_push(at::Tensor master, const at::Tensor& grad, at::Tensor m, at
                      int64_t lo, bool params_bf16, int64_t step, double lr, double b1, double b2, double eps, double wd,
                      const c10::optional<at::Tensor>& scale, int64_t rank, int64_t num_slots);
 int64_t symm_last_status();
+at::Tensor add_residual_rmsnorm(at::Tensor resid, const at::Tensor& delta, const c10::optional<at::Tensor>& w, double eps);
 void grouped_gemm_bf16_nt_table(const at::Tensor& a, const at::Tensor& b, const at::Tensor& table, const at::Tensor& count,
                                 at::Tensor out);
 void symm_moe_barrier(const std::vector<int64_t>& flag_ptrs, at::Tensor expect, int64_t slot, int64_t num_slots, int64_t rank);
@@ -109,6 +110,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_rs_pull_sumsq", &symm_rs_pull_sumsq);
   m.def("symm_adamw_push", &symm_adamw_push);
   m.def("symm_last_status", &symm_last_status);
+  m.def("add_residual_rmsnorm", &add_residual_rmsnorm);
   m.def("grouped_gemm_bf16_nt_table", &grouped_gemm_bf16_nt_table);
   m.def("symm_moe_barrier", &symm_moe_barrier);
   m.def("symm_moe_dispatch", &symm_moe_dispatch);

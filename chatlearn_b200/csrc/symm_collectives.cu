@@ -319,6 +319,34 @@ at::Tensor symm_ar_residual_rmsnorm(const std::vector<int64_t>& part_ptrs, const
   return hout;
 }
 
+// Single-rank form of the kernel above: resid += delta; returns rmsnorm(resid) * w (undefined when w is absent).
+at::Tensor add_residual_rmsnorm(at::Tensor resid, const at::Tensor& delta, const c10::optional<at::Tensor>& w, double eps) {
+  TORCH_CHECK(resid.scalar_type() == at::kBFloat16 && resid.is_contiguous() && resid.dim() == 2, "resid: contiguous bf16 [T, H]");
+  TORCH_CHECK(delta.scalar_type() == at::kBFloat16 && delta.is_contiguous() && delta.sizes() == resid.sizes(), "delta: same shape as resid");
+  const int T = (int)resid.size(0), H = (int)resid.size(1);
+  TORCH_CHECK(H % 8 == 0 && H <= 256 * 8 * 4, "hidden size must be a multiple of 8 and at most 8192");
+  at::Tensor hout;
+  const bf16* wp = nullptr;
+  if (w.has_value()) {
+    TORCH_CHECK(w->scalar_type() == at::kBFloat16 && w->numel() == H && w->is_contiguous(), "w: bf16 [H]");
+    hout = at::empty_like(resid);
+    wp = (const bf16*)w->data_ptr();
+  }
+  if (T == 0) return hout;
+  PeerTable parts, flags;
+  for (int i = 0; i < kMaxWorld; ++i) { parts.ptr[i] = nullptr; flags.ptr[i] = nullptr; }
+  parts.ptr[0] = delta.data_ptr();
+  const int grid = std::min(T, 148 * 4);
+  const int vpt = (H / 8 + 255) / 256;
+  auto st = at::cuda::getCurrentCUDAStream();
+  bf16* hp = hout.defined() ? (bf16*)hout.data_ptr() : nullptr;
+  // world = 1: the barrier inside the kernel touches neither the flag table nor the counters
+  if (vpt <= 1) ar_residual_rmsnorm_kernel<1><<<grid, 256, 0, st>>>(parts, flags, nullptr, (bf16*)resid.data_ptr(), wp, hp, T, H, (float)eps, 0, 1, 1, 0);
+  else if (vpt == 2) ar_residual_rmsnorm_kernel<2><<<grid, 256, 0, st>>>(parts, flags, nullptr, (bf16*)resid.data_ptr(), wp, hp, T, H, (float)eps, 0, 1, 1, 0);
+  else ar_residual_rmsnorm_kernel<4><<<grid, 256, 0, st>>>(parts, flags, nullptr, (bf16*)resid.data_ptr(), wp, hp, T, H, (float)eps, 0, 1, 1, 0);
+  return hout;
+}
+
 int64_t symm_last_status() {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_symm_status, sizeof(int));

@@ -144,7 +144,8 @@ class FwdCtx:
     aux_losses: List[torch.Tensor] = field(default_factory=list)
     moe_stats: List[torch.Tensor] = field(default_factory=list)
     tp_symm: Any = None                    # parallel.symm_collectives.SymmGroup of the TP group (inference)
-    pending: Any = None                    # un-reduced TP partial not yet folded into the residual stream
+    pending: Any = None                    # sub-layer output (or un-reduced TP partial) not yet added to the residual stream
+    fuse_add_norm: bool = False            # inference: fuse residual adds with the following RMSNorm (in-place stream)
 
 
 def _tp_reduce(x, ctx):
@@ -290,13 +291,34 @@ def flush_pending(x, ctx: FwdCtx, norm_w=None, eps: float = 1e-6):
     """Fold a pending tensor-parallel partial into ``x``; returns ``rmsnorm(x)`` when
     ``norm_w`` is given, else ``x``."""
     part, ctx.pending = ctx.pending, None
-    h = ctx.tp_symm.ar_residual_rmsnorm(part, x, norm_w, eps)
+    if torch.is_tensor(part):          # a local (already complete) sub-layer output
+        h = ops.add_rmsnorm_(x, part, norm_w, eps)
+    else:
+        h = ctx.tp_symm.ar_residual_rmsnorm(part, x, norm_w, eps)
     return x if norm_w is None else h
+
+
+def _decoder_layer_infer_fused(arch: ModelArch, p, x, ctx: FwdCtx, layer: int):
+    """Inference on CUDA without tensor-parallel partials: every residual add is fused with
+    the RMSNorm that follows it (the MLP output stays pending for the next layer's norm),
+    and the residual stream is updated in place."""
+    eps = arch.rms_norm_eps
+    if ctx.pending is not None:
+        h = flush_pending(x, ctx, p["input_layernorm"], eps)
+    else:
+        h = ops.rmsnorm(x, p["input_layernorm"], eps)
+    a = attention_block(arch, p, h, ctx, layer)
+    h = ops.add_rmsnorm_(x, a, p["post_attention_layernorm"], eps)
+    ctx.pending = moe_block(arch, p, h, ctx) if "router" in p else _tp_reduce(dense_mlp(p, h, ctx), ctx)
+    return x
 
 
 def decoder_layer(arch: ModelArch, p, x, ctx: FwdCtx, layer: int):
     if _tp_fused_ok(p, x, ctx):
         return _decoder_layer_tp_fused(arch, p, x, ctx, layer)
+    if ctx.fuse_add_norm and not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16 \
+            and x.dim() == 2 and x.is_contiguous():
+        return _decoder_layer_infer_fused(arch, p, x, ctx, layer)
     if ctx.pending is not None:
         x = flush_pending(x, ctx)
     h = ops.rmsnorm(x, p["input_layernorm"], arch.rms_norm_eps)

@@ -82,6 +82,7 @@ def _dispatch(name):
 
 
 rmsnorm = _dispatch("rmsnorm")
+add_rmsnorm_ = _dispatch("add_rmsnorm_")
 swiglu = _dispatch("swiglu")
 linear = _dispatch("linear")
 rope = _dispatch("rope")

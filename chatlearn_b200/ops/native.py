@@ -66,6 +66,18 @@ def rmsnorm(x, w, eps):
     return _RMSNorm.apply(x, w, eps)
 
 
+@torch.no_grad()
+def add_rmsnorm_(resid, delta, w, eps):
+    """Residual add + RMSNorm in one pass (inference): ``resid += delta`` in place, returns the norm."""
+    H = resid.shape[-1]
+    if (resid.dtype != torch.bfloat16 or delta.dtype != torch.bfloat16 or resid.dim() != 2 or H % 8 or H > 8192
+            or not resid.is_contiguous() or (w is not None and w.dtype != torch.bfloat16)):
+        library_counts["add_rmsnorm_"] += 1
+        return ref.add_rmsnorm_(resid, delta, w, eps)
+    _count("add_residual_rmsnorm")
+    return C.add_residual_rmsnorm(resid, delta.contiguous(), w, float(eps))
+
+
 # ------------------------------------------------------------------ swiglu
 class _SwiGLU(torch.autograd.Function):
     @staticmethod
@@ -405,7 +417,7 @@ def weight_sync_run(desc_table, num_descs, total_tiles, src_dtype, dst_dtype):
     _count("weight_sync")
 
 
-for _name, _fn in (("rmsnorm", rmsnorm), ("swiglu", swiglu), ("qk_norm_rope", qk_norm_rope), ("rope", rope),
+for _name, _fn in (("rmsnorm", rmsnorm), ("add_rmsnorm_", add_rmsnorm_), ("swiglu", swiglu), ("qk_norm_rope", qk_norm_rope), ("rope", rope),
                    ("linear", linear), ("lmhead_logprob_entropy", lmhead_logprob_entropy),
                    ("grpo_loss_fused", grpo_loss_fused), ("adamw_step", adamw_step), ("sumsq", sumsq),
                    ("sample", sample), ("apply_penalties", apply_penalties), ("kv_append", kv_append),

@@ -20,6 +20,14 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return (y * w.float()).to(x.dtype)
 
 
+@torch.no_grad()
+def add_rmsnorm_(resid: torch.Tensor, delta: torch.Tensor, w, eps: float):
+    """In place ``resid += delta``; returns ``rmsnorm(resid) * w`` (``None`` when ``w`` is ``None``).
+    Inference only: the residual stream is updated in place."""
+    resid.add_(delta)
+    return rmsnorm(resid, w, eps) if w is not None else None
+
+
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     """``[..., 2F] -> [..., F]``: silu(first half) * second half."""
     g, u = gate_up.float().chunk(2, dim=-1)

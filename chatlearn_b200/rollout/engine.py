@@ -181,7 +181,7 @@ class RolloutEngine:
         kv = KVCtx(self.k_cache, self.v_cache, t(slots, torch.long, "slots"), xfer.to_device(bt, dev, "bt"),
                    t(seq_lens, torch.int32, "seq_lens"), t(plan.q_lens, torch.int32, "q_lens"), plan.is_prefill)
         ctx = FwdCtx(positions=t(pos, torch.long, "pos"), cu_seqlens=t(cu, torch.int32, "cu"),
-                     max_seqlen=max(plan.q_lens), kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm())
+                     max_seqlen=max(plan.q_lens), kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm(), fuse_add_norm=True)
         return t(toks, torch.long, "toks"), ctx, t(last_rows, torch.long, "last")
 
     def _symm(self):
@@ -225,7 +225,7 @@ class RolloutEngine:
     def _decode_body(self, B: int, sp):
         gs = self._gs
         kv = KVCtx(self.k_cache, self.v_cache, gs["slots"][:B], gs["bt"][:B], gs["seq_lens"][:B], None, False)
-        ctx = FwdCtx(positions=gs["pos"][:B], cu_seqlens=None, max_seqlen=1, kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm())
+        ctx = FwdCtx(positions=gs["pos"][:B], cu_seqlens=None, max_seqlen=1, kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm(), fuse_add_norm=True)
         hidden = self.model.hidden_states(gs["tokens"][:B], ctx)
         logits = self._logits(hidden)
         ids, lp = ops.sample(logits, gs["u"][:B], sp.temperature, sp.top_k, sp.top_p, sp.min_p)
@@ -372,7 +372,7 @@ class RolloutEngine:
         kv = KVCtx(self.k_cache, self.v_cache, z(torch.long), torch.zeros(0, 1, dtype=torch.int32, device=dev),
                    z(torch.int32), z(torch.int32), True)
         ctx = FwdCtx(positions=z(torch.long), cu_seqlens=torch.zeros(1, dtype=torch.int32, device=dev),
-                     max_seqlen=0, kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm())
+                     max_seqlen=0, kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm(), fuse_add_norm=True)
         self.model.hidden_states(z(torch.long), ctx)
 
     # ------------------------------------------------------------------ public
