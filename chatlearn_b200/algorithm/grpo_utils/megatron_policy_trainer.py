@@ -69,6 +69,15 @@ class MegatronPolicyTrainer(MegatronModule):
     def _send(self, t: torch.Tensor, to_stage: int):
         dist.send(t.contiguous(), self.pp_group.ranks[to_stage], group=self.pp_group.pg)
 
+    def _exchange(self, send_t: torch.Tensor, to_stage: int, shape, dtype, from_stage: int) -> torch.Tensor:
+        """Send one tensor and receive another with both transfers posted together."""
+        out = torch.empty(tuple(shape), dtype=dtype, device=self.device)
+        ops_ = [dist.P2POp(dist.isend, send_t.contiguous(), self.pp_group.ranks[to_stage], self.pp_group.pg),
+                dist.P2POp(dist.irecv, out, self.pp_group.ranks[from_stage], self.pp_group.pg)]
+        for req in dist.batch_isend_irecv(ops_):
+            req.wait()
+        return out
+
     def _recv(self, shape, dtype, from_stage: int) -> torch.Tensor:
         t = torch.empty(shape, dtype=dtype, device=self.device)
         dist.recv(t, self.pp_group.ranks[from_stage], group=self.pp_group.pg)
@@ -167,39 +176,80 @@ class MegatronPolicyTrainer(MegatronModule):
         stats = torch.zeros(6, dtype=torch.float32, device=self.device)
         mbs = [self._prepare(mb) for mb in self._microbatches(data_list, for_train=True)]
         mbs = [m for m in mbs if m[0] is not None]
-        # schedule: forward every micro-batch through the stages, then backward in reverse
-        # order (activations of a stage are alive between its forward and backward);
-        # the stage boundary tensors travel over NCCL point-to-point
-        pending = []
-        for batch, ctx, local in mbs:
-            n_local = self._local_tokens(batch, local)
-            x_in = None
-            if not self.is_first_stage:
-                x_in = self._recv((n_local, H), self.compute_dtype, self.pp_rank - 1).requires_grad_(True)
+        # schedule: one-forward-one-backward.  Stage r first runs (stages - r - 1) forwards, then
+        # alternates a forward with the backward of its oldest micro-batch in flight, then drains;
+        # at most (stages - r) micro-batches keep their activations on a stage instead of all of
+        # them.  The stage boundary tensors travel over NCCL point-to-point; on every pair of
+        # neighbours both sides issue "activation k, then gradient j" in the same order.
+        from collections import deque
+        in_flight = deque()
+
+        prev, nxt = self.pp_rank - 1, self.pp_rank + 1
+        first, last = self.is_first_stage, self.is_last_stage
+
+        def compute_forward(batch, ctx, local, x_in):
+            nonlocal stats
             out = self._stage_forward(batch, ctx, local, x_in)
-            if self.is_last_stage:
+            if last:
                 lp, ent = out
                 loss, s = self._loss(batch, local, lp, ent, inv_norm)
                 for aux in ctx.aux_losses:
                     loss = loss + aux * (batch.loss_mask.sum() * inv_norm)
                 stats += s.detach()
-                pending.append((loss, x_in, None))
-            else:
-                self._send(out.detach(), self.pp_rank + 1)
-                # auxiliary (router) losses of intermediate stages are back-propagated locally
-                aux = sum(ctx.aux_losses) * (batch.loss_mask.sum() * inv_norm) if ctx.aux_losses else None
-                pending.append((out, x_in, aux))
-        for out, x_in, aux in reversed(pending):
-            if self.is_last_stage:
+                return loss, x_in, None
+            # auxiliary (router) losses of intermediate stages are back-propagated locally
+            aux = sum(ctx.aux_losses) * (batch.loss_mask.sum() * inv_norm) if ctx.aux_losses else None
+            return out, x_in, aux
+
+        def compute_backward(out, x_in, aux, g):
+            if last:
                 out.backward()
+            elif aux is not None:
+                torch.autograd.backward([out, aux], [g, torch.ones_like(aux)])
             else:
-                g = self._recv(out.shape, out.dtype, self.pp_rank + 1)
-                if aux is not None:
-                    torch.autograd.backward([out, aux], [g, torch.ones_like(aux)])
-                else:
-                    out.backward(g)
-            if x_in is not None:
-                self._send(x_in.grad, self.pp_rank - 1)
+                out.backward(g)
+            return x_in.grad if x_in is not None else None
+
+        def in_shape(k):
+            return (self._local_tokens(mbs[k][0], mbs[k][2]), H)
+
+        n_mb = len(mbs)
+        warm = min(self.pp_size - self.pp_rank - 1, n_mb)
+        steady = n_mb - warm
+        # warm-up: forwards only
+        for k in range(warm):
+            x_in = None if first else self._recv(in_shape(k), self.compute_dtype, prev).requires_grad_(True)
+            item = compute_forward(*mbs[k], x_in)
+            if not last:
+                self._send(item[0].detach(), nxt)
+            in_flight.append(item)
+        # steady state: the activation of the new micro-batch and the gradient of the oldest one cross
+        # a stage boundary in ONE exchange (both directions posted together), so neighbours never
+        # wait on each other's sends
+        x_in = None
+        if steady > 0 and not first:
+            x_in = self._recv(in_shape(warm), self.compute_dtype, prev).requires_grad_(True)
+        for t in range(steady):
+            k = warm + t
+            item = compute_forward(*mbs[k], x_in)
+            in_flight.append(item)
+            old = in_flight.popleft()
+            g = None
+            if not last:
+                g = self._exchange(item[0].detach(), nxt, old[0].shape, old[0].dtype, nxt)
+            dx = compute_backward(*old, g)
+            if t + 1 < steady:
+                x_in = None if first else \
+                    self._exchange(dx, prev, in_shape(k + 1), self.compute_dtype, prev).requires_grad_(True)
+            elif not first:
+                self._send(dx, prev)
+        # cool-down: backwards only
+        while in_flight:
+            old = in_flight.popleft()
+            g = None if last else self._recv(old[0].shape, old[0].dtype, nxt)
+            dx = compute_backward(*old, g)
+            if not first:
+                self._send(dx, prev)
         grad_norm = st.step()
         # metrics live on the last stage; share them with the whole model-parallel group
         if self.pp_size > 1:
