@@ -83,3 +83,18 @@ def test_grpo_tiny_packing_tp2(tmp_path):
     outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "PACKING": "1", "TP": "2", "EPISODES": "1"})
     res = _results(outs)
     assert len(res) == 2 and all(r["maxdiff"] == 0.0 for r in res)
+
+
+def test_resume_continues_from_checkpoint(tmp_path):
+    """One episode with checkpoints, then a fresh job over the same output directory: it resumes the data
+    position and the trainer state and runs only the remaining episode."""
+    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "EPISODES": "1"})
+    first = _results(outs)
+    assert all(r["episodes"] == 1 and r["consumed"] == 32 for r in first)
+    outs, logs = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "EPISODES": "2"})
+    second = _results(outs)
+    assert len(second) == 2
+    for r in second:
+        assert r["episodes"] == 1, "only the second episode runs after the resume"
+        assert r["consumed"] == 64 and r["maxdiff"] == 0.0
+    assert (tmp_path / "save_model" / "policy_trainer" / "2").exists()
