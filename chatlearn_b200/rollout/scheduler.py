@@ -130,9 +130,15 @@ class Scheduler:
                 break
             seqs.append(s); q_lens.append(n); samples.append(n == todo)
             budget -= n
-        while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs:
+        # A step is either all "fresh" (every sequence starts at position 0: packed attention over the
+        # step's own keys) or all continuation chunks (attention over the paged cache): new prompts are
+        # not admitted next to a continuation, and a prompt is only cut when it can never fit whole.
+        fresh_ok = not seqs
+        while fresh_ok and self.waiting and budget > 0 and len(self.running) < self.max_num_seqs:
             s = self.waiting[0]
             todo = s.length - s.num_computed
+            if todo > budget and seqs:
+                break
             n = min(todo, budget)
             # keep one block of head-room per running sequence so decode can proceed
             if self.alloc.blocks_for(s.num_computed + n) - len(s.blocks) > \

@@ -224,3 +224,28 @@ def test_safetensors_roundtrip_sharded_and_tp_load(tmp_path):
         want = CausalLM(arch, dtype=torch.float32, tp=2, tp_rank=r)
         want.load_hf_state_dict(sd)
         assert all(torch.equal(a.flat, b.flat) for a, b in zip(part.blocks, want.blocks))
+
+
+def test_scheduler_never_mixes_fresh_prompts_with_continuation_chunks():
+    from chatlearn_b200.rollout.scheduler import Scheduler, Sequence
+    sch = Scheduler(num_blocks=64, block_size=4, max_num_seqs=8, max_num_batched_tokens=16)
+    seqs = [Sequence(0, list(range(40)), 3), Sequence(1, list(range(10)), 3), Sequence(2, list(range(12)), 3)]
+    for q in seqs:
+        sch.add(q)
+    for _ in range(200):
+        if not sch.has_work():
+            break
+        plan = sch.schedule()
+        starts = [q.num_computed for q in plan.seqs]
+        prefilling = [n > 1 for n in plan.q_lens]
+        if any(prefilling):
+            # all at position 0 (packed attention) or all continuations (paged attention)
+            assert all(s == 0 for s in starts) or all(s > 0 for s in starts)
+            assert plan.is_prefill == all(s == 0 for s in starts)
+        for q, n, smp in zip(plan.seqs, plan.q_lens, plan.samples):
+            q.num_computed += n
+            if smp:
+                q.output.append(1)
+                if len(q.output) >= q.max_new_tokens:
+                    sch.finish(q, "length")
+    assert all(q.finished for q in seqs)
