@@ -105,8 +105,15 @@ class Executor:
                     else:
                         model.onload()
             model.timers(node.func_name).start()
-            with span(f"{tname}.compute"):
-                res = fn(chunk, iteration, **kwargs) if node.func_name != "train_step" else fn(chunk, **kwargs)
+            nvtx = bool(getattr(model.runtime_args, "nsys", False)) and torch.cuda.is_available()
+            if nvtx:                       # named ranges for timeline profilers (decorator.py:58-59,71-72)
+                torch.cuda.nvtx.range_push(tname)
+            try:
+                with span(f"{tname}.compute"):
+                    res = fn(chunk, iteration, **kwargs) if node.func_name != "train_step" else fn(chunk, **kwargs)
+            finally:
+                if nvtx:
+                    torch.cuda.nvtx.range_pop()
             model.timers(node.func_name).stop()
             if res is not None:
                 out.extend(res)
