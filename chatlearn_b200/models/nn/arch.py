@@ -9,7 +9,7 @@ same HF keys are read directly.
 import json
 import os
 from dataclasses import asdict, dataclass, field
-from typing import Any, Dict, Optional
+from typing import Any, Dict, List, Optional
 
 
 @dataclass
@@ -48,6 +48,10 @@ class ModelArch:
     qk_nope_head_dim: int = 0
     qk_rope_head_dim: int = 0
     v_head_dim: int = 0
+    # vision-language models: rotary sections (time, row, column) and the vision tower's config
+    mrope_section: Optional[List[int]] = None
+    vision_config: Optional[Dict[str, Any]] = None
+    image_token_id: Optional[int] = None
     # reward-model head
     num_labels: int = 0                  # >0: scalar/value head instead of lm_head
     bos_token_id: Optional[int] = None
@@ -123,6 +127,17 @@ class ModelArch:
     def from_hf_dict(cls, d: Dict[str, Any]) -> "ModelArch":
         known = {f for f in cls.__dataclass_fields__}  # pylint: disable=no-member
         kw, extra = {}, {}
+        if isinstance(d.get("text_config"), dict):
+            # vision-language checkpoints nest the language model's settings
+            outer = {k: v for k, v in d.items() if k != "text_config"}
+            d = {**outer, **d["text_config"]}
+            d["model_type"] = {"qwen2_5_vl": "qwen2", "qwen2_5_vl_text": "qwen2", "qwen2_vl": "qwen2",
+                               "qwen3_vl": "qwen3", "qwen3_vl_text": "qwen3"}.get(d.get("model_type"), d.get("model_type"))
+        rs = d.get("rope_scaling") or d.get("rope_parameters") or {}
+        if isinstance(rs, dict) and rs.get("mrope_section"):
+            d = dict(d, mrope_section=list(rs["mrope_section"]))
+            if "rope_theta" in rs and "rope_theta" not in d:
+                d["rope_theta"] = rs["rope_theta"]
         for k, v in d.items():
             k = cls._HF_ALIASES.get(k, k)
             if k in known and k != "extra":

@@ -146,6 +146,7 @@ class FwdCtx:
     tp_symm: Any = None                    # parallel.symm_collectives.SymmGroup of the TP group (inference)
     pending: Any = None                    # sub-layer output (or un-reduced TP partial) not yet added to the residual stream
     fuse_add_norm: bool = False            # inference: fuse residual adds with the following RMSNorm (in-place stream)
+    mrope_positions: Optional[torch.Tensor] = None   # [3, T] time/row/column positions (vision-language models)
 
 
 def _tp_reduce(x, ctx):
@@ -192,9 +193,16 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
         if ctx.sp is not None and ctx.sp.size > 1:
             # Ulysses: trade the sequence split for a head split around attention
             q, k, v = ctx.sp.seq_to_heads(q), ctx.sp.seq_to_heads(k, kv=True), ctx.sp.seq_to_heads(v, kv=True)
-        q, k = ops.qk_norm_rope(q, k, p.get("q_norm"), p.get("k_norm"), arch.rms_norm_eps,
-                                ctx.attn_positions if ctx.attn_positions is not None else ctx.positions,
-                                arch.rope_theta)
+        if ctx.mrope_positions is not None:
+            # vision-language models: time / row / column positions per rotary section
+            if p.get("q_norm") is not None:
+                q, k = ops.rmsnorm(q, p["q_norm"], arch.rms_norm_eps), ops.rmsnorm(k, p["k_norm"], arch.rms_norm_eps)
+            q = ops.rope_mrope(q, ctx.mrope_positions, arch.rope_theta, arch.mrope_section)
+            k = ops.rope_mrope(k, ctx.mrope_positions, arch.rope_theta, arch.mrope_section)
+        else:
+            q, k = ops.qk_norm_rope(q, k, p.get("q_norm"), p.get("k_norm"), arch.rms_norm_eps,
+                                    ctx.attn_positions if ctx.attn_positions is not None else ctx.positions,
+                                    arch.rope_theta)
     kv = ctx.kv
     if kv is not None:
         ops.kv_append(k, v, kv.k_cache[layer], kv.v_cache[layer], kv.slot_mapping)
@@ -394,7 +402,7 @@ class CausalLM:
     # ---- forward ----
     def hidden_states(self, tokens, ctx: FwdCtx, layer_hook=None, x=None):
         """Embedding + decoder layers (+ final norm when this rank owns the head)."""
-        if "embed" in self.block_by_name:
+        if x is None and "embed" in self.block_by_name:      # a caller may supply (multimodal) input embeddings
             x = embed(self.block_by_name["embed"].params, tokens, ctx)
             if x.dtype != self.dtype:
                 x = x.to(self.dtype)

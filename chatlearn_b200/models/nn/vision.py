@@ -1,0 +1,233 @@
+"""Vision tower and multimodal position logic of Qwen2.5-VL-style models.
+
+Parity: what the reference gets from HuggingFace through
+chatlearn/models/patches/transformers/qwen2_5_vl_patch.py (vision tower, mrope) and
+chatlearn/data/vision_utils.py (grids).  Written against the published architecture:
+
+* patches ``[N, C·Tp·P·P]`` → linear patch embedding;
+* 2-D rotary position per patch (row and column frequencies side by side), patches stored in
+  spatial-merge blocks;
+* transformer blocks (RMSNorm, fused QKV with bias, SwiGLU MLP with bias); most blocks attend
+  inside windows, the ``fullatt_block_indexes`` ones over the whole image — both are packed
+  variable-length attention over different ``cu_seqlens``, after the merge-block groups are
+  re-ordered window by window;
+* patch merger: RMSNorm, concatenate each block of ``merge²`` patches, two-layer GELU MLP to the
+  language model's width; the window order is undone at the end.
+
+Weights live in a dict keyed by the HuggingFace names (``visual.…``), so checkpoints load by name.
+"""
+from dataclasses import dataclass, field
+from typing import Dict, List, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from chatlearn_b200 import ops
+
+
+@dataclass
+class VisionArch:
+    depth: int = 32
+    hidden_size: int = 1280
+    intermediate_size: int = 3420
+    num_heads: int = 16
+    in_channels: int = 3
+    patch_size: int = 14
+    temporal_patch_size: int = 2
+    spatial_merge_size: int = 2
+    out_hidden_size: int = 3584
+    window_size: int = 112
+    fullatt_block_indexes: List[int] = field(default_factory=lambda: [7, 15, 23, 31])
+    rms_norm_eps: float = 1e-6
+
+    @property
+    def patch_dim(self) -> int:
+        return self.in_channels * self.temporal_patch_size * self.patch_size * self.patch_size
+
+    @property
+    def merge_unit(self) -> int:
+        return self.spatial_merge_size ** 2
+
+    @classmethod
+    def from_hf_dict(cls, d: Dict) -> "VisionArch":
+        keys = {f for f in cls.__dataclass_fields__}
+        kw = {k: v for k, v in d.items() if k in keys}
+        if "in_chans" in d:
+            kw["in_channels"] = d["in_chans"]
+        return cls(**kw)
+
+
+def vision_param_shapes(a: VisionArch) -> Dict[str, Tuple[int, ...]]:
+    H, I = a.hidden_size, a.intermediate_size
+    out = {"visual.patch_embed.proj.weight": (H, a.patch_dim)}
+    for i in range(a.depth):
+        b = f"visual.blocks.{i}."
+        out.update({b + "norm1.weight": (H,), b + "norm2.weight": (H,),
+                    b + "attn.qkv.weight": (3 * H, H), b + "attn.qkv.bias": (3 * H,),
+                    b + "attn.proj.weight": (H, H), b + "attn.proj.bias": (H,),
+                    b + "mlp.gate_proj.weight": (I, H), b + "mlp.gate_proj.bias": (I,),
+                    b + "mlp.up_proj.weight": (I, H), b + "mlp.up_proj.bias": (I,),
+                    b + "mlp.down_proj.weight": (H, I), b + "mlp.down_proj.bias": (H,)})
+    M = H * a.merge_unit
+    out.update({"visual.merger.ln_q.weight": (H,), "visual.merger.mlp.0.weight": (M, M), "visual.merger.mlp.0.bias": (M,),
+                "visual.merger.mlp.2.weight": (a.out_hidden_size, M), "visual.merger.mlp.2.bias": (a.out_hidden_size,)})
+    return out
+
+
+def patch_positions(grid_thw: Sequence[Sequence[int]], merge: int) -> torch.Tensor:
+    """(row, column) of every patch in storage order: merge blocks are contiguous."""
+    out = []
+    for t, h, w in grid_thw:
+        rows = torch.arange(h).view(h // merge, merge, 1, 1).expand(h // merge, merge, w // merge, merge)
+        cols = torch.arange(w).view(1, 1, w // merge, merge).expand(h // merge, merge, w // merge, merge)
+        rc = torch.stack([rows.permute(0, 2, 1, 3).reshape(-1), cols.permute(0, 2, 1, 3).reshape(-1)], -1)
+        out.append(rc.repeat(t, 1))
+    return torch.cat(out, 0)
+
+
+def window_order(grid_thw: Sequence[Sequence[int]], a: VisionArch) -> Tuple[torch.Tensor, List[int]]:
+    """Order of the merge-block groups window by window, and the cumulative patch counts of the
+    windows (empty windows removed)."""
+    m = a.spatial_merge_size
+    win = a.window_size // m // a.patch_size
+    order, cu, base = [], [0], 0
+    for t, h, w in grid_thw:
+        gh, gw = h // m, w // m
+        idx = torch.arange(t * gh * gw).view(t, gh, gw)
+        ph, pw = win - gh % win, win - gw % win            # (a full extra window of padding when already aligned)
+        idx = F.pad(idx, (0, pw, 0, ph), value=-1)
+        nh, nw = (gh + ph) // win, (gw + pw) // win
+        idx = idx.view(t, nh, win, nw, win).permute(0, 1, 3, 2, 4).reshape(t * nh * nw, win * win)
+        counts = (idx >= 0).sum(1)
+        order.append(idx.reshape(-1)[idx.reshape(-1) >= 0] + base)
+        for c in counts.tolist():
+            if c:
+                cu.append(cu[-1] + c * a.merge_unit)
+        base += t * gh * gw
+    return torch.cat(order), cu
+
+
+def _rotate_half(x):
+    x1, x2 = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2:]
+    return torch.cat((-x2, x1), -1)
+
+
+class VisionTower:
+    def __init__(self, arch: VisionArch, dtype=torch.float32, device="cpu"):
+        self.arch, self.dtype, self.device = arch, dtype, torch.device(device)
+        self.params: Dict[str, torch.Tensor] = {
+            k: torch.zeros(s, dtype=dtype, device=self.device) for k, s in vision_param_shapes(arch).items()}
+
+    def init_weights(self, seed: int = 0, std: float = 0.02):
+        g = torch.Generator().manual_seed(seed)
+        for k, p in self.params.items():
+            if k.endswith("norm1.weight") or k.endswith("norm2.weight") or k.endswith("ln_q.weight"):
+                p.fill_(1.0)
+            elif k.endswith(".bias"):
+                p.zero_()
+            else:
+                p.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
+        return self
+
+    def load_hf_state_dict(self, sd: Dict[str, torch.Tensor], strict: bool = True) -> List[str]:
+        """Accepts ``visual.*`` or ``model.visual.*`` names; the patch-embedding convolution kernel is
+        flattened to a matrix."""
+        missing = []
+        for k, p in self.params.items():
+            src = sd.get(k, sd.get("model." + k))
+            if src is None:
+                missing.append(k)
+                continue
+            p.copy_(src.reshape(p.shape).to(p.dtype))
+        if strict and missing:
+            raise KeyError(f"vision weights missing: {missing[:4]} ...")
+        return missing
+
+    def hf_state_dict(self) -> Dict[str, torch.Tensor]:
+        a = self.arch
+        out = dict(self.params)
+        out["visual.patch_embed.proj.weight"] = self.params["visual.patch_embed.proj.weight"].view(
+            a.hidden_size, a.in_channels, a.temporal_patch_size, a.patch_size, a.patch_size)
+        return out
+
+    def _lin(self, x, name):
+        return ops.linear(x, self.params[name + ".weight"], self.params.get(name + ".bias"))
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw) -> torch.Tensor:
+        """``pixel_values [N, patch_dim]``, ``grid_thw`` = (t, h, w) per image in patches.  Returns the
+        merged image embeddings ``[N / merge², out_hidden]`` in the order of the input patches."""
+        a, P = self.arch, self.params
+        grid = [tuple(int(v) for v in g) for g in (grid_thw.tolist() if torch.is_tensor(grid_thw) else grid_thw)]
+        x = ops.linear(pixel_values.to(self.dtype), P["visual.patch_embed.proj.weight"])
+        N, H, nh = x.shape[0], a.hidden_size, a.num_heads
+        d = H // nh
+        # rotary table: row frequencies then column frequencies, each d/4 wide
+        rc = patch_positions(grid, a.spatial_merge_size).to(x.device)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, d // 2, 2, dtype=torch.float32, device=x.device) / (d // 2)))
+        ang = torch.cat([rc[:, :1].float() * inv, rc[:, 1:].float() * inv], -1)          # [N, d/2]
+        order, cu_win = window_order(grid, a)
+        order = order.to(x.device)
+        u = a.merge_unit
+        x = x.view(N // u, u, H)[order].reshape(N, H)
+        ang = ang.view(N // u, u, -1)[order].reshape(N, -1)
+        emb = torch.cat([ang, ang], -1)
+        cos, sin = emb.cos()[:, None, :], emb.sin()[:, None, :]
+        cu_full = [0]
+        for t, h, w in grid:
+            for _ in range(t):
+                cu_full.append(cu_full[-1] + h * w)
+        cu_full_t = torch.tensor(cu_full, dtype=torch.int32, device=x.device)
+        cu_win_t = torch.tensor(cu_win, dtype=torch.int32, device=x.device)
+        scale = d ** -0.5
+        for i in range(a.depth):
+            b = f"visual.blocks.{i}."
+            h_ = ops.rmsnorm(x, P[b + "norm1.weight"], a.rms_norm_eps)
+            qkv = self._lin(h_, b + "attn.qkv").view(N, 3, nh, d)
+            q, k, v = qkv[:, 0].float(), qkv[:, 1].float(), qkv[:, 2]
+            q = (q * cos + _rotate_half(q) * sin).to(x.dtype)
+            k = (k * cos + _rotate_half(k) * sin).to(x.dtype)
+            full = i in a.fullatt_block_indexes
+            cu = cu_full_t if full else cu_win_t
+            lens = (cu[1:] - cu[:-1])
+            o = ops.attention_varlen(q.contiguous(), k.contiguous(), v.contiguous(), cu, int(lens.max()), scale, False)
+            x = x + self._lin(o.reshape(N, H), b + "attn.proj")
+            h_ = ops.rmsnorm(x, P[b + "norm2.weight"], a.rms_norm_eps)
+            g_ = F.silu(self._lin(h_, b + "mlp.gate_proj")) * self._lin(h_, b + "mlp.up_proj")
+            x = x + self._lin(g_, b + "mlp.down_proj")
+        x = ops.rmsnorm(x, P["visual.merger.ln_q.weight"], a.rms_norm_eps).view(N // u, u * H)
+        x = self._lin(F.gelu(self._lin(x, "visual.merger.mlp.0")), "visual.merger.mlp.2")
+        return x[torch.argsort(order)]
+
+    __call__ = forward
+
+
+def mrope_positions(input_ids: torch.Tensor, image_grid_thw, image_token_id: int, merge: int) -> Tuple[torch.Tensor, int]:
+    """Three-component (time, row, column) positions of one sequence and the offset that later text
+    positions carry: text tokens count up with all components equal; an image occupies a
+    (t, h/merge, w/merge) grid starting at the current position and advances it by max(h, w)/merge."""
+    ids = input_ids.tolist()
+    grids = [tuple(int(v) for v in g) for g in (image_grid_thw.tolist() if torch.is_tensor(image_grid_thw) else (image_grid_thw or []))]
+    out, cur, i, gi = [], 0, 0, 0
+    n = len(ids)
+    while i < n:
+        if ids[i] == image_token_id:
+            t, h, w = grids[gi]
+            gi += 1
+            gh, gw = h // merge, w // merge
+            cnt = t * gh * gw
+            tt = torch.arange(t).view(t, 1, 1).expand(t, gh, gw).reshape(-1)
+            hh = torch.arange(gh).view(1, gh, 1).expand(t, gh, gw).reshape(-1)
+            ww = torch.arange(gw).view(1, 1, gw).expand(t, gh, gw).reshape(-1)
+            out.append(torch.stack([tt, hh, ww]) + cur)
+            cur += max(gh, gw)
+            i += cnt
+        else:
+            j = i
+            while j < n and ids[j] != image_token_id:
+                j += 1
+            out.append((torch.arange(j - i) + cur).view(1, -1).expand(3, -1))
+            cur += j - i
+            i = j
+    pos = torch.cat(out, 1) if out else torch.zeros(3, 0, dtype=torch.long)
+    delta = int(pos.max().item()) + 1 - n if n else 0
+    return pos.long(), delta

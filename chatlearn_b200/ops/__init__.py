@@ -86,6 +86,7 @@ add_rmsnorm_ = _dispatch("add_rmsnorm_")
 swiglu = _dispatch("swiglu")
 linear = _dispatch("linear")
 rope = _dispatch("rope")
+rope_mrope = _dispatch("rope_mrope")
 qk_norm_rope = _dispatch("qk_norm_rope")
 attention_varlen = _dispatch("attention_varlen")
 attention_segments = _dispatch("attention_segments")

@@ -63,6 +63,23 @@ def rope(x: torch.Tensor, positions: torch.Tensor, theta: float,
     return out
 
 
+def rope_mrope(x: torch.Tensor, positions3: torch.Tensor, theta: float, sections) -> torch.Tensor:
+    """Multimodal rotary embedding (Qwen2-VL "mrope") on ``x [T, heads, d]``: frequency ``f`` of the
+    ``d/2`` rotary frequencies takes its angle from the time, row or column position according to
+    the section it falls in (``sections`` = three sizes summing to ``d/2``); ``positions3 [3, T]``."""
+    d = x.shape[-1]
+    half = d // 2
+    assert sum(sections) == half, "mrope sections must sum to head_dim / 2"
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32, device=x.device) / d))
+    comp = torch.repeat_interleave(torch.arange(3, device=x.device), torch.tensor(list(sections), device=x.device))
+    pos = positions3.to(torch.float32)[comp]                     # [d/2, T]: the position each frequency uses
+    ang = (pos * inv[:, None]).t()                               # [T, d/2]
+    c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    xf = x.float()
+    x1, x2 = xf[..., :half], xf[..., half:]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+
+
 def qk_norm_rope(q, k, qw, kw, eps, positions, theta):
     """Per-head RMSNorm on q and k (Qwen3) followed by rotary embedding."""
     if qw is not None:

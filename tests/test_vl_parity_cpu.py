@@ -1,0 +1,87 @@
+"""Vision tower, multimodal rotary positions and the vision-language forward pass against the
+HuggingFace implementation of Qwen2.5-VL (random small configuration, CPU, fp32)."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+
+def _hf():
+    from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration
+    torch.manual_seed(0)
+    cfg = Qwen2_5_VLConfig(
+        text_config=dict(vocab_size=1024, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=512,
+                         rope_scaling={"type": "mrope", "mrope_section": [4, 6, 6]}, rope_theta=10000.0),
+        vision_config=dict(depth=3, hidden_size=64, intermediate_size=96, num_heads=4, patch_size=14, spatial_merge_size=2,
+                           temporal_patch_size=2, out_hidden_size=128, window_size=56, fullatt_block_indexes=[1],
+                           # one position step per temporal grid step: still images then sit at their start position,
+                           # the published Qwen2.5-VL behaviour
+                           tokens_per_second=1),
+        image_token_id=1000, video_token_id=1001, vision_start_token_id=1002, vision_end_token_id=1003)
+    m = Qwen2_5_VLForConditionalGeneration(cfg).eval().float()
+    for p in m.parameters():                              # biases and norms away from their trivial initial values
+        if p.dim() == 1:
+            torch.nn.init.normal_(p, mean=0.5, std=0.2)
+    return cfg, m
+
+
+def _arch(cfg):
+    from chatlearn_b200.models.nn.arch import ModelArch
+    return ModelArch.from_hf_dict(cfg.to_dict())
+
+
+def test_vision_tower_matches_hf():
+    from chatlearn_b200.models.nn.vision import VisionArch, VisionTower
+    cfg, hf = _hf()
+    va = VisionArch.from_hf_dict(cfg.vision_config.to_dict())
+    tower = VisionTower(va)
+    tower.load_hf_state_dict(hf.state_dict())
+    grid = torch.tensor([[1, 6, 8], [1, 4, 4], [1, 10, 6]])             # windows of 2x2 merge groups: ragged edges
+    n = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+    px = torch.randn(n, va.patch_dim)
+    with torch.no_grad():
+        want = hf.model.visual(px, grid_thw=grid).pooler_output
+        got = tower(px, grid)
+    assert got.shape == want.shape == (n // 4, 128)
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-4), (got - want).abs().max()
+
+
+def test_mrope_positions_match_hf():
+    from chatlearn_b200.models.nn.vision import mrope_positions
+    cfg, hf = _hf()
+    grid = torch.tensor([[1, 6, 8], [1, 4, 4]])
+    ids = [5, 6, 1002] + [1000] * 12 + [1003, 7, 8, 9, 1002] + [1000] * 4 + [1003, 10, 11]
+    input_ids = torch.tensor([ids])
+    mm = (input_ids == 1000).long()
+    want, delta = hf.model.get_rope_index(input_ids, mm_token_type_ids=mm, image_grid_thw=grid)
+    got, d = mrope_positions(input_ids[0], grid, 1000, 2)
+    assert torch.equal(got, want[:, 0]) and d == int(delta[0])
+
+
+def test_full_forward_logits_match_hf():
+    from chatlearn_b200.models.nn.model import packed_ctx
+    from chatlearn_b200.models.nn.vl_model import VLCausalLM
+    cfg, hf = _hf()
+    arch = _arch(cfg)
+    assert arch.mrope_section == [4, 6, 6] and arch.image_token_id == 1000 and arch.attention_bias
+    model = VLCausalLM(arch)
+    model.load_hf_state_dict(hf.state_dict())
+    grid = torch.tensor([[1, 6, 8]])
+    ids = torch.tensor([3, 4, 1002] + [1000] * 12 + [1003, 20, 21, 22, 23])
+    px = torch.randn(48, model.varch.patch_dim)
+    with torch.no_grad():
+        want = hf(input_ids=ids[None], pixel_values=px, image_grid_thw=grid, mm_token_type_ids=(ids[None] == 1000).long()).logits[0]
+        ctx, _ = packed_ctx([ids.numel()], "cpu")
+        ctx.mrope_positions = model.positions(ids, grid)
+        got = model.logits(ids, ctx, px, grid)
+    assert torch.allclose(got, want, rtol=2e-4, atol=2e-4), (got - want).abs().max()
+    # two sequences packed into one row: each keeps its own positions and attends only to itself
+    ids2 = torch.tensor([9, 8, 7, 6])
+    with torch.no_grad():
+        want2 = hf(input_ids=ids2[None]).logits[0]
+        ctx, _ = packed_ctx([ids.numel(), ids2.numel()], "cpu")
+        ctx.mrope_positions = model.packed_positions([ids, ids2], [grid, None])
+        both = model.logits(torch.cat([ids, ids2]), ctx, px, grid)
+    assert torch.allclose(both[:ids.numel()], want, rtol=2e-4, atol=2e-4)
+    assert torch.allclose(both[ids.numel():], want2, rtol=2e-4, atol=2e-4)
