@@ -1,0 +1,103 @@
+"""Image preprocessing for vision-language prompts.
+
+Parity: chatlearn/data/vision_utils.py and the processor calls in
+chatlearn/data/vl_prompt_dataset.py (the reference delegates to the HuggingFace Qwen2-VL image
+processor and ``qwen_vl_utils``).  Implemented here from the published recipe:
+
+* ``smart_resize``: both sides become multiples of ``patch · merge`` (28), the aspect ratio is kept
+  as far as the pixel budget ``[min_pixels, max_pixels]`` allows;
+* bicubic resize, scale to [0, 1], normalise with the CLIP mean / std;
+* a still image is repeated ``temporal_patch_size`` times; patches of ``C × Tp × P × P`` values are
+  emitted merge-block by merge-block (the order the vision tower's window logic expects);
+* ``image_grid_thw = (1, H / P, W / P)``; the prompt holds ``grid_t · grid_h · grid_w / merge²`` image
+  placeholder tokens per image.
+"""
+import io
+import math
+from typing import List, Sequence, Tuple
+
+import torch
+
+CLIP_MEAN = (0.48145466, 0.4578275, 0.40821073)
+CLIP_STD = (0.26862954, 0.26130258, 0.27577711)
+
+
+def smart_resize(height: int, width: int, factor: int = 28, min_pixels: int = 56 * 56,
+                 max_pixels: int = 14 * 14 * 4 * 1280) -> Tuple[int, int]:
+    if max(height, width) / min(height, width) > 200:
+        raise ValueError("aspect ratio above 200 is not supported")
+    h = max(factor, round(height / factor) * factor)
+    w = max(factor, round(width / factor) * factor)
+    if h * w > max_pixels:
+        beta = math.sqrt(height * width / max_pixels)
+        h = max(factor, math.floor(height / beta / factor) * factor)
+        w = max(factor, math.floor(width / beta / factor) * factor)
+    elif h * w < min_pixels:
+        beta = math.sqrt(min_pixels / (height * width))
+        h = math.ceil(height * beta / factor) * factor
+        w = math.ceil(width * beta / factor) * factor
+    return h, w
+
+
+def load_image(src):
+    """PIL image from a path, raw bytes, a hex string of bytes, a dict with ``path``/``bytes``, or a PIL image."""
+    from PIL import Image
+    if isinstance(src, Image.Image):
+        return src.convert("RGB")
+    if isinstance(src, dict):
+        src = src.get("bytes") or src.get("path")
+    if isinstance(src, str):
+        try:
+            raw = bytes.fromhex(src)
+            return Image.open(io.BytesIO(raw)).convert("RGB")
+        except ValueError:
+            return Image.open(src).convert("RGB")
+    if isinstance(src, (bytes, bytearray)):
+        return Image.open(io.BytesIO(src)).convert("RGB")
+    raise TypeError(f"cannot load an image from {type(src).__name__}")
+
+
+def image_to_patches(img, patch_size: int = 14, temporal_patch_size: int = 2, merge_size: int = 2,
+                     min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280,
+                     mean: Sequence[float] = CLIP_MEAN, std: Sequence[float] = CLIP_STD):
+    """Returns ``(pixel_values [grid_h·grid_w, C·Tp·P·P] fp32, (1, grid_h, grid_w))``."""
+    import numpy as np
+    from PIL import Image
+    img = load_image(img)
+    W, H = img.size
+    h, w = smart_resize(H, W, patch_size * merge_size, min_pixels, max_pixels)
+    img = img.resize((w, h), resample=Image.BICUBIC)
+    x = torch.from_numpy(np.asarray(img, dtype=np.float32) / 255.0).permute(2, 0, 1)        # [C, h, w]
+    x = (x - torch.tensor(mean).view(3, 1, 1)) / torch.tensor(std).view(3, 1, 1)
+    frames = x.unsqueeze(0).repeat(temporal_patch_size, 1, 1, 1)                              # [Tp, C, h, w]
+    gh, gw, m, P, C = h // patch_size, w // patch_size, merge_size, patch_size, 3
+    t = frames.view(1, temporal_patch_size, C, gh // m, m, P, gw // m, m, P)
+    t = t.permute(0, 3, 6, 4, 7, 2, 1, 5, 8)        # grid_t, gh/m, gw/m, m, m, C, Tp, P, P
+    return t.reshape(gh * gw, C * temporal_patch_size * P * P).contiguous(), (1, gh, gw)
+
+
+def expand_image_tokens(input_ids: List[int], grids: Sequence[Sequence[int]], image_token_id: int,
+                        merge_size: int = 2) -> List[int]:
+    """Replace the i-th single image placeholder by as many placeholders as the i-th image has merged patches."""
+    out, gi = [], 0
+    for tok in input_ids:
+        if tok == image_token_id:
+            t, h, w = grids[gi]
+            gi += 1
+            out.extend([image_token_id] * (t * h * w // (merge_size ** 2)))
+        else:
+            out.append(tok)
+    assert gi == len(grids), f"{len(grids)} images but {gi} placeholders in the prompt"
+    return out
+
+
+def process_images(images, **kw):
+    """``(pixel_values [sum patches, D], image_grid_thw [n, 3])`` of a list of images."""
+    pv, grids = [], []
+    for im in images:
+        p, g = image_to_patches(im, **kw)
+        pv.append(p)
+        grids.append(g)
+    if not pv:
+        return torch.zeros(0, 0), torch.zeros(0, 3, dtype=torch.long)
+    return torch.cat(pv, 0), torch.tensor(grids, dtype=torch.long)

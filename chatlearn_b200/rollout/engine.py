@@ -52,9 +52,11 @@ class RolloutEngine:
                  num_blocks: Optional[int] = None, max_num_seqs: int = 256,
                  max_num_batched_tokens: int = 32768, gpu_memory_utilization: float = 0.8,
                  max_model_len: int = 4096, seed: int = 0, kv_dtype=None,
-                 lockstep_group=None, use_cuda_graphs: bool = True):
+                 lockstep_group=None, use_cuda_graphs: bool = True, vision=None):
         self.model, self.arch = model, model.arch
         self.device = model.device
+        self.vision = vision                 # models.nn.vision.VisionTower for vision-language models
+        self._embed_patch = None
         self.tp, self.ep = tp_group, ep_group
         # tensor-parallel reductions by this package's own peer-memory kernels (fused with
         # the residual add and the next RMSNorm) instead of NCCL; collective construction
@@ -164,11 +166,32 @@ class RolloutEngine:
         max_blocks = max(len(s.blocks) for s in plan.seqs)
         bt = torch.zeros(len(plan.seqs), max_blocks, dtype=torch.int32)
         seq_lens, last_rows = [], []
+        # vision-language prompts: rows of an image prompt carry (time, row, column) positions and take
+        # their embeddings from the vision tower; every later row sits at index + rope_delta
+        any_mm = any(s.mm is not None and s.num_computed < len(s.prompt) for s in plan.seqs)
+        pos3, patch_rows, patch_src = ([], [], []) if any_mm else (None, None, None)
         for i, (s, n) in enumerate(zip(plan.seqs, plan.q_lens)):
             start = s.num_computed
             all_t = s.tokens
             toks.extend(all_t[start:start + n])
-            pos.extend(range(start, start + n))
+            npr = len(s.prompt) if s.mm is not None else 0
+            pos.extend(p if p < npr else p + s.rope_delta for p in range(start, start + n))
+            if any_mm:
+                row0 = cu[-1]
+                if s.mm is not None and start < npr:
+                    hi = min(start + n, npr)
+                    pos3.append(s.mm["pos3"][:, start:hi])
+                    for p in range(start, hi):
+                        o = s.mm["ordinal"].get(p)
+                        if o is not None:
+                            patch_rows.append(row0 + p - start)
+                            patch_src.append((s, o))
+                    if hi < start + n:
+                        tail = torch.arange(hi, start + n) + s.rope_delta
+                        pos3.append(tail.view(1, -1).expand(3, -1))
+                else:
+                    tail = torch.arange(start, start + n) + s.rope_delta
+                    pos3.append(tail.view(1, -1).expand(3, -1))
             for p in range(start, start + n):
                 slots.append(s.blocks[p // bs] * bs + p % bs)
             bt[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
@@ -182,6 +205,12 @@ class RolloutEngine:
                    t(seq_lens, torch.int32, "seq_lens"), t(plan.q_lens, torch.int32, "q_lens"), plan.is_prefill)
         ctx = FwdCtx(positions=t(pos, torch.long, "pos"), cu_seqlens=t(cu, torch.int32, "cu"),
                      max_seqlen=max(plan.q_lens), kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm(), fuse_add_norm=True)
+        self._embed_patch = None
+        if any_mm:
+            ctx.mrope_positions = xfer.to_device(torch.cat(pos3, 1).contiguous(), dev, "pos3")
+            if patch_rows:
+                src = torch.stack([s.mm["embeds"][o] for s, o in patch_src])
+                self._embed_patch = (torch.tensor(patch_rows, dtype=torch.long, device=dev), src)
         return t(toks, torch.long, "toks"), ctx, t(last_rows, torch.long, "last")
 
     def _symm(self):
@@ -250,7 +279,7 @@ class RolloutEngine:
         for i, s in enumerate(seqs):
             p = s.num_computed                   # position of the token fed now
             rows[0][i] = s.output[-1] if s.output else s.prompt[-1]
-            rows[1][i] = p
+            rows[1][i] = p + s.rope_delta        # rotary position (text after images is shifted)
             rows[2][i] = s.blocks[p // bs] * bs + p % bs
             rows[3][i] = p + 1
             nb = len(s.blocks)
@@ -311,7 +340,15 @@ class RolloutEngine:
             self._finish_step(sched, plan.seqs, ids, lps, eos_id)
             return
         tokens, ctx, last_rows = self._build_inputs(plan)
-        hidden = self.model.hidden_states(tokens, ctx)
+        x = None
+        if self._embed_patch is not None:
+            # image placeholder rows take the vision tower's embeddings
+            from chatlearn_b200.models.nn.model import embed as _embed
+            rows_, src_ = self._embed_patch
+            x = _embed(self.model.block_by_name["embed"].params, tokens, ctx).to(self.model.dtype).clone()
+            x.index_copy_(0, rows_, src_.to(x.dtype))
+            self._embed_patch = None
+        hidden = self.model.hidden_states(tokens, ctx, x=x)
         for s, n in zip(plan.seqs, plan.q_lens):
             s.num_computed += n
         rows = [i for i, smp in enumerate(plan.samples) if smp]
@@ -377,8 +414,25 @@ class RolloutEngine:
 
     # ------------------------------------------------------------------ public
     @torch.no_grad()
+    @torch.no_grad()
+    def _attach_images(self, s: Sequence, mm: Dict[str, Any]):
+        """Run the vision tower once for a request and remember where its embeddings go."""
+        assert self.vision is not None, "this engine was built without a vision tower"
+        from chatlearn_b200.models.nn.vision import mrope_positions
+        grid = mm["image_grid_thw"]
+        grid = grid.tolist() if torch.is_tensor(grid) else [list(g) for g in grid]
+        px = torch.as_tensor(mm["pixel_values"]).to(self.device)
+        embeds = self.vision(px, grid).to(self.model.dtype)
+        itok = self.arch.image_token_id
+        where = [j for j, tkn in enumerate(s.prompt) if tkn == itok]
+        assert len(where) == embeds.shape[0], \
+            f"{len(where)} image placeholder tokens in the prompt but {embeds.shape[0]} image embeddings"
+        pos3, delta = mrope_positions(torch.tensor(s.prompt), grid, itok, self.vision.arch.spatial_merge_size)
+        s.mm = {"embeds": embeds, "pos3": pos3, "ordinal": {j: o for o, j in enumerate(where)}}
+        s.rope_delta = int(delta)
+
     def generate(self, prompts: List[List[int]], sampling: Any, eos_id: Optional[int] = None,
-                 max_new_tokens: Optional[List[int]] = None) -> List[Sequence]:
+                 max_new_tokens: Optional[List[int]] = None, mm_inputs: Optional[List[Optional[Dict]]] = None) -> List[Sequence]:
         """Generate for a batch of token-id prompts.  ``sampling`` is one
         ``SamplingParams`` or a list (one per prompt); ``max_new_tokens`` optionally
         overrides the per-request budget (partial rollout)."""
@@ -391,6 +445,9 @@ class RolloutEngine:
             mx = max_new_tokens[i] if max_new_tokens is not None else sp.max_tokens
             mx = max(0, min(mx, self.max_model_len - len(p)))
             s = Sequence(self._req_counter, list(p), mx, sp)
+            mm = mm_inputs[i] if mm_inputs is not None else None
+            if mm is not None and mm.get("pixel_values") is not None and len(mm["image_grid_thw"]):
+                self._attach_images(s, mm)
             self._req_counter += 1
             seqs.append(s)
             if mx == 0:

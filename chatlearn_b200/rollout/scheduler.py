@@ -54,6 +54,10 @@ class Sequence:
     finished: bool = False
     finish_reason: Optional[str] = None
     preemptions: int = 0
+    # vision-language requests: image embeddings and (time, row, column) positions of the prompt;
+    # text after the images sits at position index + rope_delta
+    mm: Optional[dict] = None
+    rope_delta: int = 0
 
     @property
     def tokens(self) -> List[int]:

@@ -85,3 +85,53 @@ def test_full_forward_logits_match_hf():
         both = model.logits(torch.cat([ids, ids2]), ctx, px, grid)
     assert torch.allclose(both[:ids.numel()], want, rtol=2e-4, atol=2e-4)
     assert torch.allclose(both[ids.numel():], want2, rtol=2e-4, atol=2e-4)
+
+
+def test_image_patches_match_hf_processor():
+    import numpy as np
+    from PIL import Image
+    from transformers import Qwen2VLImageProcessor
+    from chatlearn_b200.data.vision_utils import expand_image_tokens, image_to_patches, smart_resize
+    rng = np.random.default_rng(0)
+    img = Image.fromarray(rng.integers(0, 255, (75, 131, 3), dtype=np.uint8))
+    proc = Qwen2VLImageProcessor(min_pixels=56 * 56, max_pixels=28 * 28 * 64)
+    want = proc(images=[img], return_tensors="pt")
+    got, grid = image_to_patches(img, min_pixels=56 * 56, max_pixels=28 * 28 * 64)
+    assert list(grid) == want["image_grid_thw"][0].tolist()
+    assert got.shape == want["pixel_values"].shape
+    assert torch.allclose(got, want["pixel_values"], atol=2e-2), (got - want["pixel_values"]).abs().max()
+    assert smart_resize(75, 131, 28, 56 * 56, 28 * 28 * 64) == (grid[1] * 14, grid[2] * 14)
+    ids = expand_image_tokens([1, 1000, 2], [grid], 1000)
+    assert ids.count(1000) == grid[1] * grid[2] // 4 and ids[0] == 1 and ids[-1] == 2
+
+
+def test_rollout_engine_generates_like_hf_with_an_image():
+    from chatlearn_b200.models.nn.model import CausalLM
+    from chatlearn_b200.models.nn.vision import VisionArch, VisionTower
+    from chatlearn_b200.models.nn.vl_model import strip_language_prefix
+    from chatlearn_b200.rollout import RolloutEngine, SamplingParams
+    cfg, hf = _hf()
+    arch = _arch(cfg)
+    arch.eos_token_id = 1023
+    lm = CausalLM(arch)
+    lm.load_hf_state_dict(strip_language_prefix(hf.state_dict()))
+    tower = VisionTower(VisionArch.from_hf_dict(cfg.vision_config.to_dict()))
+    tower.load_hf_state_dict(hf.state_dict())
+    eng = RolloutEngine(lm, block_size=8, num_blocks=64, max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128,
+                        vision=tower)
+    grid = torch.tensor([[1, 6, 8]])
+    ids = [3, 4, 1002] + [1000] * 12 + [1003, 20, 21, 22, 23]
+    px = torch.randn(48, tower.arch.patch_dim)
+    text_only = [9, 8, 7, 6, 5]
+    new = 8
+    with torch.no_grad():
+        want = hf.generate(input_ids=torch.tensor([ids]), pixel_values=px, image_grid_thw=grid,
+                           mm_token_type_ids=(torch.tensor([ids]) == 1000).long(),
+                           max_new_tokens=new, do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(ids):].tolist()
+        want_text = hf.generate(input_ids=torch.tensor([text_only]), max_new_tokens=new, do_sample=False,
+                                eos_token_id=None, pad_token_id=0)[0, len(text_only):].tolist()
+    sp = SamplingParams(temperature=0.0, max_tokens=new, ignore_eos=True)
+    seqs = eng.generate([ids, text_only], sp, mm_inputs=[{"pixel_values": px, "image_grid_thw": grid}, None])
+    assert seqs[0].rope_delta == -8                    # 12 image tokens advance the position by max(3, 4)
+    assert seqs[0].output == want, (seqs[0].output, want)
+    assert seqs[1].output == want_text
