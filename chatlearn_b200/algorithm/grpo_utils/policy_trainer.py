@@ -103,7 +103,11 @@ class PolicyTrainer(FSDPModule):
                 if l >= n_ckpt:       # the last layers keep their activations: backward reaches them first
                     return decoder_layer(arch, p, x, c, l)
                 return checkpoint(lambda xx: decoder_layer(arch, p, xx, c, l), x, use_reentrant=False)
-        lp, ent = self.model.logprobs(tokens, labels, ctx, layer_hook=hook)
+        x = None
+        if getattr(self, "vision", None) is not None:
+            from chatlearn_b200.models.nn.vision import multimodal_inputs
+            x = multimodal_inputs(self.model, self.vision, tokens, batch.seq_lens, batch.mm or [], ctx)
+        lp, ent = self.model.logprobs(tokens, labels, ctx, layer_hook=hook, x=x)
         if self.sp is not None:
             lp = self.sp.gather(lp)
             ent = self.sp.gather(ent) if need_entropy else None

@@ -51,6 +51,7 @@ class PackedBatch:
     values: Optional[torch.Tensor] = None         # [T] value estimates at rollout time (PPO critic)
     returns: Optional[torch.Tensor] = None        # [T] value targets
     pad: int = 0                                  # trailing pad tokens (SP/CP alignment)
+    mm: Any = None                                # per sample (pixel_values, image_grid_thw) or None (vision-language)
 
     def to(self, device):
         for k, v in vars(self).items():
@@ -149,7 +150,9 @@ def pack_samples(samples: List[Dict[str, Any]], pad_multiple: int = 1, seq_multi
                        loss_mask=torch.cat(mask), seq_ids=torch.cat(sid), cu_seqlens=cu,
                        seq_lens=seq_lens, max_seqlen=max(seq_lens),
                        sample_ids=[int(s.get("id_in_list", i)) for i, s in enumerate(samples)],
-                       old_logprobs=cat(old), ref_logprobs=cat(ref), advantages=cat(adv), values=cat(vals or []), returns=cat(rets or []), pad=pad)
+                       old_logprobs=cat(old), ref_logprobs=cat(ref), advantages=cat(adv), values=cat(vals or []), returns=cat(rets or []), pad=pad,
+                       mm=[(s.get("pixel_values"), s.get("image_grid_thw")) for s in samples]
+                       if any(s.get("pixel_values") is not None for s in samples) else None)
 
 
 def unpack_per_sample(values: torch.Tensor, batch: PackedBatch, samples: List[Dict]) -> List[torch.Tensor]:

@@ -58,21 +58,40 @@ class PromptPipeline:
 
 
 class VLPromptPipeline(PromptPipeline):
-    """Vision-language prompts: same schema plus ``pixel_values``,
-    ``image_grid_thw`` and ``multi_modal_data`` passed through from the record
-    (pre-extracted features; no image decoding is done here)."""
+    """Vision-language prompts (chatlearn/data/vl_prompt_dataset.py).  A record carries either
+    pre-extracted ``pixel_values`` + ``image_grid_thw``, or ``images`` (paths, bytes or PIL images),
+    which are resized, normalised and cut into patches here (``data/vision_utils.py``).  Every image
+    placeholder token of the prompt is expanded to one token per merged patch of its image, so the
+    rollout engine and the trainers can drop the vision tower's embeddings into place.  Sample schema:
+    the text schema plus ``pixel_values [patches, C·Tp·P·P]``, ``image_grid_thw [[t, h, w], ...]``."""
 
     def __init__(self, data_list, max_prompt_tokens_length, tokenizer=None, processor=None,
-                 enable_thinking=False, raw_chat=False):
-        super().__init__(data_list, max_prompt_tokens_length, tokenizer, enable_thinking, raw_chat)
-        kept = {id(s): s for s in self.data}
-        j = 0
-        for item in data_list:
-            if j >= len(self.data):
-                break
-            s = self.data[j]
-            for k in ("pixel_values", "image_grid_thw", "multi_modal_data", "images"):
+                 enable_thinking=False, raw_chat=False, image_token_id=None, merge_size: int = 2,
+                 min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280):
+        # the length filter runs after the placeholder expansion, so filter here, not in the base class
+        super().__init__(data_list, 1 << 30, tokenizer, enable_thinking, raw_chat)
+        from chatlearn_b200.data.vision_utils import expand_image_tokens, process_images
+        if image_token_id is None and tokenizer is not None and hasattr(tokenizer, "convert_tokens_to_ids"):
+            image_token_id = tokenizer.convert_tokens_to_ids("<|image_pad|>")
+        kept = []
+        for item, s in zip(data_list, self.data):
+            for k in ("pixel_values", "image_grid_thw", "multi_modal_data"):
                 if k in item:
                     s[k] = item[k]
-            j += 1
-        del kept
+            if item.get("images") and s.get("pixel_values") is None:
+                pv, grid = process_images(item["images"], merge_size=merge_size, min_pixels=min_pixels,
+                                          max_pixels=max_pixels)
+                s["pixel_values"], s["image_grid_thw"] = pv, grid.tolist()
+            if s.get("pixel_values") is not None and "input_ids" in s and image_token_id is not None:
+                import torch
+                s["pixel_values"] = torch.as_tensor(s["pixel_values"], dtype=torch.float32)
+                grids = [list(map(int, g)) for g in s["image_grid_thw"]]
+                n_merged = sum(t * h * w for t, h, w in grids) // (merge_size ** 2)
+                if s["input_ids"].count(image_token_id) != n_merged:       # one placeholder per image so far
+                    s["input_ids"] = expand_image_tokens(s["input_ids"], grids, image_token_id, merge_size)
+                s["prompt_token_ids"] = s["input_ids"]
+                s["prompt_token_length"] = len(s["input_ids"])
+            if raw_chat or len(s.get("input_ids", [])) < max_prompt_tokens_length:
+                kept.append(s)
+        self.data = kept
+        self.valid_ratio = len(kept) / max(len(data_list), 1)

@@ -227,10 +227,16 @@ class BaseModule:
             if needs_tok:
                 tok = load_tokenizer(getattr(self._module_args, "load", None))
                 self.tokenizer = tok
-        cls = VLPromptPipeline if self._runtime_args.model_type == "vlm" else PromptPipeline
-        return cls(prompts, int(getattr(self._module_args, "max_prompt_tokens_length", 1 << 30)),
-                   tok, enable_thinking=getattr(self._module_args, "enable_thinking", False),
-                   raw_chat=self._runtime_args.raw_chat)
+        max_len = int(getattr(self._module_args, "max_prompt_tokens_length", 1 << 30))
+        think = getattr(self._module_args, "enable_thinking", False)
+        if self._runtime_args.model_type == "vlm":
+            arch = getattr(self, "arch", None)
+            vc = (getattr(arch, "vision_config", None) or {}) if arch is not None else {}
+            return VLPromptPipeline(prompts, max_len, tok, enable_thinking=think, raw_chat=self._runtime_args.raw_chat,
+                                    image_token_id=getattr(arch, "image_token_id", None),
+                                    merge_size=int(vc.get("spatial_merge_size", 2)),
+                                    max_pixels=int(getattr(self._module_args, "max_pixels", 14 * 14 * 4 * 1280)))
+        return PromptPipeline(prompts, max_len, tok, enable_thinking=think, raw_chat=self._runtime_args.raw_chat)
 
     def build_all_dataset(self, prompts_list: List[List[Dict]], is_eval: bool = False):
         return [self.build_dataset(p, is_eval) for p in prompts_list]

@@ -69,6 +69,11 @@ class FSDPModule(TorchModule):
             return
         self.arch = resolve_arch(self.module_args)
         self.model = self.create_model()
+        # vision-language roles keep a frozen copy of the vision tower beside the language model
+        from chatlearn_b200.models.nn.vision import build_vision_tower
+        self.vision = build_vision_tower(self.arch, self.compute_dtype, self.device, getattr(self.module_args, "load", None))
+        if self.vision is not None:
+            assert self.sp is None, "vision-language models run without Ulysses sequence parallelism"
         if self.trainable:
             oc = self.module_args.optimizer
             grad_dtype = torch.float32

@@ -256,7 +256,27 @@ def tiny_llama() -> ModelArch:
                      rope_theta=10000.0, rms_norm_eps=1e-5)
 
 
+def tiny_qwen2_5_vl() -> ModelArch:
+    """Qwen2.5-VL shape in miniature: Qwen2 language model with mrope + a windowed-attention vision tower."""
+    return ModelArch(model_type="qwen2", vocab_size=1024, hidden_size=128, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, intermediate_size=256, rope_theta=1e6,
+                     mrope_section=[4, 6, 6], image_token_id=1000,
+                     vision_config=dict(depth=2, hidden_size=64, intermediate_size=96, num_heads=4, patch_size=14,
+                                        spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=128,
+                                        window_size=56, fullatt_block_indexes=[1]))
+
+
+def qwen2_5_vl_7b() -> ModelArch:
+    return ModelArch(model_type="qwen2", vocab_size=152064, hidden_size=3584, num_hidden_layers=28,
+                     num_attention_heads=28, num_key_value_heads=4, intermediate_size=18944, rope_theta=1e6,
+                     mrope_section=[16, 24, 24], image_token_id=151655,
+                     vision_config=dict(depth=32, hidden_size=1280, intermediate_size=3420, num_heads=16, patch_size=14,
+                                        spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=3584,
+                                        window_size=112, fullatt_block_indexes=[7, 15, 23, 31]))
+
+
 PRESETS = {
+    "tiny_qwen2_5_vl": tiny_qwen2_5_vl, "qwen2_5_vl_7b": qwen2_5_vl_7b,
     "tiny_qwen3": tiny_qwen3, "qwen3_8b": qwen3_8b, "qwen3_30b_a3b": qwen3_30b_a3b,
     "llama2_7b": llama2_7b, "moonlight_16b_a3b": moonlight_16b_a3b, "tiny_moe": tiny_moe,
     "tiny_mla_moe": tiny_mla_moe, "tiny_llama": tiny_llama,

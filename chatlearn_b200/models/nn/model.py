@@ -429,9 +429,10 @@ class CausalLM:
     def logits(self, hidden):
         return ops.linear(hidden, self.lm_head_weight())
 
-    def logprobs(self, tokens, labels, ctx: FwdCtx, temperature=1.0, layer_hook=None):
-        """Per-token log p(label) and entropy for a packed row, never building ``[T, V]``."""
-        h = self.hidden_states(tokens, ctx, layer_hook)
+    def logprobs(self, tokens, labels, ctx: FwdCtx, temperature=1.0, layer_hook=None, x=None):
+        """Per-token log p(label) and entropy for a packed row, never building ``[T, V]``.
+        ``x``: input embeddings to use instead of the token embeddings (multimodal rows)."""
+        h = self.hidden_states(tokens, ctx, layer_hook, x=x)
         w = self.lm_head_weight()
         if ctx.tp is not None and ctx.tp.size > 1 and w.shape[0] != self.arch.vocab_size:
             from chatlearn_b200.parallel.tp_ops import vocab_parallel_logprob_entropy

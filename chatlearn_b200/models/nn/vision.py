@@ -231,3 +231,64 @@ def mrope_positions(input_ids: torch.Tensor, image_grid_thw, image_token_id: int
     pos = torch.cat(out, 1) if out else torch.zeros(3, 0, dtype=torch.long)
     delta = int(pos.max().item()) + 1 - n if n else 0
     return pos.long(), delta
+
+
+def build_vision_tower(arch, dtype, device, load: str = None, seed: int = 4321):
+    """The (frozen) vision tower of a vision-language role, or ``None`` for text models.  Weights come
+    from the HF checkpoint directory ``load`` when it holds them, else from a seeded random init (the
+    same on every role, so trainer and rollout agree)."""
+    if getattr(arch, "vision_config", None) is None:
+        return None
+    tower = VisionTower(VisionArch.from_hf_dict(arch.vision_config), dtype=dtype, device=device)
+    loaded = False
+    if load:
+        from chatlearn_b200.checkpoint.safetensors_io import SafetensorsDir, has_safetensors
+        if has_safetensors(load):
+            d = SafetensorsDir(load)
+            sd = {}
+            for k in tower.params:
+                t = d.get(k)
+                if t is None:
+                    t = d.get("model." + k)
+                if t is not None:
+                    sd[k] = t
+            if sd:
+                tower.load_hf_state_dict(sd, strict=True)
+                loaded = True
+            d.close()
+    if not loaded:
+        tower.init_weights(seed)
+    return tower
+
+
+def multimodal_inputs(lm, tower, tokens: torch.Tensor, seq_lens, mm, ctx):
+    """Input embeddings and (time, row, column) positions of a packed row whose samples may carry
+    images.  ``mm[i] = (pixel_values, image_grid_thw)`` or ``(None, None)`` per sample; segments
+    past ``len(mm)`` (alignment padding) count up from zero.  Sets ``ctx.mrope_positions`` and
+    returns the embeddings (image placeholder rows replaced by the tower's output)."""
+    from .model import embed
+    arch = lm.arch
+    itok, merge = arch.image_token_id, tower.arch.spatial_merge_size
+    host = tokens.detach().cpu()
+    pos, px, grids, off = [], [], [], 0
+    for i, L in enumerate(seq_lens):
+        seg = host[off:off + L]
+        pv, g = mm[i] if i < len(mm) else (None, None)
+        if pv is not None and len(g):
+            g = g.tolist() if torch.is_tensor(g) else [list(v) for v in g]
+            p3, _ = mrope_positions(seg, g, itok, merge)
+            px.append(torch.as_tensor(pv))
+            grids.extend(g)
+        else:
+            p3 = torch.arange(L).view(1, -1).expand(3, -1)
+        pos.append(p3)
+        off += L
+    ctx.mrope_positions = torch.cat(pos, 1).contiguous().to(tokens.device)
+    x = embed(lm.block_by_name["embed"].params, tokens, ctx).to(lm.dtype)
+    if px:
+        with torch.no_grad():
+            img = tower(torch.cat(px, 0).to(tokens.device), grids).to(x.dtype)
+        rows = (tokens == itok).nonzero(as_tuple=True)[0]
+        assert rows.numel() == img.shape[0], f"{rows.numel()} image tokens but {img.shape[0]} image embeddings"
+        x = x.index_put((rows,), img)                  # out of place: the embedding rows stay differentiable
+    return x

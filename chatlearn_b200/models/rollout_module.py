@@ -98,9 +98,14 @@ class RolloutModule(TorchModule):
             gpu_memory_utilization=float(ma.gpu_memory_utilization),
             max_model_len=int(ma.seq_length), seed=int(ma.seed) + 7919 * self.replica_index,
             lockstep_group=self.ep_group if self._ep > 1 else None,
-            use_cuda_graphs=not bool(getattr(ma, "enforce_eager", False)))
+            use_cuda_graphs=not bool(getattr(ma, "enforce_eager", False)),
+            vision=self._build_vision(load))
         from chatlearn_b200.data.tokenizer import load_tokenizer
         self.tokenizer = load_tokenizer(load, self.arch.vocab_size, kind=str(getattr(ma, "tokenizer", "auto")))
+
+    def _build_vision(self, load):
+        from chatlearn_b200.models.nn.vision import build_vision_tower
+        return build_vision_tower(self.arch, self.compute_dtype, self.device, load)
 
     # ------------------------------------------------------------------ generation
     def _sampling_params(self, is_eval: bool, max_tokens: int) -> SamplingParams:
@@ -125,7 +130,11 @@ class RolloutModule(TorchModule):
             b = int(s.get("max_generate_token_length", ma.max_response_tokens_length))
             budgets.append(min(b, ma.seq_length - len(ids)))
         sp = self._sampling_params(is_eval, ma.max_response_tokens_length)
-        return self.engine.generate(prompts, sp, max_new_tokens=budgets)
+        mm = None
+        if self.engine.vision is not None:
+            mm = [{"pixel_values": s["pixel_values"], "image_grid_thw": s["image_grid_thw"]}
+                  if s.get("pixel_values") is not None else None for s in data_list]
+        return self.engine.generate(prompts, sp, max_new_tokens=budgets, mm_inputs=mm)
 
     def postprocess_func(self, data_list: List[Dict], seqs) -> List[Dict]:
         out = []

@@ -1,0 +1,62 @@
+"""GRPO on a vision-language model end to end (CPU/gloo, world_size 2): images are preprocessed by the
+prompt pipeline, generated over by the rollout engine, scored and trained on with a frozen vision tower."""
+import json
+
+from tests.dist_utils import run_ranks
+
+SCRIPT = r'''
+import os, json, time, io, torch
+import numpy as np
+from PIL import Image
+from chatlearn_b200.algorithm.grpo import GrpoAlgorithm, GrpoConfig
+from chatlearn_b200.configs import to_dataclass, resolve
+from chatlearn_b200.data.synthetic import write_jsonl
+
+out = os.environ["OUT_DIR"]
+data = os.path.join(out, "train.jsonl")
+if int(os.environ["RANK"]) == 0:
+    rng = np.random.default_rng(0)
+    rows = []
+    for i in range(8):
+        img = Image.fromarray(rng.integers(0, 255, (40 + 7 * i, 60 + 5 * i, 3), dtype=np.uint8))
+        buf = io.BytesIO(); img.save(buf, format="PNG")
+        ids = [5 + i, 6, 1002, 1000, 1003] + rng.integers(0, 900, 6).tolist()      # one placeholder per image
+        rows.append({"data_source": "synthetic:mod7", "input_ids": ids, "images": [buf.getvalue().hex()],
+                     "reward_model": {"ground_truth": ""}})
+    write_jsonl(rows, data + ".tmp"); os.replace(data + ".tmp", data)
+while not os.path.exists(data): time.sleep(0.05)
+arch = {"preset": "tiny_qwen2_5_vl"}
+cfg = {
+  "runtime_args": {"train_backend": "fsdp", "exp_name": "vl", "output_dir": out, "data_path": data, "model_type": "vlm",
+     "colocation": ["policy", "policy_trainer", "ref_policy"], "num_episode": 2, "sample_per_episode": 16,
+     "train_micro_batch_size": 4, "train_global_batch_size": 16, "num_inference_per_prompt": 2,
+     "save_episode_interval": 0, "max_replay_episode": 2, "log_args_dict": {"log_dir": out}},
+  "models": {
+    "policy_trainer": {"num_gpu": 2, "fsdp_size": 2, "trainable": True, "generation_batch_size": 8, "model_arch": arch,
+       "kl_coef": 0.001, "optimizer": {"lr": 1e-4}, "packing": True, "max_token_in_packing": 512, "save_hf": False},
+    "ref_policy": {"num_gpu": 2, "fsdp_size": 2, "generation_batch_size": 8, "model_arch": arch,
+       "packing": True, "max_token_in_packing": 512},
+    "policy": {"num_gpu": 2, "generation_batch_size": 16, "model_arch": arch, "num_inference_per_prompt": 2,
+       "max_prompt_tokens_length": 128, "max_response_tokens_length": 8, "seq_length": 256, "temperature": 1.0,
+       "kv_block_size": 8, "num_kv_blocks": 512, "ignore_eos": True, "max_pixels": 28 * 28 * 16},
+    "reward": {"num_cpu": 2},
+  }}
+cfg = to_dataclass(GrpoConfig, resolve(cfg))
+algo = GrpoAlgorithm(cfg); algo.validate()
+stats = algo.run()
+eng = algo.engine
+tr = eng.named_models["policy_trainer"]
+pol = eng.named_models["policy"]
+sample_tokens = [len(d) for d in pol._all_datasets[0].data and [s["input_ids"] for s in pol._all_datasets[0].data]]
+print("RESULT " + json.dumps({"rank": int(os.environ["RANK"]), "episodes": len(stats), "train_iters": tr._train_iteration,
+      "has_tower": tr.vision is not None and pol.engine.vision is not None, "prompt_lens": sample_tokens[:3]}))
+'''
+
+
+def test_vision_language_grpo(tmp_path):
+    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path)})
+    res = [json.loads(line[7:]) for o in outs for line in o.splitlines() if line.startswith("RESULT ")]
+    assert len(res) == 2
+    for r in res:
+        assert r["episodes"] == 2 and r["train_iters"] == 2 and r["has_tower"]
+        assert all(n > 11 for n in r["prompt_lens"])          # the single placeholder was expanded to the image's tokens
