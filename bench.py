@@ -132,7 +132,11 @@ def build_config(args, out_dir, data_path, n_gpu):
                                    optimizer={"lr": 2e-6}, save_hf=False,
                                    # fp32 master + Adam shards stay on the GPU (180 GB HBM); the fp32
                                    # gradient buffer is released outside training
-                                   free_gpu_memory={"offload_weights": False, "offload_optimizer_states": False,
+                                   # On one GPU (all optimizer state on it) the bf16 compute copy is dropped
+                                   # outside training and rebuilt by a cast of the resident master weights:
+                                   # 16 GB more KV cache for the rollout.
+                                   free_gpu_memory={"offload_weights": offload and n_gpu == 1,
+                                                    "offload_optimizer_states": False,
                                                     "free_grad_buffers": offload}),
             # the frozen reference weights (16 GB) go to pinned host memory between uses only where the
             # GPU is short of room (1-2 GPUs hold large optimizer shards); from 4 GPUs on they stay resident

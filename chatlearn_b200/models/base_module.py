@@ -426,6 +426,12 @@ class TorchModule(BaseModule):
                 if tag == "grads":
                     for owner, attr in self._tagged(tag):
                         self._release(owner, attr)
+                elif tag == "weights" and self._weights_regenerable():
+                    # the resident fp32 master shards contain the weights: drop the compute copy
+                    # instead of moving it to the host, rebuild it by a cast when it is needed again
+                    for owner, attr in self._tagged(tag):
+                        self._release(owner, attr)
+                    self._weights_dropped = True
                 else:
                     # a frozen model's weights never change: after the first offload the
                     # host copy stays valid and later offloads only drop the device copy
@@ -455,6 +461,9 @@ class TorchModule(BaseModule):
             if on and not self._resident.get(tag, True):
                 if tag == "grads":
                     self._build_grad_buffers()
+                elif tag == "weights" and getattr(self, "_weights_dropped", False):
+                    self._regenerate_weights()
+                    self._weights_dropped = False
                 else:
                     mgr.onload(self._tagged(tag), self._rebind)
                 self._resident[tag] = True
@@ -463,3 +472,10 @@ class TorchModule(BaseModule):
 
     def _build_grad_buffers(self):
         pass
+
+    def _weights_regenerable(self) -> bool:
+        """Whether the compute-dtype weights can be rebuilt on the device from other resident state."""
+        return False
+
+    def _regenerate_weights(self):
+        raise NotImplementedError

@@ -131,6 +131,18 @@ class FSDPModule(TorchModule):
         else:
             setattr(owner, attr, tensor)
 
+    def _weights_regenerable(self) -> bool:
+        fg = self.module_args.free_gpu_memory
+        return (self.trainable and self.state is not None and self.state.symm is None
+                and not fg.offload_optimizer_states and self._resident.get("optimizer", True))
+
+    def _regenerate_weights(self):
+        """bf16 weights = cast of the fp32 master shards (all-gathered over the data-parallel group)."""
+        for s in self.state.states:
+            if s.block.flat is None:
+                s.block.bind(torch.empty(s.block.numel, dtype=s.block.dtype, device=self.device))
+        self.state.rebuild_params()
+
     def _build_grad_buffers(self):
         if self.state is None:
             return

@@ -238,6 +238,18 @@ class ShardedTrainState:
                     s.group.all_gather_flat(s.block.flat, new_shard.clone())
         return norm
 
+    @torch.no_grad()
+    def rebuild_params(self):
+        """Re-create the compute-dtype parameters from the fp32 master shards (cast, then all-gather):
+        what the last optimizer step wrote, bit for bit."""
+        for s in self.states:
+            if s.master is None:
+                continue
+            new_shard = s.block.flat[s.lo:s.hi]
+            new_shard.copy_(s.master)
+            if s.group.size > 1:
+                s.group.all_gather_flat(s.block.flat, new_shard.clone())
+
     # ------------------------------------------------------------------ residency
     def tensors_for(self, tag: str) -> List[List]:
         """(owner object, attribute) pairs of the tensors behind a memory tag."""

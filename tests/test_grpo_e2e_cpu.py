@@ -26,7 +26,8 @@ cfg = {
     "policy_trainer": {"num_gpu": 2, "fsdp_size": 2, "trainable": True, "generation_batch_size": 8,
        "model_arch": {"preset": "tiny_qwen3"}, "kl_coef": 0.001, "optimizer": {"lr": 1e-5},
        "packing": os.environ.get("PACKING", "0") == "1", "max_token_in_packing": 256, "save_hf": True,
-       "free_gpu_memory": {"offload_weights": True, "offload_optimizer_states": True, "free_grad_buffers": True}},
+       "free_gpu_memory": {"offload_weights": True, "offload_optimizer_states": os.environ.get("REGEN", "0") != "1",
+                           "free_grad_buffers": True}},
     "ref_policy": {"num_gpu": 2, "fsdp_size": 2, "generation_batch_size": 8, "model_arch": {"preset": "tiny_qwen3"},
        "free_gpu_memory": {"offload_weights": True}},
     "policy": {"num_gpu": 2, "tensor_model_parallel_size": int(os.environ.get("TP", "1")), "generation_batch_size": 16,
@@ -43,6 +44,7 @@ stats = algo.run()
 eng = algo.engine
 pol, tr = eng.named_models["policy"], eng.named_models["policy_trainer"]
 # after the final sync the rollout weights equal the trainer weights
+tr.onload()
 sd_t = tr.model.hf_state_dict()
 sd_p = pol.model.hf_state_dict()
 maxdiff = 0.0
@@ -98,3 +100,11 @@ def test_resume_continues_from_checkpoint(tmp_path):
         assert r["episodes"] == 1, "only the second episode runs after the resume"
         assert r["consumed"] == 64 and r["maxdiff"] == 0.0
     assert (tmp_path / "save_model" / "policy_trainer" / "2").exists()
+
+
+def test_trainer_weights_dropped_and_rebuilt_from_master(tmp_path):
+    """With the optimizer state resident, the trainer's compute-dtype weights are dropped during rollout and
+    rebuilt from the fp32 master shards (cast + all-gather): the run must be indistinguishable."""
+    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "REGEN": "1"})
+    res = _results(outs)
+    assert len(res) == 2 and all(r["episodes"] == 2 and r["maxdiff"] == 0.0 for r in res)
