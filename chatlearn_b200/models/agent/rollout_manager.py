@@ -84,6 +84,10 @@ class RolloutManager(BaseModule):
         return self.engine_module.num_replica
 
     @property
+    def loader_parallel_size(self):
+        return self.engine_module.loader_parallel_size
+
+    @property
     def is_colocate(self):
         return self.engine_module.is_colocate
 

@@ -238,6 +238,11 @@ class BaseModule:
                                     max_pixels=int(getattr(self._module_args, "max_pixels", 14 * 14 * 4 * 1280)))
         return PromptPipeline(prompts, max_len, tok, enable_thinking=think, raw_chat=self._runtime_args.raw_chat)
 
+    @property
+    def loader_parallel_size(self) -> int:
+        """Number of ways the prompt stream is split (``replica_index`` is this process's part)."""
+        return self.num_replica
+
     def build_all_dataset(self, prompts_list: List[List[Dict]], is_eval: bool = False):
         return [self.build_dataset(p, is_eval) for p in prompts_list]
 
@@ -249,10 +254,10 @@ class BaseModule:
             data_ratio=self._runtime_args.data_ratio, consumed_samples=self._consumed_samples,
             num_inference_per_prompt=n, shuffle=self._runtime_args.data_shuffle and not is_eval,
             is_eval=is_eval, data_parallel_rank=self.replica_index,
-            data_parallel_size=self.num_replica, drop_last="cycle",
+            data_parallel_size=self.loader_parallel_size, drop_last="cycle",
             data_rerank=self._runtime_args.data_rerank, seed=int(getattr(self._module_args, "seed", 0)))
         loader = RLHFDataLoader(datasets, sampler, data_parallel_rank=self.replica_index,
-                                data_parallel_size=self.num_replica, num_inference_per_prompt=n)
+                                data_parallel_size=self.loader_parallel_size, num_inference_per_prompt=n)
         if is_eval:
             self._eval_dataloader, self._eval_data_iter = loader, iter(loader)
             self._all_eval_datasets = datasets

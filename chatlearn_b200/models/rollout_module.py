@@ -70,6 +70,11 @@ class RolloutModule(TorchModule):
         return self._num_replica
 
     @property
+    def loader_parallel_size(self) -> int:
+        # every expert-parallel rank of a replica reads its own part of the prompt stream
+        return self.data_parallel_size
+
+    @property
     def compute_dtype(self):
         return torch.bfloat16 if self.device.type == "cuda" else torch.float32
 

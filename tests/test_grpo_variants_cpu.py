@@ -22,7 +22,7 @@ if int(os.environ["RANK"]) == 0:
         write_jsonl(make_prompts(8, 16, 32, 512, seed=0, data_source="synthetic:mod7"), data + ".tmp")
     os.replace(data + ".tmp", data)
 while not os.path.exists(data): time.sleep(0.05)
-arch = {"preset": "tiny_llama"}
+arch = {"preset": "tiny_moe" if mode == "moe" else "tiny_llama"}
 cfg = {
   "runtime_args": {"train_backend": "fsdp", "exp_name": mode, "output_dir": out, "data_path": data,
      "colocation": ["policy", "policy_trainer", "ref_policy"],
@@ -38,6 +38,9 @@ cfg = {
        "kv_block_size": 8, "num_kv_blocks": 512, "ignore_eos": True, "tokenizer": "byte"},
     "reward": {"num_cpu": 2},
   }}
+if mode == "moe":
+    # expert-parallel rollout: each of the two ranks hosts half of the experts and decodes its own sequences
+    cfg["models"]["policy"].update(expert_model_parallel_size=2, tokenizer="null")
 if mode == "partial":
     cfg["runtime_args"]["use_partial_rollout"] = True
     cfg["models"]["partial_rollout_manager"] = {"num_cpu": 1, "max_rollout_round": 2, "rollout_ratio": [0.5, 0.5],
@@ -79,3 +82,9 @@ def test_agent_through_rollout_manager(tmp_path):
     assert len(res) == 2 and all(r["episodes"] == 3 and r["train_iters"] == 3 for r in res)
     keys = set().union(*[set(m) for m in _metrics(tmp_path)])
     assert any(k.endswith("num_turns") for k in keys)
+
+
+def test_moe_model_with_expert_parallel_rollout(tmp_path):
+    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "MODE": "moe"})
+    res = _results(outs)
+    assert len(res) == 2 and all(r["episodes"] == 3 and r["train_iters"] == 3 for r in res)
