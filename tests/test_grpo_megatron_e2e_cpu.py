@@ -13,13 +13,14 @@ from chatlearn_b200.data.synthetic import make_prompts, write_jsonl
 out = os.environ["OUT_DIR"]
 data = os.path.join(out, "train.jsonl")
 if int(os.environ["RANK"]) == 0:
-    write_jsonl(make_prompts(8, 8, 24, 1024, seed=0, data_source="synthetic:mod7"), data + ".tmp")
+    write_jsonl(make_prompts(8, 8, 24, 256, seed=0, data_source="synthetic:mod7"), data + ".tmp")
     os.replace(data + ".tmp", data)
 while not os.path.exists(data): time.sleep(0.05)
-arch = {"preset": "tiny_qwen3"}
+arch = {"preset": os.environ.get("PRESET", "tiny_qwen3")}
 mcfg = {"num_layers": 2, "hidden_size": 256, "num_attention_heads": 4, "ffn_hidden_size": 704,
         "max_position_embeddings": 512, "kv_channels": 64}
-par = {"tensor_model_parallel_size": int(os.environ.get("TP", "2")), "pipeline_model_parallel_size": int(os.environ.get("PP", "1"))}
+par = {"tensor_model_parallel_size": int(os.environ.get("TP", "2")), "pipeline_model_parallel_size": int(os.environ.get("PP", "1")),
+       "context_parallel_size": int(os.environ.get("CP", "1")), "expert_model_parallel_size": int(os.environ.get("EP", "1"))}
 cfg = {
   "runtime_args": {"train_backend": "megatron", "exp_name": "mg", "output_dir": out, "data_path": data,
      "colocation": ["policy", "policy_trainer", "ref_policy"], "num_episode": 2, "sample_per_episode": 16,
@@ -33,7 +34,8 @@ cfg = {
        megatron_model_cfg=dict(mcfg), max_prompt_tokens_length=64, max_response_tokens_length=16),
     "policy": {"num_gpu": 2, "generation_batch_size": 16, "model_arch": arch, "num_inference_per_prompt": 2,
        "max_prompt_tokens_length": 64, "max_response_tokens_length": 16, "seq_length": 128, "temperature": 1.0,
-       "kv_block_size": 8, "num_kv_blocks": 256, "ignore_eos": True},
+       "kv_block_size": 8, "num_kv_blocks": 256, "ignore_eos": True,
+       "expert_model_parallel_size": int(os.environ.get("ROLLOUT_EP", "1"))},
     "reward": {"num_cpu": 2},
   }}
 cfg = to_dataclass(GrpoConfig, resolve(cfg))
@@ -67,4 +69,18 @@ def test_grpo_tp2_trainer(tmp_path):
 
 def test_grpo_pp2_trainer(tmp_path):
     res = _res(run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "TP": "1", "PP": "2"})[0])
+    assert len(res) == 2 and all(r["episodes"] == 2 and r["maxdiff"] == 0.0 for r in res)
+
+
+def test_grpo_moe_ep2_trainer_and_ep2_rollout(tmp_path):
+    """Expert-parallel trainer (experts re-homed over two ranks) feeding an expert-parallel rollout."""
+    env = {"OUT_DIR": str(tmp_path), "PRESET": "tiny_moe", "TP": "1", "EP": "2", "ROLLOUT_EP": "2"}
+    res = _res(run_ranks(SCRIPT, 2, env=env)[0])
+    assert len(res) == 2 and all(r["episodes"] == 2 and r["train_iters"] == 2 and r["maxdiff"] == 0.0 for r in res)
+
+
+def test_grpo_mla_moe_cp2_trainer(tmp_path):
+    """MLA attention + sigmoid-routed MoE with context parallelism 2 in the trainer."""
+    env = {"OUT_DIR": str(tmp_path), "PRESET": "tiny_mla_moe", "TP": "1", "CP": "2"}
+    res = _res(run_ranks(SCRIPT, 2, env=env)[0])
     assert len(res) == 2 and all(r["episodes"] == 2 and r["maxdiff"] == 0.0 for r in res)
