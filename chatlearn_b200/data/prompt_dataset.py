@@ -67,7 +67,8 @@ class VLPromptPipeline(PromptPipeline):
 
     def __init__(self, data_list, max_prompt_tokens_length, tokenizer=None, processor=None,
                  enable_thinking=False, raw_chat=False, image_token_id=None, merge_size: int = 2,
-                 min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280):
+                 min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280, patch_size: int = 14,
+                 temporal_patch_size: int = 2, mean=None, std=None):
         # the length filter runs after the placeholder expansion, so filter here, not in the base class
         super().__init__(data_list, 1 << 30, tokenizer, enable_thinking, raw_chat)
         from chatlearn_b200.data.vision_utils import expand_image_tokens, process_images
@@ -79,8 +80,11 @@ class VLPromptPipeline(PromptPipeline):
                 if k in item:
                     s[k] = item[k]
             if item.get("images") and s.get("pixel_values") is None:
-                pv, grid = process_images(item["images"], merge_size=merge_size, min_pixels=min_pixels,
-                                          max_pixels=max_pixels)
+                kw = dict(merge_size=merge_size, min_pixels=min_pixels, max_pixels=max_pixels, patch_size=patch_size,
+                          temporal_patch_size=temporal_patch_size)
+                if mean is not None:
+                    kw.update(mean=mean, std=std)
+                pv, grid = process_images(item["images"], **kw)
                 s["pixel_values"], s["image_grid_thw"] = pv, grid.tolist()
             if s.get("pixel_values") is not None and "input_ids" in s and image_token_id is not None:
                 import torch

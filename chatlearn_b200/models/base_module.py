@@ -235,6 +235,11 @@ class BaseModule:
             return VLPromptPipeline(prompts, max_len, tok, enable_thinking=think, raw_chat=self._runtime_args.raw_chat,
                                     image_token_id=getattr(arch, "image_token_id", None),
                                     merge_size=int(vc.get("spatial_merge_size", 2)),
+                                    patch_size=int(vc.get("patch_size", 14)),
+                                    temporal_patch_size=int(vc.get("temporal_patch_size", 2)),
+                                    # Qwen3-VL normalises to [-1, 1]; Qwen2.5-VL uses the CLIP statistics
+                                    mean=(0.5, 0.5, 0.5) if "num_position_embeddings" in vc else None,
+                                    std=(0.5, 0.5, 0.5) if "num_position_embeddings" in vc else None,
                                     max_pixels=int(getattr(self._module_args, "max_pixels", 14 * 14 * 4 * 1280)))
         return PromptPipeline(prompts, max_len, tok, enable_thinking=think, raw_chat=self._runtime_args.raw_chat)
 

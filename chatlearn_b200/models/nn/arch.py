@@ -50,6 +50,7 @@ class ModelArch:
     v_head_dim: int = 0
     # vision-language models: rotary sections (time, row, column) and the vision tower's config
     mrope_section: Optional[List[int]] = None
+    mrope_interleaved: bool = False      # Qwen3-VL frequency layout
     vision_config: Optional[Dict[str, Any]] = None
     image_token_id: Optional[int] = None
     # reward-model head
@@ -132,10 +133,11 @@ class ModelArch:
             outer = {k: v for k, v in d.items() if k != "text_config"}
             d = {**outer, **d["text_config"]}
             d["model_type"] = {"qwen2_5_vl": "qwen2", "qwen2_5_vl_text": "qwen2", "qwen2_vl": "qwen2",
-                               "qwen3_vl": "qwen3", "qwen3_vl_text": "qwen3"}.get(d.get("model_type"), d.get("model_type"))
+                               "qwen3_vl": "qwen3", "qwen3_vl_text": "qwen3", "qwen3_vl_moe": "qwen3_moe",
+                               "qwen3_vl_moe_text": "qwen3_moe"}.get(d.get("model_type"), d.get("model_type"))
         rs = d.get("rope_scaling") or d.get("rope_parameters") or {}
         if isinstance(rs, dict) and rs.get("mrope_section"):
-            d = dict(d, mrope_section=list(rs["mrope_section"]))
+            d = dict(d, mrope_section=list(rs["mrope_section"]), mrope_interleaved=bool(rs.get("mrope_interleaved", False)))
             if "rope_theta" in rs and "rope_theta" not in d:
                 d["rope_theta"] = rs["rope_theta"]
         for k, v in d.items():

@@ -147,6 +147,7 @@ class FwdCtx:
     pending: Any = None                    # sub-layer output (or un-reduced TP partial) not yet added to the residual stream
     fuse_add_norm: bool = False            # inference: fuse residual adds with the following RMSNorm (in-place stream)
     mrope_positions: Optional[torch.Tensor] = None   # [3, T] time/row/column positions (vision-language models)
+    deepstack: Any = None                  # (rows, [features per early layer]): vision taps added after layer i (Qwen3-VL)
 
 
 def _tp_reduce(x, ctx):
@@ -197,8 +198,8 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
             # vision-language models: time / row / column positions per rotary section
             if p.get("q_norm") is not None:
                 q, k = ops.rmsnorm(q, p["q_norm"], arch.rms_norm_eps), ops.rmsnorm(k, p["k_norm"], arch.rms_norm_eps)
-            q = ops.rope_mrope(q, ctx.mrope_positions, arch.rope_theta, arch.mrope_section)
-            k = ops.rope_mrope(k, ctx.mrope_positions, arch.rope_theta, arch.mrope_section)
+            q = ops.rope_mrope(q, ctx.mrope_positions, arch.rope_theta, arch.mrope_section, arch.mrope_interleaved)
+            k = ops.rope_mrope(k, ctx.mrope_positions, arch.rope_theta, arch.mrope_section, arch.mrope_interleaved)
         else:
             q, k = ops.qk_norm_rope(q, k, p.get("q_norm"), p.get("k_norm"), arch.rms_norm_eps,
                                     ctx.attn_positions if ctx.attn_positions is not None else ctx.positions,
@@ -412,6 +413,11 @@ class CausalLM:
                 x = layer_hook(l, p, x, ctx)
             else:
                 x = decoder_layer(self.arch, p, x, ctx, l)
+            if ctx.deepstack is not None and l < len(ctx.deepstack[1]):
+                # vision features of tap l join the residual stream at the image rows (a sum, so it
+                # commutes with a sub-layer output that is still pending)
+                rows, taps = ctx.deepstack
+                x = x.index_add(0, rows, taps[l].to(x.dtype))
         if "head" in self.block_by_name:
             norm_w = self.block_by_name["head"].params["norm"]
             if ctx.pending is not None:

@@ -201,6 +201,152 @@ class VisionTower:
     __call__ = forward
 
 
+# ---------------------------------------------------------------------------------------------
+# Qwen3-VL: learned position table (bilinear interpolation to the image grid), LayerNorm blocks with
+# a GELU MLP, attention over whole frames (no windows), and "deep-stack" taps: the outputs of a few
+# blocks go through their own mergers and are added to the language model's early hidden states.
+# ---------------------------------------------------------------------------------------------
+@dataclass
+class Vision3Arch:
+    depth: int = 27
+    hidden_size: int = 1152
+    intermediate_size: int = 4304
+    num_heads: int = 16
+    in_channels: int = 3
+    patch_size: int = 16
+    temporal_patch_size: int = 2
+    spatial_merge_size: int = 2
+    out_hidden_size: int = 4096
+    num_position_embeddings: int = 2304
+    deepstack_visual_indexes: List[int] = field(default_factory=lambda: [8, 16, 24])
+    hidden_act: str = "gelu_pytorch_tanh"
+
+    @property
+    def patch_dim(self) -> int:
+        return self.in_channels * self.temporal_patch_size * self.patch_size * self.patch_size
+
+    @property
+    def merge_unit(self) -> int:
+        return self.spatial_merge_size ** 2
+
+    @classmethod
+    def from_hf_dict(cls, d: Dict) -> "Vision3Arch":
+        keys = {f for f in cls.__dataclass_fields__}
+        return cls(**{k: v for k, v in d.items() if k in keys})
+
+
+def vision3_param_shapes(a: Vision3Arch) -> Dict[str, Tuple[int, ...]]:
+    H, I, M = a.hidden_size, a.intermediate_size, a.hidden_size * a.merge_unit
+    out = {"visual.patch_embed.proj.weight": (H, a.patch_dim), "visual.patch_embed.proj.bias": (H,),
+           "visual.pos_embed.weight": (a.num_position_embeddings, H)}
+    for i in range(a.depth):
+        b = f"visual.blocks.{i}."
+        out.update({b + "norm1.weight": (H,), b + "norm1.bias": (H,), b + "norm2.weight": (H,), b + "norm2.bias": (H,),
+                    b + "attn.qkv.weight": (3 * H, H), b + "attn.qkv.bias": (3 * H,),
+                    b + "attn.proj.weight": (H, H), b + "attn.proj.bias": (H,),
+                    b + "mlp.linear_fc1.weight": (I, H), b + "mlp.linear_fc1.bias": (I,),
+                    b + "mlp.linear_fc2.weight": (H, I), b + "mlp.linear_fc2.bias": (H,)})
+
+    def merger(prefix, norm_dim):
+        out.update({prefix + "norm.weight": (norm_dim,), prefix + "norm.bias": (norm_dim,),
+                    prefix + "linear_fc1.weight": (M, M), prefix + "linear_fc1.bias": (M,),
+                    prefix + "linear_fc2.weight": (a.out_hidden_size, M), prefix + "linear_fc2.bias": (a.out_hidden_size,)})
+    merger("visual.merger.", H)
+    for j in range(len(a.deepstack_visual_indexes)):
+        merger(f"visual.deepstack_merger_list.{j}.", M)
+    return out
+
+
+class VisionTower3(VisionTower):
+    """Returns ``(image embeddings, [deep-stack features per tap])``, all ``[N / merge², out_hidden]``."""
+
+    def __init__(self, arch: Vision3Arch, dtype=torch.float32, device="cpu"):  # pylint: disable=super-init-not-called
+        self.arch, self.dtype, self.device = arch, dtype, torch.device(device)
+        self.params = {k: torch.zeros(s, dtype=dtype, device=self.device) for k, s in vision3_param_shapes(arch).items()}
+
+    def init_weights(self, seed: int = 0, std: float = 0.02):
+        g = torch.Generator().manual_seed(seed)
+        for k, p in self.params.items():
+            if ".norm" in k and k.endswith(".weight"):
+                p.fill_(1.0)
+            elif k.endswith(".bias"):
+                p.zero_()
+            else:
+                p.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
+        return self
+
+    def hf_state_dict(self):
+        a = self.arch
+        out = dict(self.params)
+        out["visual.patch_embed.proj.weight"] = self.params["visual.patch_embed.proj.weight"].view(
+            a.hidden_size, a.in_channels, a.temporal_patch_size, a.patch_size, a.patch_size)
+        return out
+
+    def _pos_table(self, grid) -> torch.Tensor:
+        """Learned position embedding of every patch: the square table is sampled bilinearly at the
+        image's own grid, then put into merge-block order."""
+        a = self.arch
+        side = int(round(a.num_position_embeddings ** 0.5))
+        table = self.params["visual.pos_embed.weight"].float()
+        out, m = [], a.spatial_merge_size
+        for t, h, w in grid:
+            ys, xs = torch.linspace(0, side - 1, h, device=table.device), torch.linspace(0, side - 1, w, device=table.device)
+            y0, x0 = ys.long(), xs.long()
+            y1, x1 = (y0 + 1).clamp(max=side - 1), (x0 + 1).clamp(max=side - 1)
+            dy, dx = (ys - y0)[:, None, None], (xs - x0)[None, :, None]
+            e = lambda yy, xx: table[(yy[:, None] * side + xx[None, :])]          # noqa: E731  [h, w, H]
+            pe = e(y0, x0) * (1 - dy) * (1 - dx) + e(y0, x1) * (1 - dy) * dx + e(y1, x0) * dy * (1 - dx) + e(y1, x1) * dy * dx
+            pe = pe.view(h // m, m, w // m, m, -1).permute(0, 2, 1, 3, 4).reshape(h * w, -1)
+            out.append(pe.repeat(t, 1))
+        return torch.cat(out, 0)
+
+    def _merge(self, x, prefix, post_norm: bool):
+        a, P = self.arch, self.params
+        M = a.hidden_size * a.merge_unit
+        if post_norm:
+            x = F.layer_norm(x.view(-1, M), (M,), P[prefix + "norm.weight"], P[prefix + "norm.bias"], 1e-6)
+        else:
+            x = F.layer_norm(x, (a.hidden_size,), P[prefix + "norm.weight"], P[prefix + "norm.bias"], 1e-6).view(-1, M)
+        return self._lin(F.gelu(self._lin(x, prefix + "linear_fc1")), prefix + "linear_fc2")
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw):
+        a, P = self.arch, self.params
+        grid = [tuple(int(v) for v in g) for g in (grid_thw.tolist() if torch.is_tensor(grid_thw) else grid_thw)]
+        x = ops.linear(pixel_values.to(self.dtype), P["visual.patch_embed.proj.weight"], P["visual.patch_embed.proj.bias"])
+        x = x + self._pos_table(grid).to(x.dtype)
+        N, H, nh = x.shape[0], a.hidden_size, a.num_heads
+        d = H // nh
+        rc = patch_positions(grid, a.spatial_merge_size).to(x.device)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, d // 2, 2, dtype=torch.float32, device=x.device) / (d // 2)))
+        ang = torch.cat([rc[:, :1].float() * inv, rc[:, 1:].float() * inv], -1)
+        emb = torch.cat([ang, ang], -1)
+        cos, sin = emb.cos()[:, None, :], emb.sin()[:, None, :]
+        cu = [0]
+        for t, h, w in grid:
+            for _ in range(t):
+                cu.append(cu[-1] + h * w)
+        cu_t = torch.tensor(cu, dtype=torch.int32, device=x.device)
+        max_len = max(h * w for _, h, w in grid)
+        act = (lambda z: F.gelu(z, approximate="tanh")) if "tanh" in a.hidden_act else F.gelu
+        taps = []
+        for i in range(a.depth):
+            b = f"visual.blocks.{i}."
+            h_ = F.layer_norm(x, (H,), P[b + "norm1.weight"], P[b + "norm1.bias"], 1e-6)
+            qkv = self._lin(h_, b + "attn.qkv").view(N, 3, nh, d)
+            q, k, v = qkv[:, 0].float(), qkv[:, 1].float(), qkv[:, 2]
+            q = (q * cos + _rotate_half(q) * sin).to(x.dtype)
+            k = (k * cos + _rotate_half(k) * sin).to(x.dtype)
+            o = ops.attention_varlen(q.contiguous(), k.contiguous(), v.contiguous(), cu_t, max_len, d ** -0.5, False)
+            x = x + self._lin(o.reshape(N, H), b + "attn.proj")
+            h_ = F.layer_norm(x, (H,), P[b + "norm2.weight"], P[b + "norm2.bias"], 1e-6)
+            x = x + self._lin(act(self._lin(h_, b + "mlp.linear_fc1")), b + "mlp.linear_fc2")
+            if i in a.deepstack_visual_indexes:
+                taps.append(self._merge(x, f"visual.deepstack_merger_list.{a.deepstack_visual_indexes.index(i)}.", True))
+        return self._merge(x, "visual.merger.", False), taps
+
+    __call__ = forward
+
+
 def mrope_positions(input_ids: torch.Tensor, image_grid_thw, image_token_id: int, merge: int) -> Tuple[torch.Tensor, int]:
     """Three-component (time, row, column) positions of one sequence and the offset that later text
     positions carry: text tokens count up with all components equal; an image occupies a
@@ -239,7 +385,10 @@ def build_vision_tower(arch, dtype, device, load: str = None, seed: int = 4321):
     same on every role, so trainer and rollout agree)."""
     if getattr(arch, "vision_config", None) is None:
         return None
-    tower = VisionTower(VisionArch.from_hf_dict(arch.vision_config), dtype=dtype, device=device)
+    if "deepstack_visual_indexes" in arch.vision_config or "num_position_embeddings" in arch.vision_config:
+        tower = VisionTower3(Vision3Arch.from_hf_dict(arch.vision_config), dtype=dtype, device=device)
+    else:
+        tower = VisionTower(VisionArch.from_hf_dict(arch.vision_config), dtype=dtype, device=device)
     loaded = False
     if load:
         from chatlearn_b200.checkpoint.safetensors_io import SafetensorsDir, has_safetensors
@@ -287,8 +436,14 @@ def multimodal_inputs(lm, tower, tokens: torch.Tensor, seq_lens, mm, ctx):
     x = embed(lm.block_by_name["embed"].params, tokens, ctx).to(lm.dtype)
     if px:
         with torch.no_grad():
-            img = tower(torch.cat(px, 0).to(tokens.device), grids).to(x.dtype)
+            img = tower(torch.cat(px, 0).to(tokens.device), grids)
+        taps = []
+        if isinstance(img, tuple):
+            img, taps = img
+        img = img.to(x.dtype)
         rows = (tokens == itok).nonzero(as_tuple=True)[0]
         assert rows.numel() == img.shape[0], f"{rows.numel()} image tokens but {img.shape[0]} image embeddings"
         x = x.index_put((rows,), img)                  # out of place: the embedding rows stay differentiable
+        if taps:
+            ctx.deepstack = (rows, [t.to(x.dtype) for t in taps])
     return x

@@ -13,7 +13,7 @@ import torch
 
 from .arch import ModelArch
 from .model import CausalLM, FwdCtx
-from .vision import VisionArch, VisionTower, mrope_positions
+from .vision import build_vision_tower, mrope_positions
 
 
 def strip_language_prefix(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
@@ -32,9 +32,9 @@ class VLCausalLM:
         assert arch.vision_config is not None and arch.mrope_section is not None and arch.image_token_id is not None, \
             "a vision-language architecture needs vision_config, mrope_section and image_token_id"
         self.arch = arch
-        self.varch = VisionArch.from_hf_dict(arch.vision_config)
         self.lm = CausalLM(arch, dtype=dtype, device=device, **lm_kwargs)
-        self.visual = VisionTower(self.varch, dtype=dtype, device=device)
+        self.visual = build_vision_tower(arch, dtype, device)
+        self.varch = self.visual.arch
 
     def init_weights(self, seed: int = 0):
         self.lm.init_weights(seed)
@@ -49,22 +49,22 @@ class VLCausalLM:
         pos, _ = mrope_positions(input_ids.cpu(), image_grid_thw, self.arch.image_token_id, self.varch.spatial_merge_size)
         return pos.to(input_ids.device)
 
-    def embed(self, tokens: torch.Tensor, ctx: FwdCtx, pixel_values: Optional[torch.Tensor], image_grid_thw) -> torch.Tensor:
+    def hidden_states(self, tokens, ctx: FwdCtx, pixel_values=None, image_grid_thw=None, layer_hook=None):
+        """``tokens`` is a packed row; ``ctx.mrope_positions`` must hold the [3, T] positions (see
+        ``packed_positions``).  Image placeholder rows take the tower's embeddings (and, for towers with
+        deep-stack taps, the early layers add the tap features at those rows)."""
         from .model import embed
         x = embed(self.lm.block_by_name["embed"].params, tokens, ctx).to(self.lm.dtype)
         if pixel_values is not None and pixel_values.numel():
-            img = self.visual(pixel_values.to(x.device), image_grid_thw).to(x.dtype)
-            mask = tokens == self.arch.image_token_id
-            assert int(mask.sum()) == img.shape[0], \
-                f"{int(mask.sum())} image placeholder tokens but {img.shape[0]} image embeddings"
-            x = x.clone()
-            x[mask] = img
-        return x
-
-    def hidden_states(self, tokens, ctx: FwdCtx, pixel_values=None, image_grid_thw=None, layer_hook=None):
-        """``tokens`` is a packed row; ``ctx.mrope_positions`` must hold the [3, T] positions (see
-        ``packed_positions``)."""
-        x = self.embed(tokens, ctx, pixel_values, image_grid_thw)
+            img = self.visual(pixel_values.to(x.device), image_grid_thw)
+            taps = []
+            if isinstance(img, tuple):
+                img, taps = img
+            rows = (tokens == self.arch.image_token_id).nonzero(as_tuple=True)[0]
+            assert rows.numel() == img.shape[0], f"{rows.numel()} image placeholder tokens but {img.shape[0]} image embeddings"
+            x = x.index_put((rows,), img.to(x.dtype))
+            if taps:
+                ctx.deepstack = (rows, taps)
         return self.lm.hidden_states(tokens, ctx, layer_hook, x=x)
 
     def packed_positions(self, seqs: Sequence[torch.Tensor], grids: Sequence) -> torch.Tensor:

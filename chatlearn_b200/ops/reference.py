@@ -63,15 +63,23 @@ def rope(x: torch.Tensor, positions: torch.Tensor, theta: float,
     return out
 
 
-def rope_mrope(x: torch.Tensor, positions3: torch.Tensor, theta: float, sections) -> torch.Tensor:
+def rope_mrope(x: torch.Tensor, positions3: torch.Tensor, theta: float, sections, interleaved: bool = False) -> torch.Tensor:
     """Multimodal rotary embedding (Qwen2-VL "mrope") on ``x [T, heads, d]``: frequency ``f`` of the
     ``d/2`` rotary frequencies takes its angle from the time, row or column position according to
-    the section it falls in (``sections`` = three sizes summing to ``d/2``); ``positions3 [3, T]``."""
+    the section it falls in (``sections`` = three sizes summing to ``d/2``); ``positions3 [3, T]``.
+    ``interleaved`` (Qwen3-VL): row and column frequencies are every third one (offsets 1 and 2) up to
+    three times their section size, everything else is time."""
     d = x.shape[-1]
     half = d // 2
     assert sum(sections) == half, "mrope sections must sum to head_dim / 2"
     inv = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32, device=x.device) / d))
-    comp = torch.repeat_interleave(torch.arange(3, device=x.device), torch.tensor(list(sections), device=x.device))
+    if interleaved:
+        f = torch.arange(half, device=x.device)
+        comp = torch.zeros(half, dtype=torch.long, device=x.device)
+        comp[(f % 3 == 1) & (f < 3 * sections[1])] = 1
+        comp[(f % 3 == 2) & (f < 3 * sections[2])] = 2
+    else:
+        comp = torch.repeat_interleave(torch.arange(3, device=x.device), torch.tensor(list(sections), device=x.device))
     pos = positions3.to(torch.float32)[comp]                     # [d/2, T]: the position each frequency uses
     ang = (pos * inv[:, None]).t()                               # [T, d/2]
     c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]

@@ -210,7 +210,12 @@ class RolloutEngine:
             ctx.mrope_positions = xfer.to_device(torch.cat(pos3, 1).contiguous(), dev, "pos3")
             if patch_rows:
                 src = torch.stack([s.mm["embeds"][o] for s, o in patch_src])
-                self._embed_patch = (torch.tensor(patch_rows, dtype=torch.long, device=dev), src)
+                rows_t = torch.tensor(patch_rows, dtype=torch.long, device=dev)
+                self._embed_patch = (rows_t, src)
+                levels = max(len(s.mm["deepstack"]) for s, _ in patch_src)
+                if levels:
+                    ctx.deepstack = (rows_t, [torch.stack([s.mm["deepstack"][lv][o] for s, o in patch_src])
+                                              for lv in range(levels)])
         return t(toks, torch.long, "toks"), ctx, t(last_rows, torch.long, "last")
 
     def _symm(self):
@@ -422,13 +427,18 @@ class RolloutEngine:
         grid = mm["image_grid_thw"]
         grid = grid.tolist() if torch.is_tensor(grid) else [list(g) for g in grid]
         px = torch.as_tensor(mm["pixel_values"]).to(self.device)
-        embeds = self.vision(px, grid).to(self.model.dtype)
+        embeds = self.vision(px, grid)
+        taps = []
+        if isinstance(embeds, tuple):            # towers with deep-stack taps (Qwen3-VL)
+            embeds, taps = embeds
+        embeds = embeds.to(self.model.dtype)
         itok = self.arch.image_token_id
         where = [j for j, tkn in enumerate(s.prompt) if tkn == itok]
         assert len(where) == embeds.shape[0], \
             f"{len(where)} image placeholder tokens in the prompt but {embeds.shape[0]} image embeddings"
         pos3, delta = mrope_positions(torch.tensor(s.prompt), grid, itok, self.vision.arch.spatial_merge_size)
-        s.mm = {"embeds": embeds, "pos3": pos3, "ordinal": {j: o for o, j in enumerate(where)}}
+        s.mm = {"embeds": embeds, "pos3": pos3, "ordinal": {j: o for o, j in enumerate(where)},
+                "deepstack": [t.to(self.model.dtype) for t in taps]}
         s.rope_delta = int(delta)
 
     def generate(self, prompts: List[List[int]], sampling: Any, eos_id: Optional[int] = None,

@@ -135,3 +135,73 @@ def test_rollout_engine_generates_like_hf_with_an_image():
     assert seqs[0].rope_delta == -8                    # 12 image tokens advance the position by max(3, 4)
     assert seqs[0].output == want, (seqs[0].output, want)
     assert seqs[1].output == want_text
+
+
+def _hf3():
+    from transformers import Qwen3VLConfig, Qwen3VLForConditionalGeneration
+    torch.manual_seed(0)
+    cfg = Qwen3VLConfig(
+        text_config=dict(vocab_size=1024, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=32, max_position_embeddings=512, rope_theta=10000.0,
+                         rope_scaling={"rope_type": "default", "mrope_section": [4, 6, 6], "mrope_interleaved": True}),
+        vision_config=dict(depth=3, hidden_size=64, intermediate_size=96, num_heads=4, patch_size=16, spatial_merge_size=2,
+                           temporal_patch_size=2, out_hidden_size=128, num_position_embeddings=64, deepstack_visual_indexes=[0, 2]),
+        image_token_id=1000, video_token_id=1001, vision_start_token_id=1002, vision_end_token_id=1003)
+    m = Qwen3VLForConditionalGeneration(cfg).eval().float()
+    for p in m.parameters():
+        if p.dim() == 1:
+            torch.nn.init.normal_(p, mean=0.5, std=0.2)
+    return cfg, m
+
+
+def test_qwen3_vl_tower_and_logits_match_hf():
+    from chatlearn_b200.models.nn.model import packed_ctx
+    from chatlearn_b200.models.nn.vision import VisionTower3
+    from chatlearn_b200.models.nn.vl_model import VLCausalLM
+    cfg, hf = _hf3()
+    arch = _arch(cfg)
+    assert arch.mrope_interleaved and arch.qk_norm and not arch.attention_bias
+    model = VLCausalLM(arch)
+    assert isinstance(model.visual, VisionTower3)
+    model.load_hf_state_dict(hf.state_dict())
+    grid = torch.tensor([[1, 6, 8], [1, 4, 4]])
+    n = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+    px = torch.randn(n, model.varch.patch_dim)
+    with torch.no_grad():
+        want_v = hf.model.visual(px, grid_thw=grid)
+        got_v, taps = model.visual(px, grid)
+    assert torch.allclose(got_v, want_v.pooler_output, rtol=1e-4, atol=1e-4)
+    assert len(taps) == 2 and all(torch.allclose(a, b, rtol=1e-4, atol=1e-4) for a, b in zip(taps, want_v.deepstack_features))
+    ids = torch.tensor([3, 4, 1002] + [1000] * 12 + [1003, 20, 21, 1002] + [1000] * 4 + [1003, 22, 23])
+    with torch.no_grad():
+        want = hf(input_ids=ids[None], pixel_values=px, image_grid_thw=grid, mm_token_type_ids=(ids[None] == 1000).long()).logits[0]
+        ctx, _ = packed_ctx([ids.numel()], "cpu")
+        ctx.mrope_positions = model.positions(ids, grid)
+        got = model.logits(ids, ctx, px, grid)
+    assert torch.allclose(got, want, rtol=3e-4, atol=3e-4), (got - want).abs().max()
+
+
+def test_qwen3_vl_rollout_engine_generates_like_hf():
+    from chatlearn_b200.models.nn.model import CausalLM
+    from chatlearn_b200.models.nn.vision import build_vision_tower
+    from chatlearn_b200.models.nn.vl_model import strip_language_prefix
+    from chatlearn_b200.rollout import RolloutEngine, SamplingParams
+    cfg, hf = _hf3()
+    arch = _arch(cfg)
+    arch.eos_token_id = 1023
+    lm = CausalLM(arch)
+    lm.load_hf_state_dict(strip_language_prefix(hf.state_dict()))
+    tower = build_vision_tower(arch, torch.float32, "cpu")
+    tower.load_hf_state_dict(hf.state_dict())
+    eng = RolloutEngine(lm, block_size=8, num_blocks=64, max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128,
+                        vision=tower)
+    grid = torch.tensor([[1, 6, 8]])
+    ids = [3, 4, 1002] + [1000] * 12 + [1003, 20, 21, 22, 23]
+    px = torch.randn(48, tower.arch.patch_dim)
+    with torch.no_grad():
+        want = hf.generate(input_ids=torch.tensor([ids]), pixel_values=px, image_grid_thw=grid,
+                           mm_token_type_ids=(torch.tensor([ids]) == 1000).long(),
+                           max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(ids):].tolist()
+    seqs = eng.generate([ids], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True),
+                        mm_inputs=[{"pixel_values": px, "image_grid_thw": grid}])
+    assert seqs[0].output == want, (seqs[0].output, want)
