@@ -319,6 +319,42 @@ at::Tensor symm_ar_residual_rmsnorm(const std::vector<int64_t>& part_ptrs, const
   return hout;
 }
 
+// ------------------------------------------------------------------ all-gather / all-to-all by pushing
+// Chunk p of `src` (chunk 0 for an all-gather) goes to slot `rank` of peer p's exchange buffer:
+// plain 16-byte stores over NVLink, one grid column per destination.  The caller brackets the
+// kernel with a flag barrier and copies its own buffer out afterwards.
+__global__ void push_chunks_kernel(const uint4* __restrict__ src, PeerTable dst, int64_t chunk_vec, int64_t src_stride_vec,
+                                   int rank, int world) {
+  const int p = blockIdx.y;
+  if (p >= world) return;
+  const uint4* s = src + (int64_t)p * src_stride_vec;
+  uint4* d = static_cast<uint4*>(dst.ptr[p]) + (int64_t)rank * chunk_vec;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < chunk_vec; i += (int64_t)gridDim.x * blockDim.x) d[i] = s[i];
+}
+
+__global__ void group_barrier_kernel(PeerTable flags, uint32_t* expect, int slot, int num_slots, int rank, int world) {
+  cta_barrier(flags, expect, slot, num_slots, rank, world);
+}
+
+// src: contiguous bytes; all_to_all: `world` chunks of chunk_bytes each (chunk p -> peer p); all-gather: one chunk.
+void symm_push_chunks(const at::Tensor& src, const std::vector<int64_t>& dst_ptrs, int64_t chunk_bytes, bool all_to_all,
+                      int64_t rank) {
+  const int world = (int)dst_ptrs.size();
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && chunk_bytes % 16 == 0 && (uintptr_t)src.data_ptr() % 16 == 0,
+              "push_chunks: contiguous, 16-byte aligned, chunk a multiple of 16 bytes");
+  TORCH_CHECK((int64_t)src.numel() * src.element_size() >= chunk_bytes * (all_to_all ? world : 1), "push_chunks: source too small");
+  if (chunk_bytes == 0) return;
+  const int64_t vec = chunk_bytes / 16;
+  const int gx = (int)std::min<int64_t>((vec + 255) / 256, 148 * 4 / world + 1);
+  push_chunks_kernel<<<dim3(gx, world), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      static_cast<const uint4*>(src.data_ptr()), table_from(dst_ptrs), vec, all_to_all ? vec : 0, (int)rank, world);
+}
+
+void symm_group_barrier(const std::vector<int64_t>& flag_ptrs, at::Tensor expect, int64_t slot, int64_t num_slots, int64_t rank) {
+  group_barrier_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(table_from(flag_ptrs), reinterpret_cast<uint32_t*>(expect.data_ptr()),
+                                                                      (int)slot, (int)num_slots, (int)rank, (int)flag_ptrs.size());
+}
+
 // Single-rank form of the kernel above: resid += delta; returns rmsnorm(resid) * w (undefined when w is absent).
 at::Tensor add_residual_rmsnorm(at::Tensor resid, const at::Tensor& delta, const c10::optional<at::Tensor>& w, double eps) {
   TORCH_CHECK(resid.scalar_type() == at::kBFloat16 && resid.is_contiguous() && resid.dim() == 2, "resid: contiguous bf16 [T, H]");

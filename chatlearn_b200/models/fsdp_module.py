@@ -41,6 +41,8 @@ class FSDPModule(TorchModule):
             self.dp_outer_group = self.mesh.groups["dp_outer"]
             if sp > 1:
                 self.sp = UlyssesGroup(self.mesh.groups["sp"])
+                from chatlearn_b200.parallel import symm_collectives
+                symm_collectives.attach_exchange(self.mesh.groups["sp"])
 
     @property
     def is_data_leader(self) -> bool:

@@ -154,6 +154,9 @@ class MegatronModule(FSDPModule):
         self.model = self.create_model()
         self.ep = ExpertParallel(self.ep_group) if self.ep_size > 1 else None
         self.cp = ContextParallel(self.cp_group) if self.cp_size > 1 else None
+        if self.cp is not None:
+            from chatlearn_b200.parallel import symm_collectives
+            symm_collectives.attach_exchange(self.cp_group)
         if self.trainable:
             oc = self.module_args.optimizer
             extra = [g for g in (self.tp_group, self.pp_group) if g.size > 1]

@@ -43,6 +43,11 @@ class Group:
         if self.size == 1:
             return x
         x = x.contiguous()
+        fast = self.fast.get("exchange") if x.is_cuda else None
+        flat = fast.all_gather(x.view(-1)) if fast is not None else None
+        if flat is not None:
+            out = flat.view((self.size,) + tuple(x.shape))
+            return out.reshape((-1,) + tuple(x.shape[1:])) if dim == 0 else torch.cat(list(out.unbind(0)), dim=dim)
         out = torch.empty((self.size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(out.view(-1), x.view(-1), group=self.pg) \
             if _backend(self.pg) == "nccl" else dist.all_gather(list(out.unbind(0)), x, group=self.pg)
@@ -76,6 +81,10 @@ class Group:
         if self.size == 1:
             return x
         x = x.contiguous()
+        if out_splits is None and in_splits is None and x.is_cuda and "exchange" in self.fast:
+            out = self.fast["exchange"].all_to_all(x)
+            if out is not None:
+                return out
         if out_splits is None:
             out = torch.empty_like(x)
         else:

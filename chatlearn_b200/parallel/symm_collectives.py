@@ -60,6 +60,7 @@ class SymmGroup:
         self.push = os.environ.get("CLB200_TP_PUSH", "0") == "1"
         self.part_ptrs = [self._ptrs(t) for t in self.parts]
         self._flip = 0
+        self._xbufs, self._xptrs, self._xcap, self._xflip = None, None, 0, 0
         torch.cuda.synchronize()
         group.barrier()               # flags are zero everywhere before the first kernel signals
 
@@ -137,6 +138,49 @@ class SymmGroup:
                                scale.reshape(1).float() if scale is not None else None, self.rank, NUM_SLOTS)
         self.native.launch_counts["symm_adamw_push"] += 1
 
+    # ------------------------------------------------------------------ all-gather / all-to-all
+    def _exchange_buffers(self):
+        """Two receive buffers per rank, used alternately: a peer writes into buffer ``i`` for call
+        ``k+2`` only after the barrier of call ``k+1``, which this rank signals after it has copied
+        the result of call ``k`` out, so one barrier per call is enough.  Allocated collectively on
+        the first exchange of the group."""
+        if self._xbufs is None:
+            cap = int(os.environ.get("CLB200_SYMM_XCHG_MB", "128")) << 20
+            self._xbufs = [symm_mem.empty(cap, torch.uint8, self.device, group=self.pg) for _ in range(2)]
+            self._xptrs = [self._ptrs(t) for t in self._xbufs]
+            self._xcap = cap
+        return self._xbufs
+
+    def _exchange(self, x: torch.Tensor, chunk_bytes: int, all_to_all: bool) -> Optional[torch.Tensor]:
+        total = chunk_bytes * self.world
+        if chunk_bytes == 0 or chunk_bytes % 16 or x.data_ptr() % 16 or not x.is_contiguous():
+            return None
+        bufs = self._exchange_buffers()
+        if total > self._xcap:
+            return None
+        idx = self._xflip
+        self._xflip ^= 1
+        self.C.symm_push_chunks(x, self._xptrs[idx], chunk_bytes, all_to_all, self.rank)
+        self.C.symm_group_barrier(self.flag_ptrs, self.expect, NUM_SLOTS - 1, NUM_SLOTS, self.rank)
+        self.native.launch_counts["symm_exchange"] += 1
+        return bufs[idx][:total].view(x.dtype).clone()
+
+    def all_gather(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """Flat concatenation of every rank's ``x`` (equal sizes), or ``None`` when the tensor does
+        not qualify (the caller then uses NCCL).  Each rank stores its chunk into slot ``rank`` of
+        every peer's receive buffer; the context-parallel key/value gather and the sequence gathers
+        of Ulysses attention take this path (the reference issues NCCL collectives there:
+        chatlearn/utils/communication_op.py:30-110)."""
+        return self._exchange(x.view(-1), x.numel() * x.element_size(), False)
+
+    def all_to_all(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """Equal-split all-to-all along dim 0: chunk ``p`` of ``x`` goes to rank ``p``; the result has
+        chunk ``r`` received from rank ``r``.  ``None`` when the tensor does not qualify."""
+        if x.shape[0] % self.world:
+            return None
+        out = self._exchange(x, x.numel() * x.element_size() // self.world, True)
+        return None if out is None else out.view(x.shape)
+
     def status(self) -> int:
         return int(self.C.symm_last_status())
 
@@ -153,3 +197,14 @@ def get(group: Group) -> Optional[SymmGroup]:
     if key not in _GROUPS:
         _GROUPS[key] = SymmGroup(group)
     return _GROUPS[key]
+
+
+def attach_exchange(group: Group) -> Optional[SymmGroup]:
+    """Route the group's equal-split all-gathers and all-to-alls through the peer-memory
+    exchange kernels (``CLB200_SYMM_XCHG=0`` keeps NCCL).  Collective over the group."""
+    if os.environ.get("CLB200_SYMM_XCHG", "1") == "0":
+        return None
+    sg = get(group)
+    if sg is not None:
+        group.fast["exchange"] = sg
+    return sg

@@ -1,0 +1,89 @@
+"""Multi-GPU check of the peer-memory all-gather / all-to-all (run under torchrun, one rank per GPU)."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from chatlearn_b200.launcher.initialize import init_distributed, shutdown  # noqa: E402
+from chatlearn_b200.parallel import symm_collectives  # noqa: E402
+from chatlearn_b200.parallel.groups import Group  # noqa: E402
+from chatlearn_b200.parallel.ulysses import UlyssesGroup  # noqa: E402
+
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+init_distributed()
+rank, world = dist.get_rank(), dist.get_world_size()
+dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+g = Group(dist.group.WORLD, list(range(world)), "world")
+plain = Group(dist.group.WORLD, list(range(world)), "plain")          # NCCL only
+sg = symm_collectives.attach_exchange(g)
+assert sg is not None and "exchange" in g.fast
+res = {}
+
+torch.manual_seed(7 + rank)
+ok = True
+for shape in ((8,), (300, 24), (1024, 8, 128), (4096, 1024)):
+    for rep in range(3):                                               # both receive buffers, counters advance
+        x = torch.randn(*shape, device=dev).bfloat16()
+        for dim in (0, len(shape) - 1):
+            ok &= bool(torch.equal(g.all_gather_cat(x, dim), plain.all_gather_cat(x, dim)))
+res["all_gather_ok"] = ok
+
+ok = True
+for shape, dt in (((world * 4, 8), torch.float32), ((world * 512, 4, 128), torch.bfloat16), ((world * 3000, 1024), torch.bfloat16)):
+    for rep in range(3):
+        x = torch.randn(*shape, device=dev).to(dt)
+        ok &= bool(torch.equal(g.all_to_all_single(x), plain.all_to_all_single(x)))
+res["all_to_all_ok"] = ok
+
+# tensors the kernel does not take (chunk not a multiple of 16 bytes) go through NCCL
+before = sg.native.launch_counts["symm_exchange"]
+x = torch.randn(world * 3, 1, device=dev).bfloat16()
+ok = bool(torch.equal(g.all_to_all_single(x), plain.all_to_all_single(x)))
+ok &= bool(torch.equal(g.all_gather_cat(x[:3]), plain.all_gather_cat(x[:3])))
+res["fallback_ok"] = ok and sg.native.launch_counts["symm_exchange"] == before
+
+# Ulysses exchange with gradients: sequence split -> head split -> sequence split
+outs = []
+for grp in (g, plain):
+    torch.manual_seed(50 + rank)
+    q = torch.randn(256, 8, 64, device=dev).bfloat16().requires_grad_(True)
+    u = UlyssesGroup(grp)
+    h = u.seq_to_heads(q)
+    y = u.heads_to_seq(h * 2.0)
+    (y.float() * torch.arange(y.numel(), device=dev).view_as(y) / y.numel()).sum().backward()
+    outs.append((h.detach().clone(), y.detach().clone(), q.grad.clone()))
+res["ulysses_ok"] = all(bool(torch.equal(a, b)) for a, b in zip(*outs))
+
+
+def timed(fn, iters=20):
+    for _ in range(5):
+        fn()
+    torch.cuda.synchronize(); dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+# Ulysses query exchange of an 8192-token local sequence, 32 heads x 128 (64 MB), and the
+# context-parallel key/value gather of 8192 tokens x 8 kv heads x 128 x 2 (32 MB per rank)
+xa = torch.randn(8192 * world, 32 // world, 128, device=dev).bfloat16()
+xg = torch.randn(8192, 2 * 8 * 128, device=dev).bfloat16()
+for name, grp in (("symm", g), ("nccl", plain)):
+    res[f"a2a_ms_{name}"] = round(timed(lambda: grp.all_to_all_single(xa)), 4)
+    res[f"ag_ms_{name}"] = round(timed(lambda: grp.all_gather_cat(xg)), 4)
+res["a2a_bytes_sent_per_rank"] = xa.numel() * 2 * (world - 1) // world
+res["ag_bytes_recv_per_rank"] = xg.numel() * 2 * (world - 1)
+res["status"] = sg.status()
+if rank == 0:
+    print("RESULT " + json.dumps(res), flush=True)
+shutdown()

@@ -41,3 +41,19 @@ def test_expert_parallel_rollout_paths_agree():
         outs[flag] = {r["rank"]: r for r in res}
     assert all(outs["1"][r]["symm_ep"] and not outs["0"][r]["symm_ep"] for r in (0, 1))
     assert all(outs["1"][r]["checksum"] == outs["0"][r]["checksum"] for r in (0, 1))
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_memory_exchange_two_gpus():
+    """All-gather and equal-split all-to-all by peer stores agree bit for bit with NCCL, alone and
+    inside the Ulysses head/sequence exchange with gradients."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29645", os.path.join(ROOT, "tests", "exchange_driver.py")],
+                       capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    lines = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")]
+    assert p.returncode == 0 and lines, p.stdout[-2000:] + p.stderr[-2000:]
+    r = json.loads(lines[-1][7:])
+    for key in ("all_gather_ok", "all_to_all_ok", "fallback_ok", "ulysses_ok"):
+        assert r[key], (key, r)
+    assert r["status"] == 0
