@@ -102,7 +102,7 @@ class MegatronPolicyTrainer(MegatronModule):
                 p = self.model.layer_params(l)
                 h = hook(l, p, h, ctx) if hook else decoder_layer(self.model.arch, p, h, ctx, l)
             if self.is_last_stage:
-                h = ops.rmsnorm(h, self.model.block_by_name["head"].params["norm"], self.model.arch.rms_norm_eps)
+                h = ops.rmsnorm(h, self.model.final_norm_weight(), self.model.arch.rms_norm_eps)
         if not self.is_last_stage:
             return h
         labels = batch.labels if local is None else batch.labels.index_select(0, local)

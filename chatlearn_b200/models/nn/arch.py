@@ -53,6 +53,18 @@ class ModelArch:
     mrope_interleaved: bool = False      # Qwen3-VL frequency layout
     vision_config: Optional[Dict[str, Any]] = None
     image_token_id: Optional[int] = None
+    # Qwen3-Next: gated delta-net ("linear_attention") layers interleaved with gated full attention
+    layer_types: Optional[List[str]] = None          # per layer: "linear_attention" | "full_attention"
+    full_attention_interval: int = 4                 # default pattern when layer_types is not given
+    partial_rotary_factor: float = 1.0               # fraction of the head dim that rotates
+    attn_output_gate: bool = False                   # q_proj also emits a per-channel sigmoid gate
+    zero_centered_norm: bool = False                 # RMSNorm scales by (1 + weight)
+    linear_num_key_heads: int = 0
+    linear_num_value_heads: int = 0
+    linear_key_head_dim: int = 0
+    linear_value_head_dim: int = 0
+    linear_conv_kernel_dim: int = 4
+    shared_expert_intermediate_size: int = 0         # sigmoid-gated shared expert beside the routed ones
     # reward-model head
     num_labels: int = 0                  # >0: scalar/value head instead of lm_head
     bos_token_id: Optional[int] = None
@@ -70,6 +82,14 @@ class ModelArch:
             self.attention_bias = True
         if self.model_type in ("deepseek_v3", "deepseek_v2", "kimi_k2", "moonlight"):
             self.use_mla = self.kv_lora_rank > 0
+        if self.model_type != "qwen3_next":
+            self.layer_types = None          # other families list "full_attention" / sliding-window kinds there
+        if self.model_type == "qwen3_next":
+            self.qk_norm = self.attn_output_gate = self.zero_centered_norm = True
+            if self.layer_types is None:
+                k = max(int(self.full_attention_interval), 1)
+                self.layer_types = ["full_attention" if (i + 1) % k == 0 else "linear_attention"
+                                    for i in range(self.num_hidden_layers)]
         if self.eos_token_id is None:
             self.eos_token_id = self.vocab_size - 1
 
@@ -80,6 +100,14 @@ class ModelArch:
 
     def layer_is_moe(self, layer: int) -> bool:
         return self.is_moe and layer >= self.first_k_dense_replace
+
+    def layer_is_linear(self, layer: int) -> bool:
+        """Gated delta-net token mixer (recurrent state) instead of softmax attention."""
+        return self.layer_types is not None and self.layer_types[layer] == "linear_attention"
+
+    @property
+    def rotary_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor)
 
     @property
     def q_size(self) -> int:
@@ -96,7 +124,13 @@ class ModelArch:
         n = v * h * (1 if self.tie_word_embeddings else 2) + h
         for l in range(self.num_hidden_layers):
             n += 2 * h
-            if self.use_mla:
+            if self.layer_is_linear(l):
+                kd = self.linear_num_key_heads * self.linear_key_head_dim
+                vd = self.linear_num_value_heads * self.linear_value_head_dim
+                n += h * (2 * kd + 2 * vd + 2 * self.linear_num_value_heads) + vd * h
+                n += (2 * kd + vd) * self.linear_conv_kernel_dim + 2 * self.linear_num_value_heads
+                n += self.linear_value_head_dim
+            elif self.use_mla:
                 qd = self.qk_nope_head_dim + self.qk_rope_head_dim
                 nh = self.num_attention_heads
                 if self.q_lora_rank:
@@ -107,7 +141,7 @@ class ModelArch:
                 n += self.kv_lora_rank * nh * (self.qk_nope_head_dim + self.v_head_dim)
                 n += nh * self.v_head_dim * h
             else:
-                n += h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+                n += h * (self.q_size * (2 if self.attn_output_gate else 1) + 2 * self.kv_size) + self.q_size * h
                 if self.qk_norm:
                     n += 2 * self.head_dim
                 if self.attention_bias:
@@ -116,6 +150,8 @@ class ModelArch:
                 n += self.num_experts * h + (self.num_experts if self.router_bias else 0)
                 n += self.num_experts * 3 * h * self.moe_intermediate_size
                 n += self.n_shared_experts * 3 * h * self.moe_intermediate_size
+                if self.shared_expert_intermediate_size:
+                    n += 3 * h * self.shared_expert_intermediate_size + h
             else:
                 n += 3 * h * self.intermediate_size
         return n
@@ -140,6 +176,11 @@ class ModelArch:
             d = dict(d, mrope_section=list(rs["mrope_section"]), mrope_interleaved=bool(rs.get("mrope_interleaved", False)))
             if "rope_theta" in rs and "rope_theta" not in d:
                 d["rope_theta"] = rs["rope_theta"]
+        if isinstance(rs, dict):
+            # newer config files keep the rotary settings in one nested dict
+            for key in ("rope_theta", "partial_rotary_factor"):
+                if key in rs and key not in d:
+                    d = dict(d, **{key: rs[key]})
         for k, v in d.items():
             k = cls._HF_ALIASES.get(k, k)
             if k in known and k != "extra":
@@ -161,7 +202,7 @@ class ModelArch:
         d.update(extra)
         arch_names = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM",
                       "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
-                      "deepseek_v3": "DeepseekV3ForCausalLM"}
+                      "deepseek_v3": "DeepseekV3ForCausalLM", "qwen3_next": "Qwen3NextForCausalLM"}
         d.setdefault("architectures", [arch_names.get(self.model_type, "LlamaForCausalLM")])
         if self.model_type == "deepseek_v3":
             d["n_routed_experts"] = self.num_experts
@@ -277,7 +318,29 @@ def qwen2_5_vl_7b() -> ModelArch:
                                         window_size=112, fullatt_block_indexes=[7, 15, 23, 31]))
 
 
+def tiny_qwen3_next() -> ModelArch:
+    """Qwen3-Next in miniature: three gated delta-net layers per gated-attention layer, MoE with a
+    sigmoid-gated shared expert, a quarter of each head rotating."""
+    return ModelArch(model_type="qwen3_next", vocab_size=512, hidden_size=128, num_hidden_layers=4,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=32, partial_rotary_factor=0.25,
+                     intermediate_size=256, moe_intermediate_size=64, num_experts=8, num_experts_per_tok=2,
+                     shared_expert_intermediate_size=64, norm_topk_prob=True, rope_theta=1e6,
+                     linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=16,
+                     linear_value_head_dim=16, linear_conv_kernel_dim=4)
+
+
+def qwen3_next_80b_a3b() -> ModelArch:
+    return ModelArch(model_type="qwen3_next", vocab_size=151936, hidden_size=2048, num_hidden_layers=48,
+                     num_attention_heads=16, num_key_value_heads=2, head_dim=256, partial_rotary_factor=0.25,
+                     intermediate_size=5120, moe_intermediate_size=512, num_experts=512, num_experts_per_tok=10,
+                     shared_expert_intermediate_size=512, norm_topk_prob=True, router_aux_loss_coef=1e-3,
+                     rope_theta=1e7, max_position_embeddings=262144,
+                     linear_num_key_heads=16, linear_num_value_heads=32, linear_key_head_dim=128,
+                     linear_value_head_dim=128, linear_conv_kernel_dim=4)
+
+
 PRESETS = {
+    "tiny_qwen3_next": tiny_qwen3_next, "qwen3_next_80b_a3b": qwen3_next_80b_a3b,
     "tiny_qwen2_5_vl": tiny_qwen2_5_vl, "qwen2_5_vl_7b": qwen2_5_vl_7b,
     "tiny_qwen3": tiny_qwen3, "qwen3_8b": qwen3_8b, "qwen3_30b_a3b": qwen3_30b_a3b,
     "llama2_7b": llama2_7b, "moonlight_16b_a3b": moonlight_16b_a3b, "tiny_moe": tiny_moe,

@@ -78,16 +78,53 @@ def kv_head_range(arch: ModelArch, tp: int, tp_rank: int) -> Tuple[int, int]:
     return tp_rank // (tp // nkv), 1
 
 
+def _hybrid_mixer_leaves(arch: ModelArch, l: int, pre: str, hp: str) -> List[Leaf]:
+    """Token mixer of a Qwen3-Next layer (HF names: transformers
+    models/qwen3_next/modeling_qwen3_next.py, ``Qwen3NextGatedDeltaNet`` / ``Qwen3NextAttention``; the
+    reference maps the same tensors for Megatron in
+    chatlearn/synchronizer/mappers/megatron_llm_mapper.py:262-343)."""
+    H = arch.hidden_size
+    if arch.layer_is_linear(l):
+        a = hp + "linear_attn."
+        nk, nv = arch.linear_num_key_heads, arch.linear_num_value_heads
+        kd, vd = nk * arch.linear_key_head_dim, nv * arch.linear_value_head_dim
+        pq = 2 * kd + 2 * vd
+        # one GEMM for both input projections: rows [q k v z per key-head group | b a per group]
+        in_proj = Leaf(pre + "in_proj", (pq + 2 * nv, H), "normal",
+                       [_rows(a + "in_proj_qkvz.weight", (pq, H), 0, pq, 0),
+                        _rows(a + "in_proj_ba.weight", (2 * nv, H), 0, 2 * nv, pq)])
+        return [in_proj,
+                _full(pre + "conv1d", (2 * kd + vd, arch.linear_conv_kernel_dim), a + "conv1d.weight", "conv"),
+                _full(pre + "dt_bias", (nv,), a + "dt_bias", "ones"),
+                _full(pre + "A_log", (nv,), a + "A_log", "a_log"),
+                _full(pre + "gdn_norm", (arch.linear_value_head_dim,), a + "norm.weight", "ones"),
+                _full(pre + "out_proj", (H, vd), a + "out_proj.weight")]
+    a = hp + "self_attn."
+    nh, nkv, d = arch.num_attention_heads, arch.num_key_value_heads, arch.head_dim
+    qf, kf = (nh * 2 * d, H), (nkv * d, H)       # q_proj rows per head: [query | gate]
+    qkv = Leaf(pre + "qkv", ((2 * nh + 2 * nkv) * d, H), "normal",
+               [_rows(a + "q_proj.weight", qf, 0, qf[0], 0),
+                _rows(a + "k_proj.weight", kf, 0, kf[0], qf[0]),
+                _rows(a + "v_proj.weight", kf, 0, kf[0], qf[0] + kf[0])])
+    return [qkv, _full(pre + "q_norm", (d,), a + "q_norm.weight", "zeros"),
+            _full(pre + "k_norm", (d,), a + "k_norm.weight", "zeros"),
+            _full(pre + "o_proj", (H, nh * d), a + "o_proj.weight")]
+
+
 def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int = 1,
                  ep_rank: int = 0) -> List[Leaf]:
     """Leaves of decoder layer ``l`` for one (tp, ep) rank."""
     H = arch.hidden_size
     pre, hp = f"layers.{l}.", f"model.layers.{l}."
-    out: List[Leaf] = [_full(pre + "input_layernorm", (H,), hp + "input_layernorm.weight", "ones")]
+    norm_init = "zeros" if arch.zero_centered_norm else "ones"      # zero-centred norms scale by (1 + w)
+    out: List[Leaf] = [_full(pre + "input_layernorm", (H,), hp + "input_layernorm.weight", norm_init)]
     nh = arch.num_attention_heads
     assert nh % tp == 0, f"{nh} heads not divisible by tp={tp}"
     nh_l = nh // tp
-    if arch.use_mla:
+    if arch.layer_types is not None:
+        assert tp == 1, "the gated delta-net / gated-attention layers are not tensor-parallel"
+        out.extend(_hybrid_mixer_leaves(arch, l, pre, hp))
+    elif arch.use_mla:
         qd = arch.qk_nope_head_dim + arch.qk_rope_head_dim
         a = hp + "self_attn."
         if arch.q_lora_rank:
@@ -134,7 +171,7 @@ def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int
         fs = (H, nh * d)
         out.append(Leaf(pre + "o_proj", (H, nh_l * d), "normal",
                         [_cols(a + "o_proj.weight", fs, tp_rank * nh_l * d, nh_l * d)]))
-    out.append(_full(pre + "post_attention_layernorm", (H,), hp + "post_attention_layernorm.weight", "ones"))
+    out.append(_full(pre + "post_attention_layernorm", (H,), hp + "post_attention_layernorm.weight", norm_init))
 
     def mlp_leaves(prefix, hf_prefix, F, shard_tp):
         t, r = (tp, tp_rank) if shard_tp else (1, 0)
@@ -167,6 +204,10 @@ def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int
             Fs = arch.n_shared_experts * Fm
             sh = mlp_leaves(pre + "shared_", m + "shared_experts.", Fs, True)
             out.extend(sh)
+        if arch.shared_expert_intermediate_size:
+            # Qwen3-Next: one shared expert whose output is scaled by sigmoid(x · gate)
+            out.extend(mlp_leaves(pre + "shared_", m + "shared_expert.", arch.shared_expert_intermediate_size, True))
+            out.append(_full(pre + "shared_expert_gate", (1, H), m + "shared_expert_gate.weight"))
     else:
         out.extend(mlp_leaves(pre, hp + "mlp.", arch.intermediate_size, True))
     for lf in out:
@@ -185,7 +226,7 @@ def embed_leaves(arch: ModelArch, tp: int = 1, tp_rank: int = 0) -> List[Leaf]:
 
 def head_leaves(arch: ModelArch, tp: int = 1, tp_rank: int = 0) -> List[Leaf]:
     V, H = arch.vocab_size, arch.hidden_size
-    out = [_full("norm", (H,), "model.norm.weight", "ones")]
+    out = [_full("norm", (H,), "model.norm.weight", "zeros" if arch.zero_centered_norm else "ones")]
     if arch.num_labels > 0:
         out.append(_full("score", (arch.num_labels, H), "score.weight"))
     elif not arch.tie_word_embeddings:
@@ -224,4 +265,6 @@ def hf_tensor_shapes(arch: ModelArch) -> Dict[str, Tuple[int, ...]]:
         for lf in leaves:
             for s in lf.segments:
                 shapes[s.hf_name] = (s.hf_shape[0],) if len(lf.shape) == 1 else tuple(s.hf_shape)
+                if s.hf_name.endswith(".conv1d.weight"):       # depthwise Conv1d: [channels, 1, taps]
+                    shapes[s.hf_name] = (s.hf_shape[0], 1, s.hf_shape[1])
     return shapes

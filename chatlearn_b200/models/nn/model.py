@@ -107,6 +107,13 @@ class ParamBlock:
                 p.fill_(1.0)
             elif lf.init == "zeros":
                 p.zero_()
+            elif lf.init in ("a_log", "conv"):
+                # gated delta-net: decay rates A ~ U(1, 16) stored as log A; depthwise conv taps ~ U(-1/sqrt(k), 1/sqrt(k))
+                g = torch.Generator(device="cpu")
+                g.manual_seed((seed * 1000003 + zlib.crc32(lf.name.encode())) % (2 ** 31))
+                u = torch.rand(p.shape, generator=g)
+                v = (1.0 + 15.0 * u).log() if lf.init == "a_log" else (2.0 * u - 1.0) / math.sqrt(p.shape[-1])
+                p.copy_(v.to(p.device))
             else:
                 g = torch.Generator(device=p.device)
                 g.manual_seed((seed * 1000003 + zlib.crc32(lf.name.encode())) % (2 ** 31))
@@ -127,6 +134,7 @@ class KVCtx:
     seq_lens: torch.Tensor                 # [B] lengths including the new tokens
     q_lens: Optional[torch.Tensor] = None  # [B] new tokens per sequence (None → 1 each)
     prefill_only: bool = False             # all sequences start at position 0 → varlen kernel
+    lin: Any = None                        # models.nn.hybrid.LinearState: conv / recurrent state of gated delta-net layers
 
 
 @dataclass
@@ -268,7 +276,10 @@ def moe_block(arch: ModelArch, p, x, ctx: FwdCtx):
     else:
         y = ops.moe_experts(x, p["w13"], p["w2"], w, idx)
     if "shared_gate_up" in p:
-        y = y + _tp_reduce(dense_mlp(p, x, ctx, "shared_"), ctx)
+        sh = _tp_reduce(dense_mlp(p, x, ctx, "shared_"), ctx)
+        if "shared_expert_gate" in p:
+            sh = sh * torch.sigmoid(torch.nn.functional.linear(x, p["shared_expert_gate"]))   # one output column
+        y = y + sh
     return y
 
 
@@ -323,6 +334,9 @@ def _decoder_layer_infer_fused(arch: ModelArch, p, x, ctx: FwdCtx, layer: int):
 
 
 def decoder_layer(arch: ModelArch, p, x, ctx: FwdCtx, layer: int):
+    if arch.layer_types is not None:
+        from .hybrid import hybrid_decoder_layer
+        return hybrid_decoder_layer(arch, p, x, ctx, layer)
     if _tp_fused_ok(p, x, ctx):
         return _decoder_layer_tp_fused(arch, p, x, ctx, layer)
     if ctx.fuse_add_norm and not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16 \
@@ -419,13 +433,19 @@ class CausalLM:
                 rows, taps = ctx.deepstack
                 x = x.index_add(0, rows, taps[l].to(x.dtype))
         if "head" in self.block_by_name:
-            norm_w = self.block_by_name["head"].params["norm"]
+            norm_w = self.final_norm_weight()
             if ctx.pending is not None:
                 return flush_pending(x, ctx, norm_w, self.arch.rms_norm_eps)
             x = ops.rmsnorm(x, norm_w, self.arch.rms_norm_eps)
         elif ctx.pending is not None:
             x = flush_pending(x, ctx)
         return x
+
+    def final_norm_weight(self):
+        w = self.block_by_name["head"].params["norm"]
+        if self.arch.zero_centered_norm:
+            return (1.0 + w.float()).to(w.dtype)
+        return w
 
     def lm_head_weight(self):
         if self.arch.tie_word_embeddings:
@@ -474,6 +494,9 @@ class CausalLM:
                 full[rs:rs + nr, cs:cs + nc] = slab[r0:r0 + nr, c0:c0 + nc]
         for k in one_d:
             out[k] = out[k].squeeze(1)
+        for k in list(out):
+            if k.endswith(".conv1d.weight"):        # depthwise Conv1d weights are [channels, 1, taps]
+                out[k] = out[k].unsqueeze(1)
         return out
 
     @torch.no_grad()

@@ -90,6 +90,7 @@ class RolloutEngine:
         self._num_blocks_cfg = num_blocks
         self.k_cache: List[torch.Tensor] = []
         self.v_cache: List[torch.Tensor] = []
+        self.lin_conv, self.lin_rec, self._state_slot, self._free_state_slots = [], [], {}, []
         self.num_blocks = 0
         self.gen = torch.Generator(device=self.device)
         self.gen.manual_seed(seed)
@@ -114,7 +115,20 @@ class RolloutEngine:
             nkv_l = kv_head_range(a, tp, 0)[1]
             per_tok = nkv_l * a.head_dim * 2
         esz = torch.empty((), dtype=self.kv_dtype).element_size()
-        return per_tok * esz * self.block_size * a.num_hidden_layers
+        kv_layers = sum(1 for l in range(a.num_hidden_layers) if not a.layer_is_linear(l))
+        return per_tok * esz * self.block_size * kv_layers
+
+    def linear_state_bytes(self) -> int:
+        """Convolution taps + recurrent matrix of every gated delta-net layer, for all state slots."""
+        a = self.arch
+        n_lin = sum(1 for l in range(a.num_hidden_layers) if a.layer_is_linear(l))
+        if not n_lin:
+            return 0
+        kd, vd = a.linear_num_key_heads * a.linear_key_head_dim, a.linear_num_value_heads * a.linear_value_head_dim
+        esz = torch.empty((), dtype=self.model.dtype).element_size()
+        per_slot = (a.linear_conv_kernel_dim - 1) * (2 * kd + vd) * esz \
+            + a.linear_num_value_heads * a.linear_key_head_dim * a.linear_value_head_dim * 4
+        return n_lin * per_slot * (self.max_num_seqs + 1)
 
     def alloc_kv_cache(self):
         if self.k_cache:
@@ -125,7 +139,7 @@ class RolloutEngine:
         if nb is None:
             if self.device.type == "cuda":
                 free, total = torch.cuda.mem_get_info(self.device)
-                budget = int(free - (1.0 - self.util) * total)
+                budget = int(free - (1.0 - self.util) * total) - self.linear_state_bytes()
                 nb = max(budget // self.kv_bytes_per_block(), 1)
             else:
                 nb = 256
@@ -147,7 +161,21 @@ class RolloutEngine:
             dk = dv = a.head_dim
         # one block beyond the allocator's range is scratch: padded rows of a captured
         # decode step write their (ignored) KV there
-        for _ in range(a.num_hidden_layers):
+        self.lin_conv, self.lin_rec = [], []
+        self._state_slot, self._free_state_slots = {}, list(range(self.max_num_seqs, -1, -1))
+        for l in range(a.num_hidden_layers):
+            if a.layer_is_linear(l):
+                # gated delta-net layers keep a fixed-size state per sequence instead of keys and values
+                kd, vd = a.linear_num_key_heads * a.linear_key_head_dim, a.linear_num_value_heads * a.linear_value_head_dim
+                self.k_cache.append(torch.empty(0, device=self.device))
+                self.v_cache.append(torch.empty(0, device=self.device))
+                self.lin_conv.append(torch.zeros(self.max_num_seqs + 1, a.linear_conv_kernel_dim - 1, 2 * kd + vd,
+                                                 dtype=self.model.dtype, device=self.device))
+                self.lin_rec.append(torch.zeros(self.max_num_seqs + 1, a.linear_num_value_heads, a.linear_key_head_dim,
+                                                a.linear_value_head_dim, dtype=torch.float32, device=self.device))
+                continue
+            self.lin_conv.append(None)
+            self.lin_rec.append(None)
             self.k_cache.append(torch.zeros(nb + 1, self.block_size, nkv_l, dk, dtype=self.kv_dtype,
                                             device=self.device))
             self.v_cache.append(torch.zeros(nb + 1, self.block_size, nkv_l, dv, dtype=self.kv_dtype,
@@ -157,7 +185,34 @@ class RolloutEngine:
     def free_kv_cache(self):
         self.invalidate_graphs()
         self.k_cache, self.v_cache = [], []
+        self.lin_conv, self.lin_rec = [], []
         self.num_blocks = 0
+
+    def _linear_state(self, seqs) -> Optional[Any]:
+        """State slots of this step's sequences (assigned on first sight, reclaimed from finished or
+        preempted sequences) and which of them start from an empty state."""
+        if self.arch.layer_types is None:
+            return None
+        from chatlearn_b200.models.nn.hybrid import LinearState
+        live = {id(s) for s in seqs}
+        slots = []
+        for s in seqs:
+            slot = self._state_slot.get(id(s))
+            if slot is None:
+                if not self._free_state_slots:
+                    for key, (sl, other) in list(self._state_slot.items()):
+                        if key not in live and (other.finished or other.num_computed == 0):
+                            del self._state_slot[key]
+                            self._free_state_slots.append(sl)
+                assert self._free_state_slots, "more running sequences than state slots"
+                slot = (self._free_state_slots.pop(), s)
+                self._state_slot[id(s)] = slot
+            slots.append(slot[0])
+        fresh = [s.num_computed == 0 for s in seqs]
+        dev = self.device
+        return LinearState(self.lin_conv, self.lin_rec,
+                           xfer.to_device(torch.tensor(slots, dtype=torch.long), dev, "lin_slots"),
+                           xfer.to_device(torch.tensor(fresh, dtype=torch.bool), dev, "lin_fresh"))
 
     # ------------------------------------------------------------------ one step
     def _build_inputs(self, plan: StepPlan):
@@ -202,7 +257,8 @@ class RolloutEngine:
         # one pinned staging slot per input so the async copies never alias
         t = lambda x, dt, slot: xfer.to_device(torch.tensor(x, dtype=dt), dev, slot)  # noqa: E731
         kv = KVCtx(self.k_cache, self.v_cache, t(slots, torch.long, "slots"), xfer.to_device(bt, dev, "bt"),
-                   t(seq_lens, torch.int32, "seq_lens"), t(plan.q_lens, torch.int32, "q_lens"), plan.is_prefill)
+                   t(seq_lens, torch.int32, "seq_lens"), t(plan.q_lens, torch.int32, "q_lens"), plan.is_prefill,
+                   lin=self._linear_state(plan.seqs))
         ctx = FwdCtx(positions=t(pos, torch.long, "pos"), cu_seqlens=t(cu, torch.int32, "cu"),
                      max_seqlen=max(plan.q_lens), kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm(), fuse_add_norm=True)
         self._embed_patch = None
@@ -324,6 +380,8 @@ class RolloutEngine:
     def _can_graph(self, plan: StepPlan) -> bool:
         if not self.use_graphs or self.device.type != "cuda" or plan.is_prefill:
             return False
+        if self.arch.layer_types is not None:
+            return False        # the recurrent-state layers run on PyTorch statements outside the captured step
         if ops.get_mode() != "native":
             return False        # the PyTorch statements of the ops synchronise with the host
         if any(n != 1 for n in plan.q_lens) or len(plan.seqs) > self._BUCKETS[-1]:
@@ -405,6 +463,10 @@ class RolloutEngine:
                 sched.finish(s, "stop")
             elif len(s.output) >= s.max_new_tokens or s.length >= self.max_model_len:
                 sched.finish(s, "length")
+            if s.finished and self.arch.layer_types is not None:
+                slot = self._state_slot.pop(id(s), None)
+                if slot is not None:
+                    self._free_state_slots.append(slot[0])
 
     @torch.no_grad()
     def _idle_step(self):
@@ -412,7 +474,7 @@ class RolloutEngine:
         dev = self.device
         z = lambda dt: torch.zeros(0, dtype=dt, device=dev)  # noqa: E731
         kv = KVCtx(self.k_cache, self.v_cache, z(torch.long), torch.zeros(0, 1, dtype=torch.int32, device=dev),
-                   z(torch.int32), z(torch.int32), True)
+                   z(torch.int32), z(torch.int32), True, lin=self._linear_state([]))
         ctx = FwdCtx(positions=z(torch.long), cu_seqlens=torch.zeros(1, dtype=torch.int32, device=dev),
                      max_seqlen=0, kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm(), fuse_add_norm=True)
         self.model.hidden_states(z(torch.long), ctx)

@@ -22,7 +22,7 @@ if int(os.environ["RANK"]) == 0:
         write_jsonl(make_prompts(8, 16, 32, 512, seed=0, data_source="synthetic:mod7"), data + ".tmp")
     os.replace(data + ".tmp", data)
 while not os.path.exists(data): time.sleep(0.05)
-arch = {"preset": "tiny_moe" if mode == "moe" else "tiny_llama"}
+arch = {"preset": {"moe": "tiny_moe", "next": "tiny_qwen3_next"}.get(mode, "tiny_llama")}
 cfg = {
   "runtime_args": {"train_backend": "fsdp", "exp_name": mode, "output_dir": out, "data_path": data,
      "colocation": ["policy", "policy_trainer", "ref_policy"],
@@ -41,6 +41,8 @@ cfg = {
 if mode == "moe":
     # expert-parallel rollout: each of the two ranks hosts half of the experts and decodes its own sequences
     cfg["models"]["policy"].update(expert_model_parallel_size=2, tokenizer="null")
+if mode == "next":
+    cfg["models"]["policy"].update(tokenizer="null")
 if mode == "partial":
     cfg["runtime_args"]["use_partial_rollout"] = True
     cfg["models"]["partial_rollout_manager"] = {"num_cpu": 1, "max_rollout_round": 2, "rollout_ratio": [0.5, 0.5],
@@ -88,3 +90,13 @@ def test_moe_model_with_expert_parallel_rollout(tmp_path):
     outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "MODE": "moe"})
     res = _results(outs)
     assert len(res) == 2 and all(r["episodes"] == 3 and r["train_iters"] == 3 for r in res)
+
+
+def test_qwen3_next_hybrid_model(tmp_path):
+    """Gated delta-net + gated attention + shared-expert MoE: sharded training, weight sync into the rollout
+    engine (recurrent state per sequence), three episodes."""
+    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "MODE": "next"})
+    res = _results(outs)
+    assert len(res) == 2 and all(r["episodes"] == 3 and r["train_iters"] == 3 for r in res)
+    ms = [m for m in _metrics(tmp_path) if any(k.endswith("grad_norm") for k in m)]
+    assert ms and all(v == v and v < 1e4 for m in ms for k, v in m.items() if k.endswith("grad_norm"))
