@@ -52,6 +52,9 @@ void symm_adamw_push(at::Tensor master, const at::Tensor& grad, at::Tensor m, at
                      int64_t lo, bool params_bf16, int64_t step, double lr, double b1, double b2, double eps, double wd,
                      const c10::optional<at::Tensor>& scale, int64_t rank, int64_t num_slots);
 int64_t symm_last_status();
+at::Tensor gdn_decode_step(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& g,
+                           const at::Tensor& beta, at::Tensor state, const at::Tensor& slots, const at::Tensor& fresh,
+                           double scale);
 void symm_push_chunks(const at::Tensor& src, const std::vector<int64_t>& dst_ptrs, int64_t chunk_bytes, bool all_to_all, int64_t rank);
 void symm_group_barrier(const std::vector<int64_t>& flag_ptrs, at::Tensor expect, int64_t slot, int64_t num_slots, int64_t rank);
 at::Tensor add_residual_rmsnorm(at::Tensor resid, const at::Tensor& delta, const c10::optional<at::Tensor>& w, double eps);
@@ -129,6 +132,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_combine", &moe_combine);
   m.def("moe_row_dot", &moe_row_dot);
   m.def("symm_ar_residual_rmsnorm", &symm_ar_residual_rmsnorm);
+  m.def("gdn_decode_step", &gdn_decode_step);
   m.def("symm_push_chunks", &symm_push_chunks);
   m.def("symm_group_barrier", &symm_group_barrier);
   m.def("gemm_bf16_nt", &gemm_bf16_nt);

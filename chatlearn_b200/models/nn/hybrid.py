@@ -133,6 +133,15 @@ def gated_delta_net(arch: ModelArch, p, x, ctx, layer: int):
     if st is not None:
         idx = (lens[:, None] + torch.arange(K - 1, device=x.device)[None]).unsqueeze(-1).expand(B, K - 1, C)
         st.conv[layer].index_copy_(0, st.slots, xp.gather(1, idx).to(st.conv[layer].dtype))
+    if L == 1 and T == B and st is not None and x.is_cuda and not torch.is_grad_enabled() and ops.get_mode() == "native":
+        # decode on the GPU: normalisation, grouped heads, decay, write and read-out of the state in one kernel
+        from chatlearn_b200.ops import native
+        y1 = y[:, 0]
+        o = native.C.gdn_decode_step(y1[:, :kd].reshape(B, nk, dk).contiguous(), y1[:, kd:2 * kd].reshape(B, nk, dk).contiguous(),
+                                     y1[:, 2 * kd:].reshape(B, nv, dv).contiguous(), g.contiguous(), bgate.contiguous(),
+                                     st.rec[layer], st.slots, st.fresh, 1.0 / math.sqrt(dk))
+        native.launch_counts["gdn_decode_step"] += 1
+        return _gdn_output(arch, p, o, z, x.dtype, T, vd)
     q = _l2norm(y[..., :kd].reshape(B, L, nk, dk).float()) * (1.0 / math.sqrt(dk))
     k = _l2norm(y[..., kd:2 * kd].reshape(B, L, nk, dk).float())
     v = y[..., 2 * kd:].reshape(B, L, nv, dv).float()
@@ -152,10 +161,14 @@ def gated_delta_net(arch: ModelArch, p, x, ctx, layer: int):
         o, S = gated_delta_chunked(q, k, v, gp, bp, init)
     if st is not None:
         st.rec[layer].index_copy_(0, st.slots, S.to(st.rec[layer].dtype))
-    o = o[seq, off]                                                      # back to the packed row: [T, nv, dv]
+    return _gdn_output(arch, p, o[seq, off], z, x.dtype, T, vd)           # back to the packed row: [T, nv, dv]
+
+
+def _gdn_output(arch, p, o, z, dtype, T, vd):
+    """Per-head RMSNorm of the read-out, gated by silu(z), then the output projection."""
     o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + arch.rms_norm_eps)
-    o = (p["gdn_norm"] * o.to(x.dtype)).float() * F.silu(z.float())
-    return ops.linear(o.to(x.dtype).reshape(T, vd), p["out_proj"])
+    o = (p["gdn_norm"] * o.to(dtype)).float() * F.silu(z.float())
+    return ops.linear(o.to(dtype).reshape(T, vd), p["out_proj"])
 
 
 def gated_attention(arch: ModelArch, p, x, ctx, layer: int):
