@@ -10,6 +10,12 @@ export PYTORCH_CUDA_ALLOC_CONF=${PYTORCH_CUDA_ALLOC_CONF:-expandable_segments:Tr
 # build the sm_100a extension once, in-tree
 python -c "import __graft_entry__ as g; g.build()" || exit 1
 launch() {   # launch <algorithm> <args...>
-  python -m torch.distributed.run --nnodes=1 --nproc-per-node "${num_device}" \
-    --master-addr "${MASTER_ADDR}" --master-port "${MASTER_PORT}" -m chatlearn_b200 "$@"
+  if [ "${NNODES:-1}" -gt 1 ]; then
+    # one launcher per node (NODE_RANK, NNODES, MASTER_ADDR, MASTER_PORT from the job environment): the launchers
+    # watch each other, so a failure on any node stops the whole job
+    python -m chatlearn_b200.launcher.dlc_utils --nproc-per-node "${num_device}" -- python -m chatlearn_b200 "$@"
+  else
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node "${num_device}" \
+      --master-addr "${MASTER_ADDR}" --master-port "${MASTER_PORT}" -m chatlearn_b200 "$@"
+  fi
 }
