@@ -184,13 +184,32 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
         ckv = ops.linear(x, p["kv_a_proj_with_mqa"])
         c = ops.rmsnorm(ckv[:, :arch.kv_lora_rank].contiguous(), p["kv_a_layernorm"], arch.rms_norm_eps)
         k_rope = ckv[:, arch.kv_lora_rank:].reshape(T, 1, rp)
-        kvb = ops.linear(c, p["kv_b_proj"]).view(T, nh_l, nope + dv)
-        k_nope, v = kvb[..., :nope], kvb[..., nope:].contiguous()
         q_rope = ops.rope(q[..., nope:].contiguous(), ctx.positions, arch.rope_theta)
         k_rope = ops.rope(k_rope.contiguous(), ctx.positions, arch.rope_theta)
         q = torch.cat([q[..., :nope], q_rope], dim=-1)
-        k = torch.cat([k_nope, k_rope.expand(T, nh_l, rp)], dim=-1)
         scale = 1.0 / math.sqrt(nope + rp)
+        if ctx.kv is not None:
+            # rollout: the cache keeps one compressed row per token (normalised latent | rotary key), shared by
+            # all heads; steps that read the cache attend in the latent space with the up-projections folded
+            # into the query and the output (q·W_uk on the left, ·W_uv on the right of a 1-head attention)
+            kvc = ctx.kv
+            kc = kvc.k_cache[layer]
+            lat = torch.cat([c, k_rope.reshape(T, rp)], dim=-1)
+            kc.view(-1, kc.shape[-1]).index_copy_(0, kvc.slot_mapping, lat.to(kc.dtype))
+            if not kvc.prefill_only:
+                lora = arch.kv_lora_rank
+                w_kvb = p["kv_b_proj"].view(nh_l, nope + dv, lora)
+                q_lat = torch.cat([torch.einsum("thn,hnc->thc", q[..., :nope], w_kvb[:, :nope]), q_rope], dim=-1)
+                o_lat = ops.paged_attention(q_lat.contiguous(), kc, kvc.v_cache[layer], kvc.block_tables, kvc.seq_lens,
+                                            kvc.q_lens, scale)
+                o = torch.einsum("thc,hvc->thv", o_lat.to(x.dtype), w_kvb[:, nope:])
+                out = o.reshape(T, nh_l * dv)
+                if partial:
+                    return ctx.tp_symm.gemm_partial(out.contiguous(), p["o_proj"])
+                return _tp_reduce(ops.linear(out, p["o_proj"]), ctx)
+        kvb = ops.linear(c, p["kv_b_proj"]).view(T, nh_l, nope + dv)
+        k_nope, v = kvb[..., :nope], kvb[..., nope:].contiguous()
+        k = torch.cat([k_nope, k_rope.expand(T, nh_l, rp)], dim=-1)
         nkv_l = nh_l
     else:
         qkv = ops.linear(x, p["qkv"], p.get("qkv_bias"))
@@ -214,7 +233,8 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
                                     arch.rope_theta)
     kv = ctx.kv
     if kv is not None:
-        ops.kv_append(k, v, kv.k_cache[layer], kv.v_cache[layer], kv.slot_mapping)
+        if not arch.use_mla:                 # (the latent row of an MLA layer is already in the cache)
+            ops.kv_append(k, v, kv.k_cache[layer], kv.v_cache[layer], kv.slot_mapping)
         if kv.prefill_only:
             o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, scale)
         else:

@@ -108,8 +108,7 @@ class RolloutEngine:
         a = self.arch
         tp = self.tp.size if self.tp is not None else 1
         if a.use_mla:
-            nkv_l = a.num_attention_heads // tp
-            per_tok = nkv_l * ((a.qk_nope_head_dim + a.qk_rope_head_dim) + a.v_head_dim)
+            per_tok = a.kv_lora_rank + a.qk_rope_head_dim       # one compressed row per token, shared by all heads
         else:
             from chatlearn_b200.models.nn.layout import kv_head_range
             nkv_l = kv_head_range(a, tp, 0)[1]
@@ -153,8 +152,7 @@ class RolloutEngine:
                 nb = int(t.item())
         self.num_blocks = nb
         if a.use_mla:
-            nkv_l = a.num_attention_heads // tp
-            dk, dv = a.qk_nope_head_dim + a.qk_rope_head_dim, a.v_head_dim
+            nkv_l, dk, dv = 1, a.kv_lora_rank + a.qk_rope_head_dim, a.kv_lora_rank
         else:
             from chatlearn_b200.models.nn.layout import kv_head_range
             nkv_l = kv_head_range(a, tp, self.tp.rank if self.tp is not None else 0)[1]
@@ -178,6 +176,10 @@ class RolloutEngine:
             self.lin_rec.append(None)
             self.k_cache.append(torch.zeros(nb + 1, self.block_size, nkv_l, dk, dtype=self.kv_dtype,
                                             device=self.device))
+            if a.use_mla:
+                # the "values" of latent attention are the latent part of the same rows
+                self.v_cache.append(self.k_cache[-1][..., :dv])
+                continue
             self.v_cache.append(torch.zeros(nb + 1, self.block_size, nkv_l, dv, dtype=self.kv_dtype,
                                             device=self.device))
         self.invalidate_graphs()
