@@ -384,8 +384,8 @@ class RolloutEngine:
             return False
         if self.arch.layer_types is not None:
             return False        # the recurrent-state layers run on PyTorch statements outside the captured step
-        if ops.get_mode() != "native":
-            return False        # the PyTorch statements of the ops synchronise with the host
+        if ops.get_mode() != "native" or self.model.dtype != torch.bfloat16:
+            return False        # the PyTorch statements of the ops (also taken for fp32 weights) synchronise with the host
         if any(n != 1 for n in plan.q_lens) or len(plan.seqs) > self._BUCKETS[-1]:
             return False
         if self.lockstep is not None and self.lockstep.size > 1:

@@ -41,3 +41,19 @@ def _check(device):
         # one compressed row per token: latent rank + rotary dims, a single shared "head"
         assert eng.k_cache[0].shape[-2:] == (1, arch.kv_lora_rank + arch.qk_rope_head_dim)
         assert eng.kv_bytes_per_block() == arch.num_hidden_layers * 8 * (arch.kv_lora_rank + arch.qk_rope_head_dim) * 4
+
+
+@pytest.mark.gpu
+def test_latent_cache_decode_in_captured_steps():
+    """bf16 weights: decode steps are captured in CUDA graphs; the latent attention has no host synchronisation."""
+    torch.manual_seed(0)
+    arch = PRESETS["tiny_mla_moe"]()
+    m = CausalLM(arch, dtype=torch.bfloat16, device="cuda").init_weights(7, std=0.08)
+    prompts = [torch.randint(0, 500, (n,)).tolist() for n in (3, 17, 40)]
+    outs = {}
+    for graphs in (True, False):
+        eng = RolloutEngine(m, max_model_len=128, block_size=16, num_blocks=32, use_cuda_graphs=graphs)
+        seqs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+        outs[graphs] = [s.output for s in seqs]
+        assert bool(eng._graphs) == graphs
+    assert outs[True] == outs[False]
