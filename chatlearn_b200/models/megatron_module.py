@@ -86,7 +86,8 @@ class MegatronModule(FSDPModule):
         self.cp_size = int(ma.context_parallel_size)
         self.ep_size = int(ma.expert_model_parallel_size)
         self.etp_size = int(ma.expert_tensor_parallel_size or 1)
-        assert self.etp_size == 1, "expert tensor parallelism > 1 is not supported (experts are EP-sharded)"
+        assert self.etp_size in (1, self.tp_size), \
+            "expert tensor parallelism is either off or spans the tensor-parallel group (etp == tp)"
         self.mesh = build_mesh(self.placement, tp=self.tp_size, cp=self.cp_size, pp=self.pp_size,
                                ep=self.ep_size, etp=self.etp_size,
                                kinds=("tp", "cp", "dp", "pp", "ep", "edp", "dp_cp", "mp"))
@@ -137,7 +138,8 @@ class MegatronModule(FSDPModule):
                                       ma.decoder_first_pipeline_num_layers, ma.decoder_last_pipeline_num_layers)
         pad = math.lcm(self.dp_group.size, self.edp_group.size)
         model = CausalLM(arch, dtype=self.compute_dtype, device=self.device, tp=self.tp_size, tp_rank=self.tp_rank,
-                         ep=self.ep_size, ep_rank=self.ep_rank, layer_range=(lo, hi),
+                         ep=self.ep_size, ep_rank=self.ep_rank, etp=self.etp_size,
+                         etp_rank=self.tp_rank if self.etp_size > 1 else 0, layer_range=(lo, hi),
                          with_embed=self.is_first_stage or (arch.tie_word_embeddings and self.is_last_stage),
                          with_head=self.is_last_stage, pad_to=pad)
         from chatlearn_b200.checkpoint.safetensors_io import has_safetensors, load_into_model

@@ -318,6 +318,24 @@ def qwen2_5_vl_7b() -> ModelArch:
                                         window_size=112, fullatt_block_indexes=[7, 15, 23, 31]))
 
 
+def qwen3_235b_a22b() -> ModelArch:
+    return ModelArch(model_type="qwen3_moe", vocab_size=151936, hidden_size=4096, num_hidden_layers=94,
+                     num_attention_heads=64, num_key_value_heads=4, head_dim=128, intermediate_size=12288,
+                     moe_intermediate_size=1536, num_experts=128, num_experts_per_tok=8, norm_topk_prob=True,
+                     router_aux_loss_coef=1e-3, rope_theta=1e6, max_position_embeddings=40960)
+
+
+def deepseek_v3_671b() -> ModelArch:
+    """DeepSeek-V3 shapes (the long-context rotary rescaling of the released checkpoint is not modelled)."""
+    return ModelArch(model_type="deepseek_v3", vocab_size=129280, hidden_size=7168, num_hidden_layers=61,
+                     num_attention_heads=128, num_key_value_heads=128, intermediate_size=18432,
+                     moe_intermediate_size=2048, num_experts=256, num_experts_per_tok=8, n_shared_experts=1,
+                     first_k_dense_replace=3, scoring_func="sigmoid", n_group=8, topk_group=4,
+                     routed_scaling_factor=2.5, norm_topk_prob=True, router_bias=True, kv_lora_rank=512,
+                     q_lora_rank=1536, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, head_dim=192,
+                     rope_theta=10000.0, rms_norm_eps=1e-6, max_position_embeddings=163840)
+
+
 def tiny_qwen3_next() -> ModelArch:
     """Qwen3-Next in miniature: three gated delta-net layers per gated-attention layer, MoE with a
     sigmoid-gated shared expert, a quarter of each head rotating."""
@@ -341,6 +359,7 @@ def qwen3_next_80b_a3b() -> ModelArch:
 
 PRESETS = {
     "tiny_qwen3_next": tiny_qwen3_next, "qwen3_next_80b_a3b": qwen3_next_80b_a3b,
+    "qwen3_235b_a22b": qwen3_235b_a22b, "deepseek_v3_671b": deepseek_v3_671b,
     "tiny_qwen2_5_vl": tiny_qwen2_5_vl, "qwen2_5_vl_7b": qwen2_5_vl_7b,
     "tiny_qwen3": tiny_qwen3, "qwen3_8b": qwen3_8b, "qwen3_30b_a3b": qwen3_30b_a3b,
     "llama2_7b": llama2_7b, "moonlight_16b_a3b": moonlight_16b_a3b, "tiny_moe": tiny_moe,

@@ -112,7 +112,7 @@ def _hybrid_mixer_leaves(arch: ModelArch, l: int, pre: str, hp: str) -> List[Lea
 
 
 def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int = 1,
-                 ep_rank: int = 0) -> List[Leaf]:
+                 ep_rank: int = 0, etp: int = 1, etp_rank: int = 0) -> List[Leaf]:
     """Leaves of decoder layer ``l`` for one (tp, ep) rank."""
     H = arch.hidden_size
     pre, hp = f"layers.{l}.", f"model.layers.{l}."
@@ -188,6 +188,8 @@ def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int
         E, Fm = arch.num_experts, arch.moe_intermediate_size
         assert E % ep == 0, f"{E} experts not divisible by ep={ep}"
         El = E // ep
+        assert Fm % etp == 0, f"expert width {Fm} not divisible by etp={etp}"
+        Fe = Fm // etp
         m = hp + "mlp."
         out.append(_full(pre + "router", (E, H), m + "gate.weight"))
         if arch.router_bias:
@@ -195,11 +197,12 @@ def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int
         s13, s2 = [], []
         for j in range(El):
             e = ep_rank * El + j
-            s13.append(_rows(f"{m}experts.{e}.gate_proj.weight", (Fm, H), 0, Fm, 0, j))
-            s13.append(_rows(f"{m}experts.{e}.up_proj.weight", (Fm, H), 0, Fm, Fm, j))
-            s2.append(_rows(f"{m}experts.{e}.down_proj.weight", (H, Fm), 0, H, 0, j))
-        out.append(Leaf(pre + "w13", (El, 2 * Fm, H), "normal", s13))
-        out.append(Leaf(pre + "w2", (El, H, Fm), "normal", s2))
+            # expert tensor parallelism: every rank of the group keeps 1/etp of each expert's hidden width
+            s13.append(_rows(f"{m}experts.{e}.gate_proj.weight", (Fm, H), etp_rank * Fe, Fe, 0, j))
+            s13.append(_rows(f"{m}experts.{e}.up_proj.weight", (Fm, H), etp_rank * Fe, Fe, Fe, j))
+            s2.append(_cols(f"{m}experts.{e}.down_proj.weight", (H, Fm), etp_rank * Fe, Fe, 0, j))
+        out.append(Leaf(pre + "w13", (El, 2 * Fe, H), "normal", s13))
+        out.append(Leaf(pre + "w2", (El, H, Fe), "normal", s2))
         if arch.n_shared_experts:
             Fs = arch.n_shared_experts * Fm
             sh = mlp_leaves(pre + "shared_", m + "shared_experts.", Fs, True)
@@ -238,7 +241,7 @@ def head_leaves(arch: ModelArch, tp: int = 1, tp_rank: int = 0) -> List[Leaf]:
 
 def model_blocks(arch: ModelArch, tp=1, tp_rank=0, ep=1, ep_rank=0,
                  layer_range: Optional[Tuple[int, int]] = None,
-                 with_embed=True, with_head=True) -> List[Tuple[str, List[Leaf]]]:
+                 with_embed=True, with_head=True, etp=1, etp_rank=0) -> List[Tuple[str, List[Leaf]]]:
     """Blocks (= FSDP units / offload units) of a model instance in forward order.
     ``layer_range`` selects a pipeline stage's layers."""
     lo, hi = layer_range or (0, arch.num_hidden_layers)
@@ -246,7 +249,7 @@ def model_blocks(arch: ModelArch, tp=1, tp_rank=0, ep=1, ep_rank=0,
     if with_embed:
         blocks.append(("embed", embed_leaves(arch, tp, tp_rank)))
     for l in range(lo, hi):
-        leaves = layer_leaves(arch, l, tp, tp_rank, ep, ep_rank)
+        leaves = layer_leaves(arch, l, tp, tp_rank, ep, ep_rank, etp, etp_rank)
         experts = [lf for lf in leaves if lf.name.endswith((".w13", ".w2"))]
         blocks.append((f"layer{l}", [lf for lf in leaves if lf not in experts]))
         if experts:

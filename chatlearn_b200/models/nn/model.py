@@ -275,7 +275,17 @@ def moe_block(arch: ModelArch, p, x, ctx: FwdCtx):
     if arch.router_aux_loss_coef > 0 and torch.is_grad_enabled():
         ctx.aux_losses.append(arch.router_aux_loss_coef *
                               ops.moe_aux_loss(scores, idx, arch.num_experts, arch.num_experts_per_tok))
-    if ctx.ep is not None and ctx.ep.size > 1:
+    if p["w13"].shape[1] != 2 * arch.moe_intermediate_size:
+        # expert tensor parallelism (= the TP group): every rank holds 1/tp of each expert's hidden width and
+        # sees the same tokens, so its expert output is a partial sum; inputs and routing weights get their
+        # gradients summed over the group, the output is all-reduced
+        x_, w_ = _tp_copy(x, ctx), _tp_copy(w, ctx)
+        if ctx.ep is not None and ctx.ep.size > 1:
+            y = ctx.ep.experts(x_, p["w13"], p["w2"], w_, idx, arch.num_experts)
+        else:
+            y = ops.moe_experts(x_, p["w13"], p["w2"], w_, idx)
+        y = _tp_reduce(y, ctx)
+    elif ctx.ep is not None and ctx.ep.size > 1:
         tp = ctx.tp
         if tp is not None and tp.size > 1:
             # the ranks of a TP group hold the same tokens: each dispatches its own
@@ -391,14 +401,15 @@ class CausalLM:
 
     def __init__(self, arch: ModelArch, dtype=torch.float32, device="cpu", tp=1, tp_rank=0,
                  ep=1, ep_rank=0, layer_range=None, with_embed=True, with_head=True,
-                 pad_to: int = 1, allocate: bool = True):
+                 pad_to: int = 1, allocate: bool = True, etp: int = 1, etp_rank: int = 0):
         self.arch, self.dtype, self.device = arch, dtype, torch.device(device)
         self.tp, self.tp_rank, self.ep, self.ep_rank = tp, tp_rank, ep, ep_rank
+        self.etp, self.etp_rank = etp, etp_rank
         self.layer_range = layer_range or (0, arch.num_hidden_layers)
         self.blocks: List[ParamBlock] = [
             ParamBlock(n, leaves, dtype, self.device, pad_to, allocate)
             for n, leaves in model_blocks(arch, tp, tp_rank, ep, ep_rank, layer_range,
-                                          with_embed, with_head)]
+                                          with_embed, with_head, etp, etp_rank)]
         self.block_by_name = {b.name: b for b in self.blocks}
 
     # ---- parameters ----

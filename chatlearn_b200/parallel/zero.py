@@ -60,6 +60,8 @@ class ShardedTrainState:
                  ep_group: Optional[Group] = None, tp_group: Optional[Group] = None):
         self.model = model
         self.tp_size, self.ep_group, self.tp_group = tp_size, ep_group, tp_group
+        # expert tensor parallelism: the expert leaves of the tensor-parallel ranks are different slices
+        self.expert_tp_sharded = getattr(model, "etp", 1) > 1
         self.dp = dp_group or single_group()
         self.edp = expert_dp_group or self.dp
         self.lr, self.betas, self.eps, self.wd, self.clip = lr, betas, eps, weight_decay, clip_grad
@@ -162,8 +164,14 @@ class ShardedTrainState:
                 a, b = max(o, s.lo), min(o + lf.numel, s.hi)
                 if b <= a:
                     continue
-                # expert blocks are summed over the expert-parallel group instead (below)
-                rep = lf.replicated and not s.block.name.endswith(".experts")
+                if s.block.name.endswith(".experts"):
+                    # with an expert-data-parallel group of their own they are summed over the expert-parallel
+                    # group instead (below); otherwise the tensor-parallel ranks hold copies of the same experts
+                    # unless expert tensor parallelism slices them
+                    own = s.group is self.edp and self.edp is not self.dp
+                    rep = not own and not self.expert_tp_sharded
+                else:
+                    rep = lf.replicated
                 w = 1.0 / self.tp_size if rep else 1.0
                 if out and out[-1][2] == w and out[-1][1] == a - s.lo:
                     out[-1] = (out[-1][0], b - s.lo, w)
@@ -202,7 +210,7 @@ class ShardedTrainState:
             if self.ep_group is not None:
                 self.ep_group.all_reduce_(edp_sq)
             for g in self.extra_norm_groups:
-                if g is not self.tp_group:
+                if g is not self.tp_group or self.expert_tp_sharded:
                     g.all_reduce_(edp_sq)
         return (dp_sq + edp_sq).sqrt()
 

@@ -13,7 +13,8 @@ launch grpo --config-file template/grpo_megatron.yaml \
     models.policy_trainer.num_gpu=${num_device} \
     models.policy_trainer.load=${CHATLEARN}/pretrained_models/Moonlight-16B-A3B/ \
     models.policy_trainer.context_parallel_size=2 \
-    models.policy_trainer.tensor_model_parallel_size=1 \
-    models.policy_trainer.expert_model_parallel_size=4 \
+    models.policy_trainer.tensor_model_parallel_size=2 \
+    models.policy_trainer.expert_tensor_parallel_size=2 \
+    models.policy_trainer.expert_model_parallel_size=2 \
     models.policy.max_response_tokens_length=8192 \
     2>&1 | tee ${CHATLEARN}/output_${exp_name}.log

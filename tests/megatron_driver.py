@@ -21,7 +21,7 @@ out = os.environ["OUT_DIR"]
 tag = os.environ["TAG"]
 W = int(os.environ.get("WORLD_SIZE", "1"))
 rank = int(os.environ.get("RANK", "0"))
-tp, pp, cp, ep = (int(os.environ.get(k, "1")) for k in ("TP", "PP", "CP", "EP"))
+tp, pp, cp, ep, etp = (int(os.environ.get(k, "1")) for k in ("TP", "PP", "CP", "EP", "ETP"))
 preset = os.environ.get("PRESET", "tiny_qwen3")
 hf_dir = os.path.join(out, "hf_init")
 if rank == 0 and not os.path.exists(os.path.join(hf_dir, "done")):
@@ -42,7 +42,7 @@ cfg = {
     "models": {
         "policy_trainer": {"num_gpu": W, "trainable": True, "load": hf_dir, "tensor_model_parallel_size": tp,
                            "pipeline_model_parallel_size": pp, "context_parallel_size": cp,
-                           "expert_model_parallel_size": ep, "packing": os.environ.get("PACKING", "1") == "1",
+                           "expert_model_parallel_size": ep, "expert_tensor_parallel_size": etp, "packing": os.environ.get("PACKING", "1") == "1",
                            "max_token_in_packing": 96, "generation_batch_size": 4, "kl_coef": 0.01,
                            "entropy_coef": 0.001, "optimizer": {"lr": 1e-3, "clip_grad": 1.0},
                            "use_group_sequence_policy": os.environ.get("GSPO", "0") == "1",

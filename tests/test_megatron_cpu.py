@@ -50,7 +50,9 @@ def test_dense_parallel_matches_single(tmp_path, name, world, env):
     _compare(base, par)
 
 
-@pytest.mark.parametrize("name,world,env", [("ep2", 2, dict(EP=2)), ("tp2ep2", 4, dict(TP=2, EP=2))])
+@pytest.mark.parametrize("name,world,env", [("ep2", 2, dict(EP=2)), ("tp2ep2", 4, dict(TP=2, EP=2)),
+                                            ("tp2etp2", 2, dict(TP=2, ETP=2)), ("tp2etp2ep2", 4, dict(TP=2, ETP=2, EP=2)),
+                                            ("tp2_replicated_experts", 2, dict(TP=2))])
 def test_moe_parallel_matches_single(tmp_path, name, world, env):
     base = _run(tmp_path, "base", 1, PRESET="tiny_moe", NOAUX=1)
     par = _run(tmp_path, name, world, PRESET="tiny_moe", NOAUX=1, **env)

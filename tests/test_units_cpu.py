@@ -249,3 +249,35 @@ def test_scheduler_never_mixes_fresh_prompts_with_continuation_chunks():
                 if len(q.output) >= q.max_new_tokens:
                     sch.finish(q, "length")
     assert all(q.finished for q in seqs)
+
+
+def test_planner_gathers_expert_tensor_parallel_slices():
+    """Trainer ranks with tensor- and expert-tensor-parallel slices (tp = etp = 2, experts on two ep ranks each)
+    feed a rollout model whose experts are whole and spread over two ep ranks."""
+    from chatlearn_b200.synchronizer.parameter_sync import layout_of_model
+    from chatlearn_b200.synchronizer.plan import build_plan, validate_plan
+    arch = PRESETS["tiny_moe"]()
+    full = CausalLM(arch, dtype=torch.float32).init_weights(11)
+    hf = full.hf_state_dict()
+    src_lays, src_bufs, rank = [], {}, 0
+    for e in range(2):
+        for t in range(2):
+            m = CausalLM(arch, dtype=torch.float32, tp=2, tp_rank=t, ep=2, ep_rank=e, etp=2, etp_rank=t)
+            m.load_hf_state_dict(hf)
+            assert m.block_by_name["layer0.experts"].params["w13"].shape == (4, arch.moe_intermediate_size, arch.hidden_size)
+            src_lays.append(layout_of_model(m, rank, prefix="s/"))
+            src_bufs[rank] = {f"s/{b.name}": b.flat for b in m.blocks}
+            rank += 1
+    dst_lays, dst_models, dst_bufs = [], {}, {}
+    for e in range(2):
+        m = CausalLM(arch, dtype=torch.float32, ep=2, ep_rank=e)
+        dst_lays.append(layout_of_model(m, e, prefix="d/"))
+        dst_models[e], dst_bufs[e] = m, {f"d/{b.name}": b.flat for b in m.blocks}
+    plan = build_plan(src_lays, dst_lays)
+    validate_plan(plan, dst_lays)
+    _run_plan(plan, src_bufs, dst_bufs)
+    for e, m in dst_models.items():
+        want = CausalLM(arch, dtype=torch.float32, ep=2, ep_rank=e)
+        want.load_hf_state_dict(hf)
+        for a, b in zip(m.blocks, want.blocks):
+            assert torch.equal(a.flat, b.flat), (e, a.name)
