@@ -48,6 +48,8 @@ class ModelArch:
     qk_nope_head_dim: int = 0
     qk_rope_head_dim: int = 0
     v_head_dim: int = 0
+    rope_interleave: Optional[bool] = None   # rotary dims stored as (even, odd) pairs (DeepSeek checkpoints); None: by family
+    rope_scaling: Optional[Dict[str, Any]] = None   # {"type": "yarn", "factor", "original_max_position_embeddings", ...}
     # vision-language models: rotary sections (time, row, column) and the vision tower's config
     mrope_section: Optional[List[int]] = None
     mrope_interleaved: bool = False      # Qwen3-VL frequency layout
@@ -82,6 +84,13 @@ class ModelArch:
             self.attention_bias = True
         if self.model_type in ("deepseek_v3", "deepseek_v2", "kimi_k2", "moonlight"):
             self.use_mla = self.kv_lora_rank > 0
+            if self.rope_interleave is None:
+                self.rope_interleave = True      # the released checkpoints of this family pair up the rotary dims
+        self.rope_interleave = bool(self.rope_interleave)
+        if isinstance(self.rope_scaling, dict):
+            kind = self.rope_scaling.get("rope_type", self.rope_scaling.get("type"))
+            if kind != "yarn" or not self.use_mla:
+                self.rope_scaling = None         # only the long-context rescaling of MLA models is modelled
         if self.model_type != "qwen3_next":
             self.layer_types = None          # other families list "full_attention" / sliding-window kinds there
         if self.model_type == "qwen3_next":
@@ -181,6 +190,8 @@ class ModelArch:
             for key in ("rope_theta", "partial_rotary_factor"):
                 if key in rs and key not in d:
                     d = dict(d, **{key: rs[key]})
+            if rs.get("rope_type", rs.get("type")) == "yarn" and not d.get("rope_scaling"):
+                d = dict(d, rope_scaling=dict(rs))
         for k, v in d.items():
             k = cls._HF_ALIASES.get(k, k)
             if k in known and k != "extra":

@@ -41,3 +41,62 @@ def latent_paged_attention(q, k_cache, lora: int, block_tables, seq_lens, q_lens
     p = att.softmax(-1).to(q.dtype).view(B, max_q * nh, K)
     o = torch.bmm(p, rows[..., :lora]).view(B, max_q, nh, lora)
     return o[seq, off]
+
+
+# ------------------------------------------------------------------ rotary embedding of the decoupled key
+def yarn_mscale(factor: float, m: float = 1.0) -> float:
+    import math
+    return 0.1 * m * math.log(factor) + 1.0 if factor > 1 else 1.0
+
+
+def yarn_inv_freq(dim: int, theta: float, sc: dict):
+    """Inverse frequencies of the YaRN long-context rescaling and the factor applied to cos/sin: low
+    frequencies are interpolated by ``factor``, high ones kept, with a linear ramp between the two
+    correction dims (DeepSeek-V3's released configuration; the reference passes ``rotary_scaling_factor``
+    / ``mscale`` to Megatron in chatlearn/utils/megatron_utils.py:100-140)."""
+    import math
+    factor = float(sc["factor"])
+    orig = float(sc.get("original_max_position_embeddings", 4096))
+    beta_fast, beta_slow = float(sc.get("beta_fast", 32)), float(sc.get("beta_slow", 1))
+    mscale, mscale_all = sc.get("mscale"), sc.get("mscale_all_dim")
+    att = yarn_mscale(factor, mscale) / yarn_mscale(factor, mscale_all) if mscale and mscale_all else yarn_mscale(factor)
+
+    def corr(rot):
+        return dim * math.log(orig / (rot * 2 * math.pi)) / (2 * math.log(theta))
+    low, high = corr(beta_fast), corr(beta_slow)
+    if sc.get("truncate", True):
+        low, high = math.floor(low), math.ceil(high)
+    low, high = max(low, 0), min(high, dim - 1)
+    if low == high:
+        high += 0.001
+    pos = theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim)
+    ramp = ((torch.arange(dim // 2, dtype=torch.float32) - low) / (high - low)).clamp(0, 1)
+    inv = (1.0 / (factor * pos)) * ramp + (1.0 / pos) * (1 - ramp)
+    return inv, float(att)
+
+
+def attention_scale(arch) -> float:
+    """Softmax scale of an MLA layer; YaRN multiplies it by mscale(factor, mscale_all_dim)^2."""
+    s = (arch.qk_nope_head_dim + arch.qk_rope_head_dim) ** -0.5
+    sc = arch.rope_scaling
+    if sc and sc.get("mscale_all_dim"):
+        m = yarn_mscale(float(sc["factor"]), float(sc["mscale_all_dim"]))
+        s *= m * m
+    return s
+
+
+def rope_decoupled(arch, x, positions):
+    """Rotary embedding of the rotary slice of q or k: ``x`` [T, heads, rope dims].  Checkpoints of this
+    family store the rotary dims as (even, odd) pairs; they are brought into the half-split order first."""
+    from chatlearn_b200 import ops
+    T, h, rp = x.shape
+    if arch.rope_interleave:
+        x = x.view(T, h, rp // 2, 2).transpose(-1, -2).reshape(T, h, rp)
+    if not arch.rope_scaling:
+        return ops.rope(x.contiguous(), positions, arch.rope_theta)
+    inv, att = yarn_inv_freq(rp, arch.rope_theta, arch.rope_scaling)
+    ang = positions.float()[:, None] * inv.to(x.device)[None]              # [T, rp / 2]
+    cos, sin = (torch.cat([f, f], -1)[:, None] * att for f in (ang.cos(), ang.sin()))
+    xf = x.float()
+    rot = torch.cat([-xf[..., rp // 2:], xf[..., :rp // 2]], dim=-1)
+    return (xf * cos + rot * sin).to(x.dtype)

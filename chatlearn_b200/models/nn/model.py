@@ -184,10 +184,11 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
         ckv = ops.linear(x, p["kv_a_proj_with_mqa"])
         c = ops.rmsnorm(ckv[:, :arch.kv_lora_rank].contiguous(), p["kv_a_layernorm"], arch.rms_norm_eps)
         k_rope = ckv[:, arch.kv_lora_rank:].reshape(T, 1, rp)
-        q_rope = ops.rope(q[..., nope:].contiguous(), ctx.positions, arch.rope_theta)
-        k_rope = ops.rope(k_rope.contiguous(), ctx.positions, arch.rope_theta)
+        from .mla import attention_scale, rope_decoupled
+        q_rope = rope_decoupled(arch, q[..., nope:], ctx.positions)
+        k_rope = rope_decoupled(arch, k_rope, ctx.positions)
         q = torch.cat([q[..., :nope], q_rope], dim=-1)
-        scale = 1.0 / math.sqrt(nope + rp)
+        scale = attention_scale(arch)
         if ctx.kv is not None:
             # rollout: the cache keeps one compressed row per token (normalised latent | rotary key), shared by
             # all heads; steps that read the cache attend in the latent space with the up-projections folded
