@@ -47,6 +47,7 @@ class PolicyTrainerConfig(BaseModelConfig):
     final_clip_ratio: float = 3.0
     use_group_sequence_policy: bool = False
     train_micro_batch_size: int = 1
+    train_vision_tower: bool = False      # vision-language models: update the vision tower too (frozen otherwise)
 
     def _validate_impl(self):
         assert self.pos_clip_ratio >= 0 and self.neg_clip_ratio >= 0

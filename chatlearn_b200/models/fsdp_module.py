@@ -76,6 +76,12 @@ class FSDPModule(TorchModule):
         self.vision = build_vision_tower(self.arch, self.compute_dtype, self.device, getattr(self.module_args, "load", None))
         if self.vision is not None:
             assert self.sp is None, "vision-language models run without Ulysses sequence parallelism"
+            if self.trainable and bool(getattr(self.module_args, "train_vision_tower", False)):
+                # the tower's weights become one more parameter block: sharded optimizer state, gradient
+                # reduction, offload, checkpoints and the weight sync into the rollout engine cover it
+                from chatlearn_b200.models.nn.vision import attach_vision_block
+                dp = self.dp_group.size if self.dp_group is not None else 1
+                attach_vision_block(self.model, self.vision, pad_to=dp * 8)
         if self.trainable:
             oc = self.module_args.optimizer
             grad_dtype = torch.float32

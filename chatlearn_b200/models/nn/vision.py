@@ -410,6 +410,28 @@ def build_vision_tower(arch, dtype, device, load: str = None, seed: int = 4321):
     return tower
 
 
+def attach_vision_block(lm, tower, pad_to: int = 1):
+    """Make the tower's weights a parameter block of the language model ("vision", after the head), so that
+    the sharded optimizer state, gradient reduction, offload, checkpoints and the trainer -> rollout weight
+    sync treat them like every other block.  The reference trains the tower with the rest of the HF model
+    under FSDP (chatlearn/models/fsdp_module.py:250-295).  Leaves carry the HF names (``visual.*``); the
+    patch-embedding kernel stays flattened to a matrix."""
+    from .layout import _full
+    from .model import ParamBlock
+    if "vision" in lm.block_by_name:
+        return lm.block_by_name["vision"]
+    leaves = [_full(k, tuple(p.shape), k) for k, p in tower.params.items()]
+    blk = ParamBlock("vision", leaves, tower.dtype, tower.device, pad_to)
+    with torch.no_grad():
+        for k, p in tower.params.items():
+            blk.params[k].copy_(p)
+    tower.params = blk.params                  # the same dict: re-bound leaves (offload, autograd) stay visible
+    tower.trainable = True
+    lm.blocks.append(blk)
+    lm.block_by_name["vision"] = blk
+    return blk
+
+
 def multimodal_inputs(lm, tower, tokens: torch.Tensor, seq_lens, mm, ctx):
     """Input embeddings and (time, row, column) positions of a packed row whose samples may carry
     images.  ``mm[i] = (pixel_values, image_grid_thw)`` or ``(None, None)`` per sample; segments
@@ -435,7 +457,8 @@ def multimodal_inputs(lm, tower, tokens: torch.Tensor, seq_lens, mm, ctx):
     ctx.mrope_positions = torch.cat(pos, 1).contiguous().to(tokens.device)
     x = embed(lm.block_by_name["embed"].params, tokens, ctx).to(lm.dtype)
     if px:
-        with torch.no_grad():
+        # a tower whose weights are a parameter block of the model (attach_vision_block) is trained with it
+        with torch.set_grad_enabled(torch.is_grad_enabled() and getattr(tower, "trainable", False)):
             img = tower(torch.cat(px, 0).to(tokens.device), grids)
         taps = []
         if isinstance(img, tuple):

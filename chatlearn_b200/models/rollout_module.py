@@ -109,8 +109,13 @@ class RolloutModule(TorchModule):
         self.tokenizer = load_tokenizer(load, self.arch.vocab_size, kind=str(getattr(ma, "tokenizer", "auto")))
 
     def _build_vision(self, load):
-        from chatlearn_b200.models.nn.vision import build_vision_tower
-        return build_vision_tower(self.arch, self.compute_dtype, self.device, load)
+        from chatlearn_b200.models.nn.vision import attach_vision_block, build_vision_tower
+        tower = build_vision_tower(self.arch, self.compute_dtype, self.device, load)
+        trainer = getattr(self.global_args.models, "policy_trainer", None)
+        if tower is not None and trainer is not None and bool(getattr(trainer, "train_vision_tower", False)):
+            # the trainer updates the tower: its weights join this model's blocks and arrive with every weight sync
+            attach_vision_block(self.model, tower)
+        return tower
 
     # ------------------------------------------------------------------ generation
     def _sampling_params(self, is_eval: bool, max_tokens: int) -> SamplingParams:

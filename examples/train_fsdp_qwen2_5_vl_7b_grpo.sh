@@ -19,4 +19,5 @@ launch grpo --config-file template/grpo_fsdp.yaml \
     models.policy_trainer.ulysses_sequence_parallel_size=1 \
     models.policy.max_prompt_tokens_length=2048 \
     models.policy.max_response_tokens_length=2048 \
+    models.policy_trainer.train_vision_tower=True \
     2>&1 | tee ${CHATLEARN}/output_${exp_name}.log

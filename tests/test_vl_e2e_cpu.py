@@ -41,16 +41,35 @@ cfg = {
        "kv_block_size": 8, "num_kv_blocks": 512, "ignore_eos": True, "max_pixels": 28 * 28 * 16},
     "reward": {"num_cpu": 2},
   }}
+train_tower = os.environ.get("TRAIN_TOWER", "0") == "1"
+cfg["models"]["policy_trainer"]["train_vision_tower"] = train_tower
 cfg = to_dataclass(GrpoConfig, resolve(cfg))
 algo = GrpoAlgorithm(cfg); algo.validate()
+from chatlearn_b200.models.nn.vision import build_vision_tower
+from chatlearn_b200.models.nn import PRESETS
+w0 = build_vision_tower(PRESETS["tiny_qwen2_5_vl"](), torch.float32, "cpu").params      # the seeded initial tower
 stats = algo.run()
 eng = algo.engine
 tr = eng.named_models["policy_trainer"]
 pol = eng.named_models["policy"]
 sample_tokens = [len(d) for d in pol._all_datasets[0].data and [s["input_ids"] for s in pol._all_datasets[0].data]]
+# the rollout tower against the initial one and against the trainer's (its fp32 master weights after the last step
+# are what the last weight sync delivered when another episode follows; compare with the bf16/fp32 working copy)
+name = "visual.blocks.0.attn.qkv.weight"
+moved = float((pol.engine.vision.params[name].float() - w0[name].float()).abs().max())
 print("RESULT " + json.dumps({"rank": int(os.environ["RANK"]), "episodes": len(stats), "train_iters": tr._train_iteration,
-      "has_tower": tr.vision is not None and pol.engine.vision is not None, "prompt_lens": sample_tokens[:3]}))
+      "has_tower": tr.vision is not None and pol.engine.vision is not None, "prompt_lens": sample_tokens[:3],
+      "tower_moved": moved, "tower_block": "vision" in tr.model.block_by_name and "vision" in pol.model.block_by_name}))
 '''
+
+
+def test_vision_tower_is_trained_and_synchronised(tmp_path):
+    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "TRAIN_TOWER": "1"})
+    res = [json.loads(line[7:]) for o in outs for line in o.splitlines() if line.startswith("RESULT ")]
+    assert len(res) == 2
+    for r in res:
+        assert r["episodes"] == 2 and r["train_iters"] == 2 and r["tower_block"]
+        assert r["tower_moved"] > 0                           # the rollout engine's tower received updated weights
 
 
 def test_vision_language_grpo(tmp_path):
@@ -60,3 +79,4 @@ def test_vision_language_grpo(tmp_path):
     for r in res:
         assert r["episodes"] == 2 and r["train_iters"] == 2 and r["has_tower"]
         assert all(n > 11 for n in r["prompt_lens"])          # the single placeholder was expanded to the image's tokens
+        assert r["tower_moved"] == 0 and not r["tower_block"]  # frozen tower
