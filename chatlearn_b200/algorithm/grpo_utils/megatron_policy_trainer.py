@@ -94,8 +94,16 @@ class MegatronPolicyTrainer(MegatronModule):
 
             def hook(l, p, x, c):
                 return checkpoint(lambda xx: decoder_layer(arch, p, xx, c, l), x, use_reentrant=False)
+        x0 = None
+        if getattr(self, "vision", None) is not None:
+            from chatlearn_b200.models.nn.vision import multimodal_inputs
+            x0 = multimodal_inputs(self.model, self.vision, tokens, batch.seq_lens, batch.mm or [], ctx,
+                                   with_embeddings=self.is_first_stage)
+            if ctx.deepstack is not None:
+                lo, hi = self.model.layer_range
+                assert hi - lo >= len(ctx.deepstack[1]), "the first pipeline stage must hold every deep-stack layer"
         if self.is_first_stage:
-            h = self.model.hidden_states(tokens, ctx, hook)
+            h = self.model.hidden_states(tokens, ctx, hook, x=x0)
         else:
             h = x_in
             for l in range(*self.model.layer_range):

@@ -155,6 +155,14 @@ class MegatronModule(FSDPModule):
         self.arch = self.resolve_arch()
         self.model = self.create_model()
         self.ep = ExpertParallel(self.ep_group) if self.ep_size > 1 else None
+        # vision-language models: every stage needs the (time, row, column) positions, the first stage also the
+        # tower's embeddings (and, when the tower is trained, its weights as one more parameter block)
+        from chatlearn_b200.models.nn.vision import attach_vision_block, build_vision_tower
+        self.vision = build_vision_tower(self.arch, self.compute_dtype, self.device, getattr(self.module_args, "load", None))
+        if self.vision is not None:
+            assert self.cp_size == 1, "vision-language models run without context parallelism"
+            if self.trainable and self.is_first_stage and bool(getattr(self.module_args, "train_vision_tower", False)):
+                attach_vision_block(self.model, self.vision, pad_to=math.lcm(self.dp_group.size, self.edp_group.size))
         self.cp = ContextParallel(self.cp_group) if self.cp_size > 1 else None
         if self.cp is not None:
             from chatlearn_b200.parallel import symm_collectives

@@ -432,7 +432,7 @@ def attach_vision_block(lm, tower, pad_to: int = 1):
     return blk
 
 
-def multimodal_inputs(lm, tower, tokens: torch.Tensor, seq_lens, mm, ctx):
+def multimodal_inputs(lm, tower, tokens: torch.Tensor, seq_lens, mm, ctx, with_embeddings: bool = True):
     """Input embeddings and (time, row, column) positions of a packed row whose samples may carry
     images.  ``mm[i] = (pixel_values, image_grid_thw)`` or ``(None, None)`` per sample; segments
     past ``len(mm)`` (alignment padding) count up from zero.  Sets ``ctx.mrope_positions`` and
@@ -455,6 +455,8 @@ def multimodal_inputs(lm, tower, tokens: torch.Tensor, seq_lens, mm, ctx):
         pos.append(p3)
         off += L
     ctx.mrope_positions = torch.cat(pos, 1).contiguous().to(tokens.device)
+    if not with_embeddings:            # later pipeline stages need the positions only
+        return None
     x = embed(lm.block_by_name["embed"].params, tokens, ctx).to(lm.dtype)
     if px:
         # a tower whose weights are a parameter block of the model (attach_vision_block) is trained with it

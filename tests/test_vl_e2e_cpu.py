@@ -42,6 +42,14 @@ cfg = {
     "reward": {"num_cpu": 2},
   }}
 train_tower = os.environ.get("TRAIN_TOWER", "0") == "1"
+if os.environ.get("BACKEND", "fsdp") == "megatron":
+    # Megatron-style trainer: tensor or pipeline parallel over the two ranks
+    par = {"tensor_model_parallel_size": int(os.environ.get("TP", "1")), "pipeline_model_parallel_size": int(os.environ.get("PP", "1"))}
+    mcfg = {"num_layers": 1, "hidden_size": 8, "num_attention_heads": 1, "ffn_hidden_size": 8, "max_position_embeddings": 64, "kv_channels": 8}
+    cfg["runtime_args"]["train_backend"] = "megatron"
+    for role in ("policy_trainer", "ref_policy"):
+        cfg["models"][role].pop("fsdp_size")
+        cfg["models"][role].update(par, megatron_model_cfg=dict(mcfg))
 cfg["models"]["policy_trainer"]["train_vision_tower"] = train_tower
 cfg = to_dataclass(GrpoConfig, resolve(cfg))
 algo = GrpoAlgorithm(cfg); algo.validate()
@@ -80,3 +88,17 @@ def test_vision_language_grpo(tmp_path):
         assert r["episodes"] == 2 and r["train_iters"] == 2 and r["has_tower"]
         assert all(n > 11 for n in r["prompt_lens"])          # the single placeholder was expanded to the image's tokens
         assert r["tower_moved"] == 0 and not r["tower_block"]  # frozen tower
+
+
+def test_vision_language_grpo_megatron_backend(tmp_path):
+    """Tensor-parallel and pipeline-parallel trainers: the first stage runs the tower, every stage gets the
+    (time, row, column) positions; with a trained tower the rollout engine receives it from the first stage."""
+    for name, env in (("tp2", dict(TP="2")), ("pp2", dict(PP="2", TRAIN_TOWER="1"))):
+        d = tmp_path / name
+        d.mkdir()
+        outs, _ = run_ranks(SCRIPT, 2, env=dict(env, OUT_DIR=str(d), BACKEND="megatron"))
+        res = [json.loads(line[7:]) for o in outs for line in o.splitlines() if line.startswith("RESULT ")]
+        assert len(res) == 2, name
+        for r in res:
+            assert r["episodes"] == 2 and r["train_iters"] == 2 and r["has_tower"], (name, r)
+            assert (r["tower_moved"] > 0) == ("TRAIN_TOWER" in env), (name, r)
