@@ -177,6 +177,9 @@ class ModelArch:
             # vision-language checkpoints nest the language model's settings
             outer = {k: v for k, v in d.items() if k != "text_config"}
             d = {**outer, **d["text_config"]}
+            if "tie_word_embeddings" in outer:
+                # the wrapping model decides whether the output head shares the embedding matrix
+                d["tie_word_embeddings"] = outer["tie_word_embeddings"]
             d["model_type"] = {"qwen2_5_vl": "qwen2", "qwen2_5_vl_text": "qwen2", "qwen2_vl": "qwen2",
                                "qwen3_vl": "qwen3", "qwen3_vl_text": "qwen3", "qwen3_vl_moe": "qwen3_moe",
                                "qwen3_vl_moe_text": "qwen3_moe"}.get(d.get("model_type"), d.get("model_type"))

@@ -205,3 +205,52 @@ def test_qwen3_vl_rollout_engine_generates_like_hf():
     seqs = eng.generate([ids], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True),
                         mm_inputs=[{"pixel_values": px, "image_grid_thw": grid}])
     assert seqs[0].output == want, (seqs[0].output, want)
+
+
+def test_qwen3_vl_moe_logits_match_hf():
+    """Qwen3-VL with a mixture-of-experts language model (the 30B-A3B vision-language checkpoints)."""
+    from transformers import Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration
+    from chatlearn_b200.models.nn.model import packed_ctx
+    from chatlearn_b200.models.nn.vl_model import VLCausalLM
+    torch.manual_seed(0)
+    cfg = Qwen3VLMoeConfig(
+        text_config=dict(vocab_size=1024, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=32, max_position_embeddings=512, rope_theta=10000.0,
+                         moe_intermediate_size=48, num_experts=8, num_experts_per_tok=2, decoder_sparse_step=1, mlp_only_layers=[],
+                         norm_topk_prob=True,
+                         rope_scaling={"rope_type": "default", "mrope_section": [4, 6, 6], "mrope_interleaved": True}),
+        vision_config=dict(depth=3, hidden_size=64, intermediate_size=96, num_heads=4, patch_size=16, spatial_merge_size=2,
+                           temporal_patch_size=2, out_hidden_size=128, num_position_embeddings=64, deepstack_visual_indexes=[0, 2]),
+        image_token_id=1000, video_token_id=1001, vision_start_token_id=1002, vision_end_token_id=1003)
+    hf = Qwen3VLMoeForConditionalGeneration(cfg).eval().float()
+    for p in hf.parameters():
+        if p.dim() == 1:
+            torch.nn.init.normal_(p, mean=0.5, std=0.2)
+        elif p.dim() == 3:                       # stacked expert weights are created uninitialised
+            torch.nn.init.normal_(p, std=0.05)
+    for n, p in hf.named_parameters():
+        if n.endswith("mlp.gate.weight"):        # routers start at zero: every expert would tie
+            torch.nn.init.normal_(p, std=0.5)
+    arch = _arch(cfg)
+    assert arch.is_moe and arch.num_experts == 8 and arch.mrope_interleaved
+    sd = dict(hf.state_dict())
+    for k in [k for k in sd if k.endswith("mlp.experts.gate_up_proj") or k.endswith("mlp.experts.down_proj")]:
+        w = sd.pop(k)                            # checkpoints on disk hold one tensor per expert and projection
+        pre = k.rsplit(".", 1)[0]
+        for e in range(w.shape[0]):
+            if k.endswith("gate_up_proj"):       # [experts, 2 * width, hidden]: gate rows, then up rows
+                g, u = w[e].chunk(2, dim=0)
+                sd[f"{pre}.{e}.gate_proj.weight"], sd[f"{pre}.{e}.up_proj.weight"] = g.contiguous(), u.contiguous()
+            else:                                # [experts, hidden, width]
+                sd[f"{pre}.{e}.down_proj.weight"] = w[e].contiguous()
+    model = VLCausalLM(arch)
+    model.load_hf_state_dict(sd)
+    grid = torch.tensor([[1, 6, 8]])
+    px = torch.randn(48, model.varch.patch_dim)
+    ids = torch.tensor([3, 4, 1002] + [1000] * 12 + [1003, 20, 21, 22])
+    with torch.no_grad():
+        want = hf(input_ids=ids[None], pixel_values=px, image_grid_thw=grid, mm_token_type_ids=(ids[None] == 1000).long()).logits[0]
+        ctx, _ = packed_ctx([ids.numel()], "cpu")
+        ctx.mrope_positions = model.positions(ids, grid)
+        got = model.logits(ids, ctx, px, grid)
+    assert torch.allclose(got, want, rtol=3e-4, atol=3e-4), (got - want).abs().max()
