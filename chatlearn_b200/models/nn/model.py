@@ -530,6 +530,9 @@ class CausalLM:
         for k in list(out):
             if k.endswith(".conv1d.weight"):        # depthwise Conv1d weights are [channels, 1, taps]
                 out[k] = out[k].unsqueeze(1)
+        for k, shape in getattr(self, "hf_reshape", {}).items():
+            if k in out:                            # e.g. the vision tower's patch-embedding convolution kernel
+                out[k] = out[k].reshape(shape)
         return out
 
     @torch.no_grad()

@@ -429,6 +429,10 @@ def attach_vision_block(lm, tower, pad_to: int = 1):
     tower.trainable = True
     lm.blocks.append(blk)
     lm.block_by_name["vision"] = blk
+    # HF keeps the patch embedding as a convolution kernel [hidden, channels, frames, patch, patch]
+    a = tower.arch
+    lm.hf_reshape = {"visual.patch_embed.proj.weight": (a.hidden_size, a.in_channels, a.temporal_patch_size,
+                                                        a.patch_size, a.patch_size)}
     return blk
 
 
