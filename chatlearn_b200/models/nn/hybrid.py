@@ -129,7 +129,11 @@ def gated_delta_net(arch: ModelArch, p, x, ctx, layer: int):
         keep = (~st.fresh).to(mixed.dtype)[:, None, None]
         xp[:, :K - 1] = st.conv[layer].index_select(0, st.slots).to(mixed.dtype) * keep
     xp[seq, off + K - 1] = mixed
-    y = F.silu(F.conv1d(xp.transpose(1, 2), p["conv1d"].unsqueeze(1).to(mixed.dtype), groups=C)).transpose(1, 2)
+    if L == 1:
+        # decode: one output per channel, the taps times the last K inputs (plain statements, safe to capture)
+        y = F.silu((xp.float() * p["conv1d"].float().t().unsqueeze(0)).sum(1, keepdim=True)).to(mixed.dtype)
+    else:
+        y = F.silu(F.conv1d(xp.transpose(1, 2), p["conv1d"].unsqueeze(1).to(mixed.dtype), groups=C)).transpose(1, 2)
     if st is not None:
         idx = (lens[:, None] + torch.arange(K - 1, device=x.device)[None]).unsqueeze(-1).expand(B, K - 1, C)
         st.conv[layer].index_copy_(0, st.slots, xp.gather(1, idx).to(st.conv[layer].dtype))

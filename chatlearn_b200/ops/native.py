@@ -388,6 +388,11 @@ def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens=None, sc
     if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or \
             not C.paged_decode_supported(dk, dv, bs, nq // nkv):
         library_counts["paged_attention"] += 1
+        if (q_lens is None or q.shape[0] == seq_lens.shape[0]) and q.shape[0] > 0:
+            # decode rows: batched statements without host synchronisation, so the step can still be captured
+            from .paged_fallback import paged_decode_batched
+            return paged_decode_batched(q, k_cache, v_cache, block_tables, seq_lens,
+                                        scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]))
         return ref.paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens, scale)
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     sl = seq_lens.to(torch.int32)

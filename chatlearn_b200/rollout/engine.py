@@ -127,7 +127,7 @@ class RolloutEngine:
         esz = torch.empty((), dtype=self.model.dtype).element_size()
         per_slot = (a.linear_conv_kernel_dim - 1) * (2 * kd + vd) * esz \
             + a.linear_num_value_heads * a.linear_key_head_dim * a.linear_value_head_dim * 4
-        return n_lin * per_slot * (self.max_num_seqs + 1)
+        return n_lin * per_slot * (self.max_num_seqs + 2)
 
     def alloc_kv_cache(self):
         if self.k_cache:
@@ -167,9 +167,10 @@ class RolloutEngine:
                 kd, vd = a.linear_num_key_heads * a.linear_key_head_dim, a.linear_num_value_heads * a.linear_value_head_dim
                 self.k_cache.append(torch.empty(0, device=self.device))
                 self.v_cache.append(torch.empty(0, device=self.device))
-                self.lin_conv.append(torch.zeros(self.max_num_seqs + 1, a.linear_conv_kernel_dim - 1, 2 * kd + vd,
+                # slots 0..max_num_seqs are handed out; the last one is scratch for the padded rows of a captured step
+                self.lin_conv.append(torch.zeros(self.max_num_seqs + 2, a.linear_conv_kernel_dim - 1, 2 * kd + vd,
                                                  dtype=self.model.dtype, device=self.device))
-                self.lin_rec.append(torch.zeros(self.max_num_seqs + 1, a.linear_num_value_heads, a.linear_key_head_dim,
+                self.lin_rec.append(torch.zeros(self.max_num_seqs + 2, a.linear_num_value_heads, a.linear_key_head_dim,
                                                 a.linear_value_head_dim, dtype=torch.float32, device=self.device))
                 continue
             self.lin_conv.append(None)
@@ -196,6 +197,14 @@ class RolloutEngine:
         if self.arch.layer_types is None:
             return None
         from chatlearn_b200.models.nn.hybrid import LinearState
+        slots = self._state_slots_of(seqs)
+        fresh = [s.num_computed == 0 for s in seqs]
+        dev = self.device
+        return LinearState(self.lin_conv, self.lin_rec,
+                           xfer.to_device(torch.tensor(slots, dtype=torch.long), dev, "lin_slots"),
+                           xfer.to_device(torch.tensor(fresh, dtype=torch.bool), dev, "lin_fresh"))
+
+    def _state_slots_of(self, seqs) -> List[int]:
         live = {id(s) for s in seqs}
         slots = []
         for s in seqs:
@@ -210,11 +219,7 @@ class RolloutEngine:
                 slot = (self._free_state_slots.pop(), s)
                 self._state_slot[id(s)] = slot
             slots.append(slot[0])
-        fresh = [s.num_computed == 0 for s in seqs]
-        dev = self.device
-        return LinearState(self.lin_conv, self.lin_rec,
-                           xfer.to_device(torch.tensor(slots, dtype=torch.long), dev, "lin_slots"),
-                           xfer.to_device(torch.tensor(fresh, dtype=torch.bool), dev, "lin_fresh"))
+        return slots
 
     # ------------------------------------------------------------------ one step
     def _build_inputs(self, plan: StepPlan):
@@ -306,6 +311,10 @@ class RolloutEngine:
                             stage=torch.zeros(4, n, dtype=torch.int64, pin_memory=True),
                             bt_host=torch.zeros(n, width, dtype=torch.int32, pin_memory=True),
                             bt_len=[0] * n, bt_owner=[None] * n)
+            if self.arch.layer_types is not None:
+                # recurrent-state layers: the state slot of every row (decode rows never start fresh)
+                self._gs.update(lin_slots=z(torch.long, n), lin_fresh=z(torch.bool, n),
+                                lin_stage=torch.zeros(n, dtype=torch.int64, pin_memory=True))
         return self._gs
 
     def invalidate_graphs(self):
@@ -317,6 +326,9 @@ class RolloutEngine:
     def _decode_body(self, B: int, sp):
         gs = self._gs
         kv = KVCtx(self.k_cache, self.v_cache, gs["slots"][:B], gs["bt"][:B], gs["seq_lens"][:B], None, False)
+        if self.arch.layer_types is not None:
+            from chatlearn_b200.models.nn.hybrid import LinearState
+            kv.lin = LinearState(self.lin_conv, self.lin_rec, gs["lin_slots"][:B], gs["lin_fresh"][:B])
         ctx = FwdCtx(positions=gs["pos"][:B], cu_seqlens=None, max_seqlen=1, kv=kv, tp=self.tp, ep=self.ep, tp_symm=self._symm(), fuse_add_norm=True)
         hidden = self.model.hidden_states(gs["tokens"][:B], ctx)
         logits = self._logits(hidden)
@@ -357,6 +369,11 @@ class RolloutEngine:
                 gs["bt_host"][i, 0] = scratch_block
                 gs["bt"][i, :1].copy_(gs["bt_host"][i, :1], non_blocking=True)
                 owner[i], blen[i] = "pad", 1
+        if self.arch.layer_types is not None:
+            scratch_slot = self.max_num_seqs + 1             # padded rows update a state nobody reads
+            gs["lin_stage"][:Bg] = torch.tensor(self._state_slots_of(seqs) + [scratch_slot] * (Bg - B), dtype=torch.int64)
+            gs["lin_slots"].copy_(gs["lin_stage"], non_blocking=True)
+            xfer.h2d_bytes += gs["lin_stage"].numel() * 8
         st[:, :Bg] = torch.tensor(rows, dtype=torch.int64)
         gs["in64"].copy_(st, non_blocking=True)              # one pinned -> device copy per step
         gs["seq_lens"].copy_(gs["in64"][3])                   # int64 -> int32 on the device
@@ -367,11 +384,18 @@ class RolloutEngine:
         g = self._graphs.get(key)
         if g is None:
             # warm-up on a side stream, then capture
+            recurrent = self.arch.layer_types is not None
+            if recurrent:
+                # the warm-up run must not advance any sequence's recurrent state (the replay below does that
+                # once): every row works on the scratch slot meanwhile
+                gs["lin_slots"].fill_(self.max_num_seqs + 1)
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
                 self._decode_body(Bg, sp)
             torch.cuda.current_stream().wait_stream(side)
+            if recurrent:
+                gs["lin_slots"].copy_(gs["lin_stage"], non_blocking=True)
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 self._decode_body(Bg, sp)
@@ -382,8 +406,6 @@ class RolloutEngine:
     def _can_graph(self, plan: StepPlan) -> bool:
         if not self.use_graphs or self.device.type != "cuda" or plan.is_prefill:
             return False
-        if self.arch.layer_types is not None:
-            return False        # the recurrent-state layers run on PyTorch statements outside the captured step
         if ops.get_mode() != "native" or self.model.dtype != torch.bfloat16:
             return False        # the PyTorch statements of the ops (also taken for fp32 weights) synchronise with the host
         if any(n != 1 for n in plan.q_lens) or len(plan.seqs) > self._BUCKETS[-1]:

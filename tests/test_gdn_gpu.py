@@ -66,3 +66,20 @@ def test_qwen3_next_engine_native_matches_statements():
     # fp32 weights: only the state update differs between the two runs (kernel against statements)
     assert [o[:4] for o in outs["native"][0]] == [o[:4] for o in outs["library"][0]]
     assert float((lp_n[:, :4] - lp_r[:, :4]).abs().max()) < 1e-3
+
+
+def test_qwen3_next_decode_in_captured_steps():
+    """bf16 weights: decode steps of the hybrid model are captured in CUDA graphs (state slots are graph inputs,
+    padded rows update a scratch slot); tokens equal those of eager steps."""
+    from chatlearn_b200.models.nn import PRESETS, CausalLM
+    from chatlearn_b200.rollout.engine import RolloutEngine, SamplingParams
+    arch = PRESETS["tiny_qwen3_next"]()
+    m = CausalLM(arch, dtype=torch.bfloat16, device="cuda").init_weights(5, std=0.05)
+    prompts = [torch.randint(0, 500, (n,)).tolist() for n in (5, 23, 70)]
+    outs = {}
+    for graphs in (True, False):
+        eng = RolloutEngine(m, max_model_len=256, num_blocks=64, block_size=16, use_cuda_graphs=graphs)
+        seqs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+        outs[graphs] = [s.output for s in seqs]
+        assert bool(eng._graphs) == graphs
+    assert outs[True] == outs[False]
