@@ -51,12 +51,13 @@ class MegatronPolicyTrainer(MegatronModule):
     def _prepare(self, mb: List[Dict]):
         """Packed row of a micro-batch, this CP rank's zig-zag slice and the context."""
         cp = self.cp_size
-        batch = pack_samples(mb, seq_multiple=2 * cp if cp > 1 else 1) if mb else None
+        mult = (2 * cp if cp > 1 else 1) * (self.tp_size if self.seq_parallel else 1)    # rows split evenly over cp, then tp
+        batch = pack_samples(mb, seq_multiple=mult) if mb else None
         if batch is None:
             return None, None, None
         batch.to(self.device)
         ctx = FwdCtx(positions=batch.positions, cu_seqlens=batch.cu_seqlens, max_seqlen=batch.max_seqlen,
-                     tp=self.tp_group if self.tp_size > 1 else None, ep=self.ep)
+                     tp=self.tp_group if self.tp_size > 1 else None, ep=self.ep, seq_parallel=self.seq_parallel)
         local = None
         if cp > 1:
             plan = self.cp.plan(batch.seq_lens, self.device)
@@ -113,6 +114,10 @@ class MegatronPolicyTrainer(MegatronModule):
                 h = ops.rmsnorm(h, self.model.final_norm_weight(), self.model.arch.rms_norm_eps)
         if not self.is_last_stage:
             return h
+        if ctx.seq_parallel:
+            # the output head needs every row on every rank; its input gradient is already summed over the
+            # vocabulary shards there, so the backward of this gather just keeps this rank's rows
+            h = self.tp_group.gather_seq(h, 0)
         labels = batch.labels if local is None else batch.labels.index_select(0, local)
         w = self.model.lm_head_weight()
         if self.tp_size > 1 and w.shape[0] != self.model.arch.vocab_size:
@@ -121,7 +126,9 @@ class MegatronPolicyTrainer(MegatronModule):
         return ops.lmhead_logprob_entropy(h, w, labels)
 
     def _local_tokens(self, batch: PackedBatch, local) -> int:
-        return int(local.numel()) if local is not None else batch.num_tokens
+        """Rows of the tensors that cross a stage boundary on this rank."""
+        n = int(local.numel()) if local is not None else batch.num_tokens
+        return n // self.tp_size if self.seq_parallel else n
 
     # ------------------------------------------------------------------ scoring
     @torch.no_grad()

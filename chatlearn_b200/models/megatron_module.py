@@ -92,6 +92,8 @@ class MegatronModule(FSDPModule):
                                ep=self.ep_size, etp=self.etp_size,
                                kinds=("tp", "cp", "dp", "pp", "ep", "edp", "dp_cp", "mp"))
         self.sp = None
+        # Megatron's sequence parallelism: between the tensor-parallel layers every rank keeps 1/tp of the rows
+        self.seq_parallel = self.tp_size > 1 and bool(getattr(ma, "sequence_parallel", False))
         if self.is_member:
             g = self.mesh.groups
             self.tp_group, self.cp_group, self.pp_group = g["tp"], g["cp"], g["pp"]
@@ -161,6 +163,17 @@ class MegatronModule(FSDPModule):
         self.vision = build_vision_tower(self.arch, self.compute_dtype, self.device, getattr(self.module_args, "load", None))
         if self.vision is not None:
             assert self.cp_size == 1, "vision-language models run without context parallelism"
+            self.seq_parallel = False          # image rows are addressed in the full packed row
+        if self.seq_parallel:
+            # norms and routers see only this rank's rows: their gradients are partial sums over the group
+            for b in self.model.blocks:
+                for lf in b.leaves:
+                    if b.short(lf.name) in ("input_layernorm", "post_attention_layernorm", "norm", "router",
+                                            "shared_expert_gate"):
+                        lf.grad_sum_tp = True
+                    # experts kept whole on every tensor-parallel rank work on that rank's rows only
+                    if b.short(lf.name) in ("w13", "w2") and self.etp_size == 1 and self.ep_size == 1:
+                        lf.grad_sum_tp = True
             if self.trainable and self.is_first_stage and bool(getattr(self.module_args, "train_vision_tower", False)):
                 attach_vision_block(self.model, self.vision, pad_to=math.lcm(self.dp_group.size, self.edp_group.size))
         self.cp = ContextParallel(self.cp_group) if self.cp_size > 1 else None

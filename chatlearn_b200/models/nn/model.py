@@ -156,10 +156,16 @@ class FwdCtx:
     fuse_add_norm: bool = False            # inference: fuse residual adds with the following RMSNorm (in-place stream)
     mrope_positions: Optional[torch.Tensor] = None   # [3, T] time/row/column positions (vision-language models)
     deepstack: Any = None                  # (rows, [features per early layer]): vision taps added after layer i (Qwen3-VL)
+    seq_parallel: bool = False             # residual stream and norms hold 1/tp of the rows (Megatron sequence parallelism)
 
 
 def _tp_reduce(x, ctx):
+    """Output of a row-parallel layer: summed over the tensor-parallel group.  Under sequence parallelism
+    (Megatron's ``sequence_parallel``: the residual stream and the norms hold 1/tp of the rows) the sum is
+    reduce-scattered along the rows instead."""
     if ctx.tp is not None and ctx.tp.size > 1:
+        if ctx.seq_parallel:
+            return ctx.tp.reduce_scatter_seq(x)
         return ctx.tp.all_reduce(x)
     return x
 
@@ -168,9 +174,9 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
                     partial: bool = False):
     """``partial=True`` (tensor-parallel inference with in-kernel collectives) returns this
     rank's un-reduced output projection, written straight into symmetric staging."""
-    T = x.shape[0]
     d = arch.head_dim
     x = _tp_copy(x, ctx)
+    T = x.shape[0]                 # (under sequence parallelism the rows were gathered just now)
     tp = ctx.tp.size if ctx.tp is not None else 1
     nh_l = arch.num_attention_heads // tp
     if arch.use_mla:
@@ -255,8 +261,13 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
 
 
 def _tp_copy(x, ctx):
-    if ctx.tp is not None and ctx.tp.size > 1 and torch.is_grad_enabled():
-        return ctx.tp.copy_in(x)
+    """Input of a column-parallel layer.  Under sequence parallelism the rows are all-gathered here (the
+    gradient is reduce-scattered back); otherwise identity with an all-reduce of the gradient."""
+    if ctx.tp is not None and ctx.tp.size > 1:
+        if ctx.seq_parallel:
+            return ctx.tp.gather_sum_bwd(x)
+        if torch.is_grad_enabled():
+            return ctx.tp.copy_in(x)
     return x
 
 
@@ -281,6 +292,8 @@ def moe_block(arch: ModelArch, p, x, ctx: FwdCtx):
         # sees the same tokens, so its expert output is a partial sum; inputs and routing weights get their
         # gradients summed over the group, the output is all-reduced
         x_, w_ = _tp_copy(x, ctx), _tp_copy(w, ctx)
+        if ctx.seq_parallel and ctx.tp is not None and ctx.tp.size > 1:
+            idx = ctx.tp.all_gather_cat(idx, 0)           # the rows were gathered: so are their expert choices
         if ctx.ep is not None and ctx.ep.size > 1:
             y = ctx.ep.experts(x_, p["w13"], p["w2"], w_, idx, arch.num_experts)
         else:
@@ -288,7 +301,7 @@ def moe_block(arch: ModelArch, p, x, ctx: FwdCtx):
         y = _tp_reduce(y, ctx)
     elif ctx.ep is not None and ctx.ep.size > 1:
         tp = ctx.tp
-        if tp is not None and tp.size > 1:
+        if tp is not None and tp.size > 1 and not ctx.seq_parallel:      # (sequence-parallel rows are split already)
             # the ranks of a TP group hold the same tokens: each dispatches its own
             # 1/tp slice, so an expert sees every token once, and the outputs are
             # all-gathered back (gradient: this rank's slice)
@@ -393,7 +406,7 @@ def embed(p, tokens, ctx: FwdCtx):
         ok = (local >= 0) & (local < Vl)
         e = torch.nn.functional.embedding(local.clamp(0, Vl - 1), w)
         e = e * ok[:, None].to(e.dtype)
-        return ctx.tp.all_reduce(e)
+        return _tp_reduce(e, ctx)
     return torch.nn.functional.embedding(tokens, w)
 
 

@@ -143,6 +143,11 @@ class Group:
         (used where every rank consumes the gathered tensor differently, e.g. CP K/V)."""
         return _GatherSumBwd.apply(x, self) if self.size > 1 else x
 
+    def reduce_scatter_seq(self, x):
+        """Sum over the group, keeping this rank's slice of dim 0; backward all-gathers the gradient
+        (output of row-parallel layers under Megatron-style sequence parallelism)."""
+        return _ReduceScatterSeq.apply(x, self) if self.size > 1 else x
+
     def all_to_all(self, x, out_splits=None, in_splits=None):
         return _AllToAll.apply(x, self, out_splits, in_splits) if self.size > 1 else x
 
@@ -191,6 +196,20 @@ class _GatherSumBwd(torch.autograd.Function):
         out = torch.empty(ctx.shape, dtype=g.dtype, device=g.device)
         ctx.group.reduce_scatter_flat(out.view(-1), g.contiguous().view(-1))
         return out, None
+
+
+class _ReduceScatterSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        assert x.shape[0] % group.size == 0, f"{x.shape[0]} rows cannot be split over {group.size} ranks"
+        out = torch.empty((x.shape[0] // group.size,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        group.reduce_scatter_flat(out.view(-1), x.contiguous().view(-1))
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.group.all_gather_cat(g.contiguous(), 0), None
 
 
 class _AllToAll(torch.autograd.Function):

@@ -42,7 +42,8 @@ cfg = {
     "models": {
         "policy_trainer": {"num_gpu": W, "trainable": True, "load": hf_dir, "tensor_model_parallel_size": tp,
                            "pipeline_model_parallel_size": pp, "context_parallel_size": cp,
-                           "expert_model_parallel_size": ep, "expert_tensor_parallel_size": etp, "packing": os.environ.get("PACKING", "1") == "1",
+                           "expert_model_parallel_size": ep, "expert_tensor_parallel_size": etp,
+                           "sequence_parallel": os.environ.get("SEQ_PAR", "1") == "1", "packing": os.environ.get("PACKING", "1") == "1",
                            "max_token_in_packing": 96, "generation_batch_size": 4, "kl_coef": 0.01,
                            "entropy_coef": 0.001, "optimizer": {"lr": 1e-3, "clip_grad": 1.0},
                            "use_group_sequence_policy": os.environ.get("GSPO", "0") == "1",

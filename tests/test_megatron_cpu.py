@@ -37,7 +37,10 @@ def _compare(a, b, tol=5e-4):
 
 
 @pytest.mark.parametrize("name,world,env", [
-    ("tp2", 2, dict(TP=2)),
+    ("tp2", 2, dict(TP=2)),                      # rows split over the tensor-parallel ranks between the layers
+    ("tp2_no_seq_par", 2, dict(TP=2, SEQ_PAR=0)),
+    ("tp2pp2", 4, dict(TP=2, PP=2)),
+    ("tp2cp2", 4, dict(TP=2, CP=2)),
     ("pp2", 2, dict(PP=2)),
     ("cp2", 2, dict(CP=2)),
     ("dp2", 2, dict()),
