@@ -164,6 +164,8 @@ class MegatronModule(FSDPModule):
         if self.vision is not None:
             assert self.cp_size == 1, "vision-language models run without context parallelism"
             self.seq_parallel = False          # image rows are addressed in the full packed row
+            if self.trainable and self.is_first_stage and bool(getattr(self.module_args, "train_vision_tower", False)):
+                attach_vision_block(self.model, self.vision, pad_to=math.lcm(self.dp_group.size, self.edp_group.size))
         if self.seq_parallel:
             # norms and routers see only this rank's rows: their gradients are partial sums over the group
             for b in self.model.blocks:
@@ -174,8 +176,6 @@ class MegatronModule(FSDPModule):
                     # experts kept whole on every tensor-parallel rank work on that rank's rows only
                     if b.short(lf.name) in ("w13", "w2") and self.etp_size == 1 and self.ep_size == 1:
                         lf.grad_sum_tp = True
-            if self.trainable and self.is_first_stage and bool(getattr(self.module_args, "train_vision_tower", False)):
-                attach_vision_block(self.model, self.vision, pad_to=math.lcm(self.dp_group.size, self.edp_group.size))
         self.cp = ContextParallel(self.cp_group) if self.cp_size > 1 else None
         if self.cp is not None:
             from chatlearn_b200.parallel import symm_collectives
