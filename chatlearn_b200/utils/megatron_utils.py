@@ -3,8 +3,8 @@
 Parity: chatlearn/utils/megatron_utils.py:20-164 (``update_cfg``): for every
 Megatron-backend role the architecture block ``megatron_model_cfg`` is filled from
 the HuggingFace config of ``load`` (or the inline ``model_arch``): Qwen2.5/Qwen3
-dense, Qwen3-MoE, DeepSeek-V3 / Moonlight (MLA, sigmoid router, group top-k,
-shared experts).  The parallel layers themselves read ``ModelArch``; this keeps
+dense, Qwen2.5-VL (multimodal rotary sections), Qwen3-MoE, DeepSeek-V3 / Moonlight (MLA, sigmoid router,
+group top-k, shared experts, YaRN factor), Qwen3-Next (hybrid layer pattern, partial rotary).  The parallel layers themselves read ``ModelArch``; this keeps
 the reference's config surface populated for users and tools that inspect it.
 """
 from chatlearn_b200.models.nn.arch import ModelArch, resolve_arch
@@ -50,6 +50,18 @@ def arch_to_megatron_cfg(arch: ModelArch, mc):
         mc.qk_head_dim, mc.qk_pos_emb_head_dim = arch.qk_nope_head_dim, arch.qk_rope_head_dim
         mc.v_head_dim = arch.v_head_dim
         mc.kv_channels = arch.qk_nope_head_dim + arch.qk_rope_head_dim
+        if arch.rope_scaling:                        # YaRN long-context rescaling (DeepSeek-V3)
+            mc.rotary_scaling_factor = float(arch.rope_scaling.get("factor", 1.0))
+    if arch.mrope_section:                           # vision-language models: time / row / column rotary sections
+        mc.mrope_section = list(arch.mrope_section)
+        mc.position_embedding_type = "mrope"
+    if arch.layer_types is not None:                 # Qwen3-Next: "M-" = gated delta-net + MLP, "*-" = attention + MLP
+        mc.hybrid_override_pattern = "".join("M-" if arch.layer_is_linear(l) else "*-"
+                                             for l in range(arch.num_hidden_layers))
+        mc.is_hybrid_model = True
+        mc.rotary_percent = float(arch.partial_rotary_factor)
+        if arch.shared_expert_intermediate_size:
+            mc.moe_shared_expert_intermediate_size = arch.shared_expert_intermediate_size
     return mc
 
 

@@ -50,3 +50,26 @@ def test_example_scripts_name_existing_templates(name):
     text = open(os.path.join(ROOT, "examples", name)).read()
     tpl = [w for w in text.split() if w.startswith("template/")]
     assert tpl and all(os.path.exists(os.path.join(ROOT, t)) for t in tpl)
+
+
+def test_megatron_architecture_block_is_filled_from_the_model_description():
+    """Hybrid layer pattern, partial rotary, multimodal rotary sections and the YaRN factor reach the
+    Megatron-style architecture block that tools and users inspect."""
+    import dataclasses
+    from chatlearn_b200.configs.megatron_config import MegatronModelArchitectureConfig as C
+    from chatlearn_b200.models.nn import PRESETS
+    from chatlearn_b200.utils.megatron_utils import arch_to_megatron_cfg
+
+    def blank():
+        req = {f.name: 1 for f in dataclasses.fields(C)
+               if f.default is dataclasses.MISSING and f.default_factory is dataclasses.MISSING}
+        return C(**req)
+    nxt = arch_to_megatron_cfg(PRESETS["tiny_qwen3_next"](), blank())
+    assert nxt.hybrid_override_pattern == "M-M-M-*-" and nxt.is_hybrid_model and nxt.rotary_percent == 0.25
+    assert nxt.moe_shared_expert_intermediate_size == 64 and nxt.num_experts == 8
+    vl = arch_to_megatron_cfg(PRESETS["tiny_qwen2_5_vl"](), blank())
+    assert vl.position_embedding_type == "mrope" and vl.mrope_section == [4, 6, 6]
+    ds = PRESETS["deepseek_v3_671b"]()
+    ds.rope_scaling = {"type": "yarn", "factor": 40}
+    mc = arch_to_megatron_cfg(ds, blank())
+    assert mc.multi_latent_attention and mc.rotary_scaling_factor == 40.0 and mc.moe_router_num_groups == 8
