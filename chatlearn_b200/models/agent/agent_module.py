@@ -44,6 +44,9 @@ class AgentModule(RolloutModule):
         g = _graph_registry[agent_name](agent_name=agent_name, cfg=cfg, llm=self, tokenizer=self.tokenizer,
                                         processor=getattr(self, "processor", None),
                                         model_type=getattr(self.runtime_args, "model_type", "llm"))
+        if self.engine.vision is not None and getattr(g, "chatmodel", None) is not None:
+            g.chatmodel.vision = {"image_token_id": self.arch.image_token_id,
+                                  "merge_size": self.engine.vision.arch.spatial_merge_size}
         self.agent_factory[agent_name] = g
         return g
 
@@ -58,7 +61,8 @@ class AgentModule(RolloutModule):
             mx = int(r.sampling_params.get("max_new_tokens", sp.max_tokens))
             budgets.append(max(0, min(mx, ma.seq_length - len(r.token_ids))))
             sps.append(sp)
-        seqs = self.engine.generate([r.token_ids for r in reqs], sps, max_new_tokens=budgets)
+        mm = [r.mm for r in reqs] if self.engine.vision is not None and any(r.mm is not None for r in reqs) else None
+        seqs = self.engine.generate([r.token_ids for r in reqs], sps, max_new_tokens=budgets, mm_inputs=mm)
         return [LLMResponse(list(q.output), list(q.logprobs), q.finish_reason) for q in seqs]
 
     def _sync_objects(self, objs):

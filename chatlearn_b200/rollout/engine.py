@@ -526,6 +526,7 @@ class RolloutEngine:
         s.mm = {"embeds": embeds, "pos3": pos3, "ordinal": {j: o for o, j in enumerate(where)},
                 "deepstack": [t.to(self.model.dtype) for t in taps]}
         s.rope_delta = int(delta)
+        self._image_rows_seen = getattr(self, "_image_rows_seen", 0) + len(where)      # statistics
 
     def generate(self, prompts: List[List[int]], sampling: Any, eos_id: Optional[int] = None,
                  max_new_tokens: Optional[List[int]] = None, mm_inputs: Optional[List[Optional[Dict]]] = None) -> List[Sequence]:

@@ -23,6 +23,12 @@ if int(os.environ["RANK"]) == 0:
         ids = [5 + i, 6, 1002, 1000, 1003] + rng.integers(0, 900, 6).tolist()      # one placeholder per image
         rows.append({"data_source": "synthetic:mod7", "input_ids": ids, "images": [buf.getvalue().hex()],
                      "reward_model": {"ground_truth": ""}})
+    if os.environ.get("AGENT", "0") == "1":
+        # agent task: raw chat messages, the image rides on the record and is fed to the engine by the chat model
+        for i, r in enumerate(rows):
+            r.pop("input_ids")
+            r.update(agent_name="geo3k_agent", prompt=[{"role": "user", "content": f"what is the area of figure {i}?"}],
+                     reward_model={"ground_truth": str(i)})
     write_jsonl(rows, data + ".tmp"); os.replace(data + ".tmp", data)
 while not os.path.exists(data): time.sleep(0.05)
 arch = {"preset": "tiny_qwen2_5_vl"}
@@ -42,6 +48,10 @@ cfg = {
     "reward": {"num_cpu": 2},
   }}
 train_tower = os.environ.get("TRAIN_TOWER", "0") == "1"
+if os.environ.get("AGENT", "0") == "1":
+    cfg["runtime_args"].update(task_type="agent", use_rollout_manager=True, raw_chat=True, data_rerank=False)
+    cfg["models"]["rollout_manager"] = {"num_cpu": 1, "max_concurrent_per_engine": 8}
+    cfg["models"]["policy"]["tokenizer"] = "byte"
 if os.environ.get("BACKEND", "fsdp") == "megatron":
     # Megatron-style trainer: tensor or pipeline parallel over the two ranks
     par = {"tensor_model_parallel_size": int(os.environ.get("TP", "1")), "pipeline_model_parallel_size": int(os.environ.get("PP", "1"))}
@@ -60,14 +70,16 @@ stats = algo.run()
 eng = algo.engine
 tr = eng.named_models["policy_trainer"]
 pol = eng.named_models["policy"]
-sample_tokens = [len(d) for d in pol._all_datasets[0].data and [s["input_ids"] for s in pol._all_datasets[0].data]]
+ds = getattr(pol, "_all_datasets", None)
+sample_tokens = [len(s["input_ids"]) for s in ds[0].data if "input_ids" in s] if ds else []
+img_rows = getattr(pol.engine, "_image_rows_seen", 0)
 # the rollout tower against the initial one and against the trainer's (its fp32 master weights after the last step
 # are what the last weight sync delivered when another episode follows; compare with the bf16/fp32 working copy)
 name = "visual.blocks.0.attn.qkv.weight"
 moved = float((pol.engine.vision.params[name].float() - w0[name].float()).abs().max())
 print("RESULT " + json.dumps({"rank": int(os.environ["RANK"]), "episodes": len(stats), "train_iters": tr._train_iteration,
       "has_tower": tr.vision is not None and pol.engine.vision is not None, "prompt_lens": sample_tokens[:3],
-      "tower_moved": moved, "tower_block": "vision" in tr.model.block_by_name and "vision" in pol.model.block_by_name}))
+      "image_rows": img_rows, "tower_moved": moved, "tower_block": "vision" in tr.model.block_by_name and "vision" in pol.model.block_by_name}))
 '''
 
 
@@ -102,3 +114,14 @@ def test_vision_language_grpo_megatron_backend(tmp_path):
         for r in res:
             assert r["episodes"] == 2 and r["train_iters"] == 2 and r["has_tower"], (name, r)
             assert (r["tower_moved"] > 0) == ("TRAIN_TOWER" in env), (name, r)
+
+
+def test_vision_language_agent_task(tmp_path):
+    """Agent trajectories of a vision-language model: the chat model expands the image placeholders and hands the
+    pixels to the engine with every turn; training then sees the same rows."""
+    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "AGENT": "1"})
+    res = [json.loads(line[7:]) for o in outs for line in o.splitlines() if line.startswith("RESULT ")]
+    assert len(res) == 2
+    for r in res:
+        assert r["episodes"] == 2 and r["train_iters"] == 2 and r["has_tower"]
+        assert r["image_rows"] > 0                            # the engine embedded image patches during generation
