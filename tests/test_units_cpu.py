@@ -281,3 +281,44 @@ def test_planner_gathers_expert_tensor_parallel_slices():
         want.load_hf_state_dict(hf)
         for a, b in zip(m.blocks, want.blocks):
             assert torch.equal(a.flat, b.flat), (e, a.name)
+
+
+def test_batched_paged_decode_matches_the_per_sequence_statements():
+    """The host-synchronisation-free decode attention (used for head sizes without a kernel instance, inside
+    captured steps) against the per-sequence reference, grouped-query heads and ragged lengths."""
+    from chatlearn_b200.ops import reference as ref
+    from chatlearn_b200.ops.paged_fallback import paged_decode_batched
+    torch.manual_seed(0)
+    nb, bs, nkv, d, nq = 24, 8, 2, 48, 8
+    kc, vc = torch.randn(nb, bs, nkv, d), torch.randn(nb, bs, nkv, d)
+    bt = torch.tensor([[3, 5, 0, 0], [1, 2, 4, 7], [9, 0, 0, 0], [11, 12, 13, 0]], dtype=torch.int32)
+    sl = torch.tensor([11, 32, 1, 17], dtype=torch.int32)
+    q = torch.randn(4, nq, d)
+    want = ref.paged_attention(q, kc, vc, bt, sl, None, 0.2)
+    got = paged_decode_batched(q, kc, vc, bt, sl, 0.2)
+    assert torch.allclose(got, want, atol=1e-5, rtol=1e-5)
+
+
+def test_latent_attention_matches_expanded_heads():
+    """Latent-space attention over compressed rows equals ordinary attention over the per-head keys and values
+    obtained by up-projecting those rows (decode rows and a multi-token tail)."""
+    from chatlearn_b200.models.nn.mla import latent_paged_attention
+    from chatlearn_b200.ops import reference as ref
+    torch.manual_seed(1)
+    nb, bs, lora, rp, nh, nope, dv = 12, 4, 16, 8, 3, 10, 6
+    cache = torch.randn(nb, bs, 1, lora + rp)
+    w_uk, w_uv = torch.randn(nh, nope, lora), torch.randn(nh, dv, lora)
+    bt = torch.tensor([[2, 4, 6], [1, 3, 0]], dtype=torch.int32)
+    sl = torch.tensor([10, 5], dtype=torch.int32)
+    # expanded cache: k = [W_uk c | rope part], v = W_uv c for every head
+    c, kr = cache[..., 0, :lora], cache[..., 0, lora:]
+    k_full = torch.cat([torch.einsum("hnc,bsc->bshn", w_uk, c), kr[:, :, None].expand(nb, bs, nh, rp)], -1)
+    v_full = torch.einsum("hvc,bsc->bshv", w_uv, c)
+    for q_lens in (None, torch.tensor([3, 2], dtype=torch.int32)):
+        T = 2 if q_lens is None else int(q_lens.sum())
+        q_nope, q_rope = torch.randn(T, nh, nope), torch.randn(T, nh, rp)
+        want = ref.paged_attention(torch.cat([q_nope, q_rope], -1), k_full, v_full, bt, sl, q_lens, 0.3)
+        q_lat = torch.cat([torch.einsum("thn,hnc->thc", q_nope, w_uk), q_rope], -1)
+        o_lat = latent_paged_attention(q_lat, cache, lora, bt, sl, q_lens, 1 if q_lens is None else 3, 0.3)
+        got = torch.einsum("thc,hvc->thv", o_lat, w_uv)
+        assert torch.allclose(got, want, atol=1e-4, rtol=1e-4), float((got - want).abs().max())
