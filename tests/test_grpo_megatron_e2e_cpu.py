@@ -84,3 +84,10 @@ def test_grpo_mla_moe_cp2_trainer(tmp_path):
     env = {"OUT_DIR": str(tmp_path), "PRESET": "tiny_mla_moe", "TP": "1", "CP": "2"}
     res = _res(run_ranks(SCRIPT, 2, env=env)[0])
     assert len(res) == 2 and all(r["episodes"] == 2 and r["maxdiff"] == 0.0 for r in res)
+
+
+def test_grpo_qwen3_next_pp2_trainer(tmp_path):
+    """Gated delta-net hybrid under the Megatron-style trainer: two pipeline stages (two layers each); the
+    rollout weights equal the trainer's after the last sync."""
+    res = _res(run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "TP": "1", "PP": "2", "PRESET": "tiny_qwen3_next"})[0])
+    assert len(res) == 2 and all(r["episodes"] == 2 and r["maxdiff"] == 0.0 for r in res)
