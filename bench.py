@@ -23,6 +23,7 @@ import sys
 import tempfile
 import time
 
+T_START = time.time()
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
@@ -41,6 +42,10 @@ def parse():
     p.add_argument("--pack-tokens", type=int, default=16384)
     p.add_argument("--gemm", default=None, choices=[None, "tcgen05", "cublas"])
     p.add_argument("--no-offload", action="store_true")
+    p.add_argument("--time-budget", type=float, default=float(os.environ.get("CLB200_BENCH_BUDGET", "740")),
+                   help="wall-clock seconds for the whole process (set-up included).  When the requested "
+                        "warm-up + steps would not fit, warm-up is cut to no fewer than 3 episodes and the "
+                        "timed loop stops early; the JSON line reports the steps actually timed.  0 = no limit")
     return p.parse_args()
 
 
@@ -107,6 +112,22 @@ class ClockSampler:
             out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons),
                        samples=len(sm))
         return out
+
+
+def vs_baseline(n_gpu, value, args):
+    """value / the same-box library-class baseline of this configuration at this GPU count: this framework
+    with torch matmul, flash-attn and NCCL statements in place of its kernels (``--impl library``), recorded in
+    ``baseline/library_baseline.json``.  The reference publishes no GRPO throughput and cannot run here, so
+    this is the number there is to divide by; None where no record exists for the configuration."""
+    try:
+        rec = json.load(open(os.path.join(ROOT, "baseline", "library_baseline.json")))
+        r = rec["runs"].get(str(n_gpu))
+        same = rec["config"] == {"model": args.model, "prompts_per_gpu": args.prompts_per_gpu,
+                                 "samples_per_prompt": args.samples_per_prompt, "prompt_len": list(args.prompt_len),
+                                 "max_response": args.max_response, "pack_tokens": args.pack_tokens}
+        return round(value / r["value"], 4) if (r and same and args.impl == "native") else None
+    except (OSError, KeyError, ValueError, ZeroDivisionError):
+        return None
 
 
 def build_config(args, out_dir, data_path, n_gpu):
@@ -208,8 +229,29 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    multi = dist.is_initialized() and dist.get_world_size() > 1
+
+    def fits(n_more: int, step_s: float) -> bool:
+        """Do ``n_more`` further episodes of ``step_s`` seconds fit in the time budget?  Every rank must
+        take the same decision (an episode is collective): the slowest rank's clock decides."""
+        if args.time_budget <= 0:
+            return True
+        left = args.time_budget - (time.time() - T_START) - 15.0 - 1.1 * n_more * step_s
+        if multi:
+            t = torch.tensor([left], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            left = float(t.item())
+        return left >= 0.0
+
+    # warm-up: as many as requested while the rest of the run still fits; never fewer than 3 unless fewer were asked for
+    done_warm, last = 0, 0.0
     for ep in range(args.warmup):
+        if ep >= min(3, args.warmup) and not fits(args.warmup - ep + min(args.steps, 2), last):
+            break
+        t_ep = time.time()
         engine.run_episode(ep)
+        last = time.time() - t_ep
+        done_warm += 1
     barrier()
     sampler = ClockSampler(rank == 0)
     xfer.reset()
@@ -218,8 +260,13 @@ def main():
     t0 = time.perf_counter()
     ev0.record()
     summaries = []
-    for ep in range(args.warmup, total_steps):
-        summaries.append(engine.run_episode(ep))
+    for i in range(args.steps):
+        if i >= 1 and not fits(1, last):
+            break
+        t_ep = time.time()
+        summaries.append(engine.run_episode(done_warm + i))
+        last = time.time() - t_ep
+    done_steps = len(summaries)
     ev1.record()
     barrier()
     wall = time.perf_counter() - t0
@@ -234,7 +281,7 @@ def main():
     dev_ms, wall_ms = t.tolist()
     launches, h2d, d2h = cnt.tolist()
     if rank == 0:
-        K = args.steps
+        K = done_steps
         samples = cfg.runtime_args.sample_per_episode
         ms_per_step = dev_ms / K
         value = samples / (ms_per_step / 1e3)
@@ -244,14 +291,16 @@ def main():
         sync_ms = [g.last_ms for g in engine.model_manager.parameter_sync_groups.values()]
         line = {
             "metric": "GRPO samples/sec (rollout+sync+train step)", "value": round(value, 4), "unit": "samples/s",
-            "n_gpus": world, "steps": K, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 2),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "n_gpus": world, "steps": K, "warmup": done_warm, "steps_requested": args.steps,
+            "warmup_requested": args.warmup, "time_budget_s": args.time_budget, "ms_per_step": round(ms_per_step, 2),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": vs_baseline(world, value, args), "dtype": "bf16", "data": "synthetic",
             "impl": args.impl,
             "config": {"model": args.model, "global_batch": samples, "seq_len": seq,
                        "parallelism": f"trainer zero-dp{world} + rollout tp{2 if world >= 2 else 1}x{max(world // 2, 1) if world >= 2 else 1}",
                        "prompts": samples // args.samples_per_prompt, "samples_per_prompt": args.samples_per_prompt,
                        "prompt_len": args.prompt_len, "max_response": args.max_response,
                        "pack_tokens": args.pack_tokens, "mini_batches_per_step": 2,
+                       "ignore_eos": True, "response_len": "every response runs to max_response (random weights)",
                        "l2_policy": "inputs larger than L2 (16 GB of weights + KV streamed every step)",
                        "gemm": __import__("chatlearn_b200.ops.native", fromlist=["x"]).get_gemm_impl() if args.impl == "native" else "cublas"},
             "step_time_s": round(ms_per_step / 1e3, 3),

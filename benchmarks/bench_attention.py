@@ -1,6 +1,6 @@
 """Packed causal attention forward: this package's kernel next to the flash-attn library.
 
-    python -m chatlearn_b200.ops.bench_attention
+    python -m benchmarks.bench_attention
 
 Three workloads (6 x 2730, 32 x 512, 2 x 8192 tokens; 32 query / 8 KV heads, head dim 128), 3 warm-up and
 10 timed calls each, CUDA events; prints milliseconds and TFLOP/s of causal work per implementation.

@@ -1,6 +1,6 @@
 """Rollout-engine micro-benchmark: decode step time and its kernel breakdown.
 
-    python -m chatlearn_b200.rollout.bench_decode --model qwen3_8b --batch 128 --context 1024 --steps 32
+    python -m benchmarks.bench_decode --model qwen3_8b --batch 128 --context 1024 --steps 32
 
 Builds a random-init model, prefills ``batch`` sequences of ``context`` tokens and
 times decode steps (CUDA-graph replay and eager).  ``--profile`` prints the

@@ -1,6 +1,6 @@
 """Gated delta-net decode kernel on Qwen3-Next-80B-A3B shapes against the same update on PyTorch statements.
 
-    python -m chatlearn_b200.ops.bench_gdn
+    python -m benchmarks.bench_gdn
 
 32 value heads over 16 key heads, 128 x 128 state per head (fp32), 64 / 128 / 256 sequences.  The state of one
 layer (64 KB per head and sequence) is read and written once per token, so the roofline is twice its size over

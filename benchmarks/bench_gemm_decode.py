@@ -1,6 +1,6 @@
 """tcgen05 GEMM on decode shapes: fixed tile widths against the automatic plan.
 
-    python -m chatlearn_b200.ops.bench_gemm_decode
+    python -m benchmarks.bench_gemm_decode
 
 Qwen3-8B layer shapes at tensor-parallel size 1 and 2, 128 and 256 rows.  Every GEMM is timed inside a
 CUDA graph that walks enough weight copies to exceed L2 (5 replays, CUDA events); prints microseconds per

@@ -1,6 +1,6 @@
 """Per-kernel micro-benchmarks with roofline fractions.
 
-    python -m chatlearn_b200.ops.bench_ops [--only gemm,decode,...] [--json out.json]
+    python -m benchmarks.bench_ops [--only gemm,decode,...] [--json out.json]
 
 Each kernel is timed with CUDA events on the launching stream after warm-up;
 between timed iterations a buffer larger than L2 is written so operands start
@@ -17,7 +17,7 @@ import torch
 
 
 def peaks():
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     p = os.path.join(root, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))

@@ -1,6 +1,6 @@
 """Small, self-ending workloads for profiler captures of single kernels.
 
-    python -m chatlearn_b200.ops.profile_case --kernel gemm|gemm_decode|decode|rmsnorm|swiglu|logits|adamw|sample|attn_fwd|grouped_gemm|moe_router
+    python -m benchmarks.profile_case --kernel gemm|gemm_decode|decode|rmsnorm|swiglu|logits|adamw|sample|attn_fwd|grouped_gemm|moe_router
 
 Each case allocates a few hundred MB (operands larger than the 126 MB L2 so DRAM
 figures mean something), runs 3 warm-up launches and 3 measured launches of ONE

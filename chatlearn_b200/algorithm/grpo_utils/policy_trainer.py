@@ -140,7 +140,13 @@ class PolicyTrainer(FSDPModule):
             self.role_group.all_reduce_(n_tok)
             if self.sp is not None:
                 n_tok /= self.sp.size
-        inv_norm = 1.0 / max(float(n_tok.item()), 1.0)
+        n_global = float(n_tok.item())
+        if n_global <= 0.0:
+            # nothing to learn from on any rank (all ranks agree: the count was summed over the group):
+            # no optimizer step, so AdamW's step count and weight decay do not advance on a zero gradient
+            self._logger.warning("train_step: empty mini-batch on every rank, optimizer step skipped")
+            return
+        inv_norm = 1.0 / max(n_global, 1.0)
         st.zero_grad()
         stats = torch.zeros(6, dtype=torch.float32, device=self.device)
         pad = self.sp.size if self.sp is not None else 1

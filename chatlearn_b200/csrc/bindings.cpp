@@ -85,9 +85,13 @@ at::Tensor symm_ar_residual_rmsnorm(const std::vector<int64_t>& part_ptrs, const
 at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32);
 void gemm_bf16_nt_out(const at::Tensor& a, const at::Tensor& b, at::Tensor out);
 void gemm_set_tile_n(int64_t bn);
+at::Tensor gemm_bf16_nn(const at::Tensor& a, const at::Tensor& b, bool out_fp32);
+at::Tensor gemm_bf16_tn(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& out, bool accumulate,
+                        bool out_fp32);
 void gemm_bf16_nt_push(const at::Tensor& a, const at::Tensor& b, at::Tensor out, const std::vector<int64_t>& peer_out);
 int64_t gemm_last_status();
 void gemm_set_splitk(bool on);
+const char* clb200_source_hash();
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
@@ -138,7 +142,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16_nt", &gemm_bf16_nt);
   m.def("gemm_bf16_nt_out", &gemm_bf16_nt_out);
   m.def("gemm_set_tile_n", &gemm_set_tile_n);
+  m.def("gemm_bf16_nn", &gemm_bf16_nn);
+  m.def("gemm_bf16_tn", &gemm_bf16_tn);
   m.def("gemm_bf16_nt_push", &gemm_bf16_nt_push);
   m.def("gemm_last_status", &gemm_last_status);
   m.def("gemm_set_splitk", &gemm_set_splitk);
+  m.def("source_hash", []() { return std::string(clb200_source_hash()); });
 }

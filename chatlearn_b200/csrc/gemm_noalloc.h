@@ -38,7 +38,8 @@ extern "C" {
 // * The FIRST call on each device performs a one-time set-up with that device
 //   current (it resolves the device address of the scratch array and raises the
 //   kernel's dynamic shared-memory limit).  Make that first call before any stream
-//   capture begins.
+//   capture begins.  Host threads that make their first call at the same time are
+//   safe: the set-up runs once per device and the others wait for it.
 // * All calls share one scratch array per device.  Its contents are overwritten by
 //   every call (each k-slice rewrites its whole plane, so nothing needs clearing),
 //   which means two calls that overlap on the GPU - different streams, or different
@@ -47,6 +48,15 @@ int clb200_gemm_bf16_nt_noalloc(const void* a, const void* b, void* c, int M, in
                                 int out_fp32, void* stream);
 
 const char* clb200_gemm_noalloc_last_error(void);
+
+// A return value of 0 above means "launched".  The kernel itself never spins without a
+// limit: if one of its internal waits runs out (about two seconds) it records a code,
+// leaves the output unfinished and returns.  This function reads that code for the
+// current device and clears it: 0 = every GEMM since the last read completed, 1 / 2 / 3 =
+// the load, tensor-core or store stage gave up, -1 = the code could not be read.  It
+// synchronises the device, so call it after the work you care about, not inside a
+// latency-critical loop.  The code is shared with the regular entry point.
+int clb200_gemm_noalloc_device_status(void);
 
 #ifdef __cplusplus
 }

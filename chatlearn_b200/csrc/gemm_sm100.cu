@@ -1,6 +1,13 @@
-// bf16 GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * B[N,K]^T
-// (both operands K-major, i.e. y = x W^T of a linear layer), fp32 accumulation in
-// tensor memory.
+// bf16 GEMM on the 5th-generation tensor cores, fp32 accumulation in tensor memory.
+// Three operand layouts, selected per instantiation (AMN / BMN = the operand's M or N
+// index is the contiguous one in memory instead of K):
+//   NT  C[M,N] = A[M,K] * B[N,K]^T      y  = x W^T     forward of a linear layer
+//   NN  C[M,N] = A[M,K] * B[K,N]        dx = dy W      input gradient
+//   TN  C[M,N] = A[K,M]^T * B[K,N]      dW = dy^T x    weight gradient, optionally
+//                                                      accumulated into an fp32 C (beta = 1)
+// An MN-major operand is fetched as 64-element-wide TMA boxes (64 MN x 64 K, 128-byte
+// swizzle) and described to the tensor core with an MN-major shared-memory descriptor, so
+// no operand is ever transposed in memory.
 //
 // Persistent, warp-specialised kernel, one CTA per SM:
 //   warp 0      TMA producer: streams 128x64 (A) and 256x64 (B) bf16 tiles into a
@@ -102,6 +109,23 @@ __device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&
   }
 }
 
+// C += r for an fp32 output row segment (weight-gradient accumulation across micro-batches).
+__device__ __forceinline__ void add_row32(float* dst, const uint32_t (&r)[32], int ncols) {
+  if (ncols >= 32) {
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      float4 c = *reinterpret_cast<const float4*>(dst + v * 4);
+      c.x += __uint_as_float(r[v * 4]); c.y += __uint_as_float(r[v * 4 + 1]);
+      c.z += __uint_as_float(r[v * 4 + 2]); c.w += __uint_as_float(r[v * 4 + 3]);
+      *reinterpret_cast<float4*>(dst + v * 4) = c;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) dst[j] += __uint_as_float(r[j]);
+  }
+}
+
 // Grouped mode (mixture-of-experts): A holds the rows of all groups back to back, B the
 // groups' [N, K] matrices stacked along rows.  `table[i] = {first row, end row, first B
 // row of the group, -}` lists the row tiles (built on the device from the group offsets,
@@ -115,6 +139,7 @@ struct GroupArgs {
   // included) instead of C
   void* peer_out[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int n_peer = 0;
+  int accumulate = 0;       // fp32 output only: C += A*B instead of C = A*B
 };
 
 // Origin of a work tile: (first A/C row, first column, first B row of the group, end row).
@@ -130,7 +155,7 @@ __device__ __forceinline__ void unit_origin(const GroupArgs& grp, int tile, int 
   }
 }
 
-template <typename OutT, int BN_ = 256>
+template <typename OutT, int BN_ = 256, int AMN = 0, int BMN = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     OutT* __restrict__ C, float* __restrict__ ws, int M, int N, int K, int ldc, int splits,
@@ -182,8 +207,20 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int k = k_begin; k < k_end; ++k) {
           if (!mbar_wait(&sm->empty[stage], phase ^ 1)) { ok = false; break; }
           mbar_expect_tx(&sm->full[stage], kStageBytesA + kStageBytesB);
-          tma_load_2d(sm->a[stage], &tmA, &sm->full[stage], k * BK, m0);
-          tma_load_2d(sm->b[stage], &tmB, &sm->full[stage], k * BK, b0 + n0);
+          if constexpr (AMN == 0) {
+            tma_load_2d(sm->a[stage], &tmA, &sm->full[stage], k * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)      // boxes of 64 M-columns x BK K-rows
+              tma_load_2d(sm->a[stage] + j * (BK * 128), &tmA, &sm->full[stage], m0 + j * 64, k * BK);
+          }
+          if constexpr (BMN == 0) {
+            tma_load_2d(sm->b[stage], &tmB, &sm->full[stage], k * BK, b0 + n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)      // boxes of 64 N-columns x BK K-rows (b0: first K-row of the group)
+              tma_load_2d(sm->b[stage] + j * (BK * 128), &tmB, &sm->full[stage], n0 + j * 64, b0 + k * BK);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -192,7 +229,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, AMN, BMN);
+      // start-address step (16-byte units) of one 16-deep MMA: 32 bytes along a K-major row,
+      // 16 K-rows of 128 bytes in an MN-major box
+      constexpr uint64_t kStepA = AMN ? 128 : 2, kStepB = BMN ? 128 : 2;
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
@@ -203,13 +243,13 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int k = k_begin; k < k_end; ++k) {
           if (!mbar_wait(&sm->full[stage], phase)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint64_t da = make_kmajor_sw128_desc(smem_u32(sm->a[stage]));
-          const uint64_t db = make_kmajor_sw128_desc(smem_u32(sm->b[stage]));
+          const uint64_t da = AMN ? make_mnmajor_sw128_desc(smem_u32(sm->a[stage]), BK * 128)
+                                  : make_kmajor_sw128_desc(smem_u32(sm->a[stage]));
+          const uint64_t db = BMN ? make_mnmajor_sw128_desc(smem_u32(sm->b[stage]), BK * 128)
+                                  : make_kmajor_sw128_desc(smem_u32(sm->b[stage]));
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            // +32 bytes per 16-element K step inside the 128-byte swizzle atom
-            umma_bf16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (k > k_begin || kk > 0) ? 1u : 0u);
-          }
+          for (int kk = 0; kk < BK / 16; ++kk)
+            umma_bf16(d_tmem, da + kStepA * kk, db + kStepB * kk, idesc, (k > k_begin || kk > 0) ? 1u : 0u);
           umma_commit(&sm->empty[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -241,7 +281,12 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (row < row_end && col < N && !empty_slice) {
           if (splits == 1) {
             if (grp.n_peer == 0) {
-              store_row32<OutT>(C + (int64_t)row * ldc + col, r, min(32, N - col));
+              if constexpr (sizeof(OutT) == 4) {
+                if (grp.accumulate) add_row32(C + (int64_t)row * ldc + col, r, min(32, N - col));
+                else store_row32<OutT>(C + (int64_t)row * ldc + col, r, min(32, N - col));
+              } else {
+                store_row32<OutT>(C + (int64_t)row * ldc + col, r, min(32, N - col));
+              }
             } else {
               // GEMM + all-gather of the partial product: the tile goes straight from tensor memory
               // into every rank's staging slot (plain stores over NVLink for the peers), while the
@@ -274,9 +319,16 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 // Split-K epilogue: C = sum over the k-slice planes of the workspace.
 template <typename OutT>
-__global__ void splitk_finalize_kernel(const float* __restrict__ ws, OutT* __restrict__ C, int64_t n, int splits) {
+__global__ void splitk_finalize_kernel(const float* __restrict__ ws, OutT* __restrict__ C, int64_t n, int splits,
+                                       int accumulate = 0) {
   for (int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * blockDim.x * 4) {
     float4 v = *reinterpret_cast<const float4*>(ws + i);
+    if constexpr (sizeof(OutT) == 4) {
+      if (accumulate) {
+        const float4 c = *reinterpret_cast<const float4*>(C + i);
+        v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+      }
+    }
     for (int s = 1; s < splits; ++s) {
       const float4 u = *reinterpret_cast<const float4*>(ws + (int64_t)s * n + i);
       v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
@@ -327,9 +379,39 @@ CUtensorMap make_tmap_bf16(const void* ptr, int64_t rows, int64_t cols, int64_t 
 
 }  // namespace
 
-// a [M, K] bf16 (row stride lda), b [N, K] bf16 -> C [M, N] (bf16, or fp32 when out_fp32)
+// Per-device state: the SM count and, per kernel instantiation, whether the opt-in for more than
+// 48 KB of dynamic shared memory has been made on that device (the attribute is per device).
+static int device_sms(int dev) {
+  static int sms[64] = {};
+  TORCH_CHECK(dev >= 0 && dev < 64, "gemm: device index out of range");
+  if (!sms[dev]) C10_CUDA_CHECK(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
+  return sms[dev];
+}
+
+template <typename T, int W, int AMN, int BMN>
+static void launch_gemm(int dev, int grid, cudaStream_t st, const CUtensorMap& tmA, const CUtensorMap& tmB, T* c, float* ws,
+                        int M, int N, int K, int ldc, int splits, const GroupArgs& ga) {
+  static bool cfg[64] = {};
+  const size_t smem = sizeof(SmemLayoutT<W>) + 1024;
+  if (!cfg[dev]) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_nt_kernel<T, W, AMN, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cfg[dev] = true;
+  }
+  gemm_bf16_nt_kernel<T, W, AMN, BMN><<<grid, kThreads, smem, st>>>(tmA, tmB, c, ws, M, N, K, ldc, splits, ga);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// General entry.  amn = 0: a is [M, K] with K contiguous; amn = 1: a is [K, M] with M contiguous (the
+// product uses a^T).  bmn = 0: b is [N, K]; bmn = 1: b is [K, N].  C [M, N] is bf16, or fp32 when
+// out_fp32; `accumulate` (fp32 only) adds the product to what `out` already holds.
+static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int amn, int bmn, bool out_fp32,
+                                 const at::Tensor* out, bool accumulate = false,
+                                 const std::vector<int64_t>* peer_out = nullptr);
+
 static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bool out_fp32, const at::Tensor* out,
-                                    const std::vector<int64_t>* peer_out = nullptr);
+                                    const std::vector<int64_t>* peer_out = nullptr) {
+  return gemm_bf16_impl(a, b, 0, 0, out_fp32, out, false, peer_out);
+}
 
 // GEMM whose epilogue stores the [M, N] result to several addresses at once: the copies of a
 // symmetric-memory staging slot on every rank of a tensor-parallel group (this rank's own copy
@@ -356,33 +438,63 @@ void gemm_bf16_nt_out(const at::Tensor& a, const at::Tensor& b, at::Tensor out) 
   gemm_bf16_nt_impl(a, b, out.scalar_type() == at::kFloat, &out);
 }
 
-static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bool out_fp32, const at::Tensor* out,
-                                    const std::vector<int64_t>* peer_out) {
+// Input gradient of a linear layer: C[M, N] = a[M, K] * b[K, N] (b row-major, e.g. dx = dy W).
+at::Tensor gemm_bf16_nn(const at::Tensor& a, const at::Tensor& b, bool out_fp32) {
+  return gemm_bf16_impl(a, b, 0, 1, out_fp32, nullptr);
+}
+
+// Weight gradient of a linear layer: C[M, N] (+)= a[K, M]^T * b[K, N] (e.g. dW = dy^T x).  With `out`
+// (contiguous [M, N], bf16 or fp32) the result is written there; accumulate = true adds to an fp32 `out`.
+at::Tensor gemm_bf16_tn(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& out, bool accumulate,
+                        bool out_fp32) {
+  if (out.has_value()) {
+    const at::Tensor& o = *out;
+    TORCH_CHECK(o.is_cuda() && o.is_contiguous() && o.dim() == 2 && o.size(0) == a.size(1) && o.size(1) == b.size(1),
+                "gemm_bf16_tn: out must be contiguous [M, N]");
+    TORCH_CHECK(o.scalar_type() == at::kBFloat16 || o.scalar_type() == at::kFloat, "gemm_bf16_tn: bf16 or fp32 out");
+    TORCH_CHECK(!accumulate || o.scalar_type() == at::kFloat, "gemm_bf16_tn: accumulation needs an fp32 out");
+    TORCH_CHECK((uintptr_t)o.data_ptr() % 16 == 0, "gemm_bf16_tn: 16-byte aligned out");
+    return gemm_bf16_impl(a, b, 1, 1, o.scalar_type() == at::kFloat, &o, accumulate);
+  }
+  TORCH_CHECK(!accumulate, "gemm_bf16_tn: accumulation needs an out tensor");
+  return gemm_bf16_impl(a, b, 1, 1, out_fp32, nullptr);
+}
+
+static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int amn, int bmn, bool out_fp32,
+                                 const at::Tensor* out, bool accumulate, const std::vector<int64_t>* peer_out) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16,
-              "gemm_bf16_nt: bf16 CUDA tensors");
-  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "gemm_bf16_nt: A [M,K], B [N,K]");
-  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1, "gemm_bf16_nt: K must be the contiguous dimension");
-  const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
-  TORCH_CHECK(K % 8 == 0 && a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "gemm_bf16_nt: K and row strides must be multiples of 8");
-  TORCH_CHECK(((uintptr_t)a.data_ptr() % 16 == 0) && ((uintptr_t)b.data_ptr() % 16 == 0), "gemm_bf16_nt: 16-byte aligned operands");
+              "gemm_bf16: bf16 CUDA tensors");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm_bf16: two-dimensional operands");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1, "gemm_bf16: the last dimension of both operands must be contiguous");
+  const int64_t M = amn ? a.size(1) : a.size(0), K = amn ? a.size(0) : a.size(1);
+  const int64_t N = bmn ? b.size(1) : b.size(0), Kb = bmn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm_bf16: contraction extents differ (", K, " vs ", Kb, ")");
+  TORCH_CHECK(a.size(1) % 8 == 0 && b.size(1) % 8 == 0 && a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0,
+              "gemm_bf16: contiguous extents and row strides must be multiples of 8");
+  TORCH_CHECK(((uintptr_t)a.data_ptr() % 16 == 0) && ((uintptr_t)b.data_ptr() % 16 == 0), "gemm_bf16: 16-byte aligned operands");
+  TORCH_CHECK(!accumulate || (out != nullptr && out_fp32), "gemm_bf16: accumulation needs an fp32 out tensor");
   auto c = out ? *out : at::empty({M, N}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
   if (M == 0 || N == 0) return c;
-  if (K == 0) return c.zero_();
-  TORCH_CHECK(N % 8 == 0, "gemm_bf16_nt: N must be a multiple of 8");
-  static int num_sms = 0;
-  if (!num_sms) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, a.get_device());
+  if (K == 0) return accumulate ? c : c.zero_();
+  TORCH_CHECK(N % 8 == 0, "gemm_bf16: N must be a multiple of 8");
+  const int dev = a.get_device();
+  const int num_sms = device_sms(dev);
+  const bool plain_nt = !amn && !bmn;
+  TORCH_CHECK(!(amn && !bmn), "gemm_bf16: the layout A[K,M]^T * B[N,K]^T is not built");
   const int tiles_m = (int)((M + BM - 1) / BM);
   const int k_iters = (int)((K + BK - 1) / BK);
   // Tile width and K slicing.  Large problems: 256-wide tiles, whole K.  Few rows (a decode
   // step): every SM should stream weights exactly once, so pick, among widths 256/128/64 and
   // slice counts that keep all work in one wave, the plan with the least estimated traffic
   // time: operand bytes per SM-sequence plus, when K is sliced, the fp32 partial planes.
+  // (The gradient layouts are built 256 wide only.)
   int bn = 256, splits = 1;
-  if (g_force_bn) {
+  if (g_force_bn && plain_nt) {
     bn = g_force_bn;
   } else if (tiles_m * ((N + 255) / 256) < num_sms) {
     double best = 1e30;
     for (int cand : {256, 128, 64}) {
+      if (!plain_nt && cand != 256) continue;
       const int tiles = tiles_m * (int)((N + cand - 1) / cand);
       int max_s = 1;
       if (g_allow_splitk && N % 4 == 0 && tiles < num_sms && peer_out == nullptr) max_s = std::min({num_sms / tiles, std::max(k_iters / 4, 1), 16});
@@ -402,7 +514,7 @@ static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bo
       }
     }
   }
-  if (g_force_bn && g_allow_splitk && N % 4 == 0 && peer_out == nullptr) {
+  if (g_force_bn && plain_nt && g_allow_splitk && N % 4 == 0 && peer_out == nullptr) {
     const int tiles = tiles_m * (int)((N + bn - 1) / bn);
     if (tiles * 2 <= num_sms) {
       splits = std::min({num_sms / tiles, std::max(k_iters / 4, 1), 16});
@@ -411,34 +523,45 @@ static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bo
     }
   }
   const int tiles = tiles_m * (int)((N + bn - 1) / bn);
-  CUtensorMap tmA = make_tmap_bf16(a.data_ptr(), M, K, a.stride(0), BM);
-  CUtensorMap tmB = make_tmap_bf16(b.data_ptr(), N, K, b.stride(0), bn);
+  // K-major operand: boxes of 64 K x (tile rows); MN-major operand: boxes of 64 MN x 64 K over the [K, MN] matrix
+  CUtensorMap tmA = amn ? make_tmap_bf16(a.data_ptr(), K, M, a.stride(0), BK) : make_tmap_bf16(a.data_ptr(), M, K, a.stride(0), BM);
+  CUtensorMap tmB = bmn ? make_tmap_bf16(b.data_ptr(), K, N, b.stride(0), BK) : make_tmap_bf16(b.data_ptr(), N, K, b.stride(0), bn);
   auto st = at::cuda::getCurrentCUDAStream();
-  float* ws = splits > 1 ? splitk_workspace(a.get_device(), a.options()) : nullptr;
+  float* ws = splits > 1 ? splitk_workspace(dev, a.options()) : nullptr;
   const int grid = std::min(tiles * splits, num_sms);
   GroupArgs ga;
+  ga.accumulate = accumulate ? 1 : 0;
   if (peer_out != nullptr) {
     TORCH_CHECK(splits == 1, "pushed output needs an unsliced K");
     ga.n_peer = (int)peer_out->size();
     for (int i = 0; i < ga.n_peer; ++i) ga.peer_out[i] = reinterpret_cast<void*>((*peer_out)[i]);
   }
-#define CLB_LAUNCH_GEMM(T, W, PTR)                                                                                   \
-  do {                                                                                                                \
-    const size_t smem = sizeof(SmemLayoutT<W>) + 1024;                                                                \
-    static bool cfg = false;                                                                                          \
-    if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<T, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; } \
-    gemm_bf16_nt_kernel<T, W><<<grid, kThreads, smem, st>>>(tmA, tmB, PTR, ws, (int)M, (int)N, (int)K, (int)N, splits, ga); \
-  } while (0)
+  const int fgrid = (int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8);
+#define CLB_GEMM_ARGS(PTR) dev, grid, st, tmA, tmB, PTR, ws, (int)M, (int)N, (int)K, (int)N, splits, ga
   if (out_fp32) {
     float* p = c.data_ptr<float>();
-    if (bn == 256) CLB_LAUNCH_GEMM(float, 256, p); else if (bn == 128) CLB_LAUNCH_GEMM(float, 128, p); else CLB_LAUNCH_GEMM(float, 64, p);
-    if (splits > 1) splitk_finalize_kernel<float><<<(int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8), 256, 0, st>>>(ws, p, M * N, splits);
+    if (amn && bmn) launch_gemm<float, 256, 1, 1>(CLB_GEMM_ARGS(p));
+    else if (bmn) launch_gemm<float, 256, 0, 1>(CLB_GEMM_ARGS(p));
+    else if (bn == 256) launch_gemm<float, 256, 0, 0>(CLB_GEMM_ARGS(p));
+    else if (bn == 128) launch_gemm<float, 128, 0, 0>(CLB_GEMM_ARGS(p));
+    else launch_gemm<float, 64, 0, 0>(CLB_GEMM_ARGS(p));
+    if (splits > 1) {
+      splitk_finalize_kernel<float><<<fgrid, 256, 0, st>>>(ws, p, M * N, splits, ga.accumulate);
+      C10_CUDA_KERNEL_LAUNCH_CHECK();
+    }
   } else {
     bf16* p = (bf16*)c.data_ptr();
-    if (bn == 256) CLB_LAUNCH_GEMM(bf16, 256, p); else if (bn == 128) CLB_LAUNCH_GEMM(bf16, 128, p); else CLB_LAUNCH_GEMM(bf16, 64, p);
-    if (splits > 1) splitk_finalize_kernel<bf16><<<(int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8), 256, 0, st>>>(ws, p, M * N, splits);
+    if (amn && bmn) launch_gemm<bf16, 256, 1, 1>(CLB_GEMM_ARGS(p));
+    else if (bmn) launch_gemm<bf16, 256, 0, 1>(CLB_GEMM_ARGS(p));
+    else if (bn == 256) launch_gemm<bf16, 256, 0, 0>(CLB_GEMM_ARGS(p));
+    else if (bn == 128) launch_gemm<bf16, 128, 0, 0>(CLB_GEMM_ARGS(p));
+    else launch_gemm<bf16, 64, 0, 0>(CLB_GEMM_ARGS(p));
+    if (splits > 1) {
+      splitk_finalize_kernel<bf16><<<fgrid, 256, 0, st>>>(ws, p, M * N, splits, 0);
+      C10_CUDA_KERNEL_LAUNCH_CHECK();
+    }
   }
-#undef CLB_LAUNCH_GEMM
+#undef CLB_GEMM_ARGS
   return c;
 }
 
@@ -508,19 +631,15 @@ at::Tensor grouped_gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, const 
                                                reinterpret_cast<int4*>(table.data_ptr<int>()), count.data_ptr<int>());
   CUtensorMap tmA = make_tmap_bf16(a.data_ptr(), R, K, K, BM);
   CUtensorMap tmB = make_tmap_bf16(b.data_ptr(), G * N, K, K, BN);
-  static int num_sms = 0;
-  if (!num_sms) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, a.get_device());
-  const size_t smem = sizeof(SmemLayout) + 1024;
-  static bool cfg = false;
-  if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
+  const int num_sms = device_sms(a.get_device());
   const int tiles_n = (int)((N + BN - 1) / BN);
   const int grid = std::min(capacity * tiles_n, num_sms);
   GroupArgs g;
   g.table = reinterpret_cast<const int4*>(table.data_ptr<int>());
   g.count = count.data_ptr<int>();
   // M = capacity * BM makes the kernel's row-tile bound equal to the table capacity
-  gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, (bf16*)c.data_ptr(), nullptr, capacity * BM, (int)N,
-                                                         (int)K, (int)N, 1, g);
+  launch_gemm<bf16, 256, 0, 0>(a.get_device(), grid, st, tmA, tmB, (bf16*)c.data_ptr(), nullptr, capacity * BM, (int)N, (int)K,
+                               (int)N, 1, g);
   return c;
 }
 
@@ -543,18 +662,14 @@ void grouped_gemm_bf16_nt_table(const at::Tensor& a, const at::Tensor& b, const 
   auto st = at::cuda::getCurrentCUDAStream();
   CUtensorMap tmA = make_tmap_bf16(a.data_ptr(), R, K, K, BM);
   CUtensorMap tmB = make_tmap_bf16(b.data_ptr(), G * N, K, K, BN);
-  static int num_sms = 0;
-  if (!num_sms) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, a.get_device());
-  const size_t smem = sizeof(SmemLayout) + 1024;
-  static bool cfg = false;
-  if (!cfg) { cudaFuncSetAttribute(gemm_bf16_nt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
+  const int num_sms = device_sms(a.get_device());
   const int tiles_n = (int)((N + BN - 1) / BN);
   const int grid = std::min(capacity * tiles_n, num_sms);
   GroupArgs g;
   g.table = reinterpret_cast<const int4*>(table.data_ptr<int>());
   g.count = count.data_ptr<int>();
-  gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, (bf16*)out.data_ptr(), nullptr, capacity * BM, (int)N,
-                                                         (int)K, (int)N, 1, g);
+  launch_gemm<bf16, 256, 0, 0>(a.get_device(), grid, st, tmA, tmB, (bf16*)out.data_ptr(), nullptr, capacity * BM, (int)N, (int)K,
+                               (int)N, 1, g);
 }
 
 // ----------------------------------------------------------------------------
@@ -562,6 +677,7 @@ void grouped_gemm_bf16_nt_table(const at::Tensor& a, const at::Tensor& b, const 
 // fixed file-scope device array instead of a workspace from the allocator.
 // ----------------------------------------------------------------------------
 #include <cstdio>
+#include <mutex>
 
 #include "gemm_noalloc.h"
 
@@ -572,7 +688,9 @@ namespace {
 struct NoAllocDevice {
   float* scratch = nullptr;   // device address of g_noalloc_scratch on this device
   int num_sms = 0;
-  bool ready = false;
+  int rc = 0;                 // outcome of the one-time set-up (0 = ready)
+  char err[200] = "";
+  std::once_flag once;        // host threads that make their first call together set up once
 };
 NoAllocDevice g_noalloc_dev[64];
 thread_local char g_noalloc_err[320] = "";
@@ -584,35 +702,43 @@ int noalloc_fail(int code, const char* fmt, long long a = 0, long long b = 0, lo
 
 // In host code the array's name is only a handle: the address a kernel can use comes
 // from cudaGetSymbolAddress, once per device, with that device current.
-int noalloc_setup(int dev) {
+void noalloc_setup_once(int dev) {
   NoAllocDevice& d = g_noalloc_dev[dev];
-  if (d.ready) return 0;
+  auto fail = [&](int code, const char* what, cudaError_t e) {
+    d.rc = code;
+    std::snprintf(d.err, sizeof(d.err), "%s failed on device %d: error %d", what, dev, (int)e);
+  };
   void* p = nullptr;
   cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-  if (e != cudaSuccess || p == nullptr)
-    return noalloc_fail(10, "cudaGetSymbolAddress(scratch) failed on device %lld: error %lld", dev, (long long)e);
+  if (e != cudaSuccess || p == nullptr) return fail(10, "cudaGetSymbolAddress(scratch)", e);
   e = cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev);
-  if (e != cudaSuccess) return noalloc_fail(11, "cudaDeviceGetAttribute failed: error %lld", (long long)e);
+  if (e != cudaSuccess) return fail(11, "cudaDeviceGetAttribute", e);
   const int smem = (int)(sizeof(SmemLayout) + 1024);
   e = cudaFuncSetAttribute(gemm_bf16_nt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(gemm_bf16_nt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return noalloc_fail(12, "cudaFuncSetAttribute failed: error %lld", (long long)e);
+  if (e != cudaSuccess) return fail(12, "cudaFuncSetAttribute", e);
   d.scratch = static_cast<float*>(p);
-  d.ready = true;
+}
+
+int noalloc_setup(int dev) {
+  NoAllocDevice& d = g_noalloc_dev[dev];
+  std::call_once(d.once, noalloc_setup_once, dev);
+  if (d.rc) { std::snprintf(g_noalloc_err, sizeof(g_noalloc_err), "%s", d.err); return d.rc; }
   return 0;
 }
 
 bool noalloc_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  if (!fn) {
+  static std::once_flag once;
+  std::call_once(once, [] {
     cudaDriverEntryPointQueryResult q;
     void* p = nullptr;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess || !p)
-      return false;
-    fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
-  }
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess && p)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  });
+  if (!fn) return false;
   cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t gstride[1] = {(cuuint64_t)(ld * 2)};
   cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
@@ -625,6 +751,13 @@ bool noalloc_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t cols, 
 }  // namespace
 
 extern "C" const char* clb200_gemm_noalloc_last_error(void) { return g_noalloc_err; }
+
+extern "C" int clb200_gemm_noalloc_device_status(void) {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0 && cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
 
 extern "C" int clb200_gemm_bf16_nt_noalloc(const void* a, const void* b, void* c, int M, int N, int K, int lda,
                                            int ldb, int out_fp32, void* stream) {
@@ -639,7 +772,8 @@ extern "C" int clb200_gemm_bf16_nt_noalloc(const void* a, const void* b, void* c
     return noalloc_fail(5, "problem too large for the built-in scratch: 2*M*N = %lld floats > %lld",
                         2ll * M * N, (long long)CLB200_NOALLOC_SCRATCH_FLOATS);
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return noalloc_fail(6, "cudaGetDevice failed");
+  if (cudaGetDevice(&dev) != cudaSuccess) return noalloc_fail(6, "cudaGetDevice failed");
+  if (dev < 0 || dev >= 64) return noalloc_fail(9, "device index %lld is beyond the 64 devices this entry point keeps state for", dev);
   if (int rc = noalloc_setup(dev)) return rc;
   const NoAllocDevice& d = g_noalloc_dev[dev];
   CUtensorMap tmA, tmB;
@@ -656,12 +790,13 @@ extern "C" int clb200_gemm_bf16_nt_noalloc(const void* a, const void* b, void* c
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t mn = (int64_t)M * N;
   const int fgrid = (int)std::min<int64_t>((mn / 4 + 255) / 256, 148 * 8);
+  (void)cudaGetLastError();      // an error left behind by an earlier, unrelated call must not be blamed on these launches
   if (out_fp32) {
     gemm_bf16_nt_kernel<float><<<grid, kThreads, smem, st>>>(tmA, tmB, static_cast<float*>(c), d.scratch, M, N, K, N, splits, GroupArgs{});
-    if (splits > 1) splitk_finalize_kernel<float><<<fgrid, 256, 0, st>>>(d.scratch, static_cast<float*>(c), mn, splits);
+    if (splits > 1) splitk_finalize_kernel<float><<<fgrid, 256, 0, st>>>(d.scratch, static_cast<float*>(c), mn, splits, 0);
   } else {
     gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, static_cast<bf16*>(c), d.scratch, M, N, K, N, splits, GroupArgs{});
-    if (splits > 1) splitk_finalize_kernel<bf16><<<fgrid, 256, 0, st>>>(d.scratch, static_cast<bf16*>(c), mn, splits);
+    if (splits > 1) splitk_finalize_kernel<bf16><<<fgrid, 256, 0, st>>>(d.scratch, static_cast<bf16*>(c), mn, splits, 0);
   }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return noalloc_fail(8, "kernel launch failed: error %lld", (long long)e);

@@ -125,12 +125,28 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                                 // layout: SWIZZLE_128B
   return d;
 }
-// Instruction descriptor, kind::f16: bf16 x bf16 -> fp32, both operands K-major.
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N) {
+// Shared-memory matrix descriptor for an MN-major bf16 tile (the M or N index is the
+// contiguous one, as in a row-major [K, MN] matrix): TMA boxes of 64 MN-elements x `k_rows`
+// K-rows with the 128-byte swizzle lie back to back.  Inside a box one K-row is 128 bytes,
+// eight K-rows form a 1024-byte swizzle atom (SBO = 1024: from one group of eight K-rows to
+// the next); LBO is the distance between boxes, i.e. between 64-element chunks of MN.  One
+// 16-deep MMA step consumes two atoms, so the start address advances by 2048 bytes per step.
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, uint32_t box_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);            // start address  [0,14)
+  d |= (uint64_t)((box_bytes >> 4) & 0x3FFF) << 16;       // LBO: next 64 MN-elements
+  d |= (uint64_t)(1024 >> 4) << 32;                       // SBO: next 8 K-rows
+  d |= (uint64_t)1 << 46;                                 // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;                                 // layout: SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor, kind::f16: bf16 x bf16 -> fp32; a_mn / b_mn = 1 marks an operand
+// whose shared-memory tile is MN-major (0: K-major).
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn = 0, int b_mn = 0) {
   return (1u << 4)                      // D format: fp32
          | (1u << 7)                    // A format: bf16
          | (1u << 10)                   // B format: bf16
-         | (0u << 15) | (0u << 16)      // A, B K-major
+         | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16)
          | ((uint32_t)(N >> 3) << 17)   // N / 8
          | ((uint32_t)(M >> 4) << 24);  // M / 16
 }

@@ -15,9 +15,31 @@ import torch
 from . import launch_counts, library_counts, reference as ref, register_native
 
 _SO = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C.so")
-if not os.path.exists(_SO):
-    raise ImportError(f"{_SO} not found: run `python -m chatlearn_b200.csrc.build` "
-                      "(CUDA tensors need the sm_100a extension; there is no silent fallback)")
+
+
+def _fresh_binary():
+    """The shared object must match the sources beside it: a hash of ``csrc/`` is baked into it at
+    build time.  A missing or stale binary is rebuilt in place when a compiler is at hand (one
+    builder at a time, the other ranks wait on a file lock); otherwise the import fails with one
+    line that says so, instead of an AttributeError on a missing kernel later."""
+    from chatlearn_b200.csrc import build as _b
+    want, have = _b.source_hash(), _b.binary_hash(_SO)
+    if have == want:
+        return
+    why = f"{_SO} is {'missing' if have is None and not os.path.exists(_SO) else 'stale'} " \
+          f"(built from sources {have}, sources here are {want})"
+    import shutil
+    if os.environ.get("CLB200_NO_REBUILD") == "1" or shutil.which("nvcc") is None:
+        raise ImportError(why + ": run `python -m chatlearn_b200.csrc.build` "
+                          "(CUDA tensors need the sm_100a extension; there is no silent fallback)")
+    import warnings
+    warnings.warn(why + ": rebuilding")
+    _b.build()
+    if _b.binary_hash(_SO) != want:
+        raise ImportError(why + " and the rebuild did not produce a matching binary")
+
+
+_fresh_binary()
 _spec = importlib.util.spec_from_file_location("chatlearn_b200._C", _SO)
 C = importlib.util.module_from_spec(_spec)
 _spec.loader.exec_module(C)
@@ -160,8 +182,32 @@ def rope(x, positions, theta, rot_dim=None):
 
 
 # ------------------------------------------------------------------ linear / GEMM
+def _row_major_ok(t):
+    return t.stride(-1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+
+
+def _main_grad(w):
+    """The fp32 accumulation buffer of a parameter (a view of its block's flat gradient buffer), if it has one."""
+    g = getattr(w, "main_grad", None)
+    if g is not None and g.dtype == torch.float32 and g.is_contiguous() and g.shape == w.shape and g.data_ptr() % 16 == 0:
+        return g
+    return None
+
+
+def wgrad_accumulate(dy, x, w):
+    """Weight gradient ``dy^T x`` of ``y = x w^T`` on the tcgen05 kernel.  Where the parameter has an fp32
+    accumulation buffer the kernel adds into it in its epilogue (no bf16 gradient, no separate add) and
+    ``None`` is returned for autograd; otherwise the bf16 gradient is returned."""
+    main = _main_grad(w)
+    _count("gemm_bf16_tn")
+    if main is not None:
+        C.gemm_bf16_tn(dy, x, main, True, True)
+        return None
+    return C.gemm_bf16_tn(dy, x, None, False, False)
+
+
 class _LinearNT(torch.autograd.Function):
-    """y = x W^T with the tcgen05 kernel; backward GEMMs use cuBLAS (plain library GEMMs)."""
+    """y = x W^T, dx = dy W and dW = dy^T x, all three on the tcgen05 kernel (operand layouts NT, NN, TN)."""
 
     @staticmethod
     def forward(ctx, x, w):
@@ -172,8 +218,14 @@ class _LinearNT(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
-        dx = dy @ w if ctx.needs_input_grad[0] else None
-        dw = dy.t() @ x if ctx.needs_input_grad[1] else None
+        if not _row_major_ok(dy):
+            dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            _count("gemm_bf16_nn")
+            dx = C.gemm_bf16_nn(dy, w, False)
+        if ctx.needs_input_grad[1]:
+            dw = wgrad_accumulate(dy, x, w)
         return dx, dw
 
 
@@ -224,6 +276,18 @@ def gemm_nt(a, b, out_fp32=False):
     return C.gemm_bf16_nt(a, b, out_fp32)
 
 
+def gemm_nn(a, b, out_fp32=False):
+    """Raw C[M, N] = A[M, K] B[K, N] (both row-major) on the tcgen05 kernel (no autograd)."""
+    _count("gemm_bf16_nn")
+    return C.gemm_bf16_nn(a, b, out_fp32)
+
+
+def gemm_tn(a, b, out=None, accumulate=False, out_fp32=False):
+    """Raw C[M, N] (+)= A[K, M]^T B[K, N] (both row-major) on the tcgen05 kernel (no autograd)."""
+    _count("gemm_bf16_tn")
+    return C.gemm_bf16_tn(a, b, out, accumulate, out_fp32)
+
+
 # ------------------------------------------------------------------ lm head log-prob / entropy
 class _LMHeadLogprob(torch.autograd.Function):
     @staticmethod
@@ -255,7 +319,11 @@ class _LMHeadLogprob(torch.autograd.Function):
         T = h.shape[0]
         chunk = ctx.chunk
         gh = torch.empty_like(h)
-        gw = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        own_bwd = ctx.use_own and h.dtype == torch.bfloat16
+        # the weight gradient is accumulated by the GEMM epilogue: straight into the parameter's fp32
+        # accumulation buffer where it has one, else into a local fp32 buffer
+        main = _main_grad(w) if own_bwd else None
+        gw = main if main is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
         g_lp = g_lp.contiguous().float()
         ge = g_ent.contiguous().float() if g_ent is not None else None
         bf = h.dtype == torch.bfloat16
@@ -270,9 +338,16 @@ class _LMHeadLogprob(torch.autograd.Function):
                                g_lp[s:s + chunk], ge[s:s + chunk] if ge is not None else None,
                                ctx.inv_temp, bf)
             _count("logits_grad")
-            gh[s:s + chunk] = dz @ w
-            gw += (dz.t() @ hc).float()
-        return gh, gw.to(w.dtype), None, None, None
+            if own_bwd:
+                gh[s:s + chunk] = C.gemm_bf16_nn(dz, w, False)
+                C.gemm_bf16_tn(dz, hc, gw, True, True)
+                _count("gemm_bf16_nn")
+                _count("gemm_bf16_tn")
+            else:
+                library_counts["lmhead_backward_mm"] += 2
+                gh[s:s + chunk] = dz @ w
+                gw += (dz.t() @ hc).float()
+        return gh, (None if main is not None else gw.to(w.dtype)), None, None, None
 
 
 def lmhead_logprob_entropy(h, w, labels, temperature=1.0, chunk=2048):

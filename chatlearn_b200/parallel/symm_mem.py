@@ -6,8 +6,17 @@ peers' buffers.  Allocation and handle exchange use
 ``torch.distributed._symmetric_memory`` (CUDA VMM allocation + fabric/fd handle
 exchange); the kernels that use the pointers are this package's own.  On CPU
 ranks (gloo) nothing is allocated and ``available()`` is False.
+
+Only plain peer loads and stores are used on these buffers: no kernel here issues
+``multimem`` instructions, so binding the allocations to an NVLink multicast object
+would buy nothing, and a rank that dies while its memory is bound to one can raise
+NVLink faults on the surviving ranks' GPUs.  ``TORCH_SYMM_MEM_DISABLE_MULTICAST=1`` is
+therefore set (unless the caller chose otherwise) before the first allocation.
 """
+import os
 from typing import Dict, List, Optional
+
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 import torch
 import torch.distributed as dist
@@ -31,10 +40,6 @@ def empty(numel: int, dtype, device, group=None) -> torch.Tensor:
     (collective over ``group``)."""
     import torch.distributed._symmetric_memory as sm
     group = group or dist.group.WORLD
-    try:                                     # older torch versions need the group registered first
-        sm.enable_symm_mem_for_group(group.group_name)
-    except Exception:
-        pass
     t = sm.empty(numel, dtype=dtype, device=device)
     h = sm.rendezvous(t, group=group.group_name if hasattr(group, "group_name") else group)
     _REG[t.data_ptr()] = {"handle": h, "base": t.data_ptr(), "numel": numel, "esz": t.element_size(),

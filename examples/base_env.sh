@@ -6,6 +6,8 @@ export MASTER_ADDR=${MASTER_ADDR:-127.0.0.1}
 export MASTER_PORT=${MASTER_PORT:-29500}
 export OMP_NUM_THREADS=${OMP_NUM_THREADS:-8}
 export TOKENIZERS_PARALLELISM=false
+# symmetric memory is used with plain peer loads/stores only: keep it off NVLink multicast objects
+export TORCH_SYMM_MEM_DISABLE_MULTICAST=${TORCH_SYMM_MEM_DISABLE_MULTICAST:-1}
 export PYTORCH_CUDA_ALLOC_CONF=${PYTORCH_CUDA_ALLOC_CONF:-expandable_segments:True}
 # build the sm_100a extension once, in-tree
 python -c "import __graft_entry__ as g; g.build()" || exit 1

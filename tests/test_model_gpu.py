@@ -8,6 +8,8 @@ import sys
 import pytest
 import torch
 
+from chatlearn_b200.utils.utils import get_free_port
+
 from chatlearn_b200 import ops
 
 pytestmark = pytest.mark.gpu
@@ -60,7 +62,7 @@ def test_rollout_engine_native_matches_library():
 def test_grpo_tiny_one_gpu(tmp_path):
     script = os.path.join(ROOT, "tests", "grpo_tiny_driver.py")
     env = dict(os.environ, OUT_DIR=str(tmp_path), RANK="0", WORLD_SIZE="1", LOCAL_RANK="0",
-               MASTER_ADDR="127.0.0.1", MASTER_PORT="29533")
+               MASTER_ADDR="127.0.0.1", MASTER_PORT=str(get_free_port()))
     out = subprocess.run([sys.executable, script], env=env, capture_output=True, text=True, timeout=900)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     res = [json.loads(l[7:]) for l in out.stdout.splitlines() if l.startswith("RESULT ")]

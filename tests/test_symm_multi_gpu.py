@@ -9,15 +9,17 @@ import sys
 import pytest
 import torch
 
+from chatlearn_b200.utils.utils import get_free_port as free_port
+
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_symm_collectives_two_gpus():
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29641", os.path.join(ROOT, "tests", "symm_driver.py")],
+                        "--master-addr", "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests", "symm_driver.py")],
                        capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
     lines = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")]
     assert p.returncode == 0 and lines, p.stdout[-2000:] + p.stderr[-2000:]
@@ -32,9 +34,9 @@ def test_symm_collectives_two_gpus():
 def test_expert_parallel_rollout_paths_agree():
     outs = {}
     for flag in ("0", "1"):
-        env = dict(os.environ, NCCL_NVLS_ENABLE="0", CLB200_SYMM_EP=flag)
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1", CLB200_SYMM_EP=flag)
         p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                            "--master-addr", "127.0.0.1", "--master-port", "29643", os.path.join(ROOT, "tests", "ep_rollout_driver.py")],
+                            "--master-addr", "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests", "ep_rollout_driver.py")],
                            capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
         res = [json.loads(l[7:]) for l in p.stdout.splitlines() if l.startswith("RESULT ")]
         assert p.returncode == 0 and len(res) == 2, p.stdout[-2000:] + p.stderr[-2000:]
@@ -47,9 +49,9 @@ def test_expert_parallel_rollout_paths_agree():
 def test_peer_memory_exchange_two_gpus():
     """All-gather and equal-split all-to-all by peer stores agree bit for bit with NCCL, alone and
     inside the Ulysses head/sequence exchange with gradients."""
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29645", os.path.join(ROOT, "tests", "exchange_driver.py")],
+                        "--master-addr", "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests", "exchange_driver.py")],
                        capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
     lines = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")]
     assert p.returncode == 0 and lines, p.stdout[-2000:] + p.stderr[-2000:]

@@ -29,6 +29,7 @@ def _lib():
     fn.restype = ctypes.c_int
     fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 6 + [ctypes.c_void_p]
     lib.clb200_gemm_noalloc_last_error.restype = ctypes.c_char_p
+    lib.clb200_gemm_noalloc_device_status.restype = ctypes.c_int
     return lib, fn, native
 
 
@@ -51,6 +52,8 @@ def test_noalloc_entry_matches_regular_entry(M, N, K, out_fp32):
         c = torch.full((M, N), float("nan"), device=dev, dtype=torch.float32 if out_fp32 else torch.bfloat16)
         rc = _call(fn, a, b, c, out_fp32)
         assert rc == 0, lib.clb200_gemm_noalloc_last_error().decode()
+        # "launched" is not "finished": a plain C caller learns from this symbol whether a bounded wait gave up
+        assert lib.clb200_gemm_noalloc_device_status() == 0
         want = native.gemm_nt(a, b, out_fp32)
         torch.cuda.synchronize()
         assert native.C.gemm_last_status() == 0
