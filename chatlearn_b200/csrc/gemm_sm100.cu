@@ -21,6 +21,9 @@
 // bounded; a timeout records a status code (readable with gemm_last_status) and
 // the CTA drains and frees its tensor memory instead of hanging.
 #include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAException.h>
+#include <cstdio>
+#include <cstdlib>
 #include <cudaTypedefs.h>
 #include <torch/extension.h>
 
@@ -379,6 +382,20 @@ CUtensorMap make_tmap_bf16(const void* ptr, int64_t rows, int64_t cols, int64_t 
 
 }  // namespace
 
+// Tensor maps are encoded by a driver call, and that call needs the device's context bound to the
+// calling thread.  A thread that has made no CUDA runtime call yet has none: an autograd worker (or any
+// new host thread) whose first op is a GEMM with its output served from the allocator's cache gets
+// here that way.  cudaSetDevice on the current device binds the primary context without changing it.
+static void bind_context_to_thread(int dev) {
+  thread_local int bound = -1;
+  if (bound == dev) return;
+  int cur = -1;
+  C10_CUDA_CHECK(cudaGetDevice(&cur));
+  TORCH_CHECK(cur == dev, "gemm: operands live on device ", dev, " but the current device is ", cur);
+  C10_CUDA_CHECK(cudaSetDevice(cur));
+  bound = dev;
+}
+
 // Per-device state: the SM count and, per kernel instantiation, whether the opt-in for more than
 // 48 KB of dynamic shared memory has been made on that device (the attribute is per device).
 static int device_sms(int dev) {
@@ -460,8 +477,12 @@ at::Tensor gemm_bf16_tn(const at::Tensor& a, const at::Tensor& b, const c10::opt
   return gemm_bf16_impl(a, b, 1, 1, out_fp32, nullptr);
 }
 
+#define GTRACE(...) do { if (g_trace) { std::fprintf(stderr, "[gemm] " __VA_ARGS__); std::fprintf(stderr, "\n"); std::fflush(stderr); } } while (0)
+static const bool g_trace = std::getenv("CLB200_GEMM_TRACE") != nullptr;
+
 static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int amn, int bmn, bool out_fp32,
                                  const at::Tensor* out, bool accumulate, const std::vector<int64_t>* peer_out) {
+  GTRACE("enter amn=%d bmn=%d fp32=%d acc=%d", amn, bmn, (int)out_fp32, (int)accumulate);
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16,
               "gemm_bf16: bf16 CUDA tensors");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm_bf16: two-dimensional operands");
@@ -474,11 +495,14 @@ static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int a
   TORCH_CHECK(((uintptr_t)a.data_ptr() % 16 == 0) && ((uintptr_t)b.data_ptr() % 16 == 0), "gemm_bf16: 16-byte aligned operands");
   TORCH_CHECK(!accumulate || (out != nullptr && out_fp32), "gemm_bf16: accumulation needs an fp32 out tensor");
   auto c = out ? *out : at::empty({M, N}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  GTRACE("M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
   if (M == 0 || N == 0) return c;
   if (K == 0) return accumulate ? c : c.zero_();
   TORCH_CHECK(N % 8 == 0, "gemm_bf16: N must be a multiple of 8");
   const int dev = a.get_device();
+  bind_context_to_thread(dev);
   const int num_sms = device_sms(dev);
+  GTRACE("dev=%d sms=%d", dev, num_sms);
   const bool plain_nt = !amn && !bmn;
   TORCH_CHECK(!(amn && !bmn), "gemm_bf16: the layout A[K,M]^T * B[N,K]^T is not built");
   const int tiles_m = (int)((M + BM - 1) / BM);
@@ -523,11 +547,14 @@ static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int a
     }
   }
   const int tiles = tiles_m * (int)((N + bn - 1) / bn);
+  GTRACE("bn=%d splits=%d tiles=%d", bn, splits, tiles);
   // K-major operand: boxes of 64 K x (tile rows); MN-major operand: boxes of 64 MN x 64 K over the [K, MN] matrix
   CUtensorMap tmA = amn ? make_tmap_bf16(a.data_ptr(), K, M, a.stride(0), BK) : make_tmap_bf16(a.data_ptr(), M, K, a.stride(0), BM);
   CUtensorMap tmB = bmn ? make_tmap_bf16(b.data_ptr(), K, N, b.stride(0), BK) : make_tmap_bf16(b.data_ptr(), N, K, b.stride(0), bn);
+  GTRACE("tensor maps encoded");
   auto st = at::cuda::getCurrentCUDAStream();
   float* ws = splits > 1 ? splitk_workspace(dev, a.options()) : nullptr;
+  GTRACE("stream and workspace %p", (void*)ws);
   const int grid = std::min(tiles * splits, num_sms);
   GroupArgs ga;
   ga.accumulate = accumulate ? 1 : 0;
@@ -562,6 +589,7 @@ static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int a
     }
   }
 #undef CLB_GEMM_ARGS
+  GTRACE("launched");
   return c;
 }
 
@@ -623,6 +651,7 @@ at::Tensor grouped_gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, const 
   TORCH_CHECK(((uintptr_t)a.data_ptr() % 16 == 0) && ((uintptr_t)b.data_ptr() % 16 == 0), "grouped_gemm: 16-byte aligned operands");
   auto c = at::empty({R, N}, a.options());
   if (R == 0) return c;
+  bind_context_to_thread(a.get_device());
   const int capacity = (int)((R + BM - 1) / BM + G);      // every group adds at most one partial tile
   auto table = at::empty({capacity, 4}, a.options().dtype(at::kInt));
   auto count = at::empty({1}, a.options().dtype(at::kInt));
@@ -659,6 +688,7 @@ void grouped_gemm_bf16_nt_table(const at::Tensor& a, const at::Tensor& b, const 
   TORCH_CHECK(K % 8 == 0 && N % 8 == 0 && K > 0, "grouped_gemm_table: K and N must be multiples of 8");
   const int capacity = (int)table.size(0);
   if (R == 0 || capacity == 0) return;
+  bind_context_to_thread(a.get_device());
   auto st = at::cuda::getCurrentCUDAStream();
   CUtensorMap tmA = make_tmap_bf16(a.data_ptr(), R, K, K, BM);
   CUtensorMap tmB = make_tmap_bf16(b.data_ptr(), G * N, K, K, BN);
@@ -676,7 +706,6 @@ void grouped_gemm_bf16_nt_table(const at::Tensor& a, const at::Tensor& b, const 
 // Allocation-free entry point (see gemm_noalloc.h): same kernel, split-K planes in a
 // fixed file-scope device array instead of a workspace from the allocator.
 // ----------------------------------------------------------------------------
-#include <cstdio>
 #include <mutex>
 
 #include "gemm_noalloc.h"
@@ -774,6 +803,15 @@ extern "C" int clb200_gemm_bf16_nt_noalloc(const void* a, const void* b, void* c
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return noalloc_fail(6, "cudaGetDevice failed");
   if (dev < 0 || dev >= 64) return noalloc_fail(9, "device index %lld is beyond the 64 devices this entry point keeps state for", dev);
+  {
+    // a host thread that has made no runtime call yet has no context bound, and the driver call that
+    // encodes the tensor maps needs one; re-selecting the current device binds it and allocates nothing
+    thread_local int bound = -1;
+    if (bound != dev) {
+      if (cudaSetDevice(dev) != cudaSuccess) return noalloc_fail(13, "cudaSetDevice(%lld) failed", dev);
+      bound = dev;
+    }
+  }
   if (int rc = noalloc_setup(dev)) return rc;
   const NoAllocDevice& d = g_noalloc_dev[dev];
   CUtensorMap tmA, tmB;

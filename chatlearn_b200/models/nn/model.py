@@ -86,8 +86,11 @@ class ParamBlock:
                 p._main_grad_hooked = True
 
                 def _fold(param):
-                    param.main_grad.add_(param.grad)
-                    param.grad = None
+                    # a GEMM epilogue may already have added this gradient into main_grad
+                    # (ops.native.wgrad_accumulate): then autograd hands over nothing
+                    if param.grad is not None:
+                        param.main_grad.add_(param.grad)
+                        param.grad = None
                 p.register_post_accumulate_grad_hook(_fold)
             else:
                 p.main_grad = gview
