@@ -1,4 +1,5 @@
-"""Packed causal attention forward: this package's kernel next to the flash-attn library.
+"""Packed causal attention forward: this package's kernels (tensor-memory tcgen05 kernel, warp-level MMA kernel)
+next to the flash-attn library.
 
     python -m benchmarks.bench_attention
 
@@ -25,7 +26,8 @@ def main():
         v = torch.randn(T, nkv, D, device=dev).bfloat16()
         sc = 1 / math.sqrt(D)
         flops = sum(4 * n * n / 2 * D * nq for n in lens)
-        impls = [("own", lambda: native.C.attn_varlen_fwd(q, k, v, cu, sc, True))]
+        impls = [("tcgen05", lambda: native.C.attn_fwd_sm100(q, k, v, cu, sc, True)),
+                 ("mma_sync", lambda: native.C.attn_varlen_fwd(q, k, v, cu, sc, True))]
         if flash_attn_varlen_func is not None:
             impls.append(("flash_attn", lambda: flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens),
                                                                         softmax_scale=sc, causal=True)))

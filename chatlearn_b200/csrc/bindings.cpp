@@ -92,6 +92,10 @@ void gemm_bf16_nt_push(const at::Tensor& a, const at::Tensor& b, at::Tensor out,
 int64_t gemm_last_status();
 void gemm_set_splitk(bool on);
 const char* clb200_source_hash();
+bool attn_fwd_sm100_supported(int64_t head_dim);
+int64_t attn_sm100_last_status();
+std::vector<at::Tensor> attn_fwd_sm100(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                       const at::Tensor& cu_seqlens, double scale, bool causal);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
@@ -147,5 +151,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16_nt_push", &gemm_bf16_nt_push);
   m.def("gemm_last_status", &gemm_last_status);
   m.def("gemm_set_splitk", &gemm_set_splitk);
+  m.def("attn_fwd_sm100_supported", &attn_fwd_sm100_supported);
+  m.def("attn_sm100_last_status", &attn_sm100_last_status);
+  m.def("attn_fwd_sm100", &attn_fwd_sm100);
   m.def("source_hash", []() { return std::string(clb200_source_hash()); });
 }

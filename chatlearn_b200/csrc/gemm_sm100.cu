@@ -28,6 +28,7 @@
 #include <torch/extension.h>
 
 #include "sm100.cuh"
+#include "tmap.h"
 
 using namespace sm100;
 typedef __nv_bfloat16 bf16;
@@ -354,57 +355,18 @@ float* splitk_workspace(int device, const at::TensorOptions& opts) {
   return ws[device].data_ptr<float>();
 }
 
-PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  if (!fn) {
-    cudaDriverEntryPointQueryResult qres;
-    void* p = nullptr;
-    auto err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
-    TORCH_CHECK(err == cudaSuccess && qres == cudaDriverEntryPointSuccess && p, "cuTensorMapEncodeTiled unavailable");
-    fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
-  }
-  return fn;
-}
-
 // rows x cols bf16 row-major matrix with leading dimension ld (elements); box = box_rows x 64.
 CUtensorMap make_tmap_bf16(const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
-  CUtensorMap tm;
-  cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t gstride[1] = {(cuuint64_t)(ld * 2)};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = get_encode_fn()(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box,
-                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
-  return tm;
+  return tmap::make_bf16_2d(ptr, rows, cols, ld, box_rows, BK);
 }
 
 }  // namespace
 
-// Tensor maps are encoded by a driver call, and that call needs the device's context bound to the
-// calling thread.  A thread that has made no CUDA runtime call yet has none: an autograd worker (or any
-// new host thread) whose first op is a GEMM with its output served from the allocator's cache gets
-// here that way.  cudaSetDevice on the current device binds the primary context without changing it.
-static void bind_context_to_thread(int dev) {
-  thread_local int bound = -1;
-  if (bound == dev) return;
-  int cur = -1;
-  C10_CUDA_CHECK(cudaGetDevice(&cur));
-  TORCH_CHECK(cur == dev, "gemm: operands live on device ", dev, " but the current device is ", cur);
-  C10_CUDA_CHECK(cudaSetDevice(cur));
-  bound = dev;
-}
+using tmap::bind_context_to_thread;
+using tmap::device_sms;
 
-// Per-device state: the SM count and, per kernel instantiation, whether the opt-in for more than
-// 48 KB of dynamic shared memory has been made on that device (the attribute is per device).
-static int device_sms(int dev) {
-  static int sms[64] = {};
-  TORCH_CHECK(dev >= 0 && dev < 64, "gemm: device index out of range");
-  if (!sms[dev]) C10_CUDA_CHECK(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
-  return sms[dev];
-}
-
+// `cfg`: whether the opt-in for more than 48 KB of dynamic shared memory has been made on a device
+// (the attribute is per device, so the flag is too).
 template <typename T, int W, int AMN, int BMN>
 static void launch_gemm(int dev, int grid, cudaStream_t st, const CUtensorMap& tmA, const CUtensorMap& tmB, T* c, float* ws,
                         int M, int N, int K, int ldc, int splits, const GroupArgs& ga) {

@@ -17,6 +17,15 @@ from . import native as _n
 
 C = _n.C
 _FORCE_LIBRARY = os.environ.get("CLB200_ATTN", "native") == "library"
+# head dim 128: "tcgen05" (tensor-memory kernel, csrc/attention_sm100.cu) or "mma" (the warp-level MMA kernel that
+# also serves head dim 64)
+_IMPL = os.environ.get("CLB200_ATTN_FWD", "tcgen05")
+
+
+def set_fwd_impl(name: str):
+    global _IMPL
+    assert name in ("tcgen05", "mma")
+    _IMPL = name
 
 
 def _ok(x, D):
@@ -33,7 +42,10 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen=None, scale=None, causal=Tr
         return ref.attention_varlen(q, k, v, cu_seqlens, max_seqlen, scale, causal)
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     cu = cu_seqlens if cu_seqlens.dtype == torch.int32 else cu_seqlens.to(torch.int32)
-    out, _lse = C.attn_varlen_fwd(q, k, v, cu.contiguous(), float(scale), bool(causal))
+    if D == 128 and _IMPL == "tcgen05":
+        out, _lse = C.attn_fwd_sm100(q, k, v, cu.contiguous(), float(scale), bool(causal))
+    else:
+        out, _lse = C.attn_varlen_fwd(q, k, v, cu.contiguous(), float(scale), bool(causal))
     _n._count("attn_varlen_fwd")
     return out
 

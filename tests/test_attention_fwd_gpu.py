@@ -71,3 +71,58 @@ def test_gradient_pass_uses_library_and_matches():
     with torch.no_grad():
         o2 = ops.attention_varlen(q.detach(), k, v, cu, 200, None)
     assert (o.float() - o2.float()).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("nq,nkv", [(8, 2), (4, 4)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_tcgen05_forward_matches_sdpa(nq, nkv, causal):
+    """The tensor-memory kernel (head dim 128) on ragged lengths: single rows, lengths around the 64-key block
+    and the 128-row tile, an empty sequence, and sequences long enough for many key blocks."""
+    from chatlearn_b200.ops import native
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(3)
+    D = 128
+    lens = [1, 63, 64, 65, 127, 128, 129, 200, 0, 1000, 2730, 5]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    qkv = torch.randn(T, (nq + 2 * nkv) * D, device=dev).bfloat16()
+    q = qkv[:, :nq * D].view(T, nq, D)
+    k = qkv[:, nq * D:(nq + nkv) * D].view(T, nkv, D)
+    v = qkv[:, (nq + nkv) * D:].view(T, nkv, D)
+    scale = 1.0 / math.sqrt(D)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+    out, lse = native.C.attn_fwd_sm100(q, k, v, cu_t, scale, causal)
+    torch.cuda.synchronize()
+    assert native.C.attn_sm100_last_status() == 0, "a bounded wait inside the attention kernel ran out"
+    want = _ref(q, k, v, cu, scale, causal)
+    err = (out.float() - want).abs().max().item()
+    assert err < 2e-2, err
+    for si in (3, 9, 10):
+        s, e = cu[si], cu[si + 1]
+        logits = torch.einsum("qd,kd->qk", q[s:e, 1].float(), k[s:e, 1 * nkv // nq].float()) * scale
+        if causal:
+            logits = logits.masked_fill(torch.triu(torch.ones(e - s, e - s, device=dev, dtype=torch.bool), 1), float("-inf"))
+        assert torch.allclose(lse[1, s:e], torch.logsumexp(logits, -1), rtol=1e-3, atol=1e-2)
+
+
+def test_tcgen05_forward_large_scores_exercise_the_lazy_rescale():
+    """Scores that grow along the sequence force the running maximum far past the reference maximum, so the
+    accumulator in tensor memory is rescaled many times."""
+    from chatlearn_b200.ops import native
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(4)
+    T, nq, nkv, D = 1500, 4, 2, 128
+    q = torch.randn(T, nq, D, device=dev).bfloat16()
+    ramp = torch.linspace(0.2, 6.0, T, device=dev).view(T, 1, 1)
+    k = (torch.randn(T, nkv, D, device=dev) * ramp).bfloat16()
+    v = torch.randn(T, nkv, D, device=dev).bfloat16()
+    cu = [0, 700, 1500]
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+    scale = 1.0 / math.sqrt(D)
+    out, _ = native.C.attn_fwd_sm100(q, k, v, cu_t, scale, True)
+    torch.cuda.synchronize()
+    assert native.C.attn_sm100_last_status() == 0
+    want = _ref(q, k, v, cu, scale, True)
+    assert (out.float() - want).abs().max().item() < 3e-2
