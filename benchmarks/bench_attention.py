@@ -44,6 +44,26 @@ def main():
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / 10
             row[name] = {"ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 1)}
+        # backward (dQ, dK, dV; 2.5x the forward's work): the tensor-memory kernel against the library's
+        out, lse = native.C.attn_fwd_sm100(q, k, v, cu, sc, True)
+        d_out = torch.randn_like(out)
+        bwd = [("tcgen05_bwd", lambda: native.C.attn_bwd_sm100(q, k, v, out, d_out, lse, cu, sc, True))]
+        if flash_attn_varlen_func is not None:
+            qg, kg, vg = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+            og = flash_attn_varlen_func(qg, kg, vg, cu, cu, max(lens), max(lens), softmax_scale=sc, causal=True)
+            bwd.append(("flash_attn_bwd", lambda: torch.autograd.grad(og, (qg, kg, vg), d_out, retain_graph=True)))
+        for name, fn in bwd:
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 10
+            row[name] = {"ms": round(ms, 3), "tflops": round(2.5 * flops / ms / 1e9, 1)}
         print(f"{len(lens)} x {lens[0]}", row, flush=True)
 
 

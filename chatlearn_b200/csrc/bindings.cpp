@@ -93,6 +93,10 @@ int64_t gemm_last_status();
 void gemm_set_splitk(bool on);
 const char* clb200_source_hash();
 bool attn_fwd_sm100_supported(int64_t head_dim);
+int64_t attn_bwd_sm100_last_status();
+std::vector<at::Tensor> attn_bwd_sm100(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o,
+                                       const at::Tensor& d_o, const at::Tensor& lse, const at::Tensor& cu_seqlens, double scale,
+                                       bool causal);
 int64_t attn_sm100_last_status();
 std::vector<at::Tensor> attn_fwd_sm100(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                        const at::Tensor& cu_seqlens, double scale, bool causal);
@@ -154,5 +158,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_fwd_sm100_supported", &attn_fwd_sm100_supported);
   m.def("attn_sm100_last_status", &attn_sm100_last_status);
   m.def("attn_fwd_sm100", &attn_fwd_sm100);
+  m.def("attn_bwd_sm100", &attn_bwd_sm100);
+  m.def("attn_bwd_sm100_last_status", &attn_bwd_sm100_last_status);
   m.def("source_hash", []() { return std::string(clb200_source_hash()); });
 }

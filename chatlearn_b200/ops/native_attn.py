@@ -1,11 +1,14 @@
-"""Packed (varlen) attention on this package's forward kernel.
+"""Packed (varlen) attention on this package's kernels.
 
-``csrc/attention_fwd.cu`` covers every pass that needs no gradient: prompt prefill in
-the rollout engine and the behaviour / reference log-prob forwards.  A pass that will be
-differentiated goes to the library statement (flash-attn forward + backward), as the
-reference does for all of them (chatlearn/models/fsdp_module.py:257,269
-``attn_implementation="flash_attention_2"``).  ``CLB200_ATTN=library`` forces the library
-for every pass.
+Head dim 128 runs on the tensor-memory kernels: ``csrc/attention_sm100.cu`` (forward, with the
+log-sum-exp kept for the backward) and ``csrc/attention_bwd_sm100.cu`` (dQ, dK, dV), for passes
+with and without a gradient: prompt prefill in the rollout engine, the behaviour / reference
+log-prob forwards and the trainer's forward + backward.  Head dim 64 has the warp-level MMA
+forward of ``csrc/attention_fwd.cu`` for passes without a gradient; what no kernel covers (other
+head dims, a gradient at head dim 64) goes to the library statement, which is what the reference
+uses for every pass (chatlearn/models/fsdp_module.py:257,269
+``attn_implementation="flash_attention_2"``), and is counted in ``ops.library_counts``.
+``CLB200_ATTN=library`` forces the library for every pass.
 """
 import math
 import os
@@ -33,11 +36,37 @@ def _ok(x, D):
             and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
 
 
+class _AttnVarlen128(torch.autograd.Function):
+    """Forward and backward of packed attention at head dim 128 on the tensor-memory kernels."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu, scale, causal):
+        out, lse = C.attn_fwd_sm100(q, k, v, cu, scale, causal)
+        _n._count("attn_varlen_fwd")
+        ctx.save_for_backward(q, k, v, out, lse, cu)
+        ctx.scale, ctx.causal = scale, causal
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        if not _ok(d_out, 128):
+            d_out = d_out.contiguous()
+        dq, dk, dv = C.attn_bwd_sm100(q, k, v, out, d_out, lse, cu, ctx.scale, ctx.causal)
+        _n._count("attn_varlen_bwd", 3)
+        return dq, dk, dv, None, None, None
+
+
 def attention_varlen(q, k, v, cu_seqlens, max_seqlen=None, scale=None, causal=True):
     D = q.shape[-1]
     needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
-    if (_FORCE_LIBRARY or needs_grad or D not in (64, 128) or v.shape[-1] != D
-            or not (_ok(q, D) and _ok(k, D) and _ok(v, D)) or q.shape[1] % k.shape[1] != 0):
+    shapes_ok = (D in (64, 128) and v.shape[-1] == D and _ok(q, D) and _ok(k, D) and _ok(v, D)
+                 and q.shape[1] % k.shape[1] == 0)
+    if needs_grad and shapes_ok and D == 128 and _IMPL == "tcgen05" and not _FORCE_LIBRARY:
+        scale = scale if scale is not None else 1.0 / math.sqrt(D)
+        cu = cu_seqlens if cu_seqlens.dtype == torch.int32 else cu_seqlens.to(torch.int32)
+        return _AttnVarlen128.apply(q, k, v, cu.contiguous(), float(scale), bool(causal))
+    if _FORCE_LIBRARY or needs_grad or not shapes_ok:
         library_counts["attention_varlen"] += 1
         return ref.attention_varlen(q, k, v, cu_seqlens, max_seqlen, scale, causal)
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
