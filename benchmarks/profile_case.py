@@ -1,6 +1,6 @@
 """Small, self-ending workloads for profiler captures of single kernels.
 
-    python -m benchmarks.profile_case --kernel gemm|gemm_decode|decode|rmsnorm|swiglu|logits|adamw|sample|attn_fwd|grouped_gemm|moe_router
+    python -m benchmarks.profile_case --kernel gemm|gemm_nn|gemm_tn|gemm_decode|decode|rmsnorm|swiglu|logits|adamw|sample|attn_fwd|attn_fwd_sm100|attn_bwd_sm100|grouped_gemm|moe_router
 
 Each case allocates a few hundred MB (operands larger than the 126 MB L2 so DRAM
 figures mean something), runs 3 warm-up launches and 3 measured launches of ONE
@@ -25,6 +25,15 @@ def main():
         A = torch.randn(8192, 4096, device=dev).bfloat16()
         B = torch.randn(4096, 4096, device=dev).bfloat16()
         fn = lambda: C.gemm_bf16_nt(A, B, False)  # noqa: E731
+    elif a.kernel == "gemm_nn":          # input gradient of a 4096 -> 12288 layer over 8192 tokens: dx = dy W
+        A = torch.randn(8192, 12288, device=dev).bfloat16()
+        B = torch.randn(12288, 4096, device=dev).bfloat16()
+        fn = lambda: C.gemm_bf16_nn(A, B, False)  # noqa: E731
+    elif a.kernel == "gemm_tn":          # weight gradient of the same layer, accumulated into fp32: dW += dy^T x
+        A = torch.randn(8192, 12288, device=dev).bfloat16()
+        B = torch.randn(8192, 4096, device=dev).bfloat16()
+        acc = torch.zeros(12288, 4096, device=dev)
+        fn = lambda: C.gemm_bf16_tn(A, B, acc, True, True)  # noqa: E731
     elif a.kernel == "gemm_decode":
         A = torch.randn(128, 4096, device=dev).bfloat16()
         B = torch.randn(24576, 4096, device=dev).bfloat16()
@@ -67,6 +76,20 @@ def main():
         k = torch.randn(T, nkv, d, device=dev).bfloat16()
         v = torch.randn(T, nkv, d, device=dev).bfloat16()
         fn = lambda: C.attn_varlen_fwd(q, k, v, cu, 1 / math.sqrt(d), True)  # noqa: E731
+    elif a.kernel in ("attn_fwd_sm100", "attn_bwd_sm100"):
+        lens = [2730] * 6
+        T, nq, nkv, d = sum(lens), 32, 8, 128
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+        q = torch.randn(T, nq, d, device=dev).bfloat16()
+        k = torch.randn(T, nkv, d, device=dev).bfloat16()
+        v = torch.randn(T, nkv, d, device=dev).bfloat16()
+        sc = 1 / math.sqrt(d)
+        if a.kernel == "attn_fwd_sm100":
+            fn = lambda: C.attn_fwd_sm100(q, k, v, cu, sc, True)  # noqa: E731
+        else:
+            out, lse = C.attn_fwd_sm100(q, k, v, cu, sc, True)
+            d_out = torch.randn_like(out)
+            fn = lambda: C.attn_bwd_sm100(q, k, v, out, d_out, lse, cu, sc, True)  # noqa: E731
     elif a.kernel == "grouped_gemm":
         # Qwen3-30B-A3B expert up-projection: 128 experts, 16384 tokens x top-8 rows, [1536, 2048] each
         E, R, N, K = 128, 16384 * 8, 1536, 2048

@@ -19,7 +19,7 @@
 // MN-major shared-memory descriptors do it.
 //
 // Roles (448 threads): warp 0 TMA producer (K, V once; then Q, dO tiles and the per-row
-// statistics of each item through a 2-stage ring), warp 1 MMA issuer, warps 2..9 the
+// statistics of each item through a 3-stage ring), warp 1 MMA issuer, warps 2..9 the
 // elementwise stage (thread = key row, 32 of the 64 query columns: P = exp2(S c - lse),
 // dS = P (dP - delta) scale, both written as bf16 into swizzled shared-memory tiles, double
 // buffered), warps 10..13 the dQ read-out (thread = head-dim lane).
@@ -38,6 +38,7 @@ namespace {
 
 constexpr int BKV = 128, BQ = 64, D = 128;
 constexpr int kThreads = 448;
+constexpr int kQStages = 3;                // Q / dO ring: a stage is held from its load until the item's dK product has run
 constexpr int kTmemCols = 512;
 constexpr uint32_t COL_S = 0, COL_DP = 64, COL_DV = 128, COL_DK = 256, COL_DQ = 384;
 constexpr uint32_t kBoxKV = BKV * 128;       // one 64-column slice of a K or V tile: 128 rows x 128 bytes
@@ -46,16 +47,18 @@ constexpr uint32_t kBoxQ = BQ * 128;         // one 64-column slice of a Q or dO
 struct SmemBwd {
   uint8_t k[2][kBoxKV];                      // 32 KB (reused to stage dK at the end)
   uint8_t v[2][kBoxKV];                      // 32 KB (reused to stage dV)
-  uint8_t q[2][2][kBoxQ];                    // [stage][slice]
-  uint8_t d_o[2][2][kBoxQ];
+  uint8_t q[kQStages][2][kBoxQ];             // [stage][slice]
+  uint8_t d_o[kQStages][2][kBoxQ];
   uint8_t p[2][BKV * 128];                   // P^T  [128 keys x 64 queries] bf16, K-major, 128-byte swizzle; double buffered
   uint8_t ds[2][BKV * 128];                  // dS^T likewise
-  float lse2[2][BQ];                         // log-sum-exp of the item's query rows in log2 units (+inf past the sequence end)
-  float delta[2][BQ];                        // rowsum(dO * O)
-  uint64_t kv_full, q_full[2], q_empty[2], s_full, s_empty, p_full[2], p_empty[2], dq_full, dq_empty, dkv_full;
+  float lse2[kQStages][BQ];                         // log-sum-exp of the item's query rows in log2 units (+inf past the sequence end)
+  float delta[kQStages][BQ];                        // rowsum(dO * O)
+  uint64_t kv_full, q_full[kQStages], q_empty[kQStages], s_full, s_empty, p_full[2], p_empty[2], dq_full, dq_empty, dkv_full;
   uint32_t tmem_base, abort_flag;
   int seq, blk;
 };
+
+static_assert(sizeof(SmemBwd) <= 227 * 1024, "the backward tiles must fit the 227 KB a CTA may use");
 
 __device__ int g_attn_bwd_status = 0;
 enum : int { ST_OK = 0, ST_PRODUCER = 1, ST_MMA = 2, ST_ELEMENTWISE = 3, ST_SMEM_ALIGN = 4, ST_DQ = 5 };
@@ -107,9 +110,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(&sm->kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kQStages; ++s) {
       mbar_init(&sm->q_full[s], 2);            // the TMA transaction + the statistics written by the producer warp
       mbar_init(&sm->q_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&sm->p_full[s], 256);
       mbar_init(&sm->p_empty[s], 1);
     }
@@ -142,9 +147,9 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tma_load_2d(sm->v[1], &tmV, &sm->kv_full, kvh * D + 64, start + kv0);
     }
     for (int t = 0; t < nitems; ++t) {
-      const int st = t & 1;
+      const int st = t % kQStages;
       const int head = kvh * group + t / nper, qb = i0 + t % nper;
-      if (lane == 0) ok = mbar_wait(&sm->q_empty[st], ((t >> 1) & 1) ^ 1);
+      if (lane == 0) ok = mbar_wait(&sm->q_empty[st], ((t / kQStages) & 1) ^ 1);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       if (lane == 0) {
@@ -178,7 +183,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       bool ok = mbar_wait(&sm->kv_full, 0);
       tc_fence_after_sync();
       auto issue_back = [&](int u) -> bool {
-        const uint32_t buf = u & 1, st = u & 1;
+        const uint32_t buf = u & 1, st = u % kQStages;
         if (!mbar_wait(&sm->p_full[buf], (u >> 1) & 1)) return false;
         tc_fence_after_sync();
         const uint64_t dp = make_kmajor_sw128_desc(smem_u32(sm->p[buf]));
@@ -204,8 +209,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         return true;
       };
       for (int t = 0; t < nitems && ok; ++t) {
-        const uint32_t st = t & 1;
-        if (!mbar_wait(&sm->q_full[st], (t >> 1) & 1)) { ok = false; break; }
+        const uint32_t st = t % kQStages;
+        if (!mbar_wait(&sm->q_full[st], (t / kQStages) & 1)) { ok = false; break; }
         if (!mbar_wait(&sm->s_empty, (t & 1) ^ 1)) { ok = false; break; }
         tc_fence_after_sync();
 #pragma unroll
@@ -238,9 +243,9 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const float c = scale * 1.4426950408889634f;
     bool ok = true;
     for (int t = 0; t < nitems; ++t) {
-      const int st = t & 1, buf = t & 1;
+      const int st = t % kQStages, buf = t & 1;
       const int qb = i0 + t % nper;
-      if (!mbar_wait(&sm->q_full[st], (t >> 1) & 1)) { ok = false; break; }      // the statistics of the item are in place
+      if (!mbar_wait(&sm->q_full[st], (t / kQStages) & 1)) { ok = false; break; }      // the statistics of the item are in place
       if (!mbar_wait(&sm->s_full, t & 1)) { ok = false; break; }
       tc_fence_after_sync();
       uint32_t s[32], dp[32];
