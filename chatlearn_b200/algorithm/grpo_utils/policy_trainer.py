@@ -90,6 +90,11 @@ class PolicyTrainer(FSDPModule):
 
     def _logprobs(self, batch, need_entropy: bool):
         tokens, labels, ctx = self._ctx_and_inputs(batch)
+        if self.resharded:
+            # parameter-sharded mode: every block is gathered only while its segment runs, and a segment's
+            # activations are recomputed in its backward (which is also where its parameters are re-gathered)
+            lp, ent = self.state.logprobs(tokens, labels, ctx)
+            return lp, (ent if need_entropy else None), ctx
         hook = None
         if torch.is_grad_enabled() and getattr(self.module_args, "gradient_checkpointing", False):
             # keep only each layer's input; its activations are recomputed in backward
@@ -155,6 +160,8 @@ class PolicyTrainer(FSDPModule):
         for mb in self._microbatches(data_list, for_train=True):
             if not mb:
                 # ranks with fewer bins still join the collectives of the others
+                if self.resharded:
+                    st.join_empty_microbatch()
                 continue
             batch = pack_samples(mb, pad_multiple=pad)
             lp, ent, ctx = self._logprobs(batch, need_entropy=True)

@@ -16,6 +16,11 @@ class FSDPConfig(BaseConfig):
     meta_init: bool = False
     # optimizer-step reduce-scatter / all-gather by this package's peer-memory kernels (GPU, 2..8 ranks)
     fused_optimizer_comm: bool = True
+    # shard the compute-dtype parameters and the gradient accumulator as well (what the reference's
+    # fully_shard(..., reshard_after_forward=True) does): 1/dp of everything resident, blocks gathered per
+    # segment.  Off: parameters stay whole on every rank (fits dense models up to ~10B on 180 GB) and the
+    # only parameter collectives are one reduce-scatter and one all-gather per optimizer step.
+    reshard_after_forward: bool = False
     groupgemm: bool = False
     use_expandable_segments: bool = False
 

@@ -249,15 +249,17 @@ std::vector<at::Tensor> attn_varlen_fwd(const at::Tensor& q, const at::Tensor& k
   auto st = at::cuda::getCurrentCUDAStream();
   if (D == 128) {
     const size_t smem = sizeof(SmemFwd<128>);
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(attn_varlen_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
+    static bool cfg[64] = {};                    // the attribute is per device
+    const int dev = q.get_device();
+    if (!cfg[dev & 63]) { cudaFuncSetAttribute(attn_varlen_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg[dev & 63] = true; }
     attn_varlen_fwd_kernel<128><<<grid, kThreads, smem, st>>>((const bf16*)q.data_ptr(), (const bf16*)k.data_ptr(),
         (const bf16*)v.data_ptr(), cu_seqlens.data_ptr<int>(), B, (bf16*)out.data_ptr(), lse.data_ptr<float>(), q.stride(0),
         k.stride(0), v.stride(0), (int)nq, (int)nkv, (int)T, (float)scale, causal ? 1 : 0);
   } else {
     const size_t smem = sizeof(SmemFwd<64>);
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(attn_varlen_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }
+    static bool cfg[64] = {};
+    const int dev = q.get_device();
+    if (!cfg[dev & 63]) { cudaFuncSetAttribute(attn_varlen_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg[dev & 63] = true; }
     attn_varlen_fwd_kernel<64><<<grid, kThreads, smem, st>>>((const bf16*)q.data_ptr(), (const bf16*)k.data_ptr(),
         (const bf16*)v.data_ptr(), cu_seqlens.data_ptr<int>(), B, (bf16*)out.data_ptr(), lse.data_ptr<float>(), q.stride(0),
         k.stride(0), v.stride(0), (int)nq, (int)nkv, (int)T, (float)scale, causal ? 1 : 0);

@@ -10,6 +10,7 @@
 // kernel is bound by how fast cp.async keeps HBM busy.
 #include <ATen/cuda/CUDAContext.h>
 #include <cuda_pipeline.h>
+#include <c10/cuda/CUDAException.h>
 #include <torch/extension.h>
 
 #include "common.cuh"
@@ -234,10 +235,12 @@ void launch_tc(const at::Tensor& q, const at::Tensor& kc, const at::Tensor& vc, 
   const int Tq = (int)q.size(0);
   auto st = at::cuda::getCurrentCUDAStream();
   const size_t smem = sizeof(SmemTC<DK, DV>);
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(paged_decode_tc_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    configured = true;
+  static bool configured[64] = {};               // the attribute is per device
+  const int dev = q.get_device();
+  TORCH_CHECK(dev >= 0 && dev < 64, "paged_decode_tc: device index out of range");
+  if (!configured[dev]) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_tc_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev] = true;
   }
   at::Tensor po, pl;
   float* pop = nullptr; float* plp = nullptr;

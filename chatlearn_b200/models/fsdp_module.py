@@ -49,6 +49,10 @@ class FSDPModule(TorchModule):
         return self.is_member and self.mesh.coords.get("sp", 0) == 0
 
     @property
+    def resharded(self) -> bool:
+        return bool(getattr(self.state, "reshard", False))
+
+    @property
     def compute_dtype(self):
         return torch.bfloat16 if self.device.type == "cuda" else torch.float32
 
@@ -88,7 +92,15 @@ class FSDPModule(TorchModule):
             gd = str(getattr(self.module_args, "grad_dtype", "fp32"))
             if gd in ("bf16", "param"):
                 grad_dtype = self.compute_dtype
-            self.state = ShardedTrainState(
+            # parameter-sharded mode (FSDP2 ``reshard_after_forward``): 1/dp of parameters, gradients and
+            # optimizer state resident; blocks are gathered only while their segment runs
+            state_cls = ShardedTrainState
+            if bool(getattr(self.module_args, "reshard_after_forward", False)):
+                from chatlearn_b200.parallel.fsdp2 import ReshardedTrainState
+                assert self.sp is None and self.vision is None, \
+                    "parameter sharding is built for text models without Ulysses sequence parallelism"
+                state_cls = ReshardedTrainState
+            self.state = state_cls(
                 self.model, self.dp_group, lr=oc.lr, betas=(oc.adam_beta1, oc.adam_beta2),
                 eps=getattr(oc, "adam_eps", 1e-8), weight_decay=oc.weight_decay,
                 clip_grad=oc.clip_grad, grad_dtype=grad_dtype)
@@ -96,6 +108,7 @@ class FSDPModule(TorchModule):
             # weights and gradient buffers to stay on the device (symmetric memory)
             fg = self.module_args.free_gpu_memory
             if bool(getattr(self.module_args, "fused_optimizer_comm", True)) and not fg.offload_weights \
+                    and not self.resharded \
                     and os.environ.get("CLB200_SYMM_ZERO", "1") != "0" and ops.get_mode() == "native":
                 if self.state.enable_symm():
                     self._logger.info("optimizer step uses in-kernel reduce-scatter / all-gather over symmetric memory")
@@ -141,6 +154,8 @@ class FSDPModule(TorchModule):
 
     def _weights_regenerable(self) -> bool:
         fg = self.module_args.free_gpu_memory
+        if self.resharded:
+            return False
         return (self.trainable and self.state is not None and self.state.symm is None
                 and not fg.offload_optimizer_states and self._resident.get("optimizer", True))
 
@@ -154,6 +169,11 @@ class FSDPModule(TorchModule):
     def _build_grad_buffers(self):
         if self.state is None:
             return
+        if self.resharded:
+            for s in self.state.states:       # only the resident 1/dp accumulator; whole-block buffers are pooled
+                if s.grad_shard is None:
+                    s.grad_shard = torch.zeros(s.shard_numel, dtype=torch.float32, device=self.device)
+            return
         for s in self.state.states:
             if s.grad is None:
                 gd = self.compute_dtype if str(getattr(
@@ -166,9 +186,16 @@ class FSDPModule(TorchModule):
 
     # ------------------------------------------------------------------ parameter sync (source side)
     def sync_layout(self):
+        if self.resharded:
+            # every rank publishes the slice of each block it holds: the rollout ranks pull what they need from
+            # all of them (over NVLink where the slices live in symmetric memory)
+            rng = {s.block.name: (s.lo, s.hi) for s in self.state.states}
+            return layout_of_model(self.model, self.get_rank(), lambda name: rng[name], prefix=f"{self.name}/")
         return layout_of_model(self.model, self.get_rank(), prefix=f"{self.name}/")
 
     def sync_buffers(self) -> Dict[str, torch.Tensor]:
+        if self.resharded:
+            return {f"{self.name}/{s.block.name}": s.param_shard for s in self.state.states}
         return {f"{self.name}/{b.name}": b.flat for b in self.model.blocks}
 
     def get_fsdp_param_name(self, block_size: int = 3_000_000_000) -> List[List[str]]:
@@ -226,9 +253,14 @@ class FSDPModule(TorchModule):
         torch.save(model_sd, os.path.join(d, f"model_world_size_{W}_rank_{R}.pt"))
         torch.save({"rng": self.get_rng_state(), "iteration": iteration},
                    os.path.join(d, f"extra_state_world_size_{W}_rank_{R}.pt"))
-        if getattr(self.module_args, "save_hf", False) and R == 0:
+        if getattr(self.module_args, "save_hf", False):
             from chatlearn_b200.checkpoint.safetensors_io import save_hf_checkpoint
-            save_hf_checkpoint(self.model, os.path.join(d, "huggingface"))
+            if self.resharded:
+                with self.state.all_gathered() as whole:        # collective: every rank gathers, rank 0 writes
+                    if R == 0:
+                        save_hf_checkpoint(whole, os.path.join(d, "huggingface"))
+            elif R == 0:
+                save_hf_checkpoint(self.model, os.path.join(d, "huggingface"))
         if self.role_group is not None:
             self.role_group.barrier()
 

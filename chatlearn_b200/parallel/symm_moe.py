@@ -11,7 +11,9 @@ inference (rollout); training keeps the differentiable NCCL path.
 
 Capacity: ``capacity_factor`` × the mean rows per expert for the largest step seen so far
 (buffers grow collectively when a larger step arrives).  A full region drops the pair and sets
-status 2, which ``status()`` reports; the caller then re-runs the layer on the NCCL path.
+status 2, which ``status()`` reports; the rollout engine checks it after every ``generate`` call and
+raises (an overflow means the capacity factor is too small for the routing skew: the outputs of that
+call are not used).
 """
 from typing import Optional
 

@@ -358,12 +358,16 @@ class RolloutEngine:
             rows[2][i] = s.blocks[p // bs] * bs + p % bs
             rows[3][i] = p + 1
             nb = len(s.blocks)
-            if owner[i] is not s or blen[i] != nb:
-                first = blen[i] if owner[i] is s else 0        # only the new tail of a known table
+            # the cached row is valid for this sequence *in this life*: a preempted sequence comes back with the
+            # same object but other blocks, so the key carries its preemption count as well
+            who = (s, s.preemptions)
+            same = owner[i] is not None and owner[i] != "pad" and owner[i][0] is s and owner[i][1] == s.preemptions
+            if not same or blen[i] != nb:
+                first = blen[i] if (same and blen[i] < nb) else 0      # only the new tail of a known table
                 gs["bt_host"][i, first:nb] = torch.tensor(s.blocks[first:nb], dtype=torch.int32)
                 gs["bt"][i, first:nb].copy_(gs["bt_host"][i, first:nb], non_blocking=True)
                 xfer.h2d_bytes += (nb - first) * 4
-                owner[i], blen[i] = s, nb
+                owner[i], blen[i] = who, nb
         for i in range(B, Bg):
             if owner[i] != "pad":
                 gs["bt_host"][i, 0] = scratch_block

@@ -39,7 +39,9 @@ def layout_of_model(model, rank: int, shard_of_block=None, prefix: str = "") -> 
 
 
 def _view2d(buf: torch.Tensor, offset: int, stride: int, rows: int, cols: int) -> torch.Tensor:
-    return torch.as_strided(buf, (rows, cols), (stride, 1), offset)
+    # as_strided takes an offset into the *storage*: a buffer that is itself a slice of a larger allocation
+    # (the parameter slices of a sharded trainer live in one arena) starts at its own storage offset
+    return torch.as_strided(buf, (rows, cols), (stride, 1), buf.storage_offset() + offset)
 
 
 class ParameterSyncGroup:
