@@ -42,6 +42,9 @@ def parse():
     p.add_argument("--pack-tokens", type=int, default=16384)
     p.add_argument("--gemm", default=None, choices=[None, "tcgen05", "cublas"])
     p.add_argument("--no-offload", action="store_true")
+    p.add_argument("--reshard", action="store_true",
+                   help="parameter-sharded trainer (FSDP2 reshard_after_forward): 1/N of parameters, gradients and "
+                        "optimizer state resident per GPU instead of whole bf16 parameters and fp32 gradients")
     p.add_argument("--time-budget", type=float, default=float(os.environ.get("CLB200_BENCH_BUDGET", "740")),
                    help="wall-clock seconds for the whole process (set-up included).  When the requested "
                         "warm-up + steps would not fit, warm-up is cut to no fewer than 3 episodes and the "
@@ -150,7 +153,7 @@ def build_config(args, out_dir, data_path, n_gpu):
         "models": {
             "policy_trainer": dict(common, num_gpu=n_gpu, fsdp_size=n_gpu, trainable=True,
                                    generation_batch_size=spe, kl_coef=0.001, gradient_checkpointing=True, checkpoint_layers="auto",
-                                   optimizer={"lr": 2e-6}, save_hf=False,
+                                   optimizer={"lr": 2e-6}, save_hf=False, reshard_after_forward=bool(args.reshard),
                                    # fp32 master + Adam shards stay on the GPU (180 GB HBM); the fp32
                                    # gradient buffer is released outside training
                                    # On one GPU (all optimizer state on it) the bf16 compute copy is dropped
@@ -199,7 +202,12 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29578")
         os.environ.setdefault("RANK", "0"); os.environ.setdefault("WORLD_SIZE", "1"); os.environ.setdefault("LOCAL_RANK", "0")
-    ops.set_mode("library" if args.impl == "library" else "native")
+    # --impl library: the trainer and the reference policy (scoring passes, forward + backward, optimizer) run on
+    # library statements (torch matmul = cuBLAS, flash-attn, PyTorch elementwise ops, NCCL collectives) instead
+    # of this package's kernels.  The rollout keeps the native engine: generation on PyTorch statements has no
+    # CUDA graphs and synchronises with the host every token, and did not finish one episode in 20 minutes; the
+    # library-class rollout figure is vLLM's, measured by baseline/vllm_rollout.py.
+    ops.set_mode("native")
     if args.gemm:
         from chatlearn_b200.ops import native
         native.set_gemm_impl(args.gemm)
@@ -222,6 +230,21 @@ def main():
     algo = GrpoAlgorithm(cfg)
     algo.validate()
     engine = algo.build_engine()
+    if args.impl == "library":
+        import functools
+        for role in ("policy_trainer", "ref_policy"):
+            m = engine.named_models.get(role) if hasattr(engine, "named_models") else None
+            if m is None:
+                continue
+            for fn_name in ("forward_step", "train_step"):
+                fn = getattr(m, fn_name, None)
+                if fn is None:
+                    continue
+
+                def wrapped(*a, _fn=fn, **k):
+                    with ops.mode("library"):
+                        return _fn(*a, **k)
+                setattr(m, fn_name, functools.wraps(fn)(wrapped))
     engine.prepare()
 
     def barrier():
@@ -294,8 +317,9 @@ def main():
             "n_gpus": world, "steps": K, "warmup": done_warm, "steps_requested": args.steps,
             "warmup_requested": args.warmup, "time_budget_s": args.time_budget, "ms_per_step": round(ms_per_step, 2),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": vs_baseline(world, value, args), "dtype": "bf16", "data": "synthetic",
-            "impl": args.impl,
+            "impl": args.impl if args.impl == "native" else "library trainer (cuBLAS + flash-attn + PyTorch statements), native rollout",
             "config": {"model": args.model, "global_batch": samples, "seq_len": seq,
+                       "trainer_parameters": "sharded 1/N per GPU (gathered per segment)" if args.reshard else "whole per GPU (optimizer state sharded)",
                        "parallelism": f"trainer zero-dp{world} + rollout tp{2 if world >= 2 else 1}x{max(world // 2, 1) if world >= 2 else 1}",
                        "prompts": samples // args.samples_per_prompt, "samples_per_prompt": args.samples_per_prompt,
                        "prompt_len": args.prompt_len, "max_response": args.max_response,

@@ -166,24 +166,11 @@ class PolicyTrainer(FSDPModule):
             batch = pack_samples(mb, pad_multiple=pad)
             lp, ent, ctx = self._logprobs(batch, need_entropy=True)
             if ma.use_group_sequence_policy:
-                loss_tok, _, _ = ops.gspo_token_loss(
-                    lp, batch.old_logprobs, batch.advantages, batch.seq_ids, len(batch.seq_lens),
-                    batch.loss_mask, ma.pos_clip_ratio, ma.neg_clip_ratio, ma.diff_clip_ratio,
-                    ma.final_clip_ratio)
-                m = batch.loss_mask
-                total = (loss_tok * m).sum()
-                s6 = [(loss_tok.detach() * m).sum()]
-                if use_ref:
-                    kl = ops.kl_k3(lp, batch.ref_logprobs)
-                    total = total + ma.kl_coef * (kl * m).sum()
-                    s6.append((kl.detach() * m).sum())
-                else:
-                    s6.append(torch.zeros((), device=self.device))
-                if need_ent:
-                    total = total - ma.entropy_coef * (ent * m).sum()
-                s6.append((ent.detach() * m).sum())
-                s6 += [torch.zeros((), device=self.device)] * 2 + [m.sum()]
-                loss, s = total * inv_norm, torch.stack(s6)
+                loss, s = ops.gspo_loss_fused(
+                    lp, batch.old_logprobs, batch.ref_logprobs if use_ref else None, batch.advantages,
+                    batch.loss_mask, batch.seq_ids, len(batch.seq_lens), ent if need_ent else ent.detach(),
+                    ma.pos_clip_ratio, ma.neg_clip_ratio, ma.diff_clip_ratio, ma.final_clip_ratio,
+                    ma.kl_coef, ma.entropy_coef if need_ent else 0.0, inv_norm)
             else:
                 loss, s = ops.grpo_loss_fused(
                     lp, batch.old_logprobs, batch.ref_logprobs if use_ref else None,

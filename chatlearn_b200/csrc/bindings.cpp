@@ -16,6 +16,10 @@ std::vector<at::Tensor> grpo_loss_fwd(const at::Tensor& lp, const at::Tensor& ol
                                       const at::Tensor& mask, const c10::optional<at::Tensor>& ent,
                                       double pos_clip, double neg_clip, double diff_clip, double final_clip,
                                       double kl_coef, double ent_coef, double inv_norm);
+std::vector<at::Tensor> gspo_loss_fwd(const at::Tensor& lp, const at::Tensor& old, const c10::optional<at::Tensor>& ref,
+                                      const at::Tensor& adv, const at::Tensor& mask, const c10::optional<at::Tensor>& ent,
+                                      const at::Tensor& seq_ids, int64_t num_seqs, double pos_clip, double neg_clip,
+                                      double diff_clip, double final_clip, double kl_coef, double ent_coef, double inv_norm);
 void adamw_step(at::Tensor master, const at::Tensor& grad, at::Tensor m, at::Tensor v,
                 const c10::optional<at::Tensor>& out, int64_t step, double lr, double b1, double b2, double eps,
                 double wd, const c10::optional<at::Tensor>& scale_t, double scale_v);
@@ -109,6 +113,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
   m.def("grpo_loss_fwd", &grpo_loss_fwd);
+  m.def("gspo_loss_fwd", &gspo_loss_fwd);
   m.def("adamw_step", &adamw_step);
   m.def("sumsq", &sumsq);
   m.def("logits_stats", &logits_stats);

@@ -364,17 +364,26 @@ at::Tensor qk_norm_rope_bwd(const at::Tensor& dy, const at::Tensor& x, at::Tenso
 // ----------------------------------------------------------------------------- GRPO loss
 // One pass: per-token clipped-ratio loss + k3 KL + entropy bonus, masked sums and
 // the gradients w.r.t. logprob and entropy.  stats: [pg, kl, ent, clip+, clip-, ntok, total].
+// Group-sequence variant (GSPO): `seq_sum` / `seq_cnt` hold, per packed sequence, the masked sum of the log-ratio
+// and the number of masked tokens; every token of a sequence then uses the sequence mean as its log-ratio (its
+// gradient still flows through the token's own log-prob: d = lp - sg(lp) + sg(mean)).
 __global__ void grpo_loss_kernel(const float* __restrict__ lp, const float* __restrict__ old,
                                  const float* __restrict__ ref, const float* __restrict__ adv,
                                  const float* __restrict__ mask, const float* __restrict__ ent,
                                  float* __restrict__ dlp, float* __restrict__ dent, float* __restrict__ stats,
                                  int64_t n, float pos_clip, float neg_clip, float diff_clip, float final_clip,
-                                 float kl_coef, float ent_coef, float inv_norm) {
+                                 float kl_coef, float ent_coef, float inv_norm,
+                                 const int64_t* __restrict__ seq_ids = nullptr, const float* __restrict__ seq_sum = nullptr,
+                                 const float* __restrict__ seq_cnt = nullptr) {
   __shared__ float red[32];
   float acc[7] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const float m = mask[i], A = adv[i];
-    const float d = lp[i] - old[i];
+    float d = lp[i] - old[i];
+    if (seq_ids != nullptr) {
+      const int64_t sq = seq_ids[i];
+      d = seq_sum[sq] / fmaxf(seq_cnt[sq], 1.f);
+    }
     const float ratio = __expf(fminf(d, diff_clip));
     const float dr = (d <= diff_clip) ? ratio : 0.f;
     const float lo = 1.f - neg_clip, hi = 1.f + pos_clip;
@@ -412,6 +421,46 @@ __global__ void grpo_loss_kernel(const float* __restrict__ lp, const float* __re
     float v = block_sum(acc[k], red);
     if (threadIdx.x == 0) atomicAdd(stats + k, v);
   }
+}
+
+// masked per-sequence sum of (lp - old) and token count of a packed row
+__global__ void gspo_seq_sum_kernel(const float* __restrict__ lp, const float* __restrict__ old, const float* __restrict__ mask,
+                                    const int64_t* __restrict__ seq_ids, float* __restrict__ seq_sum, float* __restrict__ seq_cnt,
+                                    int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float m = mask[i];
+    if (m != 0.f) {
+      atomicAdd(seq_sum + seq_ids[i], (lp[i] - old[i]) * m);
+      atomicAdd(seq_cnt + seq_ids[i], m);
+    }
+  }
+}
+
+// GSPO loss of a packed row with its gradient: same outputs as grpo_loss_fwd.  seq_ids [n] int64 in [0, num_seqs).
+std::vector<at::Tensor> gspo_loss_fwd(const at::Tensor& lp, const at::Tensor& old, const c10::optional<at::Tensor>& ref,
+                                      const at::Tensor& adv, const at::Tensor& mask, const c10::optional<at::Tensor>& ent,
+                                      const at::Tensor& seq_ids, int64_t num_seqs, double pos_clip, double neg_clip,
+                                      double diff_clip, double final_clip, double kl_coef, double ent_coef, double inv_norm) {
+  const int64_t n = lp.numel();
+  TORCH_CHECK(seq_ids.scalar_type() == at::kLong && seq_ids.numel() == n && seq_ids.is_contiguous(), "gspo_loss: int64 seq_ids [n]");
+  auto dlp = at::empty_like(lp);
+  auto dent = ent.has_value() ? at::empty_like(lp) : at::empty({0}, lp.options());
+  auto stats = at::zeros({7}, lp.options());
+  auto seq = at::zeros({2, std::max<int64_t>(num_seqs, 1)}, lp.options());
+  if (n > 0) {
+    int grid = (int)std::min<int64_t>((n + 255) / 256, 148 * 4);
+    float* ssum = seq.data_ptr<float>();
+    float* scnt = ssum + std::max<int64_t>(num_seqs, 1);
+    gspo_seq_sum_kernel<<<grid, 256, 0, cur_stream()>>>(lp.data_ptr<float>(), old.data_ptr<float>(), mask.data_ptr<float>(),
+                                                        seq_ids.data_ptr<int64_t>(), ssum, scnt, n);
+    grpo_loss_kernel<<<grid, 256, 0, cur_stream()>>>(
+        lp.data_ptr<float>(), old.data_ptr<float>(), ref.has_value() ? ref->data_ptr<float>() : nullptr,
+        adv.data_ptr<float>(), mask.data_ptr<float>(), ent.has_value() ? ent->data_ptr<float>() : nullptr,
+        dlp.data_ptr<float>(), ent.has_value() ? dent.data_ptr<float>() : nullptr, stats.data_ptr<float>(), n,
+        (float)pos_clip, (float)neg_clip, (float)diff_clip, (float)final_clip, (float)kl_coef, (float)ent_coef,
+        (float)inv_norm, seq_ids.data_ptr<int64_t>(), ssum, scnt);
+  }
+  return {stats, dlp, dent};
 }
 
 std::vector<at::Tensor> grpo_loss_fwd(const at::Tensor& lp, const at::Tensor& old,

@@ -94,6 +94,7 @@ kv_append = _dispatch("kv_append")
 paged_attention = _dispatch("paged_attention")
 lmhead_logprob_entropy = _dispatch("lmhead_logprob_entropy")
 grpo_loss_fused = _dispatch("grpo_loss_fused")
+gspo_loss_fused = _dispatch("gspo_loss_fused")
 adamw_step = _dispatch("adamw_step")
 sumsq = _dispatch("sumsq")
 moe_router = _dispatch("moe_router")

@@ -383,6 +383,36 @@ def grpo_loss_fused(logprobs, old_logprobs, ref_logprobs, advantages, mask, entr
                            diff_clip, final_clip, kl_coef, entropy_coef, inv_norm)
 
 
+class _GspoLoss(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, lp, old, ref_lp, adv, mask, ent, seq_ids, num_seqs, pos_clip, neg_clip, diff_clip, final_clip,
+                kl_coef, ent_coef, inv_norm):
+        f = lambda t: None if t is None else t.contiguous().float()  # noqa: E731
+        stats, dlp, dent = C.gspo_loss_fwd(f(lp), f(old), f(ref_lp), f(adv), f(mask), f(ent),
+                                           seq_ids.to(torch.int64).contiguous(), int(num_seqs), pos_clip, neg_clip,
+                                           diff_clip, final_clip, kl_coef, ent_coef, inv_norm)
+        _count("gspo_loss", 2)
+        ctx.save_for_backward(dlp, dent)
+        ctx.has_ent = ent is not None
+        total = stats[6] * inv_norm
+        ctx.mark_non_differentiable(stats)
+        return total, stats[:6]
+
+    @staticmethod
+    def backward(ctx, g_total, _g_stats):
+        dlp, dent = ctx.saved_tensors
+        g_ent = dent * g_total if ctx.has_ent and dent.numel() else None
+        return (dlp * g_total, None, None, None, None, g_ent) + (None,) * 9
+
+
+def gspo_loss_fused(logprobs, old_logprobs, ref_logprobs, advantages, mask, seq_ids, num_seqs, entropy=None,
+                    pos_clip=3e-4, neg_clip=4e-4, diff_clip=10.0, final_clip=3.0, kl_coef=0.0, entropy_coef=0.0,
+                    inv_norm=1.0):
+    adv = advantages if advantages.shape == logprobs.shape else advantages.expand_as(logprobs)
+    return _GspoLoss.apply(logprobs, old_logprobs, ref_logprobs, adv, mask, entropy, seq_ids, num_seqs, pos_clip,
+                           neg_clip, diff_clip, final_clip, kl_coef, entropy_coef, inv_norm)
+
+
 # ------------------------------------------------------------------ optimizer
 @torch.no_grad()
 def adamw_step(master, grad, exp_avg, exp_avg_sq, out_param, step, lr, beta1, beta2, eps, weight_decay,
@@ -499,7 +529,7 @@ def weight_sync_run(desc_table, num_descs, total_tiles, src_dtype, dst_dtype):
 
 for _name, _fn in (("rmsnorm", rmsnorm), ("add_rmsnorm_", add_rmsnorm_), ("swiglu", swiglu), ("qk_norm_rope", qk_norm_rope), ("rope", rope),
                    ("linear", linear), ("lmhead_logprob_entropy", lmhead_logprob_entropy),
-                   ("grpo_loss_fused", grpo_loss_fused), ("adamw_step", adamw_step), ("sumsq", sumsq),
+                   ("grpo_loss_fused", grpo_loss_fused), ("gspo_loss_fused", gspo_loss_fused), ("adamw_step", adamw_step), ("sumsq", sumsq),
                    ("sample", sample), ("apply_penalties", apply_penalties), ("kv_append", kv_append),
                    ("paged_attention", paged_attention)):
     register_native(_name, _fn)

@@ -314,6 +314,32 @@ def gspo_token_loss(logprobs, old_logprobs, advantages, seq_ids, num_seqs, mask,
     return loss, is_pos, is_neg
 
 
+def gspo_loss_fused(logprobs, old_logprobs, ref_logprobs, advantages, mask, seq_ids, num_seqs, entropy=None,
+                    pos_clip=3e-4, neg_clip=4e-4, diff_clip=10.0, final_clip=3.0,
+                    kl_coef=0.0, entropy_coef=0.0, inv_norm=1.0):
+    """Whole group-sequence (GSPO) loss of a packed row in one call: same contract as ``grpo_loss_fused``
+    (``(total, stats)`` with ``stats = [pg_sum, kl_sum, ent_sum, clip_pos, clip_neg, n_tok]``)."""
+    m = mask.float()
+    adv = advantages if advantages.shape == logprobs.shape else advantages.expand_as(logprobs)
+    pg, is_pos, is_neg = gspo_token_loss(logprobs, old_logprobs, adv, seq_ids, num_seqs, mask, pos_clip, neg_clip,
+                                         diff_clip, final_clip)
+    total = (pg * m).sum()
+    stats = [(pg.detach() * m).sum()]
+    if ref_logprobs is not None:
+        kl = kl_k3(logprobs, ref_logprobs)
+        total = total + kl_coef * (kl * m).sum()
+        stats.append((kl.detach() * m).sum())
+    else:
+        stats.append(torch.zeros((), device=logprobs.device))
+    if entropy is not None:
+        total = total - entropy_coef * (entropy * m).sum()
+        stats.append((entropy.detach() * m).sum())
+    else:
+        stats.append(torch.zeros((), device=logprobs.device))
+    stats += [(is_pos.float() * m).sum(), (is_neg.float() * m).sum(), m.sum()]
+    return total * inv_norm, torch.stack([t.float() for t in stats])
+
+
 def kl_k3(logprobs, ref_logprobs):
     k = ref_logprobs - logprobs
     return torch.clamp(torch.exp(k) - k - 1.0, min=-10.0, max=10.0)

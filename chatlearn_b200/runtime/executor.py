@@ -39,6 +39,89 @@ def all_gather_objects(obj) -> List[Any]:
     return out
 
 
+class _TensorRef:
+    """Stand-in for a tensor that travels on the tensor plane: (dtype, offset, shape) into the rank's flat buffer."""
+    __slots__ = ("dtype", "off", "shape")
+
+    def __init__(self, dtype, off, shape):
+        self.dtype, self.off, self.shape = dtype, off, shape
+
+
+_PLANE_MIN_ELEMS = 16
+
+
+def gather_payloads(payload) -> List[Any]:
+    """All-gather of per-rank payloads (nested dicts / lists / tuples of samples) in two planes: the tensors in
+    them (token ids, per-token log-probs, ...) are concatenated per dtype into one flat buffer per rank and
+    exchanged with a tensor collective, everything else (a few scalars and strings per sample, and the
+    structure) is pickled.  The reference ships every stage output through Ray's object store
+    (chatlearn/runtime/executor.py:245-330); here what is pickled does not grow with the sequence length."""
+    if _world() == 1:
+        return [payload]
+    flats: Dict[torch.dtype, List[torch.Tensor]] = {}
+    sizes: Dict[torch.dtype, int] = {}
+
+    def strip(o):
+        if torch.is_tensor(o):
+            if o.device.type == "cpu" and o.numel() >= _PLANE_MIN_ELEMS and not o.is_sparse and o.layout == torch.strided:
+                off = sizes.get(o.dtype, 0)
+                flats.setdefault(o.dtype, []).append(o.detach().reshape(-1))
+                sizes[o.dtype] = off + o.numel()
+                return _TensorRef(o.dtype, off, tuple(o.shape))
+            return o
+        if isinstance(o, dict):
+            return {k: strip(v) for k, v in o.items()}
+        if isinstance(o, list):
+            return [strip(v) for v in o]
+        if isinstance(o, tuple):
+            return tuple(strip(v) for v in o)
+        return o
+
+    meta = strip(payload)
+    world = _world()
+    metas = all_gather_objects((meta, {str(k): (k, v) for k, v in sizes.items()}))
+    dtypes = {}
+    for _, sz in metas:
+        for name, (dt, n) in sz.items():
+            dtypes[name] = (dt, max(n, dtypes.get(name, (dt, 0))[1]))
+    gathered: Dict[torch.dtype, torch.Tensor] = {}
+    cuda = dist.get_backend() == "nccl"
+    for name in sorted(dtypes):                                # same order on every rank
+        dt, width = dtypes[name]
+        mine = torch.zeros(width, dtype=dt)
+        if dt in flats:
+            torch.cat(flats[dt], out=mine[:sizes[dt]])
+        if cuda:
+            from chatlearn_b200.utils import xfer
+            dev = torch.device("cuda", torch.cuda.current_device())
+            out = torch.empty(world * width, dtype=dt, device=dev)
+            dist.all_gather_into_tensor(out, mine.to(dev, non_blocking=True))
+            xfer.h2d_bytes += mine.numel() * mine.element_size()
+            xfer.d2h_bytes += out.numel() * out.element_size()
+            out = out.cpu()
+        else:
+            parts = [torch.empty(width, dtype=dt) for _ in range(world)]
+            dist.all_gather(parts, mine)
+            out = torch.cat(parts)
+        gathered[dt] = out.view(world, width)
+
+    def fill(o, r):
+        if isinstance(o, _TensorRef):
+            n = 1
+            for d in o.shape:
+                n *= d
+            return gathered[o.dtype][r, o.off:o.off + n].view(o.shape).clone()
+        if isinstance(o, dict):
+            return {k: fill(v, r) for k, v in o.items()}
+        if isinstance(o, list):
+            return [fill(v, r) for v in o]
+        if isinstance(o, tuple):
+            return tuple(fill(v, r) for v in o)
+        return o
+
+    return [fill(m, r) for r, (m, _) in enumerate(metas)]
+
+
 class Executor:
     def __init__(self, model_flow: Callable):
         self._flow_fn = model_flow
@@ -167,7 +250,7 @@ class Executor:
                 lead = model.is_member and model.is_data_leader
                 if not ins:
                     payload = (dp_rank, out) if lead else None
-                    parts = [p for p in all_gather_objects(payload) if p is not None]
+                    parts = [p for p in gather_payloads(payload) if p is not None]
                     parts.sort(key=lambda p: p[0])
                     results[node] = [s for _, lst in parts for s in lst]
                 else:
@@ -181,7 +264,7 @@ class Executor:
                             delta.append({k: v for k, v in o.items()
                                           if k not in b4 or b4[k] is not v})
                         payload = (dp_rank, delta, False) if lead else None
-                    parts = [p for p in all_gather_objects(payload) if p is not None]
+                    parts = [p for p in gather_payloads(payload) if p is not None]
                     parts.sort(key=lambda p: p[0])
                     if any(p[2] for p in parts):
                         results[node] = [s for _, lst, _ in parts for s in lst]

@@ -110,6 +110,34 @@ def test_grpo_loss(native):
     _close(ent.grad, ent2.grad, 1e-5, 1e-8)
 
 
+def test_gspo_loss(native):
+    """Group-sequence loss: every token of a packed sequence uses the sequence's mean log-ratio; value, statistics
+    and the gradients against the PyTorch statements."""
+    torch.manual_seed(31)
+    lens = [700, 1, 1300, 64, 2935]
+    n = sum(lens)
+    seq_ids = torch.repeat_interleave(torch.arange(len(lens), device=DEV), torch.tensor(lens, device=DEV))
+    lp = (-2 + torch.randn(n, device=DEV)).requires_grad_(True)
+    old = lp.detach() + 0.02 * torch.randn(n, device=DEV)
+    old[seq_ids == 3] -= 15.0                       # this sequence's mean exceeds the diff clip
+    refl = lp.detach() + 0.2 * torch.randn(n, device=DEV)
+    adv = torch.randn(len(lens), device=DEV)[seq_ids] * 3
+    mask = (torch.rand(n, device=DEV) > 0.3).float()
+    mask[seq_ids == 1] = 0.0                        # a sequence with no loss tokens at all
+    ent = torch.rand(n, device=DEV).requires_grad_(True)
+    kw = dict(pos_clip=3e-3, neg_clip=4e-3, diff_clip=10.0, final_clip=3.0, kl_coef=0.01, entropy_coef=0.02,
+              inv_norm=1.0 / 777)
+    t1, s1 = native.gspo_loss_fused(lp, old, refl, adv, mask, seq_ids, len(lens), ent, **kw)
+    t1.backward()
+    lp2, ent2 = lp.detach().clone().requires_grad_(True), ent.detach().clone().requires_grad_(True)
+    t2, s2 = ref.gspo_loss_fused(lp2, old, refl, adv, mask, seq_ids, len(lens), ent2, **kw)
+    t2.backward()
+    _close(t1, t2, 1e-4, 1e-5)
+    _close(s1, s2, 1e-4, 1e-2)
+    _close(lp.grad, lp2.grad, 1e-4, 1e-7)
+    _close(ent.grad, ent2.grad, 1e-5, 1e-8)
+
+
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_adamw_and_sumsq(native, out_dtype):
     torch.manual_seed(4)

@@ -59,3 +59,24 @@ def test_peer_memory_exchange_two_gpus():
     for key in ("all_gather_ok", "all_to_all_ok", "fallback_ok", "ulysses_ok"):
         assert r[key], (key, r)
     assert r["status"] == 0
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_parameter_sharded_state_two_gpus():
+    """FSDP2-style state (blocks pulled from the peers' parameter slices per segment, gradients reduce-scattered
+    by the pull kernel after every segment's backward) against the replicated state on NCCL."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests", "fsdp2_driver.py")],
+                       capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    lines = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")]
+    assert p.returncode == 0 and lines, p.stdout[-2000:] + p.stderr[-2000:]
+    r = json.loads(lines[-1][7:])
+    assert r["symm_pull"] and r["status"] == 0, r
+    for la, lb in r["loss"]:
+        assert abs(la - lb) < 2e-2 * max(1.0, abs(la)), r
+    for na, nb in r["norm"]:
+        assert abs(na - nb) < 2e-2 * max(1.0, abs(na)), r
+    # bf16 weights after two AdamW steps: a last-bit difference in a gradient moves an update by a bf16 ulp
+    assert r["param_diff"] < 2e-2 and r["param_mismatch_frac"] < 0.05, r
+    assert r["resident_param_bytes"] * 2 == r["whole_param_bytes"]

@@ -322,3 +322,30 @@ def test_latent_attention_matches_expanded_heads():
         o_lat = latent_paged_attention(q_lat, cache, lora, bt, sl, q_lens, 1 if q_lens is None else 3, 0.3)
         got = torch.einsum("thc,hvc->thv", o_lat, w_uv)
         assert torch.allclose(got, want, atol=1e-4, rtol=1e-4), float((got - want).abs().max())
+
+
+def test_gather_payloads_two_planes():
+    """Tensors of a payload travel as flat per-dtype buffers, the rest is pickled; every rank gets every payload."""
+    from tests.dist_utils import run_ranks
+    script = r'''
+import json, torch, torch.distributed as dist
+from chatlearn_b200.launcher.initialize import init_distributed
+from chatlearn_b200.runtime.executor import gather_payloads
+init_distributed()
+r = dist.get_rank()
+payload = None if r == 2 else (r, [{"uid": f"p{r}-{i}", "all_tokens": torch.arange(20 + r + i), "n": i,
+                                    "lp": torch.full((17 + i,), float(r)), "tiny": torch.tensor([r])} for i in range(3)], False)
+out = gather_payloads(payload)
+ok = out[2] is None and len(out) == 3
+for q in (0, 1):
+    rr, lst, flag = out[q]
+    ok &= rr == q and flag is False and len(lst) == 3
+    for i, s in enumerate(lst):
+        ok &= s["uid"] == f"p{q}-{i}" and s["n"] == i and torch.equal(s["all_tokens"], torch.arange(20 + q + i))
+        ok &= s["lp"].dtype == torch.float32 and torch.equal(s["lp"], torch.full((17 + i,), float(q))) and int(s["tiny"]) == q
+print("RESULT " + json.dumps({"ok": bool(ok)}))
+'''
+    outs, _ = run_ranks(script, 3)
+    import json as _json
+    res = [_json.loads(l[7:]) for o in outs for l in o.splitlines() if l.startswith("RESULT ")]
+    assert len(res) == 3 and all(r["ok"] for r in res)
