@@ -230,12 +230,11 @@ def main():
     algo = GrpoAlgorithm(cfg)
     algo.validate()
     engine = algo.build_engine()
+    engine.prepare()
     if args.impl == "library":
         import functools
         for role in ("policy_trainer", "ref_policy"):
-            m = engine.named_models.get(role) if hasattr(engine, "named_models") else None
-            if m is None:
-                continue
+            m = engine.named_models[role]          # (filled by prepare())
             for fn_name in ("forward_step", "train_step"):
                 fn = getattr(m, fn_name, None)
                 if fn is None:
@@ -245,7 +244,6 @@ def main():
                     with ops.mode("library"):
                         return _fn(*a, **k)
                 setattr(m, fn_name, functools.wraps(fn)(wrapped))
-    engine.prepare()
 
     def barrier():
         if dist.is_initialized() and dist.get_world_size() > 1:

@@ -34,7 +34,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from chatlearn_b200 import ops
-from chatlearn_b200.models.nn.model import CausalLM, decoder_layer, embed
+from chatlearn_b200.models.nn.model import CausalLM, decoder_layer, embed, flush_pending
 from .groups import Group
 from .zero import BlockState, ShardedTrainState
 
@@ -369,7 +369,12 @@ class ReshardedTrainState(ShardedTrainState):
         head = ["head"] + (["embed"] if arch.tie_word_embeddings else [])
 
         def run_head(h, lab):
-            h = ops.rmsnorm(h, m.final_norm_weight(), arch.rms_norm_eps)
+            if ctx.pending is not None:
+                # inference passes fuse every residual add into the next norm: the last layer's MLP output is
+                # still pending in the context and joins the stream here, inside the final norm
+                h = flush_pending(h, ctx, m.final_norm_weight(), arch.rms_norm_eps)
+            else:
+                h = ops.rmsnorm(h, m.final_norm_weight(), arch.rms_norm_eps)
             return ops.lmhead_logprob_entropy(h, m.lm_head_weight(), lab, temperature)
         return self._seg(head, run_head, (x, labels), grad)
 

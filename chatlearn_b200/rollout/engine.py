@@ -539,7 +539,10 @@ class RolloutEngine:
         overrides the per-request budget (partial rollout)."""
         self.alloc_kv_cache()
         eos_id = self.arch.eos_token_id if eos_id is None else eos_id
-        sched = Scheduler(self.num_blocks, self.block_size, self.max_num_seqs, self.max_tokens)
+        # requests with the same prompt (the samples of a GRPO group) share the prompt's KV blocks; not with
+        # recurrent layers, whose state is per sequence and cannot be adopted block-wise
+        share = self.arch.layer_types is None and os.environ.get("CLB200_PREFIX_SHARING", "1") != "0"
+        sched = Scheduler(self.num_blocks, self.block_size, self.max_num_seqs, self.max_tokens, prefix_sharing=share)
         seqs = []
         for i, p in enumerate(prompts):
             sp = sampling[i] if isinstance(sampling, (list, tuple)) else sampling

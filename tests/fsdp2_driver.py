@@ -50,6 +50,13 @@ for step in range(2):
         res["loss"].append((la.item(), lb.item()))
     na, nb = sa.step(), sb.step()
     res["norm"].append((float(na), float(nb)))
+# scoring pass as the trainer runs it: no tape, residual adds fused into the following norms
+with torch.no_grad():
+    lens = [90, 200]
+    toks = torch.randint(0, arch.vocab_size - 1, (sum(lens),), device=dev)
+    c1, _ = packed_ctx(lens, dev); c2, _ = packed_ctx(lens, dev)
+    c1.fuse_add_norm = c2.fuse_add_norm = True
+    res["score_diff"] = (ma.logprobs(toks, toks.roll(-1), c1)[0] - sb.logprobs(toks, toks.roll(-1), c2)[0]).abs().max().item()
 torch.cuda.synchronize()
 with sb.all_gathered() as whole:
     diffs = [(x.flat.float() - y.flat.float()).abs().max().item() for x, y in zip(ma.blocks, whole.blocks)]

@@ -349,3 +349,90 @@ print("RESULT " + json.dumps({"ok": bool(ok)}))
     import json as _json
     res = [_json.loads(l[7:]) for o in outs for l in o.splitlines() if l.startswith("RESULT ")]
     assert len(res) == 3 and all(r["ok"] for r in res)
+
+
+def _drive(sch, seqs, token=7, max_steps=2000):
+    for q in seqs:
+        sch.add(q)
+    steps = 0
+    while sch.has_work() and steps < max_steps:
+        plan = sch.schedule()
+        if plan is None:
+            break
+        for q, n, smp in zip(plan.seqs, plan.q_lens, plan.samples):
+            q.num_computed += n
+            if smp:
+                q.output.append(token)
+                if len(q.output) >= q.max_new_tokens:
+                    sch.finish(q, "length")
+        steps += 1
+    return steps
+
+
+def test_scheduler_shares_the_prompt_blocks_of_a_group():
+    """Eight samples of one prompt: one of them computes the prompt, the others adopt its full blocks by reference,
+    compute only the tail, and the pool is whole again at the end."""
+    from chatlearn_b200.rollout.scheduler import Scheduler, Sequence
+    bs = 4
+    prompts = [list(range(100, 100 + 22)), list(range(300, 300 + 9))]       # 5 and 2 full blocks
+    sch = Scheduler(num_blocks=200, block_size=bs, max_num_seqs=32, max_num_batched_tokens=64)
+    seqs = [Sequence(i, list(prompts[i // 8]), 6) for i in range(16)]
+    for q in seqs:
+        sch.add(q)
+    plan = sch.schedule()                                # the two owners start at position 0; everybody else waits
+    assert plan.is_prefill and [q.req_id for q in plan.seqs] == [0, 8]
+    for q, n in zip(plan.seqs, plan.q_lens):
+        q.num_computed += n
+        q.output.append(7)
+    plan = sch.schedule()                                # the adopters: continuation chunks over shared blocks
+    # (the second group's adopters have a single prompt token left: they join the running set and take it in
+    # the next decode step)
+    assert not plan.is_prefill and sorted(q.req_id for q in plan.seqs) == list(range(1, 8))
+    adopters = [q for q in seqs if q.req_id not in (0, 8)]
+    assert all(q in sch.running for q in adopters)
+    for q in adopters:
+        owner = seqs[0] if q.req_id < 8 else seqs[8]
+        n_shared = (len(q.prompt) - 1) // bs
+        assert q.blocks[:n_shared] == owner.blocks[:n_shared] and q.num_computed == n_shared * bs
+        assert not set(q.blocks[n_shared:]) & set(owner.blocks)
+    assert sch.stats["shared_prefix_tokens"] == 7 * 5 * bs + 7 * 2 * bs
+    used_with_sharing = sch.alloc.num_blocks - sch.alloc.num_free
+    for q, n, smp in zip(plan.seqs, plan.q_lens, plan.samples):
+        q.num_computed += n
+        if smp:
+            q.output.append(7)
+    _drive(sch, [])
+    assert all(q.finished and len(q.output) == 6 for q in seqs) and sch.alloc.num_free == 200 and not sch._prefix
+    # sixteen private copies of the prompts would hold 8 * 6 + 8 * 3 = 72 blocks at this point
+    assert used_with_sharing <= 6 + 7 + 3 + 7
+
+
+def test_prefix_sharing_survives_preemption_of_the_owner():
+    """A small pool: owners and adopters are preempted and recomputed; nothing is lost, no block leaks, and a block
+    whose owner was preempted before finishing it is never adopted."""
+    from chatlearn_b200.rollout.scheduler import Scheduler, Sequence
+    sch = Scheduler(num_blocks=14, block_size=4, max_num_seqs=8, max_num_batched_tokens=24)
+    seqs = [Sequence(i, list(range(50, 50 + 13)), 12) for i in range(6)]
+    steps = _drive(sch, seqs)
+    assert steps < 2000 and all(q.finished and len(q.output) == 12 for q in seqs)
+    assert sch.stats["preemptions"] > 0 and sch.alloc.num_free == 14 and not sch._prefix and not sch._block_key
+    assert all(r == 0 for r in sch.alloc._ref)
+
+
+def test_engine_generates_the_same_tokens_with_and_without_prefix_sharing(monkeypatch):
+    from chatlearn_b200.rollout import RolloutEngine, SamplingParams
+    arch = PRESETS["tiny_qwen3"]()
+    model = CausalLM(arch, dtype=torch.float32).init_weights(2)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, arch.vocab_size - 1, (n,), generator=g).tolist() for n in (37, 16, 9)]
+    batch = [p for p in prompts for _ in range(4)] + [prompts[0][:20] + [3, 4, 5]]     # groups, plus a partial overlap
+    outs = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("CLB200_PREFIX_SHARING", flag)
+        eng = RolloutEngine(model, block_size=8, num_blocks=128, max_num_seqs=16, max_model_len=128)
+        res = eng.generate(batch, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+        outs[flag] = [s.output for s in res]
+        shared = eng.stats.get("shared_prefix_tokens", 0)
+        assert (shared > 0) == (flag == "1")
+    assert outs["1"] == outs["0"]
+    assert all(outs["1"][i] == outs["1"][i - i % 4] for i in range(12))         # greedy: a group's samples agree
