@@ -95,6 +95,21 @@ def main():
                 rec(f"gemm_bf16_nt {M}x{N}x{K} (split-K off)", ms1, bytes_=2 * (M * K + N * K + M * N), flops=2.0 * M * N * K)
             assert native.C.gemm_last_status() == 0
             del a, b
+        # the backward layouts of the same layers over 16384 tokens: dx = dy W (NN), dW += dy^T x (TN, fp32 accumulate)
+        for (T, N, K) in [(16384, 6144, 4096), (16384, 24576, 4096), (16384, 4096, 12288)]:
+            dy = torch.randn(T, N, device=dev).bfloat16()
+            w = torch.randn(N, K, device=dev).bfloat16()
+            x = torch.randn(T, K, device=dev).bfloat16()
+            acc = torch.zeros(N, K, device=dev)
+            ms = timeit(lambda: native.C.gemm_bf16_nn(dy, w, False))
+            base = timeit(lambda: torch.mm(dy, w))
+            rec(f"gemm_bf16_nn dgrad {T}x{K}x{N}", ms, bytes_=2 * (T * N + N * K + T * K), flops=2.0 * T * N * K, base_ms=base)
+            ms = timeit(lambda: native.C.gemm_bf16_tn(dy, x, acc, True, True))
+            base = timeit(lambda: acc.add_(torch.mm(dy.t(), x)))
+            rec(f"gemm_bf16_tn wgrad+accumulate {N}x{K}x{T}", ms, bytes_=2 * (T * N + T * K) + 8 * N * K, flops=2.0 * T * N * K,
+                base_ms=base, note="library: cuBLAS mm + separate fp32 add")
+            assert native.C.gemm_last_status() == 0
+            del dy, w, x, acc
     if not only or "norm" in only:
         T, H = 16384, 4096
         x = torch.randn(T, H, device=dev).bfloat16()

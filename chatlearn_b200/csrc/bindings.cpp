@@ -16,6 +16,9 @@ std::vector<at::Tensor> grpo_loss_fwd(const at::Tensor& lp, const at::Tensor& ol
                                       const at::Tensor& mask, const c10::optional<at::Tensor>& ent,
                                       double pos_clip, double neg_clip, double diff_clip, double final_clip,
                                       double kl_coef, double ent_coef, double inv_norm);
+at::Tensor qkv_rope_append(const at::Tensor& qkv, int64_t nq, int64_t nkv, int64_t D, const c10::optional<at::Tensor>& qw,
+                           const c10::optional<at::Tensor>& kw, const at::Tensor& pos, const at::Tensor& inv_freq,
+                           const at::Tensor& slots, at::Tensor k_cache, at::Tensor v_cache, double eps);
 std::vector<at::Tensor> gspo_loss_fwd(const at::Tensor& lp, const at::Tensor& old, const c10::optional<at::Tensor>& ref,
                                       const at::Tensor& adv, const at::Tensor& mask, const c10::optional<at::Tensor>& ent,
                                       const at::Tensor& seq_ids, int64_t num_seqs, double pos_clip, double neg_clip,
@@ -114,6 +117,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
   m.def("grpo_loss_fwd", &grpo_loss_fwd);
   m.def("gspo_loss_fwd", &gspo_loss_fwd);
+  m.def("qkv_rope_append", &qkv_rope_append);
   m.def("adamw_step", &adamw_step);
   m.def("sumsq", &sumsq);
   m.def("logits_stats", &logits_stats);

@@ -328,6 +328,101 @@ static void launch_qk(const T* src, int src_stride, int n_heads, const T* w, con
     TORCH_CHECK(false, "qk_norm_rope: head dim must be 64 or 128");
 }
 
+// Inference with a paged KV cache: one launch does what three did.  For every token of the packed qkv rows
+// [T, (nq + 2 nkv) * D]: query heads get (RMSNorm and) RoPE and go to q_out [T, nq, D]; key heads get the same
+// and are stored straight into their cache slot; value heads are copied into theirs.  One warp per (token, head).
+// slots[t] < 0 skips the cache writes of a token (padding rows of a captured decode step).
+template <int D>
+__global__ void qkv_rope_append_kernel(const bf16* __restrict__ qkv, int row_stride, int nq, int nkv,
+                                       const bf16* __restrict__ qw, const bf16* __restrict__ kw,
+                                       const int64_t* __restrict__ pos, const float* __restrict__ inv_freq,
+                                       const int64_t* __restrict__ slots, bf16* __restrict__ q_out,
+                                       bf16* __restrict__ kc, bf16* __restrict__ vc, int64_t T_tokens, float eps) {
+  constexpr int HE = D / 64;
+  const int lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const int64_t wid = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  if (wid >= T_tokens * heads) return;
+  const int64_t t = wid / heads;
+  const int h = (int)(wid % heads);
+  const bf16* xr = qkv + t * row_stride + (int64_t)h * D;
+  if (h >= nq + nkv) {                                  // value head: plain copy into the cache slot
+    const int64_t slot = slots[t];
+    if (slot < 0) return;
+    bf16* o = vc + (slot * nkv + (h - nq - nkv)) * D;
+#pragma unroll
+    for (int j = 0; j < 2 * HE; ++j) o[lane + 32 * j] = xr[lane + 32 * j];
+    return;
+  }
+  const bool is_q = h < nq;
+  const bf16* w = is_q ? qw : kw;
+  bf16* o;
+  if (is_q) {
+    o = q_out + (t * nq + h) * D;
+  } else {
+    const int64_t slot = slots[t];
+    if (slot < 0) return;
+    o = kc + (slot * nkv + (h - nq)) * D;
+  }
+  const float p = (float)pos[t];
+  float a[HE], b[HE], ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < HE; ++j) {
+    a[j] = __bfloat162float(xr[lane + 32 * j]);
+    b[j] = __bfloat162float(xr[D / 2 + lane + 32 * j]);
+    ss += a[j] * a[j] + b[j] * b[j];
+  }
+  float r = 1.f;
+  if (w) {
+    ss = warp_sum(ss);
+    r = rsqrtf(ss / D + eps);
+  }
+#pragma unroll
+  for (int j = 0; j < HE; ++j) {
+    float sn, cs;
+    sincosf(p * inv_freq[lane + 32 * j], &sn, &cs);
+    const float wa = w ? __bfloat162float(w[lane + 32 * j]) : 1.f;
+    const float wb = w ? __bfloat162float(w[D / 2 + lane + 32 * j]) : 1.f;
+    // the normalised value is rounded to bf16 before the rotation, as the separate kernels do
+    const float na = w ? __bfloat162float(__float2bfloat16_rn(a[j] * r * wa)) : a[j];
+    const float nb = w ? __bfloat162float(__float2bfloat16_rn(b[j] * r * wb)) : b[j];
+    o[lane + 32 * j] = __float2bfloat16_rn(na * cs - nb * sn);
+    o[D / 2 + lane + 32 * j] = __float2bfloat16_rn(nb * cs + na * sn);
+  }
+}
+
+// qkv [T, (nq + 2 nkv) * D] bf16 (unit inner stride); caches [num_blocks, block, nkv, D] bf16; returns q_out [T, nq, D].
+at::Tensor qkv_rope_append(const at::Tensor& qkv, int64_t nq, int64_t nkv, int64_t D, const c10::optional<at::Tensor>& qw,
+                           const c10::optional<at::Tensor>& kw, const at::Tensor& pos, const at::Tensor& inv_freq,
+                           const at::Tensor& slots, at::Tensor k_cache, at::Tensor v_cache, double eps) {
+  TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.scalar_type() == at::kBFloat16 &&
+              qkv.size(1) == (nq + 2 * nkv) * D, "qkv_rope_append: qkv must be bf16 [T, (nq + 2 nkv) * D]");
+  TORCH_CHECK(k_cache.scalar_type() == at::kBFloat16 && v_cache.scalar_type() == at::kBFloat16 && k_cache.is_contiguous() &&
+              v_cache.is_contiguous() && k_cache.size(2) == nkv && k_cache.size(3) == D && v_cache.size(3) == D,
+              "qkv_rope_append: caches must be contiguous bf16 [blocks, block, nkv, D]");
+  TORCH_CHECK(pos.scalar_type() == at::kLong && slots.scalar_type() == at::kLong && inv_freq.scalar_type() == at::kFloat,
+              "qkv_rope_append: int64 positions and slots, fp32 inverse frequencies");
+  TORCH_CHECK(qw.has_value() == kw.has_value(), "qkv_rope_append: both norm weights or none");
+  const int64_t Tn = qkv.size(0);
+  auto q_out = at::empty({Tn, nq, D}, qkv.options());
+  if (Tn == 0) return q_out;
+  const int threads = 256;
+  const int64_t warps = Tn * (nq + 2 * nkv);
+  const int grid = (int)((warps * 32 + threads - 1) / threads);
+  const bf16* qwp = qw.has_value() ? (const bf16*)qw->data_ptr() : nullptr;
+  const bf16* kwp = kw.has_value() ? (const bf16*)kw->data_ptr() : nullptr;
+#define CLB_QRA(DD)                                                                                                      \
+  qkv_rope_append_kernel<DD><<<grid, threads, 0, cur_stream()>>>(                                                        \
+      (const bf16*)qkv.data_ptr(), (int)qkv.stride(0), (int)nq, (int)nkv, qwp, kwp, pos.data_ptr<int64_t>(),             \
+      inv_freq.data_ptr<float>(), slots.data_ptr<int64_t>(), (bf16*)q_out.data_ptr(), (bf16*)k_cache.data_ptr(),         \
+      (bf16*)v_cache.data_ptr(), Tn, (float)eps)
+  if (D == 128) CLB_QRA(128);
+  else if (D == 64) CLB_QRA(64);
+  else TORCH_CHECK(false, "qkv_rope_append: head dim must be 64 or 128");
+#undef CLB_QRA
+  return q_out;
+}
+
 // x: a [T, n_heads*D] slice (row stride may exceed n_heads*D: the packed qkv row).
 at::Tensor qk_norm_rope_fwd(const at::Tensor& x, int64_t n_heads, int64_t D, const c10::optional<at::Tensor>& w,
                             const at::Tensor& pos, const at::Tensor& inv_freq, double eps) {

@@ -225,6 +225,19 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
     else:
         qkv = ops.linear(x, p["qkv"], p.get("qkv_bias"))
         nkv_l = (qkv.shape[-1] // d - nh_l) // 2
+        if (ctx.kv is not None and not ctx.kv.prefill_only and ctx.mrope_positions is None and not torch.is_grad_enabled()
+                and (ctx.sp is None or ctx.sp.size == 1)):
+            # steps that attend over the paged cache (decode, continuation chunks): q/k norm + RoPE and the cache
+            # append are one kernel; the queries are all that comes back
+            kvc = ctx.kv
+            q = ops.qkv_rope_append(qkv, nh_l, nkv_l, d, p.get("q_norm"), p.get("k_norm"), arch.rms_norm_eps,
+                                    ctx.attn_positions if ctx.attn_positions is not None else ctx.positions,
+                                    arch.rope_theta, kvc.slot_mapping, kvc.k_cache[layer], kvc.v_cache[layer])
+            o = ops.paged_attention(q, kvc.k_cache[layer], kvc.v_cache[layer], kvc.block_tables, kvc.seq_lens,
+                                    kvc.q_lens, 1.0 / math.sqrt(d))
+            if partial:
+                return ctx.tp_symm.gemm_partial(o.reshape(o.shape[0], -1), p["o_proj"])
+            return _tp_reduce(ops.linear(o.reshape(o.shape[0], -1), p["o_proj"]), ctx)
         q = qkv[:, :nh_l * d].view(T, nh_l, d)
         k = qkv[:, nh_l * d:(nh_l + nkv_l) * d].view(T, nkv_l, d)
         v = qkv[:, (nh_l + nkv_l) * d:].view(T, nkv_l, d)

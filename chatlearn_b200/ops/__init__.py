@@ -88,6 +88,7 @@ linear = _dispatch("linear")
 rope = _dispatch("rope")
 rope_mrope = _dispatch("rope_mrope")
 qk_norm_rope = _dispatch("qk_norm_rope")
+qkv_rope_append = _dispatch("qkv_rope_append")
 attention_varlen = _dispatch("attention_varlen")
 attention_segments = _dispatch("attention_segments")
 kv_append = _dispatch("kv_append")

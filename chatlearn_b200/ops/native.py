@@ -174,6 +174,23 @@ def qk_norm_rope(q, k, qw, kw, eps, positions, theta):
     return (_NormRope.apply(q, qw, positions, theta, eps), _NormRope.apply(k, kw, positions, theta, eps))
 
 
+@torch.no_grad()
+def qkv_rope_append(qkv, nq, nkv, D, q_weight, k_weight, eps, positions, theta, slot_mapping, k_cache, v_cache):
+    """One kernel for q/k norm + RoPE and the cache append (see ``reference.qkv_rope_append``)."""
+    ok = (qkv.dtype == torch.bfloat16 and qkv.dim() == 2 and qkv.stride(1) == 1 and D in (64, 128)
+          and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16 and k_cache.is_contiguous()
+          and v_cache.is_contiguous() and k_cache.shape[-1] == D and v_cache.shape[-1] == D
+          and (q_weight is None) == (k_weight is None)
+          and (q_weight is None or (q_weight.dtype == torch.bfloat16 and k_weight.dtype == torch.bfloat16)))
+    if not ok:
+        library_counts["qkv_rope_append"] += 1
+        return ref.qkv_rope_append(qkv, nq, nkv, D, q_weight, k_weight, eps, positions, theta, slot_mapping, k_cache,
+                                   v_cache)
+    _count("qkv_rope_append")
+    return C.qkv_rope_append(qkv, nq, nkv, D, q_weight, k_weight, positions.to(torch.int64),
+                             _inv_freq(D, theta, qkv.device), slot_mapping.to(torch.int64), k_cache, v_cache, float(eps))
+
+
 def rope(x, positions, theta, rot_dim=None):
     if (rot_dim is not None and rot_dim != x.shape[-1]) or not _rope_ok(x):
         library_counts["rope"] += 1
@@ -527,7 +544,7 @@ def weight_sync_run(desc_table, num_descs, total_tiles, src_dtype, dst_dtype):
     _count("weight_sync")
 
 
-for _name, _fn in (("rmsnorm", rmsnorm), ("add_rmsnorm_", add_rmsnorm_), ("swiglu", swiglu), ("qk_norm_rope", qk_norm_rope), ("rope", rope),
+for _name, _fn in (("rmsnorm", rmsnorm), ("add_rmsnorm_", add_rmsnorm_), ("swiglu", swiglu), ("qk_norm_rope", qk_norm_rope), ("qkv_rope_append", qkv_rope_append), ("rope", rope),
                    ("linear", linear), ("lmhead_logprob_entropy", lmhead_logprob_entropy),
                    ("grpo_loss_fused", grpo_loss_fused), ("gspo_loss_fused", gspo_loss_fused), ("adamw_step", adamw_step), ("sumsq", sumsq),
                    ("sample", sample), ("apply_penalties", apply_penalties), ("kv_append", kv_append),

@@ -124,6 +124,19 @@ def _library_varlen(q, k, v, cu_seqlens, max_seqlen, scale):
     return st["fn"](q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens.to(torch.int32), int(max_seqlen), scale)
 
 
+def qkv_rope_append(qkv, nq, nkv, D, q_weight, k_weight, eps, positions, theta, slot_mapping, k_cache, v_cache):
+    """Inference with a paged cache: split the packed ``qkv [T, (nq + 2 nkv) D]`` rows, apply the per-head RMSNorm
+    (when weights are given) and RoPE to queries and keys, store keys and values into their cache slots and return
+    the queries ``[T, nq, D]``."""
+    T = qkv.shape[0]
+    q = qkv[:, :nq * D].view(T, nq, D)
+    k = qkv[:, nq * D:(nq + nkv) * D].view(T, nkv, D)
+    v = qkv[:, (nq + nkv) * D:].view(T, nkv, D)
+    q, k = qk_norm_rope(q, k, q_weight, k_weight, eps, positions, theta)
+    kv_append(k, v, k_cache, v_cache, slot_mapping)
+    return q
+
+
 def attention_varlen(q, k, v, cu_seqlens, max_seqlen=None, scale=None, causal=True):
     """Packed (varlen) attention.  ``q [T,nq,dq]``, ``k [T,nkv,dq]``,
     ``v [T,nkv,dv]``, ``cu_seqlens [B+1]``; segments attend only to themselves."""

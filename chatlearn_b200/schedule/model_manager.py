@@ -109,6 +109,9 @@ class ModelManager:
         for m in self.local_models:
             m.placement = self.placements[m.name]
             m.role_rank = m.placement.index(me) if me in m.placement else -1
+            # the role's bundles (ranks per node, with the node's share of CPU cores): what the reference keeps as
+            # a Ray placement group per model
+            self.resource_manager.reserve(m.name, m.placement)
         return self.local_models
 
     # ------------------------------------------------------------------ parameter sync

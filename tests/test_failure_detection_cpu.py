@@ -57,3 +57,32 @@ def test_wedged_rank_is_found_by_its_heartbeat():
 def test_silent_exit_code():
     err, _ = _run("if rank == 0:\n    os._exit(3)\ndist.barrier()\n")
     assert err is not None and "exit code 3" in err
+
+
+def test_log_lines_of_all_nodes_reach_node_zero(tmp_path):
+    """Two "nodes" tail their rank logs and publish through a key-value store; node 0 shows both, with node and rank
+    prefixes, keeps the error-like lines, and ordinary lines beyond the rate limit stay local."""
+    from datetime import timedelta
+
+    from torch.distributed import TCPStore
+
+    from chatlearn_b200.utils.log_monitor import LogMonitor, StoreLogCollector, StoreLogPublisher
+    from chatlearn_b200.utils.utils import get_free_port
+    port = get_free_port()
+    server = TCPStore("127.0.0.1", port, None, True, timeout=timedelta(seconds=20), wait_for_workers=False)
+    client = TCPStore("127.0.0.1", port, None, False, timeout=timedelta(seconds=20), wait_for_workers=False)
+    dirs = [tmp_path / "n0", tmp_path / "n1"]
+    for d in dirs:
+        d.mkdir()
+    (dirs[0] / "rank0.log").write_text("step 1 ok\n")
+    (dirs[1] / "rank5.log").write_text("step 1 ok\nRuntimeError: CUDA error: an illegal memory access\n" + "noise\n" * 100)
+    mons = [LogMonitor(str(dirs[0]), sink=StoreLogPublisher(server, 0, max_lines_per_s=5)),
+            LogMonitor(str(dirs[1]), sink=StoreLogPublisher(client, 1, max_lines_per_s=5))]
+    seen = []
+    col = StoreLogCollector(server, 2, sink=seen.append)
+    for m in mons:
+        m.poll()
+    col.poll()
+    assert "(node0:rank0) step 1 ok" in seen and "(node1:rank5) step 1 ok" in seen
+    assert any("illegal memory access" in e and e.startswith("(node1:rank5)") for e in col.errors)
+    assert sum("noise" in s for s in seen) <= 5

@@ -279,3 +279,23 @@ def test_weight_sync_kernel_local(native):
         torch.cuda.synchronize()
         for a, b in zip(dst.blocks, want.blocks):
             assert torch.equal(a.flat, b.flat), a.name
+
+
+@pytest.mark.parametrize("with_norm", [True, False])
+def test_qkv_rope_append_matches_the_separate_kernels(native, with_norm):
+    """q/k norm + RoPE + cache append in one launch against the three statements it replaces."""
+    torch.manual_seed(41)
+    T, nq, nkv, D, bs, nb = 37, 8, 2, 128, 16, 12
+    qkv = torch.randn(T, (nq + 2 * nkv) * D, device=DEV).bfloat16()
+    qw = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16() if with_norm else None
+    kw = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16() if with_norm else None
+    pos = torch.randint(0, 4000, (T,), device=DEV)
+    slots = torch.randperm(nb * bs, device=DEV)[:T]
+    slots[5] = -1                                            # a row whose cache writes are skipped
+    caches = [[torch.zeros(nb, bs, nkv, D, device=DEV, dtype=torch.bfloat16) for _ in range(2)] for _ in range(2)]
+    q1 = native.qkv_rope_append(qkv, nq, nkv, D, qw, kw, 1e-6, pos, 1e6, slots, caches[0][0], caches[0][1])
+    keep = slots >= 0
+    q2 = ref.qkv_rope_append(qkv[keep], nq, nkv, D, qw, kw, 1e-6, pos[keep], 1e6, slots[keep], caches[1][0], caches[1][1])
+    _close(q1[keep], q2, 2e-2, 2e-2)
+    _close(caches[0][0], caches[1][0], 2e-2, 2e-2)
+    assert torch.equal(caches[0][1], caches[1][1])

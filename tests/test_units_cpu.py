@@ -436,3 +436,34 @@ def test_engine_generates_the_same_tokens_with_and_without_prefix_sharing(monkey
         assert (shared > 0) == (flag == "1")
     assert outs["1"] == outs["0"]
     assert all(outs["1"][i] == outs["1"][i - i % 4] for i in range(12))         # greedy: a group's samples agree
+
+
+def test_resource_manager_bundles(monkeypatch):
+    """Placement groups over ranks: a role that fits a node is packed on one node, a larger one takes whole nodes,
+    nothing is handed out twice, and removed groups return their ranks."""
+    from chatlearn_b200.schedule.resource_manager import ResourceManager
+    monkeypatch.setenv("GPUS_PER_NODE", "4")
+    rm = ResourceManager()
+    rm.world_size, rm.total_gpu = 12, 12
+    rm.nnode = 3
+    from chatlearn_b200.schedule.resource_manager import NodeInfo
+    rm._nodes = [NodeInfo(i, f"host{i}", list(range(4 * i, 4 * i + 4)), cpus=32, free=list(range(4 * i, 4 * i + 4)))
+                 for i in range(3)]
+    a = rm.create_placement_group(2, name="reward")
+    assert a.ranks == [0, 1] and a.bundle_specs == [{"GPU": 2, "CPU": 16}]
+    b = rm.create_placement_group(2, name="ref")                           # PACK: fills node 0 before opening node 1
+    assert b.ranks == [2, 3]
+    c = rm.create_placement_group(8, name="policy")                        # larger than a node: whole nodes
+    assert c.ranks == list(range(4, 12)) and [x["GPU"] for x in c.bundle_specs] == [4, 4]
+    with pytest.raises(RuntimeError):
+        rm.create_placement_group(1)
+    d = rm.create_placement_group(0, num_cpus=[4, 4], name="managers")
+    assert d.ranks == [] and d.bundle_specs == [{"GPU": 0, "CPU": 4}, {"GPU": 0, "CPU": 4}]
+    assert rm.model_to_placegroup["policy"] is c and rm.get_placement_group_state(c) == "CREATED"
+    rm.remove_placement_groups()
+    assert all(len(n.free) == 4 for n in rm._nodes) and c.state == "REMOVED"
+    s1 = rm.create_placement_group(1, strategy="SPREAD")
+    s2 = rm.create_placement_group(1, strategy="SPREAD")
+    assert rm.node_of(s1.ranks[0]) != rm.node_of(s2.ranks[0])
+    e = rm.reserve("colocated", [5, 6, 9])
+    assert [x.node for x in e.bundles] == [1, 2] and 5 not in rm._nodes[1].free
