@@ -52,17 +52,12 @@ struct __align__(1024) SmemLayoutT {
   uint64_t empty[kStages];
   uint64_t acc_full[kAccBufs];
   uint64_t acc_empty[kAccBufs];
-  uint64_t epi_sync;              // the four epilogue warps among themselves (split-K: ticket and hand-over)
-  int last_slice;                 // split-K: this CTA stored the last k-slice of its tile and adds the planes
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
 using SmemLayout = SmemLayoutT<BN>;
 
 __device__ int g_gemm_status = 0;
-// split-K: one ticket counter per output tile (fewer tiles than SMs whenever K is sliced).  The CTA that draws the
-// last ticket of a tile adds the planes and puts the counter back to zero for the next launch.
-__device__ int g_splitk_tickets[1024];
 bool g_allow_splitk = true;
 int g_force_bn = 0;       // 0: choose the tile width per shape
 
@@ -190,7 +185,6 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
     for (int b = 0; b < kAccBufs; ++b) { mbar_init(&sm->acc_full[b], 1); mbar_init(&sm->acc_empty[b], 4); }
-    mbar_init(&sm->epi_sync, 4);
     sm->abort_flag = 0;
     fence_barrier_init();
   }
@@ -272,16 +266,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else {
     // ------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
-    uint32_t acc = 0, acc_phase = 0, epi_phase = 0;
+    uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    // rendezvous of the four epilogue warps (bounded, like every wait here)
-    auto epi_barrier = [&]() -> bool {
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm->epi_sync);
-      const bool done = mbar_wait(&sm->epi_sync, epi_phase);
-      epi_phase ^= 1;
-      return done;
-    };
     for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
       int m0, n0, b0, row_end;
       unit_origin(grp, unit % num_tiles, tiles_m, tiles_n, M, m0, n0, b0, row_end, BN);
@@ -313,8 +299,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 store_row32<OutT>(static_cast<OutT*>(grp.peer_out[p]) + (int64_t)row * ldc + col, r, min(32, N - col));
             }
           } else {
-            // every k-slice writes its partial tile to its own plane of the workspace (plain stores); the
-            // planes are added below by whichever CTA stores a tile's last slice, always in slice order
+            // every k-slice writes its partial tile to its own plane of the workspace;
+            // the finalize kernel adds the planes (plain stores: no atomics, deterministic)
             float* w = ws + ((int64_t)(unit / num_tiles) * M + row) * N + col;
             store_row32<float>(w, r, min(32, N - col));
           }
@@ -324,58 +310,6 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm->acc_empty[acc]);
       if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1; }
-      if (splits > 1) {
-        // K is sliced: this CTA's partial tile is in its plane of the workspace.  Whoever stores the last slice of
-        // a tile adds the planes (in slice order, so the sum does not depend on who that is) and writes C: no
-        // second kernel, and the addition overlaps the main loops still running on other SMs.
-        const int tile = unit % num_tiles;
-        __threadfence();                                        // this warp's plane rows are visible device-wide ...
-        if (!epi_barrier()) { ok = false; break; }              // ... and so are the other three warps'
-        if (warp == 2 && lane == 0) {
-          const int ticket = atomicAdd(&g_splitk_tickets[tile], 1);
-          sm->last_slice = (ticket == splits - 1) ? 1 : 0;
-          if (ticket == splits - 1) g_splitk_tickets[tile] = 0; // nobody else touches it before the next launch
-        }
-        if (!epi_barrier()) { ok = false; break; }
-        if (sm->last_slice) {
-          __threadfence();
-          if (row < row_end) {
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-              const int col = n0 + c;
-              if (col >= N) break;
-              const int ncols = min(32, N - col);
-              uint32_t r[32];
-#pragma unroll
-              for (int j = 0; j < 32; ++j) r[j] = 0u;
-              for (int sl = 0; sl < splits; ++sl) {
-                const float* w = ws + ((int64_t)sl * M + row) * N + col;
-                if (ncols == 32) {
-#pragma unroll
-                  for (int v = 0; v < 8; ++v) {
-                    const float4 x = __ldcg(reinterpret_cast<const float4*>(w) + v);   // written by other SMs: read through L2
-                    r[4 * v] = __float_as_uint(__uint_as_float(r[4 * v]) + x.x);
-                    r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + x.y);
-                    r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + x.z);
-                    r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + x.w);
-                  }
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 32; ++j)
-                    if (j < ncols) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(w + j));
-                }
-              }
-              if constexpr (sizeof(OutT) == 4) {
-                if (grp.accumulate) add_row32(C + (int64_t)row * ldc + col, r, ncols);
-                else store_row32<OutT>(C + (int64_t)row * ldc + col, r, ncols);
-              } else {
-                store_row32<OutT>(C + (int64_t)row * ldc + col, r, ncols);
-              }
-            }
-          }
-        }
-        if (!epi_barrier()) { ok = false; break; }              // last_slice is rewritten for the next unit only after all have read it
-      }
     }
     if (!ok && lane == 0) { atomicCAS(&g_gemm_status, ST_OK, ST_EPILOGUE_TIMEOUT); atomicExch(&sm->abort_flag, 1u); }
   }
@@ -384,6 +318,32 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Split-K epilogue: C = sum over the k-slice planes of the workspace.
+template <typename OutT>
+__global__ void splitk_finalize_kernel(const float* __restrict__ ws, OutT* __restrict__ C, int64_t n, int splits,
+                                       int accumulate = 0) {
+  for (int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(ws + i);
+    if constexpr (sizeof(OutT) == 4) {
+      if (accumulate) {
+        const float4 c = *reinterpret_cast<const float4*>(C + i);
+        v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+      }
+    }
+    for (int s = 1; s < splits; ++s) {
+      const float4 u = *reinterpret_cast<const float4*>(ws + (int64_t)s * n + i);
+      v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+    }
+    if constexpr (sizeof(OutT) == 2) {
+      __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+      uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+      *reinterpret_cast<uint2*>(C + i) = pk;
+    } else {
+      *reinterpret_cast<float4*>(C + i) = v;
+    }
   }
 }
 
@@ -531,11 +491,11 @@ static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int a
         const int waves = (tiles * s + num_sms - 1) / num_sms;
         // the longer of: all operand bytes at device bandwidth, one SM's tile loads at the rate a
         // single SM sustains from L2 (activation tiles are re-read there); then, if K is sliced,
-        // the partial planes written and re-read (by the CTA that stores a tile's last slice) plus a small fixed charge
+        // the partial planes written and re-read plus a fixed charge for the extra launch
         const double hbm = ((double)N * K + (double)M * K) * 2 / 6.5e12;
         const double sm = (double)waves * per * (BM + cand) * BK * 2 / 90e9;
         double cost = std::max(hbm, sm);
-        if (s > 1) cost += 2.0 * s * M * N * 4 / 6.5e12 + 1.0e-6;
+        if (s > 1) cost += 2.0 * s * M * N * 4 / 6.5e12 + 3.5e-6;
         if (cost < best) { best = cost; bn = cand; splits = s; }
       }
     }
@@ -565,6 +525,7 @@ static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int a
     ga.n_peer = (int)peer_out->size();
     for (int i = 0; i < ga.n_peer; ++i) ga.peer_out[i] = reinterpret_cast<void*>((*peer_out)[i]);
   }
+  const int fgrid = (int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8);
 #define CLB_GEMM_ARGS(PTR) dev, grid, st, tmA, tmB, PTR, ws, (int)M, (int)N, (int)K, (int)N, splits, ga
   if (out_fp32) {
     float* p = c.data_ptr<float>();
@@ -573,7 +534,10 @@ static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int a
     else if (bn == 256) launch_gemm<float, 256, 0, 0>(CLB_GEMM_ARGS(p));
     else if (bn == 128) launch_gemm<float, 128, 0, 0>(CLB_GEMM_ARGS(p));
     else launch_gemm<float, 64, 0, 0>(CLB_GEMM_ARGS(p));
-
+    if (splits > 1) {
+      splitk_finalize_kernel<float><<<fgrid, 256, 0, st>>>(ws, p, M * N, splits, ga.accumulate);
+      C10_CUDA_KERNEL_LAUNCH_CHECK();
+    }
   } else {
     bf16* p = (bf16*)c.data_ptr();
     if (amn && bmn) launch_gemm<bf16, 256, 1, 1>(CLB_GEMM_ARGS(p));
@@ -581,7 +545,10 @@ static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int a
     else if (bn == 256) launch_gemm<bf16, 256, 0, 0>(CLB_GEMM_ARGS(p));
     else if (bn == 128) launch_gemm<bf16, 128, 0, 0>(CLB_GEMM_ARGS(p));
     else launch_gemm<bf16, 64, 0, 0>(CLB_GEMM_ARGS(p));
-
+    if (splits > 1) {
+      splitk_finalize_kernel<bf16><<<fgrid, 256, 0, st>>>(ws, p, M * N, splits, 0);
+      C10_CUDA_KERNEL_LAUNCH_CHECK();
+    }
   }
 #undef CLB_GEMM_ARGS
   GTRACE("launched");
@@ -821,13 +788,15 @@ extern "C" int clb200_gemm_bf16_nt_noalloc(const void* a, const void* b, void* c
   const int grid = std::min(tiles * splits, d.num_sms);
   const size_t smem = sizeof(SmemLayout) + 1024;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t mn = (int64_t)M * N;
+  const int fgrid = (int)std::min<int64_t>((mn / 4 + 255) / 256, 148 * 8);
   (void)cudaGetLastError();      // an error left behind by an earlier, unrelated call must not be blamed on these launches
   if (out_fp32) {
     gemm_bf16_nt_kernel<float><<<grid, kThreads, smem, st>>>(tmA, tmB, static_cast<float*>(c), d.scratch, M, N, K, N, splits, GroupArgs{});
-
+    if (splits > 1) splitk_finalize_kernel<float><<<fgrid, 256, 0, st>>>(d.scratch, static_cast<float*>(c), mn, splits, 0);
   } else {
     gemm_bf16_nt_kernel<bf16><<<grid, kThreads, smem, st>>>(tmA, tmB, static_cast<bf16*>(c), d.scratch, M, N, K, N, splits, GroupArgs{});
-
+    if (splits > 1) splitk_finalize_kernel<bf16><<<fgrid, 256, 0, st>>>(d.scratch, static_cast<bf16*>(c), mn, splits, 0);
   }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return noalloc_fail(8, "kernel launch failed: error %lld", (long long)e);

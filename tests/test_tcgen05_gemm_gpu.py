@@ -33,9 +33,9 @@ def test_gemm_tcgen05(native, M, N, K, out_fp32):
 
 
 def test_gemm_splitk_is_deterministic_in_shape(native):
-    """Small-M problems take the split-K path (fp32 partial planes in a workspace, added inside the kernel by the
-    CTA that stores a tile's last slice, always in slice order): two calls in a row must agree bit for bit with
-    each other and, within bf16 rounding, with fp32."""
+    """Small-M problems take the split-K path (fp32 partial planes in a workspace, added in slice order by the
+    finalize kernel): two calls in a row must agree bit for bit with each other and, within bf16 rounding,
+    with fp32."""
     torch.manual_seed(11)
     a = (torch.randn(64, 4096, device=DEV) * 0.5).bfloat16()
     b = (torch.randn(4096, 4096, device=DEV) * 0.5).bfloat16()
