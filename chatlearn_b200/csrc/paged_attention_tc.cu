@@ -74,7 +74,8 @@ __global__ void __launch_bounds__(kThreads)
 paged_decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                        const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ q_seq,
                        const int* __restrict__ ctx_len, bf16* __restrict__ out, float* __restrict__ part_o,
-                       float* __restrict__ part_lse, int nq, int nkv, int num_splits, float scale) {
+                       float* __restrict__ part_lse, int nq, int nkv, int num_splits, float scale,
+                       const int* __restrict__ blk_start = nullptr, int slot_base = 0, int total_slots = 0) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   auto* sm = reinterpret_cast<SmemTC<DK, DV>*>(smem_raw);
   const int qi = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -82,8 +83,12 @@ paged_decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, 
   const int seq = q_seq ? q_seq[qi] : qi;
   const int L = ctx_len[qi];
   const int nblk = (L + BS - 1) / BS;
-  const int per = (nblk + num_splits - 1) / num_splits;
-  const int b0 = split * per, b1 = min(b0 + per, nblk);
+  // grouped mode: the first `first` blocks of this sequence are attended by the shared-prefix kernel; this kernel
+  // covers the rest and writes its partial results behind the prefix slots
+  const int first = blk_start ? blk_start[qi] : 0;
+  const int per = (nblk - first + num_splits - 1) / num_splits;
+  const int b0 = first + split * per, b1 = min(b0 + per, nblk);
+  if (total_slots == 0) total_slots = num_splits;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int* bt = block_tables + (int64_t)seq * max_blocks;
@@ -202,12 +207,194 @@ paged_decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, 
     }
     const int head = kvh * rep + r;
     const float val = den > 0.f ? num / den : 0.f;
-    if (num_splits == 1) {
+    if (total_slots == 1) {
       out[((int64_t)qi * nq + head) * DV + d] = __float2bfloat16_rn(val);
     } else {
-      part_o[(((int64_t)qi * nq + head) * num_splits + split) * DV + d] = val;
-      if (d == 0) part_lse[((int64_t)qi * nq + head) * num_splits + split] = den > 0.f ? M + logf(den) : -INFINITY;
+      const int64_t at = ((int64_t)qi * nq + head) * total_slots + slot_base + split;
+      part_o[at * DV + d] = val;
+      if (d == 0) {
+        part_lse[at] = den > 0.f ? M + logf(den) : -INFINITY;
+        // a sequence outside every group has no prefix pass: its prefix slots must not count
+        if (split == 0 && first == 0)
+          for (int sl = 0; sl < slot_base; ++sl) part_lse[((int64_t)qi * nq + head) * total_slots + sl] = -INFINITY;
+      }
     }
+  }
+}
+
+// Shared-prefix pass of the decode attention.
+//
+// Sequences that adopted the same prompt blocks form a group.  One CTA per (group, KV head, split) attends the
+// queries of ALL members (up to 8 members x `rep` query heads = up to 32 MMA rows, two m16 tiles) over the
+// group's shared blocks, so those K/V bytes are read once per group instead of once per member.  The result
+// goes out as partial (o, lse) into slot `split` of the members' rows; the per-sequence kernel covers the
+// remaining blocks into the following slots and the combine kernel merges all slots by log-sum-exp.
+template <int DK, int DV>
+struct SmemPrefix {
+  bf16 k[2][BS][DK + kPad];
+  bf16 v[2][BS][DV + kPad];
+  bf16 q[32][DK + kPad];
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(kThreads)
+paged_prefix_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+                       const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ grp_q,
+                       const int* __restrict__ grp_nblk, float* __restrict__ part_o, float* __restrict__ part_lse,
+                       int nq, int nkv, int num_splits, int total_slots, float scale) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  auto* sm = reinterpret_cast<SmemPrefix<DK, DV>*>(smem_raw);
+  const int grp = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int nblk = grp_nblk[grp];
+  if (nblk <= 0) return;                                  // unused group slot of the captured grid
+  const int rep = nq / nkv;
+  const int rows = 8 * rep;                               // <= 32 (rep <= 4)
+  const int per = (nblk + num_splits - 1) / num_splits;
+  const int b0 = split * per, b1 = min(b0 + per, nblk);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int* members = grp_q + grp * 8;
+  const int lead = members[0];                            // the first member's block table row holds the shared blocks
+  const int* bt = block_tables + (int64_t)lead * max_blocks;
+  if (b0 >= b1) {                                         // nothing for this split: its slot must not count
+    for (int idx = tid; idx < rows; idx += kThreads) {
+      const int qi = members[idx / rep];
+      if (qi >= 0) part_lse[((int64_t)qi * nq + kvh * rep + idx % rep) * total_slots + split] = -INFINITY;
+    }
+    return;
+  }
+  // Q tile: row R = member * rep + head-in-group; rows of absent members are zero
+  for (int i = tid; i < 32 * (DK / 8); i += kThreads) {
+    const int r = i / (DK / 8), o = (i % (DK / 8)) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < rows) {
+      const int qi = members[r / rep];
+      if (qi >= 0) v = *reinterpret_cast<const uint4*>(q + ((int64_t)qi * nq + kvh * rep + r % rep) * DK + o);
+    }
+    *reinterpret_cast<uint4*>(&sm->q[r][o]) = v;
+  }
+  load_tile_tc<DK, DV>(reinterpret_cast<SmemTC<DK, DV>*>(sm), 0, kc, vc, bt[b0], kvh, nkv, BS);
+  __pipeline_commit();
+  __syncthreads();
+  uint32_t qa[2][DK / 16][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int ks = 0; ks < DK / 16; ++ks) ldmatrix_x4(qa[mt][ks], &sm->q[mt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+
+  float o_acc[2][DV / 8][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) { o_acc[mt][n][0] = o_acc[mt][n][1] = o_acc[mt][n][2] = o_acc[mt][n][3] = 0.f; }
+  float m_run[2][2], l_run[2][2];                          // [m tile][row g / row g + 8] of this warp's stream
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) { m_run[mt][0] = m_run[mt][1] = -INFINITY; l_run[mt][0] = l_run[mt][1] = 0.f; }
+  const int tw = warp * 16;
+
+  for (int b = b0; b < b1; ++b) {
+    const int st = (b - b0) & 1;
+    if (b + 1 < b1) load_tile_tc<DK, DV>(reinterpret_cast<SmemTC<DK, DV>*>(sm), st ^ 1, kc, vc, bt[b + 1], kvh, nkv, BS);
+    __pipeline_commit();
+    __pipeline_wait_prior(1);
+    __syncthreads();
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      float s[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ks += 2) {
+          uint32_t kb[4];
+          ldmatrix_x4(kb, &sm->k[st][tw + j * 8 + (lane & 7)][ks * 16 + (lane >> 3) * 8]);
+          mma_bf16(s[j], qa[mt][ks], kb[0], kb[1]);
+          mma_bf16(s[j], qa[mt][ks + 1], kb[2], kb[3]);
+        }
+      }
+      uint32_t pa[4];
+      float alpha[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {                         // h = 0: row g (accumulator slots 0, 1); h = 1: row g + 8 (slots 2, 3)
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          s[j][2 * h] *= scale; s[j][2 * h + 1] *= scale;
+          mx = fmaxf(mx, fmaxf(s[j][2 * h], s[j][2 * h + 1]));
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[mt][h], mx);        // finite: whole blocks, every key is valid
+        alpha[h] = __expf(m_run[mt][h] - m_new);
+        const float p00 = __expf(s[0][2 * h] - m_new), p01 = __expf(s[0][2 * h + 1] - m_new);
+        const float p10 = __expf(s[1][2 * h] - m_new), p11 = __expf(s[1][2 * h + 1] - m_new);
+        l_run[mt][h] = l_run[mt][h] * alpha[h] + (p00 + p01 + p10 + p11);
+        m_run[mt][h] = m_new;
+        pa[h] = pack_bf16(p00, p01);                        // a0 / a1: tokens 2t, 2t+1
+        pa[2 + h] = pack_bf16(p10, p11);                    // a2 / a3: tokens 8+2t, 8+2t+1
+      }
+#pragma unroll
+      for (int n = 0; n < DV / 8; n += 2) {
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, &sm->v[st][tw + ((lane >> 3) & 1) * 8 + (lane & 7)][(n + (lane >> 4)) * 8]);
+        o_acc[mt][n][0] *= alpha[0]; o_acc[mt][n][1] *= alpha[0]; o_acc[mt][n][2] *= alpha[1]; o_acc[mt][n][3] *= alpha[1];
+        o_acc[mt][n + 1][0] *= alpha[0]; o_acc[mt][n + 1][1] *= alpha[0]; o_acc[mt][n + 1][2] *= alpha[1]; o_acc[mt][n + 1][3] *= alpha[1];
+        mma_bf16(o_acc[mt][n], pa, vb[0], vb[1]);
+        mma_bf16(o_acc[mt][n + 1], pa, vb[2], vb[3]);
+      }
+    }
+    __syncthreads();
+  }
+  __pipeline_wait_prior(0);
+  __syncthreads();
+  // ---- merge the 4 per-warp streams (the K and V rings are scratch now) ----
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      l_run[mt][h] += __shfl_xor_sync(0xffffffffu, l_run[mt][h], 1);
+      l_run[mt][h] += __shfl_xor_sync(0xffffffffu, l_run[mt][h], 2);
+    }
+  float* red_o = reinterpret_cast<float*>(&sm->k[0][0][0]);           // [4 warps][32 rows][DV]
+  float* red_m = red_o + 4 * 32 * DV;                                  // [4][32]
+  float* red_l = red_m + 4 * 32;                                       // [4][32]
+  static_assert(sizeof(float) * (4 * 32 * DV + 256) <= sizeof(bf16) * 2 * BS * (DK + kPad + DV + kPad), "scratch fits in the rings");
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) {
+      float* lo = red_o + (warp * 32 + mt * 16 + g) * DV + n * 8 + 2 * t;
+      lo[0] = o_acc[mt][n][0]; lo[1] = o_acc[mt][n][1];
+      float* hi = lo + 8 * DV;
+      hi[0] = o_acc[mt][n][2]; hi[1] = o_acc[mt][n][3];
+    }
+  if (t == 0) {
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        red_m[warp * 32 + mt * 16 + g + 8 * h] = m_run[mt][h];
+        red_l[warp * 32 + mt * 16 + g + 8 * h] = l_run[mt][h];
+      }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rows * DV; idx += kThreads) {
+    const int r = idx / DV, d = idx % DV;
+    const int qi = members[r / rep];
+    if (qi < 0) continue;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w * 32 + r]);
+    float den = 0.f, num = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float e = __expf(red_m[w * 32 + r] - M);
+      den += e * red_l[w * 32 + r];
+      num += e * red_o[(w * 32 + r) * DV + d];
+    }
+    const int64_t at = ((int64_t)qi * nq + kvh * rep + r % rep) * total_slots + split;
+    part_o[at * DV + d] = den > 0.f ? num / den : 0.f;
+    if (d == 0) part_lse[at] = den > 0.f ? M + logf(den) : -INFINITY;
   }
 }
 
@@ -258,6 +445,56 @@ void launch_tc(const at::Tensor& q, const at::Tensor& kc, const at::Tensor& vc, 
 }
 
 }  // namespace
+
+// Decode attention with shared prefixes (head dim 128, one query token per sequence).  grp_q [G, 8] int32: the
+// query rows of each group's members (-1 = no member); grp_nblk [G] int32: blocks the members share (0 = unused
+// group slot); blk_start [T] int32: blocks of every sequence that the prefix pass covers (0 outside a group).
+at::Tensor paged_decode_tc_grouped(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
+                                   const at::Tensor& block_tables, const at::Tensor& ctx_len, const at::Tensor& grp_q,
+                                   const at::Tensor& grp_nblk, const at::Tensor& blk_start, double scale,
+                                   int64_t prefix_splits, int64_t suffix_splits) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.is_contiguous(), "paged_decode_tc_grouped: bf16 contiguous q");
+  const int nq = (int)q.size(1), dk = (int)q.size(2);
+  const int bs = (int)k_cache.size(1), nkv = (int)k_cache.size(2), dv = (int)v_cache.size(3);
+  const int rep = nq / nkv;
+  TORCH_CHECK(dk == 128 && dv == 128 && bs == BS && rep >= 1 && rep <= 4, "paged_decode_tc_grouped: head dim 128, 64-token blocks, at most 4 query heads per KV head");
+  TORCH_CHECK(grp_q.scalar_type() == at::kInt && grp_q.dim() == 2 && grp_q.size(1) == 8 && grp_q.is_contiguous() &&
+              grp_nblk.scalar_type() == at::kInt && grp_nblk.numel() == grp_q.size(0) && blk_start.scalar_type() == at::kInt &&
+              blk_start.numel() == q.size(0), "paged_decode_tc_grouped: int32 group tables");
+  const int Tq = (int)q.size(0), G = (int)grp_q.size(0);
+  auto out = at::empty({q.size(0), nq, dv}, q.options());
+  if (Tq == 0) return out;
+  const int np = (int)std::max<int64_t>(prefix_splits, 1), nsx = (int)std::max<int64_t>(suffix_splits, 1);
+  const int slots = np + nsx;
+  auto po = at::empty({Tq, nq, slots, dv}, q.options().dtype(at::kFloat));
+  auto pl = at::empty({Tq, nq, slots}, q.options().dtype(at::kFloat));
+  auto st = at::cuda::getCurrentCUDAStream();
+  const int dev = q.get_device();
+  static bool configured[64] = {};
+  TORCH_CHECK(dev >= 0 && dev < 64, "paged_decode_tc_grouped: device index out of range");
+  if (!configured[dev]) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(paged_prefix_tc_kernel<128, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)sizeof(SmemPrefix<128, 128>)));
+    C10_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_tc_kernel<128, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)sizeof(SmemTC<128, 128>)));
+    configured[dev] = true;
+  }
+  if (G > 0) {
+    paged_prefix_tc_kernel<128, 128><<<dim3(G, nkv, np), kThreads, sizeof(SmemPrefix<128, 128>), st>>>(
+        (const bf16*)q.data_ptr(), (const bf16*)k_cache.data_ptr(), (const bf16*)v_cache.data_ptr(), block_tables.data_ptr<int>(),
+        (int)block_tables.size(1), grp_q.data_ptr<int>(), grp_nblk.data_ptr<int>(), po.data_ptr<float>(), pl.data_ptr<float>(),
+        nq, nkv, np, slots, (float)scale);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+  }
+  paged_decode_tc_kernel<128, 128><<<dim3(Tq, nkv, nsx), kThreads, sizeof(SmemTC<128, 128>), st>>>(
+      (const bf16*)q.data_ptr(), (const bf16*)k_cache.data_ptr(), (const bf16*)v_cache.data_ptr(), block_tables.data_ptr<int>(),
+      (int)block_tables.size(1), nullptr, ctx_len.data_ptr<int>(), (bf16*)out.data_ptr(), po.data_ptr<float>(), pl.data_ptr<float>(),
+      nq, nkv, nsx, (float)scale, blk_start.data_ptr<int>(), np, slots);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  combine_splits_tc_kernel<128><<<Tq * nq, 128, 0, st>>>(po.data_ptr<float>(), pl.data_ptr<float>(), (bf16*)out.data_ptr(), slots);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
 
 bool paged_decode_tc_supported(int64_t dk, int64_t dv, int64_t bs, int64_t rep) {
   const bool dims = (dk == 128 && dv == 128) || (dk == 64 && dv == 64) || (dk == 192 && dv == 128);

@@ -137,6 +137,7 @@ class KVCtx:
     seq_lens: torch.Tensor                 # [B] lengths including the new tokens
     q_lens: Optional[torch.Tensor] = None  # [B] new tokens per sequence (None → 1 each)
     prefill_only: bool = False             # all sequences start at position 0 → varlen kernel
+    groups: Any = None                     # decode steps: (group members, shared blocks per group, per-sequence first private block): sequences sharing their prompt blocks
     lin: Any = None                        # models.nn.hybrid.LinearState: conv / recurrent state of gated delta-net layers
 
 
@@ -234,7 +235,7 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
                                     ctx.attn_positions if ctx.attn_positions is not None else ctx.positions,
                                     arch.rope_theta, kvc.slot_mapping, kvc.k_cache[layer], kvc.v_cache[layer])
             o = ops.paged_attention(q, kvc.k_cache[layer], kvc.v_cache[layer], kvc.block_tables, kvc.seq_lens,
-                                    kvc.q_lens, 1.0 / math.sqrt(d))
+                                    kvc.q_lens, 1.0 / math.sqrt(d), groups=kvc.groups)
             if partial:
                 return ctx.tp_symm.gemm_partial(o.reshape(o.shape[0], -1), p["o_proj"])
             return _tp_reduce(ops.linear(o.reshape(o.shape[0], -1), p["o_proj"]), ctx)
@@ -263,7 +264,7 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
             o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, scale)
         else:
             o = ops.paged_attention(q, kv.k_cache[layer], kv.v_cache[layer], kv.block_tables,
-                                    kv.seq_lens, kv.q_lens, scale)
+                                    kv.seq_lens, kv.q_lens, scale, groups=kv.groups)
     elif ctx.cp is not None and ctx.cp.size > 1:
         o = ctx.cp.attention(q, k, v, ctx, scale)
     else:

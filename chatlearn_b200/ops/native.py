@@ -503,7 +503,7 @@ def _num_splits(n_ctas: int, max_ctx_blocks: int) -> int:
 
 
 @torch.no_grad()
-def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens=None, scale=None):
+def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens=None, scale=None, groups=None):
     nb, bs, nkv, dk = k_cache.shape
     dv = v_cache.shape[-1]
     nq = q.shape[1]
@@ -518,6 +518,14 @@ def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens=None, sc
         return ref.paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens, scale)
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     sl = seq_lens.to(torch.int32)
+    if (groups is not None and (q_lens is None or q.shape[0] == sl.shape[0]) and _DECODE_IMPL == "tc"
+            and dk == 128 and dv == 128 and bs == 64 and nq // nkv <= 4):
+        # sequences that adopted the same prompt blocks: the shared blocks are attended once per group (all members'
+        # queries as rows of one MMA tile), the rest per sequence, merged by log-sum-exp
+        grp_q, grp_nblk, blk_start = groups
+        _count("paged_decode_grouped", 3)
+        return C.paged_decode_tc_grouped(q.contiguous(), k_cache, v_cache, block_tables.to(torch.int32).contiguous(), sl,
+                                         grp_q, grp_nblk, blk_start, float(scale), 2, 1)
     if q_lens is None or q.shape[0] == sl.shape[0]:
         q_seq, ctx = None, sl
     else:

@@ -202,10 +202,12 @@ def kv_append(k, v, k_cache, v_cache, slot_mapping):
     v_cache.view(nb * bs, *v_cache.shape[2:])[slots] = v[ok].to(v_cache.dtype)
 
 
-def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens=None, scale=None):
+def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens=None, scale=None, groups=None):
     """Attention of new queries against a paged KV cache (keys of the new tokens
     already appended).  ``q [Tq, nq, d]`` holds ``q_lens[b]`` trailing query
-    tokens of each sequence ``b`` (1 each for decode); causal inside the tail."""
+    tokens of each sequence ``b`` (1 each for decode); causal inside the tail.
+    ``groups`` (which sequences share their first blocks) is a hint for the kernels:
+    it changes how the work is split, not the result, and is ignored here."""
     B = seq_lens.shape[0]
     nb, bs, nkv, dk = k_cache.shape
     nq = q.shape[1]

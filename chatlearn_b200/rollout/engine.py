@@ -310,7 +310,14 @@ class RolloutEngine:
                             u=z(torch.float32, n), ids=z(torch.long, n), lp=z(torch.float32, n),
                             stage=torch.zeros(4, n, dtype=torch.int64, pin_memory=True),
                             bt_host=torch.zeros(n, width, dtype=torch.int32, pin_memory=True),
-                            bt_len=[0] * n, bt_owner=[None] * n)
+                            bt_len=[0] * n, bt_owner=[None] * n,
+                            # sequences that share their first KV blocks (the samples of one prompt): up to n / 2
+                            # groups of up to 8 rows each, the shared block count per group, and per row the first
+                            # block that is its own
+                            grp_q=torch.full((max(n // 2, 1), 8), -1, dtype=torch.int32, device=dev),
+                            grp_nblk=z(torch.int32, max(n // 2, 1)), blk_start=z(torch.int32, n),
+                            grp_stage=torch.zeros(max(n // 2, 1) * 9 + n, dtype=torch.int32, pin_memory=True),
+                            grp_key=None)
             if self.arch.layer_types is not None:
                 # recurrent-state layers: the state slot of every row (decode rows never start fresh)
                 self._gs.update(lin_slots=z(torch.long, n), lin_fresh=z(torch.bool, n),
@@ -326,6 +333,8 @@ class RolloutEngine:
     def _decode_body(self, B: int, sp):
         gs = self._gs
         kv = KVCtx(self.k_cache, self.v_cache, gs["slots"][:B], gs["bt"][:B], gs["seq_lens"][:B], None, False)
+        if gs.get("use_groups"):
+            kv.groups = (gs["grp_q"][:max(B // 2, 1)], gs["grp_nblk"][:max(B // 2, 1)], gs["blk_start"][:B])
         if self.arch.layer_types is not None:
             from chatlearn_b200.models.nn.hybrid import LinearState
             kv.lin = LinearState(self.lin_conv, self.lin_rec, gs["lin_slots"][:B], gs["lin_fresh"][:B])
@@ -368,6 +377,7 @@ class RolloutEngine:
                 gs["bt"][i, first:nb].copy_(gs["bt_host"][i, first:nb], non_blocking=True)
                 xfer.h2d_bytes += (nb - first) * 4
                 owner[i], blen[i] = who, nb
+        grouped = self._update_groups(gs, seqs, Bg)
         for i in range(B, Bg):
             if owner[i] != "pad":
                 gs["bt_host"][i, 0] = scratch_block
@@ -384,7 +394,8 @@ class RolloutEngine:
         xfer.h2d_bytes += st.numel() * 8
         gs["u"][:Bg].copy_(torch.rand(Bg, device=self.device, generator=self.gen))
         sp = seqs[0].sampling
-        key = (Bg, sp.key())
+        key = (Bg, sp.key(), grouped)
+        gs["use_groups"] = grouped
         g = self._graphs.get(key)
         if g is None:
             # warm-up on a side stream, then capture
@@ -406,6 +417,54 @@ class RolloutEngine:
             self._graphs[key] = g
         g.replay()
         return gs["ids"][:B], gs["lp"][:B]
+
+    def _update_groups(self, gs, seqs, Bg: int) -> bool:
+        """Which rows of the decode batch share their first KV blocks (prefix sharing gave the samples of a prompt the
+        same physical blocks): the decode attention then reads those blocks once per group.  The tables only change
+        when the batch does; they are rebuilt and uploaded then.  Returns whether any group exists."""
+        if self.arch.use_mla or self.arch.layer_types is not None or not seqs:
+            return False
+        rep = self.arch.num_attention_heads // max(self.arch.num_key_value_heads, 1)
+        if self.arch.head_dim != 128 or self.block_size != 64 or rep > 4 or os.environ.get("CLB200_GROUPED_DECODE", "1") == "0":
+            return False
+        sig = tuple((id(s), s.preemptions) for s in seqs)
+        if gs["grp_key"] == (sig, Bg):
+            return gs["grp_any"]
+        by_first = {}
+        for i, s in enumerate(seqs):
+            if s.blocks:
+                by_first.setdefault(s.blocks[0], []).append(i)
+        G = max(Bg // 2, 1)
+        st = gs["grp_stage"]
+        st.zero_()
+        gq = st[:G * 8].view(G, 8)
+        gq.fill_(-1)
+        gn, bstart = st[G * 8:G * 9], st[G * 9:G * 9 + Bg]
+        g = 0
+        for rows in by_first.values():
+            for c in range(0, len(rows), 8):
+                part = rows[c:c + 8]
+                if len(part) < 2 or g >= G:
+                    continue
+                lists = [seqs[i].blocks for i in part]
+                n = 0                                   # blocks common to all members, always leaving each its last one
+                limit = min(len(b) for b in lists) - 1
+                while n < limit and all(b[n] == lists[0][n] for b in lists):
+                    n += 1
+                if n == 0:
+                    continue
+                gq[g, :len(part)] = torch.tensor(part, dtype=torch.int32)
+                gn[g] = n
+                for i in part:
+                    bstart[i] = n
+                g += 1
+        dev_view = G * 9 + Bg
+        gs["grp_q"][:G].copy_(st[:G * 8].view(G, 8), non_blocking=True)
+        gs["grp_nblk"][:G].copy_(gn, non_blocking=True)
+        gs["blk_start"][:Bg].copy_(bstart, non_blocking=True)
+        xfer.h2d_bytes += dev_view * 4
+        gs["grp_key"], gs["grp_any"] = (sig, Bg), g > 0
+        return g > 0
 
     def _can_graph(self, plan: StepPlan) -> bool:
         if not self.use_graphs or self.device.type != "cuda" or plan.is_prefill:

@@ -299,3 +299,60 @@ def test_qkv_rope_append_matches_the_separate_kernels(native, with_norm):
     _close(q1[keep], q2, 2e-2, 2e-2)
     _close(caches[0][0], caches[1][0], 2e-2, 2e-2)
     assert torch.equal(caches[0][1], caches[1][1])
+
+
+def test_grouped_decode_attention_matches_the_per_sequence_kernel(native):
+    """Sequences whose block tables start with the same blocks: the shared blocks attended once per group plus the
+    per-sequence remainder, merged by log-sum-exp, must equal the per-sequence kernel over the whole context."""
+    import math
+    torch.manual_seed(51)
+    nq, nkv, d, bs = 8, 2, 128, 64
+    groups = [(5, 4, [70, 1, 130, 64, 200]), (3, 8, [10, 500, 65, 3, 90, 64, 1, 129]), (2, 0, [300, 77])]   # (shared blocks, -, suffix tokens)
+    singles = [100, 640]
+    tables, ctx, members = [], [], []
+    nb_total = 0
+    for shared, _, tails in groups:
+        base = list(range(nb_total, nb_total + shared))
+        nb_total += shared
+        rows = []
+        for tail in tails:
+            own = math.ceil(tail / bs)
+            tables.append(base + list(range(nb_total, nb_total + own)))
+            nb_total += own
+            ctx.append(shared * bs + tail)
+            rows.append(len(tables) - 1)
+        members.append((rows, shared))
+    for n in singles:
+        own = math.ceil(n / bs)
+        tables.append(list(range(nb_total, nb_total + own)))
+        nb_total += own
+        ctx.append(n)
+    B, width = len(tables), max(len(t) for t in tables)
+    bt = torch.zeros(B, width, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = torch.tensor(t)
+    perm = torch.randperm(nb_total + 3).int()                      # physical block ids in no particular order
+    bt = perm[bt.long()].to(DEV)
+    kc = torch.randn(nb_total + 3, bs, nkv, d, device=DEV).bfloat16()
+    vc = torch.randn(nb_total + 3, bs, nkv, d, device=DEV).bfloat16()
+    q = torch.randn(B, nq, d, device=DEV).bfloat16()
+    sl = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    G = 6
+    grp_q = torch.full((G, 8), -1, dtype=torch.int32)
+    grp_nblk = torch.zeros(G, dtype=torch.int32)
+    blk_start = torch.zeros(B, dtype=torch.int32)
+    g = 1                                                          # leave group slot 0 unused on purpose
+    for rows, shared in members:
+        if shared == 0:
+            continue
+        grp_q[g, :len(rows)] = torch.tensor(rows, dtype=torch.int32)
+        grp_nblk[g] = shared
+        blk_start[rows] = shared
+        g += 1
+    scale = 1 / math.sqrt(d)
+    want = native.C.paged_decode_tc(q, kc, vc, bt, None, sl, scale, 1)
+    for np_, ns_ in ((1, 1), (2, 1), (3, 2)):
+        got = native.C.paged_decode_tc_grouped(q, kc, vc, bt, sl, grp_q.to(DEV), grp_nblk.to(DEV), blk_start.to(DEV), scale, np_, ns_)
+        _close(got, want, 2e-2, 2e-2)
+    ref_out = ref.paged_attention(q, kc, vc, bt, sl, None, scale)
+    _close(want, ref_out, 2e-2, 2e-2)

@@ -68,3 +68,30 @@ def test_grpo_tiny_one_gpu(tmp_path):
     res = [json.loads(l[7:]) for l in out.stdout.splitlines() if l.startswith("RESULT ")]
     assert res and res[0]["episodes"] == 2 and res[0]["maxdiff"] < 1e-2
     assert res[0]["native_launches"] > 0
+
+
+def test_grouped_decode_gives_the_same_generations(monkeypatch):
+    """Samples of one prompt share their prompt blocks; the captured decode step then attends the shared blocks once
+    per group.  Greedy generations must not depend on it."""
+    from chatlearn_b200.models.nn import ModelArch, CausalLM
+    from chatlearn_b200.rollout import RolloutEngine, SamplingParams
+    dev = torch.device("cuda", 0)
+    arch = ModelArch(model_type="qwen3", vocab_size=2048, hidden_size=512, num_hidden_layers=2, num_attention_heads=8,
+                     num_key_value_heads=2, head_dim=128, intermediate_size=1024, rope_theta=1e6)
+    model = CausalLM(arch, dtype=torch.bfloat16, device=dev).init_weights(3)
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, arch.vocab_size - 1, (n,), generator=g).tolist() for n in (200, 333, 70)]
+    batch = [p for p in prompts for _ in range(8)] + [prompts[0][:150]]
+    outs, launches = {}, {}
+    from chatlearn_b200 import ops
+    for flag in ("1", "0"):
+        monkeypatch.setenv("CLB200_GROUPED_DECODE", flag)
+        eng = RolloutEngine(model, block_size=64, num_blocks=256, max_num_seqs=32, max_model_len=512)
+        before = ops.launch_counts["paged_decode_grouped"]
+        res = eng.generate(batch, SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True))
+        outs[flag] = [s.output for s in res]
+        launches[flag] = ops.launch_counts["paged_decode_grouped"] - before
+        assert eng.stats.get("shared_prefix_tokens", 0) > 0
+    assert launches["1"] > 0 and launches["0"] == 0
+    agree = sum(a[:8] == b[:8] for a, b in zip(outs["1"], outs["0"]))
+    assert agree >= len(batch) - 2, (agree, len(batch))           # bf16 near-ties may flip a greedy choice late in a sequence
