@@ -152,7 +152,10 @@ def build_config(args, out_dir, data_path, n_gpu):
             "enable_resume_training": False, "log_args_dict": {"log_dir": out_dir}},
         "models": {
             "policy_trainer": dict(common, num_gpu=n_gpu, fsdp_size=n_gpu, trainable=True,
-                                   generation_batch_size=spe, kl_coef=0.001, gradient_checkpointing=True, checkpoint_layers="auto",
+                                   generation_batch_size=spe, kl_coef=0.001, gradient_checkpointing=True,
+                                   # the library statements save more per layer than the estimate behind
+                                   # "auto" assumes (they ran out of memory with it): every layer recomputes
+                                   checkpoint_layers="all" if args.impl == "library" else "auto",
                                    optimizer={"lr": 2e-6}, save_hf=False, reshard_after_forward=bool(args.reshard),
                                    # fp32 master + Adam shards stay on the GPU (180 GB HBM); the fp32
                                    # gradient buffer is released outside training
@@ -322,6 +325,7 @@ def main():
                        "prompts": samples // args.samples_per_prompt, "samples_per_prompt": args.samples_per_prompt,
                        "prompt_len": args.prompt_len, "max_response": args.max_response,
                        "pack_tokens": args.pack_tokens, "mini_batches_per_step": 2,
+                       "activation_recompute": "every layer" if args.impl == "library" else "as many layers kept as fit (auto)",
                        "ignore_eos": True, "response_len": "every response runs to max_response (random weights)",
                        "l2_policy": "inputs larger than L2 (16 GB of weights + KV streamed every step)",
                        "gemm": __import__("chatlearn_b200.ops.native", fromlist=["x"]).get_gemm_impl() if args.impl == "native" else "cublas"},
