@@ -39,6 +39,9 @@ class RolloutConfig(BaseModelConfig):
     enforce_eager: bool = False
     kv_block_size: int = 64
     max_num_seqs: int = 256
+    # agent tasks: "continuous" = every model turn is its own request in an open engine session (a trajectory's
+    # next turn joins the running batch as soon as its tools return); "lockstep" = one batched call per round
+    agent_scheduling: str = "continuous"
 
 
 @dataclass

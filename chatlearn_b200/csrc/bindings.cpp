@@ -46,6 +46,8 @@ bool paged_decode_tc_supported(int64_t dk, int64_t dv, int64_t bs, int64_t rep);
 at::Tensor paged_decode_tc(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
                            const at::Tensor& block_tables, const c10::optional<at::Tensor>& q_seq,
                            const at::Tensor& ctx_len, double scale, int64_t num_splits);
+at::Tensor mla_paged_decode(const at::Tensor& q, const at::Tensor& cache, const at::Tensor& block_tables,
+                            const at::Tensor& ctx_len, double scale, int64_t num_splits);
 at::Tensor paged_decode_tc_grouped(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
                                    const at::Tensor& block_tables, const at::Tensor& ctx_len, const at::Tensor& grp_q,
                                    const at::Tensor& grp_nblk, const at::Tensor& blk_start, double scale,
@@ -134,6 +136,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("paged_decode_tc_supported", &paged_decode_tc_supported);
   m.def("paged_decode_tc", &paged_decode_tc);
   m.def("paged_decode_tc_grouped", &paged_decode_tc_grouped);
+  m.def("mla_paged_decode", &mla_paged_decode);
   m.def("weight_sync_run", &weight_sync_run);
   m.def("weight_sync_desc_size", &weight_sync_desc_size);
   m.def("weight_sync_tile_elems", &weight_sync_tile_elems);

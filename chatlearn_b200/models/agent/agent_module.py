@@ -3,11 +3,15 @@
 Parity: chatlearn/models/agent/agent_module.py:27-120 (graph registry,
 ``generate_per_request``, ``postprocess_func`` field names).  The reference runs one
 coroutine per request against an async SGLang server.  Here every trajectory is a
-generator (see ``chat_model``); ``forward_step`` advances all of them until each
-waits for the model, answers all waiting requests with ONE continuous-batching call
-of the rollout engine, and repeats until every graph has finished.  Tools run
-between turns on the replica's first tensor-parallel rank and their results are
-broadcast, so side effects happen once and all ranks stay in lock-step.
+generator (see ``chat_model``) and the engine is driven through an open session
+(``rollout/engine.py::RolloutSession``): each model turn is submitted as its own
+request, the engine steps, and a trajectory whose request finished in that step runs
+its tools and submits its next turn before the next step: it joins the running batch
+without waiting for the other trajectories' turns (``agent_scheduling: continuous``,
+the default).  ``agent_scheduling: lockstep`` answers all waiting requests with one
+batched call per round instead.  Tools run on the replica's first tensor-parallel
+rank; the requests it submits are broadcast so that all ranks of the replica feed
+their engines the same way.
 """
 from typing import Any, Dict, List, Type
 
@@ -72,6 +76,50 @@ class AgentModule(RolloutModule):
         dist.broadcast_object_list(box, src=self.tp_group.ranks[0], group=self.tp_group.pg)
         return box[0]
 
+    def _request_args(self, r: LLMRequest, base: SamplingParams):
+        ma = self.module_args
+        over = {k: v for k, v in r.sampling_params.items() if hasattr(base, k)}
+        sp = SamplingParams(**{**base.__dict__, **over})
+        mx = int(r.sampling_params.get("max_new_tokens", sp.max_tokens))
+        return sp, max(0, min(mx, ma.seq_length - len(r.token_ids)))
+
+    def _run_continuous(self, gens, waiting, done, is_eval: bool, multi: bool, lead: bool):
+        """Open-session scheduling: ``waiting`` holds the first request of every trajectory (on the lead rank)."""
+        base = self._sampling_params(is_eval, self.module_args.max_response_tokens_length)
+        with_images = self.engine.vision is not None
+        sess = self.engine.open_session()
+        owner: Dict[int, int] = {}                    # request id -> trajectory
+        fresh = [(i, waiting[i]) for i in sorted(waiting)] if lead else []
+        self.agent_stats = {"requests": 0, "engine_steps": 0, "joined_running_batch": 0}
+        while True:
+            if multi:
+                # one small broadcast per step tells the other ranks whether requests follow
+                import torch.distributed as dist
+                n = torch.tensor([len(fresh)], dtype=torch.int32, device=self.engine.device)
+                dist.broadcast(n, src=self.tp_group.ranks[0], group=self.tp_group.pg)
+                fresh = self._sync_objects(fresh if lead else None) if int(n.item()) else []
+            for i, r in fresh:
+                sp, budget = self._request_args(r, base)
+                if sess.sched.running:
+                    self.agent_stats["joined_running_batch"] += 1
+                seq = sess.submit(r.token_ids, sp, budget, r.mm if with_images else None)
+                owner[seq.req_id] = i
+                self.agent_stats["requests"] += 1
+            finished = sess.poll()
+            if finished is None:
+                break
+            self.agent_stats["engine_steps"] += 1
+            fresh = []
+            for q in finished:
+                i = owner.pop(q.req_id)
+                if not lead:
+                    continue
+                try:
+                    fresh.append((i, gens[i].send(LLMResponse(list(q.output), list(q.logprobs), q.finish_reason))))
+                except StopIteration as e:
+                    done[i] = e.value
+        sess.close()
+
     def run_trajectories(self, data_list: List[Dict], is_eval: bool = False) -> List[AgentGraphOutput]:
         ma = self.module_args
         sampling = {"max_new_tokens": ma.max_response_tokens_length}
@@ -90,6 +138,9 @@ class AgentModule(RolloutModule):
                     waiting[i] = next(g)
                 except StopIteration as e:
                     done[i] = e.value
+        if str(getattr(ma, "agent_scheduling", "continuous")) == "continuous":
+            self._run_continuous(gens, waiting, done, is_eval, multi, lead)
+            waiting = {}
         while True:
             order = sorted(waiting)
             reqs = self._sync_objects([waiting[i] for i in order] if lead else None) if multi \

@@ -211,9 +211,13 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
                 lora = arch.kv_lora_rank
                 w_kvb = p["kv_b_proj"].view(nh_l, nope + dv, lora)
                 q_lat = torch.cat([torch.einsum("thn,hnc->thc", q[..., :nope], w_kvb[:, :nope]), q_rope], dim=-1)
-                from .mla import latent_paged_attention
-                o_lat = latent_paged_attention(q_lat, kc, lora, kvc.block_tables, kvc.seq_lens, kvc.q_lens,
-                                               int(ctx.max_seqlen) if kvc.q_lens is not None else 1, scale)
+                if kvc.q_lens is None or q_lat.shape[0] == kvc.seq_lens.shape[0]:
+                    # decode rows: one kernel reads every cached row once for all heads
+                    o_lat = ops.mla_paged_decode(q_lat.contiguous(), kc, lora, kvc.block_tables, kvc.seq_lens, scale)
+                else:
+                    from .mla import latent_paged_attention
+                    o_lat = latent_paged_attention(q_lat, kc, lora, kvc.block_tables, kvc.seq_lens, kvc.q_lens,
+                                                   int(ctx.max_seqlen), scale)
                 o = torch.einsum("thc,hvc->thv", o_lat.to(x.dtype), w_kvb[:, nope:])
                 out = o.reshape(T, nh_l * dv)
                 if partial:

@@ -93,6 +93,7 @@ attention_varlen = _dispatch("attention_varlen")
 attention_segments = _dispatch("attention_segments")
 kv_append = _dispatch("kv_append")
 paged_attention = _dispatch("paged_attention")
+mla_paged_decode = _dispatch("mla_paged_decode")
 lmhead_logprob_entropy = _dispatch("lmhead_logprob_entropy")
 grpo_loss_fused = _dispatch("grpo_loss_fused")
 gspo_loss_fused = _dispatch("gspo_loss_fused")

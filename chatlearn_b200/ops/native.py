@@ -546,6 +546,18 @@ def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens=None, sc
               ctx.contiguous(), float(scale), ns)
 
 
+def mla_paged_decode(q, k_cache, lora, block_tables, seq_lens, scale):
+    """Latent-attention decode on the tensor-core kernel (latent 512 + rotary 64, 64-row blocks, bf16); other
+    shapes run the batched statements."""
+    D = q.shape[-1]
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or lora != 512 or D != 576 or k_cache.shape[1] != 64:
+        library_counts["mla_paged_decode"] += 1
+        return ref.mla_paged_decode(q, k_cache, lora, block_tables, seq_lens, scale)
+    _count("mla_decode")
+    return C.mla_paged_decode(q.contiguous(), k_cache, block_tables.to(torch.int32).contiguous(),
+                              seq_lens.to(torch.int32).contiguous(), float(scale), 0)
+
+
 # ------------------------------------------------------------------ weight sync kernel
 def weight_sync_run(desc_table, num_descs, total_tiles, src_dtype, dst_dtype):
     C.weight_sync_run(desc_table, num_descs, total_tiles, src_dtype, dst_dtype)
@@ -556,7 +568,7 @@ for _name, _fn in (("rmsnorm", rmsnorm), ("add_rmsnorm_", add_rmsnorm_), ("swigl
                    ("linear", linear), ("lmhead_logprob_entropy", lmhead_logprob_entropy),
                    ("grpo_loss_fused", grpo_loss_fused), ("gspo_loss_fused", gspo_loss_fused), ("adamw_step", adamw_step), ("sumsq", sumsq),
                    ("sample", sample), ("apply_penalties", apply_penalties), ("kv_append", kv_append),
-                   ("paged_attention", paged_attention)):
+                   ("paged_attention", paged_attention), ("mla_paged_decode", mla_paged_decode)):
     register_native(_name, _fn)
 
 from . import native_moe  # noqa: E402,F401  (registers the mixture-of-experts ops)

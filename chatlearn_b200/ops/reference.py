@@ -202,6 +202,14 @@ def kv_append(k, v, k_cache, v_cache, slot_mapping):
     v_cache.view(nb * bs, *v_cache.shape[2:])[slots] = v[ok].to(v_cache.dtype)
 
 
+def mla_paged_decode(q, k_cache, lora, block_tables, seq_lens, scale):
+    """Decode step of multi-head latent attention in the absorbed form: ``q`` [B, heads, lora + rope] (one query
+    token per sequence) against the paged latent cache ``k_cache`` [blocks, block, 1, lora + rope]; the values are
+    the latent part of the cached rows.  Returns [B, heads, lora]."""
+    from chatlearn_b200.models.nn.mla import latent_paged_attention
+    return latent_paged_attention(q, k_cache, lora, block_tables, seq_lens, None, 1, scale)
+
+
 def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, q_lens=None, scale=None, groups=None):
     """Attention of new queries against a paged KV cache (keys of the new tokens
     already appended).  ``q [Tq, nq, d]`` holds ``q_lens[b]`` trailing query

@@ -1,2 +1,2 @@
-from .engine import RolloutEngine, SamplingParams
+from .engine import AsyncRollout, RolloutEngine, RolloutSession, SamplingParams
 from .scheduler import BlockAllocator, Scheduler, Sequence

@@ -591,68 +591,25 @@ class RolloutEngine:
         s.rope_delta = int(delta)
         self._image_rows_seen = getattr(self, "_image_rows_seen", 0) + len(where)      # statistics
 
+    def open_session(self, eos_id: Optional[int] = None) -> "RolloutSession":
+        """A scheduler that stays open: requests are submitted and collected one by one while the engine keeps
+        stepping (``generate`` is one session that is filled once and drained)."""
+        return RolloutSession(self, eos_id)
+
     def generate(self, prompts: List[List[int]], sampling: Any, eos_id: Optional[int] = None,
                  max_new_tokens: Optional[List[int]] = None, mm_inputs: Optional[List[Optional[Dict]]] = None) -> List[Sequence]:
         """Generate for a batch of token-id prompts.  ``sampling`` is one
         ``SamplingParams`` or a list (one per prompt); ``max_new_tokens`` optionally
         overrides the per-request budget (partial rollout)."""
-        self.alloc_kv_cache()
-        eos_id = self.arch.eos_token_id if eos_id is None else eos_id
-        # requests with the same prompt (the samples of a GRPO group) share the prompt's KV blocks; not with
-        # recurrent layers, whose state is per sequence and cannot be adopted block-wise
-        share = self.arch.layer_types is None and os.environ.get("CLB200_PREFIX_SHARING", "1") != "0"
-        sched = Scheduler(self.num_blocks, self.block_size, self.max_num_seqs, self.max_tokens, prefix_sharing=share)
+        sess = self.open_session(eos_id)
         seqs = []
         for i, p in enumerate(prompts):
             sp = sampling[i] if isinstance(sampling, (list, tuple)) else sampling
-            mx = max_new_tokens[i] if max_new_tokens is not None else sp.max_tokens
-            mx = max(0, min(mx, self.max_model_len - len(p)))
-            s = Sequence(self._req_counter, list(p), mx, sp)
-            mm = mm_inputs[i] if mm_inputs is not None else None
-            if mm is not None and mm.get("pixel_values") is not None and len(mm["image_grid_thw"]):
-                self._attach_images(s, mm)
-            self._req_counter += 1
-            seqs.append(s)
-            if mx == 0:
-                s.finished, s.finish_reason = True, "length"
-            else:
-                sched.add(s)
-        tm = {"sched_s": 0.0, "prefill_s": 0.0, "decode_s": 0.0, "prefill_steps": 0, "decode_steps": 0}
-        while True:
-            busy = sched.has_work()
-            if self.lockstep is not None and self.lockstep.size > 1:
-                flag = torch.tensor([1 if busy else 0], device=self.device)
-                import torch.distributed as dist
-                self.lockstep.all_reduce_(flag, op=dist.ReduceOp.MAX)
-                if int(flag.item()) == 0:
-                    break
-                if not busy:
-                    self._idle_step()
-                    continue
-            elif not busy:
-                break
-            t0 = time.perf_counter()
-            plan = sched.schedule()
-            t1 = time.perf_counter()
-            tm["sched_s"] += t1 - t0
-            if plan is None:
-                if self.lockstep is not None and self.lockstep.size > 1:
-                    self._idle_step()
-                    continue
-                break
-            self.step(sched, plan, eos_id)      # ends with the read-back of the sampled tokens
-            kind = "decode" if max(plan.q_lens) == 1 else "prefill"
-            tm[kind + "_s"] += time.perf_counter() - t1
-            tm[kind + "_steps"] += 1
-        self.stats = dict(sched.stats)
-        self.stats.update(tm)
-        if self.ep_symm is not None:
-            st = self.ep_symm.status()
-            if st:
-                raise RuntimeError(
-                    f"expert-parallel peer-memory dispatch reported status {st} "
-                    "(1: a peer did not arrive within the wait limit, 2: an expert's receive region overflowed; "
-                    "raise the capacity factor or set CLB200_SYMM_EP=0)")
+            seqs.append(sess.submit(p, sp, max_new_tokens[i] if max_new_tokens is not None else None,
+                                    mm_inputs[i] if mm_inputs is not None else None))
+        while sess.poll() is not None:
+            pass
+        sess.close()
         return seqs
 
     # ------------------------------------------------------------------ sleep / wake
@@ -663,3 +620,146 @@ class RolloutEngine:
     def onload(self, tags=(TAG_WEIGHTS, TAG_KV_CACHE)):
         if TAG_KV_CACHE in tags:
             self.alloc_kv_cache()
+
+
+
+class RolloutSession:
+    """Per-request front of the engine: ``submit`` a request at any time, ``poll`` runs one scheduler step and
+    returns the requests that finished in it.
+
+    Parity: the reference's agent rollouts run one coroutine per request against an asynchronous SGLang engine
+    (chatlearn/models/sglang_module.py:403-413 ``engine.async_generate``; chatlearn/models/agent/agent_module.py:
+    82-100 ``generate_per_request``), so a trajectory's next turn starts as soon as its previous one ends,
+    whatever the other requests are doing.  Here the same holds within one process: a request submitted between
+    two steps joins the running batch at the next step (continuous batching), a finished one is handed back at
+    once, and nothing waits for the slowest request of a "batch".  ``AsyncRollout`` puts asyncio futures on top.
+
+    Under lock-step groups (replicas that share expert-parallel collectives) ``poll`` keeps a replica without
+    work in its peers' collectives and reports the end (``None``) only when no replica has work left.
+    """
+
+    def __init__(self, engine: RolloutEngine, eos_id: Optional[int] = None):
+        engine.alloc_kv_cache()
+        self.engine = engine
+        self.eos_id = engine.arch.eos_token_id if eos_id is None else eos_id
+        # requests with the same prompt (the samples of a GRPO group) share the prompt's KV blocks; not with
+        # recurrent layers, whose state is per sequence and cannot be adopted block-wise
+        share = engine.arch.layer_types is None and os.environ.get("CLB200_PREFIX_SHARING", "1") != "0"
+        self.sched = Scheduler(engine.num_blocks, engine.block_size, engine.max_num_seqs, engine.max_tokens,
+                               prefix_sharing=share)
+        self.tm = {"sched_s": 0.0, "prefill_s": 0.0, "decode_s": 0.0, "prefill_steps": 0, "decode_steps": 0}
+        self._instant: List[Sequence] = []           # requests with no budget: finished on arrival
+        self.submitted = 0
+
+    def submit(self, prompt: List[int], sampling: "SamplingParams", max_new_tokens: Optional[int] = None,
+               mm: Optional[Dict[str, Any]] = None) -> Sequence:
+        eng = self.engine
+        mx = sampling.max_tokens if max_new_tokens is None else max_new_tokens
+        mx = max(0, min(mx, eng.max_model_len - len(prompt)))
+        s = Sequence(eng._req_counter, list(prompt), mx, sampling)
+        eng._req_counter += 1
+        self.submitted += 1
+        if mm is not None and mm.get("pixel_values") is not None and len(mm["image_grid_thw"]):
+            eng._attach_images(s, mm)
+        if mx == 0:
+            s.finished, s.finish_reason = True, "length"
+            self._instant.append(s)
+        else:
+            self.sched.add(s)
+        return s
+
+    def has_work(self) -> bool:
+        return bool(self._instant) or self.sched.has_work()
+
+    def poll(self) -> Optional[List[Sequence]]:
+        """One engine step.  Returns the requests that finished in it (possibly none), or ``None`` when there is
+        nothing left to do (on every replica of a lock-step group)."""
+        eng, sched = self.engine, self.sched
+        out, self._instant = self._instant, []
+        busy = sched.has_work()
+        lock = eng.lockstep is not None and eng.lockstep.size > 1
+        if lock:
+            import torch.distributed as dist
+            flag = torch.tensor([1 if (busy or out) else 0], device=eng.device)
+            eng.lockstep.all_reduce_(flag, op=dist.ReduceOp.MAX)
+            if int(flag.item()) == 0:
+                return None
+            if not busy:
+                eng._idle_step()
+                return out
+        elif not busy:
+            return out if out else None
+        t0 = time.perf_counter()
+        plan = sched.schedule()
+        t1 = time.perf_counter()
+        self.tm["sched_s"] += t1 - t0
+        if plan is None:
+            if lock:
+                eng._idle_step()
+                return out
+            return out if out else None
+        eng.step(sched, plan, self.eos_id)           # ends with the read-back of the sampled tokens
+        kind = "decode" if max(plan.q_lens) == 1 else "prefill"
+        self.tm[kind + "_s"] += time.perf_counter() - t1
+        self.tm[kind + "_steps"] += 1
+        out.extend(s for s in plan.seqs if s.finished)
+        return out
+
+    def close(self):
+        """Publish the session's statistics on the engine and check the peer-memory status words."""
+        eng = self.engine
+        eng.stats = dict(self.sched.stats)
+        eng.stats.update(self.tm)
+        if eng.ep_symm is not None:
+            st = eng.ep_symm.status()
+            if st:
+                raise RuntimeError(
+                    f"expert-parallel peer-memory dispatch reported status {st} "
+                    "(1: a peer did not arrive within the wait limit, 2: an expert's receive region overflowed; "
+                    "raise the capacity factor or set CLB200_SYMM_EP=0)")
+
+
+class AsyncRollout:
+    """asyncio front of a session: ``seq = await rollout.generate(prompt_ids, sampling)`` per request.
+
+    One task drives the engine while any request is outstanding and yields to the event loop after every step,
+    so the coroutine of a request that just finished can run its tools and submit its next turn before the
+    next step is scheduled.  For a replica of one process (no tensor-parallel peers to keep in step)."""
+
+    def __init__(self, engine: RolloutEngine, eos_id: Optional[int] = None):
+        self.session = engine.open_session(eos_id)
+        self._waiting: Dict[int, Any] = {}
+        self._driver = None
+
+    async def generate(self, prompt: List[int], sampling: "SamplingParams", max_new_tokens: Optional[int] = None,
+                       mm: Optional[Dict[str, Any]] = None) -> Sequence:
+        import asyncio
+        loop = asyncio.get_running_loop()
+        seq = self.session.submit(prompt, sampling, max_new_tokens, mm)
+        fut = loop.create_future()
+        self._waiting[seq.req_id] = fut
+        if self._driver is None or self._driver.done():
+            self._driver = loop.create_task(self._drive())
+        return await fut
+
+    async def _drive(self):
+        import asyncio
+        while self._waiting:
+            try:
+                done = self.session.poll()
+            except BaseException as e:              # every waiter learns of a failed step
+                for fut in self._waiting.values():
+                    if not fut.done():
+                        fut.set_exception(e)
+                self._waiting.clear()
+                raise
+            if done is None:
+                break
+            for s in done:
+                fut = self._waiting.pop(s.req_id, None)
+                if fut is not None and not fut.done():
+                    fut.set_result(s)
+            await asyncio.sleep(0)
+
+    def close(self):
+        self.session.close()

@@ -105,3 +105,48 @@ def test_token_balance_groups_have_even_load():
     assert sorted(d["id"] for d in out) == list(range(8))
     a, b = sum(d["all_token_length"] for d in out[:4]), sum(d["all_token_length"] for d in out[4:])
     assert abs(a - b) <= 20
+
+
+def test_continuous_scheduling_lets_a_trajectory_take_its_next_turn_while_others_decode():
+    """Two-turn trajectories with different turn lengths on a real (tiny, CPU) engine: with the open session a
+    short trajectory's second turn joins the batch while the long one is still in its first; both schedules
+    give the same tokens (greedy sampling)."""
+    import torch
+    from chatlearn_b200.configs.policy_config import PolicyConfig
+    from chatlearn_b200.models.agent.agent_module import AgentModule
+    from chatlearn_b200.models.agent.base_agent_graph import AgentGraphOutput, BaseAgentGraph
+    from chatlearn_b200.models.agent.chat_model import LLMRequest
+    from chatlearn_b200.models.nn import PRESETS, CausalLM
+    from chatlearn_b200.rollout import RolloutEngine
+
+    class TwoTurns(BaseAgentGraph):
+        def run(self, sampling_params, prompt_ids=None, first=4, **query):
+            a = yield LLMRequest(list(prompt_ids), {"max_new_tokens": first}, None)
+            b = yield LLMRequest(list(prompt_ids) + list(a.output_ids) + [7], {"max_new_tokens": 3}, None)
+            ids = list(prompt_ids) + list(a.output_ids) + [7] + list(b.output_ids)
+            return AgentGraphOutput(str_output="", prompt_ids=list(prompt_ids), all_token_ids=ids,
+                                    loss_mask=[0] * len(prompt_ids) + [1] * (len(ids) - len(prompt_ids)), num_turns=2)
+
+    arch = PRESETS["tiny_qwen3"]()
+    model = CausalLM(arch, dtype=torch.float32).init_weights(2)
+    g = torch.Generator().manual_seed(3)
+    data = [{"agent_name": "two", "prompt_ids": torch.randint(0, arch.vocab_size - 1, (n,), generator=g).tolist(),
+             "first": f} for n, f in ((12, 16), (9, 2), (15, 5))]
+    results = {}
+    for mode in ("continuous", "lockstep"):
+        mod = AgentModule.__new__(AgentModule)
+        mod._module_args = PolicyConfig(temperature=0.0, max_response_tokens_length=16, seq_length=128,
+                                        agent_scheduling=mode)
+        mod.module_args.ignore_eos = True
+        mod.engine = RolloutEngine(model, block_size=8, num_blocks=128, max_num_seqs=16, max_model_len=128)
+        mod.tp_group = None
+        mod.agent_factory = {"two": TwoTurns("two", tokenizer=TOK)}
+        outs = mod.run_trajectories(data)
+        results[mode] = [o.all_token_ids for o in outs]
+        if mode == "continuous":
+            st = mod.agent_stats
+            assert st["requests"] == 6 and st["joined_running_batch"] >= 2
+            # lock-step would need 16 + 3 steps after the prefills; here the second turns overlap the long first turn
+            assert st["engine_steps"] <= 16 + 3 + 4
+    assert results["continuous"] == results["lockstep"]
+    assert [len(t) for t in results["continuous"]] == [12 + 16 + 1 + 3, 9 + 2 + 1 + 3, 15 + 5 + 1 + 3]

@@ -356,3 +356,38 @@ def test_grouped_decode_attention_matches_the_per_sequence_kernel(native):
         _close(got, want, 2e-2, 2e-2)
     ref_out = ref.paged_attention(q, kc, vc, bt, sl, None, scale)
     _close(want, ref_out, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("heads,splits", [(16, 1), (16, 3), (40, 0), (5, 2)])
+def test_mla_paged_decode_matches_fp32_statements(heads, splits):
+    """Latent-attention decode kernel (latent 512 + rotary 64) against fp32 statements over the same paged cache:
+    ragged lengths (one below a block, one at a block edge), head counts that are not a multiple of the 16-row tile,
+    one CTA per sequence and several splits of the context."""
+    from chatlearn_b200.models.nn.mla import latent_paged_attention
+    from chatlearn_b200.ops import native
+    torch.manual_seed(3)
+    dev = "cuda"
+    lens = [1, 63, 64, 65, 700, 1531, 128, 2049]
+    B, bs, D, lora = len(lens), 64, 576, 512
+    max_blocks = (max(lens) + bs - 1) // bs + 1
+    nblocks = sum((n + bs - 1) // bs for n in lens) + 4
+    cache = (torch.randn(nblocks, bs, 1, D, device=dev) * 0.5).to(torch.bfloat16)
+    perm = torch.randperm(nblocks, device=dev).to(torch.int32)
+    bt = torch.zeros(B, max_blocks, dtype=torch.int32, device=dev)
+    at = 0
+    for i, n in enumerate(lens):
+        k = (n + bs - 1) // bs
+        bt[i, :k] = perm[at:at + k]
+        at += k
+    q = (torch.randn(B, heads, D, device=dev) * 0.3).to(torch.bfloat16)
+    sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+    scale = 192 ** -0.5
+    out = native.C.mla_paged_decode(q, cache, bt, sl, scale, splits)
+    ref = latent_paged_attention(q.float(), cache.float(), lora, bt, sl, None, 1, scale)
+    assert out.shape == (B, heads, lora) and out.dtype == torch.bfloat16
+    err = (out.float() - ref).abs().max().item()
+    assert err < 2e-2, err
+    # through the op table (automatic split choice)
+    from chatlearn_b200 import ops
+    out2 = ops.mla_paged_decode(q, cache, lora, bt, sl, scale)
+    assert (out2.float() - ref).abs().max().item() < 2e-2

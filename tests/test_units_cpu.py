@@ -467,3 +467,75 @@ def test_resource_manager_bundles(monkeypatch):
     assert rm.node_of(s1.ranks[0]) != rm.node_of(s2.ranks[0])
     e = rm.reserve("colocated", [5, 6, 9])
     assert [x.node for x in e.bundles] == [1, 2] and 5 not in rm._nodes[1].free
+
+
+def _tiny_engine(**kw):
+    from chatlearn_b200.rollout import RolloutEngine
+    arch = PRESETS["tiny_qwen3"]()
+    model = CausalLM(arch, dtype=torch.float32).init_weights(2)
+    return arch, RolloutEngine(model, block_size=8, num_blocks=128, max_num_seqs=16, max_model_len=128, **kw)
+
+
+def test_session_requests_join_and_leave_a_running_batch():
+    """A request submitted while others decode joins at the next step, finishes on its own schedule, and gets the
+    tokens it would get alone (greedy)."""
+    from chatlearn_b200.rollout import SamplingParams
+    arch, eng = _tiny_engine()
+    g = torch.Generator().manual_seed(11)
+    pa, pb = (torch.randint(0, arch.vocab_size - 1, (n,), generator=g).tolist() for n in (21, 13))
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    alone = [s.output for s in eng.generate([pa, pb], [sp, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)])]
+
+    sess = eng.open_session()
+    a = sess.submit(pa, sp)
+    order, steps, b = [], 0, None
+    while True:
+        done = sess.poll()
+        if done is None:
+            break
+        steps += 1
+        order += [s.req_id for s in done]
+        if steps == 4:                                # a is in the middle of its decode
+            assert not a.finished and len(a.output) == 4
+            b = sess.submit(pb, sp, max_new_tokens=5)
+    sess.close()
+    assert order == [b.req_id, a.req_id]              # the late, short request leaves first
+    assert [a.output, b.output] == alone
+    assert sess.poll() is None
+    z = sess.submit(pa, sp, max_new_tokens=0)         # no budget: handed back at the next poll, no engine step
+    assert z.finished and sess.poll() == [z] and sess.poll() is None
+
+
+def test_async_rollout_resolves_each_request_when_it_finishes():
+    import asyncio
+    from chatlearn_b200.rollout import SamplingParams
+    from chatlearn_b200.rollout.engine import AsyncRollout
+    arch, eng = _tiny_engine()
+    g = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(0, arch.vocab_size - 1, (n,), generator=g).tolist() for n in (9, 17, 12)]
+    budgets = [10, 3, 6]
+    finished = []
+
+    async def trajectory(ar, i):
+        # two turns: the second prompt is the first plus its answer
+        sp = SamplingParams(temperature=0.0, max_tokens=budgets[i], ignore_eos=True)
+        first = await ar.generate(prompts[i], sp)
+        finished.append((i, 1))
+        second = await ar.generate(prompts[i] + first.output, sp, max_new_tokens=2)
+        finished.append((i, 2))
+        return first.output + second.output
+
+    async def main():
+        ar = AsyncRollout(eng)
+        outs = await asyncio.gather(*(trajectory(ar, i) for i in range(3)))
+        ar.close()
+        return outs
+
+    outs = asyncio.run(main())
+    assert [len(o) for o in outs] == [12, 5, 8]
+    # the short trajectory ran both of its turns before the long one finished its first
+    assert finished.index((1, 2)) < finished.index((0, 1))
+    # greedy: a two-turn trajectory equals one uninterrupted generation of the same length
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    whole = eng.generate([prompts[0]], sp)[0].output
+    assert outs[0] == whole
