@@ -7,17 +7,16 @@
 // sizes the cache).
 //
 // One CTA (8 warps) per (sequence, tile of 16 heads, split of the context).  The 16 heads are the M dimension of
-// m16n8k16 bf16 MMAs, so a cached row is read from HBM once for all of them.  Half blocks of 32 cached rows
-// (37 KB) stream through a four-stage cp.async ring: three of them are in flight while one is consumed (with one
-// 74 KB block in flight per SM the kernel sat at 29 GB/s per SM, bound by the latency of that one load).  Per half
-// block, in three phases separated by CTA barriers:
+// m16n8k16 bf16 MMAs, so a cached row is read from HBM once for all of them.  Blocks of 64 cached rows (74 KB)
+// stream through a two-stage cp.async ring.  Per block, in three phases separated by CTA barriers:
 //   scores    warp w contracts a quarter of the 576 dims (w % 4; its slice of Q stays in 36 registers for the
 //             whole kernel) against half of the keys (w / 4): every byte of the tile is read from shared memory
-//             once; the four partial sums go to shared memory as fp32;
-//   softmax   warp w owns rows 2w and 2w + 1 (one per half warp): adds the partials, masks, keeps the running
-//             maximum and sum of its rows, writes the probabilities (bf16) and the rows' rescaling factors;
-//   output    warp w accumulates its own 64 of the 512 output columns over the 32 keys.
-// The arithmetic is ~30 FLOP per byte of cache, so the kernel is bound by how fast cp.async keeps HBM busy.
+//             once, 4 independent accumulator chains per warp; the four partial sums go to shared memory as fp32;
+//   softmax   warp w owns rows 2w and 2w + 1: adds the partials, masks, keeps the running maximum and sum of its
+//             rows, writes the probabilities (bf16) and the rows' rescaling factors to shared memory;
+//   output    warp w accumulates its own 64 of the 512 output columns over all 64 keys.
+// ~30 FLOP per byte of cache: on a B200 the kernel is bound by the warp-level MMA rate and the barriers between
+// the phases, not by HBM (a four-stage ring of half blocks, three loads in flight, was no faster).
 #include <ATen/cuda/CUDAContext.h>
 #include <cuda_pipeline.h>
 #include <c10/cuda/CUDAException.h>
@@ -32,18 +31,16 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
-constexpr int BS = 64;            // cached rows per block of the paged cache
-constexpr int SB = 32;            // rows per pipeline stage (half a block)
-constexpr int kStages = 4;
+constexpr int BS = 64;            // cached rows per block
 constexpr int kPad = 8;           // row padding (elements): keeps ldmatrix rows on distinct banks
 
 constexpr int kSPad = 8;          // fp32 padding of the partial-score rows
 
 template <int DL, int DR>
 struct SmemMLA {
-  bf16 k[kStages][SB][DL + DR + kPad];  // the last stage also stages Q before the first prefetch lands there
-  float sp[4][16][SB + kSPad];    // partial scores of the four quarters of the contraction
-  bf16 p[16][SB + kPad];
+  bf16 k[2][BS][DL + DR + kPad];  // stage 1 also stages Q before the first prefetch lands there
+  float sp[4][16][BS + kSPad];    // partial scores of the four quarters of the contraction
+  bf16 p[16][BS + kPad];
   float alpha[16];
   float row_m[16];
   float row_l[16];
@@ -70,14 +67,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// half block j of a sequence: rows (j & 1) * 32 ... of page j / 2.  Rows past `valid` are zero-filled: their
-// probabilities are 0, and 0 * garbage must not become NaN
+// rows past `valid` are zero-filled: their probabilities are 0, and 0 * garbage must not become NaN
 template <int DL, int DR>
-__device__ __forceinline__ void load_rows(SmemMLA<DL, DR>* sm, int stage, const bf16* cache, const int* bt, int j, int len) {
+__device__ __forceinline__ void load_rows(SmemMLA<DL, DR>* sm, int stage, const bf16* cache, int64_t block_id, int valid) {
   constexpr int D = DL + DR, CH = D / 8;
-  const bf16* src = cache + ((int64_t)bt[j >> 1] * BS + (j & 1) * SB) * (int64_t)D;
-  const int valid = min(SB, len - j * SB);
-  for (int i = threadIdx.x; i < SB * CH; i += kThreads) {
+  const bf16* src = cache + block_id * BS * (int64_t)D;
+  for (int i = threadIdx.x; i < BS * CH; i += kThreads) {
     const int r = i / CH, c = (i % CH) * 8;
     if (r < valid) {
       __pipeline_memcpy_async(&sm->k[stage][r][c], src + (int64_t)r * D + c, 16);
@@ -99,7 +94,7 @@ mla_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, co
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int len = ctx_len[seq];
-  const int nblk = (len + SB - 1) / SB;                    // half blocks
+  const int nblk = (len + BS - 1) / BS;
   const int per = (nblk + num_splits - 1) / num_splits;
   const int b0 = split * per, b1 = min(b0 + per, nblk);
   const int h0 = ht * 16;
@@ -112,15 +107,12 @@ mla_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, co
     return;
   }
   const int* bt = block_tables + (int64_t)seq * max_blocks;
-#pragma unroll
-  for (int i = 0; i < kStages - 1; ++i) {                  // three half blocks in flight before anything is consumed
-    if (b0 + i < b1) load_rows<DL, DR>(sm, i, cache, bt, b0 + i, len);
-    __pipeline_commit();
-  }
-  // Q through the (still unused) last stage into registers: this warp's quarter of the contraction
+  load_rows<DL, DR>(sm, 0, cache, bt[b0], min(BS, len - b0 * BS));
+  __pipeline_commit();
+  // Q through the (still unused) second stage into registers: this warp's quarter of the contraction
   constexpr int KQ = D / 16 / 4;                           // 9 k-steps per quarter
   static_assert(D % 64 == 0 && KQ * 64 == D, "the contraction splits into four quarters of whole k-steps");
-  bf16 (*qs)[D + kPad] = sm->k[kStages - 1];
+  bf16 (*qs)[D + kPad] = sm->k[1];
   for (int i = tid; i < 16 * (D / 8); i += kThreads) {
     const int r = i / (D / 8), c = (i % (D / 8)) * 8;
     uint4 v = make_uint4(0, 0, 0, 0);
@@ -137,60 +129,68 @@ mla_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, co
   float o_acc[DL / kWarps / 8][4];
 #pragma unroll
   for (int n = 0; n < DL / kWarps / 8; ++n) o_acc[n][0] = o_acc[n][1] = o_acc[n][2] = o_acc[n][3] = 0.f;
-  const int my_row = 2 * warp + (lane >> 4), hl = lane & 15;   // softmax phase: one row per half warp, two keys per lane
-  float m_run = -INFINITY;                                 // of my_row (uniform over the half warp)
-  float l_run = 0.f;                                       // this lane's share of my_row's sum
+  float m_run[2] = {-INFINITY, -INFINITY};                 // rows 2 * warp and 2 * warp + 1 (uniform over the lanes)
+  float l_run[2] = {0.f, 0.f};                             // this lane's share of those rows' sums
   const int col0 = warp * (DL / kWarps);                   // this warp's output columns
 
   for (int b = b0; b < b1; ++b) {
-    const int st = (b - b0) % kStages;
-    if (b + kStages - 1 < b1) load_rows<DL, DR>(sm, (b - b0 + kStages - 1) % kStages, cache, bt, b + kStages - 1, len);
+    const int st = (b - b0) & 1;
+    if (b + 1 < b1) load_rows<DL, DR>(sm, st ^ 1, cache, bt[b + 1], min(BS, len - (b + 1) * BS));
     __pipeline_commit();
-    __pipeline_wait_prior(kStages - 1);
+    __pipeline_wait_prior(1);
     __syncthreads();
-    // ---- partial scores: 16 rows x 16 keys over this warp's quarter of the contraction ----
+    // ---- partial scores: 16 rows x 32 keys over this warp's quarter of the contraction ----
     {
-      float s[2][4];
+      float s[4][4];
 #pragma unroll
-      for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
 #pragma unroll
       for (int j = 0; j < KQ; ++j) {
-        uint32_t kb[4];
-        ldsm_x4(kb, &sm->k[st][kh * 16 + (lane & 7) + ((lane >> 4) & 1) * 8][(kq * KQ + j) * 16 + ((lane >> 3) & 1) * 8]);
-        mma16816(s[0], qa[j], kb[0], kb[1]);
-        mma16816(s[1], qa[j], kb[2], kb[3]);
+        const int kc = (kq * KQ + j) * 16 + ((lane >> 3) & 1) * 8;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t kb[4];
+          ldsm_x4(kb, &sm->k[st][kh * 32 + h * 16 + (lane & 7) + ((lane >> 4) & 1) * 8][kc]);
+          mma16816(s[2 * h], qa[j], kb[0], kb[1]);
+          mma16816(s[2 * h + 1], qa[j], kb[2], kb[3]);
+        }
       }
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
-        const int c = kh * 16 + n * 8 + 2 * t;
+      for (int n = 0; n < 4; ++n) {
+        const int c = kh * 32 + n * 8 + 2 * t;
         *reinterpret_cast<float2*>(&sm->sp[kq][g][c]) = make_float2(s[n][0], s[n][1]);
         *reinterpret_cast<float2*>(&sm->sp[kq][g + 8][c]) = make_float2(s[n][2], s[n][3]);
       }
     }
     __syncthreads();
-    // ---- softmax of this half warp's row over the 32 keys (two per lane) ----
+    // ---- softmax of this warp's two rows over the 64 keys (two per lane) ----
     {
-      const int key = b * SB + 2 * hl;
-      float2 a = *reinterpret_cast<const float2*>(&sm->sp[0][my_row][2 * hl]);
+      const int key = b * BS + 2 * lane;
+      const bool v0 = key < len, v1 = key + 1 < len;
 #pragma unroll
-      for (int k4 = 1; k4 < 4; ++k4) {
-        const float2 x = *reinterpret_cast<const float2*>(&sm->sp[k4][my_row][2 * hl]);
-        a.x += x.x; a.y += x.y;
+      for (int r = 0; r < 2; ++r) {
+        const int row = 2 * warp + r;
+        float2 a = *reinterpret_cast<const float2*>(&sm->sp[0][row][2 * lane]);
+#pragma unroll
+        for (int k4 = 1; k4 < 4; ++k4) {
+          const float2 x = *reinterpret_cast<const float2*>(&sm->sp[k4][row][2 * lane]);
+          a.x += x.x; a.y += x.y;
+        }
+        const float s0 = v0 ? a.x * scale : -INFINITY, s1 = v1 ? a.y * scale : -INFINITY;
+        float mx = fmaxf(s0, s1);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float m_new = fmaxf(m_run[r], mx);           // finite: the block holds at least one valid key
+        const float al = __expf(m_run[r] - m_new);
+        const float p0 = __expf(s0 - m_new), p1 = __expf(s1 - m_new);
+        l_run[r] = l_run[r] * al + p0 + p1;
+        m_run[r] = m_new;
+        *reinterpret_cast<uint32_t*>(&sm->p[row][2 * lane]) = pack2(p0, p1);
+        if (lane == 0) sm->alpha[row] = al;
       }
-      const float s0 = key < len ? a.x * scale : -INFINITY, s1 = key + 1 < len ? a.y * scale : -INFINITY;
-      float mx = fmaxf(s0, s1);
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-      const float m_new = fmaxf(m_run, mx);                // finite: the half block holds at least one valid key
-      const float al = __expf(m_run - m_new);
-      const float p0 = __expf(s0 - m_new), p1 = __expf(s1 - m_new);
-      l_run = l_run * al + p0 + p1;
-      m_run = m_new;
-      *reinterpret_cast<uint32_t*>(&sm->p[my_row][2 * hl]) = pack2(p0, p1);
-      if (hl == 0) sm->alpha[my_row] = al;
     }
     __syncthreads();
-    // ---- this warp's 64 output columns over the 32 keys ----
+    // ---- this warp's 64 output columns over all 64 keys ----
     {
       const float a0 = sm->alpha[g], a1 = sm->alpha[g + 8];
 #pragma unroll
@@ -198,7 +198,7 @@ mla_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, co
         o_acc[n][0] *= a0; o_acc[n][1] *= a0; o_acc[n][2] *= a1; o_acc[n][3] *= a1;
       }
 #pragma unroll
-      for (int kk = 0; kk < SB / 16; ++kk) {
+      for (int kk = 0; kk < BS / 16; ++kk) {
         uint32_t pa[4];
         ldsm_x4(pa, &sm->p[lane & 15][kk * 16 + (lane >> 4) * 8]);
 #pragma unroll
@@ -215,8 +215,11 @@ mla_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, co
   __pipeline_wait_prior(0);
   // ---- row sums: over the lanes of the owning warp, then to everybody ----
 #pragma unroll
-  for (int o = 8; o > 0; o >>= 1) l_run += __shfl_xor_sync(0xffffffffu, l_run, o);
-  if (hl == 0) { sm->row_l[my_row] = l_run; sm->row_m[my_row] = m_run; }
+  for (int r = 0; r < 2; ++r) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], o);
+    if (lane == 0) { sm->row_l[2 * warp + r] = l_run[r]; sm->row_m[2 * warp + r] = m_run[r]; }
+  }
   __syncthreads();
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
