@@ -56,6 +56,9 @@ __global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict_
 
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)); dw += dy * xhat (fp32 atomics, one
 // partial per CTA: each CTA walks a strided set of rows and keeps dw in registers).
+// A thread owns at most MAXV 16-byte vectors of a row.  The row's x and dy stay in registers between the
+// reduction and the write of dx (read once), the weights are loaded once per CTA, and the next row's
+// vectors are requested before the current row's reduction, so the loads overlap the barriers.
 template <typename T, int MAXV>
 __global__ void rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w,
                                    const T* __restrict__ dy, const float* __restrict__ rstd,
@@ -63,42 +66,64 @@ __global__ void rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict_
   __shared__ float red[32];
   constexpr int V = Vec16<T>::N;
   float dwacc[MAXV][V];
+  Vec16<T> wv[MAXV], xv[MAXV], gv[MAXV], nx[MAXV], ng[MAXV];
+  int col[MAXV];
 #pragma unroll
-  for (int a = 0; a < MAXV; ++a)
+  for (int a = 0; a < MAXV; ++a) {
+    col[a] = (threadIdx.x + a * blockDim.x) * V;
 #pragma unroll
     for (int j = 0; j < V; ++j) dwacc[a][j] = 0.f;
-  for (int64_t row = blockIdx.x; row < N; row += gridDim.x) {
-    const T* xr = x + row * H;
-    const T* dyr = dy + row * H;
+    if (col[a] < H) wv[a] = ld16(w + col[a]);
+  }
+  int64_t row = blockIdx.x;
+  if (row < N) {
+#pragma unroll
+    for (int a = 0; a < MAXV; ++a)
+      if (col[a] < H) { xv[a] = ld16(x + row * H + col[a]); gv[a] = ld16(dy + row * H + col[a]); }
+  }
+  while (row < N) {
+    const int64_t next = row + gridDim.x;
+    if (next < N) {
+#pragma unroll
+      for (int a = 0; a < MAXV; ++a)
+        if (col[a] < H) { nx[a] = ld16(x + next * H + col[a]); ng[a] = ld16(dy + next * H + col[a]); }
+    }
     const float r = rstd[row];
     float dot = 0.f;
-    int a = 0;
-    for (int i = threadIdx.x * V; i < H; i += blockDim.x * V, ++a) {
-      Vec16<T> xv = ld16(xr + i), gv = ld16(dyr + i), wv = ld16(w + i);
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        float xh = Cvt<T>::to_f(xv.v[j]) * r;
-        float g = Cvt<T>::to_f(gv.v[j]);
-        dot += g * Cvt<T>::to_f(wv.v[j]) * xh;
-        if (a < MAXV) dwacc[a][j] += g * xh;
+    for (int a = 0; a < MAXV; ++a) {
+      if (col[a] < H) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = Cvt<T>::to_f(xv[a].v[j]) * r;
+          const float g = Cvt<T>::to_f(gv[a].v[j]);
+          dot += g * Cvt<T>::to_f(wv[a].v[j]) * xh;
+          dwacc[a][j] += g * xh;
+        }
       }
     }
     dot = block_sum(dot, red) / H;
-    for (int i = threadIdx.x * V; i < H; i += blockDim.x * V) {
-      Vec16<T> xv = ld16(xr + i), gv = ld16(dyr + i), wv = ld16(w + i), o;
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        float xh = Cvt<T>::to_f(xv.v[j]) * r;
-        o.v[j] = Cvt<T>::from_f(r * (Cvt<T>::to_f(gv.v[j]) * Cvt<T>::to_f(wv.v[j]) - xh * dot));
+    for (int a = 0; a < MAXV; ++a) {
+      if (col[a] < H) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = Cvt<T>::to_f(xv[a].v[j]) * r;
+          o.v[j] = Cvt<T>::from_f(r * (Cvt<T>::to_f(gv[a].v[j]) * Cvt<T>::to_f(wv[a].v[j]) - xh * dot));
+        }
+        st16(dx + row * H + col[a], o);
       }
-      st16(dx + row * H + i, o);
     }
-  }
-  int a = 0;
-  for (int i = threadIdx.x * V; i < H; i += blockDim.x * V, ++a) {
-    if (a < MAXV) {
 #pragma unroll
-      for (int j = 0; j < V; ++j) atomicAdd(dw + i + j, dwacc[a][j]);
+    for (int a = 0; a < MAXV; ++a) { xv[a] = nx[a]; gv[a] = ng[a]; }
+    row = next;
+  }
+#pragma unroll
+  for (int a = 0; a < MAXV; ++a) {
+    if (col[a] < H) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) atomicAdd(dw + col[a] + j, dwacc[a][j]);
     }
   }
 }
