@@ -69,7 +69,7 @@ class RuntimeConfig(BaseConfig):
     eval_episode_interval: int = 0
     enable_eval_before_training: bool = False
     # memory / scheduling
-    bucket_size_mb_in_memory_manager: int = 1024
+    bucket_size_mb_in_memory_manager: float = 1024      # largest message of the point-to-point weight sync (MB)
     cpu_schedule_strategy: str = "SPREAD"
     policy_to_regroup_queue: str = "global_barrier"
     log_args_dict: LogConfig = field(default_factory=LogConfig)

@@ -120,7 +120,8 @@ class ModelManager:
         for src, dst in self._sync_pairs:
             key = f"{src.name}->{dst.name}"
             mode = str(getattr(dst.module_args, "sync_mode", "auto"))
-            self.parameter_sync_groups[key] = ParameterSyncGroup(src, dst, mode=mode)
+            self.parameter_sync_groups[key] = ParameterSyncGroup(
+                src, dst, mode=mode, bucket_size_mb=float(getattr(self.runtime_args, "bucket_size_mb_in_memory_manager", 1024)))
 
     def sync_parameters(self, episode_offset: int = 0, requires_grad=None, validate: bool = False):
         """onload trainer weights → onload rollout weights → sync → offload trainer →

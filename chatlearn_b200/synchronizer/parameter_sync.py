@@ -12,7 +12,10 @@ Execution back ends, chosen per call:
   source buffers in symmetric memory (CUDA only);
 * ``p2p``     – portable path: per (sender, receiver) pair the sender packs its
   pieces (already cast) into one message, ``batch_isend_irecv`` moves it, the
-  receiver unpacks; this is also the NCCL baseline the kernel is compared with;
+  receiver unpacks; this is also the NCCL baseline the kernel is compared with.
+  The transfer runs in iterations planned under a memory budget (``plan.build_iterations``:
+  messages of at most ``bucket_size_mb``, and per iteration no rank stages more than
+  ``max_memory_fraction`` of its device memory minus what is already in use);
 * local-only plans (every rectangle already on the destination rank) run as
   strided copies with no communication in either mode.
 """
@@ -23,7 +26,8 @@ import torch
 import torch.distributed as dist
 
 from chatlearn_b200.utils.logger import logger
-from .plan import BufferInfo, CopyDesc, LeafPlacement, RankLayout, build_plan, plan_stats, validate_plan
+from .plan import (BufferInfo, CopyDesc, LeafPlacement, RankLayout, build_iterations, build_plan, iteration_stats,
+                   plan_stats, validate_plan)
 
 
 def layout_of_model(model, rank: int, shard_of_block=None, prefix: str = "") -> RankLayout:
@@ -45,13 +49,17 @@ def _view2d(buf: torch.Tensor, offset: int, stride: int, rows: int, cols: int) -
 
 
 class ParameterSyncGroup:
-    def __init__(self, src_model, dst_model, world_group=None, mode: str = "auto"):
+    def __init__(self, src_model, dst_model, world_group=None, mode: str = "auto", bucket_size_mb: float = 1024,
+                 max_memory_fraction: float = 0.8):
         """``src_model`` / ``dst_model`` are modules exposing ``sync_layout()`` →
         ``RankLayout`` (or ``None`` on ranks that do not host the role) and
         ``sync_buffers()`` → ``{buffer name: flat tensor}``."""
         self.src, self.dst = src_model, dst_model
         self.group = world_group
         self.mode = mode
+        self.bucket_bytes = max(int(float(bucket_size_mb) * (1 << 20)), 1024)
+        self.max_memory_fraction = float(max_memory_fraction)
+        self.iterations = None
         self.plan: Optional[Dict[int, List[CopyDesc]]] = None
         self.stats: Dict[str, float] = {}
         self.rank = dist.get_rank() if dist.is_initialized() else 0
@@ -92,32 +100,53 @@ class ParameterSyncGroup:
             t = _view2d(dst_bufs[d.dst_buffer], d.dst_offset, d.dst_stride, d.rows, d.cols)
             t.copy_(s)
 
+    def _staging_budgets(self, dev) -> Dict[int, int]:
+        """Bytes every rank may stage per iteration: ``max_memory_fraction`` of its device memory minus what is in
+        use now (chatlearn/synchronizer/planners/tensor_planner.py:100-108).  CPU ranks are not bounded."""
+        mine = -1
+        if dev.type == "cuda":
+            free, total = torch.cuda.mem_get_info(dev)
+            # memory this process has cached but not allocated can be reused for the messages
+            free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
+            mine = int(free - (1.0 - self.max_memory_fraction) * total)
+        got = [mine]
+        if self.world > 1:
+            got = [None] * self.world
+            dist.all_gather_object(got, mine)
+        return {r: max(b, 1 << 20) for r, b in enumerate(got) if b is not None and b >= 0}
+
+    def _plan_iterations(self, dev, elem_size: int):
+        if self.iterations is None:
+            self.iterations = build_iterations(self.plan, elem_size, self.bucket_bytes, self._staging_budgets(dev))
+            self.stats.update(iteration_stats(self.iterations, elem_size))
+            if self.rank == 0:
+                logger.info(f"parameter sync {self.src.name}->{self.dst.name}: {self.stats['iterations']} iteration(s), "
+                            f"at most {self.stats['peak_staged_mb']} MB staged per rank")
+        return self.iterations
+
     @torch.no_grad()
     def _run_p2p(self, src_bufs, dst_bufs):
         me = self.rank
         mine = self.plan.get(me, [])
         self._run_local([d for d in mine if d.src_rank == me], src_bufs, dst_bufs)
-        # what I send: pieces of every destination whose source is me
-        send: Dict[int, List[CopyDesc]] = {}
-        for dst, ds in self.plan.items():
-            if dst == me:
-                continue
-            for d in ds:
-                if d.src_rank == me:
-                    send.setdefault(dst, []).append(d)
-        recv: Dict[int, List[CopyDesc]] = {}
-        for d in mine:
-            if d.src_rank != me:
-                recv.setdefault(d.src_rank, []).append(d)
-        if not send and not recv:
+        if all(d.src_rank == dst for dst, ds in self.plan.items() for d in ds):
             return
         dst_dtype = None
         if dst_bufs:
             dst_dtype = next(iter(dst_bufs.values())).dtype
-        dev = next(iter((src_bufs or dst_bufs).values())).device
-        ops_, keep = [], []
+        bufs = src_bufs or dst_bufs
+        dev = next(iter(bufs.values())).device if bufs else \
+            torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         # the message dtype is the destination dtype: the cast happens at the source
         wire = self._wire_dtype(dst_dtype, dev)
+        for it in self._plan_iterations(dev, torch.empty(0, dtype=wire).element_size()):
+            send = {dst: ds for (src, dst), ds in it.items() if src == me}
+            recv = {src: ds for (src, dst), ds in it.items() if dst == me}
+            if send or recv:
+                self._exchange(send, recv, src_bufs, dst_bufs, wire, dev)
+
+    def _exchange(self, send, recv, src_bufs, dst_bufs, wire, dev):
+        ops_, keep = [], []
         for dst, ds in sorted(send.items()):
             msg = torch.empty(sum(d.numel for d in ds), dtype=wire, device=dev)
             off = 0

@@ -265,3 +265,79 @@ def plan_stats(plan: Dict[int, List[CopyDesc]], elem_bytes: int = 2) -> Dict[str
                 per_sender[d.src_rank] = per_sender.get(d.src_rank, 0) + d.numel
     return {"descriptors": n, "local_bytes": local * elem_bytes, "remote_bytes": remote * elem_bytes,
             "max_sender_bytes": max(per_sender.values(), default=0) * elem_bytes}
+
+
+# ---------------------------------------------------------------------------- memory-budgeted iterations
+def split_rows(d: CopyDesc, max_elems: int) -> List[CopyDesc]:
+    """Cut a rectangle into row bands of at most ``max_elems`` elements (a single row is never cut)."""
+    if d.numel <= max_elems or d.rows <= 1:
+        return [d]
+    band = max(1, max_elems // max(d.cols, 1))
+    out = []
+    for r0 in range(0, d.rows, band):
+        n = min(band, d.rows - r0)
+        out.append(CopyDesc(d.src_rank, d.src_buffer, d.src_offset + r0 * d.src_stride, d.src_stride,
+                            d.dst_rank, d.dst_buffer, d.dst_offset + r0 * d.dst_stride, d.dst_stride, n, d.cols, d.hf_name))
+    return out
+
+
+def build_iterations(plan: Dict[int, List[CopyDesc]], elem_size: int, bucket_bytes: int,
+                     budget_bytes: Optional[Dict[int, int]] = None) -> List[Dict[Tuple[int, int], List[CopyDesc]]]:
+    """Schedule the remote pieces of a plan into iterations with bounded staging memory.
+
+    Parity: chatlearn/synchronizer/planners/tensor_planner.py:39-176 (``_check_constraint`` / ``build_iteration``:
+    a bucket per sender and receiver group never exceeds ``bucket_size``, and the buckets a GPU holds in one
+    iteration, sent and received, fit into ``max_memory_fraction`` of its memory).  The point-to-point executor
+    packs what one rank sends another into one message, so per iteration a rank stages the messages it sends and
+    the messages it receives.  Here: every message is at most ``bucket_bytes``; the bytes a rank stages in one
+    iteration (both directions) are at most ``budget_bytes[rank]`` (no entry: unbounded); pieces larger than a
+    bucket are cut into row bands first.  Pieces are placed first-fit in a canonical order, so every rank derives
+    the same schedule from the same plan.  Returns, per iteration, ``{(src, dst): [pieces]}``; pieces whose source
+    is their destination are not scheduled (they are local copies).
+    """
+    budget_bytes = budget_bytes or {}
+    max_elems = max(1, bucket_bytes // elem_size)
+    pieces: List[CopyDesc] = []
+    for dst in sorted(plan):
+        for d in plan[dst]:
+            if d.src_rank != dst:
+                pieces.extend(split_rows(d, max_elems))
+    pieces.sort(key=lambda d: (d.src_rank, d.dst_rank))          # stable: plan order within a pair
+    iters: List[Dict[Tuple[int, int], List[CopyDesc]]] = []
+    staged: List[Dict[int, int]] = []                              # per iteration: bytes staged per rank
+    msg: List[Dict[Tuple[int, int], int]] = []                     # per iteration: bytes per message
+    for d in pieces:
+        nb = d.numel * elem_size
+        pair = (d.src_rank, d.dst_rank)
+        for need in (d.src_rank, d.dst_rank):
+            if need in budget_bytes and nb > budget_bytes[need]:
+                raise RuntimeError(f"parameter sync: a piece of {nb} bytes ({d.hf_name or d.src_buffer}) does not fit "
+                                   f"the staging budget of rank {need} ({budget_bytes[need]} bytes); lower the bucket size")
+        placed = False
+        for it in range(len(iters)):
+            if msg[it].get(pair, 0) + nb > bucket_bytes and msg[it].get(pair, 0) > 0:
+                continue
+            if any(staged[it].get(r, 0) + nb > budget_bytes[r] for r in pair if r in budget_bytes):
+                continue
+            placed = True
+            break
+        if not placed:
+            iters.append({}); staged.append({}); msg.append({})
+            it = len(iters) - 1
+        iters[it].setdefault(pair, []).append(d)
+        msg[it][pair] = msg[it].get(pair, 0) + nb
+        for r in pair:
+            staged[it][r] = staged[it].get(r, 0) + nb
+    return iters
+
+
+def iteration_stats(iters, elem_size: int) -> Dict[str, float]:
+    peak = 0
+    for it in iters:
+        per_rank: Dict[int, int] = {}
+        for (s, d), ds in it.items():
+            nb = sum(x.numel for x in ds) * elem_size
+            per_rank[s] = per_rank.get(s, 0) + nb
+            per_rank[d] = per_rank.get(d, 0) + nb
+        peak = max([peak] + list(per_rank.values()))
+    return {"iterations": len(iters), "peak_staged_mb": round(peak / 2 ** 20, 2)}

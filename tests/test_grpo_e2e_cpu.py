@@ -21,10 +21,12 @@ cfg = {
      "data_checkpoint_path": out + "/data_ckpt", "num_episode": int(os.environ.get("EPISODES", "2")),
      "sample_per_episode": 32, "train_micro_batch_size": 4, "train_global_batch_size": 32,
      "num_inference_per_prompt": 4, "save_episode_interval": 1, "max_replay_episode": 2,
+     "bucket_size_mb_in_memory_manager": float(os.environ.get("SYNC_BUCKET_MB", "1024")),
      "log_args_dict": {"log_dir": out}},
   "models": {
     "policy_trainer": {"num_gpu": 2, "fsdp_size": 2, "trainable": True, "generation_batch_size": 8,
        "model_arch": {"preset": "tiny_qwen3"}, "kl_coef": 0.001, "optimizer": {"lr": 1e-5},
+       "reshard_after_forward": os.environ.get("RESHARD", "0") == "1",
        "packing": os.environ.get("PACKING", "0") == "1", "max_token_in_packing": 256, "save_hf": True,
        "free_gpu_memory": {"offload_weights": True, "offload_optimizer_states": os.environ.get("REGEN", "0") != "1",
                            "free_grad_buffers": True}},
@@ -45,7 +47,11 @@ eng = algo.engine
 pol, tr = eng.named_models["policy"], eng.named_models["policy_trainer"]
 # after the final sync the rollout weights equal the trainer weights
 tr.onload()
-sd_t = tr.model.hf_state_dict()
+if os.environ.get("RESHARD", "0") == "1":
+    with tr.state.all_gathered():
+        sd_t = {k: v.clone() for k, v in tr.model.hf_state_dict().items()}
+else:
+    sd_t = tr.model.hf_state_dict()
 sd_p = pol.model.hf_state_dict()
 maxdiff = 0.0
 for k, v in sd_p.items():
@@ -53,7 +59,8 @@ for k, v in sd_p.items():
     maxdiff = max(maxdiff, (v - sd_t[k])[nz].abs().max().item() if nz.any() else 0.0)
 print("RESULT " + json.dumps({"rank": int(os.environ["RANK"]), "episodes": len(stats), "maxdiff": maxdiff,
       "iters": eng.trainer.iteration, "consumed": cfg.runtime_args.consumed_samples,
-      "tps": stats[-1].get("tps_throughput", 0)}))
+      "tps": stats[-1].get("tps_throughput", 0),
+      "sync_iterations": max(g.stats.get("iterations", 0) for g in eng.model_manager.parameter_sync_groups.values())}))
 '''
 
 
@@ -85,6 +92,17 @@ def test_grpo_tiny_packing_tp2(tmp_path):
     outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "PACKING": "1", "TP": "2", "EPISODES": "1"})
     res = _results(outs)
     assert len(res) == 2 and all(r["maxdiff"] == 0.0 for r in res)
+
+
+def test_weight_sync_in_memory_budgeted_iterations(tmp_path):
+    """Parameter-sharded trainer (every rank holds half of each block, so the rollout ranks pull remote pieces),
+    messages capped at 16 KB: the point-to-point weight sync runs as several planned iterations and the rollout
+    weights still equal the trainer's."""
+    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "TP": "2", "EPISODES": "1", "SYNC_BUCKET_MB": "0.015625",
+                                        "RESHARD": "1"})
+    res = _results(outs)
+    assert len(res) == 2 and all(r["maxdiff"] == 0.0 for r in res)
+    assert all(r["sync_iterations"] > 1 for r in res), res
 
 
 def test_resume_continues_from_checkpoint(tmp_path):

@@ -539,3 +539,61 @@ def test_async_rollout_resolves_each_request_when_it_finishes():
     sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
     whole = eng.generate([prompts[0]], sp)[0].output
     assert outs[0] == whole
+
+
+def test_budgeted_iterations_cover_the_plan_within_bucket_and_memory_limits():
+    """The remote pieces of a plan, cut into row bands and scheduled into iterations: every element is moved exactly
+    once, no message exceeds the bucket, no rank stages more than its budget in one iteration, and executing the
+    iterations one after the other gives the same result as the whole plan at once."""
+    from chatlearn_b200.synchronizer.parameter_sync import layout_of_model
+    from chatlearn_b200.synchronizer.plan import build_iterations, build_plan, iteration_stats
+    arch = PRESETS["tiny_moe"]()
+    src_dp, dst_tp = 2, 2
+    full = CausalLM(arch, dtype=torch.float32, pad_to=src_dp).init_weights(11)
+    src_lays, src_bufs = [], {}
+    for r in range(src_dp):
+        shards = {b.name: (r * b.numel // src_dp, (r + 1) * b.numel // src_dp) for b in full.blocks}
+        src_lays.append(layout_of_model(full, r, lambda n, s=shards: s[n], "s/"))
+        src_bufs[r] = {f"s/{b.name}": b.flat[shards[b.name][0]:shards[b.name][1]].clone() for b in full.blocks}
+    dst_lays, dst_bufs, ref_bufs = [], {}, {}
+    for t in range(dst_tp):
+        m = CausalLM(arch, dtype=torch.float32, tp=dst_tp, tp_rank=t)
+        dst_lays.append(layout_of_model(m, t, prefix="d/"))
+        dst_bufs[t] = {f"d/{b.name}": b.flat for b in m.blocks}
+        ref_bufs[t] = {k: torch.zeros_like(v) for k, v in dst_bufs[t].items()}
+    plan = build_plan(src_lays, dst_lays)
+    _run_plan(plan, src_bufs, ref_bufs)
+    remote = sum(d.numel for ds in plan.values() for d in ds if d.src_rank != d.dst_rank)
+    assert remote > 0
+    bucket, budget = 4096, {0: 24 * 1024, 1: 24 * 1024}
+    iters = build_iterations(plan, 4, bucket, budget)
+    assert iters == build_iterations(plan, 4, bucket, budget)                 # every rank derives the same schedule
+    assert len(iters) > 1
+    moved = 0
+    for it in iters:
+        staged = {}
+        for (s, d), ds in it.items():
+            nb = sum(x.numel for x in ds) * 4
+            assert nb <= bucket or len(ds) == 1
+            staged[s] = staged.get(s, 0) + nb
+            staged[d] = staged.get(d, 0) + nb
+            moved += sum(x.numel for x in ds)
+        assert all(v <= budget[r] for r, v in staged.items())
+    assert moved == remote
+    st = iteration_stats(iters, 4)
+    assert st["iterations"] == len(iters) and st["peak_staged_mb"] <= 24 / 1024 + 1e-9
+    # local pieces + the iterations, one after the other, reproduce the one-shot result
+    local = {dst: [d for d in ds if d.src_rank == dst] for dst, ds in plan.items()}
+    _run_plan(local, src_bufs, dst_bufs)
+    for it in iters:
+        by_dst = {}
+        for (s, d), ds in it.items():
+            by_dst.setdefault(d, []).extend(ds)
+        _run_plan(by_dst, src_bufs, dst_bufs)
+    for r in dst_bufs:
+        for k in dst_bufs[r]:
+            assert torch.equal(dst_bufs[r][k], ref_bufs[r][k]), (r, k)
+    # a piece that cannot fit a rank's budget is reported, not silently staged
+    import pytest as _pt
+    with _pt.raises(RuntimeError):
+        build_iterations(plan, 4, 1 << 30, {0: 16, 1: 16})
