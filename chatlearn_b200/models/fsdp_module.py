@@ -5,8 +5,10 @@ sharding, optimizer, weight export for sync, offload, checkpoints, RNG state).
 The reference wraps a HuggingFace model with torch ``fully_shard``; this module
 builds the framework's own ``CausalLM`` over flat parameter blocks and shards the
 optimizer state with ``parallel.zero.ShardedTrainState``.  ``fsdp_size`` smaller
-than the role's GPU count (HSDP) is accepted; optimizer shards then span the
-whole data-parallel group, which yields the same update.
+than the role's GPU count is hybrid sharding (HSDP, the reference's 2-D device mesh
+``(replicate, shard)``): neighbouring ranks form shard groups of ``fsdp_size`` that
+reduce-scatter gradients and all-gather parameters among themselves, and the ranks
+holding the same shard in different groups all-reduce their gradient shards.
 """
 import os
 import random
@@ -34,10 +36,18 @@ class FSDPModule(TorchModule):
     # ------------------------------------------------------------------ groups
     def init(self):
         sp = int(getattr(self.module_args, "ulysses_sequence_parallel_size", 1) or 1)
-        self.mesh = build_mesh(self.placement, sp=sp, kinds=("dp", "sp", "dp_outer"))
+        n = len(self.placement)
+        fs = int(getattr(self.module_args, "fsdp_size", n) or n)
+        hybrid = 0 < fs < n and n % fs == 0
+        kinds = ("dp", "sp", "dp_outer") + (("dp_shard", "dp_rep") if hybrid else ())
+        self.mesh = build_mesh(self.placement, sp=sp, kinds=kinds, shard=fs if hybrid else 0)
+        self.shard_group = self.replica_group = None
         if self.is_member:
             self.role_group = self.mesh.groups["dp"]
             self.dp_group = self.mesh.groups["dp"]           # gradient reduction: all ranks
+            # optimizer-state shards: the whole role, or its shard group under hybrid sharding
+            self.shard_group = self.mesh.groups["dp_shard"] if hybrid else self.dp_group
+            self.replica_group = self.mesh.groups["dp_rep"] if hybrid else None
             self.dp_outer_group = self.mesh.groups["dp_outer"]
             if sp > 1:
                 self.sp = UlyssesGroup(self.mesh.groups["sp"])
@@ -59,7 +69,7 @@ class FSDPModule(TorchModule):
     # ------------------------------------------------------------------ model
     def create_model(self) -> CausalLM:
         arch = resolve_arch(self.module_args)
-        dp = self.dp_group.size if self.dp_group is not None else 1
+        dp = self.shard_group.size if self.shard_group is not None else 1
         # blocks padded so that every rank's shard is a whole number of 16-byte vectors
         model = CausalLM(arch, dtype=self.compute_dtype, device=self.device, pad_to=dp * 8)
         load = getattr(self.module_args, "load", None)
@@ -84,7 +94,7 @@ class FSDPModule(TorchModule):
                 # the tower's weights become one more parameter block: sharded optimizer state, gradient
                 # reduction, offload, checkpoints and the weight sync into the rollout engine cover it
                 from chatlearn_b200.models.nn.vision import attach_vision_block
-                dp = self.dp_group.size if self.dp_group is not None else 1
+                dp = self.shard_group.size if self.shard_group is not None else 1
                 attach_vision_block(self.model, self.vision, pad_to=dp * 8)
         if self.trainable:
             oc = self.module_args.optimizer
@@ -100,10 +110,14 @@ class FSDPModule(TorchModule):
                 assert self.sp is None and self.vision is None, \
                     "parameter sharding is built for text models without Ulysses sequence parallelism"
                 state_cls = ReshardedTrainState
+            extra = {}
+            if self.replica_group is not None:
+                assert state_cls is ShardedTrainState, "hybrid sharding is built for the replicated-parameter state"
+                extra["replica_group"] = self.replica_group
             self.state = state_cls(
-                self.model, self.dp_group, lr=oc.lr, betas=(oc.adam_beta1, oc.adam_beta2),
+                self.model, self.shard_group, lr=oc.lr, betas=(oc.adam_beta1, oc.adam_beta2),
                 eps=getattr(oc, "adam_eps", 1e-8), weight_decay=oc.weight_decay,
-                clip_grad=oc.clip_grad, grad_dtype=grad_dtype)
+                clip_grad=oc.clip_grad, grad_dtype=grad_dtype, **extra)
             # optimizer-step collectives by this package's peer-memory kernels; needs the
             # weights and gradient buffers to stay on the device (symmetric memory)
             fg = self.module_args.free_gpu_memory

@@ -24,6 +24,7 @@ class Mesh:
     ep: int = 1
     etp: int = 1
     sp: int = 1                            # Ulysses (inside dp)
+    shard: int = 0                         # hybrid sharding: ranks per shard group inside dp (0 = all of dp)
     groups: Dict[str, Group] = field(default_factory=dict)
     coords: Dict[str, int] = field(default_factory=dict)
 
@@ -52,6 +53,8 @@ class Mesh:
         c["edp"] = e
         c["sp"] = c["dp"] % self.sp
         c["dp_outer"] = c["dp"] // self.sp
+        shard = self.shard or self.dp
+        c["dp_shard"], c["dp_rep"] = c["dp"] % shard, c["dp"] // shard
         return c
 
     def group_ranks(self, kind: str) -> List[List[int]]:
@@ -59,7 +62,10 @@ class Mesh:
         keys = {"tp": ("cp", "dp", "pp"), "cp": ("tp", "dp", "pp"), "dp": ("tp", "cp", "pp"),
                 "pp": ("tp", "cp", "dp"), "ep": ("etp", "edp", "pp"), "etp": ("ep", "edp", "pp"),
                 "edp": ("etp", "ep", "pp"), "sp": ("tp", "cp", "dp_outer", "pp"),
-                "dp_cp": ("tp", "pp"), "mp": ("dp",), "dp_outer": ("tp", "cp", "sp", "pp")}[kind]
+                "dp_cp": ("tp", "pp"), "mp": ("dp",), "dp_outer": ("tp", "cp", "sp", "pp"),
+                # hybrid sharding: neighbours in dp form a shard group, ranks with the same place in their shard
+                # group form a replica group
+                "dp_shard": ("tp", "cp", "dp_rep", "pp"), "dp_rep": ("tp", "cp", "dp_shard", "pp")}[kind]
         buckets: Dict[tuple, List[int]] = {}
         for r in range(self.world):
             c = self.coord_of(r)
@@ -68,12 +74,13 @@ class Mesh:
 
 
 def build_mesh(ranks: List[int], tp=1, cp=1, pp=1, ep=1, etp=1, sp=1,
-               kinds=("tp", "cp", "dp", "pp", "ep", "edp", "sp", "dp_cp", "mp")) -> Mesh:
+               kinds=("tp", "cp", "dp", "pp", "ep", "edp", "sp", "dp_cp", "mp"), shard=0) -> Mesh:
     """Create the process groups of a role.  Collective over the *whole job*:
     every rank of the job must call it with identical arguments (ranks outside
     ``ranks`` take part in group creation only)."""
-    m = Mesh(list(ranks), tp, cp, pp, ep, etp, sp)
+    m = Mesh(list(ranks), tp, cp, pp, ep, etp, sp, shard)
     assert m.world % (tp * cp * pp) == 0 and m.world % (etp * ep * pp) == 0
+    assert not shard or m.dp % shard == 0, "the shard group size must divide the data-parallel size"
     assert m.dp % sp == 0, "Ulysses size must divide the data-parallel size"
     me = dist.get_rank() if dist.is_initialized() else 0
     role_rank = m.ranks.index(me) if me in m.ranks else -1

@@ -57,8 +57,13 @@ class ShardedTrainState:
                  expert_dp_group: Optional[Group] = None, lr=2e-6, betas=(0.9, 0.95), eps=1e-8,
                  weight_decay=0.01, clip_grad=1.0, grad_dtype=torch.float32,
                  extra_norm_groups: Optional[List[Group]] = None, tp_size: int = 1,
-                 ep_group: Optional[Group] = None, tp_group: Optional[Group] = None):
+                 ep_group: Optional[Group] = None, tp_group: Optional[Group] = None,
+                 replica_group: Optional[Group] = None):
         self.model = model
+        # hybrid sharding (HSDP): ``dp_group`` is the shard group (one node, say); the ranks with the same shard
+        # in the other shard groups form ``replica_group`` and sum their gradient shards after the reduce-scatter,
+        # so parameters are gathered inside the shard group only
+        self.replica = replica_group if (replica_group is not None and replica_group.size > 1) else None
         self.tp_size, self.ep_group, self.tp_group = tp_size, ep_group, tp_group
         # expert tensor parallelism: the expert leaves of the tensor-parallel ranks are different slices
         self.expert_tp_sharded = getattr(model, "etp", 1) > 1
@@ -146,6 +151,9 @@ class ShardedTrainState:
             else:
                 src = s.grad if s.grad.dtype == torch.float32 else s.grad.float()
                 g.reduce_scatter_flat(s.grad_shard, src)
+            if self.replica is not None and g is self.dp:
+                self.replica.all_reduce_(s.grad_shard)
+                s.sq_partial = None          # the squared norm a fused reduce-scatter left predates this sum
 
     @torch.no_grad()
     def _norm_ranges(self, s: "BlockState"):

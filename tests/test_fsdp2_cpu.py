@@ -149,3 +149,57 @@ def test_grpo_end_to_end_with_sharded_parameters(tmp_path):
     assert len(res) == 2
     for r in res:
         assert r["episodes"] == 2 and r["maxdiff"] < 1e-6 and r["hf_saved"], r
+
+
+HSDP = r'''
+import json, os, torch, torch.distributed as dist
+from chatlearn_b200.launcher.initialize import init_distributed
+from chatlearn_b200.models.nn import PRESETS, CausalLM, packed_ctx
+from chatlearn_b200.parallel import build_mesh
+from chatlearn_b200.parallel.zero import ShardedTrainState
+
+init_distributed()
+rank, world = dist.get_rank(), dist.get_world_size()
+mesh = build_mesh(list(range(world)), kinds=("dp", "dp_shard", "dp_rep"), shard=2)
+whole, shard, rep = mesh.groups["dp"], mesh.groups["dp_shard"], mesh.groups["dp_rep"]
+assert shard.ranks == [rank - rank % 2, rank - rank % 2 + 1] and rep.ranks == [rank % 2, rank % 2 + 2]
+dev = torch.device("cpu")
+arch = PRESETS["tiny_qwen3"]()
+ma = CausalLM(arch, dtype=torch.float32, device=dev, pad_to=world * 8).init_weights(7)
+mb = CausalLM(arch, dtype=torch.float32, device=dev, pad_to=world * 8).init_weights(7)
+sa = ShardedTrainState(ma, whole, lr=1e-2, clip_grad=1.0)                       # shards over all four ranks
+sb = ShardedTrainState(mb, shard, lr=1e-2, clip_grad=1.0, replica_group=rep)    # two shard groups of two
+res = {"rank": rank, "norm": [], "shard_fraction": sb.states[0].shard_numel / sb.states[0].block.numel}
+for step in range(2):
+    sa.zero_grad(); sb.zero_grad()
+    torch.manual_seed(100 * step + rank)
+    lens = [11 + rank, 23, 6]
+    T = sum(lens)
+    toks = torch.randint(0, arch.vocab_size - 1, (T,))
+    for m in (ma, mb):
+        ctx, _ = packed_ctx(lens, dev)
+        lp, ent = m.logprobs(toks, toks.roll(-1), ctx)
+        (-(lp.sum() + 0.01 * ent.sum()) / T).backward()
+    na, nb = sa.step(), sb.step()
+    res["norm"].append((float(na), float(nb)))
+res["param_diff"] = max((x.flat - y.flat).abs().max().item() for x, y in zip(ma.blocks, mb.blocks))
+# every rank of the job holds the same parameters afterwards
+ref = [b.flat.clone() for b in mb.blocks]
+for t in ref:
+    dist.broadcast(t, 0)
+res["rank_diff"] = max((x.flat - t).abs().max().item() for x, t in zip(mb.blocks, ref))
+print("RESULT " + json.dumps(res))
+'''
+
+
+def test_hybrid_sharding_matches_sharding_over_all_ranks():
+    """Four ranks as two shard groups of two (reduce-scatter and all-gather inside a group, all-reduce of the
+    gradient shards between the groups) against one shard group of four: same gradient norm, same parameters."""
+    outs, _ = run_ranks(HSDP, 4)
+    res = _results(outs)
+    assert len(res) == 4
+    for r in res:
+        assert abs(r["shard_fraction"] - 0.5) < 1e-6
+        for na, nb in r["norm"]:
+            assert abs(na - nb) < 1e-4 * max(1.0, abs(na)), r
+        assert r["param_diff"] < 5e-4 and r["rank_diff"] == 0.0, r

@@ -24,7 +24,7 @@ cfg = {
      "bucket_size_mb_in_memory_manager": float(os.environ.get("SYNC_BUCKET_MB", "1024")),
      "log_args_dict": {"log_dir": out}},
   "models": {
-    "policy_trainer": {"num_gpu": 2, "fsdp_size": 2, "trainable": True, "generation_batch_size": 8,
+    "policy_trainer": {"num_gpu": 2, "fsdp_size": int(os.environ.get("FSDP_SIZE", "2")), "trainable": True, "generation_batch_size": 8,
        "model_arch": {"preset": "tiny_qwen3"}, "kl_coef": 0.001, "optimizer": {"lr": 1e-5},
        "reshard_after_forward": os.environ.get("RESHARD", "0") == "1",
        "packing": os.environ.get("PACKING", "0") == "1", "max_token_in_packing": 256, "save_hf": True,
@@ -103,6 +103,13 @@ def test_weight_sync_in_memory_budgeted_iterations(tmp_path):
     res = _results(outs)
     assert len(res) == 2 and all(r["maxdiff"] == 0.0 for r in res)
     assert all(r["sync_iterations"] > 1 for r in res), res
+
+
+def test_hybrid_sharding_two_replicas_of_one(tmp_path):
+    """``fsdp_size`` 1 on two GPUs: every rank is its own shard group and the two all-reduce their gradients."""
+    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "EPISODES": "1", "FSDP_SIZE": "1"})
+    res = _results(outs)
+    assert len(res) == 2 and all(r["episodes"] == 1 and r["maxdiff"] == 0.0 for r in res)
 
 
 def test_resume_continues_from_checkpoint(tmp_path):
