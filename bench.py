@@ -42,6 +42,10 @@ def parse():
     p.add_argument("--pack-tokens", type=int, default=16384)
     p.add_argument("--gemm", default=None, choices=[None, "tcgen05", "cublas"])
     p.add_argument("--no-offload", action="store_true")
+    p.add_argument("--rollout-tp", type=int, default=1,
+                   help="tensor-parallel size of a rollout replica (1: every GPU generates for its own samples; 2: pairs "
+                        "of GPUs share a replica through the fused GEMM + all-reduce kernel, 13.1 ms per decode step of "
+                        "256 sequences against 10.4 ms for 128 on one GPU)")
     p.add_argument("--reshard", action="store_true",
                    help="parameter-sharded trainer (FSDP2 reshard_after_forward): 1/N of parameters, gradients and "
                         "optimizer state resident per GPU instead of whole bf16 parameters and fp32 gradients")
@@ -134,7 +138,7 @@ def vs_baseline(n_gpu, value, args):
 
 
 def build_config(args, out_dir, data_path, n_gpu):
-    tp = 2 if n_gpu >= 2 else 1
+    tp = max(1, min(int(args.rollout_tp), n_gpu))
     n = args.samples_per_prompt
     spe = args.prompts_per_gpu * n * n_gpu
     offload = not args.no_offload
@@ -321,7 +325,7 @@ def main():
             "impl": args.impl if args.impl == "native" else "library trainer (cuBLAS + flash-attn + PyTorch statements), native rollout",
             "config": {"model": args.model, "global_batch": samples, "seq_len": seq,
                        "trainer_parameters": "sharded 1/N per GPU (gathered per segment)" if args.reshard else "whole per GPU (optimizer state sharded)",
-                       "parallelism": f"trainer zero-dp{world} + rollout tp{2 if world >= 2 else 1}x{max(world // 2, 1) if world >= 2 else 1}",
+                       "parallelism": f"trainer zero-dp{world} + rollout tp{max(1, min(args.rollout_tp, world))}x{world // max(1, min(args.rollout_tp, world))}",
                        "prompts": samples // args.samples_per_prompt, "samples_per_prompt": args.samples_per_prompt,
                        "prompt_len": args.prompt_len, "max_response": args.max_response,
                        "pack_tokens": args.pack_tokens, "mini_batches_per_step": 2,
