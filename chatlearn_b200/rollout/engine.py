@@ -102,6 +102,10 @@ class RolloutEngine:
         self.use_graphs = use_cuda_graphs
         self._graphs: Dict[Any, Any] = {}
         self._gs = None
+        # pipelined decode: the step launched last whose sampled tokens the host has not read yet
+        self._pending = None
+        self._finished_buf: List[Sequence] = []
+        self.pipelined = os.environ.get("CLB200_PIPELINED_DECODE", "0") != "0"
 
     # ------------------------------------------------------------------ memory
     def kv_bytes_per_block(self) -> int:
@@ -304,11 +308,17 @@ class RolloutEngine:
             n = min(b for b in self._BUCKETS if b >= n) if n <= self._BUCKETS[-1] else n
             width = math.ceil(self.max_model_len / self.block_size)
             z = lambda dt, *shape: torch.zeros(*shape, dtype=dt, device=dev)  # noqa: E731
-            in64 = z(torch.long, 4, n)          # rows: token, position, KV slot, sequence length
-            self._gs = dict(n=n, width=width, in64=in64, tokens=in64[0], pos=in64[1],
+            # rows: token (when the host knows it), position, KV slot, sequence length, and for a token that is
+            # still on the device its row in the previous step's batch plus a flag
+            in64 = z(torch.long, 6, n)
+            self._gs = dict(n=n, width=width, in64=in64, tokens=z(torch.long, n), pos=in64[1],
                             slots=in64[2], seq_lens=z(torch.int32, n), bt=z(torch.int32, n, width),
                             u=z(torch.float32, n), ids=z(torch.long, n), lp=z(torch.float32, n),
-                            stage=torch.zeros(4, n, dtype=torch.int64, pin_memory=True),
+                            stage=torch.zeros(6, n, dtype=torch.int64, pin_memory=True),
+                            out_dev=[z(torch.float32, 2, n) for _ in range(2)],
+                            out_host=[torch.zeros(2, n, dtype=torch.float32, pin_memory=True) for _ in range(2)],
+                            out_event=[torch.cuda.Event() for _ in range(2)] if dev.type == "cuda" else [None, None],
+                            parity=0,
                             bt_host=torch.zeros(n, width, dtype=torch.int32, pin_memory=True),
                             bt_len=[0] * n, bt_owner=[None] * n,
                             # sequences that share their first KV blocks (the samples of one prompt): up to n / 2
@@ -358,11 +368,15 @@ class RolloutEngine:
         scratch_block = self.num_blocks          # one block past the allocator's range
         # plain Python lists, one tensor construction: per-element tensor writes would
         # cost more host time than the whole step takes on the GPU
-        rows = [[0] * Bg, [0] * Bg, [scratch_block * bs] * Bg, [1] * Bg]
+        rows = [[0] * Bg, [0] * Bg, [scratch_block * bs] * Bg, [1] * Bg, [0] * Bg, [0] * Bg]
         owner, blen = gs["bt_owner"], gs["bt_len"]
         for i, s in enumerate(seqs):
             p = s.num_computed                   # position of the token fed now
-            rows[0][i] = s.output[-1] if s.output else s.prompt[-1]
+            if s.inflight:
+                # sampled by the step before, not read back yet: the device takes it from that step's output
+                rows[4][i], rows[5][i] = s._row, 1
+            else:
+                rows[0][i] = s.output[-1] if s.output else s.prompt[-1]
             rows[1][i] = p + s.rope_delta        # rotary position (text after images is shifted)
             rows[2][i] = s.blocks[p // bs] * bs + p % bs
             rows[3][i] = p + 1
@@ -391,6 +405,9 @@ class RolloutEngine:
         st[:, :Bg] = torch.tensor(rows, dtype=torch.int64)
         gs["in64"].copy_(st, non_blocking=True)              # one pinned -> device copy per step
         gs["seq_lens"].copy_(gs["in64"][3])                   # int64 -> int32 on the device
+        # input tokens: from the host where it knows them, else from the previous step's samples on the device
+        # (outside the captured graph: a warm-up run of the body overwrites ``ids``)
+        torch.where(gs["in64"][5] != 0, gs["ids"].index_select(0, gs["in64"][4]), gs["in64"][0], out=gs["tokens"])
         xfer.h2d_bytes += st.numel() * 8
         gs["u"][:Bg].copy_(torch.rand(Bg, device=self.device, generator=self.gen))
         sp = seqs[0].sampling
@@ -481,14 +498,87 @@ class RolloutEngine:
         k0 = sp0.key()
         return all(s.sampling is sp0 or s.sampling.key() == k0 for s in plan.seqs)
 
+    # ------------------------------------------------------------------ pipelined decode
+    # A captured decode step ends with the sampled tokens on the device.  The next step's inputs (positions, KV
+    # slots, block tables) do not depend on their values, and its input tokens can be taken from the device, so
+    # the next step is launched first and the previous step's tokens are read back while it runs: the host's
+    # work per step (scheduling, staging, appending tokens, stop checks) overlaps the GPU instead of adding to it.
+    # Stop conditions that depend on a token's value (EOS, stop tokens) are therefore seen one step late: the
+    # sequence takes part in one more step whose token is dropped.  A sequence whose pending token is its last by
+    # length is known in advance and left out of the next step.
+    def _last_by_length(self, s: Sequence) -> bool:
+        return len(s.output) + s.inflight >= s.max_new_tokens or s.length + s.inflight >= self.max_model_len
+
+    def _start_readback(self, seqs, ids, lps):
+        """Snapshot the step's samples and start their copy to pinned host memory; returns the pending record."""
+        gs = self._gs
+        par = gs["parity"]
+        gs["parity"] = par ^ 1
+        B = len(seqs)
+        dev_buf, host_buf = gs["out_dev"][par], gs["out_host"][par]
+        dev_buf[0, :B].copy_(ids)                      # token ids are exact in fp32: vocab < 2^24
+        dev_buf[1, :B].copy_(lps)
+        host_buf[:, :B].copy_(dev_buf[:, :B], non_blocking=True)
+        gs["out_event"][par].record()
+        xfer.d2h_bytes += 2 * B * 4
+        return {"seqs": list(seqs), "par": par}
+
+    def _complete(self, pend, sched: Scheduler, eos_id):
+        """Wait for a launched step's tokens, append them and apply the stop conditions."""
+        gs = self._gs
+        gs["out_event"][pend["par"]].synchronize()
+        B = len(pend["seqs"])
+        both = gs["out_host"][pend["par"]][:, :B].tolist()
+        for s in pend["seqs"]:
+            s.inflight = 0
+        live = [(s, int(t), lp) for s, t, lp in zip(pend["seqs"], both[0], both[1]) if not s.finished]
+        self._apply_tokens(sched, live, eos_id)
+
+    def drain(self, sched: Scheduler, eos_id):
+        """Read back the step that is still in flight, if any."""
+        pend, self._pending = self._pending, None
+        if pend is not None:
+            self._complete(pend, sched, eos_id)
+
+    def take_finished(self) -> List[Sequence]:
+        out, self._finished_buf = self._finished_buf, []
+        return out
+
     @torch.no_grad()
     def step(self, sched: Scheduler, plan: StepPlan, eos_id: Optional[int]):
+        pend = self._pending
         if self._can_graph(plan):
-            ids, lps = self._graph_decode(plan)
-            for s in plan.seqs:
-                s.num_computed += 1
-            self._finish_step(sched, plan.seqs, ids, lps, eos_id)
+            seqs = plan.seqs
+            if pend is not None:
+                # sequences whose token in flight is their last one do not decode again
+                seqs = [s for s in seqs if not (s.inflight and self._last_by_length(s))]
+            if seqs:
+                part = plan if len(seqs) == len(plan.seqs) else StepPlan(seqs, [1] * len(seqs), False, [True] * len(seqs))
+                ids, lps = self._graph_decode(part)
+                for s in seqs:
+                    s.num_computed += 1
+                if not self.pipelined:
+                    self._finish_step(sched, seqs, ids, lps, eos_id)
+                    return
+                new = self._start_readback(seqs, ids, lps)
+                if pend is not None:
+                    self._complete(pend, sched, eos_id)      # the previous step's tokens, while this one runs
+                for i, s in enumerate(seqs):
+                    s.inflight, s._row = 1, i
+                self._pending = new
+                return
+            self.drain(sched, eos_id)
             return
+        if pend is not None:
+            # this step needs the host to know every token: finish the step in flight first and drop the
+            # sequences that turn out to have ended with it
+            self.drain(sched, eos_id)
+            if any(s.finished for s in plan.seqs):
+                keep = [i for i, s in enumerate(plan.seqs) if not s.finished]
+                if not keep:
+                    return
+                plan = StepPlan([plan.seqs[i] for i in keep], [plan.q_lens[i] for i in keep], plan.is_prefill,
+                                [plan.samples[i] for i in keep])
         tokens, ctx, last_rows = self._build_inputs(plan)
         x = None
         if self._embed_patch is not None:
@@ -541,8 +631,10 @@ class RolloutEngine:
         """Read the sampled tokens back and apply the stop conditions."""
         # one device -> host read per step (token ids are exact in fp32: vocab < 2^24)
         both = xfer.tolist(torch.stack([ids.float(), lps.float()]))
-        ids_h, lps_h = [int(x) for x in both[0]], both[1]
-        for s, tok, lp in zip(seqs, ids_h, lps_h):
+        self._apply_tokens(sched, [(s, int(t), lp) for s, t, lp in zip(seqs, both[0], both[1])], eos_id)
+
+    def _apply_tokens(self, sched: Scheduler, triples, eos_id):
+        for s, tok, lp in triples:
             s.output.append(tok)
             s.logprobs.append(lp)
             sp = s.sampling
@@ -550,10 +642,12 @@ class RolloutEngine:
                 sched.finish(s, "stop")
             elif len(s.output) >= s.max_new_tokens or s.length >= self.max_model_len:
                 sched.finish(s, "length")
-            if s.finished and self.arch.layer_types is not None:
-                slot = self._state_slot.pop(id(s), None)
-                if slot is not None:
-                    self._free_state_slots.append(slot[0])
+            if s.finished:
+                self._finished_buf.append(s)
+                if self.arch.layer_types is not None:
+                    slot = self._state_slot.pop(id(s), None)
+                    if slot is not None:
+                        self._free_state_slots.append(slot[0])
 
     @torch.no_grad()
     def _idle_step(self):
@@ -677,6 +771,10 @@ class RolloutSession:
         eng, sched = self.engine, self.sched
         out, self._instant = self._instant, []
         busy = sched.has_work()
+        if not busy and eng._pending is not None:
+            eng.drain(sched, self.eos_id)                # the last step's tokens (all dropped or final)
+            out.extend(eng.take_finished())
+            busy = sched.has_work()
         lock = eng.lockstep is not None and eng.lockstep.size > 1
         if lock:
             import torch.distributed as dist
@@ -702,12 +800,14 @@ class RolloutSession:
         kind = "decode" if max(plan.q_lens) == 1 else "prefill"
         self.tm[kind + "_s"] += time.perf_counter() - t1
         self.tm[kind + "_steps"] += 1
-        out.extend(s for s in plan.seqs if s.finished)
+        out.extend(eng.take_finished())
         return out
 
     def close(self):
         """Publish the session's statistics on the engine and check the peer-memory status words."""
         eng = self.engine
+        eng.drain(self.sched, self.eos_id)
+        eng.take_finished()
         eng.stats = dict(self.sched.stats)
         eng.stats.update(self.tm)
         if eng.ep_symm is not None:

@@ -82,6 +82,9 @@ class Sequence:
     # text after the images sits at position index + rope_delta
     mm: Optional[dict] = None
     rope_delta: int = 0
+    # tokens sampled on the device whose values the host has not read yet (pipelined decode: 0 or 1); they
+    # count for block allocation and positions, their values arrive one step later
+    inflight: int = 0
 
     @property
     def tokens(self) -> List[int]:
@@ -244,7 +247,7 @@ class Scheduler:
         budget = self.max_tokens
         seqs, q_lens, samples = [], [], []
         # sequences already admitted but with prompt KV still missing come first
-        partial = [s for s in self.running if s.length - s.num_computed > 1]
+        partial = [s for s in self.running if s.length + s.inflight - s.num_computed > 1]
         for s in partial:
             if budget <= 0:
                 break
@@ -299,7 +302,7 @@ class Scheduler:
         for s in list(self.running):
             if id(s) in gone:
                 continue
-            while not self._ensure_blocks(s, s.length):
+            while not self._ensure_blocks(s, s.length + s.inflight):
                 victim = self._preempt_one(keep=s)
                 if victim is None:
                     raise RuntimeError("KV cache too small for one sequence")

@@ -95,3 +95,48 @@ def test_grouped_decode_gives_the_same_generations(monkeypatch):
     assert launches["1"] > 0 and launches["0"] == 0
     agree = sum(a[:8] == b[:8] for a, b in zip(outs["1"], outs["0"]))
     assert agree >= len(batch) - 2, (agree, len(batch))           # bf16 near-ties may flip a greedy choice late in a sequence
+
+
+def test_pipelined_decode_gives_the_same_generations(monkeypatch):
+    """The decode step is launched before the previous step's tokens are read back.  Sequences that stop on a
+    token value (seen one step late), on their length budget (known in advance) and requests that join late
+    must come out exactly as with a read-back after every step."""
+    from chatlearn_b200.models.nn import ModelArch, CausalLM
+    from chatlearn_b200.rollout import RolloutEngine, SamplingParams
+    dev = torch.device("cuda", 0)
+    arch = ModelArch(model_type="qwen3", vocab_size=2048, hidden_size=512, num_hidden_layers=2, num_attention_heads=8,
+                     num_key_value_heads=2, head_dim=128, intermediate_size=1024, rope_theta=1e6)
+    model = CausalLM(arch, dtype=torch.bfloat16, device=dev).init_weights(3)
+    g = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(0, arch.vocab_size - 1, (n,), generator=g).tolist() for n in (90, 33, 150, 64, 65, 7)]
+    budgets = [40, 3, 17, 1, 25, 40]
+    # a first pass finds tokens that the greedy generations really produce, to use as stop tokens
+    eng = RolloutEngine(model, block_size=64, num_blocks=128, max_num_seqs=16, max_model_len=256)
+    free = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True), max_new_tokens=budgets)
+    stops = (free[0].output[11], free[5].output[20])
+    sp = SamplingParams(temperature=0.0, max_tokens=40, stop_token_ids=stops)
+    res = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("CLB200_PIPELINED_DECODE", flag)
+        eng = RolloutEngine(model, block_size=64, num_blocks=128, max_num_seqs=16, max_model_len=256)
+        assert eng.pipelined == (flag == "1")
+        sess = eng.open_session(eos_id=-1)
+        seqs = [sess.submit(p, sp, b) for p, b in zip(prompts[:5], budgets[:5])]
+        steps, order = 0, []
+        while True:
+            done = sess.poll()
+            if done is None:
+                break
+            steps += 1
+            order += [s.req_id - seqs[0].req_id for s in done]
+            if steps == 6:
+                seqs.append(sess.submit(prompts[5], sp, budgets[5]))      # joins the running batch
+        sess.close()
+        res[flag] = [(s.output, s.finish_reason, [round(x, 3) for x in s.logprobs]) for s in seqs]
+        assert sorted(order) == list(range(6)) and all(s.finished and not s.inflight for s in seqs)
+    for a, b in zip(res["1"], res["0"]):
+        assert a[0] == b[0] and a[1] == b[1], (a[:2], b[:2])
+        assert max(abs(x - y) for x, y in zip(a[2], b[2])) < 1e-3
+    reasons = [r[1] for r in res["1"]]
+    assert reasons[0] == "stop" and len(res["1"][0][0]) <= 12 and reasons[1] == "length" and reasons[3] == "length"
+    assert len(res["1"][3][0]) == 1 and len(res["1"][1][0]) == 3
