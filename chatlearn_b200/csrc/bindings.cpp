@@ -85,11 +85,15 @@ bool attn_varlen_fwd_supported(int64_t head_dim);
 std::vector<at::Tensor> attn_varlen_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                         const at::Tensor& cu_seqlens, double scale, bool causal);
 at::Tensor grouped_gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets);
+at::Tensor grouped_gemm_bf16_nn(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets);
+at::Tensor grouped_gemm_bf16_tn(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets, at::Tensor out,
+                                bool accumulate);
 std::vector<at::Tensor> moe_router_topk(const at::Tensor& logits, int64_t k, bool sigmoid, bool norm,
                                         const c10::optional<at::Tensor>& bias, int64_t n_group, int64_t topk_group,
                                         double scale);
-std::vector<at::Tensor> moe_permute(const at::Tensor& x, const at::Tensor& idx, const at::Tensor& offsets);
-at::Tensor moe_permute_at(const at::Tensor& x, const at::Tensor& pos, const c10::optional<at::Tensor>& scale);
+std::vector<at::Tensor> moe_permute(const at::Tensor& x, const at::Tensor& idx, const at::Tensor& offsets, int64_t total_rows);
+at::Tensor moe_permute_at(const at::Tensor& x, const at::Tensor& pos, const c10::optional<at::Tensor>& scale,
+                          int64_t total_rows);
 at::Tensor moe_combine(const at::Tensor& y, const at::Tensor& pos, const c10::optional<at::Tensor>& weights);
 at::Tensor moe_row_dot(const at::Tensor& dy, const at::Tensor& y, const at::Tensor& pos);
 at::Tensor symm_ar_residual_rmsnorm(const std::vector<int64_t>& part_ptrs, const std::vector<int64_t>& flag_ptrs,
@@ -155,9 +159,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_varlen_fwd_supported", &attn_varlen_fwd_supported);
   m.def("attn_varlen_fwd", &attn_varlen_fwd);
   m.def("grouped_gemm_bf16_nt", &grouped_gemm_bf16_nt);
+  m.def("grouped_gemm_bf16_nn", &grouped_gemm_bf16_nn);
+  m.def("grouped_gemm_bf16_tn", &grouped_gemm_bf16_tn, py::arg("a"), py::arg("b"), py::arg("offsets"), py::arg("out"),
+        py::arg("accumulate") = false);
   m.def("moe_router_topk", &moe_router_topk);
-  m.def("moe_permute", &moe_permute);
-  m.def("moe_permute_at", &moe_permute_at);
+  m.def("moe_permute", &moe_permute, py::arg("x"), py::arg("idx"), py::arg("offsets"), py::arg("total_rows") = -1);
+  m.def("moe_permute_at", &moe_permute_at, py::arg("x"), py::arg("pos"), py::arg("scale"), py::arg("total_rows") = -1);
   m.def("moe_combine", &moe_combine);
   m.def("moe_row_dot", &moe_row_dot);
   m.def("symm_ar_residual_rmsnorm", &symm_ar_residual_rmsnorm);

@@ -144,6 +144,10 @@ struct GroupArgs {
   void* peer_out[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int n_peer = 0;
   int accumulate = 0;       // fp32 output only: C += A*B instead of C = A*B
+  // ragged_m > 0: grouped weight gradient.  The contraction runs over a group's rows: table entries are
+  // {first C row, end C row, first K row, end K row}; C is [groups * ragged_m, N] and a tile's columns of
+  // the (MN-major) A operand start at (first C row) % ragged_m.
+  int ragged_m = 0;
 };
 
 // Origin of a work tile: (first A/C row, first column, first B row of the group, end row).
@@ -207,7 +211,13 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
         int m0, n0, b0, row_end;
         unit_origin(grp, unit % num_tiles, tiles_m, tiles_n, M, m0, n0, b0, row_end, BN);
-        const int k_begin = (unit / num_tiles) * k_per_split, k_end = min(k_begin + k_per_split, k_iters);
+        int k_begin = (unit / num_tiles) * k_per_split, k_end = min(k_begin + k_per_split, k_iters);
+        int a_m0 = m0, a_k0 = 0;                   // ragged: A columns of the tile, first K row of the group
+        if (grp.ragged_m > 0) {
+          const int4 e = grp.table[(unit % num_tiles) / tiles_n];
+          a_m0 = e.x % grp.ragged_m; a_k0 = e.z;
+          k_begin = 0; k_end = (e.w - e.z + BK - 1) / BK;
+        }
         for (int k = k_begin; k < k_end; ++k) {
           if (!mbar_wait(&sm->empty[stage], phase ^ 1)) { ok = false; break; }
           mbar_expect_tx(&sm->full[stage], kStageBytesA + kStageBytesB);
@@ -216,7 +226,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)      // boxes of 64 M-columns x BK K-rows
-              tma_load_2d(sm->a[stage] + j * (BK * 128), &tmA, &sm->full[stage], m0 + j * 64, k * BK);
+              tma_load_2d(sm->a[stage] + j * (BK * 128), &tmA, &sm->full[stage], a_m0 + j * 64, a_k0 + k * BK);
           }
           if constexpr (BMN == 0) {
             tma_load_2d(sm->b[stage], &tmB, &sm->full[stage], k * BK, b0 + n0);
@@ -240,7 +250,11 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
-        const int k_begin = (unit / num_tiles) * k_per_split, k_end = min(k_begin + k_per_split, k_iters);
+        int k_begin = (unit / num_tiles) * k_per_split, k_end = min(k_begin + k_per_split, k_iters);
+        if (grp.ragged_m > 0) {
+          const int4 e = grp.table[(unit % num_tiles) / tiles_n];
+          k_begin = 0; k_end = (e.w - e.z + BK - 1) / BK;
+        }
         if (!mbar_wait(&sm->acc_empty[acc], acc_phase ^ 1)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -271,7 +285,11 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
       int m0, n0, b0, row_end;
       unit_origin(grp, unit % num_tiles, tiles_m, tiles_n, M, m0, n0, b0, row_end, BN);
-      const bool empty_slice = (unit / num_tiles) * k_per_split >= k_iters;   // nothing was accumulated
+      bool empty_slice = (unit / num_tiles) * k_per_split >= k_iters;   // nothing was accumulated
+      if (grp.ragged_m > 0) {
+        const int4 e = grp.table[(unit % num_tiles) / tiles_n];
+        empty_slice = e.w <= e.z;
+      }
       if (!mbar_wait(&sm->acc_full[acc], acc_phase)) { ok = false; break; }
       tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
@@ -632,6 +650,115 @@ at::Tensor grouped_gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, const 
   launch_gemm<bf16, 256, 0, 0>(a.get_device(), grid, st, tmA, tmB, (bf16*)c.data_ptr(), nullptr, capacity * BM, (int)N, (int)K,
                                (int)N, 1, g);
   return c;
+}
+
+// Input gradient of grouped expert layers: C[r] = a[r] * b[g] for the rows r of group g, with b [G, K, N]
+// (a group's weight as stored for the forward, rows = the forward's output features).  a [R, K] bf16 rows sorted
+// by group, offsets [G+1] int64 on the device.  Returns C [R, N] bf16; rows outside every group are not written.
+at::Tensor grouped_gemm_bf16_nn(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && offsets.is_cuda(), "grouped_gemm_nn: CUDA tensors");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && offsets.scalar_type() == at::kLong,
+              "grouped_gemm_nn: bf16 operands, int64 offsets");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 3 && a.size(1) == b.size(1) && a.is_contiguous() && b.is_contiguous(),
+              "grouped_gemm_nn: A [R, K], B [G, K, N], contiguous");
+  const int64_t R = a.size(0), K = a.size(1), G = b.size(0), N = b.size(2);
+  TORCH_CHECK(offsets.numel() == G + 1 && G <= 1024, "grouped_gemm_nn: offsets [G+1], at most 1024 groups");
+  // a K tile of B that runs past a group's K rows reads the next group's: A's columns there must not exist
+  TORCH_CHECK(K % BK == 0 && N % 8 == 0 && K > 0, "grouped_gemm_nn: K must be a multiple of 64, N of 8");
+  TORCH_CHECK(((uintptr_t)a.data_ptr() % 16 == 0) && ((uintptr_t)b.data_ptr() % 16 == 0), "grouped_gemm_nn: 16-byte aligned operands");
+  auto c = at::empty({R, N}, a.options());
+  if (R == 0) return c;
+  bind_context_to_thread(a.get_device());
+  const int capacity = (int)((R + BM - 1) / BM + G);
+  auto table = at::empty({capacity, 4}, a.options().dtype(at::kInt));
+  auto count = at::empty({1}, a.options().dtype(at::kInt));
+  auto st = at::cuda::getCurrentCUDAStream();
+  build_group_table_kernel<<<1, 1024, 0, st>>>(offsets.data_ptr<int64_t>(), (int)G, (int)K, capacity,
+                                               reinterpret_cast<int4*>(table.data_ptr<int>()), count.data_ptr<int>());
+  CUtensorMap tmA = make_tmap_bf16(a.data_ptr(), R, K, K, BM);
+  CUtensorMap tmB = make_tmap_bf16(b.data_ptr(), G * K, N, N, BK);      // MN-major: boxes of 64 N x 64 K rows
+  const int num_sms = device_sms(a.get_device());
+  const int tiles_n = (int)((N + BN - 1) / BN);
+  const int grid = std::min(capacity * tiles_n, num_sms);
+  GroupArgs g;
+  g.table = reinterpret_cast<const int4*>(table.data_ptr<int>());
+  g.count = count.data_ptr<int>();
+  launch_gemm<bf16, 256, 0, 1>(a.get_device(), grid, st, tmA, tmB, (bf16*)c.data_ptr(), nullptr, capacity * BM, (int)N, (int)K,
+                               (int)N, 1, g);
+  return c;
+}
+
+// Row tiles of a grouped weight gradient: group g with rows [lo, hi) gets ceil(m / BM) entries
+// {g * m + t * BM, (g + 1) * m, lo, hi}; empty groups get none (their part of C keeps what it holds).
+static __global__ void build_ragged_table_kernel(const int64_t* __restrict__ offsets, int num_groups, int m, int capacity,
+                                                 int4* __restrict__ table, int* __restrict__ count) {
+  __shared__ int scan[1024];
+  const int g = threadIdx.x;
+  int lo = 0, hi = 0;
+  if (g < num_groups) { lo = (int)offsets[g]; hi = (int)offsets[g + 1]; }
+  const int mine = hi > lo ? (m + BM - 1) / BM : 0;
+  scan[g] = mine;
+  __syncthreads();
+  for (int d = 1; d < 1024; d <<= 1) {
+    const int v = g >= d ? scan[g - d] : 0;
+    __syncthreads();
+    scan[g] += v;
+    __syncthreads();
+  }
+  int at = scan[g] - mine;
+  for (int t = 0; t < mine && at < capacity; ++t, ++at)
+    table[at] = make_int4(g * m + t * BM, (g + 1) * m, lo, hi);
+  if (g == 1023) count[0] = min(scan[1023], capacity);
+}
+
+// Weight gradient of grouped expert layers: C[g] (+)= a[rows of g]^T * b[rows of g], a [R, M] and b [R, N] bf16 with
+// rows sorted by group.  Every group must start at a multiple of 64 rows, and the rows between a group's last
+// row and the next group's first must be zero in a or in b (the contraction runs in tiles of 64 rows).
+// offsets [G+1] int64 on the device.  `out` [G, M, N]: bf16 (overwritten; groups without rows are zeroed) or fp32
+// (accumulate = true adds).  Returns out.
+at::Tensor grouped_gemm_bf16_tn(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets, at::Tensor out,
+                                bool accumulate) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && offsets.is_cuda() && out.is_cuda(), "grouped_gemm_tn: CUDA tensors");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && offsets.scalar_type() == at::kLong,
+              "grouped_gemm_tn: bf16 operands, int64 offsets");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(0) == b.size(0) && a.is_contiguous() && b.is_contiguous(),
+              "grouped_gemm_tn: A [R, M], B [R, N], contiguous");
+  const int64_t R = a.size(0), M = a.size(1), N = b.size(1), G = offsets.numel() - 1;
+  TORCH_CHECK(out.dim() == 3 && out.size(0) == G && out.size(1) == M && out.size(2) == N && out.is_contiguous(),
+              "grouped_gemm_tn: out [G, M, N], contiguous");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat, "grouped_gemm_tn: bf16 or fp32 out");
+  TORCH_CHECK(!accumulate || out.scalar_type() == at::kFloat, "grouped_gemm_tn: accumulation needs an fp32 out");
+  TORCH_CHECK(G >= 1 && G <= 1024 && M % 8 == 0 && N % 8 == 0, "grouped_gemm_tn: 1..1024 groups, M and N multiples of 8");
+  TORCH_CHECK(((uintptr_t)a.data_ptr() % 16 == 0) && ((uintptr_t)b.data_ptr() % 16 == 0) && ((uintptr_t)out.data_ptr() % 16 == 0),
+              "grouped_gemm_tn: 16-byte aligned operands");
+  if (!accumulate) out.zero_();
+  if (R == 0) return out;
+  bind_context_to_thread(a.get_device());
+  const int tiles_m = (int)((M + BM - 1) / BM);
+  const int capacity = (int)(G * tiles_m);
+  auto table = at::empty({capacity, 4}, a.options().dtype(at::kInt));
+  auto count = at::empty({1}, a.options().dtype(at::kInt));
+  auto st = at::cuda::getCurrentCUDAStream();
+  build_ragged_table_kernel<<<1, 1024, 0, st>>>(offsets.data_ptr<int64_t>(), (int)G, (int)M, capacity,
+                                                reinterpret_cast<int4*>(table.data_ptr<int>()), count.data_ptr<int>());
+  CUtensorMap tmA = make_tmap_bf16(a.data_ptr(), R, M, M, BK);      // MN-major: boxes of 64 columns x 64 rows
+  CUtensorMap tmB = make_tmap_bf16(b.data_ptr(), R, N, N, BK);
+  const int num_sms = device_sms(a.get_device());
+  const int tiles_n = (int)((N + BN - 1) / BN);
+  const int grid = std::min(capacity * tiles_n, num_sms);
+  GroupArgs g;
+  g.table = reinterpret_cast<const int4*>(table.data_ptr<int>());
+  g.count = count.data_ptr<int>();
+  g.ragged_m = (int)M;
+  g.accumulate = accumulate ? 1 : 0;
+  // K is only used for the split-K bookkeeping, which this mode does not use (one slice)
+  if (out.scalar_type() == at::kFloat)
+    launch_gemm<float, 256, 1, 1>(a.get_device(), grid, st, tmA, tmB, out.data_ptr<float>(), nullptr, capacity * BM, (int)N, (int)R,
+                                  (int)N, 1, g);
+  else
+    launch_gemm<bf16, 256, 1, 1>(a.get_device(), grid, st, tmA, tmB, (bf16*)out.data_ptr(), nullptr, capacity * BM, (int)N, (int)R,
+                                 (int)N, 1, g);
+  return out;
 }
 
 // Grouped GEMM over a caller-built tile table (rows {first, end, first B row, -} as above; `count`

@@ -236,12 +236,14 @@ std::vector<at::Tensor> moe_router_topk(const at::Tensor& logits, int64_t k, boo
 
 // x [T, H] bf16, idx [T, k] int64, offsets [E+1] int64 (exclusive prefix of the histogram).
 // Returns {xs [T*k, H] rows sorted by expert, pos [T, k] int32 (row of each pair)}.
-std::vector<at::Tensor> moe_permute(const at::Tensor& x, const at::Tensor& idx, const at::Tensor& offsets) {
+// total_rows > 0: the groups are padded (offsets holds padded starts); xs gets that many rows, zero where no pair lands.
+std::vector<at::Tensor> moe_permute(const at::Tensor& x, const at::Tensor& idx, const at::Tensor& offsets, int64_t total_rows) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() == 2, "moe_permute: bf16 [T, H]");
   TORCH_CHECK(idx.scalar_type() == at::kLong && idx.is_contiguous() && offsets.scalar_type() == at::kLong, "moe_permute: int64 idx/offsets");
   const int64_t T_ = x.size(0), H = x.size(1), k = idx.size(1), pairs = T_ * k;
   TORCH_CHECK(H % 8 == 0, "moe_permute: hidden size must be a multiple of 8");
-  auto xs = at::empty({pairs, H}, x.options());
+  TORCH_CHECK(total_rows <= 0 || total_rows >= pairs, "moe_permute: total_rows smaller than the number of pairs");
+  auto xs = total_rows > 0 ? at::zeros({total_rows, H}, x.options()) : at::empty({pairs, H}, x.options());
   auto pos = at::empty({T_, k}, x.options().dtype(at::kInt));
   if (pairs == 0) return {xs, pos};
   auto cursor = at::zeros({offsets.numel()}, x.options().dtype(at::kInt));
@@ -253,11 +255,12 @@ std::vector<at::Tensor> moe_permute(const at::Tensor& x, const at::Tensor& idx, 
 }
 
 // Rows of x [T, H] placed at known positions, optionally scaled per pair: out[pos[t,s]] = scale[t,s] * x[t].
-at::Tensor moe_permute_at(const at::Tensor& x, const at::Tensor& pos, const c10::optional<at::Tensor>& scale) {
+at::Tensor moe_permute_at(const at::Tensor& x, const at::Tensor& pos, const c10::optional<at::Tensor>& scale,
+                          int64_t total_rows) {
   const int64_t T_ = x.size(0), H = x.size(1), k = pos.size(1), pairs = T_ * k;
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous() && pos.scalar_type() == at::kInt && pos.is_contiguous() && H % 8 == 0,
               "moe_permute_at: bf16 [T, H], int32 pos");
-  auto out = at::empty({pairs, H}, x.options());
+  auto out = total_rows > 0 ? at::zeros({total_rows, H}, x.options()) : at::empty({pairs, H}, x.options());
   if (pairs == 0) return out;
   const float* sp = nullptr;
   at::Tensor sc;

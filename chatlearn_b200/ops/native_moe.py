@@ -64,10 +64,17 @@ def moe_router(logits, top_k, scoring="softmax", norm_topk=True, bias=None, n_gr
 
 
 # ------------------------------------------------------------------ dispatch / combine
-def _offsets(idx, num_experts):
+_PAD = 64     # every expert's rows start at a multiple of the K tile of the weight-gradient GEMM
+
+
+def _offsets(idx, num_experts, pad: int = 1):
+    """First row of every expert in the sorted layout (device tensor, no host read-back).  ``pad`` > 1 rounds every
+    expert's row count up to a multiple of it; the rows in between stay zero."""
     hist = getattr(idx, "_moe_hist", None)
     if hist is None or hist.numel() != num_experts:
         hist = torch.bincount(idx.reshape(-1), minlength=num_experts)
+    if pad > 1:
+        hist = (hist + (pad - 1)) // pad * pad
     off = torch.zeros(num_experts + 1, dtype=torch.long, device=idx.device)
     off[1:] = hist.cumsum(0)
     return off
@@ -75,8 +82,8 @@ def _offsets(idx, num_experts):
 
 class _Permute(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, idx, offsets):
-        xs, pos = C.moe_permute(x.contiguous(), idx.contiguous(), offsets)
+    def forward(ctx, x, idx, offsets, total_rows=-1):
+        xs, pos = C.moe_permute(x.contiguous(), idx.contiguous(), offsets, int(total_rows))
         _count("moe_permute")
         ctx.save_for_backward(pos)
         ctx.mark_non_differentiable(pos)
@@ -86,7 +93,7 @@ class _Permute(torch.autograd.Function):
     def backward(ctx, dxs, _):
         (pos,) = ctx.saved_tensors
         _count("moe_combine")
-        return C.moe_combine(dxs.contiguous(), pos, None), None, None
+        return C.moe_combine(dxs.contiguous(), pos, None), None, None, None
 
 
 class _Combine(torch.autograd.Function):
@@ -101,29 +108,49 @@ class _Combine(torch.autograd.Function):
         ys, pos, weights = ctx.saved_tensors
         dy = dy.contiguous()
         _count("moe_permute")
-        dys = C.moe_permute_at(dy, pos, weights)
+        # same row layout as ys (padded or not); rows no pair maps to are zero
+        dys = C.moe_permute_at(dy, pos, weights, int(ys.shape[0]) if ys.shape[0] != pos.numel() else -1)
         _count("moe_row_dot")
         dw = C.moe_row_dot(dy, ys, pos)
         return dys, None, dw.to(weights.dtype)
 
 
 class _GroupedMLP(torch.autograd.Function):
-    """SwiGLU expert MLPs over rows sorted by expert (``offsets`` on the device)."""
+    """SwiGLU expert MLPs over rows sorted by expert (``offsets`` on the device).
+
+    ``padded``: every expert's rows start at a multiple of 64 and the rows between two experts are zero.  The
+    backward then runs on the grouped tcgen05 GEMMs as well (input gradients: the forward's tile table with the
+    weights read in their stored layout; weight gradients: one tile per (expert, 128 x 256 block of its weight),
+    contraction over the expert's rows), with no read-back of the group sizes.  Otherwise (rows packed densely,
+    as the expert-parallel exchange delivers them) the backward loops over the experts on library GEMMs."""
 
     @staticmethod
-    def forward(ctx, xs, w13, w2, offsets):
+    def forward(ctx, xs, w13, w2, offsets, padded=False):
         h13 = C.grouped_gemm_bf16_nt(xs, w13, offsets)
         act = C.swiglu_fwd(h13)
         ys = C.grouped_gemm_bf16_nt(act, w2, offsets)
         _count("grouped_gemm_bf16_nt", 2)
         _count("swiglu_fwd")
         ctx.save_for_backward(xs, w13, w2, offsets, h13)
+        ctx.padded = bool(padded) and w13.shape[1] % 64 == 0 and w2.shape[1] % 64 == 0
         return ys
 
     @staticmethod
     def backward(ctx, dys):
         xs, w13, w2, offsets, h13 = ctx.saved_tensors
         dys = dys.contiguous()
+        if ctx.padded:
+            act = C.swiglu_fwd(h13)
+            dact = C.grouped_gemm_bf16_nn(dys, w2, offsets)                               # [R, F]
+            dw2 = C.grouped_gemm_bf16_tn(dys, act, offsets, torch.empty_like(w2), False)  # [E, H, F]
+            dh13 = C.swiglu_bwd(h13, dact)
+            dxs = C.grouped_gemm_bf16_nn(dh13, w13, offsets)                              # [R, H]
+            dw13 = C.grouped_gemm_bf16_tn(dh13, xs, offsets, torch.empty_like(w13), False)
+            _count("grouped_gemm_bf16_nn", 2)
+            _count("grouped_gemm_bf16_tn", 2)
+            _count("swiglu_fwd")
+            _count("swiglu_bwd")
+            return dxs, dw13, dw2, None, None
         bounds = offsets.tolist()                      # one read-back per layer
         act = C.swiglu_fwd(h13)
         dact = torch.empty_like(act)
@@ -142,7 +169,7 @@ class _GroupedMLP(torch.autograd.Function):
                 torch.mm(dh13[s:t], w13[e], out=dxs[s:t])
                 torch.mm(dh13[s:t].t(), xs[s:t], out=dw13[e])
         library_counts["grouped_gemm_bwd"] += 1
-        return dxs, dw13, dw2, None
+        return dxs, dw13, dw2, None, None
 
 
 def _moe_ok(x, w13, w2):
@@ -164,9 +191,16 @@ def moe_experts(x, w13, w2, weights, idx):
     if not _moe_ok(x, w13, w2) or x.shape[0] == 0:
         library_counts["moe_experts"] += 1
         return ref.moe_experts(x, w13, w2, weights, idx)
-    offsets = _offsets(idx, w13.shape[0])
-    xs, pos = _Permute.apply(x, idx, offsets)
-    ys = _GroupedMLP.apply(xs, w13, w2, offsets)
+    E = w13.shape[0]
+    if torch.is_grad_enabled() and (x.requires_grad or w13.requires_grad):
+        # training: padded groups, so that the backward runs on the grouped kernels too
+        offsets = _offsets(idx, E, _PAD)
+        xs, pos = _Permute.apply(x, idx, offsets, idx.numel() + E * _PAD)
+        ys = _GroupedMLP.apply(xs, w13, w2, offsets, True)
+    else:
+        offsets = _offsets(idx, E)
+        xs, pos = _Permute.apply(x, idx, offsets)
+        ys = _GroupedMLP.apply(xs, w13, w2, offsets)
     return _Combine.apply(ys, pos, weights.float())
 
 

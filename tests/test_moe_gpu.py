@@ -82,3 +82,90 @@ def test_moe_experts_forward_backward():
         rel = (a.grad.float() - b.grad).norm() / b.grad.norm()
         assert rel < 3e-2, (name, rel)
     assert ops.launch_counts["grouped_gemm_bf16_nt"] >= 2
+
+
+@pytest.mark.parametrize("G,K,N,M", [(8, 256, 192, 320), (40, 128, 512, 64)])
+def test_grouped_gemm_backward_layouts(G, K, N, M):
+    """Input-gradient (NN) and weight-gradient (ragged contraction) forms of the grouped GEMM against fp32
+    statements: groups padded to 64 rows with zero rows in between, some groups empty."""
+    from chatlearn_b200.ops import native
+    torch.manual_seed(5)
+    dev = _dev()
+    counts = torch.randint(0, 150, (G,))
+    counts[1] = 0
+    counts[G - 1] = 0
+    padded = (counts + 63) // 64 * 64
+    off = torch.zeros(G + 1, dtype=torch.long)
+    off[1:] = padded.cumsum(0)
+    R = int(off[-1]) + 64                                    # a tail no group covers
+    a = torch.zeros(R, K)
+    bt = torch.zeros(R, N)
+    for g in range(G):
+        s, n = int(off[g]), int(counts[g])
+        a[s:s + n] = torch.randn(n, K)
+        bt[s:s + n] = torch.randn(n, N)
+    a, bt = a.to(dev).bfloat16(), bt.to(dev).bfloat16()
+    offd = off.to(dev)
+    # NN: c[r] = a[r] @ w[g], w [G, K, N]
+    w = (torch.randn(G, K, N, device=dev) * 0.1).bfloat16()
+    c = native.C.grouped_gemm_bf16_nn(a, w, offd)
+    for g in range(G):
+        s, t = int(off[g]), int(off[g + 1])
+        if t > s:
+            want = a[s:t].float() @ w[g].float()
+            assert (c[s:t].float() - want).norm() <= 5e-3 * max(want.norm().item(), 1e-6), g
+    # TN: out[g] = a[rows of g]^T @ bt[rows of g], a as [R, M = K]
+    out = torch.full((G, K, N), 7.0, device=dev).bfloat16()
+    native.C.grouped_gemm_bf16_tn(a, bt, offd, out, False)
+    acc = torch.ones(G, K, N, device=dev)
+    native.C.grouped_gemm_bf16_tn(a, bt, offd, acc, True)
+    assert native.C.gemm_last_status() == 0
+    for g in range(G):
+        s, t = int(off[g]), int(off[g + 1])
+        want = a[s:t].float().t() @ bt[s:t].float()
+        tol = 5e-3 * max(want.norm().item(), 1.0)
+        assert (out[g].float() - want).norm() <= tol, g
+        assert (acc[g] - 1.0 - want).norm() <= 1e-3 * max(want.norm().item(), 1.0), g
+    # second shape family: M (rows of the weight) not a multiple of the 128-row tile
+    a2 = torch.zeros(R, M)
+    for g in range(G):
+        s, n = int(off[g]), int(counts[g])
+        a2[s:s + n] = torch.randn(n, M)
+    a2 = a2.to(dev).bfloat16()
+    out2 = torch.empty(G, M, N, device=dev, dtype=torch.bfloat16)
+    native.C.grouped_gemm_bf16_tn(a2, bt, offd, out2, False)
+    for g in range(G):
+        s, t = int(off[g]), int(off[g + 1])
+        want = a2[s:t].float().t() @ bt[s:t].float()
+        assert (out2[g].float() - want).norm() <= 5e-3 * max(want.norm().item(), 1.0), g
+
+
+def test_moe_experts_backward_uses_the_grouped_kernels_with_empty_experts():
+    from chatlearn_b200 import ops
+    from chatlearn_b200.ops import reference as ref
+    torch.manual_seed(4)
+    T, H, F, E, k = 90, 192, 96, 64, 2                        # 180 pairs over 64 experts: several experts get no token
+    dev = _dev()
+    x = torch.randn(T, H, device=dev).bfloat16()
+    w13 = (torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16()
+    w2 = (torch.randn(E, H, F, device=dev) * 0.05).bfloat16()
+    wts, idx, _ = ref.moe_router(torch.randn(T, E, device=dev), k)
+    assert torch.bincount(idx.reshape(-1), minlength=E).min().item() == 0
+    args1 = [t.clone().requires_grad_(True) for t in (x, w13, w2, wts)]
+    args0 = [t.float().clone().requires_grad_(True) for t in (x, w13, w2, wts)]
+    before = ops.launch_counts["grouped_gemm_bf16_tn"], ops.library_counts["grouped_gemm_bwd"]
+    y1 = ops.moe_experts(args1[0], args1[1], args1[2], args1[3], idx)
+    y0 = ref.moe_experts(args0[0], args0[1], args0[2], args0[3], idx)
+    assert (y1.float() - y0).norm() / y0.norm() < 2e-2
+    g = torch.randn_like(y0)
+    y1.backward(g.bfloat16())
+    y0.backward(g)
+    for a, b, name in zip(args1, args0, ("x", "w13", "w2", "weights")):
+        rel = (a.grad.float() - b.grad).norm() / b.grad.norm()
+        assert rel < 3e-2, (name, rel)
+    assert ops.launch_counts["grouped_gemm_bf16_tn"] == before[0] + 2
+    assert ops.library_counts["grouped_gemm_bwd"] == before[1]
+    # without a tape the rows are packed densely (no padding)
+    with torch.no_grad():
+        y2 = ops.moe_experts(x, w13, w2, wts, idx)
+    assert (y2.float() - y0.detach()).norm() / y0.norm() < 2e-2
