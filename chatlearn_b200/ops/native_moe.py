@@ -8,9 +8,14 @@ combine           csrc/moe.cu  moe_combine (fp32 weighted sum of the k expert ou
 The reference gets these from TransformerEngine (grouped GEMM, permute/unpermute:
 chatlearn/models/patches/transformers/layers/groupgemm.py:65-208) and from eager torch
 (router: qwen3_moe_patch.py:36-43).  Backward passes run here as well: routing
-gradients are closed-form, data gradients of the expert GEMMs go through cuBLAS per
-expert (the group sizes are read back once per layer for that).
+gradients are closed-form; the expert GEMMs' input and weight gradients run on the same
+grouped kernel (every expert's rows padded to a multiple of 64 in the sorted layout, so
+the weight gradient's contraction over an expert's rows never touches a neighbour's).
+Rows that arrive densely packed from the expert-parallel exchange (``grouped_mlp``) keep
+the per-expert library GEMMs after one read-back of the group sizes.
 """
+import os
+
 import torch
 
 from . import library_counts, reference as ref, register_native
@@ -65,6 +70,8 @@ def moe_router(logits, top_k, scoring="softmax", norm_topk=True, bias=None, n_gr
 
 # ------------------------------------------------------------------ dispatch / combine
 _PAD = 64     # every expert's rows start at a multiple of the K tile of the weight-gradient GEMM
+# "grouped": backward on the grouped tcgen05 kernels; "library": per-expert library GEMMs (kept for comparison)
+_BWD_IMPL = os.environ.get("CLB200_MOE_BWD", "grouped")
 
 
 def _offsets(idx, num_experts, pad: int = 1):
@@ -192,7 +199,7 @@ def moe_experts(x, w13, w2, weights, idx):
         library_counts["moe_experts"] += 1
         return ref.moe_experts(x, w13, w2, weights, idx)
     E = w13.shape[0]
-    if torch.is_grad_enabled() and (x.requires_grad or w13.requires_grad):
+    if torch.is_grad_enabled() and (x.requires_grad or w13.requires_grad) and _BWD_IMPL == "grouped":
         # training: padded groups, so that the backward runs on the grouped kernels too
         offsets = _offsets(idx, E, _PAD)
         xs, pos = _Permute.apply(x, idx, offsets, idx.numel() + E * _PAD)

@@ -105,7 +105,7 @@ class RolloutEngine:
         # pipelined decode: the step launched last whose sampled tokens the host has not read yet
         self._pending = None
         self._finished_buf: List[Sequence] = []
-        self.pipelined = os.environ.get("CLB200_PIPELINED_DECODE", "0") != "0"
+        self.pipelined = os.environ.get("CLB200_PIPELINED_DECODE", "1") != "0"
 
     # ------------------------------------------------------------------ memory
     def kv_bytes_per_block(self) -> int:
