@@ -189,8 +189,22 @@ def grouped_mlp(xs, w13, w2, counts):
     if not _moe_ok(xs, w13, w2) or xs.shape[0] == 0:
         library_counts["grouped_mlp"] += 1
         return ref.grouped_mlp(xs, w13, w2, counts)
+    c = torch.tensor(counts, dtype=torch.long)
     off = torch.zeros(len(counts) + 1, dtype=torch.long)
-    off[1:] = torch.tensor(counts, dtype=torch.long).cumsum(0)
+    off[1:] = c.cumsum(0)
+    if torch.is_grad_enabled() and (xs.requires_grad or w13.requires_grad) and _BWD_IMPL == "grouped" \
+            and w13.shape[1] % 64 == 0 and w2.shape[1] % 64 == 0:
+        # training: move the rows into the layout whose groups start at multiples of 64 (zero rows in between),
+        # so that the backward runs on the grouped kernels; the group sizes are on the host already
+        p = (c + (_PAD - 1)) // _PAD * _PAD
+        poff = torch.zeros(len(counts) + 1, dtype=torch.long)
+        poff[1:] = p.cumsum(0)
+        R, dev = xs.shape[0], xs.device
+        shift = (poff[:-1] - off[:-1]).to(dev, non_blocking=True)
+        keep = torch.arange(R, device=dev) + torch.repeat_interleave(shift, c.to(dev, non_blocking=True), output_size=R)
+        xs_pad = xs.new_zeros(int(poff[-1]), xs.shape[1]).index_copy(0, keep, xs)
+        ys = _GroupedMLP.apply(xs_pad, w13, w2, poff.to(dev, non_blocking=True), True)
+        return ys.index_select(0, keep)
     return _GroupedMLP.apply(xs.contiguous(), w13, w2, off.to(xs.device, non_blocking=True))
 
 

@@ -169,3 +169,31 @@ def test_moe_experts_backward_uses_the_grouped_kernels_with_empty_experts():
     with torch.no_grad():
         y2 = ops.moe_experts(x, w13, w2, wts, idx)
     assert (y2.float() - y0.detach()).norm() / y0.norm() < 2e-2
+
+
+def test_grouped_mlp_with_host_counts_trains_on_the_grouped_kernels():
+    """Rows packed densely by expert with the group sizes on the host (what the expert-parallel exchange delivers):
+    with a tape they are moved into the padded layout, so the backward takes the grouped kernels."""
+    from chatlearn_b200 import ops
+    from chatlearn_b200.ops import reference as ref
+    torch.manual_seed(8)
+    E, H, F = 6, 128, 64
+    counts = [70, 0, 128, 5, 64, 33]
+    dev = _dev()
+    R = sum(counts)
+    xs = torch.randn(R, H, device=dev).bfloat16()
+    w13 = (torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16()
+    w2 = (torch.randn(E, H, F, device=dev) * 0.05).bfloat16()
+    a1 = [t.clone().requires_grad_(True) for t in (xs, w13, w2)]
+    a0 = [t.float().clone().requires_grad_(True) for t in (xs, w13, w2)]
+    before = ops.launch_counts["grouped_gemm_bf16_tn"], ops.library_counts["grouped_gemm_bwd"]
+    y1 = ops.grouped_mlp(a1[0], a1[1], a1[2], counts)
+    y0 = ref.grouped_mlp(a0[0], a0[1], a0[2], counts)
+    assert y1.shape == y0.shape and (y1.float() - y0).norm() / y0.norm() < 2e-2
+    g = torch.randn_like(y0)
+    y1.backward(g.bfloat16())
+    y0.backward(g)
+    for a, b, name in zip(a1, a0, ("x", "w13", "w2")):
+        rel = (a.grad.float() - b.grad).norm() / b.grad.norm()
+        assert rel < 3e-2, (name, rel)
+    assert ops.launch_counts["grouped_gemm_bf16_tn"] == before[0] + 2 and ops.library_counts["grouped_gemm_bwd"] == before[1]
