@@ -84,10 +84,13 @@ class MegatronPolicyTrainer(MegatronModule):
         dist.recv(t, self.pp_group.ranks[from_stage], group=self.pp_group.pg)
         return t
 
-    def _stage_forward(self, batch: PackedBatch, ctx: FwdCtx, local, x_in: Optional[torch.Tensor]):
-        """Forward of this pipeline stage.  Returns hidden states (intermediate
-        stages) or ``(logprobs, entropy)`` on the last stage."""
+    def _stage_forward(self, batch: PackedBatch, ctx: FwdCtx, local, x_in: Optional[torch.Tensor],
+                       chunk: Optional[int] = None):
+        """Forward of this pipeline stage (of its model chunk ``chunk`` under the interleaved schedule).  Returns
+        hidden states, or ``(logprobs, entropy)`` where the model ends."""
         tokens = batch.tokens if local is None else batch.tokens.index_select(0, local)
+        first = self.is_first_stage and (chunk is None or chunk == 0)
+        last = self.is_last_stage and (chunk is None or chunk == self.vpp_size - 1)
         hook = None
         if torch.is_grad_enabled() and getattr(self.module_args, "recompute_granularity", None) == "full":
             from torch.utils.checkpoint import checkpoint
@@ -99,20 +102,13 @@ class MegatronPolicyTrainer(MegatronModule):
         if getattr(self, "vision", None) is not None:
             from chatlearn_b200.models.nn.vision import multimodal_inputs
             x0 = multimodal_inputs(self.model, self.vision, tokens, batch.seq_lens, batch.mm or [], ctx,
-                                   with_embeddings=self.is_first_stage)
+                                   with_embeddings=first)
             if ctx.deepstack is not None:
                 lo, hi = self.model.layer_range
                 assert hi - lo >= len(ctx.deepstack[1]), "the first pipeline stage must hold every deep-stack layer"
-        if self.is_first_stage:
-            h = self.model.hidden_states(tokens, ctx, hook, x=x0)
-        else:
-            h = x_in
-            for l in range(*self.model.layer_range):
-                p = self.model.layer_params(l)
-                h = hook(l, p, h, ctx) if hook else decoder_layer(self.model.arch, p, h, ctx, l)
-            if self.is_last_stage:
-                h = ops.rmsnorm(h, self.model.final_norm_weight(), self.model.arch.rms_norm_eps)
-        if not self.is_last_stage:
+        # embedding where the model starts, final norm where it ends (both decided inside by the layer range)
+        h = self.model.hidden_states(tokens, ctx, hook, x=x0 if first else x_in, chunk=chunk)
+        if not last:
             return h
         if ctx.seq_parallel:
             # the output head needs every row on every rank; its input gradient is already summed over the
@@ -140,11 +136,25 @@ class MegatronPolicyTrainer(MegatronModule):
             if batch is None:
                 continue
             n_local = self._local_tokens(batch, local)
-            x_in = None if self.is_first_stage else self._recv((n_local, H), self.compute_dtype, self.pp_rank - 1)
-            out = self._stage_forward(batch, ctx, local, x_in)
-            if not self.is_last_stage:
-                self._send(out, self.pp_rank + 1)
-                continue
+            if self.vpp_size > 1:
+                # the model's chunks in order: chunk g lives on stage g % pp; the row travels round the stages
+                # once per chunk of a stage (a scoring pass has no bubble to fill, so no interleaving here)
+                P, out = self.pp_size, None
+                for gchunk in range(P * self.vpp_size):
+                    if gchunk % P != self.pp_rank:
+                        continue
+                    x_in = None if gchunk == 0 else self._recv((n_local, H), self.compute_dtype, (self.pp_rank - 1) % P)
+                    out = self._stage_forward(batch, ctx, local, x_in, chunk=gchunk // P)
+                    if gchunk < P * self.vpp_size - 1:
+                        self._send(out, (self.pp_rank + 1) % P)
+                if not self.is_last_stage:
+                    continue
+            else:
+                x_in = None if self.is_first_stage else self._recv((n_local, H), self.compute_dtype, self.pp_rank - 1)
+                out = self._stage_forward(batch, ctx, local, x_in)
+                if not self.is_last_stage:
+                    self._send(out, self.pp_rank + 1)
+                    continue
             lp = out[0]
             if self.cp_size > 1:
                 lp = self.cp.gather_tokens(lp, ctx.cp_plan)      # true all-gather, global order
@@ -202,22 +212,24 @@ class MegatronPolicyTrainer(MegatronModule):
         prev, nxt = self.pp_rank - 1, self.pp_rank + 1
         first, last = self.is_first_stage, self.is_last_stage
 
-        def compute_forward(batch, ctx, local, x_in):
+        def compute_forward(batch, ctx, local, x_in, chunk=None, n_aux=0):
             nonlocal stats
-            out = self._stage_forward(batch, ctx, local, x_in)
-            if last:
+            out = self._stage_forward(batch, ctx, local, x_in, chunk)
+            ends = last and (chunk is None or chunk == self.vpp_size - 1)
+            auxes = ctx.aux_losses[n_aux:]              # the router losses of this chunk's layers
+            if ends:
                 lp, ent = out
                 loss, s = self._loss(batch, local, lp, ent, inv_norm)
-                for aux in ctx.aux_losses:
+                for aux in auxes:
                     loss = loss + aux * (batch.loss_mask.sum() * inv_norm)
                 stats += s.detach()
-                return loss, x_in, None
+                return loss, x_in, None, True
             # auxiliary (router) losses of intermediate stages are back-propagated locally
-            aux = sum(ctx.aux_losses) * (batch.loss_mask.sum() * inv_norm) if ctx.aux_losses else None
-            return out, x_in, aux
+            aux = sum(auxes) * (batch.loss_mask.sum() * inv_norm) if auxes else None
+            return out, x_in, aux, False
 
-        def compute_backward(out, x_in, aux, g):
-            if last:
+        def compute_backward(out, x_in, aux, ends, g):
+            if ends:
                 out.backward()
             elif aux is not None:
                 torch.autograd.backward([out, aux], [g, torch.ones_like(aux)])
@@ -228,6 +240,9 @@ class MegatronPolicyTrainer(MegatronModule):
         def in_shape(k):
             return (self._local_tokens(mbs[k][0], mbs[k][2]), H)
 
+        if self.vpp_size > 1:
+            self._run_interleaved(mbs, compute_forward, compute_backward, in_shape)
+            return self._finish_train_step(st, stats)
         n_mb = len(mbs)
         warm = min(self.pp_size - self.pp_rank - 1, n_mb)
         steady = n_mb - warm
@@ -265,6 +280,131 @@ class MegatronPolicyTrainer(MegatronModule):
             dx = compute_backward(*old, g)
             if not first:
                 self._send(dx, prev)
+        return self._finish_train_step(st, stats)
+
+    # ------------------------------------------------------------------ interleaved (virtual pipeline) schedule
+    @staticmethod
+    def interleaved_order(P: int, V: int, m: int, r: int):
+        """Units of stage ``r`` in execution order, ``("F" | "B", micro-batch, chunk)``: Megatron's interleaved
+        one-forward-one-backward order.  Micro-batches advance in groups of ``P``; a stage runs the group through
+        its chunk 0, then through chunk 1, ...; backwards visit the chunks in reverse.  ``(P - r - 1) * 2 +
+        (V - 1) * P`` forwards run before the first backward."""
+        def unit(k, back):
+            group, idx = divmod(k, P * V)
+            width = min(P, m - group * P)              # the last group may hold fewer micro-batches
+            if width < P:
+                j, i = divmod(k - group * P * V, width)
+            else:
+                j, i = divmod(idx, P)
+            return (group * P + i, (V - 1 - j) if back else j)
+        total = m * V
+        warm = min((P - r - 1) * 2 + (V - 1) * P, total)
+        order = [("F",) + unit(k, False) for k in range(warm)]
+        for i in range(total - warm):
+            order.append(("F",) + unit(warm + i, False))
+            order.append(("B",) + unit(i, True))
+        order += [("B",) + unit(i, True) for i in range(total - warm, total)]
+        return order
+
+    @staticmethod
+    def interleaved_ticks(P: int, V: int, m: int):
+        """Global time table of the interleaved schedule: ``ticks[r][t]`` is the unit stage ``r`` runs at tick ``t``
+        (or None).  A unit runs at the first tick after its input exists: the forward of chunk g needs the forward
+        of chunk g - 1 of the same micro-batch (sent at the end of the tick it ran in), the backward of chunk g the
+        backward of chunk g + 1 (or, for the last chunk, its own forward).  Every stage derives the same table, so
+        at every tick a stage knows what its neighbours send it."""
+        G = P * V
+
+        def simulate(orders):
+            done = {}                                          # (kind, mb, global chunk) -> tick
+            at = [0] * P
+            ticks = [[] for _ in range(P)]
+            t = 0
+            while any(at[r] < len(orders[r]) for r in range(P)):
+                ran = []
+                for r in range(P):
+                    u = None
+                    if at[r] < len(orders[r]):
+                        kind, mb, j = orders[r][at[r]]
+                        g = j * P + r
+                        if kind == "F":
+                            dep = None if g == 0 else ("F", mb, g - 1)
+                        else:
+                            dep = ("F", mb, g) if g == G - 1 else ("B", mb, g + 1)
+                        if dep is None or done.get(dep, t) < t:
+                            u = (kind, mb, j)
+                            ran.append((kind, mb, g))
+                            at[r] += 1
+                    ticks[r].append(u)
+                if not ran:
+                    return None                                # every stage waits for another: not a valid order
+                for key in ran:
+                    done[key] = t
+                t += 1
+            return ticks
+
+        ticks = simulate([MegatronPolicyTrainer.interleaved_order(P, V, m, r) for r in range(P)])
+        if ticks is None:
+            # always valid: every forward (chunk by chunk), then every backward
+            fwd = [[("F", k, j) for j in range(V) for k in range(m)] for _ in range(P)]
+            bwd = [[("B", k, j) for j in reversed(range(V)) for k in range(m)] for _ in range(P)]
+            ticks = simulate([f + b for f, b in zip(fwd, bwd)])
+        assert ticks is not None
+        return ticks
+
+    def _run_interleaved(self, mbs, compute_forward, compute_backward, in_shape):
+        """Interleaved one-forward-one-backward over ``vpp_size`` model chunks per stage.  All stages walk the same
+        global time table; what a tick's units produce crosses the stage boundaries in ONE batched exchange at the
+        end of that tick (a stage posts the receive for a neighbour's output in the tick the neighbour produces
+        it), so sends and receives always meet inside the same exchange."""
+        P, V, r = self.pp_size, self.vpp_size, self.pp_rank
+        G = P * V
+        ticks = self.interleaved_ticks(P, V, len(mbs))
+        nxt, prv = (r + 1) % P, (r - 1) % P
+        acts, grads, saved = {}, {}, {}                        # inputs that arrived, by (micro-batch, chunk)
+        for t in range(len(ticks[r])):
+            u = ticks[r][t]
+            send = []
+            if u is not None:
+                kind, k, j = u
+                g = j * P + r
+                if kind == "F":
+                    x_in = None
+                    if g > 0:
+                        x_in = acts.pop((k, j)).requires_grad_(True)
+                    ctx = mbs[k][1]
+                    n_aux = len(ctx.aux_losses)
+                    item = compute_forward(mbs[k][0], ctx, mbs[k][2], x_in, j, n_aux)
+                    saved[(k, j)] = item
+                    if g < G - 1:
+                        send.append((item[0].detach(), nxt))
+                else:
+                    item = saved.pop((k, j))
+                    dx = compute_backward(*item, None if g == G - 1 else grads.pop((k, j)))
+                    if g > 0:
+                        send.append((dx, prv))
+            recv = []
+            for peer, want in ((prv, "F"), (nxt, "B")):
+                pu = ticks[peer][t] if t < len(ticks[peer]) else None
+                if pu is None or pu[0] != want:
+                    continue
+                pg = pu[2] * P + peer
+                if want == "F" and pg < G - 1:                 # its output is the input of my chunk pg + 1
+                    recv.append((acts, (pu[1], (pg + 1) // P), peer))
+                elif want == "B" and pg > 0:                   # its input gradient belongs to my chunk pg - 1
+                    recv.append((grads, (pu[1], (pg - 1) // P), peer))
+            if not send and not recv:
+                continue
+            ops_ = [dist.P2POp(dist.isend, x.contiguous(), self.pp_group.ranks[to], self.pp_group.pg) for x, to in send]
+            for store, key, peer in recv:
+                buf = torch.empty(in_shape(key[0]), dtype=self.compute_dtype, device=self.device)
+                store[key] = buf
+                ops_.append(dist.P2POp(dist.irecv, buf, self.pp_group.ranks[peer], self.pp_group.pg))
+            for req in dist.batch_isend_irecv(ops_):
+                req.wait()
+        assert not acts and not grads and not saved
+
+    def _finish_train_step(self, st, stats):
         grad_norm = st.step()
         # metrics live on the last stage; share them with the whole model-parallel group
         if self.pp_size > 1:

@@ -75,6 +75,16 @@ def pipeline_layer_range(num_layers: int, pp: int, stage: int, first: Optional[i
     return lo, lo + sizes[stage]
 
 
+def pipeline_chunk_ranges(num_layers: int, pp: int, vpp: int, stage: int) -> List[Tuple[int, int]]:
+    """Layer ranges of the ``vpp`` model chunks a stage holds under the interleaved schedule: the model is cut
+    into ``pp * vpp`` equal chunks and chunk ``c`` lives on stage ``c % pp`` (Megatron's
+    ``virtual_pipeline_model_parallel_size``; chatlearn/configs/megatron_config.py:106 passes it through)."""
+    assert num_layers % (pp * vpp) == 0, \
+        f"{num_layers} layers do not split into {pp} stages x {vpp} chunks of equal size"
+    per = num_layers // (pp * vpp)
+    return [((j * pp + stage) * per, (j * pp + stage + 1) * per) for j in range(vpp)]
+
+
 class MegatronModule(FSDPModule):
     """Shares checkpoint / residency plumbing with the FSDP-style role; differs in
     how the model is partitioned and which groups reduce what."""
@@ -86,6 +96,8 @@ class MegatronModule(FSDPModule):
         self.cp_size = int(ma.context_parallel_size)
         self.ep_size = int(ma.expert_model_parallel_size)
         self.etp_size = int(ma.expert_tensor_parallel_size or 1)
+        self.vpp_size = int(getattr(ma, "virtual_pipeline_model_parallel_size", None) or 1)
+        assert self.vpp_size == 1 or self.pp_size > 1, "model chunks (virtual pipeline) need pipeline parallelism"
         assert self.etp_size in (1, self.tp_size), \
             "expert tensor parallelism is either off or spans the tensor-parallel group (etp == tp)"
         self.mesh = build_mesh(self.placement, tp=self.tp_size, cp=self.cp_size, pp=self.pp_size,
@@ -136,12 +148,17 @@ class MegatronModule(FSDPModule):
     def create_model(self) -> CausalLM:
         ma = self.module_args
         arch = self.resolve_arch()
-        lo, hi = pipeline_layer_range(arch.num_hidden_layers, self.pp_size, self.pp_rank,
-                                      ma.decoder_first_pipeline_num_layers, ma.decoder_last_pipeline_num_layers)
+        if self.vpp_size > 1:
+            assert ma.decoder_first_pipeline_num_layers is None and ma.decoder_last_pipeline_num_layers is None, \
+                "uneven first / last stages are not combined with model chunks"
+            ranges = pipeline_chunk_ranges(arch.num_hidden_layers, self.pp_size, self.vpp_size, self.pp_rank)
+        else:
+            ranges = pipeline_layer_range(arch.num_hidden_layers, self.pp_size, self.pp_rank,
+                                          ma.decoder_first_pipeline_num_layers, ma.decoder_last_pipeline_num_layers)
         pad = math.lcm(self.dp_group.size, self.edp_group.size)
         model = CausalLM(arch, dtype=self.compute_dtype, device=self.device, tp=self.tp_size, tp_rank=self.tp_rank,
                          ep=self.ep_size, ep_rank=self.ep_rank, etp=self.etp_size,
-                         etp_rank=self.tp_rank if self.etp_size > 1 else 0, layer_range=(lo, hi),
+                         etp_rank=self.tp_rank if self.etp_size > 1 else 0, layer_range=ranges,
                          with_embed=self.is_first_stage or (arch.tie_word_embeddings and self.is_last_stage),
                          with_head=self.is_last_stage, pad_to=pad)
         from chatlearn_b200.checkpoint.safetensors_io import has_safetensors, load_into_model

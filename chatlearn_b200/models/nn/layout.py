@@ -243,19 +243,23 @@ def model_blocks(arch: ModelArch, tp=1, tp_rank=0, ep=1, ep_rank=0,
                  layer_range: Optional[Tuple[int, int]] = None,
                  with_embed=True, with_head=True, etp=1, etp_rank=0) -> List[Tuple[str, List[Leaf]]]:
     """Blocks (= FSDP units / offload units) of a model instance in forward order.
-    ``layer_range`` selects a pipeline stage's layers."""
-    lo, hi = layer_range or (0, arch.num_hidden_layers)
+    ``layer_range`` selects a pipeline stage's layers: one ``(lo, hi)`` pair, or a list of pairs when the
+    stage holds several model chunks (interleaved pipeline schedule)."""
+    ranges = layer_range or (0, arch.num_hidden_layers)
+    if ranges and isinstance(ranges[0], int):
+        ranges = [tuple(ranges)]
     blocks = []
     if with_embed:
         blocks.append(("embed", embed_leaves(arch, tp, tp_rank)))
-    for l in range(lo, hi):
-        leaves = layer_leaves(arch, l, tp, tp_rank, ep, ep_rank, etp, etp_rank)
-        experts = [lf for lf in leaves if lf.name.endswith((".w13", ".w2"))]
-        blocks.append((f"layer{l}", [lf for lf in leaves if lf not in experts]))
-        if experts:
-            # expert weights are replicated over a different group (expert-DP), so
-            # they shard, reduce and offload as a block of their own
-            blocks.append((f"layer{l}.experts", experts))
+    for lo, hi in ranges:
+        for l in range(lo, hi):
+            leaves = layer_leaves(arch, l, tp, tp_rank, ep, ep_rank, etp, etp_rank)
+            experts = [lf for lf in leaves if lf.name.endswith((".w13", ".w2"))]
+            blocks.append((f"layer{l}", [lf for lf in leaves if lf not in experts]))
+            if experts:
+                # expert weights are replicated over a different group (expert-DP), so
+                # they shard, reduce and offload as a block of their own
+                blocks.append((f"layer{l}.experts", experts))
     if with_head:
         blocks.append(("head", head_leaves(arch, tp, tp_rank)))
     return blocks

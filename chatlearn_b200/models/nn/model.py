@@ -440,7 +440,10 @@ class CausalLM:
         self.arch, self.dtype, self.device = arch, dtype, torch.device(device)
         self.tp, self.tp_rank, self.ep, self.ep_rank = tp, tp_rank, ep, ep_rank
         self.etp, self.etp_rank = etp, etp_rank
-        self.layer_range = layer_range or (0, arch.num_hidden_layers)
+        # one (lo, hi) pair, or several when a pipeline stage holds more than one model chunk
+        rs = layer_range or (0, arch.num_hidden_layers)
+        self.layer_ranges = [tuple(rs)] if isinstance(rs[0], int) else [tuple(r) for r in rs]
+        self.layer_range = self.layer_ranges[0]
         self.blocks: List[ParamBlock] = [
             ParamBlock(n, leaves, dtype, self.device, pad_to, allocate)
             for n, leaves in model_blocks(arch, tp, tp_rank, ep, ep_rank, layer_range,
@@ -482,13 +485,18 @@ class CausalLM:
         return self
 
     # ---- forward ----
-    def hidden_states(self, tokens, ctx: FwdCtx, layer_hook=None, x=None):
-        """Embedding + decoder layers (+ final norm when this rank owns the head)."""
-        if x is None and "embed" in self.block_by_name:      # a caller may supply (multimodal) input embeddings
+    def hidden_states(self, tokens, ctx: FwdCtx, layer_hook=None, x=None, chunk: Optional[int] = None):
+        """Embedding + decoder layers (+ final norm when this rank owns the head).  ``chunk`` runs one of several
+        model chunks of a pipeline stage: only the chunk that starts the model embeds, only the one that ends it
+        applies the final norm."""
+        lo, hi = self.layer_range if chunk is None else self.layer_ranges[chunk]
+        starts = chunk is None or lo == 0
+        ends = chunk is None or hi == self.arch.num_hidden_layers
+        if x is None and starts and "embed" in self.block_by_name:      # a caller may supply (multimodal) input embeddings
             x = embed(self.block_by_name["embed"].params, tokens, ctx)
             if x.dtype != self.dtype:
                 x = x.to(self.dtype)
-        for l in range(*self.layer_range):
+        for l in range(lo, hi):
             p = self.layer_params(l)
             if layer_hook is not None:
                 x = layer_hook(l, p, x, ctx)
@@ -499,7 +507,7 @@ class CausalLM:
                 # commutes with a sub-layer output that is still pending)
                 rows, taps = ctx.deepstack
                 x = x.index_add(0, rows, taps[l].to(x.dtype))
-        if "head" in self.block_by_name:
+        if "head" in self.block_by_name and ends:
             norm_w = self.final_norm_weight()
             if ctx.pending is not None:
                 return flush_pending(x, ctx, norm_w, self.arch.rms_norm_eps)

@@ -26,6 +26,8 @@ preset = os.environ.get("PRESET", "tiny_qwen3")
 hf_dir = os.path.join(out, "hf_init")
 if rank == 0 and not os.path.exists(os.path.join(hf_dir, "done")):
     a0 = PRESETS[preset]()
+    if os.environ.get("LAYERS"):
+        a0.num_hidden_layers = int(os.environ["LAYERS"])
     if os.environ.get("NOAUX", "0") == "1":
         a0.router_aux_loss_coef = 0.0      # the balancing loss depends on how tokens are grouped into micro-batches
     m = CausalLM(a0, dtype=torch.float32).init_weights(7, std=0.05)
@@ -42,6 +44,7 @@ cfg = {
     "models": {
         "policy_trainer": {"num_gpu": W, "trainable": True, "load": hf_dir, "tensor_model_parallel_size": tp,
                            "pipeline_model_parallel_size": pp, "context_parallel_size": cp,
+                           "virtual_pipeline_model_parallel_size": int(os.environ.get("VPP", "1")),
                            "expert_model_parallel_size": ep, "expert_tensor_parallel_size": etp,
                            "sequence_parallel": os.environ.get("SEQ_PAR", "1") == "1", "packing": os.environ.get("PACKING", "1") == "1",
                            "max_token_in_packing": 96, "generation_batch_size": 4, "kl_coef": 0.01,

@@ -20,7 +20,8 @@ arch = {"preset": os.environ.get("PRESET", "tiny_qwen3")}
 mcfg = {"num_layers": 2, "hidden_size": 256, "num_attention_heads": 4, "ffn_hidden_size": 704,
         "max_position_embeddings": 512, "kv_channels": 64}
 par = {"tensor_model_parallel_size": int(os.environ.get("TP", "2")), "pipeline_model_parallel_size": int(os.environ.get("PP", "1")),
-       "context_parallel_size": int(os.environ.get("CP", "1")), "expert_model_parallel_size": int(os.environ.get("EP", "1"))}
+       "context_parallel_size": int(os.environ.get("CP", "1")), "expert_model_parallel_size": int(os.environ.get("EP", "1")),
+       "virtual_pipeline_model_parallel_size": int(os.environ.get("VPP", "1"))}
 cfg = {
   "runtime_args": {"train_backend": "megatron", "exp_name": "mg", "output_dir": out, "data_path": data,
      "colocation": ["policy", "policy_trainer", "ref_policy"], "num_episode": 2, "sample_per_episode": 16,
@@ -90,4 +91,12 @@ def test_grpo_qwen3_next_pp2_trainer(tmp_path):
     """Gated delta-net hybrid under the Megatron-style trainer: two pipeline stages (two layers each); the
     rollout weights equal the trainer's after the last sync."""
     res = _res(run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "TP": "1", "PP": "2", "PRESET": "tiny_qwen3_next"})[0])
+    assert len(res) == 2 and all(r["episodes"] == 2 and r["maxdiff"] == 0.0 for r in res)
+
+
+def test_grpo_pp2_with_two_model_chunks_per_stage(tmp_path):
+    """Interleaved pipeline schedule end to end: four layers as 2 stages x 2 chunks (stage 0 holds layers 0 and 2),
+    scoring, training, checkpoint, and a weight sync that leaves the rollout weights equal to the trainer's."""
+    res = _res(run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "TP": "1", "PP": "2", "VPP": "2",
+                                         "PRESET": "tiny_qwen3_next"})[0])
     assert len(res) == 2 and all(r["episodes"] == 2 and r["maxdiff"] == 0.0 for r in res)

@@ -45,9 +45,11 @@ def _compare(a, b, tol=5e-4):
     ("cp2", 2, dict(CP=2)),
     ("dp2", 2, dict()),
     ("tp2_gspo", 2, dict(TP=2, GSPO=1)),
+    # two model chunks per stage, interleaved one-forward-one-backward over a global time table
+    ("pp2vpp2", 2, dict(PP=2, VPP=2, LAYERS=4)),
 ])
 def test_dense_parallel_matches_single(tmp_path, name, world, env):
-    base_env = {k: v for k, v in env.items() if k == "GSPO"}
+    base_env = {k: v for k, v in env.items() if k in ("GSPO", "LAYERS")}
     base = _run(tmp_path, "base", 1, **base_env)
     par = _run(tmp_path, name, world, **env)
     _compare(base, par)

@@ -68,3 +68,11 @@ def test_expert_parallel_layouts_match_one_gpu(tmp_path):
     for name, world, env in MOE:
         if world <= NGPU:
             _compare(base, _run(tmp_path, name, world, PRESET="tiny_moe", NOAUX=1, **env))
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs two GPUs")
+def test_interleaved_pipeline_matches_one_gpu(tmp_path):
+    """Two stages with two model chunks each (interleaved one-forward-one-backward, stage boundaries over NCCL
+    point-to-point in one batched exchange per tick) against one GPU holding the same four layers."""
+    base = _run(tmp_path, "base4", 1, LAYERS=4)
+    _compare(base, _run(tmp_path, "pp2vpp2", 2, PP=2, VPP=2, LAYERS=4))

@@ -597,3 +597,28 @@ def test_budgeted_iterations_cover_the_plan_within_bucket_and_memory_limits():
     import pytest as _pt
     with _pt.raises(RuntimeError):
         build_iterations(plan, 4, 1 << 30, {0: 16, 1: 16})
+
+
+def test_interleaved_pipeline_time_table():
+    """Every stage runs each (micro-batch, chunk) forward and backward once, inputs exist before they are used, and
+    the interleaved table is shorter than plain one-forward-one-backward with the same number of layers per stage."""
+    from chatlearn_b200.algorithm.grpo_utils.megatron_policy_trainer import MegatronPolicyTrainer as T
+    for P, V, m in [(2, 2, 4), (4, 2, 8), (2, 3, 5), (4, 2, 3), (2, 2, 1), (3, 2, 6)]:
+        ticks = T.interleaved_ticks(P, V, m)
+        G = P * V
+        when = {}
+        for r in range(P):
+            assert len(ticks[r]) == len(ticks[0])
+            units = [u for u in ticks[r] if u is not None]
+            assert sorted(units) == sorted([(k, i, j) for k in "FB" for i in range(m) for j in range(V)])
+            for t, u in enumerate(ticks[r]):
+                if u is not None:
+                    when[(u[0], u[1], u[2] * P + r)] = t
+        for (kind, mb, g), t in when.items():
+            if kind == "F" and g > 0:
+                assert when[("F", mb, g - 1)] < t
+            if kind == "B":
+                assert when[("F", mb, g)] < t and (g == G - 1 or when[("B", mb, g + 1)] < t)
+        if m % P == 0 and m >= 2 * P:
+            # plain 1F1B: (m + P - 1) slots of V chunk-units each, forward and backward
+            assert len(ticks[0]) < 2 * V * (m + P - 1)
