@@ -1,0 +1,21 @@
+#!/bin/bash
+# qwen3-8b-mcore-grpo-partial: run from the repository root.
+set -x
+export CHATLEARN=$(pwd)
+export PYTHONPATH=${CHATLEARN}:${PYTHONPATH}
+source examples/base_env.sh
+export exp_name=qwen3-8b-mcore-grpo-partial
+launch grpo --config-file template/grpo_megatron.yaml \
+    runtime_args.exp_name=${exp_name} \
+    runtime_args.output_dir=${CHATLEARN}/output/${exp_name} \
+    runtime_args.data_path=${CHATLEARN}/dataset/MATH-lighteval/train.json \
+    runtime_args.eval_data_path=${CHATLEARN}/dataset/MATH-lighteval/test.json \
+    models.policy_trainer.num_gpu=${num_device} \
+    models.policy_trainer.load=${CHATLEARN}/pretrained_models/Qwen3-8B/ \
+    models.policy_trainer.tensor_model_parallel_size=2 \
+    runtime_args.use_partial_rollout=True \
+    runtime_args.max_replay_episode=4 \
+    models.policy.max_response_tokens_length=8192 \
+    models.partial_rollout_manager.max_rollout_round=2 \
+    models.partial_rollout_manager.rollout_ratio=[0.5,0.5] \
+    2>&1 | tee ${CHATLEARN}/output_${exp_name}.log

@@ -73,3 +73,21 @@ def test_megatron_architecture_block_is_filled_from_the_model_description():
     ds.rope_scaling = {"type": "yarn", "factor": 40}
     mc = arch_to_megatron_cfg(ds, blank())
     assert mc.multi_latent_attention and mc.rotary_scaling_factor == 40.0 and mc.moe_router_num_groups == 8
+
+
+@pytest.mark.parametrize("name", sorted(f for f in os.listdir(os.path.join(ROOT, "examples")) if f.startswith("train_")))
+def test_example_scripts_compose_into_configurations(name):
+    """Every ``key=value`` override of a launch script names a field the configuration schema has and takes a
+    value of its type (shell variables replaced by stand-ins)."""
+    import re
+    text = open(os.path.join(ROOT, "examples", name)).read().replace("\\\n", " ")
+    text = re.sub(r"\$\(\(.*?\)\)", "64", text)              # shell arithmetic (contains spaces)
+    algo = re.search(r"launch (\w+) --config-file", text).group(1)
+    tpl = re.search(r"template/(\S+)", text).group(1)
+    ov = [w for w in text.split() if re.match(r"^(runtime_args|models)\.[\w.]+=", w)]
+    subs = ((r"\$\{CHATLEARN\}", "/x"), (r"\$\{exp_name\}", "e"), (r"\$\{num_device\}", "8"), (r"\$\(\(.*?\)\)", "64"),
+            (r"\$\{\w+(:-(\w+))?\}", r"\2"))
+    for pat, rep in subs:
+        ov = [re.sub(pat, rep, o) for o in ov]
+    cfg = _cfg(algo, tpl, ov)
+    assert cfg.runtime_args.exp_name == "e"
