@@ -4,9 +4,40 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+#include <utility>
+
 namespace cl {
 
 constexpr int kWarp = 32;
+
+// ----------------------------------------------------------------------------- programmatic dependent launch
+// A kernel launched through launch_pdl may be started while its predecessor in the stream still runs: its CTAs
+// become resident as the predecessor's leave, run whatever does not touch the predecessor's data (barrier set-up,
+// tensor-memory allocation, descriptor prefetch) and block in pdl_wait() until the predecessor has completed and
+// its writes are visible.  pdl_trigger() tells the hardware that the successor may start; a grid's successor
+// starts once every CTA of the grid has triggered or exited.  Both are no-ops in a kernel launched the ordinary
+// way, and a successor launched the ordinary way waits for full completion as always.  Rule for every kernel
+// launched through launch_pdl: pdl_wait() comes before its first access to global memory.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static const bool on = [] { const char* e = std::getenv("CLB200_PDL"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}
 
 template <typename T> struct Cvt;
 template <> struct Cvt<float> {

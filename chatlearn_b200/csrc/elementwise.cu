@@ -4,6 +4,7 @@
 // of the reference stack (HF/Megatron model internals, loss_gallery.py, torch
 // AdamW); all are single-pass over their operands.
 #include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAException.h>
 #include <torch/extension.h>
 
 #include "common.cuh"
@@ -30,6 +31,8 @@ template <typename T>
 __global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
                                    float* __restrict__ rstd, int H, float eps) {
   __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const T* xr = x + row * H;
   T* yr = y + row * H;
@@ -140,9 +143,9 @@ std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, do
     constexpr int V = Vec16<scalar_t>::N;
     TORCH_CHECK(H % V == 0, "rmsnorm: hidden size must be a multiple of ", V);
     int threads = std::min(1024, std::max(32, ((H / V + 31) / 32) * 32));
-    rmsnorm_fwd_kernel<scalar_t><<<N, threads, 0, cur_stream()>>>(
+    C10_CUDA_CHECK(launch_pdl(rmsnorm_fwd_kernel<scalar_t>, dim3((unsigned)N), dim3(threads), 0, cur_stream(),
         (const scalar_t*)x.data_ptr(), (const scalar_t*)w.data_ptr(), (scalar_t*)y.data_ptr(),
-        rstd.data_ptr<float>(), H, (float)eps);
+        rstd.data_ptr<float>(), H, (float)eps));
   });
   return {y, rstd};
 }
@@ -173,6 +176,8 @@ std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& x, const at::Tensor& w, co
 // ----------------------------------------------------------------------------- SwiGLU
 template <typename T>
 __global__ void swiglu_fwd_kernel(const T* __restrict__ gu, T* __restrict__ y, int64_t rows, int F) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int V = Vec16<T>::N;
   const int64_t nvec = rows * (F / V);
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < nvec;
@@ -224,8 +229,8 @@ at::Tensor swiglu_fwd(const at::Tensor& gu) {
     TORCH_CHECK(F % V == 0, "swiglu: F must be a multiple of ", V);
     int64_t nvec = rows * (F / V);
     int grid = (int)std::min<int64_t>((nvec + 255) / 256, 148 * 16);
-    swiglu_fwd_kernel<scalar_t><<<grid, 256, 0, cur_stream()>>>((const scalar_t*)gu.data_ptr(),
-                                                                (scalar_t*)y.data_ptr(), rows, F);
+    C10_CUDA_CHECK(launch_pdl(swiglu_fwd_kernel<scalar_t>, dim3(grid), dim3(256), 0, cur_stream(), (const scalar_t*)gu.data_ptr(),
+                              (scalar_t*)y.data_ptr(), rows, F));
   });
   return y;
 }
@@ -407,6 +412,8 @@ __global__ void qkv_rope_append_kernel(const bf16* __restrict__ qkv, int row_str
                                        const int64_t* __restrict__ slots, bf16* __restrict__ q_out,
                                        bf16* __restrict__ kc, bf16* __restrict__ vc, int64_t T_tokens, float eps) {
   constexpr int HE = D / 64;
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
   const int64_t wid = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
@@ -480,10 +487,10 @@ at::Tensor qkv_rope_append(const at::Tensor& qkv, int64_t nq, int64_t nkv, int64
   const bf16* qwp = qw.has_value() ? (const bf16*)qw->data_ptr() : nullptr;
   const bf16* kwp = kw.has_value() ? (const bf16*)kw->data_ptr() : nullptr;
 #define CLB_QRA(DD)                                                                                                      \
-  qkv_rope_append_kernel<DD><<<grid, threads, 0, cur_stream()>>>(                                                        \
+  C10_CUDA_CHECK(launch_pdl(qkv_rope_append_kernel<DD>, dim3(grid), dim3(threads), 0, cur_stream(),                       \
       (const bf16*)qkv.data_ptr(), (int)qkv.stride(0), (int)nq, (int)nkv, qwp, kwp, pos.data_ptr<int64_t>(),             \
       inv_freq.data_ptr<float>(), slots.data_ptr<int64_t>(), (bf16*)q_out.data_ptr(), (bf16*)k_cache.data_ptr(),         \
-      (bf16*)v_cache.data_ptr(), Tn, (float)eps)
+      (bf16*)v_cache.data_ptr(), Tn, (float)eps))
   if (D == 128) CLB_QRA(128);
   else if (D == 64) CLB_QRA(64);
   else TORCH_CHECK(false, "qkv_rope_append: head dim must be 64 or 128");

@@ -27,10 +27,14 @@
 #include <cudaTypedefs.h>
 #include <torch/extension.h>
 
+#include "common.cuh"
 #include "sm100.cuh"
 #include "tmap.h"
 
 using namespace sm100;
+using cl::launch_pdl;
+using cl::pdl_trigger;
+using cl::pdl_wait;
 typedef __nv_bfloat16 bf16;
 
 namespace {
@@ -179,6 +183,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   const bool grouped = grp.table != nullptr;
+  if (grouped) pdl_wait();                      // the tile table and its count come from the kernel before this one
   const int num_tiles = (grouped ? min(grp.count[0], tiles_m) : tiles_m) * tiles_n;   // grouped: tiles_m = table capacity
   const int k_iters = (K + BK - 1) / BK;
   // split-K: a work unit is (tile, k-slice); units of one k-slice are consecutive so
@@ -200,6 +205,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sm->tmem_base;
+  // everything above touched only this CTA's shared and tensor memory; the operands and the output belong to
+  // the kernels before this one in the stream
+  pdl_trigger();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------ TMA producer
@@ -343,6 +352,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 template <typename OutT>
 __global__ void splitk_finalize_kernel(const float* __restrict__ ws, OutT* __restrict__ C, int64_t n, int splits,
                                        int accumulate = 0) {
+  pdl_trigger();
+  pdl_wait();
   for (int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * blockDim.x * 4) {
     float4 v = *reinterpret_cast<const float4*>(ws + i);
     if constexpr (sizeof(OutT) == 4) {
@@ -394,7 +405,8 @@ static void launch_gemm(int dev, int grid, cudaStream_t st, const CUtensorMap& t
     C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_nt_kernel<T, W, AMN, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cfg[dev] = true;
   }
-  gemm_bf16_nt_kernel<T, W, AMN, BMN><<<grid, kThreads, smem, st>>>(tmA, tmB, c, ws, M, N, K, ldc, splits, ga);
+  C10_CUDA_CHECK(launch_pdl(gemm_bf16_nt_kernel<T, W, AMN, BMN>, dim3(grid), dim3(kThreads), smem, st, tmA, tmB, c, ws, M, N, K, ldc,
+                            splits, ga));
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
@@ -553,7 +565,7 @@ static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int a
     else if (bn == 128) launch_gemm<float, 128, 0, 0>(CLB_GEMM_ARGS(p));
     else launch_gemm<float, 64, 0, 0>(CLB_GEMM_ARGS(p));
     if (splits > 1) {
-      splitk_finalize_kernel<float><<<fgrid, 256, 0, st>>>(ws, p, M * N, splits, ga.accumulate);
+      C10_CUDA_CHECK(launch_pdl(splitk_finalize_kernel<float>, dim3(fgrid), dim3(256), 0, st, ws, p, M * N, splits, ga.accumulate));
       C10_CUDA_KERNEL_LAUNCH_CHECK();
     }
   } else {
@@ -564,7 +576,7 @@ static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int a
     else if (bn == 128) launch_gemm<bf16, 128, 0, 0>(CLB_GEMM_ARGS(p));
     else launch_gemm<bf16, 64, 0, 0>(CLB_GEMM_ARGS(p));
     if (splits > 1) {
-      splitk_finalize_kernel<bf16><<<fgrid, 256, 0, st>>>(ws, p, M * N, splits, 0);
+      C10_CUDA_CHECK(launch_pdl(splitk_finalize_kernel<bf16>, dim3(fgrid), dim3(256), 0, st, ws, p, M * N, splits, 0));
       C10_CUDA_KERNEL_LAUNCH_CHECK();
     }
   }

@@ -77,6 +77,8 @@ paged_decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, 
                        float* __restrict__ part_lse, int nq, int nkv, int num_splits, float scale,
                        const int* __restrict__ blk_start = nullptr, int slot_base = 0, int total_slots = 0) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_trigger();
+  pdl_wait();                                     // q, the cache and the tables come from earlier kernels
   auto* sm = reinterpret_cast<SmemTC<DK, DV>*>(smem_raw);
   const int qi = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int rep = nq / nkv;
@@ -243,6 +245,8 @@ paged_prefix_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, 
                        const int* __restrict__ grp_nblk, float* __restrict__ part_o, float* __restrict__ part_lse,
                        int nq, int nkv, int num_splits, int total_slots, float scale) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_trigger();
+  pdl_wait();
   auto* sm = reinterpret_cast<SmemPrefix<DK, DV>*>(smem_raw);
   const int grp = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int nblk = grp_nblk[grp];
@@ -401,6 +405,8 @@ paged_prefix_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, 
 template <int DV>
 __global__ void combine_splits_tc_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                          bf16* __restrict__ out, int num_splits) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t qh = blockIdx.x;
   const int d = threadIdx.x;
   float mx = -INFINITY;
@@ -437,11 +443,13 @@ void launch_tc(const at::Tensor& q, const at::Tensor& kc, const at::Tensor& vc, 
     pop = po.data_ptr<float>(); plp = pl.data_ptr<float>();
   }
   dim3 grid(Tq, nkv, ns);
-  paged_decode_tc_kernel<DK, DV><<<grid, kThreads, smem, st>>>(
+  C10_CUDA_CHECK(launch_pdl(paged_decode_tc_kernel<DK, DV>, grid, dim3(kThreads), smem, st,
       (const bf16*)q.data_ptr(), (const bf16*)kc.data_ptr(), (const bf16*)vc.data_ptr(), bt.data_ptr<int>(),
-      (int)bt.size(1), q_seq, ctx_len.data_ptr<int>(), (bf16*)out.data_ptr(), pop, plp, nq, nkv, ns, scale);
+      (int)bt.size(1), q_seq, ctx_len.data_ptr<int>(), (bf16*)out.data_ptr(), pop, plp, nq, nkv, ns, scale,
+      (const int*)nullptr, 0, 0));
   if (ns > 1)
-    combine_splits_tc_kernel<DV><<<Tq * nq, ((DV + 31) / 32) * 32, 0, st>>>(pop, plp, (bf16*)out.data_ptr(), ns);
+    C10_CUDA_CHECK(launch_pdl(combine_splits_tc_kernel<DV>, dim3(Tq * nq), dim3(((DV + 31) / 32) * 32), 0, st,
+                              (const float*)pop, (const float*)plp, (bf16*)out.data_ptr(), ns));
 }
 
 }  // namespace
@@ -480,19 +488,17 @@ at::Tensor paged_decode_tc_grouped(const at::Tensor& q, const at::Tensor& k_cach
     configured[dev] = true;
   }
   if (G > 0) {
-    paged_prefix_tc_kernel<128, 128><<<dim3(G, nkv, np), kThreads, sizeof(SmemPrefix<128, 128>), st>>>(
+    C10_CUDA_CHECK(launch_pdl(paged_prefix_tc_kernel<128, 128>, dim3(G, nkv, np), dim3(kThreads), sizeof(SmemPrefix<128, 128>), st,
         (const bf16*)q.data_ptr(), (const bf16*)k_cache.data_ptr(), (const bf16*)v_cache.data_ptr(), block_tables.data_ptr<int>(),
         (int)block_tables.size(1), grp_q.data_ptr<int>(), grp_nblk.data_ptr<int>(), po.data_ptr<float>(), pl.data_ptr<float>(),
-        nq, nkv, np, slots, (float)scale);
-    C10_CUDA_KERNEL_LAUNCH_CHECK();
+        nq, nkv, np, slots, (float)scale));
   }
-  paged_decode_tc_kernel<128, 128><<<dim3(Tq, nkv, nsx), kThreads, sizeof(SmemTC<128, 128>), st>>>(
+  C10_CUDA_CHECK(launch_pdl(paged_decode_tc_kernel<128, 128>, dim3(Tq, nkv, nsx), dim3(kThreads), sizeof(SmemTC<128, 128>), st,
       (const bf16*)q.data_ptr(), (const bf16*)k_cache.data_ptr(), (const bf16*)v_cache.data_ptr(), block_tables.data_ptr<int>(),
-      (int)block_tables.size(1), nullptr, ctx_len.data_ptr<int>(), (bf16*)out.data_ptr(), po.data_ptr<float>(), pl.data_ptr<float>(),
-      nq, nkv, nsx, (float)scale, blk_start.data_ptr<int>(), np, slots);
-  C10_CUDA_KERNEL_LAUNCH_CHECK();
-  combine_splits_tc_kernel<128><<<Tq * nq, 128, 0, st>>>(po.data_ptr<float>(), pl.data_ptr<float>(), (bf16*)out.data_ptr(), slots);
-  C10_CUDA_KERNEL_LAUNCH_CHECK();
+      (int)block_tables.size(1), (const int*)nullptr, ctx_len.data_ptr<int>(), (bf16*)out.data_ptr(), po.data_ptr<float>(),
+      pl.data_ptr<float>(), nq, nkv, nsx, (float)scale, blk_start.data_ptr<int>(), np, slots));
+  C10_CUDA_CHECK(launch_pdl(combine_splits_tc_kernel<128>, dim3(Tq * nq), dim3(128), 0, st, po.data_ptr<float>(), pl.data_ptr<float>(),
+                            (bf16*)out.data_ptr(), slots));
   return out;
 }
 

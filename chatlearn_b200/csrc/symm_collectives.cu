@@ -16,6 +16,7 @@
 //
 // No TMA, no multicast: peer traffic is plain 16-byte ld/st.global.
 #include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAException.h>
 #include <torch/extension.h>
 
 #include "common.cuh"
@@ -178,6 +179,8 @@ __global__ void ar_residual_rmsnorm_kernel(PeerTable parts, PeerTable flags, uin
                                            const bf16* __restrict__ w, bf16* __restrict__ hout, int T, int H,
                                            float eps, int rank, int world, int num_slots, int slot_base) {
   __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
   if (!cta_barrier(flags, expect, slot_base + blockIdx.x, num_slots, rank, world)) return;
   const int nvec = H / 8;
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
@@ -377,9 +380,13 @@ at::Tensor add_residual_rmsnorm(at::Tensor resid, const at::Tensor& delta, const
   auto st = at::cuda::getCurrentCUDAStream();
   bf16* hp = hout.defined() ? (bf16*)hout.data_ptr() : nullptr;
   // world = 1: the barrier inside the kernel touches neither the flag table nor the counters
-  if (vpt <= 1) ar_residual_rmsnorm_kernel<1><<<grid, 256, 0, st>>>(parts, flags, nullptr, (bf16*)resid.data_ptr(), wp, hp, T, H, (float)eps, 0, 1, 1, 0);
-  else if (vpt == 2) ar_residual_rmsnorm_kernel<2><<<grid, 256, 0, st>>>(parts, flags, nullptr, (bf16*)resid.data_ptr(), wp, hp, T, H, (float)eps, 0, 1, 1, 0);
-  else ar_residual_rmsnorm_kernel<4><<<grid, 256, 0, st>>>(parts, flags, nullptr, (bf16*)resid.data_ptr(), wp, hp, T, H, (float)eps, 0, 1, 1, 0);
+#define CLB_ARN(VPT)                                                                                                      \
+  C10_CUDA_CHECK(launch_pdl(ar_residual_rmsnorm_kernel<VPT>, dim3(grid), dim3(256), 0, st, parts, flags, (uint32_t*)nullptr, \
+                            (bf16*)resid.data_ptr(), wp, hp, T, H, (float)eps, 0, 1, 1, 0))
+  if (vpt <= 1) CLB_ARN(1);
+  else if (vpt == 2) CLB_ARN(2);
+  else CLB_ARN(4);
+#undef CLB_ARN
   return hout;
 }
 
