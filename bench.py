@@ -41,6 +41,10 @@ def parse():
     p.add_argument("--max-response", type=int, default=2048)
     p.add_argument("--pack-tokens", type=int, default=16384)
     p.add_argument("--gemm", default=None, choices=[None, "tcgen05", "cublas"])
+    p.add_argument("--layers", type=int, default=0,
+                   help="run the model with this many decoder layers instead of its own depth (exercises a large "
+                        "architecture on few GPUs; the JSON line then names the reduced depth and is not a figure "
+                        "for the full model)")
     p.add_argument("--no-offload", action="store_true")
     p.add_argument("--rollout-tp", type=int, default=1,
                    help="tensor-parallel size of a rollout replica (1: every GPU generates for its own samples; 2: pairs "
@@ -143,6 +147,8 @@ def build_config(args, out_dir, data_path, n_gpu):
     spe = args.prompts_per_gpu * n * n_gpu
     offload = not args.no_offload
     arch = {"preset": args.model}
+    if args.layers > 0:
+        arch["num_hidden_layers"] = args.layers
     seq = args.prompt_len[1] + args.max_response
     common = {"model_arch": arch, "packing": True, "max_token_in_packing": args.pack_tokens,
               "max_prompt_tokens_length": args.prompt_len[1] + 1, "max_response_tokens_length": args.max_response}
@@ -323,7 +329,8 @@ def main():
             "warmup_requested": args.warmup, "time_budget_s": args.time_budget, "ms_per_step": round(ms_per_step, 2),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": vs_baseline(world, value, args), "dtype": "bf16", "data": "synthetic",
             "impl": args.impl if args.impl == "native" else "library trainer (cuBLAS + flash-attn + PyTorch statements), native rollout",
-            "config": {"model": args.model, "global_batch": samples, "seq_len": seq,
+            "config": {"model": args.model if args.layers <= 0 else f"{args.model} cut to {args.layers} layers",
+                       "global_batch": samples, "seq_len": seq,
                        "trainer_parameters": "sharded 1/N per GPU (gathered per segment)" if args.reshard else "whole per GPU (optimizer state sharded)",
                        "parallelism": f"trainer zero-dp{world} + rollout tp{max(1, min(args.rollout_tp, world))}x{world // max(1, min(args.rollout_tp, world))}",
                        "prompts": samples // args.samples_per_prompt, "samples_per_prompt": args.samples_per_prompt,

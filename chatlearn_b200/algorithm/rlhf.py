@@ -137,7 +137,8 @@ class RewardModel(ScalarHeadModule):
             batch = pack_samples(mb, pad_multiple=pad)
             v = self._scores(batch)
             # the last real token of each sequence (any alignment pad comes after it)
-            lens = torch.tensor([int(s["prompt_token_length"]) + int(s["response_token_length"]) for s in mb])
+            lens = torch.tensor([int(s["prompt_token_length"]) + int(s["response_token_length"]) for s in mb],
+                                device=batch.cu_seqlens.device)
             last = batch.cu_seqlens[:len(mb)].long() + lens - 1
             sc = v[last.to(v.device)]
             if clip > 0:
