@@ -84,6 +84,8 @@ int64_t symm_moe_last_status();
 bool attn_varlen_fwd_supported(int64_t head_dim);
 std::vector<at::Tensor> attn_varlen_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                         const at::Tensor& cu_seqlens, double scale, bool causal);
+void gemm_bf16_nt_scatter(const at::Tensor& a, const at::Tensor& b, const std::vector<int64_t>& dst, int64_t rows_per_rank);
+at::Tensor symm_sum_slots(const at::Tensor& buf, int64_t world, int64_t rows, int64_t cols);
 at::Tensor grouped_gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets);
 at::Tensor grouped_gemm_bf16_nn(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets);
 at::Tensor grouped_gemm_bf16_tn(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets, at::Tensor out,
@@ -158,6 +160,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_moe_last_status", &symm_moe_last_status);
   m.def("attn_varlen_fwd_supported", &attn_varlen_fwd_supported);
   m.def("attn_varlen_fwd", &attn_varlen_fwd);
+  m.def("gemm_bf16_nt_scatter", &gemm_bf16_nt_scatter);
+  m.def("symm_sum_slots", &symm_sum_slots);
   m.def("grouped_gemm_bf16_nt", &grouped_gemm_bf16_nt);
   m.def("grouped_gemm_bf16_nn", &grouped_gemm_bf16_nn);
   m.def("grouped_gemm_bf16_tn", &grouped_gemm_bf16_tn, py::arg("a"), py::arg("b"), py::arg("offsets"), py::arg("out"),

@@ -58,6 +58,9 @@ struct __align__(1024) SmemLayoutT {
   uint64_t acc_empty[kAccBufs];
   uint32_t tmem_base;
   uint32_t abort_flag;
+  // reduce-scatter epilogue: per epilogue warp, 32 rows x 64 bf16 columns (128 bytes, padded to 144 against bank
+  // conflicts) staged so that the stores that cross NVLink cover whole 128-byte row segments
+  alignas(16) uint8_t stage_c[4][32 * 144];
 };
 using SmemLayout = SmemLayoutT<BN>;
 
@@ -147,6 +150,9 @@ struct GroupArgs {
   // included) instead of C
   void* peer_out[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int n_peer = 0;
+  // scatter_rows > 0 (with n_peer > 0): reduce-scatter form.  Row r of the product goes to destination
+  // r / scatter_rows only, at row r % scatter_rows of that destination's buffer (this rank's chunk of it)
+  int scatter_rows = 0;
   int accumulate = 0;       // fp32 output only: C += A*B instead of C = A*B
   // ragged_m > 0: grouped weight gradient.  The contraction runs over a group's rows: table entries are
   // {first C row, end C row, first K row, end K row}; C is [groups * ragged_m, N] and a tile's columns of
@@ -309,6 +315,47 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
         const int col = n0 + c;
+        if constexpr (sizeof(OutT) == 2) {
+          if (grp.scatter_rows > 0 && grp.n_peer > 0) {
+            // GEMM + reduce-scatter: every row of this rank's partial product is stored once, into the receive
+            // buffer of the rank that owns the row (over NVLink unless that is this rank), while the MMA warp
+            // already works on the next tile; the owner adds the chunks up.  Two 32-column chunks are packed to
+            // bf16 and staged in shared memory, then written with lanes laid along the row: every store
+            // instruction covers four rows of 128 contiguous bytes instead of 32 separate 16-byte pieces.
+            uint8_t* stg = sm->stage_c[q];
+            const int half = (c >> 5) & 1;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 pk;
+              uint32_t* pp = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+                pp[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(stg + lane * 144 + half * 64 + v * 16) = pk;
+            }
+            if (half == 1 || c + 32 >= BN) {
+              __syncwarp();
+              const int cbase = n0 + (c & ~63);               // first column of the staged pair
+              const int piece = lane & 7;                     // 16 bytes = 8 columns
+              const int gcol = cbase + piece * 8;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rr = 4 * i + (lane >> 3);
+                const int grow = m0 + q * 32 + rr;
+                if (grow < row_end && gcol < N && !empty_slice && (half == 1 || piece < 4)) {
+                  const int dst = grow / grp.scatter_rows;
+                  const uint4 val = *reinterpret_cast<const uint4*>(stg + rr * 144 + piece * 16);
+                  *reinterpret_cast<uint4*>(static_cast<bf16*>(grp.peer_out[dst]) +
+                                            (int64_t)(grow - dst * grp.scatter_rows) * ldc + gcol) = val;
+                }
+              }
+              __syncwarp();
+            }
+            continue;
+          }
+        }
         if (row < row_end && col < N && !empty_slice) {
           if (splits == 1) {
             if (grp.n_peer == 0) {
@@ -415,7 +462,7 @@ static void launch_gemm(int dev, int grid, cudaStream_t st, const CUtensorMap& t
 // out_fp32; `accumulate` (fp32 only) adds the product to what `out` already holds.
 static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int amn, int bmn, bool out_fp32,
                                  const at::Tensor* out, bool accumulate = false,
-                                 const std::vector<int64_t>* peer_out = nullptr);
+                                 const std::vector<int64_t>* peer_out = nullptr, int64_t scatter_rows = 0);
 
 static at::Tensor gemm_bf16_nt_impl(const at::Tensor& a, const at::Tensor& b, bool out_fp32, const at::Tensor* out,
                                     const std::vector<int64_t>* peer_out = nullptr) {
@@ -435,6 +482,19 @@ void gemm_bf16_nt_push(const at::Tensor& a, const at::Tensor& b, at::Tensor out,
 
 at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32) {
   return gemm_bf16_nt_impl(a, b, out_fp32, nullptr);
+}
+
+// GEMM + reduce-scatter push: this rank's partial product a[M, K] * b[N, K]^T, rows split into `dst.size()` blocks
+// of rows_per_rank; block d is stored (bf16) at dst[d], an address inside rank d's receive buffer (this rank's
+// chunk of it, [rows_per_rank, N] contiguous).  Nothing is written locally except block `rank`.
+void gemm_bf16_nt_scatter(const at::Tensor& a, const at::Tensor& b, const std::vector<int64_t>& dst, int64_t rows_per_rank) {
+  TORCH_CHECK(!dst.empty() && dst.size() <= 8, "gemm_bf16_nt_scatter: 1..8 destinations");
+  TORCH_CHECK(rows_per_rank > 0 && a.size(0) == rows_per_rank * (int64_t)dst.size(),
+              "gemm_bf16_nt_scatter: the rows must split evenly over the destinations");
+  for (int64_t p : dst) TORCH_CHECK(p % 16 == 0, "gemm_bf16_nt_scatter: 16-byte aligned destinations");
+  // the shared code path wants an output tensor for its dtype; in this mode no element of it is written
+  auto unused = at::empty({8}, a.options());
+  gemm_bf16_impl(a, b, 0, 0, false, &unused, false, &dst, rows_per_rank);
 }
 
 // Same GEMM, result written into a caller-provided contiguous [M, N] tensor (for
@@ -473,7 +533,8 @@ at::Tensor gemm_bf16_tn(const at::Tensor& a, const at::Tensor& b, const c10::opt
 static const bool g_trace = std::getenv("CLB200_GEMM_TRACE") != nullptr;
 
 static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int amn, int bmn, bool out_fp32,
-                                 const at::Tensor* out, bool accumulate, const std::vector<int64_t>* peer_out) {
+                                 const at::Tensor* out, bool accumulate, const std::vector<int64_t>* peer_out,
+                                 int64_t scatter_rows) {
   GTRACE("enter amn=%d bmn=%d fp32=%d acc=%d", amn, bmn, (int)out_fp32, (int)accumulate);
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16,
               "gemm_bf16: bf16 CUDA tensors");
@@ -553,6 +614,7 @@ static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int a
   if (peer_out != nullptr) {
     TORCH_CHECK(splits == 1, "pushed output needs an unsliced K");
     ga.n_peer = (int)peer_out->size();
+    ga.scatter_rows = (int)scatter_rows;
     for (int i = 0; i < ga.n_peer; ++i) ga.peer_out[i] = reinterpret_cast<void*>((*peer_out)[i]);
   }
   const int fgrid = (int)std::min<int64_t>((M * N / 4 + 255) / 256, 148 * 8);

@@ -358,6 +358,38 @@ void symm_group_barrier(const std::vector<int64_t>& flag_ptrs, at::Tensor expect
                                                                       (int)slot, (int)num_slots, (int)rank, (int)flag_ptrs.size());
 }
 
+// out[i] = sum over the `world` chunks of buf (chunk stride n elements), fp32 accumulation in a fixed order:
+// the owner's side of a reduce-scatter whose chunks were pushed into its receive buffer.
+__global__ void sum_slots_kernel(const bf16* __restrict__ buf, int world, int64_t n, bf16* __restrict__ out) {
+  for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v * 8 < n; v += (int64_t)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int r = 0; r < world; ++r) {
+      Vec16<bf16> x = ld16(buf + (int64_t)r * n + v * 8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(x.v[j]);
+    }
+    Vec16<bf16> o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o.v[j] = __float2bfloat16(acc[j]);
+    st16(out + v * 8, o);
+  }
+}
+
+// buf: this rank's receive buffer holding `world` chunks of rows x cols bf16 values back to back.
+at::Tensor symm_sum_slots(const at::Tensor& buf, int64_t world, int64_t rows, int64_t cols) {
+  const int64_t n = rows * cols;
+  TORCH_CHECK(buf.is_cuda() && buf.is_contiguous() && (int64_t)buf.numel() * buf.element_size() >= world * n * 2 && n % 8 == 0 &&
+                  (uintptr_t)buf.data_ptr() % 16 == 0, "sum_slots: contiguous buffer of world chunks, chunk a multiple of 8 elements");
+  auto out = at::empty({rows, cols}, buf.options().dtype(at::kBFloat16));
+  if (n == 0) return out;
+  const int grid = (int)std::min<int64_t>((n / 8 + 255) / 256, 148 * 8);
+  sum_slots_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>((const bf16*)buf.data_ptr(), (int)world, n, (bf16*)out.data_ptr());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
 // Single-rank form of the kernel above: resid += delta; returns rmsnorm(resid) * w (undefined when w is absent).
 at::Tensor add_residual_rmsnorm(at::Tensor resid, const at::Tensor& delta, const c10::optional<at::Tensor>& w, double eps) {
   TORCH_CHECK(resid.scalar_type() == at::kBFloat16 && resid.is_contiguous() && resid.dim() == 2, "resid: contiguous bf16 [T, H]");

@@ -18,6 +18,8 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
+from chatlearn_b200 import ops
+
 from chatlearn_b200.models.base_module import TorchModule
 from chatlearn_b200.models.fsdp_module import FSDPModule
 from chatlearn_b200.models.nn import CausalLM, ModelArch, resolve_arch
@@ -193,6 +195,10 @@ class MegatronModule(FSDPModule):
                     # experts kept whole on every tensor-parallel rank work on that rank's rows only
                     if b.short(lf.name) in ("w13", "w2") and self.etp_size == 1 and self.ep_size == 1:
                         lf.grad_sum_tp = True
+        if self.seq_parallel and self.device.type == "cuda" and self.trainable and ops.get_mode() == "native":
+            # row-parallel layers: product and reduce-scatter in one pass over peer memory
+            from chatlearn_b200.parallel import symm_collectives
+            symm_collectives.attach_gemm_reduce_scatter(self.tp_group)
         self.cp = ContextParallel(self.cp_group) if self.cp_size > 1 else None
         if self.cp is not None:
             from chatlearn_b200.parallel import symm_collectives

@@ -174,6 +174,20 @@ def _tp_reduce(x, ctx):
     return x
 
 
+def _row_parallel(x, w, ctx):
+    """Row-parallel linear layer and the sum of its output over the tensor-parallel group.  Under sequence
+    parallelism on GPUs the product and the reduce-scatter are one pass (the GEMM epilogue stores every row block
+    into its owner's receive buffer over NVLink: ``SymmGroup.gemm_reduce_scatter``)."""
+    tp = ctx.tp
+    if tp is not None and tp.size > 1 and ctx.seq_parallel and x.is_cuda:
+        fused = tp.fast.get("gemm_rs")
+        if fused is not None:
+            y = fused(x, w)
+            if y is not None:
+                return y
+    return _tp_reduce(ops.linear(x, w), ctx)
+
+
 def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx, layer: int,
                     partial: bool = False):
     """``partial=True`` (tensor-parallel inference with in-kernel collectives) returns this
@@ -222,7 +236,7 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
                 out = o.reshape(T, nh_l * dv)
                 if partial:
                     return ctx.tp_symm.gemm_partial(out.contiguous(), p["o_proj"])
-                return _tp_reduce(ops.linear(out, p["o_proj"]), ctx)
+                return _row_parallel(out, p["o_proj"], ctx)
         kvb = ops.linear(c, p["kv_b_proj"]).view(T, nh_l, nope + dv)
         k_nope, v = kvb[..., :nope], kvb[..., nope:].contiguous()
         k = torch.cat([k_nope, k_rope.expand(T, nh_l, rp)], dim=-1)
@@ -242,7 +256,7 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
                                     kvc.q_lens, 1.0 / math.sqrt(d), groups=kvc.groups)
             if partial:
                 return ctx.tp_symm.gemm_partial(o.reshape(o.shape[0], -1), p["o_proj"])
-            return _tp_reduce(ops.linear(o.reshape(o.shape[0], -1), p["o_proj"]), ctx)
+            return _row_parallel(o.reshape(o.shape[0], -1), p["o_proj"], ctx)
         q = qkv[:, :nh_l * d].view(T, nh_l, d)
         k = qkv[:, nh_l * d:(nh_l + nkv_l) * d].view(T, nkv_l, d)
         v = qkv[:, (nh_l + nkv_l) * d:].view(T, nkv_l, d)
@@ -292,11 +306,14 @@ def _tp_copy(x, ctx):
     return x
 
 
-def dense_mlp(p, x, ctx, prefix="", partial: bool = False):
+def dense_mlp(p, x, ctx, prefix="", partial: bool = False, reduce: bool = False):
+    """``reduce``: return the output already summed over the tensor-parallel group."""
     x = _tp_copy(x, ctx)
     h = ops.swiglu(ops.linear(x, p[prefix + "gate_up"]))
     if partial:
         return ctx.tp_symm.gemm_partial(h, p[prefix + "down_proj"])
+    if reduce:
+        return _row_parallel(h, p[prefix + "down_proj"], ctx)
     return ops.linear(h, p[prefix + "down_proj"])
 
 
@@ -395,7 +412,7 @@ def _decoder_layer_infer_fused(arch: ModelArch, p, x, ctx: FwdCtx, layer: int):
         h = ops.rmsnorm(x, p["input_layernorm"], eps)
     a = attention_block(arch, p, h, ctx, layer)
     h = ops.add_rmsnorm_(x, a, p["post_attention_layernorm"], eps)
-    ctx.pending = moe_block(arch, p, h, ctx) if "router" in p else _tp_reduce(dense_mlp(p, h, ctx), ctx)
+    ctx.pending = moe_block(arch, p, h, ctx) if "router" in p else dense_mlp(p, h, ctx, reduce=True)
     return x
 
 
@@ -415,7 +432,7 @@ def decoder_layer(arch: ModelArch, p, x, ctx: FwdCtx, layer: int):
     h = ops.rmsnorm(x, p["post_attention_layernorm"], arch.rms_norm_eps)
     if "router" in p:
         return x + moe_block(arch, p, h, ctx)
-    return x + _tp_reduce(dense_mlp(p, h, ctx), ctx)
+    return x + dense_mlp(p, h, ctx, reduce=True)
 
 
 def embed(p, tokens, ctx: FwdCtx):

@@ -145,7 +145,7 @@ class SymmGroup:
         the result of call ``k`` out, so one barrier per call is enough.  Allocated collectively on
         the first exchange of the group."""
         if self._xbufs is None:
-            cap = int(os.environ.get("CLB200_SYMM_XCHG_MB", "128")) << 20
+            cap = int(os.environ.get("CLB200_SYMM_XCHG_MB", "192")) << 20
             self._xbufs = [symm_mem.empty(cap, torch.uint8, self.device, group=self.pg) for _ in range(2)]
             self._xptrs = [self._ptrs(t) for t in self._xbufs]
             self._xcap = cap
@@ -164,6 +164,31 @@ class SymmGroup:
         self.C.symm_group_barrier(self.flag_ptrs, self.expect, NUM_SLOTS - 1, NUM_SLOTS, self.rank)
         self.native.launch_counts["symm_exchange"] += 1
         return bufs[idx][:total].view(x.dtype).clone()
+
+    def gemm_reduce_scatter(self, x2d: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tensor]:
+        """``reduce_scatter(x2d @ w.T)`` along the rows in one pass: the GEMM epilogue stores every row block of
+        this rank's partial product straight into the receive buffer of the rank that owns the block (tile by
+        tile, over NVLink, while the next tile is being multiplied), one flag barrier makes the chunks visible,
+        and the owner adds its ``world`` chunks.  Output of a row-parallel layer under sequence parallelism
+        (the reference leaves it to Megatron: GEMM, then an NCCL reduce-scatter).  ``None`` when the shapes do
+        not qualify (the caller then multiplies and reduce-scatters separately)."""
+        M, N = x2d.shape[0], w.shape[0]
+        if M % self.world or M == 0 or not self.native.push_ok(x2d, w) or N % 8:
+            return None
+        rows = M // self.world
+        chunk_bytes = rows * N * 2
+        if chunk_bytes % 16:
+            return None
+        bufs = self._exchange_buffers()
+        if chunk_bytes * self.world > self._xcap:
+            return None
+        idx = self._xflip
+        self._xflip ^= 1
+        dst = [p + self.rank * chunk_bytes for p in self._xptrs[idx]]       # my chunk of every rank's buffer
+        self.C.gemm_bf16_nt_scatter(x2d, w, dst, rows)
+        self.C.symm_group_barrier(self.flag_ptrs, self.expect, NUM_SLOTS - 1, NUM_SLOTS, self.rank)
+        self.native.launch_counts["symm_gemm_reduce_scatter"] += 1
+        return self.C.symm_sum_slots(bufs[idx], self.world, rows, N)
 
     def all_gather(self, x: torch.Tensor) -> Optional[torch.Tensor]:
         """Flat concatenation of every rank's ``x`` (equal sizes), or ``None`` when the tensor does
@@ -207,4 +232,49 @@ def attach_exchange(group: Group) -> Optional[SymmGroup]:
     sg = get(group)
     if sg is not None:
         group.fast["exchange"] = sg
+    return sg
+
+
+class _LinearReduceScatter(torch.autograd.Function):
+    """``reduce_scatter(x @ w.T)`` along the rows, fused (forward); the backward all-gathers the output gradient
+    and runs the input- and weight-gradient GEMMs of an ordinary linear layer."""
+
+    @staticmethod
+    def forward(ctx, x, w, group, sg):
+        y = sg.gemm_reduce_scatter(x, w)
+        ctx.save_for_backward(x, w)
+        ctx.group = group
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        native = __import__("chatlearn_b200.ops.native", fromlist=["x"])
+        gf = ctx.group.all_gather_cat(g.contiguous(), 0)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = native.gemm_nn(gf, w)
+        if ctx.needs_input_grad[1]:
+            dw = native.wgrad_accumulate(gf, x, w)
+        return dx, dw, None, None
+
+
+def attach_gemm_reduce_scatter(group: Group) -> Optional[SymmGroup]:
+    """Route the row-parallel layers of a tensor-parallel group under sequence parallelism through the fused
+    GEMM + reduce-scatter (``CLB200_SYMM_GEMM_RS=0`` keeps GEMM + NCCL).  Collective over the group."""
+    if os.environ.get("CLB200_SYMM_GEMM_RS", "1") == "0":
+        return None
+    sg = get(group)
+    if sg is None:
+        return None
+    world = sg.world
+
+    def fused(x, w):
+        x2 = x.reshape(-1, x.shape[-1])
+        M, N = x2.shape[0], w.shape[0]
+        if M == 0 or M % world or not sg.native.push_ok(x2, w) or N % 8 or (M // world) * N * 2 % 16 \
+                or M * N * 2 > (int(os.environ.get("CLB200_SYMM_XCHG_MB", "192")) << 20):
+            return None
+        return _LinearReduceScatter.apply(x2, w, group, sg)
+    group.fast["gemm_rs"] = fused
     return sg

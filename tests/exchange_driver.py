@@ -84,6 +84,63 @@ for name, grp in (("symm", g), ("nccl", plain)):
     res[f"ag_ms_{name}"] = round(timed(lambda: grp.all_gather_cat(xg)), 4)
 res["a2a_bytes_sent_per_rank"] = xa.numel() * 2 * (world - 1) // world
 res["ag_bytes_recv_per_rank"] = xg.numel() * 2 * (world - 1)
+# ---- fused GEMM + reduce-scatter (row-parallel layer under sequence parallelism) against GEMM + NCCL ----
+from chatlearn_b200 import ops  # noqa: E402
+ops.set_mode("native")
+fused = symm_collectives.attach_gemm_reduce_scatter(g)
+assert fused is not None and "gemm_rs" in g.fast
+ok, worst = True, 0.0
+for M, N, K in ((world * 256, 512, 384), (world * 1000, 4096, 1024), (16384, 4096, 2048)):
+    for rep in range(3):                                               # both receive buffers
+        x = (torch.randn(M, K, device=dev) * 0.5).bfloat16().requires_grad_(True)
+        w = (torch.randn(N, K, device=dev) * 0.05).bfloat16().requires_grad_(True)
+        y = g.fast["gemm_rs"](x, w)
+        full = x.detach().float() @ w.detach().float().t()
+        dist.all_reduce(full)
+        want = full[rank * (M // world):(rank + 1) * (M // world)]
+        err = ((y.float() - want).norm() / want.norm()).item()
+        worst = max(worst, err)
+        ok &= y.shape == want.shape and err < 1e-2
+        # gradients: those of all_gather(dy) through an ordinary linear layer
+        gy = torch.randn_like(y)
+        y.backward(gy)
+        gfull = plain.all_gather_cat(gy, 0).float()
+        ok &= ((x.grad.float() - gfull @ w.detach().float()).norm() / (gfull @ w.detach().float()).norm()).item() < 1e-2
+        ok &= ((w.grad.float() - gfull.t() @ x.detach().float()).norm() / (gfull.t() @ x.detach().float()).norm()).item() < 1e-2
+res["gemm_reduce_scatter_ok"], res["gemm_reduce_scatter_rel_err"] = bool(ok), round(worst, 5)
+M, N, K = 16384, 4096, 12288 // world                                   # down projection of Qwen3-8B, K split over the ranks
+x = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+w = (torch.randn(N, K, device=dev) * 0.05).bfloat16()
+out_nccl = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
+
+
+def rs_fused():
+    return sg.gemm_reduce_scatter(x, w)
+
+
+def gemm_only():
+    return __import__("chatlearn_b200.ops.native", fromlist=["x"]).gemm_nt(x, w)
+
+
+def rs_nccl2():
+    dist.reduce_scatter_tensor(out_nccl, gemm_only())
+    return out_nccl
+
+
+for name, fn in (("fused", rs_fused), ("gemm_then_nccl", rs_nccl2), ("gemm_alone", gemm_only)):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize(); dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        fn()
+    e1.record(); torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    res[f"gemm_rs_{name}_us"] = round(t.item() * 1e3, 1)
+res["gemm_rs_shape"] = [M, N, K]
+res["gemm_rs_bytes_over_nvlink_per_rank"] = M * N * 2 * (world - 1) // world
 res["status"] = sg.status()
 if rank == 0:
     print("RESULT " + json.dumps(res), flush=True)

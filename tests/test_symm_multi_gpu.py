@@ -56,7 +56,7 @@ def test_peer_memory_exchange_two_gpus():
     lines = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")]
     assert p.returncode == 0 and lines, p.stdout[-2000:] + p.stderr[-2000:]
     r = json.loads(lines[-1][7:])
-    for key in ("all_gather_ok", "all_to_all_ok", "fallback_ok", "ulysses_ok"):
+    for key in ("all_gather_ok", "all_to_all_ok", "fallback_ok", "ulysses_ok", "gemm_reduce_scatter_ok"):
         assert r[key], (key, r)
     assert r["status"] == 0
 
