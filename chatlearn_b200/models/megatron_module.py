@@ -199,6 +199,8 @@ class MegatronModule(FSDPModule):
             # row-parallel layers: product and reduce-scatter in one pass over peer memory
             from chatlearn_b200.parallel import symm_collectives
             symm_collectives.attach_gemm_reduce_scatter(self.tp_group)
+            # and the gathers of the sequence-parallel rows in front of the column-parallel layers as peer stores
+            symm_collectives.attach_exchange(self.tp_group)
         self.cp = ContextParallel(self.cp_group) if self.cp_size > 1 else None
         if self.cp is not None:
             from chatlearn_b200.parallel import symm_collectives
