@@ -131,6 +131,56 @@ __global__ void rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict_
   }
 }
 
+// Warp per row: the row stays in registers (VPL 16-byte vectors per lane), one read, one warp reduction, no
+// shared memory.  For hidden sizes of exactly 32 * VPL vectors.
+template <typename T, int VPL>
+__global__ void rmsnorm_fwd_rows_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                                        float* __restrict__ rstd, int64_t N, float eps) {
+  constexpr int V = Vec16<T>::N;
+  constexpr int H = 32 * VPL * V;
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t row = blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= N) return;
+  const T* xr = x + row * H;
+  Vec16<T> a[VPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    a[k] = ld16(xr + (k * 32 + lane) * V);
+#pragma unroll
+    for (int j = 0; j < V; ++j) { const float f = Cvt<T>::to_f(a[k].v[j]); ss += f * f; }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / H + eps);
+  if (lane == 0 && rstd) rstd[row] = r;
+  T* yr = y + row * H;
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    Vec16<T> ww = ld16(w + (k * 32 + lane) * V), o;
+#pragma unroll
+    for (int j = 0; j < V; ++j) o.v[j] = Cvt<T>::from_f(Cvt<T>::to_f(a[k].v[j]) * r * Cvt<T>::to_f(ww.v[j]));
+    st16(yr + (k * 32 + lane) * V, o);
+  }
+}
+
+// Launches the warp-per-row kernel when the hidden size is 32 * VPL vectors for a built VPL; false otherwise.
+template <typename T>
+static bool launch_rmsnorm_rows(const T* x, const T* w, T* y, float* rstd, int64_t N, int H, float eps) {
+  constexpr int V = Vec16<T>::N;
+  if (H % (32 * V) != 0) return false;
+  const int vpl = H / (32 * V);
+  const int warps = 4;
+  const dim3 grid((unsigned)((N + warps - 1) / warps)), block(warps * 32);
+  if (vpl == 2) C10_CUDA_CHECK(launch_pdl(rmsnorm_fwd_rows_kernel<T, 2>, grid, block, 0, cur_stream(), x, w, y, rstd, N, eps));
+  else if (vpl == 4) C10_CUDA_CHECK(launch_pdl(rmsnorm_fwd_rows_kernel<T, 4>, grid, block, 0, cur_stream(), x, w, y, rstd, N, eps));
+  else if (vpl == 8) C10_CUDA_CHECK(launch_pdl(rmsnorm_fwd_rows_kernel<T, 8>, grid, block, 0, cur_stream(), x, w, y, rstd, N, eps));
+  else if (vpl == 16) C10_CUDA_CHECK(launch_pdl(rmsnorm_fwd_rows_kernel<T, 16>, grid, block, 0, cur_stream(), x, w, y, rstd, N, eps));
+  else return false;
+  return true;
+}
+
 std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && w.is_contiguous(), "rmsnorm: contiguous CUDA tensors");
   const int H = x.size(-1);
@@ -142,6 +192,9 @@ std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, do
   DISPATCH_FLOAT_BF16(x, "rmsnorm", [&] {
     constexpr int V = Vec16<scalar_t>::N;
     TORCH_CHECK(H % V == 0, "rmsnorm: hidden size must be a multiple of ", V);
+    if (launch_rmsnorm_rows<scalar_t>((const scalar_t*)x.data_ptr(), (const scalar_t*)w.data_ptr(), (scalar_t*)y.data_ptr(),
+                                      rstd.data_ptr<float>(), N, H, (float)eps))
+      return;
     int threads = std::min(1024, std::max(32, ((H / V + 31) / 32) * 32));
     C10_CUDA_CHECK(launch_pdl(rmsnorm_fwd_kernel<scalar_t>, dim3((unsigned)N), dim3(threads), 0, cur_stream(),
         (const scalar_t*)x.data_ptr(), (const scalar_t*)w.data_ptr(), (scalar_t*)y.data_ptr(),
@@ -728,11 +781,31 @@ void adamw_step(at::Tensor master, const at::Tensor& grad, at::Tensor m, at::Ten
 template <typename T>
 __global__ void sumsq_partial_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ part) {
   __shared__ float red[32];
+  constexpr int V = Vec16<T>::N;
   float s = 0.f;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    float f = Cvt<T>::to_f(x[i]);
-    s += f * f;
+  // 16-byte loads, four in flight per thread; the (at most V - 1 + misaligned) elements at the ends go one by one
+  const int64_t mis = (int64_t)(((16 - (reinterpret_cast<uintptr_t>(x) & 15)) & 15) / sizeof(T));
+  const int64_t head = mis < n ? mis : n;
+  const int64_t nvec = (n - head) / V;
+  const T* xv = x + head;
+  const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t v = tid;
+  for (; v + 3 * stride < nvec; v += 4 * stride) {
+    Vec16<T> a = ld16(xv + v * V), b = ld16(xv + (v + stride) * V), c = ld16(xv + (v + 2 * stride) * V),
+             d = ld16(xv + (v + 3 * stride) * V);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float fa = Cvt<T>::to_f(a.v[j]), fb = Cvt<T>::to_f(b.v[j]), fc = Cvt<T>::to_f(c.v[j]), fd = Cvt<T>::to_f(d.v[j]);
+      s += fa * fa + fb * fb + fc * fc + fd * fd;
+    }
   }
+  for (; v < nvec; v += stride) {
+    Vec16<T> a = ld16(xv + v * V);
+#pragma unroll
+    for (int j = 0; j < V; ++j) { const float f = Cvt<T>::to_f(a.v[j]); s += f * f; }
+  }
+  for (int64_t i = tid; i < head; i += stride) { const float f = Cvt<T>::to_f(x[i]); s += f * f; }
+  for (int64_t i = head + nvec * V + tid; i < n; i += stride) { const float f = Cvt<T>::to_f(x[i]); s += f * f; }
   s = block_sum(s, red);
   if (threadIdx.x == 0) part[blockIdx.x] = s;
 }
@@ -748,7 +821,7 @@ at::Tensor sumsq(const at::Tensor& x) {
   auto out = at::zeros({}, x.options().dtype(at::kFloat));
   const int64_t n = x.numel();
   if (n == 0) return out;
-  const int grid = (int)std::min<int64_t>((n + 1023) / 1024, 592);
+  const int grid = (int)std::min<int64_t>((n + 8191) / 8192, 148 * 8);
   auto part = at::empty({grid}, x.options().dtype(at::kFloat));
   auto xc = x.contiguous();
   DISPATCH_FLOAT_BF16(xc, "sumsq", [&] {
