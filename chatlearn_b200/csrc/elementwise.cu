@@ -342,7 +342,6 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ src, int src_stride, i
   __shared__ float dw_red[BWD ? 8 : 1][BWD ? D : 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int e0 = HE * lane;
-  const int64_t items = T_tokens * n_heads;
   const int64_t stride = ((int64_t)gridDim.x * blockDim.x) >> 5;
   float fr[HE], wa[HE], wb[HE];
 #pragma unroll
@@ -351,13 +350,15 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ src, int src_stride, i
   float dwa[HE], dwb[HE];
 #pragma unroll
   for (int j = 0; j < HE; ++j) dwa[j] = dwb[j] = 0.f;
-  for (int64_t wid = ((blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5); wid < items; wid += stride) {
-    const int64_t t = wid / n_heads;
-    const int h = (int)(wid % n_heads);
+  // a warp takes a token and walks its heads: the rotation angles are computed once per token, not once per head
+  for (int64_t wid = ((blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5); wid < T_tokens; wid += stride) {
+    const int64_t t = wid;
     const float p = (float)pos[t];
     float c[HE], s[HE];
 #pragma unroll
     for (int j = 0; j < HE; ++j) sincosf(p * fr[j], &s[j], &c[j]);
+#pragma unroll 2
+    for (int h = 0; h < n_heads; ++h) {
     if (!BWD) {
       const T* xr = src + t * src_stride + h * D;
       float a[HE], b[HE], ss = 0.f;
@@ -422,6 +423,7 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ src, int src_stride, i
       st_he<T, HE>(o + e0, oa);
       st_he<T, HE>(o + D / 2 + e0, ob);
     }
+    }
   }
   if (BWD && w) {
 #pragma unroll
@@ -441,8 +443,7 @@ static void launch_qk(const T* src, int src_stride, int n_heads, const T* w, con
                       float eps) {
   if (Tn * n_heads == 0) return;
   const int threads = 256;                       // 8 warps: the size of the backward's shared reduction
-  const int64_t warps = Tn * n_heads;
-  const int64_t want = (warps * 32 + threads - 1) / threads;
+  const int64_t want = (Tn * 32 + threads - 1) / threads;      // one warp per token
   const int grid = (int)std::min<int64_t>(want, 148 * 8);
   if (D == 128)
     qk_norm_rope_kernel<T, 128, BWD><<<grid, threads, 0, cur_stream()>>>(src, src_stride, n_heads, w, pos, inv_freq,
