@@ -18,7 +18,10 @@ std::vector<at::Tensor> grpo_loss_fwd(const at::Tensor& lp, const at::Tensor& ol
                                       double kl_coef, double ent_coef, double inv_norm);
 at::Tensor qkv_rope_append(const at::Tensor& qkv, int64_t nq, int64_t nkv, int64_t D, const c10::optional<at::Tensor>& qw,
                            const c10::optional<at::Tensor>& kw, const at::Tensor& pos, const at::Tensor& inv_freq,
-                           const at::Tensor& slots, at::Tensor k_cache, at::Tensor v_cache, double eps);
+                           const at::Tensor& slots, at::Tensor k_cache, at::Tensor v_cache, double eps,
+                           const c10::optional<at::Tensor>& planes);
+std::vector<at::Tensor> gemm_bf16_nt_planes(const at::Tensor& a, const at::Tensor& b);
+at::Tensor planes_residual_rmsnorm(at::Tensor resid, const at::Tensor& planes, const c10::optional<at::Tensor>& w, double eps);
 std::vector<at::Tensor> gspo_loss_fwd(const at::Tensor& lp, const at::Tensor& old, const c10::optional<at::Tensor>& ref,
                                       const at::Tensor& adv, const at::Tensor& mask, const c10::optional<at::Tensor>& ent,
                                       const at::Tensor& seq_ids, int64_t num_seqs, double pos_clip, double neg_clip,
@@ -129,7 +132,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
   m.def("grpo_loss_fwd", &grpo_loss_fwd);
   m.def("gspo_loss_fwd", &gspo_loss_fwd);
-  m.def("qkv_rope_append", &qkv_rope_append);
+  m.def("qkv_rope_append", &qkv_rope_append, py::arg("qkv"), py::arg("nq"), py::arg("nkv"), py::arg("D"), py::arg("qw"),
+        py::arg("kw"), py::arg("pos"), py::arg("inv_freq"), py::arg("slots"), py::arg("k_cache"), py::arg("v_cache"),
+        py::arg("eps"), py::arg("planes") = c10::optional<at::Tensor>());
+  m.def("gemm_bf16_nt_planes", &gemm_bf16_nt_planes);
+  m.def("planes_residual_rmsnorm", &planes_residual_rmsnorm);
   m.def("adamw_step", &adamw_step);
   m.def("sumsq", &sumsq);
   m.def("logits_stats", &logits_stats);

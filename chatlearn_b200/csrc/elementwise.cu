@@ -464,7 +464,8 @@ __global__ void qkv_rope_append_kernel(const bf16* __restrict__ qkv, int row_str
                                        const bf16* __restrict__ qw, const bf16* __restrict__ kw,
                                        const int64_t* __restrict__ pos, const float* __restrict__ inv_freq,
                                        const int64_t* __restrict__ slots, bf16* __restrict__ q_out,
-                                       bf16* __restrict__ kc, bf16* __restrict__ vc, int64_t T_tokens, float eps) {
+                                       bf16* __restrict__ kc, bf16* __restrict__ vc, int64_t T_tokens, float eps,
+                                       const float* __restrict__ planes, int S, int64_t plane_stride) {
   constexpr int HE = D / 64;
   pdl_trigger();
   pdl_wait();
@@ -474,13 +475,21 @@ __global__ void qkv_rope_append_kernel(const bf16* __restrict__ qkv, int row_str
   if (wid >= T_tokens * heads) return;
   const int64_t t = wid / heads;
   const int h = (int)(wid % heads);
-  const bf16* xr = qkv + t * row_stride + (int64_t)h * D;
+  const int64_t base = t * row_stride + (int64_t)h * D;
+  // the projection's output: a bf16 row, or (planes != nullptr) the K-slice planes of the GEMM that produced it, added
+  // up here and rounded to bf16 exactly as the finalize kernel would have done
+  auto ldx = [&](int e) -> float {
+    if (planes == nullptr) return __bfloat162float(qkv[base + e]);
+    float v = planes[base + e];
+    for (int s = 1; s < S; ++s) v += planes[(int64_t)s * plane_stride + base + e];
+    return __bfloat162float(__float2bfloat16_rn(v));
+  };
   if (h >= nq + nkv) {                                  // value head: plain copy into the cache slot
     const int64_t slot = slots[t];
     if (slot < 0) return;
     bf16* o = vc + (slot * nkv + (h - nq - nkv)) * D;
 #pragma unroll
-    for (int j = 0; j < 2 * HE; ++j) o[lane + 32 * j] = xr[lane + 32 * j];
+    for (int j = 0; j < 2 * HE; ++j) o[lane + 32 * j] = __float2bfloat16_rn(ldx(lane + 32 * j));
     return;
   }
   const bool is_q = h < nq;
@@ -497,8 +506,8 @@ __global__ void qkv_rope_append_kernel(const bf16* __restrict__ qkv, int row_str
   float a[HE], b[HE], ss = 0.f;
 #pragma unroll
   for (int j = 0; j < HE; ++j) {
-    a[j] = __bfloat162float(xr[lane + 32 * j]);
-    b[j] = __bfloat162float(xr[D / 2 + lane + 32 * j]);
+    a[j] = ldx(lane + 32 * j);
+    b[j] = ldx(D / 2 + lane + 32 * j);
     ss += a[j] * a[j] + b[j] * b[j];
   }
   float r = 1.f;
@@ -523,9 +532,20 @@ __global__ void qkv_rope_append_kernel(const bf16* __restrict__ qkv, int row_str
 // qkv [T, (nq + 2 nkv) * D] bf16 (unit inner stride); caches [num_blocks, block, nkv, D] bf16; returns q_out [T, nq, D].
 at::Tensor qkv_rope_append(const at::Tensor& qkv, int64_t nq, int64_t nkv, int64_t D, const c10::optional<at::Tensor>& qw,
                            const c10::optional<at::Tensor>& kw, const at::Tensor& pos, const at::Tensor& inv_freq,
-                           const at::Tensor& slots, at::Tensor k_cache, at::Tensor v_cache, double eps) {
+                           const at::Tensor& slots, at::Tensor k_cache, at::Tensor v_cache, double eps,
+                           const c10::optional<at::Tensor>& planes) {
   TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.scalar_type() == at::kBFloat16 &&
               qkv.size(1) == (nq + 2 * nkv) * D, "qkv_rope_append: qkv must be bf16 [T, (nq + 2 nkv) * D]");
+  // planes: the projection's K-slice planes fp32 [S, T, width] (then qkv only gives the shape; it is not read)
+  const float* plp = nullptr;
+  int S = 0;
+  if (planes.has_value() && planes->numel() > 0) {
+    TORCH_CHECK(planes->scalar_type() == at::kFloat && planes->dim() == 3 && planes->is_contiguous() &&
+                planes->size(1) == qkv.size(0) && planes->size(2) == qkv.size(1) && qkv.stride(0) == qkv.size(1),
+                "qkv_rope_append: planes must be contiguous fp32 [S, T, width] of a contiguous qkv");
+    plp = planes->data_ptr<float>();
+    S = (int)planes->size(0);
+  }
   TORCH_CHECK(k_cache.scalar_type() == at::kBFloat16 && v_cache.scalar_type() == at::kBFloat16 && k_cache.is_contiguous() &&
               v_cache.is_contiguous() && k_cache.size(2) == nkv && k_cache.size(3) == D && v_cache.size(3) == D,
               "qkv_rope_append: caches must be contiguous bf16 [blocks, block, nkv, D]");
@@ -544,7 +564,7 @@ at::Tensor qkv_rope_append(const at::Tensor& qkv, int64_t nq, int64_t nkv, int64
   C10_CUDA_CHECK(launch_pdl(qkv_rope_append_kernel<DD>, dim3(grid), dim3(threads), 0, cur_stream(),                       \
       (const bf16*)qkv.data_ptr(), (int)qkv.stride(0), (int)nq, (int)nkv, qwp, kwp, pos.data_ptr<int64_t>(),             \
       inv_freq.data_ptr<float>(), slots.data_ptr<int64_t>(), (bf16*)q_out.data_ptr(), (bf16*)k_cache.data_ptr(),         \
-      (bf16*)v_cache.data_ptr(), Tn, (float)eps))
+      (bf16*)v_cache.data_ptr(), Tn, (float)eps, plp, S, (int64_t)(Tn * qkv.size(1))))
   if (D == 128) CLB_QRA(128);
   else if (D == 64) CLB_QRA(64);
   else TORCH_CHECK(false, "qkv_rope_append: head dim must be 64 or 128");

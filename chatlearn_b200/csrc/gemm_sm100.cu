@@ -460,6 +460,11 @@ static void launch_gemm(int dev, int grid, cudaStream_t st, const CUtensorMap& t
 // General entry.  amn = 0: a is [M, K] with K contiguous; amn = 1: a is [K, M] with M contiguous (the
 // product uses a^T).  bmn = 0: b is [N, K]; bmn = 1: b is [K, N].  C [M, N] is bf16, or fp32 when
 // out_fp32; `accumulate` (fp32 only) adds the product to what `out` already holds.
+// A caller that consumes the K-slice planes itself (a kernel that adds them up while it does its own work) sets
+// `want` around one call; the call then skips the finalize kernel and reports where the planes are.
+struct DeferredFinalize { bool want = false; int splits = 1; float* ws = nullptr; };
+static thread_local DeferredFinalize g_defer;
+
 static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int amn, int bmn, bool out_fp32,
                                  const at::Tensor* out, bool accumulate = false,
                                  const std::vector<int64_t>* peer_out = nullptr, int64_t scatter_rows = 0);
@@ -482,6 +487,29 @@ void gemm_bf16_nt_push(const at::Tensor& a, const at::Tensor& b, at::Tensor out,
 
 at::Tensor gemm_bf16_nt(const at::Tensor& a, const at::Tensor& b, bool out_fp32) {
   return gemm_bf16_nt_impl(a, b, out_fp32, nullptr);
+}
+
+// C = A B^T whose K-slice planes are left for the consumer: returns {out bf16 [M, N], planes fp32 [S, M, N]}.  With
+// S > 1 `out` is NOT written and `planes` is a view of the per-device split-K workspace: it is valid until the next
+// K-sliced GEMM on this device, so the consumer kernel must be the next thing launched.  With S = 1 (the shape was
+// not sliced) `out` holds the result and `planes` is an empty tensor.
+std::vector<at::Tensor> gemm_bf16_nt_planes(const at::Tensor& a, const at::Tensor& b) {
+  g_defer = DeferredFinalize{true, 1, nullptr};
+  at::Tensor out;
+  try {
+    out = gemm_bf16_nt_impl(a, b, false, nullptr);
+  } catch (...) {
+    g_defer = DeferredFinalize{};
+    throw;
+  }
+  const DeferredFinalize d = g_defer;
+  g_defer = DeferredFinalize{};
+  at::Tensor planes;
+  if (d.splits > 1 && d.ws != nullptr)
+    planes = at::from_blob(d.ws, {d.splits, out.size(0), out.size(1)}, out.options().dtype(at::kFloat));
+  else
+    planes = at::empty({0}, out.options().dtype(at::kFloat));
+  return {out, planes};
 }
 
 // GEMM + reduce-scatter push: this rank's partial product a[M, K] * b[N, K]^T, rows split into `dst.size()` blocks
@@ -637,7 +665,10 @@ static at::Tensor gemm_bf16_impl(const at::Tensor& a, const at::Tensor& b, int a
     else if (bn == 256) launch_gemm<bf16, 256, 0, 0>(CLB_GEMM_ARGS(p));
     else if (bn == 128) launch_gemm<bf16, 128, 0, 0>(CLB_GEMM_ARGS(p));
     else launch_gemm<bf16, 64, 0, 0>(CLB_GEMM_ARGS(p));
-    if (splits > 1) {
+    if (splits > 1 && g_defer.want) {
+      g_defer.splits = splits;
+      g_defer.ws = ws;
+    } else if (splits > 1) {
       C10_CUDA_CHECK(launch_pdl(splitk_finalize_kernel<bf16>, dim3(fgrid), dim3(256), 0, st, ws, p, M * N, splits, 0));
       C10_CUDA_KERNEL_LAUNCH_CHECK();
     }

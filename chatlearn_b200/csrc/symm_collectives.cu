@@ -390,6 +390,90 @@ at::Tensor symm_sum_slots(const at::Tensor& buf, int64_t world, int64_t rows, in
   return out;
 }
 
+// resid += sum of the K-slice planes of a GEMM (fp32 [S, T, H], rounded to bf16 first, as the finalize kernel would);
+// returns rmsnorm(resid) * w.  Consumes the planes of gemm_bf16_nt_planes without the finalize launch in between.
+template <int VPT>
+__global__ void planes_residual_rmsnorm_kernel(const float* __restrict__ planes, int S, int64_t plane_stride,
+                                               bf16* __restrict__ resid, const bf16* __restrict__ w, bf16* __restrict__ hout,
+                                               int T, int H, float eps) {
+  __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
+  const int nvec = H / 8;
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    float val[VPT][8];
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int v = threadIdx.x + k * blockDim.x;
+      if (v < nvec) {
+        const int64_t off = (int64_t)row * H + v * 8;
+        float acc[8];
+        {
+          const float4 a0 = *reinterpret_cast<const float4*>(planes + off), a1 = *reinterpret_cast<const float4*>(planes + off + 4);
+          acc[0] = a0.x; acc[1] = a0.y; acc[2] = a0.z; acc[3] = a0.w; acc[4] = a1.x; acc[5] = a1.y; acc[6] = a1.z; acc[7] = a1.w;
+        }
+        for (int s = 1; s < S; ++s) {
+          const float* ps = planes + (int64_t)s * plane_stride + off;
+          const float4 a0 = *reinterpret_cast<const float4*>(ps), a1 = *reinterpret_cast<const float4*>(ps + 4);
+          acc[0] += a0.x; acc[1] += a0.y; acc[2] += a0.z; acc[3] += a0.w; acc[4] += a1.x; acc[5] += a1.y; acc[6] += a1.z; acc[7] += a1.w;
+        }
+        Vec16<bf16> rs = ld16(resid + off), o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = __bfloat162float(__float2bfloat16_rn(acc[j]));        // what the finalize kernel would have stored
+          o.v[j] = __float2bfloat16(d + __bfloat162float(rs.v[j]));
+          val[k][j] = __bfloat162float(o.v[j]);
+          sq += val[k][j] * val[k][j];
+        }
+        st16(resid + off, o);
+      }
+    }
+    if (w == nullptr) continue;
+    sq = block_sum(sq, red);
+    const float r = rsqrtf(sq / H + eps);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int v = threadIdx.x + k * blockDim.x;
+      if (v < nvec) {
+        const int64_t off = (int64_t)row * H + v * 8;
+        Vec16<bf16> ww = ld16(w + v * 8), o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.v[j] = __float2bfloat16(val[k][j] * r * __bfloat162float(ww.v[j]));
+        st16(hout + off, o);
+      }
+    }
+  }
+}
+
+at::Tensor planes_residual_rmsnorm(at::Tensor resid, const at::Tensor& planes, const c10::optional<at::Tensor>& w, double eps) {
+  TORCH_CHECK(resid.scalar_type() == at::kBFloat16 && resid.is_contiguous() && resid.dim() == 2, "resid: contiguous bf16 [T, H]");
+  TORCH_CHECK(planes.scalar_type() == at::kFloat && planes.dim() == 3 && planes.is_contiguous() && planes.size(1) == resid.size(0) &&
+                  planes.size(2) == resid.size(1) && planes.size(0) >= 1, "planes: contiguous fp32 [S, T, H]");
+  const int T = (int)resid.size(0), H = (int)resid.size(1), S = (int)planes.size(0);
+  TORCH_CHECK(H % 8 == 0 && H <= 256 * 8 * 4, "hidden size must be a multiple of 8 and at most 8192");
+  at::Tensor hout;
+  const bf16* wp = nullptr;
+  if (w.has_value()) {
+    TORCH_CHECK(w->scalar_type() == at::kBFloat16 && w->numel() == H && w->is_contiguous(), "w: bf16 [H]");
+    hout = at::empty_like(resid);
+    wp = (const bf16*)w->data_ptr();
+  }
+  if (T == 0) return hout;
+  const int grid = std::min(T, 148 * 4);
+  const int vpt = (H / 8 + 255) / 256;
+  auto st = at::cuda::getCurrentCUDAStream();
+  bf16* hp = hout.defined() ? (bf16*)hout.data_ptr() : nullptr;
+#define CLB_PRN(VPT)                                                                                                        \
+  C10_CUDA_CHECK(launch_pdl(planes_residual_rmsnorm_kernel<VPT>, dim3(grid), dim3(256), 0, st, planes.data_ptr<float>(), S, \
+                            (int64_t)T * H, (bf16*)resid.data_ptr(), wp, hp, T, H, (float)eps))
+  if (vpt <= 1) CLB_PRN(1);
+  else if (vpt == 2) CLB_PRN(2);
+  else CLB_PRN(4);
+#undef CLB_PRN
+  return hout;
+}
+
 // Single-rank form of the kernel above: resid += delta; returns rmsnorm(resid) * w (undefined when w is absent).
 at::Tensor add_residual_rmsnorm(at::Tensor resid, const at::Tensor& delta, const c10::optional<at::Tensor>& w, double eps) {
   TORCH_CHECK(resid.scalar_type() == at::kBFloat16 && resid.is_contiguous() && resid.dim() == 2, "resid: contiguous bf16 [T, H]");

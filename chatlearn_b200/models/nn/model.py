@@ -158,6 +158,7 @@ class FwdCtx:
     tp_symm: Any = None                    # parallel.symm_collectives.SymmGroup of the TP group (inference)
     pending: Any = None                    # sub-layer output (or un-reduced TP partial) not yet added to the residual stream
     fuse_add_norm: bool = False            # inference: fuse residual adds with the following RMSNorm (in-place stream)
+    planes_ok: bool = False                # GEMM outputs may be handed on as un-added K-slice planes (set per layer)
     mrope_positions: Optional[torch.Tensor] = None   # [3, T] time/row/column positions (vision-language models)
     deepstack: Any = None                  # (rows, [features per early layer]): vision taps added after layer i (Qwen3-VL)
     seq_parallel: bool = False             # residual stream and norms hold 1/tp of the rows (Megatron sequence parallelism)
@@ -179,6 +180,10 @@ def _row_parallel(x, w, ctx):
     parallelism on GPUs the product and the reduce-scatter are one pass (the GEMM epilogue stores every row block
     into its owner's receive buffer over NVLink: ``SymmGroup.gemm_reduce_scatter``)."""
     tp = ctx.tp
+    if ctx.planes_ok and (tp is None or tp.size == 1):
+        # the caller adds the product to the residual stream in its next kernel, which can read the GEMM's K-slice
+        # planes directly
+        return ops.linear_planes(x, w)
     if tp is not None and tp.size > 1 and ctx.seq_parallel and x.is_cuda:
         fused = tp.fast.get("gemm_rs")
         if fused is not None:
@@ -242,10 +247,14 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
         k = torch.cat([k_nope, k_rope.expand(T, nh_l, rp)], dim=-1)
         nkv_l = nh_l
     else:
-        qkv = ops.linear(x, p["qkv"], p.get("qkv_bias"))
+        paged = (ctx.kv is not None and not ctx.kv.prefill_only and ctx.mrope_positions is None and not torch.is_grad_enabled()
+                 and (ctx.sp is None or ctx.sp.size == 1))
+        if paged and ctx.planes_ok and p.get("qkv_bias") is None and x.dim() == 2:
+            qkv = ops.linear_planes(x, p["qkv"])          # the fused kernel below adds the K slices up itself
+        else:
+            qkv = ops.linear(x, p["qkv"], p.get("qkv_bias"))
         nkv_l = (qkv.shape[-1] // d - nh_l) // 2
-        if (ctx.kv is not None and not ctx.kv.prefill_only and ctx.mrope_positions is None and not torch.is_grad_enabled()
-                and (ctx.sp is None or ctx.sp.size == 1)):
+        if paged:
             # steps that attend over the paged cache (decode, continuation chunks): q/k norm + RoPE and the cache
             # append are one kernel; the queries are all that comes back
             kvc = ctx.kv
@@ -394,7 +403,7 @@ def flush_pending(x, ctx: FwdCtx, norm_w=None, eps: float = 1e-6):
     """Fold a pending tensor-parallel partial into ``x``; returns ``rmsnorm(x)`` when
     ``norm_w`` is given, else ``x``."""
     part, ctx.pending = ctx.pending, None
-    if torch.is_tensor(part):          # a local (already complete) sub-layer output
+    if torch.is_tensor(part) or hasattr(part, "planes"):   # a local sub-layer output (possibly still as K-slice planes)
         h = ops.add_rmsnorm_(x, part, norm_w, eps)
     else:
         h = ctx.tp_symm.ar_residual_rmsnorm(part, x, norm_w, eps)
@@ -406,6 +415,8 @@ def _decoder_layer_infer_fused(arch: ModelArch, p, x, ctx: FwdCtx, layer: int):
     the RMSNorm that follows it (the MLP output stays pending for the next layer's norm),
     and the residual stream is updated in place."""
     eps = arch.rms_norm_eps
+    # every GEMM output of this layer that goes into the residual stream is consumed by the very next kernel
+    ctx.planes_ok = ctx.tp is None or ctx.tp.size == 1
     if ctx.pending is not None:
         h = flush_pending(x, ctx, p["input_layernorm"], eps)
     else:

@@ -85,6 +85,7 @@ rmsnorm = _dispatch("rmsnorm")
 add_rmsnorm_ = _dispatch("add_rmsnorm_")
 swiglu = _dispatch("swiglu")
 linear = _dispatch("linear")
+linear_planes = _dispatch("linear_planes")
 rope = _dispatch("rope")
 rope_mrope = _dispatch("rope_mrope")
 qk_norm_rope = _dispatch("qk_norm_rope")

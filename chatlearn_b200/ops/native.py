@@ -88,9 +88,42 @@ def rmsnorm(x, w, eps):
     return _RMSNorm.apply(x, w, eps)
 
 
+class SplitKPlanes:
+    """Result of a K-sliced GEMM whose fp32 partial planes have not been added up yet.  ``planes`` [S, M, N] is a
+    view of the per-device split-K workspace: it is valid until the next K-sliced GEMM on the device, so the
+    consumer (``add_rmsnorm_`` or ``qkv_rope_append``, which add the planes up while they do their own work) must be
+    the next kernel.  ``shape`` / ``out`` describe the bf16 result that was not written."""
+    __slots__ = ("out", "planes")
+
+    def __init__(self, out, planes):
+        self.out, self.planes = out, planes
+
+    @property
+    def shape(self):
+        return self.out.shape
+
+
+_FUSE_FINALIZE = os.environ.get("CLB200_FUSE_FINALIZE", "1") != "0"
+
+
+def linear_planes(x, w):
+    """``x @ w.T`` for a consumer that accepts ``SplitKPlanes`` (inference only, no autograd): when the GEMM slices
+    K, the separate kernel that adds the slices is skipped and the consumer reads the planes."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if _FUSE_FINALIZE and _GEMM_IMPL == "tcgen05" and not torch.is_grad_enabled() and x2.shape[0] > 0 and _gemm_ok(x2, w) \
+            and x.dim() == 2:
+        _count("gemm_bf16_nt")
+        out, planes = C.gemm_bf16_nt_planes(x2, w)
+        return SplitKPlanes(out, planes) if planes.numel() > 0 else out
+    return linear(x, w)
+
+
 @torch.no_grad()
 def add_rmsnorm_(resid, delta, w, eps):
     """Residual add + RMSNorm in one pass (inference): ``resid += delta`` in place, returns the norm."""
+    if isinstance(delta, SplitKPlanes):
+        _count("planes_residual_rmsnorm")
+        return C.planes_residual_rmsnorm(resid, delta.planes, w, float(eps))
     H = resid.shape[-1]
     if (resid.dtype != torch.bfloat16 or delta.dtype != torch.bfloat16 or resid.dim() != 2 or H % 8 or H > 8192
             or not resid.is_contiguous() or (w is not None and w.dtype != torch.bfloat16)):
@@ -177,6 +210,9 @@ def qk_norm_rope(q, k, qw, kw, eps, positions, theta):
 @torch.no_grad()
 def qkv_rope_append(qkv, nq, nkv, D, q_weight, k_weight, eps, positions, theta, slot_mapping, k_cache, v_cache):
     """One kernel for q/k norm + RoPE and the cache append (see ``reference.qkv_rope_append``)."""
+    planes = None
+    if isinstance(qkv, SplitKPlanes):
+        qkv, planes = qkv.out, qkv.planes
     ok = (qkv.dtype == torch.bfloat16 and qkv.dim() == 2 and qkv.stride(1) == 1 and D in (64, 128)
           and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16 and k_cache.is_contiguous()
           and v_cache.is_contiguous() and k_cache.shape[-1] == D and v_cache.shape[-1] == D
@@ -188,7 +224,8 @@ def qkv_rope_append(qkv, nq, nkv, D, q_weight, k_weight, eps, positions, theta, 
                                    v_cache)
     _count("qkv_rope_append")
     return C.qkv_rope_append(qkv, nq, nkv, D, q_weight, k_weight, positions.to(torch.int64),
-                             _inv_freq(D, theta, qkv.device), slot_mapping.to(torch.int64), k_cache, v_cache, float(eps))
+                             _inv_freq(D, theta, qkv.device), slot_mapping.to(torch.int64), k_cache, v_cache, float(eps),
+                             planes)
 
 
 def rope(x, positions, theta, rot_dim=None):
@@ -568,7 +605,8 @@ for _name, _fn in (("rmsnorm", rmsnorm), ("add_rmsnorm_", add_rmsnorm_), ("swigl
                    ("linear", linear), ("lmhead_logprob_entropy", lmhead_logprob_entropy),
                    ("grpo_loss_fused", grpo_loss_fused), ("gspo_loss_fused", gspo_loss_fused), ("adamw_step", adamw_step), ("sumsq", sumsq),
                    ("sample", sample), ("apply_penalties", apply_penalties), ("kv_append", kv_append),
-                   ("paged_attention", paged_attention), ("mla_paged_decode", mla_paged_decode)):
+                   ("paged_attention", paged_attention), ("mla_paged_decode", mla_paged_decode),
+                   ("linear_planes", linear_planes)):
     register_native(_name, _fn)
 
 from . import native_moe  # noqa: E402,F401  (registers the mixture-of-experts ops)

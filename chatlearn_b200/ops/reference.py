@@ -202,6 +202,12 @@ def kv_append(k, v, k_cache, v_cache, slot_mapping):
     v_cache.view(nb * bs, *v_cache.shape[2:])[slots] = v[ok].to(v_cache.dtype)
 
 
+def linear_planes(x, w):
+    """``linear`` for consumers that also accept the un-added K-slice planes of a GEMM (a kernel-side notion: here
+    simply the product)."""
+    return linear(x, w)
+
+
 def mla_paged_decode(q, k_cache, lora, block_tables, seq_lens, scale):
     """Decode step of multi-head latent attention in the absorbed form: ``q`` [B, heads, lora + rope] (one query
     token per sequence) against the paged latent cache ``k_cache`` [blocks, block, 1, lora + rope]; the values are
