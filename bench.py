@@ -45,6 +45,9 @@ def parse():
                    help="run the model with this many decoder layers instead of its own depth (exercises a large "
                         "architecture on few GPUs; the JSON line then names the reduced depth and is not a figure "
                         "for the full model)")
+    p.add_argument("--ulysses", type=int, default=1,
+                   help="Ulysses sequence-parallel size of the trainer and the reference model (heads <-> sequence "
+                        "all-to-all around attention, through the peer-memory exchange kernels)")
     p.add_argument("--no-offload", action="store_true")
     p.add_argument("--rollout-tp", type=int, default=1,
                    help="tensor-parallel size of a rollout replica (1: every GPU generates for its own samples; 2: pairs "
@@ -167,6 +170,7 @@ def build_config(args, out_dir, data_path, n_gpu):
                                    # "auto" assumes (they ran out of memory with it): every layer recomputes
                                    checkpoint_layers="all" if args.impl == "library" else "auto",
                                    optimizer={"lr": 2e-6}, save_hf=False, reshard_after_forward=bool(args.reshard),
+                                   ulysses_sequence_parallel_size=int(args.ulysses),
                                    # fp32 master + Adam shards stay on the GPU (180 GB HBM); the fp32
                                    # gradient buffer is released outside training
                                    # On one GPU (all optimizer state on it) the bf16 compute copy is dropped
@@ -178,6 +182,7 @@ def build_config(args, out_dir, data_path, n_gpu):
             # the frozen reference weights (16 GB) go to pinned host memory between uses only where the
             # GPU is short of room (1-2 GPUs hold large optimizer shards); from 4 GPUs on they stay resident
             "ref_policy": dict(common, num_gpu=n_gpu, fsdp_size=n_gpu, generation_batch_size=spe,
+                               ulysses_sequence_parallel_size=int(args.ulysses),
                                free_gpu_memory={"offload_weights": offload and n_gpu < 4}),
             "policy": dict(common, num_gpu=n_gpu, tensor_model_parallel_size=tp, generation_batch_size=spe,
                            num_inference_per_prompt=n, temperature=1.0, top_p=1.0, top_k=-1,
@@ -332,7 +337,7 @@ def main():
             "config": {"model": args.model if args.layers <= 0 else f"{args.model} cut to {args.layers} layers",
                        "global_batch": samples, "seq_len": seq,
                        "trainer_parameters": "sharded 1/N per GPU (gathered per segment)" if args.reshard else "whole per GPU (optimizer state sharded)",
-                       "parallelism": f"trainer zero-dp{world} + rollout tp{max(1, min(args.rollout_tp, world))}x{world // max(1, min(args.rollout_tp, world))}",
+                       "parallelism": (f"ulysses{args.ulysses} x " if args.ulysses > 1 else "") + f"trainer zero-dp{world} + rollout tp{max(1, min(args.rollout_tp, world))}x{world // max(1, min(args.rollout_tp, world))}",
                        "prompts": samples // args.samples_per_prompt, "samples_per_prompt": args.samples_per_prompt,
                        "prompt_len": args.prompt_len, "max_response": args.max_response,
                        "pack_tokens": args.pack_tokens, "mini_batches_per_step": 2,
