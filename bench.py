@@ -144,6 +144,18 @@ def vs_baseline(n_gpu, value, args):
         return None
 
 
+def rollout_trainer_diff(out_dir, last_k):
+    """Mean |log-prob the rollout engine sampled with - log-prob the trainer assigns to the same token| over the
+    timed episodes (from the run's metrics file): a check that generation and scoring see the same model."""
+    try:
+        vals = [v for line in open(os.path.join(out_dir, "metrics.jsonl")) for k, v in json.loads(line).items()
+                if k.endswith("rollout_logprob_abs_diff")]
+        vals = vals[-last_k:]
+        return round(sum(vals) / len(vals), 6) if vals else None
+    except (OSError, ValueError):
+        return None
+
+
 def build_config(args, out_dir, data_path, n_gpu):
     tp = max(1, min(int(args.rollout_tp), n_gpu))
     n = args.samples_per_prompt
@@ -354,6 +366,7 @@ def main():
             "e2e": {"value": round(samples / (wall_ms / 1e3 / K), 4), "unit": "samples/s",
                     "h2d_bytes_per_step": int(h2d / K), "d2h_bytes_per_step": int(d2h / K),
                     "how": "host wall clock around the same K episodes driven through Engine.run_episode"},
+            "rollout_vs_trainer_logprob_abs_diff": rollout_trainer_diff(out_dir, K),
             "gpu_launches": int(launches),
             "library_calls": {k: int(v) for k, v in ops.library_counts.items()},
         }

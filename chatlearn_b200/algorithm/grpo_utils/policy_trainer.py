@@ -125,6 +125,7 @@ class PolicyTrainer(FSDPModule):
         if not data_list:
             return data_list
         pad = self.sp.size if self.sp is not None else 1
+        diff_sum, diff_max, diff_n = 0.0, 0.0, 0
         for mb in self._microbatches(data_list, for_train=False):
             if not mb:
                 continue
@@ -132,6 +133,17 @@ class PolicyTrainer(FSDPModule):
             lp, _, _ = self._logprobs(batch, need_entropy=False)
             for s, v in zip(mb, unpack_per_sample(lp, batch, mb)):
                 s[tag] = v
+                r = s.get("rollout_logprobs")
+                if self.trainable and r is not None and len(r):
+                    # how far the engine that generated the tokens and the trainer disagree about their
+                    # log-probabilities (same weights: the difference is numerics; a large value means the
+                    # rollout ran on other weights or sampled from another distribution than the trainer scores)
+                    P, R = int(s["prompt_token_length"]), int(s["response_token_length"])
+                    n = min(R, len(r))
+                    d = (v[P - 1:P - 1 + n] - torch.as_tensor(r[:n], dtype=torch.float32)).abs()
+                    diff_sum += float(d.sum()); diff_max = max(diff_max, float(d.max())); diff_n += n
+        if diff_n:
+            self._metric_list.append({"rollout_logprob_abs_diff": diff_sum / diff_n, "rollout_logprob_abs_diff_max": diff_max})
         return data_list
 
     # ------------------------------------------------------------------ training

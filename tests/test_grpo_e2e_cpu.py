@@ -86,6 +86,10 @@ def test_grpo_tiny_gloo_ws2(tmp_path):
     assert (d / "model_world_size_2_rank_0.pt").exists() and (d / "optim_world_size_2_rank_1.pt").exists()
     assert (d / "huggingface" / "model.safetensors").exists()
     assert (tmp_path / "metrics.jsonl").exists()
+    # the engine that generated the tokens and the trainer agree on their log-probabilities (fp32 on CPU)
+    diffs = [v for line in open(tmp_path / "metrics.jsonl") for k, v in json.loads(line).items()
+             if k.endswith("rollout_logprob_abs_diff_max")]
+    assert diffs and max(diffs) < 1e-4, diffs
 
 
 def test_grpo_tiny_packing_tp2(tmp_path):
