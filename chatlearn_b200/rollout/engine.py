@@ -293,7 +293,16 @@ class RolloutEngine:
     @torch.no_grad()
     def _logits(self, hidden_last):
         w = self.model.lm_head_weight()
-        logits = ops.linear(hidden_last, w).float()
+        logits = None
+        if hidden_last.is_cuda and ops.get_mode() == "native" and hidden_last.dtype == torch.bfloat16:
+            # fp32 logits straight from the GEMM's accumulators: the trainer scores the same tokens from fp32 logits,
+            # and a bf16 round trip here showed up as a rollout / trainer log-prob difference
+            from chatlearn_b200.ops import native
+            h2 = hidden_last.contiguous()
+            if h2.shape[0] > 0 and native.get_gemm_impl() == "tcgen05" and native._gemm_ok(h2, w):
+                logits = native.gemm_nt(h2, w, out_fp32=True)
+        if logits is None:
+            logits = ops.linear(hidden_last, w).float()
         if self.tp is not None and self.tp.size > 1 and w.shape[0] != self.arch.vocab_size:
             logits = self.tp.all_gather_cat(logits, dim=1)
         return logits
