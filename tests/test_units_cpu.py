@@ -622,3 +622,30 @@ def test_interleaved_pipeline_time_table():
         if m % P == 0 and m >= 2 * P:
             # plain 1F1B: (m + P - 1) slots of V chunk-units each, forward and backward
             assert len(ticks[0]) < 2 * V * (m + P - 1)
+
+
+def test_scheduler_counts_tokens_in_flight():
+    """A token sampled on the device but not read back yet (pipelined decode) counts for block allocation and for
+    the 'prompt KV still missing' test: the decode step after it may need a fresh block."""
+    from chatlearn_b200.rollout.scheduler import Scheduler, Sequence
+    sched = Scheduler(num_blocks=8, block_size=4, max_num_seqs=4, max_num_batched_tokens=64, prefix_sharing=False)
+    s = Sequence(0, [1, 2, 3], 16)                      # 3 prompt tokens: one block
+    sched.add(s)
+    plan = sched.schedule()                             # prefill
+    assert plan.is_prefill and plan.q_lens == [3] and len(s.blocks) == 1
+    s.num_computed = 3
+    s.output.append(7)                                  # first sampled token, known to the host: length 4
+    plan = sched.schedule()                             # decode: feeds token 7 at position 3 -> still block 0
+    assert plan.q_lens == [1] and len(s.blocks) == 1
+    s.num_computed = 4
+    s.inflight = 1                                      # its sample is on the device; the host still sees length 4
+    plan = sched.schedule()                             # the next step writes position 4: a second block is needed
+    assert plan.q_lens == [1] and not plan.is_prefill and len(s.blocks) == 2
+    s.num_computed = 5
+    s.output.append(9)                                  # the read-back of the first in-flight token arrives
+    plan = sched.schedule()                             # length 5 + 1 in flight = 6 tokens: still two blocks
+    assert plan.q_lens == [1] and len(s.blocks) == 2
+    s.inflight = 0
+    s.output.append(11)
+    sched.finish(s, "length")
+    assert sched.alloc.num_free == 8 and not sched.has_work()
