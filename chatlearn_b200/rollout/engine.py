@@ -99,7 +99,11 @@ class RolloutEngine:
         # ranks that exchange tokens inside a forward (expert parallel) must run the
         # same number of forwards: they agree on "anyone still busy" every step
         self.lockstep = lockstep_group
-        self.use_graphs = use_cuda_graphs
+        # "emulate": the captured decode step's host side (persistent input buffers, cached block tables, input
+        # tokens fed from the previous step's samples, read-back one step late) with the step's body run directly
+        # instead of through a CUDA graph: the same logic on CPU ranks, where the tests exercise it
+        self._emulate_graphs = use_cuda_graphs == "emulate"
+        self.use_graphs = bool(use_cuda_graphs)
         self._graphs: Dict[Any, Any] = {}
         self._gs = None
         # pipelined decode: the step launched last whose sampled tokens the host has not read yet
@@ -317,30 +321,31 @@ class RolloutEngine:
             n = min(b for b in self._BUCKETS if b >= n) if n <= self._BUCKETS[-1] else n
             width = math.ceil(self.max_model_len / self.block_size)
             z = lambda dt, *shape: torch.zeros(*shape, dtype=dt, device=dev)  # noqa: E731
+            pin = dev.type == "cuda"
             # rows: token (when the host knows it), position, KV slot, sequence length, and for a token that is
             # still on the device its row in the previous step's batch plus a flag
             in64 = z(torch.long, 6, n)
             self._gs = dict(n=n, width=width, in64=in64, tokens=z(torch.long, n), pos=in64[1],
                             slots=in64[2], seq_lens=z(torch.int32, n), bt=z(torch.int32, n, width),
                             u=z(torch.float32, n), ids=z(torch.long, n), lp=z(torch.float32, n),
-                            stage=torch.zeros(6, n, dtype=torch.int64, pin_memory=True),
+                            stage=torch.zeros(6, n, dtype=torch.int64, pin_memory=pin),
                             out_dev=[z(torch.float32, 2, n) for _ in range(2)],
-                            out_host=[torch.zeros(2, n, dtype=torch.float32, pin_memory=True) for _ in range(2)],
+                            out_host=[torch.zeros(2, n, dtype=torch.float32, pin_memory=pin) for _ in range(2)],
                             out_event=[torch.cuda.Event() for _ in range(2)] if dev.type == "cuda" else [None, None],
                             parity=0,
-                            bt_host=torch.zeros(n, width, dtype=torch.int32, pin_memory=True),
+                            bt_host=torch.zeros(n, width, dtype=torch.int32, pin_memory=pin),
                             bt_len=[0] * n, bt_owner=[None] * n,
                             # sequences that share their first KV blocks (the samples of one prompt): up to n / 2
                             # groups of up to 8 rows each, the shared block count per group, and per row the first
                             # block that is its own
                             grp_q=torch.full((max(n // 2, 1), 8), -1, dtype=torch.int32, device=dev),
                             grp_nblk=z(torch.int32, max(n // 2, 1)), blk_start=z(torch.int32, n),
-                            grp_stage=torch.zeros(max(n // 2, 1) * 9 + n, dtype=torch.int32, pin_memory=True),
+                            grp_stage=torch.zeros(max(n // 2, 1) * 9 + n, dtype=torch.int32, pin_memory=pin),
                             grp_key=None)
             if self.arch.layer_types is not None:
                 # recurrent-state layers: the state slot of every row (decode rows never start fresh)
                 self._gs.update(lin_slots=z(torch.long, n), lin_fresh=z(torch.bool, n),
-                                lin_stage=torch.zeros(n, dtype=torch.int64, pin_memory=True))
+                                lin_stage=torch.zeros(n, dtype=torch.int64, pin_memory=pin))
         return self._gs
 
     def invalidate_graphs(self):
@@ -422,6 +427,9 @@ class RolloutEngine:
         sp = seqs[0].sampling
         key = (Bg, sp.key(), grouped)
         gs["use_groups"] = grouped
+        if self._emulate_graphs:
+            self._decode_body(Bg, sp)
+            return gs["ids"][:B], gs["lp"][:B]
         g = self._graphs.get(key)
         if g is None:
             # warm-up on a side stream, then capture
@@ -493,10 +501,13 @@ class RolloutEngine:
         return g > 0
 
     def _can_graph(self, plan: StepPlan) -> bool:
-        if not self.use_graphs or self.device.type != "cuda" or plan.is_prefill:
+        if not self.use_graphs or plan.is_prefill:
             return False
-        if ops.get_mode() != "native" or self.model.dtype != torch.bfloat16:
-            return False        # the PyTorch statements of the ops (also taken for fp32 weights) synchronise with the host
+        if not self._emulate_graphs:
+            if self.device.type != "cuda":
+                return False
+            if ops.get_mode() != "native" or self.model.dtype != torch.bfloat16:
+                return False    # the PyTorch statements of the ops (also taken for fp32 weights) synchronise with the host
         if any(n != 1 for n in plan.q_lens) or len(plan.seqs) > self._BUCKETS[-1]:
             return False
         if self.lockstep is not None and self.lockstep.size > 1:
@@ -528,14 +539,16 @@ class RolloutEngine:
         dev_buf[0, :B].copy_(ids)                      # token ids are exact in fp32: vocab < 2^24
         dev_buf[1, :B].copy_(lps)
         host_buf[:, :B].copy_(dev_buf[:, :B], non_blocking=True)
-        gs["out_event"][par].record()
+        if gs["out_event"][par] is not None:
+            gs["out_event"][par].record()
         xfer.d2h_bytes += 2 * B * 4
         return {"seqs": list(seqs), "par": par}
 
     def _complete(self, pend, sched: Scheduler, eos_id):
         """Wait for a launched step's tokens, append them and apply the stop conditions."""
         gs = self._gs
-        gs["out_event"][pend["par"]].synchronize()
+        if gs["out_event"][pend["par"]] is not None:
+            gs["out_event"][pend["par"]].synchronize()
         B = len(pend["seqs"])
         both = gs["out_host"][pend["par"]][:, :B].tolist()
         for s in pend["seqs"]:

@@ -649,3 +649,44 @@ def test_scheduler_counts_tokens_in_flight():
     s.output.append(11)
     sched.finish(s, "length")
     assert sched.alloc.num_free == 8 and not sched.has_work()
+
+
+def test_pipelined_decode_host_logic_on_cpu(monkeypatch):
+    """The host side of the captured, pipelined decode step (persistent input buffers, cached block tables, input
+    tokens taken from the previous step's samples, tokens read back one step late) with the step's body run
+    directly: stop tokens seen one step late, length limits known in advance, a request that joins late and a KV
+    pool that forces preemptions must give exactly the generations of the plain step-by-step engine."""
+    from chatlearn_b200.rollout import RolloutEngine, SamplingParams
+    arch = PRESETS["tiny_qwen3"]()
+    model = CausalLM(arch, dtype=torch.float32).init_weights(2)
+    g = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(0, arch.vocab_size - 1, (n,), generator=g).tolist() for n in (30, 11, 41, 8, 17, 5)]
+    budgets = [24, 3, 17, 1, 20, 24]
+    free = RolloutEngine(model, block_size=8, num_blocks=64, max_num_seqs=8, max_model_len=96, use_cuda_graphs=False) \
+        .generate(prompts, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True), max_new_tokens=budgets)
+    stops = (free[0].output[9], free[5].output[15])
+    sp = SamplingParams(temperature=0.0, max_tokens=24, stop_token_ids=stops)
+    res, pre = {}, {}
+    for name, graphs, pipe in (("pipelined", "emulate", "1"), ("buffers", "emulate", "0"), ("plain", False, "0")):
+        monkeypatch.setenv("CLB200_PIPELINED_DECODE", pipe)
+        # the six sequences would need 28 blocks at their longest; 13 force preemptions
+        eng = RolloutEngine(model, block_size=8, num_blocks=13, max_num_seqs=8, max_model_len=96, use_cuda_graphs=graphs)
+        assert eng.pipelined == (pipe == "1")
+        sess = eng.open_session(eos_id=-1)
+        seqs = [sess.submit(p, sp, b) for p, b in zip(prompts[:5], budgets[:5])]
+        steps, order = 0, []
+        while True:
+            done = sess.poll()
+            if done is None:
+                break
+            steps += 1
+            order += [s.req_id - seqs[0].req_id for s in done]
+            if steps == 5:
+                seqs.append(sess.submit(prompts[5], sp, budgets[5]))
+        sess.close()
+        assert sorted(order) == list(range(6)) and all(s.finished and not s.inflight for s in seqs), name
+        res[name] = [(s.output, s.finish_reason) for s in seqs]
+        pre[name] = eng.stats["preemptions"]
+    assert res["pipelined"] == res["plain"] and res["buffers"] == res["plain"]
+    assert pre["plain"] > 0 and pre["pipelined"] > 0
+    assert res["plain"][0][1] == "stop" and res["plain"][1] == (free[1].output[:3], "length") and len(res["plain"][3][0]) == 1
