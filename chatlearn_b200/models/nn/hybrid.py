@@ -106,9 +106,13 @@ def gated_delta_net(arch: ModelArch, p, x, ctx, layer: int):
     T = x.shape[0]
     if T == 0:
         return x
-    nk, nv = arch.linear_num_key_heads, arch.linear_num_value_heads
+    from .model import _tp_copy
+    x = _tp_copy(x, ctx)                       # (sequence-parallel rows are gathered here)
+    T = x.shape[0]
     dk, dv, K = arch.linear_key_head_dim, arch.linear_value_head_dim, arch.linear_conv_kernel_dim
-    r = nv // nk
+    r = arch.linear_num_value_heads // arch.linear_num_key_heads
+    nv = p["A_log"].shape[0]                   # this rank's heads (1/tp of the layer's)
+    nk = nv // r
     kd, vd = nk * dk, nv * dv
     C = 2 * kd + vd
     st: Optional[LinearState] = ctx.kv.lin if ctx.kv is not None else None
@@ -145,7 +149,7 @@ def gated_delta_net(arch: ModelArch, p, x, ctx, layer: int):
                                      y1[:, 2 * kd:].reshape(B, nv, dv).contiguous(), g.contiguous(), bgate.contiguous(),
                                      st.rec[layer], st.slots, st.fresh, 1.0 / math.sqrt(dk))
         native.launch_counts["gdn_decode_step"] += 1
-        return _gdn_output(arch, p, o, z, x.dtype, T, vd)
+        return _gdn_output(arch, p, o, z, x.dtype, T, vd, ctx)
     q = _l2norm(y[..., :kd].reshape(B, L, nk, dk).float()) * (1.0 / math.sqrt(dk))
     k = _l2norm(y[..., kd:2 * kd].reshape(B, L, nk, dk).float())
     v = y[..., 2 * kd:].reshape(B, L, nv, dv).float()
@@ -165,21 +169,26 @@ def gated_delta_net(arch: ModelArch, p, x, ctx, layer: int):
         o, S = gated_delta_chunked(q, k, v, gp, bp, init)
     if st is not None:
         st.rec[layer].index_copy_(0, st.slots, S.to(st.rec[layer].dtype))
-    return _gdn_output(arch, p, o[seq, off], z, x.dtype, T, vd)           # back to the packed row: [T, nv, dv]
+    return _gdn_output(arch, p, o[seq, off], z, x.dtype, T, vd, ctx)      # back to the packed row: [T, nv, dv]
 
 
-def _gdn_output(arch, p, o, z, dtype, T, vd):
-    """Per-head RMSNorm of the read-out, gated by silu(z), then the output projection."""
+def _gdn_output(arch, p, o, z, dtype, T, vd, ctx):
+    """Per-head RMSNorm of the read-out, gated by silu(z), then the (row-parallel) output projection."""
+    from .model import _row_parallel
     o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + arch.rms_norm_eps)
     o = (p["gdn_norm"] * o.to(dtype)).float() * F.silu(z.float())
-    return ops.linear(o.to(dtype).reshape(T, vd), p["out_proj"])
+    return _row_parallel(o.to(dtype).reshape(T, vd), p["out_proj"], ctx)
 
 
 def gated_attention(arch: ModelArch, p, x, ctx, layer: int):
-    T = x.shape[0]
-    d, nh, nkv = arch.head_dim, arch.num_attention_heads, arch.num_key_value_heads
+    from .model import _row_parallel, _tp_copy
     assert (ctx.sp is None or ctx.sp.size == 1) and (ctx.cp is None or ctx.cp.size == 1), \
-        "Qwen3-Next layers run without sequence / context parallelism"
+        "Qwen3-Next layers run without Ulysses / context parallelism"
+    x = _tp_copy(x, ctx)
+    T = x.shape[0]
+    d = arch.head_dim
+    nh = p["o_proj"].shape[1] // d             # this rank's query heads and key/value heads
+    nkv = (p["qkv"].shape[0] // d - 2 * nh) // 2
     qkv = ops.linear(x, p["qkv"])
     qg = qkv[:, :2 * nh * d].view(T, nh, 2 * d)
     q, gate = qg[..., :d], qg[..., d:].reshape(T, nh * d)
@@ -204,7 +213,7 @@ def gated_attention(arch: ModelArch, p, x, ctx, layer: int):
     else:
         o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, scale)
     o = o.reshape(T, nh * d) * torch.sigmoid(gate)
-    return ops.linear(o, p["o_proj"])
+    return _row_parallel(o, p["o_proj"], ctx)
 
 
 def hybrid_decoder_layer(arch: ModelArch, p, x, ctx, layer: int):
@@ -216,4 +225,4 @@ def hybrid_decoder_layer(arch: ModelArch, p, x, ctx, layer: int):
     mix = gated_delta_net(arch, p, h, ctx, layer) if "in_proj" in p else gated_attention(arch, p, h, ctx, layer)
     x = x + mix
     h = ops.rmsnorm(x, zc(p["post_attention_layernorm"]), eps)
-    return x + (moe_block(arch, p, h, ctx) if "router" in p else dense_mlp(p, h, ctx))
+    return x + (moe_block(arch, p, h, ctx) if "router" in p else dense_mlp(p, h, ctx, reduce=True))

@@ -37,6 +37,9 @@ class Leaf:
     segments: List[Segment] = field(default_factory=list)
     replicated: bool = False           # same content on every model-parallel rank
     grad_sum_tp: bool = False          # gradient is a partial sum per TP rank (needs an all-reduce)
+    # key/value heads replicated over tensor-parallel ranks (tp > kv heads): (first row, rows, this rank's kv head,
+    # kv heads); the gradients of those rows are summed over the ranks that hold the same head
+    grad_sum_kv: Optional[Tuple[int, int, int, int]] = None
 
     @property
     def numel(self) -> int:
@@ -78,37 +81,64 @@ def kv_head_range(arch: ModelArch, tp: int, tp_rank: int) -> Tuple[int, int]:
     return tp_rank // (tp // nkv), 1
 
 
-def _hybrid_mixer_leaves(arch: ModelArch, l: int, pre: str, hp: str) -> List[Leaf]:
+def _hybrid_mixer_leaves(arch: ModelArch, l: int, pre: str, hp: str, tp: int = 1, tp_rank: int = 0) -> List[Leaf]:
     """Token mixer of a Qwen3-Next layer (HF names: transformers
     models/qwen3_next/modeling_qwen3_next.py, ``Qwen3NextGatedDeltaNet`` / ``Qwen3NextAttention``; the
     reference maps the same tensors for Megatron in
-    chatlearn/synchronizer/mappers/megatron_llm_mapper.py:262-343)."""
+    chatlearn/synchronizer/mappers/megatron_llm_mapper.py:262-343).  Under tensor parallelism a rank owns
+    ``1/tp`` of the key heads of a delta-net layer with their value heads (input projections, convolution
+    channels, decay parameters by rows; output projection by columns) and ``1/tp`` of the query heads of a gated
+    attention layer with their output gates."""
     H = arch.hidden_size
     if arch.layer_is_linear(l):
         a = hp + "linear_attn."
         nk, nv = arch.linear_num_key_heads, arch.linear_num_value_heads
-        kd, vd = nk * arch.linear_key_head_dim, nv * arch.linear_value_head_dim
-        pq = 2 * kd + 2 * vd
+        dk, dv = arch.linear_key_head_dim, arch.linear_value_head_dim
+        assert nk % tp == 0, f"{nk} key heads of the delta-net layers not divisible by tp={tp}"
+        nk_l, nv_l = nk // tp, nv // tp
+        kd, vd = nk * dk, nv * dv
+        kd_l, vd_l = nk_l * dk, nv_l * dv
+        pq, pq_l = 2 * kd + 2 * vd, 2 * kd_l + 2 * vd_l
+        C, K = 2 * kd + vd, arch.linear_conv_kernel_dim
         # one GEMM for both input projections: rows [q k v z per key-head group | b a per group]
-        in_proj = Leaf(pre + "in_proj", (pq + 2 * nv, H), "normal",
-                       [_rows(a + "in_proj_qkvz.weight", (pq, H), 0, pq, 0),
-                        _rows(a + "in_proj_ba.weight", (2 * nv, H), 0, 2 * nv, pq)])
-        return [in_proj,
-                _full(pre + "conv1d", (2 * kd + vd, arch.linear_conv_kernel_dim), a + "conv1d.weight", "conv"),
-                _full(pre + "dt_bias", (nv,), a + "dt_bias", "ones"),
-                _full(pre + "A_log", (nv,), a + "A_log", "a_log"),
-                _full(pre + "gdn_norm", (arch.linear_value_head_dim,), a + "norm.weight", "ones"),
-                _full(pre + "out_proj", (H, vd), a + "out_proj.weight")]
+        in_proj = Leaf(pre + "in_proj", (pq_l + 2 * nv_l, H), "normal",
+                       [_rows(a + "in_proj_qkvz.weight", (pq, H), tp_rank * pq_l, pq_l, 0),
+                        _rows(a + "in_proj_ba.weight", (2 * nv, H), tp_rank * 2 * nv_l, 2 * nv_l, pq_l)])
+        if tp == 1:
+            conv = _full(pre + "conv1d", (C, K), a + "conv1d.weight", "conv")
+            dt_bias = _full(pre + "dt_bias", (nv,), a + "dt_bias", "ones")
+            a_log = _full(pre + "A_log", (nv,), a + "A_log", "a_log")
+            out_proj = _full(pre + "out_proj", (H, vd), a + "out_proj.weight")
+        else:
+            # channels of the convolution: [q | k | v], each split by heads
+            conv = Leaf(pre + "conv1d", (2 * kd_l + vd_l, K), "conv",
+                        [_rows(a + "conv1d.weight", (C, K), tp_rank * kd_l, kd_l, 0),
+                         _rows(a + "conv1d.weight", (C, K), kd + tp_rank * kd_l, kd_l, kd_l),
+                         _rows(a + "conv1d.weight", (C, K), 2 * kd + tp_rank * vd_l, vd_l, 2 * kd_l)])
+            dt_bias = Leaf(pre + "dt_bias", (nv_l,), "ones", [_rows(a + "dt_bias", (nv, 1), tp_rank * nv_l, nv_l, 0)])
+            a_log = Leaf(pre + "A_log", (nv_l,), "a_log", [_rows(a + "A_log", (nv, 1), tp_rank * nv_l, nv_l, 0)])
+            out_proj = Leaf(pre + "out_proj", (H, vd_l), "normal",
+                            [_cols(a + "out_proj.weight", (H, vd), tp_rank * vd_l, vd_l)])
+        norm = _full(pre + "gdn_norm", (dv,), a + "norm.weight", "ones")
+        norm.grad_sum_tp = tp > 1                 # shared by all heads: every rank holds a partial gradient
+        return [in_proj, conv, dt_bias, a_log, norm, out_proj]
     a = hp + "self_attn."
     nh, nkv, d = arch.num_attention_heads, arch.num_key_value_heads, arch.head_dim
+    nh_l = nh // tp
+    kv0, nkv_l = kv_head_range(arch, tp, tp_rank)
     qf, kf = (nh * 2 * d, H), (nkv * d, H)       # q_proj rows per head: [query | gate]
-    qkv = Leaf(pre + "qkv", ((2 * nh + 2 * nkv) * d, H), "normal",
-               [_rows(a + "q_proj.weight", qf, 0, qf[0], 0),
-                _rows(a + "k_proj.weight", kf, 0, kf[0], qf[0]),
-                _rows(a + "v_proj.weight", kf, 0, kf[0], qf[0] + kf[0])])
-    return [qkv, _full(pre + "q_norm", (d,), a + "q_norm.weight", "zeros"),
-            _full(pre + "k_norm", (d,), a + "k_norm.weight", "zeros"),
-            _full(pre + "o_proj", (H, nh * d), a + "o_proj.weight")]
+    qkv = Leaf(pre + "qkv", ((2 * nh_l + 2 * nkv_l) * d, H), "normal",
+               [_rows(a + "q_proj.weight", qf, tp_rank * nh_l * 2 * d, nh_l * 2 * d, 0),
+                _rows(a + "k_proj.weight", kf, kv0 * d, nkv_l * d, nh_l * 2 * d),
+                _rows(a + "v_proj.weight", kf, kv0 * d, nkv_l * d, (2 * nh_l + nkv_l) * d)])
+    if tp > nkv:
+        qkv.grad_sum_kv = (2 * nh_l * d, 2 * nkv_l * d, kv0, nkv)
+    qn = _full(pre + "q_norm", (d,), a + "q_norm.weight", "zeros")
+    kn = _full(pre + "k_norm", (d,), a + "k_norm.weight", "zeros")
+    qn.grad_sum_tp = kn.grad_sum_tp = tp > 1
+    o_proj = Leaf(pre + "o_proj", (H, nh_l * d), "normal",
+                  [_cols(a + "o_proj.weight", (H, nh * d), tp_rank * nh_l * d, nh_l * d)])
+    return [qkv, qn, kn, o_proj]
 
 
 def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int = 1,
@@ -122,8 +152,7 @@ def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int
     assert nh % tp == 0, f"{nh} heads not divisible by tp={tp}"
     nh_l = nh // tp
     if arch.layer_types is not None:
-        assert tp == 1, "the gated delta-net / gated-attention layers are not tensor-parallel"
-        out.extend(_hybrid_mixer_leaves(arch, l, pre, hp))
+        out.extend(_hybrid_mixer_leaves(arch, l, pre, hp, tp, tp_rank))
     elif arch.use_mla:
         qd = arch.qk_nope_head_dim + arch.qk_rope_head_dim
         a = hp + "self_attn."
@@ -158,11 +187,14 @@ def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int
                 _rows(a + "v_proj.weight", kf, kv0 * d, nkv_l * d, (nh_l + nkv_l) * d)]
         rows = (nh_l + 2 * nkv_l) * d
         out.append(Leaf(pre + "qkv", (rows, H), "normal", segs))
+        kv_rep = (nh_l * d, 2 * nkv_l * d, kv0, arch.num_key_value_heads) if tp > arch.num_key_value_heads else None
+        out[-1].grad_sum_kv = kv_rep
         if arch.attention_bias:
             bs = [Segment(a + "q_proj.bias", (nh * d, 1), (tp_rank * nh_l * d, 0), (nh_l * d, 1), (0, 0)),
                   Segment(a + "k_proj.bias", (kf[0], 1), (kv0 * d, 0), (nkv_l * d, 1), (nh_l * d, 0)),
                   Segment(a + "v_proj.bias", (kf[0], 1), (kv0 * d, 0), (nkv_l * d, 1), ((nh_l + nkv_l) * d, 0))]
             out.append(Leaf(pre + "qkv_bias", (rows,), "zeros", bs))
+            out[-1].grad_sum_kv = kv_rep
         if arch.qk_norm:
             out.append(_full(pre + "q_norm", (d,), a + "q_norm.weight", "ones"))
             out.append(_full(pre + "k_norm", (d,), a + "k_norm.weight", "ones"))

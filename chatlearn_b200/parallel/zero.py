@@ -137,6 +137,17 @@ class ShardedTrainState:
                     if getattr(lf, "grad_sum_tp", False):
                         o = s.block.offsets[lf.name]
                         self.tp_group.all_reduce_(s.grad[o:o + lf.numel])
+                    kv = getattr(lf, "grad_sum_kv", None)
+                    if kv is not None:
+                        # key/value heads held by several ranks: every rank puts its rows into the slot of its head,
+                        # the sum over the group completes each head's gradient
+                        r0, n, head, heads = kv
+                        o = s.block.offsets[lf.name]
+                        rows = s.grad[o:o + lf.numel].view(lf.matrix_shape)[r0:r0 + n]
+                        buf = rows.new_zeros((heads,) + tuple(rows.shape))
+                        buf[head].copy_(rows)
+                        self.tp_group.all_reduce_(buf)
+                        rows.copy_(buf[head])
             g = s.group
             fused = g.fast.get("reduce_scatter_f32")
             if self.symm is not None and getattr(s, "symm", False):
@@ -169,9 +180,6 @@ class ShardedTrainState:
             out = []
             for lf in s.block.leaves:
                 o = s.block.offsets[lf.name]
-                a, b = max(o, s.lo), min(o + lf.numel, s.hi)
-                if b <= a:
-                    continue
                 if s.block.name.endswith(".experts"):
                     # with an expert-data-parallel group of their own they are summed over the expert-parallel
                     # group instead (below); otherwise the tensor-parallel ranks hold copies of the same experts
@@ -181,10 +189,21 @@ class ShardedTrainState:
                 else:
                     rep = lf.replicated
                 w = 1.0 / self.tp_size if rep else 1.0
-                if out and out[-1][2] == w and out[-1][1] == a - s.lo:
-                    out[-1] = (out[-1][0], b - s.lo, w)
-                else:
-                    out.append((a - s.lo, b - s.lo, w))
+                pieces = [(o, o + lf.numel, w)]
+                kv = getattr(lf, "grad_sum_kv", None)
+                if kv is not None:
+                    # rows of key/value heads that tp / heads ranks hold: counted once per head
+                    cols = lf.matrix_shape[1]
+                    k0, k1 = o + kv[0] * cols, o + (kv[0] + kv[1]) * cols
+                    pieces = [(o, k0, w), (k0, k1, kv[3] / self.tp_size), (k1, o + lf.numel, w)]
+                for p0, p1, pw in pieces:
+                    a, b = max(p0, s.lo), min(p1, s.hi)
+                    if b <= a:
+                        continue
+                    if out and out[-1][2] == pw and out[-1][1] == a - s.lo:
+                        out[-1] = (out[-1][0], b - s.lo, pw)
+                    else:
+                        out.append((a - s.lo, b - s.lo, pw))
         s._norm_ranges = out
         return out
 

@@ -172,13 +172,15 @@ class RolloutEngine:
         for l in range(a.num_hidden_layers):
             if a.layer_is_linear(l):
                 # gated delta-net layers keep a fixed-size state per sequence instead of keys and values
-                kd, vd = a.linear_num_key_heads * a.linear_key_head_dim, a.linear_num_value_heads * a.linear_value_head_dim
+                # (of this tensor-parallel rank's heads)
+                nk_l, nv_l = a.linear_num_key_heads // tp, a.linear_num_value_heads // tp
+                kd, vd = nk_l * a.linear_key_head_dim, nv_l * a.linear_value_head_dim
                 self.k_cache.append(torch.empty(0, device=self.device))
                 self.v_cache.append(torch.empty(0, device=self.device))
                 # slots 0..max_num_seqs are handed out; the last one is scratch for the padded rows of a captured step
                 self.lin_conv.append(torch.zeros(self.max_num_seqs + 2, a.linear_conv_kernel_dim - 1, 2 * kd + vd,
                                                  dtype=self.model.dtype, device=self.device))
-                self.lin_rec.append(torch.zeros(self.max_num_seqs + 2, a.linear_num_value_heads, a.linear_key_head_dim,
+                self.lin_rec.append(torch.zeros(self.max_num_seqs + 2, nv_l, a.linear_key_head_dim,
                                                 a.linear_value_head_dim, dtype=torch.float32, device=self.device))
                 continue
             self.lin_conv.append(None)

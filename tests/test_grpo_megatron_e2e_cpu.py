@@ -36,7 +36,8 @@ cfg = {
     "policy": {"num_gpu": 2, "generation_batch_size": 16, "model_arch": arch, "num_inference_per_prompt": 2,
        "max_prompt_tokens_length": 64, "max_response_tokens_length": 16, "seq_length": 128, "temperature": 1.0,
        "kv_block_size": 8, "num_kv_blocks": 256, "ignore_eos": True,
-       "expert_model_parallel_size": int(os.environ.get("ROLLOUT_EP", "1"))},
+       "expert_model_parallel_size": int(os.environ.get("ROLLOUT_EP", "1")),
+       "tensor_model_parallel_size": int(os.environ.get("ROLLOUT_TP", "1"))},
     "reward": {"num_cpu": 2},
   }}
 cfg = to_dataclass(GrpoConfig, resolve(cfg))
@@ -98,5 +99,14 @@ def test_grpo_pp2_with_two_model_chunks_per_stage(tmp_path):
     """Interleaved pipeline schedule end to end: four layers as 2 stages x 2 chunks (stage 0 holds layers 0 and 2),
     scoring, training, checkpoint, and a weight sync that leaves the rollout weights equal to the trainer's."""
     res = _res(run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "TP": "1", "PP": "2", "VPP": "2",
+                                         "PRESET": "tiny_qwen3_next"})[0])
+    assert len(res) == 2 and all(r["episodes"] == 2 and r["maxdiff"] == 0.0 for r in res)
+
+
+def test_grpo_qwen3_next_tensor_parallel(tmp_path):
+    """Gated delta-net hybrid with the heads of both mixer kinds split over two tensor-parallel ranks, in the trainer
+    (sequence-parallel rows between the layers) and in the rollout engine (recurrent state of this rank's heads):
+    after the last sync every rank's rollout shard equals the trainer's."""
+    res = _res(run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "TP": "2", "PP": "1", "ROLLOUT_TP": "2",
                                          "PRESET": "tiny_qwen3_next"})[0])
     assert len(res) == 2 and all(r["episodes"] == 2 and r["maxdiff"] == 0.0 for r in res)

@@ -27,11 +27,17 @@ def _run(out_dir, tag, world, **env):
     return torch.load(os.path.join(out_dir, f"{tag}.pt"), weights_only=False)
 
 
-def _compare(a, b, tol=5e-4):
+def _compare(a, b, tol=5e-4, outliers=0):
+    """``outliers``: how many elements per tensor may differ by more than ``tol`` (Adam's first step moves an
+    element by the learning rate times the sign of its gradient, so a gradient at rounding level can land on either
+    side: at most 2 * lr apart)."""
     assert set(a["sd"]) == set(b["sd"])
     for k in a["sd"]:
-        d = (a["sd"][k] - b["sd"][k]).abs().max().item()
-        assert d < tol, (k, d)
+        d = (a["sd"][k] - b["sd"][k]).abs()
+        if outliers:
+            assert int((d >= tol).sum()) <= outliers and d.max().item() < 2.1e-3, (k, d.max().item(), int((d >= tol).sum()))
+        else:
+            assert d.max().item() < tol, (k, d.max().item())
     for k in ("pg_loss", "kl_loss", "entropy_loss", "grad_norm"):
         assert abs(a["metrics"][k] - b["metrics"][k]) < 5e-4 * max(1.0, abs(a["metrics"][k])), (k, a["metrics"], b["metrics"])
 
@@ -47,6 +53,8 @@ def _compare(a, b, tol=5e-4):
     ("tp2_gspo", 2, dict(TP=2, GSPO=1)),
     # two model chunks per stage, interleaved one-forward-one-backward over a global time table
     ("pp2vpp2", 2, dict(PP=2, VPP=2, LAYERS=4)),
+    # more ranks than key/value heads: two ranks hold each head, and the gradients of its rows are summed over them
+    ("tp4_replicated_kv_heads", 4, dict(TP=4)),
 ])
 def test_dense_parallel_matches_single(tmp_path, name, world, env):
     base_env = {k: v for k, v in env.items() if k in ("GSPO", "LAYERS")}
@@ -62,3 +70,15 @@ def test_moe_parallel_matches_single(tmp_path, name, world, env):
     base = _run(tmp_path, "base", 1, PRESET="tiny_moe", NOAUX=1)
     par = _run(tmp_path, name, world, PRESET="tiny_moe", NOAUX=1, **env)
     _compare(base, par, tol=5e-4)
+
+
+@pytest.mark.parametrize("name,world,env", [
+    ("tp2", 2, dict(TP=2)), ("tp2_no_seq_par", 2, dict(TP=2, SEQ_PAR=0)), ("tp2pp2", 4, dict(TP=2, PP=2)),
+    # four key heads in the delta-net layers, two key/value heads (each on two ranks) in the attention layers
+    ("tp4", 4, dict(TP=4, ARCH_JSON='{"linear_num_key_heads": 4}'))])
+def test_hybrid_parallel_matches_single(tmp_path, name, world, env):
+    """Qwen3-Next: the heads of the gated delta-net layers (input projections, convolution channels, decay
+    parameters, recurrent state) and of the gated attention layers split over the tensor-parallel ranks."""
+    base = _run(tmp_path, "base", 1, PRESET="tiny_qwen3_next", NOAUX=1, **{k: v for k, v in env.items() if k == "ARCH_JSON"})
+    par = _run(tmp_path, name, world, PRESET="tiny_qwen3_next", NOAUX=1, **env)
+    _compare(base, par, tol=5e-4, outliers=2)

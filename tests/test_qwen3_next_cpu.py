@@ -163,3 +163,37 @@ def test_model_gradients_match_hf():
                                ("layers.3.input_layernorm", "model.layers.3.input_layernorm.weight")):
         a, b_ = grads[ours_name], hfp[hf_name].grad.reshape(grads[ours_name].shape)
         assert float((a - b_).norm() / b_.norm()) < 1e-3, (ours_name, float((a - b_).abs().max()))
+
+
+_TP_SCRIPT = r'''
+import json, os, torch, torch.distributed as dist
+from chatlearn_b200.models.nn import PRESETS, CausalLM
+from chatlearn_b200.parallel.groups import Group
+from chatlearn_b200.rollout.engine import RolloutEngine, SamplingParams
+dist.init_process_group("gloo")
+rank = dist.get_rank()
+arch = PRESETS["tiny_qwen3_next"]()
+full = CausalLM(arch, dtype=torch.float32).init_weights(5, std=0.05)
+g = torch.Generator().manual_seed(3)
+prompts = [torch.randint(0, 500, (n,), generator=g).tolist() for n in (5, 23, 70, 9)]
+sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+want = [s.output for s in RolloutEngine(full, max_model_len=256).generate(prompts, sp)]
+shard = CausalLM(arch, dtype=torch.float32, tp=2, tp_rank=rank)
+shard.load_hf_state_dict(full.hf_state_dict())
+tp = Group(dist.group.WORLD, [0, 1], "tp")
+# whole prompts, then prompts in chunks of 16 tokens with the state carried between the chunks
+got = [[s.output for s in RolloutEngine(shard, tp_group=tp, max_model_len=256, **kw).generate(prompts, sp)]
+       for kw in (dict(), dict(max_num_batched_tokens=16))]
+print("RESULT " + json.dumps({"rank": rank, "same": [g == want for g in got]}))
+'''
+
+
+def test_tensor_parallel_engine_generates_the_same_tokens():
+    """Two tensor-parallel ranks, each with half of the heads of every mixer (and the recurrent state of those
+    heads), generate token for token what one rank generates."""
+    import json
+
+    from tests.dist_utils import run_ranks
+    outs, _ = run_ranks(_TP_SCRIPT, 2)
+    res = [json.loads(line[7:]) for o in outs for line in o.splitlines() if line.startswith("RESULT ")]
+    assert len(res) == 2 and all(r["same"] == [True, True] for r in res), res
