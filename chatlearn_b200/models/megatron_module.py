@@ -54,12 +54,11 @@ def arch_from_megatron_cfg(mc) -> ModelArch:
         qk_rope_head_dim=mc.qk_pos_emb_head_dim if mla else 0, v_head_dim=(mc.v_head_dim or 0) if mla else 0)
 
 
-def pipeline_layer_range(num_layers: int, pp: int, stage: int, first: Optional[int] = None,
-                         last: Optional[int] = None) -> Tuple[int, int]:
-    """Layers of a pipeline stage; ``first`` / ``last`` fix the size of the first and
-    last stage (uneven pipelines, megatron_config ``decoder_first/last_pipeline_num_layers``)."""
+def pipeline_stage_sizes(num_layers: int, pp: int, first: Optional[int] = None, last: Optional[int] = None) -> List[int]:
+    """Layers per pipeline stage; ``first`` / ``last`` fix the size of the first and last stage (uneven
+    pipelines, megatron_config ``decoder_first/last_pipeline_num_layers``), the others share the rest."""
     if pp == 1:
-        return 0, num_layers
+        return [num_layers]
     sizes = [0] * pp
     rem, mids = num_layers, list(range(pp))
     if first is not None:
@@ -70,21 +69,36 @@ def pipeline_layer_range(num_layers: int, pp: int, stage: int, first: Optional[i
         sizes[-1] = last
         rem -= last
         mids.remove(pp - 1)
-    base, extra = divmod(rem, len(mids))
-    for i, s in enumerate(mids):
-        sizes[s] = base + (1 if i < extra else 0)
+    base, extra = divmod(rem, len(mids)) if mids else (0, 0)
+    assert mids or rem == 0, "the first and last stage must hold all layers of a two-stage pipeline"
+    for i, st in enumerate(mids):
+        sizes[st] = base + (1 if i < extra else 0)
+    return sizes
+
+
+def pipeline_layer_range(num_layers: int, pp: int, stage: int, first: Optional[int] = None,
+                         last: Optional[int] = None) -> Tuple[int, int]:
+    """Layers of a pipeline stage."""
+    sizes = pipeline_stage_sizes(num_layers, pp, first, last)
     lo = sum(sizes[:stage])
     return lo, lo + sizes[stage]
 
 
-def pipeline_chunk_ranges(num_layers: int, pp: int, vpp: int, stage: int) -> List[Tuple[int, int]]:
-    """Layer ranges of the ``vpp`` model chunks a stage holds under the interleaved schedule: the model is cut
-    into ``pp * vpp`` equal chunks and chunk ``c`` lives on stage ``c % pp`` (Megatron's
-    ``virtual_pipeline_model_parallel_size``; chatlearn/configs/megatron_config.py:106 passes it through)."""
-    assert num_layers % (pp * vpp) == 0, \
-        f"{num_layers} layers do not split into {pp} stages x {vpp} chunks of equal size"
-    per = num_layers // (pp * vpp)
-    return [((j * pp + stage) * per, (j * pp + stage + 1) * per) for j in range(vpp)]
+def pipeline_chunk_ranges(num_layers: int, pp: int, vpp: int, stage: int, first: Optional[int] = None,
+                          last: Optional[int] = None) -> List[Tuple[int, int]]:
+    """Layer ranges of the ``vpp`` model chunks a stage holds under the interleaved schedule: every stage cuts its
+    layers into ``vpp`` equal chunks, and the model runs through chunk 0 of all stages, then chunk 1 of all stages and
+    so on, so chunk ``c`` of the model lives on stage ``c % pp`` (Megatron's
+    ``virtual_pipeline_model_parallel_size``; chatlearn/configs/megatron_config.py:106 passes it through, and
+    chatlearn/models/megatron_module.py:259-283 names the layers by the same offsets).  With ``first`` / ``last`` the
+    chunks of the first and last stage have their own size."""
+    sizes = pipeline_stage_sizes(num_layers, pp, first, last)
+    assert all(n % vpp == 0 for n in sizes), \
+        f"stages of {sizes} layers do not split into {vpp} chunks of equal size"
+    per = [n // vpp for n in sizes]
+    round_layers = sum(per)
+    lo = sum(per[:stage])
+    return [(j * round_layers + lo, j * round_layers + lo + per[stage]) for j in range(vpp)]
 
 
 class MegatronModule(FSDPModule):
@@ -151,9 +165,8 @@ class MegatronModule(FSDPModule):
         ma = self.module_args
         arch = self.resolve_arch()
         if self.vpp_size > 1:
-            assert ma.decoder_first_pipeline_num_layers is None and ma.decoder_last_pipeline_num_layers is None, \
-                "uneven first / last stages are not combined with model chunks"
-            ranges = pipeline_chunk_ranges(arch.num_hidden_layers, self.pp_size, self.vpp_size, self.pp_rank)
+            ranges = pipeline_chunk_ranges(arch.num_hidden_layers, self.pp_size, self.vpp_size, self.pp_rank,
+                                           ma.decoder_first_pipeline_num_layers, ma.decoder_last_pipeline_num_layers)
         else:
             ranges = pipeline_layer_range(arch.num_hidden_layers, self.pp_size, self.pp_rank,
                                           ma.decoder_first_pipeline_num_layers, ma.decoder_last_pipeline_num_layers)

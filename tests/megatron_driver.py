@@ -48,6 +48,7 @@ cfg = {
                            "pipeline_model_parallel_size": pp, "context_parallel_size": cp,
                            "virtual_pipeline_model_parallel_size": int(os.environ.get("VPP", "1")),
                            "expert_model_parallel_size": ep, "expert_tensor_parallel_size": etp,
+                           "decoder_first_pipeline_num_layers": int(os.environ["FIRST"]) if os.environ.get("FIRST") else None,
                            "sequence_parallel": os.environ.get("SEQ_PAR", "1") == "1", "packing": os.environ.get("PACKING", "1") == "1",
                            "max_token_in_packing": 96, "generation_batch_size": 4, "kl_coef": 0.01,
                            "entropy_coef": 0.001, "optimizer": {"lr": 1e-3, "clip_grad": 1.0},

@@ -53,6 +53,8 @@ def _compare(a, b, tol=5e-4, outliers=0):
     ("tp2_gspo", 2, dict(TP=2, GSPO=1)),
     # two model chunks per stage, interleaved one-forward-one-backward over a global time table
     ("pp2vpp2", 2, dict(PP=2, VPP=2, LAYERS=4)),
+    # ... and with four of the six layers on the first stage: chunks of two layers there, of one layer on the second
+    ("pp2vpp2_uneven", 2, dict(PP=2, VPP=2, LAYERS=6, FIRST=4)),
     # more ranks than key/value heads: two ranks hold each head, and the gradients of its rows are summed over them
     ("tp4_replicated_kv_heads", 4, dict(TP=4)),
 ])

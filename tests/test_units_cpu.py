@@ -690,3 +690,17 @@ def test_pipelined_decode_host_logic_on_cpu(monkeypatch):
     assert res["pipelined"] == res["plain"] and res["buffers"] == res["plain"]
     assert pre["plain"] > 0 and pre["pipelined"] > 0
     assert res["plain"][0][1] == "stop" and res["plain"][1] == (free[1].output[:3], "length") and len(res["plain"][3][0]) == 1
+
+
+def test_model_chunks_of_uneven_pipeline_stages():
+    from chatlearn_b200.models.megatron_module import pipeline_chunk_ranges, pipeline_layer_range, pipeline_stage_sizes
+    assert pipeline_stage_sizes(10, 4, first=1, last=1) == [1, 4, 4, 1]
+    assert pipeline_layer_range(10, 4, 2, first=1, last=1) == (5, 9)
+    assert [pipeline_chunk_ranges(8, 2, 2, s) for s in range(2)] == [[(0, 2), (4, 6)], [(2, 4), (6, 8)]]
+    # 16 layers, 4 stages of (2, 6, 6, 2) layers, two chunks each: a round is 1 + 3 + 3 + 1 layers
+    got = [pipeline_chunk_ranges(16, 4, 2, s, first=2, last=2) for s in range(4)]
+    assert got == [[(0, 1), (8, 9)], [(1, 4), (9, 12)], [(4, 7), (12, 15)], [(7, 8), (15, 16)]]
+    covered = sorted(l for st in got for lo, hi in st for l in range(lo, hi))
+    assert covered == list(range(16))
+    with pytest.raises(AssertionError):
+        pipeline_chunk_ranges(10, 4, 2, 0, first=1, last=1)
