@@ -11,7 +11,6 @@ import argparse
 import json
 import math
 import os
-import sys
 
 import torch
 

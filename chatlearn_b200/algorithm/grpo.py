@@ -7,7 +7,7 @@ FSDP-style or TP/EP-style trainers of this framework).
 """
 from collections import defaultdict
 from dataclasses import dataclass, field
-from typing import Any, Dict, Optional
+from typing import Any, Optional
 
 from chatlearn_b200.algorithm.base_algo import BaseAlgorithm
 from chatlearn_b200.algorithm.grpo_utils.advantage_compute import AdvantageComputer

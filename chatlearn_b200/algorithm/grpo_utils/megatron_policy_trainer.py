@@ -19,7 +19,6 @@ from chatlearn_b200 import ops
 from chatlearn_b200.models.megatron_module import MegatronModule
 from chatlearn_b200.models.nn import FwdCtx
 from chatlearn_b200.models.nn.model import decoder_layer
-from chatlearn_b200.parallel.context_parallel import zigzag_indices
 from chatlearn_b200.utils import xfer
 from .trainer_utils import PackedBatch, pack_samples, split_microbatch, unpack_per_sample
 

@@ -14,7 +14,6 @@ from typing import Any, Dict, List, Optional
 import torch
 
 from chatlearn_b200.utils import xfer
-from chatlearn_b200.utils.utils import even_slice
 
 
 def split_microbatch(data_list: List[Dict], micro_batch_size: Optional[int] = None,
@@ -51,7 +50,7 @@ class PackedBatch:
     values: Optional[torch.Tensor] = None         # [T] value estimates at rollout time (PPO critic)
     returns: Optional[torch.Tensor] = None        # [T] value targets
     pad: int = 0                                  # trailing pad tokens (SP/CP alignment)
-    mm: Any = None                                # per sample (pixel_values, image_grid_thw) or None (vision-language)
+    mm: Any = None                                # per sample (pixel_values, image_grid_thw, visual_time_steps) or None (vision-language)
 
     def to(self, device):
         for k, v in vars(self).items():
@@ -151,7 +150,7 @@ def pack_samples(samples: List[Dict[str, Any]], pad_multiple: int = 1, seq_multi
                        seq_lens=seq_lens, max_seqlen=max(seq_lens),
                        sample_ids=[int(s.get("id_in_list", i)) for i, s in enumerate(samples)],
                        old_logprobs=cat(old), ref_logprobs=cat(ref), advantages=cat(adv), values=cat(vals or []), returns=cat(rets or []), pad=pad,
-                       mm=[(s.get("pixel_values"), s.get("image_grid_thw")) for s in samples]
+                       mm=[(s.get("pixel_values"), s.get("image_grid_thw"), s.get("visual_time_steps")) for s in samples]
                        if any(s.get("pixel_values") is not None for s in samples) else None)
 
 

@@ -16,7 +16,6 @@ HF rectangle layout travels with the file, a checkpoint can be re-assembled into
 HF tensors offline (``offline_ckpt_converter``) without this framework's classes.
 """
 import os
-from typing import Dict
 
 import torch
 

@@ -14,9 +14,8 @@ import json
 import mmap
 import os
 import struct
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Dict, List, Optional
 
-import numpy as np
 import torch
 
 _DTYPES = {"F32": torch.float32, "F16": torch.float16, "BF16": torch.bfloat16, "I64": torch.int64,

@@ -11,7 +11,7 @@ import json
 import math
 import random
 from abc import ABC, abstractmethod
-from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence
+from typing import Any, Callable, Dict, List, Optional, Sequence
 
 from chatlearn_b200.utils.utils import even_slice
 

@@ -14,7 +14,7 @@ processor and ``qwen_vl_utils``).  Implemented here from the published recipe:
 """
 import io
 import math
-from typing import List, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 
@@ -40,10 +40,14 @@ def smart_resize(height: int, width: int, factor: int = 28, min_pixels: int = 56
 
 
 def load_image(src):
-    """PIL image from a path, raw bytes, a hex string of bytes, a dict with ``path``/``bytes``, or a PIL image."""
+    """PIL image from a path, raw bytes, a hex string of bytes, a dict with ``path``/``bytes``, an ``[H, W, 3]``
+    uint8 array (a decoded video frame), or a PIL image."""
     from PIL import Image
     if isinstance(src, Image.Image):
         return src.convert("RGB")
+    if hasattr(src, "shape") and hasattr(src, "dtype") and len(src.shape) == 3:
+        import numpy as np
+        return Image.fromarray(np.asarray(src, dtype=np.uint8)).convert("RGB")
     if isinstance(src, dict):
         src = src.get("bytes") or src.get("path")
     if isinstance(src, str):
@@ -76,19 +80,77 @@ def image_to_patches(img, patch_size: int = 14, temporal_patch_size: int = 2, me
     return t.reshape(gh * gw, C * temporal_patch_size * P * P).contiguous(), (1, gh, gw)
 
 
+def video_to_patches(frames, fps: float = 2.0, patch_size: int = 14, temporal_patch_size: int = 2, merge_size: int = 2,
+                     min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 320,
+                     mean: Sequence[float] = CLIP_MEAN, std: Sequence[float] = CLIP_STD):
+    """Frames of one video (paths, bytes, arrays or PIL images, sampled at ``fps`` frames per second) as
+    ``(pixel_values [grid_t·grid_h·grid_w, C·Tp·P·P] fp32, (grid_t, grid_h, grid_w), seconds per temporal grid step)``:
+    every frame is resized to the size the first one gets, ``Tp`` consecutive frames form one temporal grid step (the
+    last frame is repeated to fill the last step), and the patches are ordered like those of an image."""
+    import numpy as np
+    from PIL import Image
+    imgs = [load_image(f) for f in frames]
+    assert imgs, "a video needs at least one frame"
+    W, H = imgs[0].size
+    h, w = smart_resize(H, W, patch_size * merge_size, min_pixels, max_pixels)
+    mean_t, std_t = torch.tensor(mean).view(3, 1, 1), torch.tensor(std).view(3, 1, 1)
+    xs = []
+    for im in imgs:
+        x = torch.from_numpy(np.asarray(im.resize((w, h), resample=Image.BICUBIC), dtype=np.float32) / 255.0).permute(2, 0, 1)
+        xs.append((x - mean_t) / std_t)
+    while len(xs) % temporal_patch_size:
+        xs.append(xs[-1])
+    x = torch.stack(xs)                                                                      # [T, C, h, w]
+    gt, gh, gw, m, P, C = len(xs) // temporal_patch_size, h // patch_size, w // patch_size, merge_size, patch_size, 3
+    t = x.view(gt, temporal_patch_size, C, gh // m, m, P, gw // m, m, P)
+    t = t.permute(0, 3, 6, 4, 7, 2, 1, 5, 8)        # grid_t, gh/m, gw/m, m, m, C, Tp, P, P
+    return t.reshape(gt * gh * gw, C * temporal_patch_size * P * P).contiguous(), (gt, gh, gw), temporal_patch_size / float(fps)
+
+
 def expand_image_tokens(input_ids: List[int], grids: Sequence[Sequence[int]], image_token_id: int,
-                        merge_size: int = 2) -> List[int]:
-    """Replace the i-th single image placeholder by as many placeholders as the i-th image has merged patches."""
+                        merge_size: int = 2, video_token_id: Optional[int] = None) -> List[int]:
+    """Replace the i-th single image (or video) placeholder by as many placeholders as the i-th item of ``grids``
+    (images and videos in the order of their placeholders) has merged patches."""
     out, gi = [], 0
     for tok in input_ids:
-        if tok == image_token_id:
+        if tok == image_token_id or (video_token_id is not None and tok == video_token_id):
             t, h, w = grids[gi]
             gi += 1
-            out.extend([image_token_id] * (t * h * w // (merge_size ** 2)))
+            out.extend([tok] * (t * h * w // (merge_size ** 2)))
         else:
             out.append(tok)
-    assert gi == len(grids), f"{len(grids)} images but {gi} placeholders in the prompt"
+    assert gi == len(grids), f"{len(grids)} images / videos but {gi} placeholders in the prompt"
     return out
+
+
+def process_visuals(input_ids: List[int], images, videos, image_token_id: int, video_token_id: Optional[int],
+                    tokens_per_second: float = 1.0, video_kw=None, **kw):
+    """Patches of a prompt's images and videos in the order of their (single) placeholders:
+    ``(pixel_values, grids [[t, h, w], ...], time steps per item)``.  ``videos[i]`` is a list of frames or
+    ``{"frames": [...], "fps": f}``; a video's time step is its seconds per temporal grid step x
+    ``tokens_per_second`` (``None`` for images)."""
+    images, videos = list(images or []), list(videos or [])
+    pv, grids, steps, ii, vi = [], [], [], 0, 0
+    for tok in input_ids:
+        if tok == image_token_id and ii < len(images):
+            p, g = image_to_patches(images[ii], **kw)
+            ii += 1
+            steps.append(None)
+        elif video_token_id is not None and tok == video_token_id and vi < len(videos):
+            v = videos[vi]
+            vi += 1
+            frames, fps = (v["frames"], float(v.get("fps", 2.0))) if isinstance(v, dict) else (v, 2.0)
+            p, g, sec = video_to_patches(frames, fps=fps, **{**kw, **(video_kw or {})})
+            steps.append(sec * tokens_per_second)
+        else:
+            continue
+        pv.append(p)
+        grids.append(list(g))
+    assert ii == len(images) and vi == len(videos), \
+        f"{len(images)} images and {len(videos)} videos but {ii} and {vi} placeholders in the prompt"
+    if not pv:
+        return torch.zeros(0, 0), [], []
+    return torch.cat(pv, 0), grids, steps
 
 
 def process_images(images, **kw):

@@ -11,8 +11,7 @@ import os
 import sys
 from typing import Dict, List, Optional, Tuple, Type
 
-from chatlearn_b200.configs import (ConfigError, apply_dotlist, load_yaml, merge, missing_keys, resolve,
-                                    to_dataclass)
+from chatlearn_b200.configs import ConfigError, apply_dotlist, load_yaml, missing_keys, resolve, to_dataclass
 
 ALGO_REGISTRY: Dict[str, Tuple[str, str, str]] = {
     # name: (module, algorithm class, config class)

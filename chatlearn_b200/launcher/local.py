@@ -12,7 +12,6 @@ others blocked in a collective.
 import os
 import signal
 import subprocess
-import sys
 import tempfile
 import time
 from typing import List, Optional

@@ -13,7 +13,7 @@ batched call per round instead.  Tools run on the replica's first tensor-paralle
 rank; the requests it submits are broadcast so that all ranks of the replica feed
 their engines the same way.
 """
-from typing import Any, Dict, List, Type
+from typing import Dict, List, Type
 
 import torch
 

@@ -13,7 +13,7 @@ reference's.
 import os
 import time
 from itertools import cycle
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, List
 
 import torch
 
@@ -234,6 +234,8 @@ class BaseModule:
             vc = (getattr(arch, "vision_config", None) or {}) if arch is not None else {}
             return VLPromptPipeline(prompts, max_len, tok, enable_thinking=think, raw_chat=self._runtime_args.raw_chat,
                                     image_token_id=getattr(arch, "image_token_id", None),
+                                    video_token_id=getattr(arch, "video_token_id", None),
+                                    tokens_per_second=float(vc.get("tokens_per_second", 1)),
                                     merge_size=int(vc.get("spatial_merge_size", 2)),
                                     patch_size=int(vc.get("patch_size", 14)),
                                     temporal_patch_size=int(vc.get("temporal_patch_size", 2)),

@@ -14,13 +14,11 @@ separate translation step.
 """
 import math
 import os
-from typing import Dict, List, Optional, Tuple
+from typing import List, Optional, Tuple
 
-import torch
 
 from chatlearn_b200 import ops
 
-from chatlearn_b200.models.base_module import TorchModule
 from chatlearn_b200.models.fsdp_module import FSDPModule
 from chatlearn_b200.models.nn import CausalLM, ModelArch, resolve_arch
 from chatlearn_b200.parallel import ContextParallel, ExpertParallel, build_mesh

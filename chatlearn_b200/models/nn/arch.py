@@ -9,7 +9,7 @@ same HF keys are read directly.
 import json
 import os
 from dataclasses import asdict, dataclass, field
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, List, Optional, Tuple
 
 
 @dataclass
@@ -55,6 +55,7 @@ class ModelArch:
     mrope_interleaved: bool = False      # Qwen3-VL frequency layout
     vision_config: Optional[Dict[str, Any]] = None
     image_token_id: Optional[int] = None
+    video_token_id: Optional[int] = None             # placeholder of video frames (same tower, own temporal positions)
     # Qwen3-Next: gated delta-net ("linear_attention") layers interleaved with gated full attention
     layer_types: Optional[List[str]] = None          # per layer: "linear_attention" | "full_attention"
     full_attention_interval: int = 4                 # default pattern when layer_types is not given
@@ -205,6 +206,16 @@ class ModelArch:
         arch.extra = extra
         return arch
 
+    @property
+    def visual_token_ids(self) -> Tuple[int, ...]:
+        """Placeholder tokens whose rows take the vision tower's output."""
+        return tuple(t for t in (self.image_token_id, self.video_token_id) if t is not None)
+
+    @property
+    def tokens_per_second(self) -> float:
+        """Temporal positions per second of video (Qwen2.5-VL; 1 where the tower's settings do not say)."""
+        return float((self.vision_config or {}).get("tokens_per_second", 1))
+
     @classmethod
     def from_pretrained(cls, path: str) -> "ModelArch":
         with open(os.path.join(path, "config.json"), "r", encoding="utf-8") as f:
@@ -317,7 +328,7 @@ def tiny_qwen2_5_vl() -> ModelArch:
     """Qwen2.5-VL shape in miniature: Qwen2 language model with mrope + a windowed-attention vision tower."""
     return ModelArch(model_type="qwen2", vocab_size=1024, hidden_size=128, num_hidden_layers=2,
                      num_attention_heads=4, num_key_value_heads=2, intermediate_size=256, rope_theta=1e6,
-                     mrope_section=[4, 6, 6], image_token_id=1000,
+                     mrope_section=[4, 6, 6], image_token_id=1000, video_token_id=1001,
                      vision_config=dict(depth=2, hidden_size=64, intermediate_size=96, num_heads=4, patch_size=14,
                                         spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=128,
                                         window_size=56, fullatt_block_indexes=[1]))
@@ -326,7 +337,7 @@ def tiny_qwen2_5_vl() -> ModelArch:
 def qwen2_5_vl_7b() -> ModelArch:
     return ModelArch(model_type="qwen2", vocab_size=152064, hidden_size=3584, num_hidden_layers=28,
                      num_attention_heads=28, num_key_value_heads=4, intermediate_size=18944, rope_theta=1e6,
-                     mrope_section=[16, 24, 24], image_token_id=151655,
+                     mrope_section=[16, 24, 24], image_token_id=151655, video_token_id=151656,
                      vision_config=dict(depth=32, hidden_size=1280, intermediate_size=3420, num_heads=16, patch_size=14,
                                         spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=3584,
                                         window_size=112, fullatt_block_indexes=[7, 15, 23, 31]))

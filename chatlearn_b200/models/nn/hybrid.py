@@ -14,7 +14,7 @@ positions made neutral (no decay, no write) so the final state of every sequence
 """
 import math
 from dataclasses import dataclass
-from typing import Any, List, Optional
+from typing import List, Optional
 
 import torch
 import torch.nn.functional as F

@@ -17,7 +17,7 @@ chatlearn/data/vision_utils.py (grids).  Written against the published architect
 Weights live in a dict keyed by the HuggingFace names (``visual.…``), so checkpoints load by name.
 """
 from dataclasses import dataclass, field
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.nn.functional as F
@@ -347,29 +347,37 @@ class VisionTower3(VisionTower):
     __call__ = forward
 
 
-def mrope_positions(input_ids: torch.Tensor, image_grid_thw, image_token_id: int, merge: int) -> Tuple[torch.Tensor, int]:
+def mrope_positions(input_ids: torch.Tensor, image_grid_thw, image_token_id: int, merge: int,
+                    video_token_id: Optional[int] = None, time_steps=None) -> Tuple[torch.Tensor, int]:
     """Three-component (time, row, column) positions of one sequence and the offset that later text
-    positions carry: text tokens count up with all components equal; an image occupies a
-    (t, h/merge, w/merge) grid starting at the current position and advances it by max(h, w)/merge."""
+    positions carry: text tokens count up with all components equal; an image or a video occupies a
+    (t, h/merge, w/merge) grid starting at the current position, and the text after it continues one past the
+    largest position of the grid.  ``image_grid_thw`` lists the grids of all images and videos in the order of
+    their placeholder runs; ``time_steps[i]`` is the temporal position step between two frame groups of item ``i``
+    (Qwen2.5-VL: seconds per temporal grid step x the tower's ``tokens_per_second``, truncated per frame group;
+    ``None``: one position per frame group).  The reference patches the same rule into HuggingFace's model
+    (chatlearn/models/patches/transformers/qwen2_5_vl_patch.py:10-140)."""
     ids = input_ids.tolist()
     grids = [tuple(int(v) for v in g) for g in (image_grid_thw.tolist() if torch.is_tensor(image_grid_thw) else (image_grid_thw or []))]
+    visual = {t for t in (image_token_id, video_token_id) if t is not None}
     out, cur, i, gi = [], 0, 0, 0
     n = len(ids)
     while i < n:
-        if ids[i] == image_token_id:
+        if ids[i] in visual:
             t, h, w = grids[gi]
+            step = time_steps[gi] if time_steps is not None and time_steps[gi] is not None else 1
             gi += 1
             gh, gw = h // merge, w // merge
             cnt = t * gh * gw
-            tt = torch.arange(t).view(t, 1, 1).expand(t, gh, gw).reshape(-1)
+            tt = (torch.arange(t) * step).long().view(t, 1, 1).expand(t, gh, gw).reshape(-1)
             hh = torch.arange(gh).view(1, gh, 1).expand(t, gh, gw).reshape(-1)
             ww = torch.arange(gw).view(1, 1, gw).expand(t, gh, gw).reshape(-1)
             out.append(torch.stack([tt, hh, ww]) + cur)
-            cur += max(gh, gw)
+            cur += max(int(tt[-1]) + 1, gh, gw)
             i += cnt
         else:
             j = i
-            while j < n and ids[j] != image_token_id:
+            while j < n and ids[j] not in visual:
                 j += 1
             out.append((torch.arange(j - i) + cur).view(1, -1).expand(3, -1))
             cur += j - i
@@ -438,20 +446,21 @@ def attach_vision_block(lm, tower, pad_to: int = 1):
 
 def multimodal_inputs(lm, tower, tokens: torch.Tensor, seq_lens, mm, ctx, with_embeddings: bool = True):
     """Input embeddings and (time, row, column) positions of a packed row whose samples may carry
-    images.  ``mm[i] = (pixel_values, image_grid_thw)`` or ``(None, None)`` per sample; segments
+    images or videos.  ``mm[i] = (pixel_values, image_grid_thw[, visual_time_steps])`` or ``(None, None)`` per
+    sample (grids of all images and videos in the order of their placeholder runs); segments
     past ``len(mm)`` (alignment padding) count up from zero.  Sets ``ctx.mrope_positions`` and
     returns the embeddings (image placeholder rows replaced by the tower's output)."""
     from .model import embed
     arch = lm.arch
-    itok, merge = arch.image_token_id, tower.arch.spatial_merge_size
+    itok, vtok, merge = arch.image_token_id, arch.video_token_id, tower.arch.spatial_merge_size
     host = tokens.detach().cpu()
     pos, px, grids, off = [], [], [], 0
     for i, L in enumerate(seq_lens):
         seg = host[off:off + L]
-        pv, g = mm[i] if i < len(mm) else (None, None)
+        pv, g, steps = (tuple(mm[i]) + (None,))[:3] if i < len(mm) else (None, None, None)
         if pv is not None and len(g):
             g = g.tolist() if torch.is_tensor(g) else [list(v) for v in g]
-            p3, _ = mrope_positions(seg, g, itok, merge)
+            p3, _ = mrope_positions(seg, g, itok, merge, vtok, steps)
             px.append(torch.as_tensor(pv))
             grids.extend(g)
         else:
@@ -470,8 +479,8 @@ def multimodal_inputs(lm, tower, tokens: torch.Tensor, seq_lens, mm, ctx, with_e
         if isinstance(img, tuple):
             img, taps = img
         img = img.to(x.dtype)
-        rows = (tokens == itok).nonzero(as_tuple=True)[0]
-        assert rows.numel() == img.shape[0], f"{rows.numel()} image tokens but {img.shape[0]} image embeddings"
+        rows = ((tokens == itok) | (tokens == vtok) if vtok is not None else tokens == itok).nonzero(as_tuple=True)[0]
+        assert rows.numel() == img.shape[0], f"{rows.numel()} image / video tokens but {img.shape[0]} embeddings"
         x = x.index_put((rows,), img)                  # out of place: the embedding rows stay differentiable
         if taps:
             ctx.deepstack = (rows, [t.to(x.dtype) for t in taps])

@@ -7,7 +7,7 @@ language model is this package's ``CausalLM`` (flat parameter blocks, so ZeRO sh
 and weight sync apply to it unchanged); the tower's weights are kept by HF name.  Image embeddings
 replace the embeddings of the image placeholder tokens; positions are (time, row, column) triples.
 """
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Sequence
 
 import torch
 
@@ -45,8 +45,9 @@ class VLCausalLM:
         self.lm.load_hf_state_dict(strip_language_prefix(sd))
         self.visual.load_hf_state_dict(sd)
 
-    def positions(self, input_ids: torch.Tensor, image_grid_thw) -> torch.Tensor:
-        pos, _ = mrope_positions(input_ids.cpu(), image_grid_thw, self.arch.image_token_id, self.varch.spatial_merge_size)
+    def positions(self, input_ids: torch.Tensor, image_grid_thw, time_steps=None) -> torch.Tensor:
+        pos, _ = mrope_positions(input_ids.cpu(), image_grid_thw, self.arch.image_token_id, self.varch.spatial_merge_size,
+                                 self.arch.video_token_id, time_steps)
         return pos.to(input_ids.device)
 
     def hidden_states(self, tokens, ctx: FwdCtx, pixel_values=None, image_grid_thw=None, layer_hook=None):
@@ -60,8 +61,11 @@ class VLCausalLM:
             taps = []
             if isinstance(img, tuple):
                 img, taps = img
-            rows = (tokens == self.arch.image_token_id).nonzero(as_tuple=True)[0]
-            assert rows.numel() == img.shape[0], f"{rows.numel()} image placeholder tokens but {img.shape[0]} image embeddings"
+            vis = tokens == self.arch.image_token_id
+            if self.arch.video_token_id is not None:
+                vis = vis | (tokens == self.arch.video_token_id)
+            rows = vis.nonzero(as_tuple=True)[0]
+            assert rows.numel() == img.shape[0], f"{rows.numel()} image / video placeholder tokens but {img.shape[0]} embeddings"
             x = x.index_put((rows,), img.to(x.dtype))
             if taps:
                 ctx.deepstack = (rows, taps)

@@ -142,7 +142,8 @@ class RolloutModule(TorchModule):
         sp = self._sampling_params(is_eval, ma.max_response_tokens_length)
         mm = None
         if self.engine.vision is not None:
-            mm = [{"pixel_values": s["pixel_values"], "image_grid_thw": s["image_grid_thw"]}
+            mm = [{"pixel_values": s["pixel_values"], "image_grid_thw": s["image_grid_thw"],
+                   "visual_time_steps": s.get("visual_time_steps")}
                   if s.get("pixel_values") is not None else None for s in data_list]
         return self.engine.generate(prompts, sp, max_new_tokens=budgets, mm_inputs=mm)
 

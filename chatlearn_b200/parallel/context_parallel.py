@@ -9,7 +9,7 @@ into ``2·cp`` chunks; rank ``r`` keeps chunks ``r`` and ``2·cp-1-r`` (balanced
 work).  K and V are all-gathered (the cheap tensors under GQA/MLA), reordered to
 sequence order, and each local query chunk attends to its causal prefix.
 """
-from typing import List, Tuple
+from typing import List
 
 import torch
 

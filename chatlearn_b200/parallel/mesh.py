@@ -8,7 +8,7 @@ role over the role's rank set, so a trainer at TP2·EP4 and a rollout engine at
 TP2 × 4 replicas coexist in one job.
 """
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 import torch.distributed as dist
 

@@ -14,7 +14,7 @@ NVLink faults on the surviving ranks' GPUs.  ``TORCH_SYMM_MEM_DISABLE_MULTICAST=
 therefore set (unless the caller chose otherwise) before the first allocation.
 """
 import os
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 

@@ -7,7 +7,6 @@ and issues three a2a (q, k, v) before RoPE and one after attention; KV heads are
 replicated when ``sp > n_kv``.  Here the same exchange is two methods on a
 group object the attention block calls.
 """
-import torch
 
 from .groups import Group
 

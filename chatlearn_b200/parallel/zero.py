@@ -20,8 +20,7 @@ are issued per block so they can overlap the backward of earlier blocks and the
 update of later ones; the fused NVLink kernels (reduce-scatter + AdamW on the
 owned shard, all-gather of the cast result) plug in through ``Group.fast``.
 """
-import math
-from typing import Callable, Dict, List, Optional
+from typing import Dict, List, Optional
 
 import torch
 

@@ -17,7 +17,6 @@ from typing import Any, Dict, List, Optional, Sequence as Seq
 import torch
 
 from chatlearn_b200 import ops
-from chatlearn_b200.models.nn.arch import ModelArch
 from chatlearn_b200.models.nn.model import CausalLM, FwdCtx, KVCtx
 from chatlearn_b200.utils import xfer
 from chatlearn_b200.utils.constant import TAG_KV_CACHE, TAG_WEIGHTS
@@ -686,7 +685,6 @@ class RolloutEngine:
 
     # ------------------------------------------------------------------ public
     @torch.no_grad()
-    @torch.no_grad()
     def _attach_images(self, s: Sequence, mm: Dict[str, Any]):
         """Run the vision tower once for a request and remember where its embeddings go."""
         assert self.vision is not None, "this engine was built without a vision tower"
@@ -699,11 +697,12 @@ class RolloutEngine:
         if isinstance(embeds, tuple):            # towers with deep-stack taps (Qwen3-VL)
             embeds, taps = embeds
         embeds = embeds.to(self.model.dtype)
-        itok = self.arch.image_token_id
-        where = [j for j, tkn in enumerate(s.prompt) if tkn == itok]
+        itok, visual = self.arch.image_token_id, set(self.arch.visual_token_ids)
+        where = [j for j, tkn in enumerate(s.prompt) if tkn in visual]
         assert len(where) == embeds.shape[0], \
-            f"{len(where)} image placeholder tokens in the prompt but {embeds.shape[0]} image embeddings"
-        pos3, delta = mrope_positions(torch.tensor(s.prompt), grid, itok, self.vision.arch.spatial_merge_size)
+            f"{len(where)} image / video placeholder tokens in the prompt but {embeds.shape[0]} embeddings"
+        pos3, delta = mrope_positions(torch.tensor(s.prompt), grid, itok, self.vision.arch.spatial_merge_size,
+                                      self.arch.video_token_id, mm.get("visual_time_steps"))
         s.mm = {"embeds": embeds, "pos3": pos3, "ordinal": {j: o for o, j in enumerate(where)},
                 "deepstack": [t.to(self.model.dtype) for t in taps]}
         s.rope_delta = int(delta)

@@ -24,7 +24,7 @@ through ``llm.generate`` (chatlearn/models/vllm_module.py:360-411) and
 """
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional, Tuple
+from typing import Deque, Dict, List, Optional
 
 
 class BlockAllocator:

@@ -12,7 +12,6 @@ Every rank runs this loop (SPMD); phases are timed with CUDA events and the
 summary reports the maximum over ranks.
 """
 import os
-import time
 from typing import Dict, List, Optional
 
 import torch

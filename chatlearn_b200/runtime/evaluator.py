@@ -1,6 +1,5 @@
 """Evaluation executor (chatlearn/runtime/evaluator.py:74-132): runs the eval flow
 over the whole evaluation set and hands the results to ``post_process``."""
-from typing import Dict, List
 
 from chatlearn_b200.runtime.executor import Executor
 

@@ -11,7 +11,6 @@ added are then exchanged so that every rank holds the complete, identically
 ordered list (only the delta travels, and not at all when consumer and producer
 partition the data the same way).
 """
-import time
 from typing import Any, Callable, Dict, List, Optional
 
 import torch

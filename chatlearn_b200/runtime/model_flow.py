@@ -6,7 +6,7 @@ data; each call becomes a ``ModelNode`` whose inputs are the nodes that produced
 its arguments.  Nodes are then levelled topologically.  ``ControlDependencies``
 adds ordering edges between models with no data dependency.
 """
-from typing import Any, Callable, Dict, List, Optional, Sequence
+from typing import Callable, Dict, List, Optional, Sequence
 
 from chatlearn_b200.utils import global_vars
 

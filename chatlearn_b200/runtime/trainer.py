@@ -4,7 +4,6 @@ Parity: chatlearn/runtime/trainer.py:57-105.  Step ``i`` on data-parallel rank
 ``r`` trains on mini-batch ``r * num_iteration + i`` of the stream dataset (the
 episode is sliced by DP rank first, then into iterations).
 """
-from typing import Dict, List
 
 from chatlearn_b200.runtime.executor import Executor
 

@@ -11,10 +11,8 @@ fractional-GPU Ray actors inside placement groups; with one process per GPU a
   rule of ``find_model_packing_strategy`` (model_manager.py:220-263);
 * CPU roles (``num_cpu`` > 0) run data-parallel on every rank.
 """
-import time
 from typing import Dict, List, Tuple
 
-import torch.distributed as dist
 
 from chatlearn_b200.schedule.resource_manager import ResourceManager
 from chatlearn_b200.utils.constant import TAG_KV_CACHE, TAG_WEIGHTS

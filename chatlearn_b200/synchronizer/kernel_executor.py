@@ -7,7 +7,7 @@ memory (``parallel.symm_mem``); the kernel reads them with plain loads over
 NVLink and writes the rollout layout directly, casting on the fly.  Pointers are
 re-resolved when a buffer was re-allocated (offload/onload cycles).
 """
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 import numpy as np
 import torch

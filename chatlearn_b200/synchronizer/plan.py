@@ -21,7 +21,7 @@ cases: they are all "this rectangle goes there".
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
-from chatlearn_b200.models.nn.layout import Leaf, Segment
+from chatlearn_b200.models.nn.layout import Leaf
 
 Rect = Tuple[int, int, int, int]  # row0, col0, rows, cols
 

@@ -10,7 +10,6 @@ between steps, and the supervisor ends the job when a file appears.
 """
 import os
 import threading
-import time
 from typing import Callable, List, Optional
 
 

@@ -3,7 +3,6 @@ raises, a rank that exits, a rank that stops beating while its peers wait in a c
 import sys
 import time
 
-import pytest
 
 from chatlearn_b200.launcher.local import RankFailure, launch_local
 

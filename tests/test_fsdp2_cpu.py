@@ -1,6 +1,5 @@
 """Parameter-sharded (FSDP2-style) training state against the replicated one, on gloo with two ranks."""
 import json
-import os
 
 from tests.dist_utils import run_ranks
 

@@ -1,6 +1,5 @@
 """Unit tests of the host-side pieces: planner, sampler, config loader, flow tracing, packing,
 scheduler, checkpoints and the offline converter."""
-import json
 import os
 
 import pytest

@@ -23,6 +23,14 @@ if int(os.environ["RANK"]) == 0:
         ids = [5 + i, 6, 1002, 1000, 1003] + rng.integers(0, 900, 6).tolist()      # one placeholder per image
         rows.append({"data_source": "synthetic:mod7", "input_ids": ids, "images": [buf.getvalue().hex()],
                      "reward_model": {"ground_truth": ""}})
+        if os.environ.get("VIDEO", "0") == "1" and i % 2:
+            # every other record also shows a three-frame clip in front of its image
+            frames = []
+            for _ in range(3):
+                fb = io.BytesIO(); Image.fromarray(rng.integers(0, 255, (44, 58, 3), dtype=np.uint8)).save(fb, format="PNG")
+                frames.append(fb.getvalue().hex())
+            rows[-1]["videos"] = [{"frames": frames, "fps": 2.0}]
+            rows[-1]["input_ids"] = [7, 1002, 1001, 1003] + ids
     if os.environ.get("AGENT", "0") == "1":
         # agent task: raw chat messages, the image rides on the record and is fed to the engine by the chat model
         for i, r in enumerate(rows):
@@ -100,6 +108,17 @@ def test_vision_language_grpo(tmp_path):
         assert r["episodes"] == 2 and r["train_iters"] == 2 and r["has_tower"]
         assert all(n > 11 for n in r["prompt_lens"])          # the single placeholder was expanded to the image's tokens
         assert r["tower_moved"] == 0 and not r["tower_block"]  # frozen tower
+
+
+def test_vision_language_grpo_with_video_clips(tmp_path):
+    """Half of the records carry a clip of three frames in front of their image: preprocessing (temporal groups of two
+    frames), rollout, scoring and training with the video rows of the tower's output and their temporal positions."""
+    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "VIDEO": "1"})
+    res = [json.loads(line[7:]) for o in outs for line in o.splitlines() if line.startswith("RESULT ")]
+    assert len(res) == 2
+    for r in res:
+        assert r["episodes"] == 2 and r["train_iters"] == 2 and r["has_tower"]
+        assert max(r["prompt_lens"]) > min(r["prompt_lens"]) + 8        # the clips' tokens
 
 
 def test_vision_language_grpo_megatron_backend(tmp_path):

@@ -254,3 +254,105 @@ def test_qwen3_vl_moe_logits_match_hf():
         ctx.mrope_positions = model.positions(ids, grid)
         got = model.logits(ids, ctx, px, grid)
     assert torch.allclose(got, want, rtol=3e-4, atol=3e-4), (got - want).abs().max()
+
+
+def test_video_positions_follow_the_published_rule():
+    """Qwen2.5-VL's documented example: a video of 3 temporal grid steps x 2 x 2 merged patches whose steps are 50
+    temporal positions apart (2 s per step x 25 positions per second), followed by five text tokens."""
+    from chatlearn_b200.models.nn.vision import mrope_positions
+    ids = torch.tensor([1001] * 12 + [5, 6, 7, 8, 9])
+    pos, delta = mrope_positions(ids, [[3, 4, 4]], 1000, 2, video_token_id=1001, time_steps=[2.0 * 25])
+    assert pos[0].tolist() == [0] * 4 + [50] * 4 + [100] * 4 + [101, 102, 103, 104, 105]
+    assert pos[1].tolist() == [0, 0, 1, 1] * 3 + [101, 102, 103, 104, 105]
+    assert pos[2].tolist() == [0, 1, 0, 1] * 3 + [101, 102, 103, 104, 105]
+    assert delta == 106 - 17
+    # an image, text, then a video at half a second per step and 2 positions per second (one position per step)
+    ids = torch.tensor([3, 1000, 1000, 1000, 1000, 4, 1001, 1001, 5])
+    pos, _ = mrope_positions(ids, [[1, 4, 4], [2, 2, 2]], 1000, 2, video_token_id=1001, time_steps=[None, 1.0])
+    assert pos[0].tolist() == [0, 1, 1, 1, 1, 3, 4, 5, 6] and pos[1].tolist() == [0, 1, 1, 2, 2, 3, 4, 4, 6]
+
+
+def test_video_frames_become_patches_and_reach_the_model():
+    """Frames -> temporal groups of two -> patches in the image order (checked against the image path on a video of
+    one repeated frame), placeholder expansion in the order of the prompt, and a forward pass whose video rows take
+    the tower's output (equal to HuggingFace's with the same positions)."""
+    import numpy as np
+
+    from chatlearn_b200.data.vision_utils import expand_image_tokens, image_to_patches, process_visuals, video_to_patches
+    from chatlearn_b200.models.nn.model import packed_ctx
+    from chatlearn_b200.models.nn.vl_model import VLCausalLM
+    rng = np.random.default_rng(0)
+    frame = lambda: rng.integers(0, 255, (56, 84, 3), dtype=np.uint8)          # noqa: E731
+    f0 = frame()
+    pv_img, g_img = image_to_patches(f0)
+    pv_vid, g_vid, sec = video_to_patches([f0, f0, f0], fps=4.0)               # 3 frames: the last group is padded
+    assert g_vid == (2, g_img[1], g_img[2]) and sec == 0.5
+    n = pv_img.shape[0]
+    assert torch.equal(pv_vid[:n], pv_img) and torch.equal(pv_vid[n:], pv_img)
+    # order of the items follows the prompt: video placeholder first, then the image
+    vid = [frame() for _ in range(4)]
+    prompt = [7, 1002, 1001, 1003, 8, 1002, 1000, 1003, 9]
+    pv, grids, steps = process_visuals(prompt, [f0], [{"frames": vid, "fps": 2.0}], 1000, 1001, tokens_per_second=2.0)
+    assert grids == [[2, 4, 6], [1, 4, 6]] and steps == [2.0, None] and pv.shape[0] == 3 * 24
+    ids = expand_image_tokens(prompt, grids, 1000, 2, 1001)
+    assert ids.count(1001) == 12 and ids.count(1000) == 6 and ids.index(1001) < ids.index(1000)
+
+    cfg, hf = _hf()
+    model = VLCausalLM(_arch(cfg))
+    assert model.arch.video_token_id == 1001
+    model.load_hf_state_dict(hf.state_dict())
+    t = torch.tensor(ids)
+    pos = model.positions(t, grids, steps)
+    nv = 2 * 24
+    with torch.no_grad():
+        # HuggingFace takes images and videos separately; its own position rule for videos differs between
+        # releases, so both sides get the same positions
+        want = hf(input_ids=t[None], pixel_values=pv[nv:], image_grid_thw=torch.tensor(grids[1:]),
+                  pixel_values_videos=pv[:nv], video_grid_thw=torch.tensor(grids[:1]),
+                  position_ids=pos[:, None, :]).logits[0]
+        ctx, _ = packed_ctx([t.numel()], "cpu")
+        ctx.mrope_positions = pos
+        got = model.logits(t, ctx, pv, grids)
+    assert torch.allclose(got, want, rtol=2e-4, atol=2e-4), (got - want).abs().max()
+
+
+def test_rollout_engine_generates_with_a_video_prompt():
+    """A record with a video and an image through the prompt pipeline into the rollout engine: greedy generation equals
+    the argmax continuation of the full forward pass with the same positions (prefill in chunks of 16 tokens)."""
+    import numpy as np
+
+    from chatlearn_b200.data.prompt_dataset import VLPromptPipeline
+    from chatlearn_b200.models.nn.model import CausalLM, packed_ctx
+    from chatlearn_b200.models.nn.vision import VisionArch, VisionTower
+    from chatlearn_b200.models.nn.vl_model import VLCausalLM, strip_language_prefix
+    from chatlearn_b200.rollout import RolloutEngine, SamplingParams
+    cfg, hf = _hf()
+    arch = _arch(cfg)
+    rng = np.random.default_rng(1)
+    rec = {"input_ids": [7, 1002, 1001, 1003, 8, 1002, 1000, 1003, 9], "data_source": "x", "ground_truth": "",
+           "images": [rng.integers(0, 255, (56, 56, 3), dtype=np.uint8)],
+           "videos": [{"frames": [rng.integers(0, 255, (56, 84, 3), dtype=np.uint8) for _ in range(4)], "fps": 1.0}]}
+    pipe = VLPromptPipeline([rec], 512, image_token_id=1000, video_token_id=1001, tokens_per_second=arch.tokens_per_second)
+    s = pipe.data[0]
+    assert s["image_grid_thw"] == [[2, 4, 6], [1, 4, 4]] and s["visual_time_steps"] == [2.0, None]
+    ids = s["input_ids"]
+    assert len(ids) == 7 + 12 + 4 and s["prompt_token_length"] == len(ids)
+
+    full = VLCausalLM(arch)
+    full.load_hf_state_dict(hf.state_dict())
+    new, cur = 6, list(ids)
+    for _ in range(new):                                   # reference: one full forward per generated token
+        t = torch.tensor(cur)
+        ctx, _ = packed_ctx([t.numel()], "cpu")
+        ctx.mrope_positions = full.positions(t, s["image_grid_thw"], s["visual_time_steps"])
+        with torch.no_grad():
+            cur.append(int(full.logits(t, ctx, s["pixel_values"], s["image_grid_thw"])[-1].argmax()))
+    lm = CausalLM(arch)
+    lm.load_hf_state_dict(strip_language_prefix(hf.state_dict()))
+    tower = VisionTower(VisionArch.from_hf_dict(cfg.vision_config.to_dict()))
+    tower.load_hf_state_dict(hf.state_dict())
+    eng = RolloutEngine(lm, block_size=8, num_blocks=64, max_num_seqs=4, max_num_batched_tokens=16, max_model_len=128,
+                        vision=tower)
+    mm = {k: s[k] for k in ("pixel_values", "image_grid_thw", "visual_time_steps")}
+    out = eng.generate([ids], SamplingParams(temperature=0.0, max_tokens=new, ignore_eos=True), mm_inputs=[mm])
+    assert out[0].output == cur[len(ids):], (out[0].output, cur[len(ids):])
