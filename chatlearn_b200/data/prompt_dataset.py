@@ -91,11 +91,16 @@ class VLPromptPipeline(PromptPipeline):
                 kw.update(mean=mean, std=std)
             if item.get("videos") and s.get("pixel_values") is None:
                 # images and videos in the order of their placeholders in the tokenised prompt
-                assert "input_ids" in s and image_token_id is not None and video_token_id is not None, \
-                    "records with videos need a tokenised prompt and the two placeholder token ids"
-                pv, grids, steps = process_visuals(s["input_ids"], item.get("images"), item["videos"], image_token_id,
-                                                   video_token_id, tokens_per_second,
-                                                   video_kw=dict(max_pixels=video_max_pixels), **kw)
+                if "input_ids" in s:
+                    assert image_token_id is not None and video_token_id is not None, \
+                        "tokenised records with videos need the two placeholder token ids"
+                    order, itok, vtok = s["input_ids"], image_token_id, video_token_id
+                else:
+                    # raw chat records are tokenised turn by turn later: their images come first, then their videos
+                    itok, vtok = 0, 1
+                    order = [itok] * len(item.get("images") or []) + [vtok] * len(item["videos"])
+                pv, grids, steps = process_visuals(order, item.get("images"), item["videos"], itok, vtok,
+                                                   tokens_per_second, video_kw=dict(max_pixels=video_max_pixels), **kw)
                 s["pixel_values"], s["image_grid_thw"], s["visual_time_steps"] = pv, grids, steps
             elif item.get("images") and s.get("pixel_values") is None:
                 pv, grid = process_images(item["images"], **kw)

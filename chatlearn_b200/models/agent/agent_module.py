@@ -49,7 +49,7 @@ class AgentModule(RolloutModule):
                                         processor=getattr(self, "processor", None),
                                         model_type=getattr(self.runtime_args, "model_type", "llm"))
         if self.engine.vision is not None and getattr(g, "chatmodel", None) is not None:
-            g.chatmodel.vision = {"image_token_id": self.arch.image_token_id,
+            g.chatmodel.vision = {"image_token_id": self.arch.image_token_id, "video_token_id": self.arch.video_token_id,
                                   "merge_size": self.engine.vision.arch.spatial_merge_size}
         self.agent_factory[agent_name] = g
         return g
@@ -177,6 +177,7 @@ class AgentModule(RolloutModule):
                 "str_outputs": o.str_output,
                 "num_turns": o.num_turns,
                 "pixel_values": o.pixel_values, "image_grid_thw": o.image_grid_thw,
+                "visual_time_steps": o.visual_time_steps,
                 "attention_mask": o.attention_mask,
             })
             if o.response_logprobs is not None:

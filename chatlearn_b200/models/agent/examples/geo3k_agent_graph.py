@@ -19,4 +19,5 @@ class Geo3kAgentGraph(ToolLoopAgentGraph):
     def run(self, messages=None, sampling_params=None, **query):
         out = yield from super().run(messages, sampling_params, **query)
         out.pixel_values, out.image_grid_thw = query.get("pixel_values"), query.get("image_grid_thw")
+        out.visual_time_steps = query.get("visual_time_steps")
         return out

@@ -39,14 +39,14 @@ class ToolLoopAgentGraph(BaseAgentGraph):
 
         def call_model(state, config):
             c = config["configurable"]
-            mm = {"pixel_values": c.get("pixel_values"), "image_grid_thw": c.get("image_grid_thw")} \
-                if c.get("pixel_values") is not None else None
+            mm = {"pixel_values": c.get("pixel_values"), "image_grid_thw": c.get("image_grid_thw"),
+                  "visual_time_steps": c.get("visual_time_steps")} if c.get("pixel_values") is not None else None
             msg = yield from c["chat_model"].invoke(state["messages"], c["sampling_params"], mm)
             return {"messages": [msg]}
 
         def tool_node(state, config):
             extra = {k: v for k, v in config["configurable"].items()
-                     if k not in ("chat_model", "sampling_params", "pixel_values", "image_grid_thw")}
+                     if k not in ("chat_model", "sampling_params", "pixel_values", "image_grid_thw", "visual_time_steps")}
             outs = []
             for call in state["messages"][-1].tool_calls:
                 args = copy.deepcopy(call["args"])
@@ -77,6 +77,7 @@ class ToolLoopAgentGraph(BaseAgentGraph):
         self.graph = g.compile()
 
     def run(self, messages=None, sampling_params: Dict[str, Any] = None, **query):
-        extra = {k: query[k] for k in ("ground_truth", "data_source", "pixel_values", "image_grid_thw") if k in query}
+        extra = {k: query[k] for k in ("ground_truth", "data_source", "pixel_values", "image_grid_thw",
+                                       "visual_time_steps") if k in query}
         out = yield from self.default_run(messages, sampling_params or {}, **extra)
         return out

@@ -135,10 +135,14 @@ def test_vision_language_grpo_megatron_backend(tmp_path):
             assert (r["tower_moved"] > 0) == ("TRAIN_TOWER" in env), (name, r)
 
 
-def test_vision_language_agent_task(tmp_path):
-    """Agent trajectories of a vision-language model: the chat model expands the image placeholders and hands the
-    pixels to the engine with every turn; training then sees the same rows."""
-    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "AGENT": "1"})
+import pytest  # noqa: E402
+
+
+@pytest.mark.parametrize("video", ["0", "1"])
+def test_vision_language_agent_task(tmp_path, video):
+    """Agent trajectories of a vision-language model: the chat model expands the image (and video) placeholders and
+    hands the pixels to the engine with every turn; training then sees the same rows."""
+    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "AGENT": "1", "VIDEO": video})
     res = [json.loads(line[7:]) for o in outs for line in o.splitlines() if line.startswith("RESULT ")]
     assert len(res) == 2
     for r in res:
