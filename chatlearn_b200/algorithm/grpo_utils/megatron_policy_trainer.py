@@ -100,8 +100,21 @@ class MegatronPolicyTrainer(MegatronModule):
         x0 = None
         if getattr(self, "vision", None) is not None:
             from chatlearn_b200.models.nn.vision import multimodal_inputs
-            x0 = multimodal_inputs(self.model, self.vision, tokens, batch.seq_lens, batch.mm or [], ctx,
+            # (image rows and positions are addressed in the whole packed row: under context parallelism the inputs
+            # are built for the whole row and this rank keeps its slice)
+            x0 = multimodal_inputs(self.model, self.vision, batch.tokens, batch.seq_lens, batch.mm or [], ctx,
                                    with_embeddings=first)
+            if local is not None:
+                ctx.mrope_positions = ctx.mrope_positions.index_select(1, local)
+                if x0 is not None:
+                    x0 = x0.index_select(0, local)
+                if ctx.deepstack is not None:
+                    rows, taps = ctx.deepstack
+                    where = torch.full((batch.tokens.shape[0],), -1, dtype=torch.long, device=rows.device)
+                    where[local] = torch.arange(local.numel(), device=rows.device)
+                    mine = where[rows]
+                    keep = (mine >= 0).nonzero(as_tuple=True)[0]
+                    ctx.deepstack = (mine[keep], [t.index_select(0, keep) for t in taps])
             if ctx.deepstack is not None:
                 lo, hi = self.model.layer_range
                 assert hi - lo >= len(ctx.deepstack[1]), "the first pipeline stage must hold every deep-stack layer"

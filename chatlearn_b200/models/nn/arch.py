@@ -334,6 +334,17 @@ def tiny_qwen2_5_vl() -> ModelArch:
                                         window_size=56, fullatt_block_indexes=[1]))
 
 
+def tiny_qwen3_vl() -> ModelArch:
+    """Qwen3-VL shape in miniature: Qwen3 language model with the interleaved mrope layout + a vision tower with a
+    learned position table whose early layers feed deep-stack taps into the first language layers."""
+    return ModelArch(model_type="qwen3", vocab_size=1024, hidden_size=128, num_hidden_layers=3,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=32, intermediate_size=256, rope_theta=1e6,
+                     mrope_section=[4, 6, 6], mrope_interleaved=True, image_token_id=1000, video_token_id=1001,
+                     vision_config=dict(depth=3, hidden_size=64, intermediate_size=96, num_heads=4, patch_size=16,
+                                        spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=128,
+                                        num_position_embeddings=64, deepstack_visual_indexes=[0, 2]))
+
+
 def qwen2_5_vl_7b() -> ModelArch:
     return ModelArch(model_type="qwen2", vocab_size=152064, hidden_size=3584, num_hidden_layers=28,
                      num_attention_heads=28, num_key_value_heads=4, intermediate_size=18944, rope_theta=1e6,
@@ -385,7 +396,7 @@ def qwen3_next_80b_a3b() -> ModelArch:
 PRESETS = {
     "tiny_qwen3_next": tiny_qwen3_next, "qwen3_next_80b_a3b": qwen3_next_80b_a3b,
     "qwen3_235b_a22b": qwen3_235b_a22b, "deepseek_v3_671b": deepseek_v3_671b,
-    "tiny_qwen2_5_vl": tiny_qwen2_5_vl, "qwen2_5_vl_7b": qwen2_5_vl_7b,
+    "tiny_qwen2_5_vl": tiny_qwen2_5_vl, "tiny_qwen3_vl": tiny_qwen3_vl, "qwen2_5_vl_7b": qwen2_5_vl_7b,
     "tiny_qwen3": tiny_qwen3, "qwen3_8b": qwen3_8b, "qwen3_30b_a3b": qwen3_30b_a3b,
     "llama2_7b": llama2_7b, "moonlight_16b_a3b": moonlight_16b_a3b, "tiny_moe": tiny_moe,
     "tiny_mla_moe": tiny_mla_moe, "tiny_llama": tiny_llama,

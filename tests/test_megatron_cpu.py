@@ -84,3 +84,17 @@ def test_hybrid_parallel_matches_single(tmp_path, name, world, env):
     base = _run(tmp_path, "base", 1, PRESET="tiny_qwen3_next", NOAUX=1, **{k: v for k, v in env.items() if k == "ARCH_JSON"})
     par = _run(tmp_path, name, world, PRESET="tiny_qwen3_next", NOAUX=1, **env)
     _compare(base, par, tol=5e-4, outliers=2)
+
+
+@pytest.mark.parametrize("name,world,env", [
+    ("cp2", 2, dict(CP=2)), ("tp2", 2, dict(TP=2)), ("pp2", 2, dict(PP=2)),
+    # Qwen3-VL: the tower's deep-stack taps are added to the first layers at the image rows this rank holds
+    ("deepstack_cp2", 2, dict(CP=2, PRESET="tiny_qwen3_vl")), ("deepstack_tp2", 2, dict(TP=2, PRESET="tiny_qwen3_vl"))])
+def test_vision_language_parallel_matches_single(tmp_path, name, world, env):
+    """Rows with image patches: the tower's embeddings and the (time, row, column) positions are built for the whole
+    packed row; a context-parallel rank keeps its zig-zag slice of both, later pipeline stages only the positions."""
+    env = dict(env)
+    preset = env.pop("PRESET", "tiny_qwen2_5_vl")
+    base = _run(tmp_path, "base", 1, PRESET=preset)
+    par = _run(tmp_path, name, world, PRESET=preset, **env)
+    _compare(base, par, tol=5e-4, outliers=2)
