@@ -100,10 +100,12 @@ class MegatronPolicyTrainer(MegatronModule):
         x0 = None
         if getattr(self, "vision", None) is not None:
             from chatlearn_b200.models.nn.vision import multimodal_inputs
-            # (image rows and positions are addressed in the whole packed row: under context parallelism the inputs
-            # are built for the whole row and this rank keeps its slice)
+            # (image rows and positions are addressed in the whole packed row: under context and sequence parallelism
+            # the inputs are built for the whole row and this rank keeps its slice)
+            sp_rows, ctx.seq_parallel = ctx.seq_parallel and self.tp_size > 1, False
             x0 = multimodal_inputs(self.model, self.vision, batch.tokens, batch.seq_lens, batch.mm or [], ctx,
                                    with_embeddings=first)
+            ctx.seq_parallel = sp_rows
             if local is not None:
                 ctx.mrope_positions = ctx.mrope_positions.index_select(1, local)
                 if x0 is not None:
@@ -114,6 +116,15 @@ class MegatronPolicyTrainer(MegatronModule):
                     where[local] = torch.arange(local.numel(), device=rows.device)
                     mine = where[rows]
                     keep = (mine >= 0).nonzero(as_tuple=True)[0]
+                    ctx.deepstack = (mine[keep], [t.index_select(0, keep) for t in taps])
+            if sp_rows:
+                n = (batch.tokens.shape[0] if local is None else local.numel()) // self.tp_size
+                if x0 is not None:
+                    x0 = self.tp_group.scatter_seq(x0)           # (backward: the gradient rows of all ranks)
+                if ctx.deepstack is not None:
+                    rows, taps = ctx.deepstack
+                    mine = rows - self.tp_rank * n
+                    keep = ((mine >= 0) & (mine < n)).nonzero(as_tuple=True)[0]
                     ctx.deepstack = (mine[keep], [t.index_select(0, keep) for t in taps])
             if ctx.deepstack is not None:
                 lo, hi = self.model.layer_range

@@ -192,7 +192,6 @@ class MegatronModule(FSDPModule):
         from chatlearn_b200.models.nn.vision import attach_vision_block, build_vision_tower
         self.vision = build_vision_tower(self.arch, self.compute_dtype, self.device, getattr(self.module_args, "load", None))
         if self.vision is not None:
-            self.seq_parallel = False          # image rows are addressed in the full packed row
             if self.trainable and self.is_first_stage and bool(getattr(self.module_args, "train_vision_tower", False)):
                 attach_vision_block(self.model, self.vision, pad_to=math.lcm(self.dp_group.size, self.edp_group.size))
         if self.seq_parallel:

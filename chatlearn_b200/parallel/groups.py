@@ -148,6 +148,11 @@ class Group:
         (output of row-parallel layers under Megatron-style sequence parallelism)."""
         return _ReduceScatterSeq.apply(x, self) if self.size > 1 else x
 
+    def scatter_seq(self, x):
+        """This rank's slice of dim 0 of a tensor every rank holds whole; backward all-gathers the gradient
+        (entry into a sequence-parallel region)."""
+        return _ScatterSeq.apply(x, self) if self.size > 1 else x
+
     def all_to_all(self, x, out_splits=None, in_splits=None):
         return _AllToAll.apply(x, self, out_splits, in_splits) if self.size > 1 else x
 
@@ -206,6 +211,19 @@ class _ReduceScatterSeq(torch.autograd.Function):
         out = torch.empty((x.shape[0] // group.size,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         group.reduce_scatter_flat(out.view(-1), x.contiguous().view(-1))
         return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.group.all_gather_cat(g.contiguous(), 0), None
+
+
+class _ScatterSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        assert x.shape[0] % group.size == 0, f"{x.shape[0]} rows cannot be split over {group.size} ranks"
+        n = x.shape[0] // group.size
+        return x.narrow(0, group.rank * n, n).contiguous()
 
     @staticmethod
     def backward(ctx, g):

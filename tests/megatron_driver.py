@@ -53,6 +53,7 @@ cfg = {
                            "max_token_in_packing": 96, "generation_batch_size": 4, "kl_coef": 0.01,
                            "entropy_coef": 0.001, "optimizer": {"lr": 1e-3, "clip_grad": 1.0},
                            "use_group_sequence_policy": os.environ.get("GSPO", "0") == "1",
+                           "train_vision_tower": os.environ.get("TRAIN_TOWER", "0") == "1",
                            "megatron_model_cfg": {"num_layers": 1, "hidden_size": 8, "num_attention_heads": 1,
                                                   "ffn_hidden_size": 8, "max_position_embeddings": 64,
                                                   "kv_channels": 8}},

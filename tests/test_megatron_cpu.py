@@ -87,7 +87,9 @@ def test_hybrid_parallel_matches_single(tmp_path, name, world, env):
 
 
 @pytest.mark.parametrize("name,world,env", [
-    ("cp2", 2, dict(CP=2)), ("tp2", 2, dict(TP=2)), ("pp2", 2, dict(PP=2)),
+    ("cp2", 2, dict(CP=2)), ("tp2", 2, dict(TP=2)), ("pp2", 2, dict(PP=2)), ("tp2_no_seq_par", 2, dict(TP=2, SEQ_PAR=0)),
+    # sequence-parallel rows and a context-parallel slice at once, with the tower's weights trained
+    ("tp2cp2_trained_tower", 4, dict(TP=2, CP=2, TRAIN_TOWER=1)),
     # Qwen3-VL: the tower's deep-stack taps are added to the first layers at the image rows this rank holds
     ("deepstack_cp2", 2, dict(CP=2, PRESET="tiny_qwen3_vl")), ("deepstack_tp2", 2, dict(TP=2, PRESET="tiny_qwen3_vl"))])
 def test_vision_language_parallel_matches_single(tmp_path, name, world, env):
@@ -95,6 +97,6 @@ def test_vision_language_parallel_matches_single(tmp_path, name, world, env):
     packed row; a context-parallel rank keeps its zig-zag slice of both, later pipeline stages only the positions."""
     env = dict(env)
     preset = env.pop("PRESET", "tiny_qwen2_5_vl")
-    base = _run(tmp_path, "base", 1, PRESET=preset)
+    base = _run(tmp_path, "base", 1, PRESET=preset, **{k: v for k, v in env.items() if k == "TRAIN_TOWER"})
     par = _run(tmp_path, name, world, PRESET=preset, **env)
     _compare(base, par, tol=5e-4, outliers=2)
