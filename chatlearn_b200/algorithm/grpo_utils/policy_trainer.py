@@ -94,6 +94,8 @@ class PolicyTrainer(FSDPModule):
             # parameter-sharded mode: every block is gathered only while its segment runs, and a segment's
             # activations are recomputed in its backward (which is also where its parameters are re-gathered)
             lp, ent = self.state.logprobs(tokens, labels, ctx)
+            if self.sp is not None:
+                lp, ent = self.sp.gather(lp), self.sp.gather(ent)
             return lp, (ent if need_entropy else None), ctx
         hook = None
         if torch.is_grad_enabled() and getattr(self.module_args, "gradient_checkpointing", False):

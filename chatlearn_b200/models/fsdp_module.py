@@ -107,8 +107,7 @@ class FSDPModule(TorchModule):
             state_cls = ShardedTrainState
             if bool(getattr(self.module_args, "reshard_after_forward", False)):
                 from chatlearn_b200.parallel.fsdp2 import ReshardedTrainState
-                assert self.sp is None and self.vision is None, \
-                    "parameter sharding is built for text models without Ulysses sequence parallelism"
+                assert self.vision is None, "parameter sharding is built for text models"
                 state_cls = ReshardedTrainState
             extra = {}
             if self.replica_group is not None:

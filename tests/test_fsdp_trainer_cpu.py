@@ -1,0 +1,62 @@
+"""The data-parallel trainer with Ulysses sequence parallelism, hybrid sharding or sharded parameters must reproduce
+the single-rank result: same log-probs, same loss statistics, same weights after one optimizer step."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from chatlearn_b200.utils.utils import get_free_port
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DRIVER = os.path.join(ROOT, "tests", "fsdp_trainer_driver.py")
+
+
+def _run(out_dir, tag, world, **env):
+    port = get_free_port()
+    procs = []
+    for r in range(world):
+        e = dict(os.environ, OUT_DIR=str(out_dir), TAG=tag, RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE=str(world),
+                 MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CHATLEARN_FORCE_CPU="1", OMP_NUM_THREADS="2")
+        e.update({k: str(v) for k, v in env.items()})
+        procs.append(subprocess.Popen([sys.executable, DRIVER], env=e, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(o[-2500:] for o in outs)
+    return torch.load(os.path.join(out_dir, f"{tag}.pt"), weights_only=False)
+
+
+def _compare(a, b, tol=5e-4, outliers=2):
+    """Adam's first step moves an element by the learning rate times the sign of its gradient, so a gradient at
+    rounding level can land on either side (at most 2 * lr apart): a few such elements per tensor are allowed."""
+    for x, y in zip(a["logprobs"], b["logprobs"]):
+        assert (x - y).abs().max().item() < 1e-4
+    assert set(a["sd"]) == set(b["sd"])
+    for k in a["sd"]:
+        d = (a["sd"][k] - b["sd"][k]).abs()
+        assert int((d >= tol).sum()) <= outliers and d.max().item() < 2.1e-3, (k, d.max().item(), int((d >= tol).sum()))
+    for k in ("pg_loss", "kl_loss", "entropy_loss", "grad_norm"):
+        assert abs(a["metrics"][k] - b["metrics"][k]) < 5e-4 * max(1.0, abs(a["metrics"][k])), (k, a["metrics"], b["metrics"])
+
+
+@pytest.mark.parametrize("name,world,env", [
+    ("dp2", 2, dict()),
+    ("ulysses2", 2, dict(ULYSSES=2)),                    # every packed row split over the two ranks
+    ("ulysses2_dp2", 4, dict(ULYSSES=2)),
+    ("ulysses2_gspo", 2, dict(ULYSSES=2, GSPO=1)),
+    ("ulysses2_resharded", 2, dict(ULYSSES=2, RESHARD=1)),
+    ("ulysses4_replicated_kv_heads", 4, dict(ULYSSES=4)),   # four ranks, two key/value heads
+])
+def test_dense_matches_single(tmp_path, name, world, env):
+    base = _run(tmp_path, "base", 1, **{k: v for k, v in env.items() if k == "GSPO"})
+    par = _run(tmp_path, name, world, **env)
+    _compare(base, par)
+
+
+@pytest.mark.parametrize("name,world,env", [("moe_dp2", 2, dict(PRESET="tiny_moe")),
+                                            ("moe_ulysses2", 2, dict(PRESET="tiny_moe", ULYSSES=2))])
+def test_moe_matches_single(tmp_path, name, world, env):
+    base = _run(tmp_path, "base", 1, PRESET=env["PRESET"])
+    par = _run(tmp_path, name, world, **env)
+    _compare(base, par)
