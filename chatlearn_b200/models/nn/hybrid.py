@@ -125,6 +125,26 @@ def gated_delta_net(arch: ModelArch, p, x, ctx, layer: int):
                        qkvz[..., 2 * dk:2 * dk + r * dv].reshape(T, vd)], dim=-1)
     bgate = torch.sigmoid(ba[..., :r].reshape(T, nv).float())
     g = -p["A_log"].float().exp() * F.softplus(ba[..., r:].reshape(T, nv).float() + p["dt_bias"].float())
+    conv_w = p["conv1d"]
+    sp = ctx.sp if ctx.sp is not None and ctx.sp.size > 1 else None
+    if sp is not None:
+        # Ulysses: trade the sequence split for a head split around the convolution and the recurrence (both run
+        # per head over whole sequences): this rank gets 1/sp of the key heads with their value heads, all rows
+        assert st is None and nk % sp.size == 0, "Ulysses needs the key heads divisible by the group, and no rollout state"
+        T_loc, nv_all, vd_all = T, nv, vd
+        q_ = sp.seq_to_heads(mixed[:, :kd].reshape(T, nk, dk))
+        k_ = sp.seq_to_heads(mixed[:, kd:2 * kd].reshape(T, nk, dk))
+        v_ = sp.seq_to_heads(mixed[:, 2 * kd:].reshape(T, nv, dv))
+        gb = sp.seq_to_heads(torch.stack([g, bgate], dim=-1))
+        nk_l, nv_l = nk // sp.size, nv // sp.size
+        lo_k, lo_v = sp.rank * nk_l * dk, sp.rank * nv_l * dv
+        conv_w = torch.cat([conv_w.narrow(0, lo_k, nk_l * dk), conv_w.narrow(0, kd + lo_k, nk_l * dk),
+                            conv_w.narrow(0, 2 * kd + lo_v, nv_l * dv)], dim=0)
+        nk, nv, T = nk_l, nv_l, q_.shape[0]
+        kd, vd = nk * dk, nv * dv
+        C = 2 * kd + vd
+        mixed = torch.cat([q_.reshape(T, kd), k_.reshape(T, kd), v_.reshape(T, vd)], dim=-1)
+        g, bgate = gb[..., 0].contiguous(), gb[..., 1].contiguous()
 
     seq, off, B, L, lens = _pack_index(ctx, T, x.device)
     # causal depthwise convolution over [previous taps | this step's rows] of every sequence
@@ -135,9 +155,9 @@ def gated_delta_net(arch: ModelArch, p, x, ctx, layer: int):
     xp[seq, off + K - 1] = mixed
     if L == 1:
         # decode: one output per channel, the taps times the last K inputs (plain statements, safe to capture)
-        y = F.silu((xp.float() * p["conv1d"].float().t().unsqueeze(0)).sum(1, keepdim=True)).to(mixed.dtype)
+        y = F.silu((xp.float() * conv_w.float().t().unsqueeze(0)).sum(1, keepdim=True)).to(mixed.dtype)
     else:
-        y = F.silu(F.conv1d(xp.transpose(1, 2), p["conv1d"].unsqueeze(1).to(mixed.dtype), groups=C)).transpose(1, 2)
+        y = F.silu(F.conv1d(xp.transpose(1, 2), conv_w.unsqueeze(1).to(mixed.dtype), groups=C)).transpose(1, 2)
     if st is not None:
         idx = (lens[:, None] + torch.arange(K - 1, device=x.device)[None]).unsqueeze(-1).expand(B, K - 1, C)
         st.conv[layer].index_copy_(0, st.slots, xp.gather(1, idx).to(st.conv[layer].dtype))
@@ -169,7 +189,11 @@ def gated_delta_net(arch: ModelArch, p, x, ctx, layer: int):
         o, S = gated_delta_chunked(q, k, v, gp, bp, init)
     if st is not None:
         st.rec[layer].index_copy_(0, st.slots, S.to(st.rec[layer].dtype))
-    return _gdn_output(arch, p, o[seq, off], z, x.dtype, T, vd, ctx)      # back to the packed row: [T, nv, dv]
+    o = o[seq, off]                                                        # back to the packed row: [T, nv, dv]
+    if sp is not None:
+        o = sp.heads_to_seq(o.contiguous())                                # this rank's rows, all heads
+        T, vd = T_loc, vd_all
+    return _gdn_output(arch, p, o, z, x.dtype, T, vd, ctx)
 
 
 def _gdn_output(arch, p, o, z, dtype, T, vd, ctx):
@@ -182,8 +206,8 @@ def _gdn_output(arch, p, o, z, dtype, T, vd, ctx):
 
 def gated_attention(arch: ModelArch, p, x, ctx, layer: int):
     from .model import _row_parallel, _tp_copy
-    assert (ctx.sp is None or ctx.sp.size == 1) and (ctx.cp is None or ctx.cp.size == 1), \
-        "Qwen3-Next layers run without Ulysses / context parallelism"
+    assert ctx.cp is None or ctx.cp.size == 1, "Qwen3-Next layers run without context parallelism"
+    sp = ctx.sp if ctx.sp is not None and ctx.sp.size > 1 else None
     x = _tp_copy(x, ctx)
     T = x.shape[0]
     d = arch.head_dim
@@ -203,6 +227,10 @@ def gated_attention(arch: ModelArch, p, x, ctx, layer: int):
         k = torch.cat([ops.rope(k[..., :rd].contiguous(), pos, arch.rope_theta), k[..., rd:]], dim=-1)
     scale = 1.0 / math.sqrt(d)
     kv = ctx.kv
+    if sp is not None:
+        # Ulysses: all rows of 1/sp of the heads through attention, then back (the output gate stays with the rows)
+        assert kv is None
+        q, k, v = sp.seq_to_heads(q.contiguous()), sp.seq_to_heads(k.contiguous(), kv=True), sp.seq_to_heads(v.contiguous(), kv=True)
     if kv is not None:
         ops.kv_append(k, v.contiguous(), kv.k_cache[layer], kv.v_cache[layer], kv.slot_mapping)
         if kv.prefill_only:
@@ -212,6 +240,8 @@ def gated_attention(arch: ModelArch, p, x, ctx, layer: int):
                                     kv.seq_lens, kv.q_lens, scale)
     else:
         o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, scale)
+    if sp is not None:
+        o = sp.heads_to_seq(o.contiguous())
     o = o.reshape(T, nh * d) * torch.sigmoid(gate)
     return _row_parallel(o, p["o_proj"], ctx)
 

@@ -54,8 +54,10 @@ def test_dense_matches_single(tmp_path, name, world, env):
     _compare(base, par)
 
 
-@pytest.mark.parametrize("name,world,env", [("moe_dp2", 2, dict(PRESET="tiny_moe")),
-                                            ("moe_ulysses2", 2, dict(PRESET="tiny_moe", ULYSSES=2))])
+@pytest.mark.parametrize("name,world,env", [
+    ("moe_dp2", 2, dict(PRESET="tiny_moe")), ("moe_ulysses2", 2, dict(PRESET="tiny_moe", ULYSSES=2)),
+    # Qwen3-Next: the convolution and the recurrence of the delta-net layers run per head over whole sequences
+    ("hybrid_dp2", 2, dict(PRESET="tiny_qwen3_next")), ("hybrid_ulysses2", 2, dict(PRESET="tiny_qwen3_next", ULYSSES=2))])
 def test_moe_matches_single(tmp_path, name, world, env):
     base = _run(tmp_path, "base", 1, PRESET=env["PRESET"])
     par = _run(tmp_path, name, world, **env)
