@@ -113,7 +113,17 @@ class PolicyTrainer(FSDPModule):
         x = None
         if getattr(self, "vision", None) is not None:
             from chatlearn_b200.models.nn.vision import multimodal_inputs
-            x = multimodal_inputs(self.model, self.vision, tokens, batch.seq_lens, batch.mm or [], ctx)
+            # (image rows and the three-component positions are addressed in the whole packed row; under Ulysses this
+            # rank keeps its rows of the embeddings, the positions stay whole for the attention after the exchange)
+            x = multimodal_inputs(self.model, self.vision, batch.tokens, batch.seq_lens, batch.mm or [], ctx)
+            if self.sp is not None:
+                n = tokens.shape[0]
+                x = self.sp.split(x)
+                if ctx.deepstack is not None:
+                    rows, taps = ctx.deepstack
+                    mine = rows - self.sp.rank * n
+                    keep = ((mine >= 0) & (mine < n)).nonzero(as_tuple=True)[0]
+                    ctx.deepstack = (mine[keep], [t.index_select(0, keep) for t in taps])
         lp, ent = self.model.logprobs(tokens, labels, ctx, layer_hook=hook, x=x)
         if self.sp is not None:
             lp = self.sp.gather(lp)

@@ -89,7 +89,6 @@ class FSDPModule(TorchModule):
         from chatlearn_b200.models.nn.vision import build_vision_tower
         self.vision = build_vision_tower(self.arch, self.compute_dtype, self.device, getattr(self.module_args, "load", None))
         if self.vision is not None:
-            assert self.sp is None, "vision-language models run without Ulysses sequence parallelism"
             if self.trainable and bool(getattr(self.module_args, "train_vision_tower", False)):
                 # the tower's weights become one more parameter block: sharded optimizer state, gradient
                 # reduction, offload, checkpoints and the weight sync into the rollout engine cover it

@@ -39,7 +39,8 @@ trainer = {"num_gpu": W, "trainable": True, "load": hf_dir, "fsdp_size": int(os.
            "reshard_after_forward": os.environ.get("RESHARD", "0") == "1",
            "packing": True, "max_token_in_packing": 96, "generation_batch_size": 4, "kl_coef": 0.01,
            "entropy_coef": 0.001, "optimizer": {"lr": 1e-3, "clip_grad": 1.0}, "save_hf": False,
-           "use_group_sequence_policy": os.environ.get("GSPO", "0") == "1"}
+           "use_group_sequence_policy": os.environ.get("GSPO", "0") == "1",
+           "train_vision_tower": os.environ.get("TRAIN_TOWER", "0") == "1"}
 cfg = {
     "runtime_args": {"train_backend": "fsdp", "exp_name": tag, "output_dir": os.path.join(out, tag),
                      "data_path": "none", "num_episode": 1, "sample_per_episode": 8, "train_micro_batch_size": 2,
@@ -66,9 +67,18 @@ arch = mod.model.arch
 samples = []
 for i in range(8):
     pl, rl = int(torch.randint(4, 12, (1,), generator=g)), int(torch.randint(6, 20, (1,), generator=g))
-    toks = torch.randint(0, arch.vocab_size - 1, (pl + rl,), generator=g)
+    toks = torch.randint(0, min(arch.vocab_size - 1, 900), (pl + rl,), generator=g)
     samples.append({"all_tokens": toks, "prompt_token_length": pl, "response_token_length": rl,
                     "advantages": float(torch.randn((), generator=g)), "prompt_uid": str(i // 2), "uid": i})
+    if arch.vision_config is not None and i % 4 != 3:
+        # vision-language rows: an image of (1, 4, 4) or (1, 4, 6) patches in the prompt (one sample in four has none;
+        # the random text stays below the placeholder ids)
+        grid = [1, 4, 4 + 2 * (i % 2)]
+        n_tok = grid[1] * grid[2] // 4
+        pdim = 3 * 2 * int(arch.vision_config["patch_size"]) ** 2
+        toks = torch.cat([toks[:2], torch.tensor([1002] + [arch.image_token_id] * n_tok + [1003]), toks[2:]])
+        samples[-1].update(all_tokens=toks, prompt_token_length=pl + n_tok + 2, image_grid_thw=[grid],
+                           pixel_values=torch.randn(grid[1] * grid[2], pdim, generator=g))
 noise = [0.05 * torch.randn(s["all_tokens"].numel() - 1, generator=g) for s in samples]
 dp, dpr = mod.data_parallel_size, mod.data_parallel_rank
 per = len(samples) // dp

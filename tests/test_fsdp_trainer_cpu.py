@@ -62,3 +62,15 @@ def test_moe_matches_single(tmp_path, name, world, env):
     base = _run(tmp_path, "base", 1, PRESET=env["PRESET"])
     par = _run(tmp_path, name, world, **env)
     _compare(base, par)
+
+
+@pytest.mark.parametrize("name,world,env", [
+    ("vl_dp2", 2, dict(PRESET="tiny_qwen2_5_vl")), ("vl_ulysses2", 2, dict(PRESET="tiny_qwen2_5_vl", ULYSSES=2)),
+    # Qwen3-VL: deep-stack taps at the image rows this rank holds; the tower's weights trained
+    ("vl3_ulysses2_trained_tower", 2, dict(PRESET="tiny_qwen3_vl", ULYSSES=2, TRAIN_TOWER=1))])
+def test_vision_language_matches_single(tmp_path, name, world, env):
+    """Rows with image patches under Ulysses: embeddings and positions are built for the whole packed row, a rank
+    keeps its rows of the embeddings and the whole positions (the attention runs on all rows of its heads)."""
+    base = _run(tmp_path, "base", 1, **{k: v for k, v in env.items() if k in ("PRESET", "TRAIN_TOWER")})
+    par = _run(tmp_path, name, world, **env)
+    _compare(base, par)
