@@ -110,7 +110,6 @@ class FSDPModule(TorchModule):
                 state_cls = ReshardedTrainState
             extra = {}
             if self.replica_group is not None:
-                assert state_cls is ShardedTrainState, "hybrid sharding is built for the replicated-parameter state"
                 extra["replica_group"] = self.replica_group
             self.state = state_cls(
                 self.model, self.shard_group, lr=oc.lr, betas=(oc.adam_beta1, oc.adam_beta2),

@@ -256,6 +256,10 @@ class ReshardedTrainState(ShardedTrainState):
         # every segment's gradient was reduce-scattered right after its backward; wait for the last ones
         if self.comm is not None:
             torch.cuda.current_stream().wait_stream(self.comm)
+        if self.replica is not None:
+            # hybrid sharding: the other shard groups hold the same shards of their own samples' gradients
+            for s in self.states:
+                self.replica.all_reduce_(s.grad_shard)
 
     @torch.no_grad()
     def step(self, lr: Optional[float] = None):
