@@ -88,12 +88,34 @@ class PolicyTrainer(FSDPModule):
             ctx.positions = self.sp.split(positions)
         return tokens, labels, ctx
 
+    def _multimodal_embed(self, batch, ctx):
+        """Vision-language models: the function that turns this rank's tokens into input embeddings with the tower's
+        output in the image rows (and leaves the three-component positions and deep-stack rows in ``ctx``); ``None``
+        for text models.  Image rows and positions are addressed in the whole packed row: under Ulysses this rank
+        keeps its rows of the embeddings, and the positions stay whole for the attention after the exchange."""
+        if getattr(self, "vision", None) is None:
+            return None
+        from chatlearn_b200.models.nn.vision import multimodal_inputs
+
+        def fn(tokens):
+            x = multimodal_inputs(self.model, self.vision, batch.tokens, batch.seq_lens, batch.mm or [], ctx)
+            if self.sp is not None:
+                n = tokens.shape[0]
+                x = self.sp.split(x)
+                if ctx.deepstack is not None:
+                    rows, taps = ctx.deepstack
+                    mine = rows - self.sp.rank * n
+                    keep = ((mine >= 0) & (mine < n)).nonzero(as_tuple=True)[0]
+                    ctx.deepstack = (mine[keep], [t.index_select(0, keep) for t in taps])
+            return x
+        return fn
+
     def _logprobs(self, batch, need_entropy: bool):
         tokens, labels, ctx = self._ctx_and_inputs(batch)
         if self.resharded:
             # parameter-sharded mode: every block is gathered only while its segment runs, and a segment's
             # activations are recomputed in its backward (which is also where its parameters are re-gathered)
-            lp, ent = self.state.logprobs(tokens, labels, ctx)
+            lp, ent = self.state.logprobs(tokens, labels, ctx, embed_fn=self._multimodal_embed(batch, ctx))
             if self.sp is not None:
                 lp, ent = self.sp.gather(lp), self.sp.gather(ent)
             return lp, (ent if need_entropy else None), ctx
@@ -110,20 +132,8 @@ class PolicyTrainer(FSDPModule):
                 if l >= n_ckpt:       # the last layers keep their activations: backward reaches them first
                     return decoder_layer(arch, p, x, c, l)
                 return checkpoint(lambda xx: decoder_layer(arch, p, xx, c, l), x, use_reentrant=False)
-        x = None
-        if getattr(self, "vision", None) is not None:
-            from chatlearn_b200.models.nn.vision import multimodal_inputs
-            # (image rows and the three-component positions are addressed in the whole packed row; under Ulysses this
-            # rank keeps its rows of the embeddings, the positions stay whole for the attention after the exchange)
-            x = multimodal_inputs(self.model, self.vision, batch.tokens, batch.seq_lens, batch.mm or [], ctx)
-            if self.sp is not None:
-                n = tokens.shape[0]
-                x = self.sp.split(x)
-                if ctx.deepstack is not None:
-                    rows, taps = ctx.deepstack
-                    mine = rows - self.sp.rank * n
-                    keep = ((mine >= 0) & (mine < n)).nonzero(as_tuple=True)[0]
-                    ctx.deepstack = (mine[keep], [t.index_select(0, keep) for t in taps])
+        embed_fn = self._multimodal_embed(batch, ctx)
+        x = embed_fn(tokens) if embed_fn is not None else None
         lp, ent = self.model.logprobs(tokens, labels, ctx, layer_hook=hook, x=x)
         if self.sp is not None:
             lp = self.sp.gather(lp)

@@ -360,16 +360,27 @@ class ReshardedTrainState(ShardedTrainState):
         j = i + step
         return self.order[j] if 0 <= j < len(self.order) else None
 
-    def logprobs(self, tokens, labels, ctx, temperature: float = 1.0, x=None):
-        """``CausalLM.logprobs`` with every block gathered only while its segment runs."""
+    def logprobs(self, tokens, labels, ctx, temperature: float = 1.0, x=None, embed_fn=None):
+        """``CausalLM.logprobs`` with every block gathered only while its segment runs.  ``embed_fn(tokens)``
+        replaces the plain embedding look-up (vision-language rows: the tower's output goes into the image rows; it
+        runs inside the first segment, with the embedding block and, if it is trained, the tower's block gathered)."""
         m = self.model
         arch = m.arch
         grad = torch.is_grad_enabled()
         if x is None:
-            x = self._seg(["embed"], lambda t: _as(m.dtype, embed(m.block_by_name["embed"].params, t, ctx)), (tokens,), grad)
+            first = ["embed"] + (["vision"] if embed_fn is not None and "vision" in self.by_name else [])
+            fn = embed_fn if embed_fn is not None else (lambda t: embed(m.block_by_name["embed"].params, t, ctx))
+            x = self._seg(first, lambda t: _as(m.dtype, fn(t)), (tokens,), grad)
         for l in range(*m.layer_range):
             names = [f"layer{l}"] + ([f"layer{l}.experts"] if f"layer{l}.experts" in m.block_by_name else [])
-            x = self._seg(names, lambda xx, l=l: decoder_layer(arch, m.layer_params(l), xx, ctx, l), (x,), grad)
+            def run_layer(xx, l=l):
+                xx = decoder_layer(arch, m.layer_params(l), xx, ctx, l)
+                if ctx.deepstack is not None and l < len(ctx.deepstack[1]):
+                    # vision features of tap l join the residual stream at the image rows (Qwen3-VL)
+                    rows, taps = ctx.deepstack
+                    xx = xx.index_add(0, rows, taps[l].to(xx.dtype))
+                return xx
+            x = self._seg(names, run_layer, (x,), grad)
         head = ["head"] + (["embed"] if arch.tie_word_embeddings else [])
 
         def run_head(h, lab):
