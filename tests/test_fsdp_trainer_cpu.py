@@ -27,6 +27,24 @@ def _run(out_dir, tag, world, **env):
     return torch.load(os.path.join(out_dir, f"{tag}.pt"), weights_only=False)
 
 
+_BASE = {}
+
+
+@pytest.fixture(scope="module")
+def base_dir(tmp_path_factory):
+    return tmp_path_factory.mktemp("single_rank")
+
+
+def _base(base_dir, **env):
+    """The single-rank result for one set of model settings (computed once per module)."""
+    key = tuple(sorted((k, str(v)) for k, v in env.items()))
+    if key not in _BASE:
+        d = base_dir / f"base{len(_BASE)}"
+        d.mkdir()
+        _BASE[key] = _run(d, "base", 1, **env)
+    return _BASE[key]
+
+
 def _compare(a, b, tol=5e-4, outliers=2):
     """Adam's first step moves an element by the learning rate times the sign of its gradient, so a gradient at
     rounding level can land on either side (at most 2 * lr apart): a few such elements per tensor are allowed."""
@@ -51,32 +69,32 @@ def _compare(a, b, tol=5e-4, outliers=2):
     ("hsdp2x2", 4, dict(FSDP=2)), ("hsdp2x2_resharded", 4, dict(FSDP=2, RESHARD=1)),
     ("dp2_resharded", 2, dict(RESHARD=1)),
 ])
-def test_dense_matches_single(tmp_path, name, world, env):
-    base = _run(tmp_path, "base", 1, **{k: v for k, v in env.items() if k == "GSPO"})
+def test_dense_matches_single(tmp_path, base_dir, name, world, env):
+    base = _base(base_dir, **{k: v for k, v in env.items() if k == "GSPO"})
     par = _run(tmp_path, name, world, **env)
     _compare(base, par)
 
 
 @pytest.mark.parametrize("name,world,env", [
-    ("moe_dp2", 2, dict(PRESET="tiny_moe")), ("moe_ulysses2", 2, dict(PRESET="tiny_moe", ULYSSES=2)),
+    ("moe_ulysses2", 2, dict(PRESET="tiny_moe", ULYSSES=2)),
     # Qwen3-Next: the convolution and the recurrence of the delta-net layers run per head over whole sequences
-    ("hybrid_dp2", 2, dict(PRESET="tiny_qwen3_next")), ("hybrid_ulysses2", 2, dict(PRESET="tiny_qwen3_next", ULYSSES=2))])
-def test_moe_matches_single(tmp_path, name, world, env):
-    base = _run(tmp_path, "base", 1, PRESET=env["PRESET"])
+    ("hybrid_ulysses2", 2, dict(PRESET="tiny_qwen3_next", ULYSSES=2))])
+def test_moe_matches_single(tmp_path, base_dir, name, world, env):
+    base = _base(base_dir, PRESET=env["PRESET"])
     par = _run(tmp_path, name, world, **env)
     _compare(base, par)
 
 
 @pytest.mark.parametrize("name,world,env", [
-    ("vl_dp2", 2, dict(PRESET="tiny_qwen2_5_vl")), ("vl_ulysses2", 2, dict(PRESET="tiny_qwen2_5_vl", ULYSSES=2)),
+    ("vl_ulysses2", 2, dict(PRESET="tiny_qwen2_5_vl", ULYSSES=2)),
     # Qwen3-VL: deep-stack taps at the image rows this rank holds; the tower's weights trained
     ("vl3_ulysses2_trained_tower", 2, dict(PRESET="tiny_qwen3_vl", ULYSSES=2, TRAIN_TOWER=1)),
     # sharded parameters: the tower's output enters inside the first segment (embedding and tower blocks gathered)
     ("vl_resharded_trained_tower", 2, dict(PRESET="tiny_qwen2_5_vl", RESHARD=1, TRAIN_TOWER=1)),
     ("vl3_resharded_ulysses2", 2, dict(PRESET="tiny_qwen3_vl", RESHARD=1, ULYSSES=2))])
-def test_vision_language_matches_single(tmp_path, name, world, env):
+def test_vision_language_matches_single(tmp_path, base_dir, name, world, env):
     """Rows with image patches under Ulysses: embeddings and positions are built for the whole packed row, a rank
     keeps its rows of the embeddings and the whole positions (the attention runs on all rows of its heads)."""
-    base = _run(tmp_path, "base", 1, **{k: v for k, v in env.items() if k in ("PRESET", "TRAIN_TOWER")})
+    base = _base(base_dir, **{k: v for k, v in env.items() if k in ("PRESET", "TRAIN_TOWER")})
     par = _run(tmp_path, name, world, **env)
     _compare(base, par)

@@ -27,6 +27,24 @@ def _run(out_dir, tag, world, **env):
     return torch.load(os.path.join(out_dir, f"{tag}.pt"), weights_only=False)
 
 
+_BASE = {}
+
+
+@pytest.fixture(scope="module")
+def base_dir(tmp_path_factory):
+    return tmp_path_factory.mktemp("single_rank")
+
+
+def _base(base_dir, **env):
+    """The single-rank result for one set of model settings (computed once per module)."""
+    key = tuple(sorted((k, str(v)) for k, v in env.items()))
+    if key not in _BASE:
+        d = base_dir / f"base{len(_BASE)}"
+        d.mkdir()
+        _BASE[key] = _run(d, "base", 1, **env)
+    return _BASE[key]
+
+
 def _compare(a, b, tol=5e-4, outliers=0):
     """``outliers``: how many elements per tensor may differ by more than ``tol`` (Adam's first step moves an
     element by the learning rate times the sign of its gradient, so a gradient at rounding level can land on either
@@ -58,9 +76,9 @@ def _compare(a, b, tol=5e-4, outliers=0):
     # more ranks than key/value heads: two ranks hold each head, and the gradients of its rows are summed over them
     ("tp4_replicated_kv_heads", 4, dict(TP=4)),
 ])
-def test_dense_parallel_matches_single(tmp_path, name, world, env):
+def test_dense_parallel_matches_single(tmp_path, base_dir, name, world, env):
     base_env = {k: v for k, v in env.items() if k in ("GSPO", "LAYERS")}
-    base = _run(tmp_path, "base", 1, **base_env)
+    base = _base(base_dir, **base_env)
     par = _run(tmp_path, name, world, **env)
     _compare(base, par)
 
@@ -68,8 +86,8 @@ def test_dense_parallel_matches_single(tmp_path, name, world, env):
 @pytest.mark.parametrize("name,world,env", [("ep2", 2, dict(EP=2)), ("tp2ep2", 4, dict(TP=2, EP=2)),
                                             ("tp2etp2", 2, dict(TP=2, ETP=2)), ("tp2etp2ep2", 4, dict(TP=2, ETP=2, EP=2)),
                                             ("tp2_replicated_experts", 2, dict(TP=2))])
-def test_moe_parallel_matches_single(tmp_path, name, world, env):
-    base = _run(tmp_path, "base", 1, PRESET="tiny_moe", NOAUX=1)
+def test_moe_parallel_matches_single(tmp_path, base_dir, name, world, env):
+    base = _base(base_dir, PRESET="tiny_moe", NOAUX=1)
     par = _run(tmp_path, name, world, PRESET="tiny_moe", NOAUX=1, **env)
     _compare(base, par, tol=5e-4)
 
@@ -78,10 +96,10 @@ def test_moe_parallel_matches_single(tmp_path, name, world, env):
     ("tp2", 2, dict(TP=2)), ("tp2_no_seq_par", 2, dict(TP=2, SEQ_PAR=0)), ("tp2pp2", 4, dict(TP=2, PP=2)),
     # four key heads in the delta-net layers, two key/value heads (each on two ranks) in the attention layers
     ("tp4", 4, dict(TP=4, ARCH_JSON='{"linear_num_key_heads": 4}'))])
-def test_hybrid_parallel_matches_single(tmp_path, name, world, env):
+def test_hybrid_parallel_matches_single(tmp_path, base_dir, name, world, env):
     """Qwen3-Next: the heads of the gated delta-net layers (input projections, convolution channels, decay
     parameters, recurrent state) and of the gated attention layers split over the tensor-parallel ranks."""
-    base = _run(tmp_path, "base", 1, PRESET="tiny_qwen3_next", NOAUX=1, **{k: v for k, v in env.items() if k == "ARCH_JSON"})
+    base = _base(base_dir, PRESET="tiny_qwen3_next", NOAUX=1, **{k: v for k, v in env.items() if k == "ARCH_JSON"})
     par = _run(tmp_path, name, world, PRESET="tiny_qwen3_next", NOAUX=1, **env)
     _compare(base, par, tol=5e-4, outliers=2)
 
@@ -92,11 +110,11 @@ def test_hybrid_parallel_matches_single(tmp_path, name, world, env):
     ("tp2cp2_trained_tower", 4, dict(TP=2, CP=2, TRAIN_TOWER=1)),
     # Qwen3-VL: the tower's deep-stack taps are added to the first layers at the image rows this rank holds
     ("deepstack_cp2", 2, dict(CP=2, PRESET="tiny_qwen3_vl")), ("deepstack_tp2", 2, dict(TP=2, PRESET="tiny_qwen3_vl"))])
-def test_vision_language_parallel_matches_single(tmp_path, name, world, env):
+def test_vision_language_parallel_matches_single(tmp_path, base_dir, name, world, env):
     """Rows with image patches: the tower's embeddings and the (time, row, column) positions are built for the whole
     packed row; a context-parallel rank keeps its zig-zag slice of both, later pipeline stages only the positions."""
     env = dict(env)
     preset = env.pop("PRESET", "tiny_qwen2_5_vl")
-    base = _run(tmp_path, "base", 1, PRESET=preset, **{k: v for k, v in env.items() if k == "TRAIN_TOWER"})
+    base = _base(base_dir, PRESET=preset, **{k: v for k, v in env.items() if k == "TRAIN_TOWER"})
     par = _run(tmp_path, name, world, PRESET=preset, **env)
     _compare(base, par, tol=5e-4, outliers=2)
