@@ -102,6 +102,37 @@ def _pack_index(ctx, T: int, device):
     return seq, off, B, int(ctx.max_seqlen), lens
 
 
+class _HeadExchange:
+    """Rows of all heads <-> all rows of 1/n of the heads, over the Ulysses group or the context-parallel group.  A
+    context-parallel rank holds a zig-zag slice of every sequence: after the exchange the rows arrive rank by rank and
+    are put back into sequence order (``inv``), and leave in rank order again (``fwd``)."""
+
+    def __init__(self, ctx):
+        from chatlearn_b200.parallel.ulysses import UlyssesGroup
+        self.inv = self.fwd = None
+        if ctx.sp is not None and ctx.sp.size > 1:
+            self.ex = ctx.sp
+        else:
+            self.ex = UlyssesGroup(ctx.cp.group)
+            self.inv = ctx.cp_plan["inv"]
+            self.fwd = torch.empty_like(self.inv)
+            self.fwd[self.inv] = torch.arange(self.inv.numel(), device=self.inv.device)
+        self.size, self.rank = self.ex.size, self.ex.rank
+
+    @staticmethod
+    def of(ctx):
+        if (ctx.sp is not None and ctx.sp.size > 1) or (ctx.cp is not None and ctx.cp.size > 1):
+            return _HeadExchange(ctx)
+        return None
+
+    def seq_to_heads(self, x):
+        y = self.ex.seq_to_heads(x)
+        return y if self.inv is None else y.index_select(0, self.inv)
+
+    def heads_to_seq(self, x):
+        return self.ex.heads_to_seq(x.contiguous() if self.fwd is None else x.index_select(0, self.fwd))
+
+
 def gated_delta_net(arch: ModelArch, p, x, ctx, layer: int):
     T = x.shape[0]
     if T == 0:
@@ -126,11 +157,13 @@ def gated_delta_net(arch: ModelArch, p, x, ctx, layer: int):
     bgate = torch.sigmoid(ba[..., :r].reshape(T, nv).float())
     g = -p["A_log"].float().exp() * F.softplus(ba[..., r:].reshape(T, nv).float() + p["dt_bias"].float())
     conv_w = p["conv1d"]
-    sp = ctx.sp if ctx.sp is not None and ctx.sp.size > 1 else None
+    sp = _HeadExchange.of(ctx)
     if sp is not None:
-        # Ulysses: trade the sequence split for a head split around the convolution and the recurrence (both run
-        # per head over whole sequences): this rank gets 1/sp of the key heads with their value heads, all rows
-        assert st is None and nk % sp.size == 0, "Ulysses needs the key heads divisible by the group, and no rollout state"
+        # Ulysses / context parallelism: trade the sequence split for a head split around the convolution and the
+        # recurrence (both run per head over whole sequences): this rank gets 1/n of the key heads with their value
+        # heads, all rows
+        assert st is None and nk % sp.size == 0, \
+            "sequence-split delta-net layers need the key heads divisible by the group, and no rollout state"
         T_loc, nv_all, vd_all = T, nv, vd
         q_ = sp.seq_to_heads(mixed[:, :kd].reshape(T, nk, dk))
         k_ = sp.seq_to_heads(mixed[:, kd:2 * kd].reshape(T, nk, dk))
@@ -191,7 +224,7 @@ def gated_delta_net(arch: ModelArch, p, x, ctx, layer: int):
         st.rec[layer].index_copy_(0, st.slots, S.to(st.rec[layer].dtype))
     o = o[seq, off]                                                        # back to the packed row: [T, nv, dv]
     if sp is not None:
-        o = sp.heads_to_seq(o.contiguous())                                # this rank's rows, all heads
+        o = sp.heads_to_seq(o)                                             # this rank's rows, all heads
         T, vd = T_loc, vd_all
     return _gdn_output(arch, p, o, z, x.dtype, T, vd, ctx)
 
@@ -206,7 +239,6 @@ def _gdn_output(arch, p, o, z, dtype, T, vd, ctx):
 
 def gated_attention(arch: ModelArch, p, x, ctx, layer: int):
     from .model import _row_parallel, _tp_copy
-    assert ctx.cp is None or ctx.cp.size == 1, "Qwen3-Next layers run without context parallelism"
     sp = ctx.sp if ctx.sp is not None and ctx.sp.size > 1 else None
     x = _tp_copy(x, ctx)
     T = x.shape[0]
@@ -238,6 +270,8 @@ def gated_attention(arch: ModelArch, p, x, ctx, layer: int):
         else:
             o = ops.paged_attention(q, kv.k_cache[layer], kv.v_cache[layer], kv.block_tables,
                                     kv.seq_lens, kv.q_lens, scale)
+    elif ctx.cp is not None and ctx.cp.size > 1:
+        o = ctx.cp.attention(q.contiguous(), k.contiguous(), v.contiguous(), ctx, scale)    # keys / values gathered
     else:
         o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, scale)
     if sp is not None:

@@ -95,7 +95,10 @@ def test_moe_parallel_matches_single(tmp_path, base_dir, name, world, env):
 @pytest.mark.parametrize("name,world,env", [
     ("tp2", 2, dict(TP=2)), ("tp2_no_seq_par", 2, dict(TP=2, SEQ_PAR=0)), ("tp2pp2", 4, dict(TP=2, PP=2)),
     # four key heads in the delta-net layers, two key/value heads (each on two ranks) in the attention layers
-    ("tp4", 4, dict(TP=4, ARCH_JSON='{"linear_num_key_heads": 4}'))])
+    ("tp4", 4, dict(TP=4, ARCH_JSON='{"linear_num_key_heads": 4}')),
+    # context parallelism: the delta-net layers exchange their zig-zag rows for all rows of half of the heads, the
+    # attention layers gather keys and values
+    ("cp2", 2, dict(CP=2)), ("tp2cp2", 4, dict(TP=2, CP=2, ARCH_JSON='{"linear_num_key_heads": 4}'))])
 def test_hybrid_parallel_matches_single(tmp_path, base_dir, name, world, env):
     """Qwen3-Next: the heads of the gated delta-net layers (input projections, convolution channels, decay
     parameters, recurrent state) and of the gated attention layers split over the tensor-parallel ranks."""
