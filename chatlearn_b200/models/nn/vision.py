@@ -363,7 +363,7 @@ def mrope_positions(input_ids: torch.Tensor, image_grid_thw, image_token_id: int
     out, cur, i, gi = [], 0, 0, 0
     n = len(ids)
     while i < n:
-        if ids[i] in visual:
+        if ids[i] in visual and gi < len(grids):        # (a placeholder token the model generated itself is text)
             t, h, w = grids[gi]
             step = time_steps[gi] if time_steps is not None and time_steps[gi] is not None else 1
             gi += 1
@@ -376,8 +376,8 @@ def mrope_positions(input_ids: torch.Tensor, image_grid_thw, image_token_id: int
             cur += max(int(tt[-1]) + 1, gh, gw)
             i += cnt
         else:
-            j = i
-            while j < n and ids[j] not in visual:
+            j = i + 1 if ids[i] in visual else i
+            while j < n and (ids[j] not in visual or gi >= len(grids)):
                 j += 1
             out.append((torch.arange(j - i) + cur).view(1, -1).expand(3, -1))
             cur += j - i
@@ -454,7 +454,7 @@ def multimodal_inputs(lm, tower, tokens: torch.Tensor, seq_lens, mm, ctx, with_e
     arch = lm.arch
     itok, vtok, merge = arch.image_token_id, arch.video_token_id, tower.arch.spatial_merge_size
     host = tokens.detach().cpu()
-    pos, px, grids, off = [], [], [], 0
+    pos, px, grids, rows, off = [], [], [], [], 0
     for i, L in enumerate(seq_lens):
         seg = host[off:off + L]
         pv, g, steps = (tuple(mm[i]) + (None,))[:3] if i < len(mm) else (None, None, None)
@@ -463,6 +463,13 @@ def multimodal_inputs(lm, tower, tokens: torch.Tensor, seq_lens, mm, ctx, with_e
             p3, _ = mrope_positions(seg, g, itok, merge, vtok, steps)
             px.append(torch.as_tensor(pv))
             grids.extend(g)
+            # the rows of this sample's images: its first placeholder tokens, as many as it has merged patches
+            # (a placeholder token the model generated later in the response is an ordinary token)
+            vis = (seg == itok) | (seg == vtok) if vtok is not None else seg == itok
+            want = sum(int(t) * int(h) * int(w) for t, h, w in g) // (merge * merge)
+            mine = vis.nonzero(as_tuple=True)[0][:want]
+            assert mine.numel() == want, f"{mine.numel()} image / video tokens but {want} embeddings in sample {i}"
+            rows.append(mine + off)
         else:
             p3 = torch.arange(L).view(1, -1).expand(3, -1)
         pos.append(p3)
@@ -479,7 +486,7 @@ def multimodal_inputs(lm, tower, tokens: torch.Tensor, seq_lens, mm, ctx, with_e
         if isinstance(img, tuple):
             img, taps = img
         img = img.to(x.dtype)
-        rows = ((tokens == itok) | (tokens == vtok) if vtok is not None else tokens == itok).nonzero(as_tuple=True)[0]
+        rows = torch.cat(rows).to(tokens.device)
         assert rows.numel() == img.shape[0], f"{rows.numel()} image / video tokens but {img.shape[0]} embeddings"
         x = x.index_put((rows,), img)                  # out of place: the embedding rows stay differentiable
         if taps:

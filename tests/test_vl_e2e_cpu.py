@@ -52,7 +52,8 @@ cfg = {
        "packing": True, "max_token_in_packing": 512},
     "policy": {"num_gpu": 2, "generation_batch_size": 16, "model_arch": arch, "num_inference_per_prompt": 2,
        "max_prompt_tokens_length": 128, "max_response_tokens_length": 8, "seq_length": 256, "temperature": 1.0,
-       "kv_block_size": 8, "num_kv_blocks": 512, "ignore_eos": True, "max_pixels": 28 * 28 * 16},
+       "kv_block_size": 8, "num_kv_blocks": 512, "ignore_eos": True, "max_pixels": 28 * 28 * 16,
+       "tensor_model_parallel_size": int(os.environ.get("ROLLOUT_TP", "1"))},
     "reward": {"num_cpu": 2},
   }}
 train_tower = os.environ.get("TRAIN_TOWER", "0") == "1"
@@ -112,8 +113,9 @@ def test_vision_language_grpo(tmp_path):
 
 def test_vision_language_grpo_with_video_clips(tmp_path):
     """Half of the records carry a clip of three frames in front of their image: preprocessing (temporal groups of two
-    frames), rollout, scoring and training with the video rows of the tower's output and their temporal positions."""
-    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "VIDEO": "1"})
+    frames), rollout (one tensor-parallel replica over the two ranks), scoring and training with the video rows of the
+    tower's output and their temporal positions."""
+    outs, _ = run_ranks(SCRIPT, 2, env={"OUT_DIR": str(tmp_path), "VIDEO": "1", "ROLLOUT_TP": "2"})
     res = [json.loads(line[7:]) for o in outs for line in o.splitlines() if line.startswith("RESULT ")]
     assert len(res) == 2
     for r in res:

@@ -356,3 +356,13 @@ def test_rollout_engine_generates_with_a_video_prompt():
     mm = {k: s[k] for k in ("pixel_values", "image_grid_thw", "visual_time_steps")}
     out = eng.generate([ids], SamplingParams(temperature=0.0, max_tokens=new, ignore_eos=True), mm_inputs=[mm])
     assert out[0].output == cur[len(ids):], (out[0].output, cur[len(ids):])
+
+
+def test_placeholder_tokens_in_a_response_are_text():
+    """A response may contain the image placeholder id (sampled like any token): positions and image rows follow
+    the prompt's images only."""
+    from chatlearn_b200.models.nn.vision import mrope_positions
+    ids = torch.tensor([5, 1000, 1000, 1000, 1000, 6, 7, 1000, 8, 1001, 1001, 9])
+    pos, delta = mrope_positions(ids, [[1, 4, 4]], 1000, 2, video_token_id=1001)
+    assert pos[0].tolist() == [0, 1, 1, 1, 1, 3, 4, 5, 6, 7, 8, 9] and pos[2].tolist() == [0, 1, 2, 1, 2, 3, 4, 5, 6, 7, 8, 9]
+    assert delta == 10 - 12
