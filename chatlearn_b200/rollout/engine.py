@@ -698,7 +698,9 @@ class RolloutEngine:
             embeds, taps = embeds
         embeds = embeds.to(self.model.dtype)
         itok, visual = self.arch.image_token_id, set(self.arch.visual_token_ids)
-        where = [j for j, tkn in enumerate(s.prompt) if tkn in visual]
+        # (a prompt that continues an earlier partial response may hold placeholder tokens the model generated
+        # itself, after those of its images: they are ordinary tokens)
+        where = [j for j, tkn in enumerate(s.prompt) if tkn in visual][:embeds.shape[0]]
         assert len(where) == embeds.shape[0], \
             f"{len(where)} image / video placeholder tokens in the prompt but {embeds.shape[0]} embeddings"
         pos3, delta = mrope_positions(torch.tensor(s.prompt), grid, itok, self.vision.arch.spatial_merge_size,
