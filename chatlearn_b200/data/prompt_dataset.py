@@ -63,7 +63,7 @@ class VLPromptPipeline(PromptPipeline):
     which are resized, normalised and cut into patches here (``data/vision_utils.py``).  Every image
     placeholder token of the prompt is expanded to one token per merged patch of its image, so the
     rollout engine and the trainers can drop the vision tower's embeddings into place.  ``videos`` (per video a
-    list of frames, or ``{"frames": [...], "fps": f}``) go the same way behind their own placeholder token: images
+    list of frames, ``{"frames": [...], "fps": f}``, a file path or ``{"path": ..., "fps": rate}``) go the same way behind their own placeholder token: images
     and videos share ``pixel_values`` / ``image_grid_thw`` in the order of their placeholders, and
     ``visual_time_steps`` holds per item the temporal position step (``None`` for images).  Sample schema:
     the text schema plus ``pixel_values [patches, C·Tp·P·P]``, ``image_grid_thw [[t, h, w], ...]``."""

@@ -80,6 +80,38 @@ def image_to_patches(img, patch_size: int = 14, temporal_patch_size: int = 2, me
     return t.reshape(gh * gw, C * temporal_patch_size * P * P).contiguous(), (1, gh, gw)
 
 
+def load_video(path: str, fps: float = 2.0, max_frames: int = 768):
+    """Frames of a video file sampled at ``fps`` frames per second (at most ``max_frames``, then evenly thinned) as
+    ``([H, W, 3] uint8 arrays, the sampling rate that was reached)``.  Decoding uses OpenCV."""
+    try:
+        import cv2
+    except ImportError as e:                                        # pragma: no cover
+        raise RuntimeError("reading video files needs OpenCV (cv2); pass decoded frames instead") from e
+    cap = cv2.VideoCapture(path)
+    if not cap.isOpened():
+        raise FileNotFoundError(f"cannot open video '{path}'")
+    native = cap.get(cv2.CAP_PROP_FPS) or 0.0
+    step = max(native / fps, 1.0) if native > 0 else 1.0
+    frames, want, i = [], 0.0, 0
+    while True:
+        ok, img = cap.read()
+        if not ok:
+            break
+        if i >= want - 1e-6:
+            frames.append(cv2.cvtColor(img, cv2.COLOR_BGR2RGB))
+            want += step
+        i += 1
+    cap.release()
+    if not frames:
+        raise ValueError(f"video '{path}' holds no frames")
+    rate = (native / step) if native > 0 else fps
+    if len(frames) > max_frames:
+        keep = [int(round(j * (len(frames) - 1) / (max_frames - 1))) for j in range(max_frames)]
+        rate *= max_frames / len(frames)
+        frames = [frames[j] for j in keep]
+    return frames, rate
+
+
 def video_to_patches(frames, fps: float = 2.0, patch_size: int = 14, temporal_patch_size: int = 2, merge_size: int = 2,
                      min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 320,
                      mean: Sequence[float] = CLIP_MEAN, std: Sequence[float] = CLIP_STD):
@@ -126,8 +158,8 @@ def expand_image_tokens(input_ids: List[int], grids: Sequence[Sequence[int]], im
 def process_visuals(input_ids: List[int], images, videos, image_token_id: int, video_token_id: Optional[int],
                     tokens_per_second: float = 1.0, video_kw=None, **kw):
     """Patches of a prompt's images and videos in the order of their (single) placeholders:
-    ``(pixel_values, grids [[t, h, w], ...], time steps per item)``.  ``videos[i]`` is a list of frames or
-    ``{"frames": [...], "fps": f}``; a video's time step is its seconds per temporal grid step x
+    ``(pixel_values, grids [[t, h, w], ...], time steps per item)``.  ``videos[i]`` is a list of frames,
+    ``{"frames": [...], "fps": f}``, a file path or ``{"path": ..., "fps": sampling rate}``; a video's time step is its seconds per temporal grid step x
     ``tokens_per_second`` (``None`` for images)."""
     images, videos = list(images or []), list(videos or [])
     pv, grids, steps, ii, vi = [], [], [], 0, 0
@@ -139,7 +171,12 @@ def process_visuals(input_ids: List[int], images, videos, image_token_id: int, v
         elif video_token_id is not None and tok == video_token_id and vi < len(videos):
             v = videos[vi]
             vi += 1
-            frames, fps = (v["frames"], float(v.get("fps", 2.0))) if isinstance(v, dict) else (v, 2.0)
+            if isinstance(v, str) or (isinstance(v, dict) and "path" in v):
+                # a video file: decoded and sampled here
+                path, target = (v, 2.0) if isinstance(v, str) else (v["path"], float(v.get("fps", 2.0)))
+                frames, fps = load_video(path, target, int(v.get("max_frames", 768)) if isinstance(v, dict) else 768)
+            else:
+                frames, fps = (v["frames"], float(v.get("fps", 2.0))) if isinstance(v, dict) else (v, 2.0)
             p, g, sec = video_to_patches(frames, fps=fps, **{**kw, **(video_kw or {})})
             steps.append(sec * tokens_per_second)
         else:

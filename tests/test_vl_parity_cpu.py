@@ -366,3 +366,25 @@ def test_placeholder_tokens_in_a_response_are_text():
     pos, delta = mrope_positions(ids, [[1, 4, 4]], 1000, 2, video_token_id=1001)
     assert pos[0].tolist() == [0, 1, 1, 1, 1, 3, 4, 5, 6, 7, 8, 9] and pos[2].tolist() == [0, 1, 2, 1, 2, 3, 4, 5, 6, 7, 8, 9]
     assert delta == 10 - 12
+
+
+def test_video_file_is_decoded_and_sampled(tmp_path):
+    """A 12-frame clip at 8 frames per second sampled at 2 per second gives 3 frames (the first of every 4), and goes
+    through the prompt pipeline's item list like decoded frames do."""
+    cv2 = pytest.importorskip("cv2")
+    import numpy as np
+
+    from chatlearn_b200.data.vision_utils import load_video, process_visuals
+    path = str(tmp_path / "clip.avi")
+    wr = cv2.VideoWriter(path, cv2.VideoWriter_fourcc(*"MJPG"), 8.0, (84, 56))
+    if not wr.isOpened():
+        pytest.skip("this OpenCV build cannot write MJPG")
+    for i in range(12):
+        wr.write(np.full((56, 84, 3), 20 * i, dtype=np.uint8))
+    wr.release()
+    frames, rate = load_video(path, fps=2.0)
+    assert len(frames) == 3 and abs(rate - 2.0) < 1e-6 and frames[0].shape == (56, 84, 3)
+    levels = [int(f.mean()) for f in frames]
+    assert abs(levels[0] - 0) <= 3 and abs(levels[1] - 80) <= 3 and abs(levels[2] - 160) <= 3
+    pv, grids, steps = process_visuals([7, 1001, 8], [], [{"path": path, "fps": 2.0}], 1000, 1001, tokens_per_second=2.0)
+    assert grids == [[2, 4, 6]] and steps == [2.0] and pv.shape[0] == 48
