@@ -106,10 +106,6 @@ class FSDPModule(TorchModule):
             state_cls = ShardedTrainState
             if bool(getattr(self.module_args, "reshard_after_forward", False)):
                 from chatlearn_b200.parallel.fsdp2 import ReshardedTrainState
-                # (a trained tower with deep-stack taps would need the taps' gradients to cross segment boundaries)
-                assert self.vision is None or not (bool(getattr(self.module_args, "train_vision_tower", False))
-                                                   and "deepstack_visual_indexes" in (self.arch.vision_config or {})), \
-                    "parameter sharding with a trained vision tower is built for towers without deep-stack taps"
                 state_cls = ReshardedTrainState
             extra = {}
             if self.replica_group is not None:

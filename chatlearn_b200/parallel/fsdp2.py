@@ -370,17 +370,28 @@ class ReshardedTrainState(ShardedTrainState):
         if x is None:
             first = ["embed"] + (["vision"] if embed_fn is not None and "vision" in self.by_name else [])
             fn = embed_fn if embed_fn is not None else (lambda t: embed(m.block_by_name["embed"].params, t, ctx))
-            x = self._seg(first, lambda t: _as(m.dtype, fn(t)), (tokens,), grad)
+
+            def run_embed(t):
+                # deep-stack taps of a vision tower leave the segment as outputs (and enter their layers' segments
+                # as inputs), so that a trained tower receives their gradients across the segment boundaries
+                ctx.deepstack = None
+                h = _as(m.dtype, fn(t))
+                return (h,) + tuple(ctx.deepstack[1]) if ctx.deepstack is not None else h
+            x = self._seg(first, run_embed, (tokens,), grad)
+        taps = ()
+        if isinstance(x, (tuple, list)):
+            x, taps = x[0], tuple(x[1:])
         for l in range(*m.layer_range):
             names = [f"layer{l}"] + ([f"layer{l}.experts"] if f"layer{l}.experts" in m.block_by_name else [])
-            def run_layer(xx, l=l):
+            def run_layer(xx, tap=None, l=l):
                 xx = decoder_layer(arch, m.layer_params(l), xx, ctx, l)
-                if ctx.deepstack is not None and l < len(ctx.deepstack[1]):
+                if tap is None and ctx.deepstack is not None and l < len(ctx.deepstack[1]):
+                    tap = ctx.deepstack[1][l]
+                if tap is not None:
                     # vision features of tap l join the residual stream at the image rows (Qwen3-VL)
-                    rows, taps = ctx.deepstack
-                    xx = xx.index_add(0, rows, taps[l].to(xx.dtype))
+                    xx = xx.index_add(0, ctx.deepstack[0], tap.to(xx.dtype))
                 return xx
-            x = self._seg(names, run_layer, (x,), grad)
+            x = self._seg(names, run_layer, (x, taps[l]) if l < len(taps) else (x,), grad)
         head = ["head"] + (["embed"] if arch.tie_word_embeddings else [])
 
         def run_head(h, lab):

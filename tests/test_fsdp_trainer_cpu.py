@@ -91,7 +91,9 @@ def test_moe_matches_single(tmp_path, base_dir, name, world, env):
     ("vl3_ulysses2_trained_tower", 2, dict(PRESET="tiny_qwen3_vl", ULYSSES=2, TRAIN_TOWER=1)),
     # sharded parameters: the tower's output enters inside the first segment (embedding and tower blocks gathered)
     ("vl_resharded_trained_tower", 2, dict(PRESET="tiny_qwen2_5_vl", RESHARD=1, TRAIN_TOWER=1)),
-    ("vl3_resharded_ulysses2", 2, dict(PRESET="tiny_qwen3_vl", RESHARD=1, ULYSSES=2))])
+    ("vl3_resharded_ulysses2", 2, dict(PRESET="tiny_qwen3_vl", RESHARD=1, ULYSSES=2)),
+    # ... and the deep-stack taps of a trained tower cross the segment boundaries as outputs / inputs
+    ("vl3_resharded_trained_tower", 2, dict(PRESET="tiny_qwen3_vl", RESHARD=1, TRAIN_TOWER=1))])
 def test_vision_language_matches_single(tmp_path, base_dir, name, world, env):
     """Rows with image patches under Ulysses: embeddings and positions are built for the whole packed row, a rank
     keeps its rows of the embeddings and the whole positions (the attention runs on all rows of its heads)."""
