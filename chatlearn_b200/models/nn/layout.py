@@ -159,6 +159,8 @@ def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int
         if arch.q_lora_rank:
             out.append(_full(pre + "q_a_proj", (arch.q_lora_rank, H), a + "q_a_proj.weight"))
             out.append(_full(pre + "q_a_layernorm", (arch.q_lora_rank,), a + "q_a_layernorm.weight", "ones"))
+            # the compressed query feeds this rank's heads only: the gradients of the two are partial sums
+            out[-1].grad_sum_tp = out[-2].grad_sum_tp = tp > 1
             fs = (nh * qd, arch.q_lora_rank)
             out.append(Leaf(pre + "q_b_proj", (nh_l * qd, arch.q_lora_rank), "normal",
                             [_rows(a + "q_b_proj.weight", fs, tp_rank * nh_l * qd, nh_l * qd, 0)]))
@@ -169,6 +171,8 @@ def layer_leaves(arch: ModelArch, l: int, tp: int = 1, tp_rank: int = 0, ep: int
         out.append(_full(pre + "kv_a_proj_with_mqa", (arch.kv_lora_rank + arch.qk_rope_head_dim, H),
                          a + "kv_a_proj_with_mqa.weight"))
         out.append(_full(pre + "kv_a_layernorm", (arch.kv_lora_rank,), a + "kv_a_layernorm.weight", "ones"))
+        # the latent and the rotary key are shared by all heads, of which a rank sees its own: partial gradients
+        out[-1].grad_sum_tp = out[-2].grad_sum_tp = tp > 1
         kvd = arch.qk_nope_head_dim + arch.v_head_dim
         fs = (nh * kvd, arch.kv_lora_rank)
         out.append(Leaf(pre + "kv_b_proj", (nh_l * kvd, arch.kv_lora_rank), "normal",

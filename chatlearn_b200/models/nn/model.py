@@ -246,6 +246,9 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
         k_nope, v = kvb[..., :nope], kvb[..., nope:].contiguous()
         k = torch.cat([k_nope, k_rope.expand(T, nh_l, rp)], dim=-1)
         nkv_l = nh_l
+        if ctx.sp is not None and ctx.sp.size > 1:
+            # Ulysses: the rotary parts were rotated with this rank's positions; trade rows for heads
+            q, k, v = ctx.sp.seq_to_heads(q.contiguous()), ctx.sp.seq_to_heads(k.contiguous()), ctx.sp.seq_to_heads(v)
     else:
         paged = (ctx.kv is not None and not ctx.kv.prefill_only and ctx.mrope_positions is None and not torch.is_grad_enabled()
                  and (ctx.sp is None or ctx.sp.size == 1))
@@ -296,7 +299,7 @@ def attention_block(arch: ModelArch, p: Dict[str, torch.Tensor], x, ctx: FwdCtx,
         o = ctx.cp.attention(q, k, v, ctx, scale)
     else:
         o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, scale)
-    if ctx.sp is not None and ctx.sp.size > 1 and not arch.use_mla:
+    if ctx.sp is not None and ctx.sp.size > 1:
         o = ctx.sp.heads_to_seq(o)
     if partial:
         return ctx.tp_symm.gemm_partial(o.reshape(o.shape[0], -1), p["o_proj"])

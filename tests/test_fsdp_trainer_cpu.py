@@ -77,6 +77,8 @@ def test_dense_matches_single(tmp_path, base_dir, name, world, env):
 
 @pytest.mark.parametrize("name,world,env", [
     ("moe_ulysses2", 2, dict(PRESET="tiny_moe", ULYSSES=2)),
+    # latent attention: queries, (decompressed) keys and values trade rows for heads after the rotary parts were rotated
+    ("mla_ulysses2", 2, dict(PRESET="tiny_mla_moe", ULYSSES=2)),
     # Qwen3-Next: the convolution and the recurrence of the delta-net layers run per head over whole sequences
     ("hybrid_ulysses2", 2, dict(PRESET="tiny_qwen3_next", ULYSSES=2))])
 def test_moe_matches_single(tmp_path, base_dir, name, world, env):

@@ -121,3 +121,17 @@ def test_vision_language_parallel_matches_single(tmp_path, base_dir, name, world
     base = _base(base_dir, PRESET=preset, **{k: v for k, v in env.items() if k == "TRAIN_TOWER"})
     par = _run(tmp_path, name, world, PRESET=preset, **env)
     _compare(base, par, tol=5e-4, outliers=2)
+
+
+@pytest.mark.parametrize("name,world,env", [
+    ("tp2", 2, dict(TP=2)), ("cp2", 2, dict(CP=2)), ("tp2ep2", 4, dict(TP=2, EP=2)),
+    # compressed queries as well: their down-projection and norm feed this rank's heads only
+    ("tp2_q_lora", 2, dict(TP=2, ARCH_JSON='{"q_lora_rank": 24}'))])
+def test_latent_attention_parallel_matches_single(tmp_path, base_dir, name, world, env):
+    """DeepSeek-V3 / Moonlight layers: the latent, the rotary key and the compressed query are shared by all heads, of
+    which a tensor-parallel rank sees its own, so the gradients of those projections and norms are summed over the
+    group."""
+    benv = dict(PRESET="tiny_mla_moe", NOAUX=1, **{k: v for k, v in env.items() if k == "ARCH_JSON"})
+    base = _base(base_dir, **benv)
+    par = _run(tmp_path, name, world, **benv, **{k: v for k, v in env.items() if k != "ARCH_JSON"})
+    _compare(base, par, outliers=2)
