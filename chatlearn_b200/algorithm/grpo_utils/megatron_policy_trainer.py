@@ -199,7 +199,9 @@ class MegatronPolicyTrainer(MegatronModule):
                 lp_full, batch.old_logprobs, batch.advantages, batch.seq_ids, len(batch.seq_lens),
                 batch.loss_mask, ma.pos_clip_ratio, ma.neg_clip_ratio, ma.diff_clip_ratio, ma.final_clip_ratio)
             m = batch.loss_mask
-            total = (loss_tok * m).sum() / max(self.cp_size, 1)   # every CP rank holds the full row
+            # every CP rank evaluates the loss of the full row, and the backward of the gather hands each rank the
+            # gradient of its own rows only: the sum over the ranks' rows is the full gradient, once
+            total = (loss_tok * m).sum()
             stats = torch.stack([(loss_tok.detach() * m).sum(), torch.zeros((), device=self.device),
                                  torch.zeros((), device=self.device), (cpos.float() * m).sum(),
                                  (cneg.float() * m).sum(), m.sum()]) / max(self.cp_size, 1)
@@ -427,7 +429,19 @@ class MegatronPolicyTrainer(MegatronModule):
                 req.wait()
         assert not acts and not grads and not saved
 
+    def _sum_tied_embedding_grads(self, st):
+        """Tied input / output embeddings under pipeline parallelism: the first stage holds the matrix for the
+        look-up, the last stage a copy for the output head.  Their gradients are exchanged and added, so both copies
+        take the same step (the reference leaves this to Megatron's embedding-gradient all-reduce between the two
+        stages)."""
+        if self.pp_size == 1 or not self.model.arch.tie_word_embeddings or not (self.is_first_stage or self.is_last_stage):
+            return
+        s = next(x for x in st.states if x.block.name == "embed")
+        other = self.pp_size - 1 if self.is_first_stage else 0
+        s.grad.add_(self._exchange(s.grad, other, s.grad.shape, s.grad.dtype, other))
+
     def _finish_train_step(self, st, stats):
+        self._sum_tied_embedding_grads(st)
         grad_norm = st.step()
         # metrics live on the last stage; share them with the whole model-parallel group
         if self.pp_size > 1:

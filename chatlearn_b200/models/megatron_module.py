@@ -223,6 +223,9 @@ class MegatronModule(FSDPModule):
                 weight_decay=oc.weight_decay, clip_grad=oc.clip_grad, extra_norm_groups=extra,
                 tp_size=self.tp_size, ep_group=self.ep_group if self.ep_size > 1 else None,
                 tp_group=self.tp_group if self.tp_size > 1 else None)
+            if self.pp_size > 1 and self.arch.tie_word_embeddings:
+                # the first and the last stage hold copies of the tied embedding: half of its squared norm each
+                self.state.block_norm_weight["embed"] = 0.5
 
     # ------------------------------------------------------------------ checkpoints (Megatron layout)
     def checkpoint_dir(self, iteration: int) -> str:

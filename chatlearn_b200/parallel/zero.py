@@ -63,6 +63,9 @@ class ShardedTrainState:
         # in the other shard groups form ``replica_group`` and sum their gradient shards after the reduce-scatter,
         # so parameters are gathered inside the shard group only
         self.replica = replica_group if (replica_group is not None and replica_group.size > 1) else None
+        # weight of a block's squared gradient norm in the global norm: below 1 for a block of which several
+        # pipeline stages hold copies (tied embeddings on the first and the last stage)
+        self.block_norm_weight: Dict[str, float] = {}
         self.tp_size, self.ep_group, self.tp_group = tp_size, ep_group, tp_group
         # expert tensor parallelism: the expert leaves of the tensor-parallel ranks are different slices
         self.expert_tp_sharded = getattr(model, "etp", 1) > 1
@@ -173,8 +176,9 @@ class ShardedTrainState:
         cached = getattr(s, "_norm_ranges", None)
         if cached is not None:
             return cached
+        share = self.block_norm_weight.get(s.block.name, 1.0)     # a block that several pipeline stages hold
         if self.tp_size == 1:
-            out = [(0, s.shard_numel, 1.0)]
+            out = [(0, s.shard_numel, share)]
         else:
             out = []
             for lf in s.block.leaves:
@@ -187,14 +191,14 @@ class ShardedTrainState:
                     rep = not own and not self.expert_tp_sharded
                 else:
                     rep = lf.replicated
-                w = 1.0 / self.tp_size if rep else 1.0
+                w = (1.0 / self.tp_size if rep else 1.0) * share
                 pieces = [(o, o + lf.numel, w)]
                 kv = getattr(lf, "grad_sum_kv", None)
                 if kv is not None:
                     # rows of key/value heads that tp / heads ranks hold: counted once per head
                     cols = lf.matrix_shape[1]
                     k0, k1 = o + kv[0] * cols, o + (kv[0] + kv[1]) * cols
-                    pieces = [(o, k0, w), (k0, k1, kv[3] / self.tp_size), (k1, o + lf.numel, w)]
+                    pieces = [(o, k0, w), (k0, k1, share * kv[3] / self.tp_size), (k1, o + lf.numel, w)]
                 for p0, p1, pw in pieces:
                     a, b = max(p0, s.lo), min(p1, s.hi)
                     if b <= a:

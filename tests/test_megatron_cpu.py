@@ -69,6 +69,10 @@ def _compare(a, b, tol=5e-4, outliers=0):
     ("cp2", 2, dict(CP=2)),
     ("dp2", 2, dict()),
     ("tp2_gspo", 2, dict(TP=2, GSPO=1)),
+    ("cp2_gspo", 2, dict(CP=2, GSPO=1)),         # sequence-level ratios need every rank's rows of a sequence
+    # tied input / output embeddings: the first and the last stage hold copies and exchange their gradients
+    ("pp2_tied", 2, dict(PP=2, ARCH_JSON='{"tie_word_embeddings": true}')),
+    ("tp2pp2_tied", 4, dict(TP=2, PP=2, ARCH_JSON='{"tie_word_embeddings": true}')),
     # two model chunks per stage, interleaved one-forward-one-backward over a global time table
     ("pp2vpp2", 2, dict(PP=2, VPP=2, LAYERS=4)),
     # ... and with four of the six layers on the first stage: chunks of two layers there, of one layer on the second
@@ -77,7 +81,7 @@ def _compare(a, b, tol=5e-4, outliers=0):
     ("tp4_replicated_kv_heads", 4, dict(TP=4)),
 ])
 def test_dense_parallel_matches_single(tmp_path, base_dir, name, world, env):
-    base_env = {k: v for k, v in env.items() if k in ("GSPO", "LAYERS")}
+    base_env = {k: v for k, v in env.items() if k in ("GSPO", "LAYERS", "ARCH_JSON")}
     base = _base(base_dir, **base_env)
     par = _run(tmp_path, name, world, **env)
     _compare(base, par)
