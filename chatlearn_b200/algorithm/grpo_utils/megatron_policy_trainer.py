@@ -58,11 +58,17 @@ class MegatronPolicyTrainer(MegatronModule):
         ctx = FwdCtx(positions=batch.positions, cu_seqlens=batch.cu_seqlens, max_seqlen=batch.max_seqlen,
                      tp=self.tp_group if self.tp_size > 1 else None, ep=self.ep, seq_parallel=self.seq_parallel)
         local = None
+        valid = batch.valid
         if cp > 1:
             plan = self.cp.plan(batch.seq_lens, self.device)
             local = plan["local"]
             ctx.cp, ctx.cp_plan = self.cp, plan
             ctx.positions = batch.positions.index_select(0, local)
+            valid = valid.index_select(0, local) if valid is not None else None
+        if valid is not None and self.seq_parallel and self.tp_size > 1:
+            n = valid.shape[0] // self.tp_size                     # this tensor-parallel rank's rows
+            valid = valid.narrow(0, self.tp_rank * n, n)
+        ctx.row_valid = valid
         return batch, ctx, local
 
     # ------------------------------------------------------------------ pipeline plumbing

@@ -80,9 +80,11 @@ class PolicyTrainer(FSDPModule):
         ctx = FwdCtx(positions=positions, cu_seqlens=batch.cu_seqlens, max_seqlen=batch.max_seqlen,
                      fuse_add_norm=not torch.is_grad_enabled())
         labels = batch.labels
+        ctx.row_valid = batch.valid
         if self.sp is not None:
             ctx.sp = self.sp
             ctx.attn_positions = positions
+            ctx.row_valid = self.sp.split(batch.valid) if batch.valid is not None else None
             tokens = self.sp.split(tokens)
             labels = self.sp.split(labels)
             ctx.positions = self.sp.split(positions)

@@ -50,6 +50,7 @@ class PackedBatch:
     values: Optional[torch.Tensor] = None         # [T] value estimates at rollout time (PPO critic)
     returns: Optional[torch.Tensor] = None        # [T] value targets
     pad: int = 0                                  # trailing pad tokens (SP/CP alignment)
+    valid: Optional[torch.Tensor] = None          # [T] bool: a token of a sample (not alignment padding)
     mm: Any = None                                # per sample (pixel_values, image_grid_thw, visual_time_steps) or None (vision-language)
 
     def to(self, device):
@@ -86,7 +87,7 @@ def pack_samples(samples: List[Dict[str, Any]], pad_multiple: int = 1, seq_multi
     ``seq_multiple`` pads every sequence (context parallel needs multiples of
     ``2·cp``); ``pad_multiple`` pads the row (Ulysses needs a multiple of ``sp``).
     Padding tokens carry loss mask 0 and form their own attention segment."""
-    toks, pos, lab, mask, sid, seq_lens = [], [], [], [], [], []
+    toks, pos, lab, mask, sid, seq_lens, valid = [], [], [], [], [], [], []
     old, ref, adv = [], [], []
     have_old = all("old_logprobs" in s for s in samples)
     have_ref = all("ref_logprobs" in s for s in samples)
@@ -115,6 +116,7 @@ def pack_samples(samples: List[Dict[str, Any]], pad_multiple: int = 1, seq_multi
             m[pl - 1:n - 1] = 1.0
         mask.append(m)
         sid.append(torch.full((L,), i, dtype=torch.long))
+        valid.append(torch.arange(L) < n)
         seq_lens.append(L)
         if have_old:
             old.append(torch.nn.functional.pad(_per_token(s["old_logprobs"], pl, n), (0, n_pad)))
@@ -138,6 +140,7 @@ def pack_samples(samples: List[Dict[str, Any]], pad_multiple: int = 1, seq_multi
         lab.append(torch.zeros(pad, dtype=torch.long))
         mask.append(torch.zeros(pad))
         sid.append(torch.full((pad,), len(samples), dtype=torch.long))
+        valid.append(torch.zeros(pad, dtype=torch.bool))
         seq_lens.append(pad)
         for lst in (old, ref, adv, vals, rets):
             if lst:
@@ -149,7 +152,7 @@ def pack_samples(samples: List[Dict[str, Any]], pad_multiple: int = 1, seq_multi
                        loss_mask=torch.cat(mask), seq_ids=torch.cat(sid), cu_seqlens=cu,
                        seq_lens=seq_lens, max_seqlen=max(seq_lens),
                        sample_ids=[int(s.get("id_in_list", i)) for i, s in enumerate(samples)],
-                       old_logprobs=cat(old), ref_logprobs=cat(ref), advantages=cat(adv), values=cat(vals or []), returns=cat(rets or []), pad=pad,
+                       old_logprobs=cat(old), ref_logprobs=cat(ref), advantages=cat(adv), values=cat(vals or []), returns=cat(rets or []), pad=pad, valid=torch.cat(valid) if valid else None,
                        mm=[(s.get("pixel_values"), s.get("image_grid_thw"), s.get("visual_time_steps")) for s in samples]
                        if any(s.get("pixel_values") is not None for s in samples) else None)
 

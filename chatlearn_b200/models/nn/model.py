@@ -162,6 +162,7 @@ class FwdCtx:
     mrope_positions: Optional[torch.Tensor] = None   # [3, T] time/row/column positions (vision-language models)
     deepstack: Any = None                  # (rows, [features per early layer]): vision taps added after layer i (Qwen3-VL)
     seq_parallel: bool = False             # residual stream and norms hold 1/tp of the rows (Megatron sequence parallelism)
+    row_valid: Optional[torch.Tensor] = None   # [rows] bool: False for alignment padding (kept out of the balancing loss)
 
 
 def _tp_reduce(x, ctx):
@@ -329,14 +330,45 @@ def dense_mlp(p, x, ctx, prefix="", partial: bool = False, reduce: bool = False)
     return ops.linear(h, p[prefix + "down_proj"])
 
 
+def _router_aux_loss(arch: ModelArch, scores, idx, ctx: FwdCtx):
+    """Load-balancing loss E · Σ_e f_e · P_e of one layer over the rows of the micro-batch.  Where the rows of a
+    micro-batch are split over ranks (sequence-parallel tensor ranks, context-parallel ranks, Ulysses ranks) the
+    routed fractions f and the mean probabilities P are those of all the rows: the counts are summed over the groups,
+    the probability sums too, with the gradient passing to this rank's rows only (every rank adds the same loss value
+    and back-propagates its own rows' share, so the ranks together apply the loss once)."""
+    E, k = arch.num_experts, arch.num_experts_per_tok
+    groups = []
+    if ctx.seq_parallel and ctx.tp is not None and ctx.tp.size > 1:
+        groups.append(ctx.tp)
+    if ctx.cp is not None and ctx.cp.size > 1:
+        groups.append(ctx.cp.group)
+    if ctx.sp is not None and ctx.sp.size > 1:
+        groups.append(ctx.sp.group)
+    valid = ctx.row_valid
+    if valid is not None and valid.shape[0] != scores.shape[0]:
+        valid = None
+    if not groups and valid is None:
+        return ops.moe_aux_loss(scores, idx, E, k)
+    w = torch.ones(scores.shape[0], device=scores.device) if valid is None else valid.to(torch.float32)
+    f = torch.zeros(E, device=scores.device, dtype=torch.float32)
+    f.index_add_(0, idx.reshape(-1), w.repeat_interleave(idx.shape[1]))
+    P = (scores.float() * w[:, None]).sum(0)
+    rows = w.sum()
+    for g in groups:
+        g.all_reduce_(f)
+        g.all_reduce_(rows)
+        P = g.all_reduce(P)
+    rows = rows.clamp_min(1.0)
+    return E * ((f / (rows * k)) * (P / rows)).sum()
+
+
 def moe_block(arch: ModelArch, p, x, ctx: FwdCtx):
     logits = ops.linear(x.float(), p["router"].float())
     w, idx, scores = ops.moe_router(logits, arch.num_experts_per_tok, arch.scoring_func,
                                     arch.norm_topk_prob, p.get("router_bias"), arch.n_group,
                                     arch.topk_group, arch.routed_scaling_factor)
     if arch.router_aux_loss_coef > 0 and torch.is_grad_enabled():
-        ctx.aux_losses.append(arch.router_aux_loss_coef *
-                              ops.moe_aux_loss(scores, idx, arch.num_experts, arch.num_experts_per_tok))
+        ctx.aux_losses.append(arch.router_aux_loss_coef * _router_aux_loss(arch, scores, idx, ctx))
     if p["w13"].shape[1] != 2 * arch.moe_intermediate_size:
         # expert tensor parallelism (= the TP group): every rank holds 1/tp of each expert's hidden width and
         # sees the same tokens, so its expert output is a partial sum; inputs and routing weights get their

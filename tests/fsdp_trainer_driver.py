@@ -27,7 +27,8 @@ if rank == 0 and not os.path.exists(os.path.join(hf_dir, "done")):
     a0 = PRESETS[preset]()
     for k, v in json.loads(os.environ.get("ARCH_JSON", "{}")).items():
         setattr(a0, k, v)
-    a0.router_aux_loss_coef = 0.0          # the balancing loss depends on how tokens are grouped into micro-batches
+    if os.environ.get("AUX", "0") != "1":
+        a0.router_aux_loss_coef = 0.0      # the balancing loss depends on how tokens are grouped into micro-batches
     m = CausalLM(a0, dtype=torch.float32).init_weights(7, std=0.05)
     save_hf_checkpoint(m, hf_dir, dtype=torch.float32)
     open(os.path.join(hf_dir, "done"), "w").close()

@@ -77,12 +77,13 @@ def test_dense_matches_single(tmp_path, base_dir, name, world, env):
 
 @pytest.mark.parametrize("name,world,env", [
     ("moe_ulysses2", 2, dict(PRESET="tiny_moe", ULYSSES=2)),
+    ("moe_ulysses2_balancing_loss", 2, dict(PRESET="tiny_moe", ULYSSES=2, AUX=1)),   # statistics over both ranks' rows
     # latent attention: queries, (decompressed) keys and values trade rows for heads after the rotary parts were rotated
     ("mla_ulysses2", 2, dict(PRESET="tiny_mla_moe", ULYSSES=2)),
     # Qwen3-Next: the convolution and the recurrence of the delta-net layers run per head over whole sequences
     ("hybrid_ulysses2", 2, dict(PRESET="tiny_qwen3_next", ULYSSES=2))])
 def test_moe_matches_single(tmp_path, base_dir, name, world, env):
-    base = _base(base_dir, PRESET=env["PRESET"])
+    base = _base(base_dir, **{k: v for k, v in env.items() if k in ("PRESET", "AUX")})
     par = _run(tmp_path, name, world, **env)
     _compare(base, par)
 

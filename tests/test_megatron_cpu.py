@@ -139,3 +139,13 @@ def test_latent_attention_parallel_matches_single(tmp_path, base_dir, name, worl
     base = _base(base_dir, **benv)
     par = _run(tmp_path, name, world, **benv, **{k: v for k, v in env.items() if k != "ARCH_JSON"})
     _compare(base, par, outliers=2)
+
+
+@pytest.mark.parametrize("name,world,env", [("tp2", 2, dict(TP=2)), ("cp2", 2, dict(CP=2))])
+def test_balancing_loss_covers_all_rows_of_a_micro_batch(tmp_path, base_dir, name, world, env):
+    """Router load-balancing loss switched on: where the rows of a micro-batch are split over sequence-parallel or
+    context-parallel ranks, the routed fractions and mean probabilities are those of all its rows (alignment padding
+    left out), and the ranks together apply the loss once."""
+    base = _base(base_dir, PRESET="tiny_moe")
+    par = _run(tmp_path, name, world, PRESET="tiny_moe", **env)
+    _compare(base, par, outliers=2)
