@@ -114,6 +114,7 @@ class PolicyTrainer(FSDPModule):
 
     def _logprobs(self, batch, need_entropy: bool):
         tokens, labels, ctx = self._ctx_and_inputs(batch)
+        ctx.aux_weight = getattr(self, "_aux_scale", None)
         if self.resharded:
             # parameter-sharded mode: every block is gathered only while its segment runs, and a segment's
             # activations are recomputed in its backward (which is also where its parameters are re-gathered)
@@ -200,6 +201,7 @@ class PolicyTrainer(FSDPModule):
                     st.join_empty_microbatch()
                 continue
             batch = pack_samples(mb, pad_multiple=pad)
+            self._aux_scale = float(batch.loss_mask.sum()) * inv_norm      # weight of the router losses (below)
             lp, ent, ctx = self._logprobs(batch, need_entropy=True)
             if ma.use_group_sequence_policy:
                 loss, s = ops.gspo_loss_fused(

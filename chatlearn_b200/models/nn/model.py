@@ -154,6 +154,7 @@ class FwdCtx:
     attn_positions: Optional[torch.Tensor] = None  # positions of the rows attention sees (Ulysses)
     cp_plan: Optional[Dict[str, Any]] = None       # ContextParallel.plan() of this packed row
     aux_losses: List[torch.Tensor] = field(default_factory=list)
+    aux_weight: Any = None                 # weight of the auxiliary losses in the objective (segment-wise backward passes)
     moe_stats: List[torch.Tensor] = field(default_factory=list)
     tp_symm: Any = None                    # parallel.symm_collectives.SymmGroup of the TP group (inference)
     pending: Any = None                    # sub-layer output (or un-reduced TP partial) not yet added to the residual stream

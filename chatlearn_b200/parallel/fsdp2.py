@@ -367,6 +367,7 @@ class ReshardedTrainState(ShardedTrainState):
         m = self.model
         arch = m.arch
         grad = torch.is_grad_enabled()
+        self._fwd_ctx = ctx                # (the segments' backward passes find the auxiliary-loss weight here)
         if x is None:
             first = ["embed"] + (["vision"] if embed_fn is not None and "vision" in self.by_name else [])
             fn = embed_fn if embed_fn is not None else (lambda t: embed(m.block_by_name["embed"].params, t, ctx))
@@ -436,10 +437,19 @@ class _Segment(torch.autograd.Function):
         state, names = ctx.state, ctx.names
         inputs = [t.detach().requires_grad_(t.is_floating_point()) for t in ctx.saved_tensors]
         state.gather(names, with_grad=True, prefetch=state._neighbour(names[0], -1))
+        fc = getattr(state, "_fwd_ctx", None)
+        n_aux = len(fc.aux_losses) if fc is not None else 0
         with torch.enable_grad():
             out = ctx.run(*inputs)
         outs = out if isinstance(out, (tuple, list)) else (out,)
         pairs = [(o, g) for o, g in zip(outs, grads) if g is not None and o.requires_grad]
+        if fc is not None and len(fc.aux_losses) > n_aux:
+            # auxiliary (router balancing) losses of this segment: the forward ran without a tape, so they are
+            # back-propagated here, from the re-run, with their weight in the objective
+            aux, w = fc.aux_losses[n_aux:], fc.aux_weight
+            del fc.aux_losses[n_aux:]
+            if w is not None:
+                pairs += [(a, torch.as_tensor(w, dtype=a.dtype, device=a.device)) for a in aux if a.requires_grad]
         if pairs:
             torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
         state.release(names, reduce_grads=True)

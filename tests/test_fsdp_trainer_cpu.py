@@ -78,6 +78,9 @@ def test_dense_matches_single(tmp_path, base_dir, name, world, env):
 @pytest.mark.parametrize("name,world,env", [
     ("moe_ulysses2", 2, dict(PRESET="tiny_moe", ULYSSES=2)),
     ("moe_ulysses2_balancing_loss", 2, dict(PRESET="tiny_moe", ULYSSES=2, AUX=1)),   # statistics over both ranks' rows
+    # sharded parameters: the segments' forward runs without a tape, the balancing losses are back-propagated from
+    # the re-run inside each segment's backward
+    ("moe_resharded_ulysses2_balancing_loss", 2, dict(PRESET="tiny_moe", ULYSSES=2, RESHARD=1, AUX=1)),
     # latent attention: queries, (decompressed) keys and values trade rows for heads after the rotary parts were rotated
     ("mla_ulysses2", 2, dict(PRESET="tiny_mla_moe", ULYSSES=2)),
     # Qwen3-Next: the convolution and the recurrence of the delta-net layers run per head over whole sequences
