@@ -61,13 +61,11 @@ def _compare(a, b, tol=5e-4, outliers=2):
 @pytest.mark.parametrize("name,world,env", [
     ("dp2", 2, dict()),
     ("ulysses2", 2, dict(ULYSSES=2)),                    # every packed row split over the two ranks
-    ("ulysses2_dp2", 4, dict(ULYSSES=2)),
     ("ulysses2_gspo", 2, dict(ULYSSES=2, GSPO=1)),
     ("ulysses2_resharded", 2, dict(ULYSSES=2, RESHARD=1)),
     ("ulysses4_replicated_kv_heads", 4, dict(ULYSSES=4)),   # four ranks, two key/value heads
-    # hybrid sharding: two shard groups of two ranks, whole parameters and sharded parameters
-    ("hsdp2x2", 4, dict(FSDP=2)), ("hsdp2x2_resharded", 4, dict(FSDP=2, RESHARD=1)),
-    ("dp2_resharded", 2, dict(RESHARD=1)),
+    # hybrid sharding: two shard groups of two ranks with sharded parameters
+    ("hsdp2x2_resharded", 4, dict(FSDP=2, RESHARD=1)),
 ])
 def test_dense_matches_single(tmp_path, base_dir, name, world, env):
     base = _base(base_dir, **{k: v for k, v in env.items() if k == "GSPO"})

@@ -112,11 +112,11 @@ def test_hybrid_parallel_matches_single(tmp_path, base_dir, name, world, env):
 
 
 @pytest.mark.parametrize("name,world,env", [
-    ("cp2", 2, dict(CP=2)), ("tp2", 2, dict(TP=2)), ("pp2", 2, dict(PP=2)), ("tp2_no_seq_par", 2, dict(TP=2, SEQ_PAR=0)),
+    ("cp2", 2, dict(CP=2)), ("tp2", 2, dict(TP=2)), ("pp2", 2, dict(PP=2)),
     # sequence-parallel rows and a context-parallel slice at once, with the tower's weights trained
     ("tp2cp2_trained_tower", 4, dict(TP=2, CP=2, TRAIN_TOWER=1)),
     # Qwen3-VL: the tower's deep-stack taps are added to the first layers at the image rows this rank holds
-    ("deepstack_cp2", 2, dict(CP=2, PRESET="tiny_qwen3_vl")), ("deepstack_tp2", 2, dict(TP=2, PRESET="tiny_qwen3_vl"))])
+    ("deepstack_cp2", 2, dict(CP=2, PRESET="tiny_qwen3_vl"))])
 def test_vision_language_parallel_matches_single(tmp_path, base_dir, name, world, env):
     """Rows with image patches: the tower's embeddings and the (time, row, column) positions are built for the whole
     packed row; a context-parallel rank keeps its zig-zag slice of both, later pipeline stages only the positions."""
