@@ -64,7 +64,7 @@ class VLCausalLM:
             vis = tokens == self.arch.image_token_id
             if self.arch.video_token_id is not None:
                 vis = vis | (tokens == self.arch.video_token_id)
-            rows = vis.nonzero(as_tuple=True)[0]
+            rows = vis.nonzero(as_tuple=True)[0][:img.shape[0]]     # (placeholder ids generated later on are text)
             assert rows.numel() == img.shape[0], f"{rows.numel()} image / video placeholder tokens but {img.shape[0]} embeddings"
             x = x.index_put((rows,), img.to(x.dtype))
             if taps:
